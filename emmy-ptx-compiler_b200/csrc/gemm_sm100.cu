@@ -1,0 +1,387 @@
+// Dense contraction C[M,N] = epilogue(A[M,K] . B), fp16 / bf16 operands, fp32 accumulation.
+//
+// The reference builds this from per-warp m16n8k16 `mma.sync` cells fed through registers by
+// `ldmatrix` / `cp.async` (emmyptx/mma.py:65-242, emmyptx/kernel.py:735-755) inside a rotated K loop
+// (emmyptx/loops.py:231-264), converts with `cvt.rn` and stores two elements at a time, and
+// refuses fused store epilogues (emmyptx/mma.py:201-203). This file is the sm_100a form:
+//
+//   * persistent CTAs, one per SM, walking 128 x BN output tiles in an order that keeps a band
+//     of A row-blocks hot in L2;
+//   * warp 0 (one thread) streams 128x64 A tiles and 64xBN B tiles into a ring of
+//     128-byte-swizzled shared-memory stages with TMA, out-of-range parts zero-filled, so
+//     ragged M, N, K need no guards in the main loop;
+//   * warp 1 (one thread) issues tcgen05.mma 128 x BN x 16 from shared-memory descriptors into
+//     one of two accumulator buffers in tensor memory, and releases stages / publishes
+//     accumulators with tcgen05.commit;
+//   * warps 2-5 drain the other accumulator buffer (tcgen05.ld), apply the epilogue on the fp32
+//     values, round once to the output type and store 16-byte vectors, overlapping the next
+//     tile's main loop.
+//
+// B may be row-major K x N (an "MN-major" operand: TMA boxes of 64 N-elements per K row, and
+// the MMA told to transpose) or row-major N x K (K-major, like A).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace emmy {
+
+constexpr int kBM = 128, kBK = 64, kUmmaK = 16;
+constexpr int kGemmThreads = 192;
+constexpr int kEpiWarp0 = 2;
+
+template <int BN>
+struct GemmSmem {
+    static constexpr int kABytes = kBM * kBK * 2;
+    static constexpr int kBBytes = BN * kBK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = (BN == 256) ? 4 : (BN == 192 ? 5 : 6);
+    static constexpr int kBarrierBytes = 256;
+    static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;   // + alignment slack
+};
+
+struct GemmParams {
+    void* C;
+    int64_t ldc;
+    int M, N, K;
+    int m_blocks, n_blocks;
+    uint32_t* status;
+};
+
+__device__ uint32_t g_gemm_status;
+
+// Tile order: bands of 16 row-blocks, column-blocks inside a band, row-blocks fastest, so CTAs that
+// run together share B column-blocks and a small set of A row-blocks.
+__device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, int& mb, int& nb) {
+    constexpr int kBand = 16;
+    const int per_band = kBand * n_blocks;
+    const int band = t / per_band;
+    const int first = band * kBand;
+    const int rows = min(kBand, m_blocks - first);
+    const int within = t - band * per_band;
+    mb = first + within % rows;
+    nb = within / rows;
+}
+
+// x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3): algebraically the tanh form of GELU, with no
+// cancellation for large negative x. ex2 / rcp approximations: relative error around 1e-6, far
+// below the one rounding to a 16-bit type that follows.
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+    const float u = 0.7978845608f * fmaf(0.044715f * x * x, x, x);
+    const float e = ptx::ex2_approx(-2.8853900818f * u);       // exp(-2u) = 2^(-2 log2(e) u)
+    return x * ptx::rcp_approx(1.0f + e);
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    if constexpr (BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    } else {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+}
+
+template <bool BF16>
+__device__ __forceinline__ void store_scalar(void* C, int64_t off, float v) {
+    if constexpr (BF16) reinterpret_cast<__nv_bfloat16*>(C)[off] = __float2bfloat16_rn(v);
+    else reinterpret_cast<__half*>(C)[off] = __float2half_rn(v);
+}
+
+template <int BN, bool BF16, int EPI, bool B_NK>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+    using S = GemmSmem<BN>;
+    constexpr int kStages = S::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + kStages * S::kStageBytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
+    auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 2 + s); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages * S::kStageBytes + 8 * (2 * kStages + 4));
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = (p.K + kBK - 1) / kBK;
+    const int tiles = p.m_blocks * p.n_blocks;
+    const WaitCtx wctx{abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < 2; ++s) { ptx::mbar_init(acc_full_bar(s), 1); ptx::mbar_init(acc_empty_bar(s), 4); }
+        *abort_flag = 0;
+        ptx::mbar_fence_init();
+        ptx::prefetch_tensormap(&map_a);
+        ptx::prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), 512);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer ---------------------------------------------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                int mb, nb;
+                tile_coords(t, p.m_blocks, p.n_blocks, mb, nb);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!(ok = bounded_wait(wctx, empty_bar(s), ph ^ 1, 0x01010000u | s))) break;
+                    const uint32_t a_dst = smem_base + s * S::kStageBytes;
+                    const uint32_t b_dst = a_dst + S::kABytes;
+                    ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
+                    ptx::tma_load_2d(a_dst, &map_a, full_bar(s), kb * kBK, mb * kBM);
+                    if constexpr (B_NK) {
+                        ptx::tma_load_2d(b_dst, &map_b, full_bar(s), kb * kBK, nb * BN);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            ptx::tma_load_2d(b_dst + j * (kBK * 128), &map_b, full_bar(s), nb * BN + j * 64, kb * kBK);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---- MMA issuer -----------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::mma_idesc_f16(BF16, false, !B_NK, kBM, BN);
+            uint32_t it = 0, acc_it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++acc_it) {
+                const int as = acc_it & 1;
+                const uint32_t aph = (acc_it >> 1) & 1;
+                if (!(ok = bounded_wait(wctx, acc_empty_bar(as), aph ^ 1, 0x01020000u | as))) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + as * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!(ok = bounded_wait(wctx, full_bar(s), ph, 0x01030000u | s))) break;
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_src = smem_base + s * S::kStageBytes;
+                    const uint32_t b_src = a_src + S::kABytes;
+#pragma unroll
+                    for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+                        const uint64_t a_desc = ptx::smem_desc_sw128(a_src + kk * (kUmmaK * 2), 16, 1024);
+                        const uint64_t b_desc = B_NK ? ptx::smem_desc_sw128(b_src + kk * (kUmmaK * 2), 16, 1024)
+                                                     : ptx::smem_desc_sw128(b_src + kk * (kUmmaK * 128), kBK * 128, 1024);
+                        ptx::mma_ss(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0);
+                    }
+                    ptx::mma_commit(empty_bar(s));
+                }
+                if (ok) ptx::mma_commit(acc_full_bar(as));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---- epilogue: 4 warps, warp w owns tensor-memory lanes 32 (w % 4) .. +32 -----------------
+        const int quarter = warp & 3;
+        uint32_t acc_it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++acc_it) {
+            int mb, nb;
+            tile_coords(t, p.m_blocks, p.n_blocks, mb, nb);
+            const int as = acc_it & 1;
+            const uint32_t aph = (acc_it >> 1) & 1;
+            if (!(ok = bounded_wait(wctx, acc_full_bar(as), aph, 0x01040000u | as))) break;
+            ptx::tc_fence_after_sync();
+            const int row = mb * kBM + quarter * 32 + lane;
+            const int64_t row_off = (int64_t)row * p.ldc;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(t_row + c, r);
+                ptx::tmem_ld_wait();
+                const int col0 = nb * BN + c;
+                if (row < p.M && col0 < p.N) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float f = __uint_as_float(r[j]);
+                        v[j] = (EPI == EMMYB200_EPI_GELU_TANH) ? gelu_tanh_fast(f) : f;
+                    }
+                    if (col0 + 32 <= p.N) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 o;
+                            o.x = pack2<BF16>(v[8 * q + 0], v[8 * q + 1]);
+                            o.y = pack2<BF16>(v[8 * q + 2], v[8 * q + 3]);
+                            o.z = pack2<BF16>(v[8 * q + 4], v[8 * q + 5]);
+                            o.w = pack2<BF16>(v[8 * q + 6], v[8 * q + 7]);
+                            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.C) + row_off + col0 + 8 * q) = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < p.N; ++j) store_scalar<BF16>(p.C, row_off + col0 + j, v[j]);
+                    }
+                }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(acc_empty_bar(as));
+        }
+    }
+
+    // ---- teardown -------------------------------------------------------------------------------
+    if (*abort_flag) {                          // give copies still in flight time to land
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- host -----------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+int make_tensor_map_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                       uint32_t box_rows, uint32_t box_cols) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return fail(EMMYB200_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(EMMYB200_ERR_ARG, "cuTensorMapEncodeTiled (2-D %llu x %llu, ld %llu) failed: %d",
+                                       (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld, (int)r);
+    return EMMYB200_OK;
+}
+
+int make_tensor_map_3d(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
+                       uint32_t box_rows, uint32_t box_cols) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return fail(EMMYB200_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {cols, rows, planes};
+    cuuint64_t strides[2] = {cols * 2, rows * cols * 2};
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(EMMYB200_ERR_ARG, "cuTensorMapEncodeTiled (3-D) failed: %d", (int)r);
+    return EMMYB200_OK;
+}
+
+int check_sm100() {
+    int dev = 0, major = 0;
+    EMMY_CUDA(cudaGetDevice(&dev));
+    EMMY_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) return fail(EMMYB200_ERR_DEVICE, "device %d has compute capability %d.x; these kernels are sm_100a only", dev, major);
+    return EMMYB200_OK;
+}
+
+int gemm_read_status(uint32_t* out) {
+    uint32_t zero = 0;
+    EMMY_CUDA(cudaDeviceSynchronize());
+    EMMY_CUDA(cudaMemcpyFromSymbol(out, g_gemm_status, sizeof(uint32_t)));
+    if (*out) EMMY_CUDA(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(uint32_t)));
+    return EMMYB200_OK;
+}
+
+template <int BN, bool BF16, int EPI, bool B_NK>
+static int launch_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                       int64_t ldc, cudaStream_t stream) {
+    using S = GemmSmem<BN>;
+    CUtensorMap map_a, map_b;
+    int rc = make_tensor_map_2d(&map_a, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBM, kBK);
+    if (rc != EMMYB200_OK) return rc;
+    rc = B_NK ? make_tensor_map_2d(&map_b, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, kBK)
+              : make_tensor_map_2d(&map_b, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, kBK, 64);
+    if (rc != EMMYB200_OK) return rc;
+    auto kernel = gemm_tcgen05_kernel<BN, BF16, EPI, B_NK>;
+    EMMY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+    GemmParams p;
+    p.C = C; p.ldc = ldc; p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.m_blocks = (int)((M + kBM - 1) / kBM);
+    p.n_blocks = (int)((N + BN - 1) / BN);
+    EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
+    const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(map_a, map_b, p);
+    return launch_status("gemm_tcgen05_kernel");
+}
+
+template <bool BF16, int EPI, bool B_NK>
+static int pick_tile(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                     int64_t ldc, cudaStream_t stream) {
+    // 128 x 256 tiles unless they leave most of the machine idle or the last wave mostly empty.
+    const int64_t sms = sm_count();
+    const int64_t mb = (M + kBM - 1) / kBM;
+    auto waste = [&](int bn) {
+        const int64_t tiles = mb * ((N + bn - 1) / bn);
+        const int64_t waves = (tiles + sms - 1) / sms;
+        return (double)(waves * sms * bn) / (double)(mb * N);     // scheduled columns per useful column
+    };
+    if (waste(256) <= 1.08 * waste(128)) return launch_gemm<256, BF16, EPI, B_NK>(A, B, C, M, N, K, lda, ldb, ldc, stream);
+    return launch_gemm<128, BF16, EPI, B_NK>(A, B, C, M, N, K, lda, ldb, ldc, stream);
+}
+
+}  // namespace emmy
+
+extern "C" int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, const void* B, void* C, int64_t M,
+                             int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* cuda_stream) {
+    using namespace emmy;
+    if (dtype != EMMYB200_F16 && dtype != EMMYB200_BF16) return fail(EMMYB200_ERR_UNSUPPORTED, "gemm: dtype %d (f16 and bf16 only)", dtype);
+    if (epilogue != EMMYB200_EPI_NONE && epilogue != EMMYB200_EPI_GELU_TANH) return fail(EMMYB200_ERR_ARG, "gemm: unknown epilogue %d", epilogue);
+    if (flags & ~EMMYB200_GEMM_B_NK) return fail(EMMYB200_ERR_ARG, "gemm: unknown flags 0x%x", flags);
+    if (M < 0 || N < 0 || K < 0) return fail(EMMYB200_ERR_SHAPE, "gemm: negative extent");
+    if (M == 0 || N == 0) return EMMYB200_OK;
+    if (K == 0) return fail(EMMYB200_ERR_SHAPE, "gemm: K = 0 (the caller zeroes C, emmyptx/mma.py:77-79 starts accumulators at 0)");
+    if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "gemm: extents must be below 2^31");
+    if (A == nullptr || B == nullptr || C == nullptr) return fail(EMMYB200_ERR_ARG, "gemm: null buffer");
+    const bool b_nk = flags & EMMYB200_GEMM_B_NK;
+    if (lda < K || ldc < N || ldb < (b_nk ? K : N)) return fail(EMMYB200_ERR_SHAPE, "gemm: leading dimension smaller than the row");
+    if ((lda | ldb | ldc) & 7) return fail(EMMYB200_ERR_ALIGN, "gemm: leading dimensions must be multiples of 8 elements (16 bytes)");
+    if (!aligned(A, 16) || !aligned(B, 16) || !aligned(C, 16)) return fail(EMMYB200_ERR_ALIGN, "gemm: buffers must be 16-byte aligned");
+    int rc = check_sm100();
+    if (rc != EMMYB200_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    const bool bf16 = dtype == EMMYB200_BF16;
+    const bool gelu = epilogue == EMMYB200_EPI_GELU_TANH;
+#define EMMY_GEMM_CASE(BF, EP, NK) \
+    if (bf16 == BF && gelu == (EP == EMMYB200_EPI_GELU_TANH) && b_nk == NK) return pick_tile<BF, EP, NK>(A, B, C, M, N, K, lda, ldb, ldc, s);
+    EMMY_GEMM_CASE(false, EMMYB200_EPI_NONE, false)
+    EMMY_GEMM_CASE(false, EMMYB200_EPI_NONE, true)
+    EMMY_GEMM_CASE(false, EMMYB200_EPI_GELU_TANH, false)
+    EMMY_GEMM_CASE(false, EMMYB200_EPI_GELU_TANH, true)
+    EMMY_GEMM_CASE(true, EMMYB200_EPI_NONE, false)
+    EMMY_GEMM_CASE(true, EMMYB200_EPI_NONE, true)
+    EMMY_GEMM_CASE(true, EMMYB200_EPI_GELU_TANH, false)
+    EMMY_GEMM_CASE(true, EMMYB200_EPI_GELU_TANH, true)
+#undef EMMY_GEMM_CASE
+    return fail(EMMYB200_ERR_UNSUPPORTED, "gemm: no kernel variant");
+}

@@ -1,0 +1,99 @@
+// Streaming fp32 elementwise kernels: y[i] = op(x[i]).
+//
+// The reference lowers a one-axis `Tile` to one thread per element with 4-byte accesses and no
+// loop (emmyptx/kernel.py:551-585 for the thread map, :632-677 / :714-733 for the scalar
+// ld/st, emmyptx/ops.py:212-290 for the op bodies). Here each thread moves 128-bit vectors,
+// several per trip of a grid-stride loop, so every warp access is four full 128-byte lines and
+// a few independent loads are in flight per thread; the grid is capped at a multiple of the SM
+// count. The op bodies are the <= 2 ulp functions of emmy_math.cuh.
+#include "common.cuh"
+#include "emmy_math.cuh"
+
+namespace emmy {
+
+template <int OP>
+__device__ __forceinline__ float apply_op(float x) {
+    if constexpr (OP == EMMYB200_OP_EXP_SIN_TANH) return emmy_exp_sin_tanh(x);
+    else if constexpr (OP == EMMYB200_OP_EXP) return emmy_expf(x);
+    else if constexpr (OP == EMMYB200_OP_SIN) return emmy_sinf(x);
+    else if constexpr (OP == EMMYB200_OP_COS) return emmy_cosf(x);
+    else if constexpr (OP == EMMYB200_OP_TANH) return emmy_tanhf(x);
+    else return emmy_gelu_tanhf(x);
+}
+
+constexpr int kThreads = 256;
+constexpr int kVecPerTrip = 2;     // float4 loads in flight per thread
+
+// x and y are not __restrict__: the op may run in place.
+template <int OP>
+__global__ void __launch_bounds__(kThreads) pointwise_vec4_kernel(const float4* x, float4* y, int64_t n4,
+                                                                   const float* x_tail, float* y_tail, int tail) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t base = (int64_t)blockIdx.x * kThreads + threadIdx.x; base < n4; base += stride * kVecPerTrip) {
+        float4 v[kVecPerTrip];
+#pragma unroll
+        for (int k = 0; k < kVecPerTrip; ++k) {
+            int64_t idx = base + k * stride;
+            if (idx < n4) v[k] = __ldcs(x + idx);
+        }
+#pragma unroll
+        for (int k = 0; k < kVecPerTrip; ++k) {
+            int64_t idx = base + k * stride;
+            if (idx < n4) {
+                float4 r;
+                r.x = apply_op<OP>(v[k].x);
+                r.y = apply_op<OP>(v[k].y);
+                r.z = apply_op<OP>(v[k].z);
+                r.w = apply_op<OP>(v[k].w);
+                __stcs(y + idx, r);
+            }
+        }
+    }
+    if (blockIdx.x == 0 && (int)threadIdx.x < tail) y_tail[threadIdx.x] = apply_op<OP>(x_tail[threadIdx.x]);
+}
+
+// Buffers that are not 16-byte aligned (a view into a larger allocation): 4-byte accesses,
+// still one full line per warp.
+template <int OP>
+__global__ void __launch_bounds__(kThreads) pointwise_scalar_kernel(const float* x, float* y, int64_t n) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) y[i] = apply_op<OP>(x[i]);
+}
+
+template <int OP>
+static int launch_pointwise(const float* x, float* y, int64_t n, cudaStream_t stream) {
+    const int64_t max_blocks = (int64_t)sm_count() * 8;
+    if (aligned(x, 16) && aligned(y, 16)) {
+        int64_t n4 = n / 4;
+        int tail = (int)(n - n4 * 4);
+        int64_t want = (n4 + (int64_t)kThreads * kVecPerTrip - 1) / ((int64_t)kThreads * kVecPerTrip);
+        int64_t blocks = want < 1 ? 1 : (want > max_blocks ? max_blocks : want);
+        pointwise_vec4_kernel<OP><<<(unsigned)blocks, kThreads, 0, stream>>>(
+            reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), n4, x + n4 * 4, y + n4 * 4, tail);
+        return launch_status("pointwise_vec4_kernel");
+    }
+    int64_t want = (n + kThreads - 1) / kThreads;
+    int64_t blocks = want > max_blocks ? max_blocks : want;
+    pointwise_scalar_kernel<OP><<<(unsigned)blocks, kThreads, 0, stream>>>(x, y, n);
+    return launch_status("pointwise_scalar_kernel");
+}
+
+}  // namespace emmy
+
+extern "C" int emmyb200_pointwise_f32(int op, const float* x, float* y, int64_t n, void* cuda_stream) {
+    using namespace emmy;
+    if (n < 0) return fail(EMMYB200_ERR_SHAPE, "pointwise: n = %lld is negative", (long long)n);
+    if (n == 0) return EMMYB200_OK;
+    if (x == nullptr || y == nullptr) return fail(EMMYB200_ERR_ARG, "pointwise: null buffer");
+    if (!aligned(x, 4) || !aligned(y, 4)) return fail(EMMYB200_ERR_ALIGN, "pointwise: buffers must be 4-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    switch (op) {
+        case EMMYB200_OP_EXP_SIN_TANH: return launch_pointwise<EMMYB200_OP_EXP_SIN_TANH>(x, y, n, s);
+        case EMMYB200_OP_EXP: return launch_pointwise<EMMYB200_OP_EXP>(x, y, n, s);
+        case EMMYB200_OP_SIN: return launch_pointwise<EMMYB200_OP_SIN>(x, y, n, s);
+        case EMMYB200_OP_COS: return launch_pointwise<EMMYB200_OP_COS>(x, y, n, s);
+        case EMMYB200_OP_TANH: return launch_pointwise<EMMYB200_OP_TANH>(x, y, n, s);
+        case EMMYB200_OP_GELU_TANH: return launch_pointwise<EMMYB200_OP_GELU_TANH>(x, y, n, s);
+        default: return fail(EMMYB200_ERR_ARG, "pointwise: unknown op %d", op);
+    }
+}

@@ -1,0 +1,153 @@
+"""ctypes binding of libemmyb200.so, the sm_100a kernel library.
+
+The reference reaches its kernels through the CUDA driver API (`tools/run_local.py:64-72` loads
+PTX, `:100-102` launches it). Here the kernels are precompiled, so the binding is one
+`ctypes.CDLL` and typed entry points; device memory and streams are torch's. There is no CPU
+path: without the library, or without a CUDA device, every call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libemmyb200.so"
+
+F32, F16, BF16, I32 = 0, 1, 2, 3
+OP_EXP_SIN_TANH, OP_EXP, OP_SIN, OP_COS, OP_TANH, OP_GELU_TANH = range(6)
+POINTWISE_OPS = {"exp_sin_tanh": OP_EXP_SIN_TANH, "exp": OP_EXP, "sin": OP_SIN, "cos": OP_COS,
+                 "tanh": OP_TANH, "gelu_tanh": OP_GELU_TANH}
+EPI_NONE, EPI_GELU_TANH = 0, 1
+EPILOGUES = {None: EPI_NONE, "none": EPI_NONE, "gelu_tanh": EPI_GELU_TANH}
+GEMM_B_NK = 1
+GATHER_TRUNC = 1
+
+_SIGNATURES = {
+    "emmyb200_version": (ctypes.c_int, []),
+    "emmyb200_last_error": (ctypes.c_char_p, []),
+    "emmyb200_pointwise_f32": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                              ctypes.c_void_p]),
+    "emmyb200_index_gather_i32": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                                                 ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                                 ctypes.c_void_p]),
+    "emmyb200_gemm": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                     ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                     ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),
+    "emmyb200_attention_fwd": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                              ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                              ctypes.c_int64, ctypes.c_float, ctypes.c_void_p]),
+    "emmyb200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
+}
+EXPORTS = tuple(_SIGNATURES)
+
+
+class KernelError(RuntimeError):
+    """A non-zero status from the library (the reference raises RuntimeError for driver errors,
+    tools/run_local.py:44-48)."""
+
+    def __init__(self, status: int, message: str) -> None:
+        super().__init__(f"emmyb200 status {status}: {message}")
+        self.status = status
+
+
+_lib = None
+
+
+def library() -> ctypes.CDLL:
+    """The loaded library. Raises if it has not been built: there is nothing to fall back to."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python {LIB_PATH.parent.parent / 'build.py'}`")
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise KernelError(status, library().emmyb200_last_error().decode())
+
+
+def _stream(stream) -> int:
+    import torch
+    return (torch.cuda.current_stream() if stream is None else stream).cuda_stream
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("emmyb200 kernels take CUDA tensors only (there is no CPU path)")
+        if not t.is_contiguous():
+            raise RuntimeError("emmyb200 kernels take contiguous tensors")
+
+
+def dtype_code(t) -> int:
+    import torch
+    return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int32: I32}[t.dtype]
+
+
+def pointwise(op: str, x, out=None, stream=None):
+    """out[i] = op(x[i]) for a float32 CUDA tensor; `op` is a key of POINTWISE_OPS."""
+    import torch
+    _need_cuda(x)
+    if x.dtype != torch.float32:
+        raise TypeError("pointwise: float32 only")
+    out = torch.empty_like(x) if out is None else out
+    _need_cuda(out)
+    check(library().emmyb200_pointwise_f32(POINTWISE_OPS[op], x.data_ptr(), out.data_ptr(), x.numel(), _stream(stream)))
+    return out
+
+
+def index_gather(x, mul: int, add: int, div: int, shift: int, trunc: bool = False, out=None, stream=None):
+    """out[i] = (x[(i*mul + add) mod n] // div) ^ (i >> shift) for an int32 CUDA tensor."""
+    import torch
+    _need_cuda(x)
+    if x.dtype != torch.int32:
+        raise TypeError("index_gather: int32 only")
+    out = torch.empty_like(x) if out is None else out
+    _need_cuda(out)
+    check(library().emmyb200_index_gather_i32(x.data_ptr(), out.data_ptr(), x.numel(), mul, add, div, shift,
+                                              GATHER_TRUNC if trunc else 0, _stream(stream)))
+    return out
+
+
+def gemm(a, b, epilogue: str | None = None, b_is_nk: bool = False, out=None, stream=None):
+    """out = epilogue(a @ b) (or a @ b.T when `b_is_nk`), fp16 / bf16, fp32 accumulation."""
+    import torch
+    _need_cuda(a, b)
+    if a.dtype != b.dtype or a.dim() != 2 or b.dim() != 2:
+        raise TypeError("gemm: two 2-D tensors of one 16-bit dtype")
+    m, k = a.shape
+    n = b.shape[0] if b_is_nk else b.shape[1]
+    if (b.shape[1] if b_is_nk else b.shape[0]) != k:
+        raise ValueError(f"gemm: inner extents differ: {tuple(a.shape)} x {tuple(b.shape)}")
+    out = torch.empty((m, n), dtype=a.dtype, device=a.device) if out is None else out
+    _need_cuda(out)
+    check(library().emmyb200_gemm(dtype_code(a), EPILOGUES[epilogue], GEMM_B_NK if b_is_nk else 0, a.data_ptr(),
+                                  b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),
+                                  _stream(stream)))
+    return out
+
+
+def attention(q, k, v, scale: float | None = None, out=None, stream=None):
+    """softmax(q k^T * scale) v over the last two axes; leading axes are independent units."""
+    import torch
+    _need_cuda(q, k, v)
+    d = q.shape[-1]
+    units = q.numel() // (q.shape[-2] * d)
+    out = torch.empty_like(q) if out is None else out
+    _need_cuda(out)
+    scale = d ** -0.5 if scale is None else scale
+    check(library().emmyb200_attention_fwd(dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), units,
+                                           q.shape[-2], k.shape[-2], d, scale, _stream(stream)))
+    return out
+
+
+def device_status() -> int:
+    """Reads and clears the device status word (non-zero: a bounded device-side wait expired)."""
+    word = ctypes.c_uint32(0)
+    check(library().emmyb200_device_status(ctypes.byref(word)))
+    return word.value

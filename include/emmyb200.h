@@ -1,0 +1,104 @@
+/* emmyb200 -- C ABI of the sm_100a kernel library that stands in for the PTX entry points
+ * emmyptx prints.
+ *
+ * In the reference a compiled kernel is a `.visible .entry <name>(.param .u64 buf, ...)` in PTX
+ * text (emmyptx/kernel.py:130-155, parameters in meta.json's `arg_order`, :166-183), loaded and
+ * launched with the CUDA driver API (tools/run_local.py:64-72, :100-102). Here the kernels are
+ * precompiled; each entry point below takes the same caller-owned device buffers (plain
+ * pointers, never retained), the extents the reference bakes into the PTX as constants, and
+ * the CUDA stream to launch on (the reference always uses the NULL stream). Calls are
+ * asynchronous: they enqueue work and return.
+ *
+ * Status: 0 = ok; < 0 = the arguments were rejected before anything was launched;
+ * > 0 = the cudaError_t of a failed runtime call. `emmyb200_last_error()` gives the text
+ * for the calling host thread. Nothing in the library traps, and every device-side wait is
+ * bounded: a pipeline wait that gives up records where in a status word that
+ * `emmyb200_device_status()` reads back (the reference's only device-side error path is a
+ * `trap`, emmyptx/kernel.py:685-691).
+ */
+#ifndef EMMYB200_H
+#define EMMYB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EMMYB200_OK 0
+#define EMMYB200_ERR_ARG (-1)         /* null pointer, bad enum */
+#define EMMYB200_ERR_SHAPE (-2)       /* extent the kernel family does not cover */
+#define EMMYB200_ERR_ALIGN (-3)       /* pointer or leading dimension not aligned as required */
+#define EMMYB200_ERR_UNSUPPORTED (-4) /* valid request, no kernel variant for it */
+#define EMMYB200_ERR_DEVICE (-5)      /* not an sm_100 device */
+#define EMMYB200_ERR_TIMEOUT (-6)     /* a bounded device-side wait expired (see device_status) */
+
+/* Element types of buffers, named as in emmyptx/kernel.py:34-35 (`ELEM`). */
+#define EMMYB200_F32 0
+#define EMMYB200_F16 1
+#define EMMYB200_BF16 2
+#define EMMYB200_I32 3
+
+int emmyb200_version(void);
+
+/* Text of the last non-zero status on this host thread (never NULL). */
+const char* emmyb200_last_error(void);
+
+/* Unary fp32 ops of the elementwise table, emmyptx/ops.py:212-290 (`lower_op`), applied to a
+ * flat array the way a one-axis `Tile` does (emmyptx/kernel.py:551-585): y[i] = op(x[i]).
+ * EXP_SIN_TANH is the fused expression exp(x) + sin(x) * tanh(x). Each function is within
+ * 2 ulp of the correctly rounded value for every fp32 input. x and y may be the same buffer. */
+#define EMMYB200_OP_EXP_SIN_TANH 0
+#define EMMYB200_OP_EXP 1
+#define EMMYB200_OP_SIN 2
+#define EMMYB200_OP_COS 3
+#define EMMYB200_OP_TANH 4
+#define EMMYB200_OP_GELU_TANH 5
+int emmyb200_pointwise_f32(int op, const float* x, float* y, int64_t n, void* cuda_stream);
+
+/* The int32 index-math gather
+ *     y[i] = (x[(i * mul + add) mod n] div d) xor (i >> shift),   0 <= i < n,
+ * i.e. the s32 instruction stream of emmyptx/intmath.py:36-38, :87-117 and
+ * emmyptx/ops.py:294-309 around one gathered load (emmyptx/kernel.py:632-677).
+ * The index is the mathematical (i * mul + add) mod n, which for a power-of-two n equals
+ * the wrapped-int32 value the reference masks with n - 1. `div` rounds toward minus infinity
+ * (torch's `//`, tools/torch_cases/dtypes.py:17-19) unless EMMYB200_GATHER_TRUNC is set, which
+ * gives the reference PTX's `div.s32` (toward zero). Requires n >= 1, n < 2^31, 0 <= mul,
+ * 0 <= add, d >= 1, 0 <= shift <= 31; x and y must not overlap. */
+#define EMMYB200_GATHER_TRUNC 1
+int emmyb200_index_gather_i32(const int32_t* x, int32_t* y, int64_t n, int64_t mul, int64_t add,
+                              int32_t d, int32_t shift, int32_t flags, void* cuda_stream);
+
+/* C[M,N] = epilogue(A[M,K] . B) with fp32 accumulation and one rounding to the output type,
+ * replacing the RegFragment / LdmatrixLoad / MmaSyncPtx / RegStore statement family
+ * (emmyptx/mma.py:65-242). A is row-major with leading dimension lda. B is row-major K x N
+ * (ldb >= N) or, with EMMYB200_GEMM_B_NK, row-major N x K (`b_trans`, emmyptx/mma.py:112-113;
+ * ldb >= K). dtype (F16 or BF16) is the type of A, B and C. Epilogues: NONE, or GELU_TANH =
+ * 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) on the fp32 accumulator -- the fusion the
+ * reference refuses (emmyptx/mma.py:201-203). Any M, N, K >= 1; pointers 16-byte aligned and
+ * leading dimensions multiples of 8 elements. */
+#define EMMYB200_EPI_NONE 0
+#define EMMYB200_EPI_GELU_TANH 1
+#define EMMYB200_GEMM_B_NK 1
+int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, const void* B, void* C,
+                  int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                  void* cuda_stream);
+
+/* O = softmax(Q K^T * scale) V per (batch, head) unit, fp32 softmax, non-causal: what the
+ * reference emits as generic fused statements (dot-product Loops + Accum, WarpShuffle /
+ * TreeHalve row reductions, `_exp`: emmyptx/kernel.py:786-797, :856-900, emmyptx/ops.py:49-77).
+ * Q, O: [units, seq_q, d]; K, V: [units, seq_k, d]; contiguous, dtype F16 or BF16, d = 128
+ * or 64, any seq_q, seq_k >= 1. */
+int emmyb200_attention_fwd(int dtype, const void* Q, const void* K, const void* V, void* O,
+                           int64_t units, int64_t seq_q, int64_t seq_k, int64_t d, float scale,
+                           void* cuda_stream);
+
+/* Reads (and clears) the device status word of the current device: 0 if no bounded wait has
+ * expired since the last call, else a code naming kernel, role and pipeline stage.
+ * Synchronises the device. */
+int emmyb200_device_status(uint32_t* status_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EMMYB200_H */

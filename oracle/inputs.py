@@ -1,0 +1,51 @@
+"""Seeded synthetic inputs with the shapes and value distributions of the five configurations.
+
+Seeds follow the reference's runner: argument i of a kernel is drawn from
+`np.random.default_rng(i)` (`tools/run_local.py:86-87`, `tools/check_torch.py:186-191`).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+def to_bf16_bits(values) -> np.ndarray:
+    """fp32 -> bf16 bit patterns, round to nearest even (as `tools/run_local.py:31-37`)."""
+    bits = np.ascontiguousarray(values, dtype=np.float32).view(np.uint32)
+    return ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def from_bf16_bits(raw) -> np.ndarray:
+    """bf16 bit patterns -> fp32 (as `tools/run_local.py:40-41`)."""
+    return (np.asarray(raw).astype(np.uint32) << 16).view(np.float32)
+
+
+def c1_input(n: int = 2**20, seed: int = 0) -> np.ndarray:
+    """x ~ Uniform[-4, 4], float32."""
+    return np.random.default_rng(seed).uniform(-4.0, 4.0, n).astype(np.float32)
+
+
+def c2_input(n: int = 2**26, seed: int = 0) -> np.ndarray:
+    """x ~ Uniform int32 [-2^30, 2^30]."""
+    return np.random.default_rng(seed).integers(-2**30, 2**30, n, dtype=np.int32, endpoint=True)
+
+
+def gemm_inputs(m: int, n: int, k: int, dtype: str, b_is_nk: bool = False):
+    """A[m,k], B[k,n] (or [n,k]) ~ N(0,1)/sqrt(k), rounded to `dtype` ('f16' or 'bf16').
+    Returns torch CPU tensors of that dtype."""
+    import torch
+    scale = np.float32(1.0 / np.sqrt(k))
+    a = np.random.default_rng(0).standard_normal((m, k), dtype=np.float32) * scale
+    b = np.random.default_rng(1).standard_normal((n, k) if b_is_nk else (k, n), dtype=np.float32) * scale
+    td = torch.float16 if dtype == "f16" else torch.bfloat16
+    return torch.from_numpy(a).to(td), torch.from_numpy(b).to(td)
+
+
+def attention_inputs(units: int, seq_q: int, seq_k: int, d: int, dtype: str = "bf16"):
+    """Q[units,seq_q,d], K, V[units,seq_k,d] ~ N(0,1), rounded to `dtype`; torch CPU tensors."""
+    import torch
+    td = torch.float16 if dtype == "f16" else torch.bfloat16
+    out = []
+    for seed, s in ((0, seq_q), (1, seq_k), (2, seq_k)):
+        x = np.random.default_rng(seed).standard_normal((units, s, d), dtype=np.float32)
+        out.append(torch.from_numpy(x).to(td))
+    return tuple(out)

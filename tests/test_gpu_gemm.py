@@ -1,0 +1,121 @@
+"""tcgen05 GEMM (C3, C4 and the ragged shapes of tools/torch_cases/matmul.py) against the oracle.
+
+Tolerance (stated by the task for fp16/bf16 GEMMs): |c - ref| <= 1e-2 |ref| + 1e-2 std(ref) with
+ref the fp32-accumulated product of the same rounded inputs. The reference's own classes for
+tensor-core matmuls (rtol 2e-2 / atol 1e-1 for f16, 5e-2 / 5e-1 for bf16, matmul.py:5-7) are
+looser and are implied.
+"""
+import numpy as np
+import pytest
+
+from oracle import inputs, reference
+
+pytestmark = pytest.mark.gpu
+
+
+def _gemm(a, b, cuda, **kw):
+    import torch
+    from emmyptx import runtime
+    c = runtime.gemm(a.to(cuda), b.to(cuda), **kw)
+    torch.cuda.synchronize()
+    assert runtime.device_status() == 0
+    return c.cpu()
+
+
+SHAPES = [
+    (128, 256, 64), (128, 256, 256), (256, 512, 512), (512, 512, 512),          # m_f16_mm_staged / m_bf16_mm sizes
+    (256, 256, 256),                                                             # m_f16_mm
+    (100, 200, 72), (100, 72, 200),                                              # m_f16_mm_odd: ragged M, N, K
+    (1, 8, 8), (129, 264, 8), (300, 1000, 136), (64, 512, 256),                  # tiny and tail-heavy
+    (1024, 1024, 1024), (2048, 512, 1024),                                       # x14_matmul_2048-like
+]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_gemm_matches_oracle(m, n, k, dtype, cuda):
+    a, b = inputs.gemm_inputs(m, n, k, dtype)
+    got = _gemm(a, b, cuda)
+    ok, ratio = reference.gemm_tolerance_ok(got, reference.gemm_reference(a, b))
+    assert ok, f"worst error {ratio:.2f}x the bound"
+    assert got.abs().sum() > 0
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 512, 512), (100, 200, 72), (64, 512, 256), (1024, 1024, 1024)])
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_gemm_b_stored_n_by_k(m, n, k, dtype, cuda):
+    """F.linear's weight layout (m_f16_linear, matmul.py:32)."""
+    a, b = inputs.gemm_inputs(m, n, k, dtype, b_is_nk=True)
+    got = _gemm(a, b, cuda, b_is_nk=True)
+    ok, ratio = reference.gemm_tolerance_ok(got, reference.gemm_reference(a, b, b_is_nk=True))
+    assert ok, f"worst error {ratio:.2f}x the bound"
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 512, 512), (100, 200, 72), (1024, 2048, 1024)])
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_gemm_gelu_epilogue(m, n, k, dtype, cuda):
+    import torch
+    a, b = inputs.gemm_inputs(m, n, k, dtype)
+    a = a * 8                                  # spread the pre-activation over GELU's curved part
+    got = _gemm(a, b, cuda, epilogue="gelu_tanh")
+    ok, ratio = reference.gemm_tolerance_ok(got, reference.gemm_reference(a, b, "gelu_tanh"))
+    assert ok, f"worst error {ratio:.2f}x the bound"
+
+
+def test_gemm_unnormalised_randn_reference_tolerance(cuda):
+    """The reference's own case m_f16_mm_staged: randn inputs, rtol 2e-2 / atol 1e-1 vs float64."""
+    import torch
+    a = torch.from_numpy(np.random.default_rng(0).standard_normal((512, 512)).astype(np.float16))
+    b = torch.from_numpy(np.random.default_rng(1).standard_normal((512, 512)).astype(np.float16))
+    got = _gemm(a, b, cuda)
+    ref = reference.gemm_reference(a, b, double=True)
+    assert reference.compare(got.float().numpy(), ref.numpy(), 2e-2, 1e-1)["ok"]
+
+
+def test_c3_full_size(cuda):
+    a, b = inputs.gemm_inputs(4096, 4096, 4096, "f16")
+    got = _gemm(a, b, cuda)
+    ok, ratio = reference.gemm_tolerance_ok(got, reference.gemm_reference(a, b))
+    assert ok, f"worst error {ratio:.2f}x the bound"
+
+
+def test_linearity_at_size(cuda):
+    """Size-independent property at a large size: (2A) B = 2 (A B) exactly (scaling by 2 is exact
+    in fp16), and rows of a row-permuted A give the permuted rows of C bit for bit."""
+    import torch
+    a, b = inputs.gemm_inputs(4096, 2048, 2048, "f16")
+    c1 = _gemm(a, b, cuda)
+    c2 = _gemm(a * 2, b, cuda)
+    assert torch.equal(c1 * 2, c2)
+    perm = torch.from_numpy(np.random.default_rng(5).permutation(4096))
+    assert torch.equal(_gemm(a[perm].contiguous(), b, cuda), c1[perm])
+
+
+def test_leading_dimensions(cuda):
+    """Row pitches larger than the rows (views into wider allocations)."""
+    import torch
+    from emmyptx import runtime
+    a, b = inputs.gemm_inputs(200, 136, 264, "bf16")
+    A = torch.zeros(200, 512, dtype=torch.bfloat16, device=cuda); A[:, :264] = a.to(cuda)
+    B = torch.zeros(264, 256, dtype=torch.bfloat16, device=cuda); B[:, :136] = b.to(cuda)
+    C = torch.full((200, 144), 7.0, dtype=torch.bfloat16, device=cuda)
+    runtime.check(runtime.library().emmyb200_gemm(runtime.BF16, 0, 0, A.data_ptr(), B.data_ptr(), C.data_ptr(), 200, 136, 264,
+                                                  512, 256, 144, None))
+    torch.cuda.synchronize()
+    ok, ratio = reference.gemm_tolerance_ok(C[:, :136].cpu(), reference.gemm_reference(a, b))
+    assert ok, ratio
+    assert torch.all(C[:, 136:] == 7.0)        # nothing written past N
+
+
+def test_rejects_bad_arguments(cuda, lib):
+    import torch
+    x = torch.zeros(64 * 64, dtype=torch.float16, device=cuda)
+    p = x.data_ptr()
+    g = lib.emmyb200_gemm
+    assert g(0, 0, 0, p, p, p, 64, 64, 64, 64, 64, 64, None) == -4          # f32 operands
+    assert g(1, 7, 0, p, p, p, 64, 64, 64, 64, 64, 64, None) == -1          # epilogue
+    assert g(1, 0, 0, p, p, p, 64, 64, 64, 60, 64, 64, None) == -2          # lda < K
+    assert g(1, 0, 0, p, p, p, 60, 60, 60, 60, 60, 60, None) == -3          # pitches not multiples of 8
+    assert g(1, 0, 0, p + 2, p, p, 64, 64, 64, 64, 64, 64, None) == -3      # misaligned pointer
+    assert g(1, 0, 0, p, p, p, 0, 64, 64, 64, 64, 64, None) == 0            # empty
+    assert g(1, 0, 0, p, p, p, 64, 64, 0, 64, 64, 64, None) == -2           # K = 0
