@@ -1,0 +1,540 @@
+"""Benchmark driver: one JSON line per run.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c4|c3|c5|c1|c2]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+The default workload is configuration 4 of BASELINE.json: bf16 GEMM + tanh-approx GELU epilogue,
+M = N = K = 16384, fp32 accumulation, bf16 output, split by M rows over the ranks (the metric is
+quoted at 1/2/4/8 GPUs on this case). A step is one pass of the fused GEMM kernel over the rank's
+row shard followed, for N > 1, by the all-gather of the output shards. Inputs are seeded synthetic
+tensors of the configuration's shape and distribution, resident in HBM before the timed region
+(`value`), or staged from pinned host memory through the public Python API every step (`e2e`).
+
+`--impl reference` times the reference's CPU path for the same workload -- the torch CPU evaluation of
+the same expression (tools/check_torch.py:194-237 defines it as the truth) -- on the host cores, on a
+bounded sample of the rows.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (str(ROOT), str(ROOT / "emmy-ptx-compiler_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+WORKLOADS = {
+    "c1": "fp32 exp(x)+sin(x)*tanh(x), N=2^20, x~U[-4,4]",
+    "c2": "int32 gather y[i]=(x[(i*7919+13) mod N]//3)^(i>>2), N=2^26",
+    "c3": "fp16 GEMM M=N=K=4096, fp32 accumulate, fp16 out",
+    "c4": "bf16 GEMM + tanh-GELU epilogue M=N=K=16384, fp32 accumulate, bf16 out, M-row shards",
+    "c5": "bf16 attention fwd B16 H16 S4096 d128, non-causal, fp32 softmax, (batch x head) shards",
+}
+
+
+def peaks() -> tuple[dict, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return json.loads(p.read_text()), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index: int) -> None:
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self) -> None:
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---- the five workloads -------------------------------------------------------------------------------
+class Workload:
+    """One configuration: device-resident inputs for this rank, the step, its algorithmic work."""
+
+    name = ""
+    metric = ""
+    unit = ""
+    dtype = ""
+    bound = "hbm"
+    scaling = "strong"
+
+    def step(self) -> None: ...
+    def work_per_step(self) -> float: ...        # whole job, in the metric's base unit (flop or bytes)
+    def kernel_work_per_launch(self) -> float: ...
+    def launches_per_step(self) -> int: return 1
+
+
+class GemmWorkload(Workload):
+    metric, unit, bound = "gemm_tflops", "TFLOP/s", "tensor"
+
+    def __init__(self, name, m, n, k, dtype, epilogue, rank, world, dev, gather=True):
+        import torch
+        from emmyptx import runtime
+        self.rt, self.torch = runtime, torch
+        self.name, self.dtype = name, dtype
+        self.m, self.n, self.k, self.epilogue = m, n, k, epilogue
+        self.rank, self.world = rank, world
+        self.rows = m // world
+        td = torch.float16 if dtype == "f16" else torch.bfloat16
+        g = torch.Generator(device=dev)
+        g.manual_seed(1)
+        self.b = (torch.randn(k, n, device=dev, generator=g, dtype=torch.float32) / k**0.5).to(td)
+        g.manual_seed(1000 + rank)
+        self.a = (torch.randn(self.rows, k, device=dev, generator=g, dtype=torch.float32) / k**0.5).to(td)
+        self.c_full = torch.empty(m, n, device=dev, dtype=td)
+        self.c = self.c_full[rank * self.rows:(rank + 1) * self.rows]
+        self.gather = gather and world > 1
+        self.host = None
+
+    def step(self):
+        self.rt.gemm(self.a, self.b, epilogue=self.epilogue, out=self.c)
+        if self.gather:
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(self.c_full, self.c)
+
+    def kernel_only(self):
+        self.rt.gemm(self.a, self.b, epilogue=self.epilogue, out=self.c)
+
+    def work_per_step(self):
+        return 2.0 * self.m * self.n * self.k
+
+    def kernel_work_per_launch(self):
+        return 2.0 * self.rows * self.n * self.k
+
+    def e2e_setup(self):
+        t = self.torch
+        self.host = {"a": self.a.cpu().pin_memory(), "b": self.b.cpu().pin_memory(),
+                     "c": t.empty_like(self.c, device="cpu").pin_memory()}
+        return self.host["a"].numel() * 2 + self.host["b"].numel() * 2, self.host["c"].numel() * 2
+
+    def e2e_step(self):
+        h = self.host
+        self.a.copy_(h["a"], non_blocking=True)
+        self.b.copy_(h["b"], non_blocking=True)
+        self.step()
+        h["c"].copy_(self.c, non_blocking=True)
+
+
+class PointwiseWorkload(Workload):
+    metric, unit, dtype, scaling = "elementwise_gbs", "GB/s", "f32", "weak"
+
+    def __init__(self, n, rank, world, dev):
+        import torch
+        from emmyptx import runtime
+        self.rt, self.torch, self.world = runtime, torch, world
+        self.name = "c1"
+        self.n = n
+        g = torch.Generator(device=dev)
+        g.manual_seed(rank)
+        self.x = torch.rand(n, device=dev, generator=g) * 8 - 4
+        self.y = torch.empty_like(self.x)
+
+    def step(self):
+        self.rt.pointwise("exp_sin_tanh", self.x, out=self.y)
+
+    kernel_only = step
+
+    def work_per_step(self):
+        return 8.0 * self.n * self.world
+
+    def kernel_work_per_launch(self):
+        return 8.0 * self.n
+
+    def e2e_setup(self):
+        self.host = {"x": self.x.cpu().pin_memory(), "y": self.torch.empty_like(self.y, device="cpu").pin_memory()}
+        return self.n * 4, self.n * 4
+
+    def e2e_step(self):
+        self.x.copy_(self.host["x"], non_blocking=True)
+        self.step()
+        self.host["y"].copy_(self.y, non_blocking=True)
+
+
+class GatherWorkload(PointwiseWorkload):
+    dtype = "i32"
+
+    def __init__(self, n, rank, world, dev):
+        import torch
+        from emmyptx import runtime
+        self.rt, self.torch, self.world = runtime, torch, world
+        self.name = "c2"
+        self.n = n
+        g = torch.Generator(device=dev)
+        g.manual_seed(rank)
+        self.x = torch.randint(-2**30, 2**30 + 1, (n,), device=dev, generator=g, dtype=torch.int32)
+        self.y = torch.empty_like(self.x)
+
+    def step(self):
+        self.rt.index_gather(self.x, 7919, 13, 3, 2, out=self.y)
+
+    kernel_only = step
+
+
+class AttentionWorkload(Workload):
+    metric, unit, dtype, bound = "attention_tflops", "TFLOP/s", "bf16", "tensor"
+
+    def __init__(self, units, seq, d, rank, world, dev, gather=True):
+        import torch
+        from emmyptx import runtime
+        self.rt, self.torch = runtime, torch
+        self.name = "c5"
+        self.units, self.seq, self.d, self.world, self.rank = units, seq, d, world, rank
+        self.local = units // world
+        g = torch.Generator(device=dev)
+        g.manual_seed(2000 + rank)
+        mk = lambda: torch.randn(self.local, seq, d, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+        self.q, self.k, self.v = mk(), mk(), mk()
+        self.o_full = torch.empty(units, seq, d, device=dev, dtype=torch.bfloat16)
+        self.o = self.o_full[rank * self.local:(rank + 1) * self.local]
+        self.gather = gather and world > 1
+
+    def step(self):
+        self.rt.attention(self.q, self.k, self.v, out=self.o)
+        if self.gather:
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(self.o_full, self.o)
+
+    def kernel_only(self):
+        self.rt.attention(self.q, self.k, self.v, out=self.o)
+
+    def work_per_step(self):
+        return 4.0 * self.units * self.seq * self.seq * self.d
+
+    def kernel_work_per_launch(self):
+        return 4.0 * self.local * self.seq * self.seq * self.d
+
+    def e2e_setup(self):
+        t = self.torch
+        self.host = {n: getattr(self, n).cpu().pin_memory() for n in "qkv"}
+        self.host["o"] = t.empty_like(self.o, device="cpu").pin_memory()
+        return 3 * self.q.numel() * 2, self.o.numel() * 2
+
+    def e2e_step(self):
+        for n in "qkv":
+            getattr(self, n).copy_(self.host[n], non_blocking=True)
+        self.step()
+        self.host["o"].copy_(self.o, non_blocking=True)
+
+
+def make_workload(name, rank, world, dev):
+    if name == "c4":
+        return GemmWorkload("c4", 16384, 16384, 16384, "bf16", "gelu_tanh", rank, world, dev)
+    if name == "c3":
+        return GemmWorkload("c3", 4096, 4096, 4096, "f16", None, rank, world, dev)
+    if name == "c5":
+        return AttentionWorkload(256, 4096, 128, rank, world, dev)
+    if name == "c1":
+        return PointwiseWorkload(2**20, rank, world, dev)
+    if name == "c2":
+        return GatherWorkload(2**26, rank, world, dev)
+    raise SystemExit(f"unknown workload {name!r}")
+
+
+# ---- timing ---------------------------------------------------------------------------------------------
+def timed(torch, dist, world, fn, steps, warmup):
+    """Device time of exactly `steps` calls of fn, max over ranks, in ms (total)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def graph_timed(torch, fn, launches, reps=5):
+    """Average device time per launch of `fn` captured `launches` times in one CUDA graph (takes the
+    host's launch cost out of the measurement of kernels that run for a few microseconds)."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(3):
+            fn()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for _ in range(launches):
+                fn()
+    torch.cuda.synchronize()
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (reps * launches)
+
+
+# ---- the reference's CPU path -------------------------------------------------------------------------------
+def cpu_reference_step(name: str, threads: int):
+    """(callable running one bounded sample, work of that sample in the metric's base unit, unit scale,
+    description). The expression is the case's torch code on CPU, all host threads."""
+    import torch
+    import numpy as np
+    torch.set_num_threads(threads)
+    if name in ("c3", "c4"):
+        n = k = 16384 if name == "c4" else 4096
+        rows = 1024 if name == "c4" else 4096
+        td = torch.bfloat16 if name == "c4" else torch.float16
+        g = torch.Generator().manual_seed(0)
+        a = (torch.randn(rows, k, generator=g) / k**0.5).to(td)
+        b = (torch.randn(k, n, generator=g) / k**0.5).to(td)
+        if name == "c4":
+            fn = lambda: torch.nn.functional.gelu(a @ b, approximate="tanh")
+        else:
+            fn = lambda: a @ b
+        return fn, 2.0 * rows * n * k, 1e12, f"{rows} of {n} rows of A against the full B, torch CPU {td}"
+    if name == "c5":
+        units, s, d = 4, 4096, 128
+        g = torch.Generator().manual_seed(0)
+        q, kk, v = (torch.randn(units, s, d, generator=g).to(torch.bfloat16) for _ in range(3))
+        fn = lambda: torch.nn.functional.scaled_dot_product_attention(q, kk, v)
+        return fn, 4.0 * units * s * s * d, 1e12, f"{units} of 256 (batch, head) units, torch CPU bf16 SDPA"
+    if name == "c1":
+        n = 2**20
+        x = torch.from_numpy(np.random.default_rng(0).uniform(-4, 4, n).astype(np.float32))
+        fn = lambda: torch.exp(x) + torch.sin(x) * torch.tanh(x)
+        return fn, 8.0 * n, 1e9, "the full 2^20 array, torch CPU fp32"
+    if name == "c2":
+        n = 2**26
+        from oracle import inputs, reference
+        x = torch.from_numpy(inputs.c2_input(n))
+        fn = lambda: reference.c2_torch(x)
+        return fn, 8.0 * n, 1e9, "the full 2^26 array, torch CPU int32/int64"
+    raise SystemExit(name)
+
+
+def time_cpu(fn, budget_s: float = 12.0, min_reps: int = 2) -> float:
+    """Best wall time of fn over as many repetitions as fit the budget (after one warm-up)."""
+    fn()
+    best, t_end, reps = float("inf"), time.perf_counter() + budget_s, 0
+    while reps < min_reps or time.perf_counter() < t_end:
+        t0 = time.perf_counter()
+        fn()
+        best = min(best, time.perf_counter() - t0)
+        reps += 1
+        if reps >= 50:
+            break
+    return best
+
+
+def run_reference(args, rank: int) -> int:
+    if rank != 0:
+        return 0
+    threads = os.cpu_count() or 1
+    fn, work, scale, sample = cpu_reference_step(args.workload, threads)
+    for _ in range(args.warmup):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn()
+    dt = time.perf_counter() - t0
+    w0 = WORKLOADS[args.workload]
+    value = work * args.steps / dt / scale
+    unit = "TFLOP/s" if scale == 1e12 else "GB/s"
+    metric = {"c1": "elementwise_gbs", "c2": "elementwise_gbs", "c5": "attention_tflops"}.get(args.workload, "gemm_tflops")
+    print(json.dumps({
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": {"c1": "f32", "c2": "i32", "c3": "f16"}.get(args.workload, "bf16"), "data": "synthetic",
+        "config": {"workload": w0, "note": "each step is a bounded sample of the workload on the host cores"},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "reference", "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+    return 0
+
+
+# ---- main ---------------------------------------------------------------------------------------------------
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=tuple(WORKLOADS), default="c4")
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads and the CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        return run_reference(args, rank)
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    from emmyptx import runtime
+    runtime.library()
+
+    wl = make_workload(args.workload, rank, world, dev)
+    pk, pk_kind = peaks()
+
+    # kernel-only time for the roofline (CUDA events on the launching stream, same steps)
+    k_ms = timed(torch, dist, 1, wl.kernel_only, args.steps, args.warmup) / args.steps
+    # the timed region proper
+    with ClockSampler(local_rank) as clocks:
+        total_ms = timed(torch, dist, world, wl.step, args.steps, args.warmup)
+    status = runtime.device_status()
+    ms_per_step = total_ms / args.steps
+    scale = 1e12 if wl.unit == "TFLOP/s" else 1e9
+    value = wl.work_per_step() / (ms_per_step * 1e-3) / scale
+
+    # end to end: pinned host inputs in, result out, through the Python API, every step
+    h2d, d2h = wl.e2e_setup()
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_ms = timed(torch, dist, world, wl.e2e_step, e2e_steps, 1) / e2e_steps
+    e2e_value = wl.work_per_step() / (e2e_ms * 1e-3) / scale
+
+    if wl.bound == "tensor":
+        achieved = wl.kernel_work_per_launch() / (k_ms * 1e-3) / 1e12
+        peak = pk.get("bf16_tflops_sustained", pk["bf16_tflops"])
+        roof_unit, peak_note = "TFLOP/s", f"{pk_kind} cuBLAS bf16, sustained"
+    else:
+        achieved = wl.kernel_work_per_launch() / (k_ms * 1e-3) / 1e9
+        peak = pk["hbm_gbs"]
+        roof_unit, peak_note = "GB/s", f"{pk_kind} copy bandwidth"
+    traffic_file = ROOT / "profiles" / "traffic.json"
+    traffic = None
+    if traffic_file.exists():
+        traffic = json.loads(traffic_file.read_text()).get(args.workload)
+
+    line = {
+        "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype,
+        "data": "synthetic",
+        "config": {"workload": WORKLOADS[args.workload], "l2": "inputs larger than L2" if args.workload not in ("c1",) else
+                   "8 MiB working set, L2-resident by construction of the configuration", "parallelism": f"rows/{world}",
+                   "collective": "nccl all_gather of the output shards" if world > 1 else "none"},
+        "roofline": {"bound": "tensor" if wl.bound == "tensor" else "hbm", "achieved": achieved, "peak": peak, "unit": roof_unit,
+                     "frac": achieved / peak, "traffic": traffic, "peak_source": peak_note, "kernel_ms": k_ms},
+        "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+        "gpu_launches": args.steps * wl.launches_per_step(),
+        "clocks": clocks.summary(),
+        "device_status": status,
+    }
+
+    if rank == 0 and world == 1 and not args.no_extras:
+        threads = os.cpu_count() or 1
+        fn, work, cscale, sample = cpu_reference_step(args.workload, threads)
+        best = time_cpu(fn)
+        line["cpu_baseline"] = {"value": work / best / cscale, "unit": wl.unit, "cores": threads, "kind": "reference",
+                                "sample": sample}
+        line["other_workloads"] = other_workloads(torch, dist, dev, pk, args.workload)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def other_workloads(torch, dist, dev, pk, skip: str) -> dict:
+    """Short device-resident measurements of the remaining configurations (1 GPU), each with its roofline
+    fraction; kernels of a few microseconds are timed inside a CUDA graph."""
+    out = {}
+    for name in WORKLOADS:
+        if name == skip:
+            continue
+        try:
+            wl = make_workload(name, 0, 1, dev)
+            if name == "c1":
+                ms = graph_timed(torch, wl.kernel_only, 50)
+            else:
+                ms = timed(torch, dist, 1, wl.kernel_only, 5, 3) / 5
+            scale = 1e12 if wl.unit == "TFLOP/s" else 1e9
+            val = wl.kernel_work_per_launch() / (ms * 1e-3) / scale
+            peak = pk.get("bf16_tflops", 1.0) if wl.bound == "tensor" else pk["hbm_gbs"]
+            out[name] = {"workload": WORKLOADS[name], "value": val, "unit": wl.unit, "ms": ms, "frac_of_peak": val / peak}
+            del wl
+            torch.cuda.empty_cache()
+        except Exception as e:  # noqa: BLE001 - a missing kernel must not hide the main line
+            out[name] = {"workload": WORKLOADS[name], "error": f"{type(e).__name__}: {e}"[:200]}
+    try:
+        from emmyptx import runtime
+        n = 2**28
+        x = torch.rand(n, device=dev) * 8 - 4
+        y = torch.empty_like(x)
+        ms = timed(torch, dist, 1, lambda: runtime.pointwise("exp_sin_tanh", x, out=y), 5, 3) / 5
+        out["c1_at_2^28"] = {"value": 8.0 * n / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms": ms,
+                             "frac_of_peak": 8.0 * n / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+    except Exception as e:  # noqa: BLE001
+        out["c1_at_2^28"] = {"error": str(e)[:200]}
+    return out
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,86 @@
+"""Attention forward (C5 and the shapes of the reference's f_sdpa / f_sdpa_f16 / x16_attn_512 cases)
+against the fp32 oracle.
+
+Tolerance: |o - ref| <= 1e-2 |ref| + 1e-2 std(ref), ref = fp32 softmax(QK^T/sqrt(d))V of the same rounded
+inputs (the reference's class for attention is MM, rtol = atol = 1e-3 on fp32 buffers, and HALF 1e-2 for
+16-bit ones: tools/torch_cases/__init__.py:20-21, fused.py:21-28).
+"""
+import numpy as np
+import pytest
+
+from oracle import inputs, reference
+
+pytestmark = pytest.mark.gpu
+
+
+def _attn(q, k, v, cuda, **kw):
+    import torch
+    from emmyptx import runtime
+    o = runtime.attention(q.to(cuda), k.to(cuda), v.to(cuda), **kw)
+    torch.cuda.synchronize()
+    assert runtime.device_status() == 0
+    return o.cpu()
+
+
+@pytest.mark.parametrize("units,sq,sk,d", [
+    (2, 128, 128, 128), (3, 256, 384, 128), (2, 512, 512, 128),       # x16_attn_512-like
+    (2, 100, 200, 128), (1, 1, 1, 128), (2, 129, 257, 128), (1, 300, 77, 128),   # ragged
+    (4, 256, 256, 64), (2, 130, 190, 64),                              # f_sdpa_f16 head size
+    (1, 2048, 2048, 128),
+])
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_attention_matches_oracle(units, sq, sk, d, dtype, cuda):
+    q, k, v = inputs.attention_inputs(units, sq, sk, d, dtype)
+    got = _attn(q, k, v, cuda)
+    ref = reference.attention_reference(q, k, v)
+    ok, ratio = reference.gemm_tolerance_ok(got, ref)
+    assert ok, f"worst error {ratio:.2f}x the bound"
+
+
+def test_large_logits_and_scale(cuda):
+    """Scores spread over hundreds of log2 units: the running max must be raised (and the accumulator
+    rescaled) many times."""
+    import torch
+    q, k, v = inputs.attention_inputs(2, 256, 1024, 128, "bf16")
+    k = k.clone()
+    k[:, 512:] *= 3                       # later keys dominate
+    got = _attn(q * 2, k, v, cuda, scale=1.0)
+    ref = reference.attention_reference(q * 2, k, v, scale=1.0)
+    ok, ratio = reference.gemm_tolerance_ok(got, ref)
+    assert ok, f"worst error {ratio:.2f}x the bound"
+
+
+def test_c5_sampled_units(cuda):
+    """Full sequence length of C5 (4096) on a few (batch, head) units; every unit is independent."""
+    q, k, v = inputs.attention_inputs(3, 4096, 4096, 128, "bf16")
+    got = _attn(q, k, v, cuda)
+    ref = reference.attention_reference(q, k, v)
+    ok, ratio = reference.gemm_tolerance_ok(got, ref)
+    assert ok, f"worst error {ratio:.2f}x the bound"
+
+
+def test_rows_sum_property(cuda):
+    """Size-independent property: with V = all ones every output element is exactly 1 up to rounding
+    (softmax rows sum to 1), and permuting the keys together with the values leaves O unchanged up to
+    summation order."""
+    import torch
+    q, k, v = inputs.attention_inputs(2, 512, 1024, 128, "bf16")
+    ones = torch.ones_like(v)
+    got = _attn(q, k, ones, cuda)
+    assert (got.float() - 1).abs().max() <= 2 ** -7
+    perm = torch.from_numpy(np.random.default_rng(9).permutation(1024))
+    a = _attn(q, k, v, cuda)
+    b = _attn(q, k[:, perm].contiguous(), v[:, perm].contiguous(), cuda)
+    assert (a.float() - b.float()).abs().max() <= 1e-2 * a.float().std() + 1e-2 * a.float().abs().max()
+
+
+def test_rejects_bad_arguments(cuda, lib):
+    import torch
+    x = torch.zeros(2 * 128 * 128, dtype=torch.bfloat16, device=cuda)
+    p = x.data_ptr()
+    f = lib.emmyb200_attention_fwd
+    assert f(2, p, p, p, p, 2, 128, 128, 96, 0.1, None) == -4      # head dim
+    assert f(0, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -4     # f32
+    assert f(2, p, p, p, p, 2, 128, 0, 128, 0.1, None) == -2       # no keys
+    assert f(2, p, p, p, p, 0, 128, 128, 128, 0.1, None) == 0      # no units
+    assert f(2, None, p, p, p, 2, 128, 128, 128, 0.1, None) == -1
