@@ -1,0 +1,402 @@
+"""Stand-in Kernel IR node classes, and builders for the benchmark configurations.
+
+The reference never imports IR classes: it dispatches on `type(node).__name__` and reads attributes
+(`emmyptx/kernel.py:313, 487`; `emmyptx/loops.py:51-63`), and gets the real objects from the tracer
+package `emmy-ml` through `emmy.compiler.graph.Graph.from_dict` (`compile.py:15, 43`). This module
+provides classes with the same names and attributes, so a kernel can be described, serialised to
+`<kernel>.ir.json` and compiled without the tracer; objects from the real tracer are accepted just the
+same, because the matcher here is duck-typed in the same way.
+"""
+from __future__ import annotations
+
+import dataclasses
+from dataclasses import dataclass, field
+from typing import Any
+
+_NODES: dict[str, type] = {}
+
+
+def _node(cls):
+    cls = dataclass(cls)
+    _NODES[cls.__name__] = cls
+    return cls
+
+
+# ---- graph ------------------------------------------------------------------------------------------
+@_node
+class Dim:
+    value: int
+
+    def as_static(self) -> int:
+        return int(self.value)
+
+
+@_node
+class DType:
+    name: str
+
+
+@_node
+class TensorInfo:
+    name: str
+    shape: list
+    dtype: Any
+
+
+@_node
+class Node:
+    op: Any
+    inputs: list = field(default_factory=list)
+    outputs: list = field(default_factory=list)
+
+
+@_node
+class InputOp:
+    name: str = "input"
+
+
+@_node
+class Graph:
+    nodes: dict
+
+    def to_dict(self) -> dict:
+        return to_jsonable(self)
+
+    @staticmethod
+    def from_dict(d: dict) -> "Graph":
+        return from_jsonable(d)
+
+
+def tensor(name: str, shape, dtype: str) -> TensorInfo:
+    return TensorInfo(name, [Dim(int(s)) for s in shape], DType(dtype))
+
+
+# ---- expressions ---------------------------------------------------------------------------------------
+class _Expr:
+    def free_vars(self) -> set:
+        out = set()
+        for f in dataclasses.fields(self):
+            v = getattr(self, f.name)
+            for item in (v if isinstance(v, (list, tuple)) else [v]):
+                if isinstance(item, _Expr):
+                    out |= item.free_vars()
+        return out
+
+
+@_node
+class Literal(_Expr):
+    value: Any
+    dtype: Any = None
+
+
+@_node
+class Var(_Expr):
+    name: str
+
+    def free_vars(self) -> set:
+        return {self.name}
+
+
+@_node
+class BinaryExpr(_Expr):
+    op: str
+    left: Any
+    right: Any
+
+
+@_node
+class TernaryExpr(_Expr):
+    cond: Any
+    if_true: Any
+    if_false: Any
+
+
+@_node
+class CastExpr(_Expr):
+    dtype: str
+    expr: Any
+
+
+@_node
+class FuncCallExpr(_Expr):
+    name: str
+    args: list
+
+
+# ---- statements ------------------------------------------------------------------------------------------
+@_node
+class Op:
+    name: str
+    identity: Any = None
+
+
+@_node
+class Axis:
+    name: str
+    extent: Any
+
+
+@_node
+class KernelOp:
+    name: str
+    body: list
+
+
+@_node
+class Tile:
+    axes: list
+    body: list
+    aux_threads: int = 0
+    block_threads: int = 0
+    raster_group: int = 0
+    raster_axes: Any = None
+    raster_orient: str = "m"
+
+
+@_node
+class Load:
+    names: list
+    input: str
+    index: list
+
+
+@_node
+class Write:
+    output: str
+    index: list
+    values: list
+    atomic: bool = False
+    swizzle: str = "NONE"
+
+
+@_node
+class Assign:
+    name: str
+    op: Any
+    args: list
+    dtype: Any = None
+
+
+@_node
+class Let:
+    name: str
+    value: Any
+    dtype: Any = None
+
+
+@_node
+class Loop:
+    axis: Any
+    body: list
+    unroll: bool = False
+    seed: bool = True
+
+
+@_node
+class Accum:
+    name: str
+    base: Any
+    value: str
+    op: Any
+
+
+@_node
+class Smem:
+    name: str
+    dtype: str
+    extents: list
+    align: int = 16
+
+
+@_node
+class RegFragment:
+    name: str
+    role: str
+    dtype: Any
+    shape: tuple = (16, 8, 16)
+    count: int = 1
+    nregs: Any = None
+
+
+@_node
+class LdmatrixLoad:
+    frag: str
+    role: str
+    src_buffer: str
+    src_index: list
+    ldm: int = 0
+    staged: bool = False
+    b_trans: bool = False
+    pair_frag: Any = None
+    swizzle: str = "NONE"
+    fragment_layout: str = "m16n8k16"
+    byte_slab: bool = False
+    scale_buffer: Any = None
+    gmem_guard: Any = None
+    k_zero: Any = None
+
+
+@_node
+class MmaSyncPtx:
+    c_frag: str
+    a_frag: str
+    b_frag: str
+    shape: tuple = (16, 8, 16)
+    ab_dtype: str = "f16"
+    c_dtype: str = "f32"
+    b_row_major: bool = False
+    sfa_frag: Any = None
+
+
+@_node
+class RegStore:
+    frag: str
+    dst_buffer: str
+    dst_index: list
+    ldm: int = 0
+    row_dim: Any = None
+    col_dim: Any = None
+    m_guard: Any = None
+    n_guard: Any = None
+    atomic: bool = False
+    epilogue: Any = None
+    extra_frags: Any = None
+    swizzle: str = "NONE"
+    fragment_layout: str = "m16n8k16"
+    volta_interleaved: bool = False
+
+
+@_node
+class WarpShuffle:
+    state: list
+    state_b: list
+    combine_states: list
+    length: int = 32
+
+
+# ---- (de)serialisation ----------------------------------------------------------------------------------
+def to_jsonable(x):
+    if dataclasses.is_dataclass(x) and not isinstance(x, type):
+        d = {"__node__": type(x).__name__}
+        for f in dataclasses.fields(x):
+            d[f.name] = to_jsonable(getattr(x, f.name))
+        return d
+    if isinstance(x, dict):
+        return {k: to_jsonable(v) for k, v in x.items()}
+    if isinstance(x, (list, tuple)):
+        return [to_jsonable(v) for v in x]
+    return x
+
+
+def from_jsonable(x):
+    if isinstance(x, dict) and "__node__" in x:
+        cls = _NODES[x["__node__"]]
+        return cls(**{k: from_jsonable(v) for k, v in x.items() if k != "__node__"})
+    if isinstance(x, dict):
+        return {k: from_jsonable(v) for k, v in x.items()}
+    if isinstance(x, list):
+        return [from_jsonable(v) for v in x]
+    return x
+
+
+# ---- builders: the five benchmark configurations as Kernel IR --------------------------------------------
+def _graph(kernel: KernelOp, inputs: list[TensorInfo], outputs: list[TensorInfo]) -> Graph:
+    nodes = {t.name: Node(InputOp(), [], [t]) for t in inputs}
+    nodes[kernel.name] = Node(kernel, [t.name for t in inputs], outputs)
+    return Graph(nodes)
+
+
+def _launch(kernel: KernelOp, arg_names: list[str], cells: int, block: int = 256, smem: int = 0) -> dict:
+    return {"entry": kernel.name, "arg_order": arg_names, "grid": [-(-cells // block), 1, 1], "block": [block, 1, 1],
+            "smem_bytes": smem}
+
+
+def pointwise_kernel(n: int, expr: str = "exp_sin_tanh", name: str = "k_pointwise"):
+    """y = op(x) over a one-axis tile. `exp_sin_tanh` is exp(x) + sin(x) * tanh(x), the statement list the
+    tracer produces for that torch expression: one Load, four Assigns through the op table, one Write."""
+    a0 = Axis("a0", Dim(n))
+    body = [Load(["v0"], "x", [Var("a0")])]
+    if expr == "exp_sin_tanh":
+        body += [Assign("v1", Op("exp"), ["v0"]), Assign("v2", Op("sin"), ["v0"]), Assign("v3", Op("tanh"), ["v0"]),
+                 Assign("v4", Op("multiply"), ["v2", "v3"]), Assign("v5", Op("add"), ["v1", "v4"])]
+        out = "v5"
+    elif expr == "gelu_tanh":
+        body += [Assign("c0", Op("multiply"), ["v0", "v0"]), Assign("c1", Op("multiply"), ["c0", "v0"]),
+                 Assign("c2", Op("multiply"), ["c1", 0.044715]), Assign("c3", Op("add"), ["v0", "c2"]),
+                 Assign("c4", Op("multiply"), ["c3", 0.7978845608028654]), Assign("c5", Op("tanh"), ["c4"]),
+                 Assign("c6", Op("add"), ["c5", 1.0]), Assign("c7", Op("multiply"), ["v0", 0.5]),
+                 Assign("c8", Op("multiply"), ["c7", "c6"])]
+        out = "c8"
+    else:
+        body += [Assign("v1", Op(expr), ["v0"])]
+        out = "v1"
+    body.append(Write("y", [Var("a0")], [out]))
+    k = KernelOp(name, [Tile([a0], body)])
+    g = _graph(k, [tensor("x", [n], "f32")], [tensor("y", [n], "f32")])
+    return g, k, _launch(k, ["x", "y"], n)
+
+
+def index_gather_kernel(n: int, mul: int = 7919, add: int = 13, div: int = 3, shift: int = 2, name: str = "k_gather"):
+    """y[i] = (x[(i*mul + add) % n] // div) ^ (i >> shift), int32."""
+    a0 = Axis("a0", Dim(n))
+    i = Var("a0")
+    idx = BinaryExpr("%", BinaryExpr("+", BinaryExpr("*", i, Literal(mul, "int")), Literal(add, "int")), Literal(n, "int"))
+    body = [Load(["g"], "x", [idx]),
+            Assign("q", Op("floor_divide"), ["g", div], "int"),
+            Let("s", BinaryExpr(">>", i, Literal(shift, "int")), "int"),
+            Assign("r", Op("bitwise_xor"), ["q", "s"], "int"),
+            Write("y", [i], ["r"])]
+    k = KernelOp(name, [Tile([a0], body)])
+    g = _graph(k, [tensor("x", [n], "i32")], [tensor("y", [n], "i32")])
+    return g, k, _launch(k, ["x", "y"], n)
+
+
+def gemm_kernel(m: int, n: int, k: int, dtype: str = "f16", epilogue: str | None = None, b_trans: bool = False,
+                name: str = "k_gemm"):
+    """C = A B on mma.sync cells, as the tracer schedules a 16-bit matmul: accumulator / operand fragments, a K
+    loop of fragment loads and MMAs, a fragment store (optionally with a fused epilogue, which the reference
+    rejects). One warp per 16x8 cell here; the tile sizes of the real schedule do not matter to the matcher."""
+    am, an = Axis("m0", Dim(-(-m // 16))), Axis("n0", Dim(-(-n // 8)))
+    kk = Axis("k0", Dim(-(-k // 16)))
+    row, col = BinaryExpr("*", Var("m0"), Literal(16, "int")), BinaryExpr("*", Var("n0"), Literal(8, "int"))
+    kof = BinaryExpr("*", Var("k0"), Literal(16, "int"))
+    b_index = [col, kof] if b_trans else [kof, col]
+    body = [RegFragment("_c", "c", DType("f32")), RegFragment("_a", "a", DType(dtype)), RegFragment("_b", "b", DType(dtype)),
+            Loop(kk, [LdmatrixLoad("_a", "a", "A", [row, kof]),
+                      LdmatrixLoad("_b", "b", "B", b_index, b_trans=b_trans),
+                      MmaSyncPtx("_c", "_a", "_b", ab_dtype=dtype)]),
+            RegStore("_c", "C", [row, col], epilogue=epilogue)]
+    kern = KernelOp(name, [Tile([am, an], body)])
+    g = _graph(kern, [tensor("A", [m, k], dtype), tensor("B", [n, k] if b_trans else [k, n], dtype)], [tensor("C", [m, n], dtype)])
+    return g, kern, _launch(kern, ["A", "B", "C"], am.extent.value * an.extent.value * 32, block=128)
+
+
+def attention_kernel(units_shape: list[int], seq_q: int, seq_k: int, d: int, dtype: str = "bf16", scale: float | None = None,
+                     name: str = "k_sdpa"):
+    """softmax(Q K^T * scale) V as fused generic statements: two MMA groups with an exp and a row reduction between
+    them. Only the features the matcher keys on are spelled out."""
+    scale = d ** -0.5 if scale is None else scale
+    u = 1
+    for s in units_shape:
+        u *= s
+    ax = [Axis("u0", Dim(u)), Axis("q0", Dim(-(-seq_q // 16)))]
+    body = [RegFragment("_s", "c", DType("f32")), RegFragment("_o", "c", DType("f32")),
+            RegFragment("_q", "a", DType(dtype)), RegFragment("_k", "b", DType(dtype)), RegFragment("_v", "b", DType(dtype)),
+            Loop(Axis("j0", Dim(-(-seq_k // 8))), [
+                LdmatrixLoad("_q", "a", "Q", [Var("u0"), Var("q0"), Literal(0, "int")]),
+                LdmatrixLoad("_k", "b", "K", [Var("u0"), Var("j0"), Literal(0, "int")], b_trans=True),
+                MmaSyncPtx("_s", "_q", "_k", ab_dtype=dtype),
+                Assign("t0", Op("multiply"), ["_s", scale]),
+                WarpShuffle(["mx"], ["mx_b"], [Assign("mx", Op("maximum"), ["mx", "mx_b"])], 4),
+                Assign("t1", Op("subtract"), ["t0", "mx"]), Assign("p", Op("exp"), ["t1"]),
+                WarpShuffle(["sm"], ["sm_b"], [Assign("sm", Op("add"), ["sm", "sm_b"])], 4),
+                LdmatrixLoad("_v", "b", "V", [Var("u0"), Var("j0"), Literal(0, "int")]),
+                MmaSyncPtx("_o", "p", "_v", ab_dtype=dtype)]),
+            Assign("o", Op("divide"), ["_o", "sm"]),
+            RegStore("_o", "O", [Var("u0"), Var("q0"), Literal(0, "int")])]
+    kern = KernelOp(name, [Tile(ax, body)])
+    shp = list(units_shape)
+    g = _graph(kern, [tensor("Q", shp + [seq_q, d], dtype), tensor("K", shp + [seq_k, d], dtype),
+                      tensor("V", shp + [seq_k, d], dtype)], [tensor("O", shp + [seq_q, d], dtype)])
+    return g, kern, _launch(kern, ["Q", "K", "V", "O"], u * ax[1].extent.value * 32, block=128)
+

@@ -1,0 +1,380 @@
+"""Kernel IR -> precompiled sm_100a kernel variant.
+
+Where the reference's `KernelCompiler` prints PTX statement by statement, the replacement ships a fixed set
+of hand-written kernels. This module decides which of them computes a given `KernelOp`, and with which
+parameters -- or that none does, which is a `CompileError` (there is no generic fallback and no CPU path).
+
+Streaming kernels are recognised by behaviour, not by spelling: the cell program (Load / Let / Assign /
+Write under one `Tile`, the statements of `emmyptx/kernel.py:632-822`) is run on a handful of probe cells
+in float64 / exact integers over synthetic buffer contents, and compared with what each kernel variant
+computes for the same cells. Two programs that mean the same thing match the same kernel, however the
+tracer happened to arrange them. Contractions are recognised by their tensor-core statements
+(`RegFragment` / `LdmatrixLoad` / `MmaSyncPtx` / `RegStore`, `emmyptx/mma.py`), whose buffers, layout flags
+and epilogue give the GEMM's parameters; the tile sizes the tracer chose are irrelevant here.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+from .ops import FLOAT_OPS, INT_OPS, INT_OPS_TRUNC, OpError, Program, lower_int_op, lower_op
+
+INT_DTYPES = {"int", "i32", "i64", "int32", "int64", "u32", "u8", "i8"}      # emmyptx/kernel.py:41
+_FUNC_ALIASES = {"fmax": "maximum", "fmin": "minimum", "fabs": "abs"}       # emmyptx/kernel.py:55
+
+
+class Unmatched(Exception):
+    """The IR is well-formed but no kernel variant computes it."""
+
+
+def children(stmt) -> list:
+    out = []
+    for attr in ("body", "else_body", "combine_states"):
+        sub = getattr(stmt, attr, None)
+        if sub is not None and not isinstance(sub, (str, bytes)):
+            out.append(sub)
+    return out
+
+
+def walk(body):
+    """Every statement in `body`, nested ones included (emmyptx/loops.py:51-56)."""
+    for s in body:
+        yield s
+        for sub in children(s):
+            yield from walk(sub)
+
+
+def _kind(x) -> str:
+    return type(x).__name__
+
+
+def _dtype_name(dt):
+    return None if dt is None else getattr(dt, "name", dt)
+
+
+def tensor_table(graph) -> dict:
+    """name -> (shape, dtype) for every tensor the graph knows (emmyptx/kernel.py:122-125)."""
+    out = {}
+    for node in graph.nodes.values():
+        for t in node.outputs:
+            out[t.name] = (tuple(int(d.as_static()) for d in t.shape) or (1,), _dtype_name(t.dtype))
+    return out
+
+
+# ---- probe buffers: contents as a pure function of the element index -------------------------------------
+def _hash(idx: np.ndarray, salt: int) -> np.ndarray:
+    h = (idx.astype(np.uint64) + np.uint64(salt)) * np.uint64(0x9E3779B97F4A7C15)
+    h ^= h >> np.uint64(29)
+    h *= np.uint64(0xBF58476D1CE4E5B9)
+    h ^= h >> np.uint64(32)
+    return h
+
+
+def probe_values(name: str, dtype: str, idx: np.ndarray) -> np.ndarray:
+    salt = sum(ord(c) * 131 ** i for i, c in enumerate(name)) % (2**31)
+    h = _hash(idx, salt)
+    if dtype in ("i32", "i64"):
+        return (h % np.uint64(2**31 + 1)).astype(np.int64) - 2**30
+    return (h % np.uint64(2**24)).astype(np.float64) / 2**24 * 8.0 - 4.0
+
+
+# ---- the cell interpreter -----------------------------------------------------------------------------------
+class CellInterpreter:
+    """Runs a pointwise cell program on `cells` (flat cell ids) with numpy arrays as values."""
+
+    def __init__(self, tensors: dict, cells: np.ndarray, int_ops: dict) -> None:
+        self.tensors, self.cells, self.int_ops = tensors, cells, int_ops
+        self.env: dict = {}
+        self.loads: list = []       # (buffer, flat index array)
+        self.writes: list = []      # (buffer, flat index array, [value arrays])
+        self.program = Program()
+
+    def lookup(self, name):
+        if isinstance(name, bool):
+            return np.full(self.cells.shape, float(name))
+        if isinstance(name, int):
+            return np.full(self.cells.shape, name, dtype=np.int64)
+        if isinstance(name, float):
+            return np.full(self.cells.shape, name, dtype=np.float64)
+        if name not in self.env:
+            raise Unmatched(f"use of undefined name {name!r}")
+        return self.env[name]
+
+    @staticmethod
+    def _is_int(v) -> bool:
+        return np.asarray(v).dtype.kind in "iub"
+
+    def expr(self, e):
+        k = _kind(e)
+        if k == "Literal":
+            if isinstance(e.value, bool):
+                return np.full(self.cells.shape, e.value)
+            dt = _dtype_name(e.dtype)
+            if dt in INT_DTYPES or (dt is None and isinstance(e.value, int)):
+                return np.full(self.cells.shape, int(e.value), dtype=np.int64)
+            return np.full(self.cells.shape, float(e.value), dtype=np.float64)
+        if k == "Var":
+            return self.lookup(e.name)
+        if k == "BinaryExpr":
+            return self.binary(e.op, self.expr(e.left), self.expr(e.right))
+        if k == "TernaryExpr":
+            return np.where(self.truthy(self.expr(e.cond)), self.expr(e.if_true), self.expr(e.if_false))
+        if k == "CastExpr":
+            v = self.expr(e.expr)
+            return np.trunc(v).astype(np.int64) if e.dtype in INT_DTYPES else np.asarray(v, dtype=np.float64)
+        if k == "FuncCallExpr":
+            name = _FUNC_ALIASES.get(e.name, e.name)
+            if name not in FLOAT_OPS:
+                raise OpError(f"elementwise op {name!r} is not supported")
+            return FLOAT_OPS[name][1](*[np.asarray(self.expr(a), dtype=np.float64) for a in e.args])
+        if k == "FlatIndex":
+            return self.flat_index(e.buffer, e.index)
+        raise Unmatched(f"unsupported expression {k}")
+
+    @staticmethod
+    def truthy(v):
+        return np.asarray(v) != 0
+
+    def binary(self, op, a, b):
+        if op in ("&&", "||"):
+            return (self.truthy(a) & self.truthy(b)) if op == "&&" else (self.truthy(a) | self.truthy(b))
+        cmp = {"<": np.less, "<=": np.less_equal, ">": np.greater, ">=": np.greater_equal, "==": np.equal, "!=": np.not_equal}
+        if op in cmp:
+            return cmp[op](a, b)
+        if not (self._is_int(a) and self._is_int(b)):
+            f = {"+": np.add, "-": np.subtract, "*": np.multiply, "/": np.divide, "max": np.maximum, "min": np.minimum}
+            if op not in f:
+                raise Unmatched(f"float operator {op!r} is not supported")
+            return f[op](np.asarray(a, np.float64), np.asarray(b, np.float64))
+        a, b = np.asarray(a, np.int64), np.asarray(b, np.int64)
+        # Index arithmetic is exact (no int32 wrap): for the power-of-two moduli the reference's masks
+        # assume, the wrapped and the exact value agree (emmyptx/intmath.py:108-116, :231-233).
+        if op in ("/", "//"):
+            q = np.abs(a) // np.abs(b)
+            return np.where((a < 0) != (b < 0), -q, q)
+        if op == "%":
+            return np.mod(a, b) if np.all(b > 0) else a - b * np.trunc(a / b).astype(np.int64)
+        f = {"+": np.add, "-": np.subtract, "*": np.multiply, "<<": np.left_shift, ">>": np.right_shift, "&": np.bitwise_and,
+             "|": np.bitwise_or, "^": np.bitwise_xor, "max": np.maximum, "min": np.minimum}
+        if op not in f:
+            raise Unmatched(f"integer operator {op!r} is not supported")
+        return f[op](a, b)
+
+    def flat_index(self, buffer: str, index) -> np.ndarray:
+        """Row-major element offset (emmyptx/kernel.py:410-421)."""
+        index = list(index)
+        if buffer not in self.tensors:
+            raise Unmatched(f"unknown buffer {buffer!r}")
+        shape = self.tensors[buffer][0]
+        if len(shape) != len(index):
+            shape = (1,) * len(index)
+        flat = np.zeros(self.cells.shape, dtype=np.int64)
+        for dim, e in enumerate(index):
+            flat = flat * shape[dim] + np.asarray(self.expr(e), dtype=np.int64)
+        return flat
+
+    def run(self, stmts) -> None:
+        for s in stmts:
+            k = _kind(s)
+            if k == "Load":
+                flat = self.flat_index(s.input, s.index)
+                dtype = self.tensors[s.input][1]
+                for j, name in enumerate(s.names):
+                    self.env[name] = probe_values(s.input, dtype, flat + j)
+                self.loads.append((s.input, flat, len(s.names)))
+            elif k == "Let":
+                v = self.expr(s.value)
+                dt = _dtype_name(s.dtype)
+                if dt is not None:
+                    v = np.trunc(v).astype(np.int64) if dt in INT_DTYPES else np.asarray(v, np.float64)
+                self.env[s.name] = v
+            elif k == "Assign":
+                is_int = _dtype_name(s.dtype) in INT_DTYPES
+                args = [self.lookup(a) for a in s.args]
+                if is_int:
+                    lower_int_op(self.program, s.op.name, list(s.args), s.name)
+                    self.env[s.name] = self.int_ops[s.op.name][1](*[np.asarray(a, np.int64) for a in args])
+                else:
+                    lower_op(self.program, s.op.name, list(s.args), s.name)
+                    self.env[s.name] = FLOAT_OPS[s.op.name][1](*[np.asarray(a, np.float64) for a in args])
+            elif k == "Write":
+                if getattr(s, "atomic", False):
+                    raise Unmatched("atomic writes belong to split-K schedules, which have no variant")
+                self.writes.append((s.output, self.flat_index(s.output, s.index), [self.lookup(v) for v in s.values]))
+            else:
+                raise Unmatched(f"statement {k} inside a streaming tile has no kernel variant")
+
+
+# ---- variants -------------------------------------------------------------------------------------------------
+POINTWISE_F64 = {
+    "exp_sin_tanh": lambda x: np.exp(x) + np.sin(x) * np.tanh(x),
+    "exp": np.exp, "sin": np.sin, "cos": np.cos, "tanh": np.tanh,
+    "gelu_tanh": lambda x: 0.5 * x * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * x**3))),
+}
+
+
+def _int_literals(kernel) -> set:
+    """Every integer constant spelled in the kernel: Literals in expressions and numeric Assign arguments."""
+    found = set()
+
+    def visit(x):
+        if _kind(x) == "Literal" and isinstance(x.value, int) and not isinstance(x.value, bool):
+            found.add(int(x.value))
+        for attr in ("left", "right", "cond", "if_true", "if_false", "expr", "value"):
+            sub = getattr(x, attr, None)
+            if sub is not None and not isinstance(sub, (str, int, float, bool)):
+                visit(sub)
+        for attr in ("args", "index"):
+            for sub in getattr(x, attr, None) or []:
+                if isinstance(sub, int) and not isinstance(sub, bool):
+                    found.add(sub)
+                elif not isinstance(sub, (str, float, bool)):
+                    visit(sub)
+
+    for s in walk(kernel.body):
+        visit(s)
+    return found
+
+
+def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
+    tensors = tensor_table(graph)
+    tiles = [s for s in kernel.body if _kind(s) == "Tile"]
+    if len(kernel.body) != 1 or len(tiles) != 1:
+        raise Unmatched("a streaming kernel is one Tile")
+    tile = tiles[0]
+    n = math.prod(int(a.extent.as_static()) for a in tile.axes)
+    if n > 2**31 - 1:
+        raise Unmatched(f"a tile of {n} cells needs 64-bit indexing")           # emmyptx/kernel.py:556-557
+    rng = np.random.default_rng(0)
+    cells = np.unique(np.concatenate([np.arange(min(n, 96)), rng.integers(0, n, 160), [n - 1]])).astype(np.int64)
+    it = CellInterpreter(tensors, cells, INT_OPS_TRUNC if int_div == "trunc" else INT_OPS)
+    # axis variables: last axis fastest (emmyptx/kernel.py:587-626, without rasterisation)
+    rem = cells.copy()
+    for a in reversed(tile.axes):
+        e = int(a.extent.as_static())
+        it.env[a.name] = rem % e
+        rem = rem // e
+    it.run(tile.body)
+    if len(it.writes) != 1 or len(it.writes[0][2]) != 1:
+        raise Unmatched("streaming variants write one value per cell to one buffer")
+    out_name, out_idx, (value,) = it.writes[0]
+    if not np.array_equal(out_idx, cells) or math.prod(tensors[out_name][0]) != n:
+        raise Unmatched("streaming variants write cell i to element i")
+    buffers = {b for b, _, _ in it.loads}
+    if len(buffers) != 1 or any(cnt != 1 for _, _, cnt in it.loads):
+        raise Unmatched("streaming variants read one input buffer, one element per load")
+    (src,) = buffers
+    src_shape, src_dtype = tensors[src]
+    out_dtype = tensors[out_name][1]
+    idx = it.loads[0][1]
+    if any(not np.array_equal(i, idx) for _, i, _ in it.loads):
+        raise Unmatched("streaming variants read one element per cell")
+    if src_dtype == "f32" and out_dtype == "f32":
+        if not np.array_equal(idx, cells) or math.prod(src_shape) != n:
+            raise Unmatched("float streaming variants read element i for cell i")
+        x = probe_values(src, "f32", cells)
+        got = np.asarray(value, dtype=np.float64)
+        for op, f in POINTWISE_F64.items():
+            if np.allclose(got, f(x), rtol=1e-9, atol=1e-12):
+                return {"variant": "pointwise_f32", "params": {"op": op, "n": n}, "inputs": [src], "outputs": [out_name]}
+        raise Unmatched("no float streaming variant computes this expression "
+                        f"(have: {', '.join(POINTWISE_F64)})")
+    if src_dtype == "i32" and out_dtype == "i32":
+        size = math.prod(src_shape)
+        if size != n:
+            raise Unmatched("the index gather reads a buffer as large as the tile")
+        add = int(idx[cells == 0][0]) % size if 0 in cells else None
+        mul = (int(idx[cells == 1][0]) - add) % size if n > 1 else 0
+        if add is None or not np.array_equal(idx, (cells * mul + add) % size):
+            raise Unmatched("the gather index is not (i * mul + add) mod n")
+        g = probe_values(src, "i32", idx)
+        lits = sorted(_int_literals(kernel))
+        divs = [d for d in lits if d >= 1] or [1]
+        shifts = [s for s in lits if 0 <= s <= 31] + [0]
+        got = np.asarray(value, dtype=np.int64)
+        div = INT_OPS_TRUNC["floor_divide"][1] if int_div == "trunc" else INT_OPS["floor_divide"][1]
+        for d in divs:
+            for sh in dict.fromkeys(shifts):
+                if np.array_equal(got, np.bitwise_xor(div(g, np.int64(d)), cells >> sh)):
+                    return {"variant": "index_gather_i32", "inputs": [src], "outputs": [out_name],
+                            "params": {"n": n, "mul": mul, "add": add, "div": d, "shift": sh, "trunc": int_div == "trunc"}}
+        raise Unmatched("the integer expression is not (x[idx] div d) xor (i >> s)")
+    raise Unmatched(f"no streaming variant for {src_dtype} -> {out_dtype}")
+
+
+def _epilogue_name(ep):
+    if ep is None:
+        return None
+    name = getattr(ep, "name", ep)
+    name = str(name).lower()
+    if name in ("none", ""):
+        return None
+    if name in ("gelu_tanh", "gelu"):
+        return "gelu_tanh"
+    raise Unmatched(f"store epilogue {name!r} has no fused variant (have: gelu_tanh)")
+
+
+def match_contraction(graph, kernel, launch: dict) -> dict:
+    tensors = tensor_table(graph)
+    stmts = list(walk(kernel.body))
+    loads = [s for s in stmts if _kind(s) == "LdmatrixLoad"]
+    mmas = [s for s in stmts if _kind(s) == "MmaSyncPtx"]
+    stores = [s for s in stmts if _kind(s) == "RegStore"]
+    for m in mmas:
+        if tuple(m.shape) != (16, 8, 16) or m.c_dtype != "f32" or m.ab_dtype not in ("f16", "bf16") or m.sfa_frag is not None:
+            raise Unmatched("only f16 / bf16 operands with f32 accumulators are supported")      # emmyptx/mma.py:185-187
+    if len(stores) != 1:
+        raise Unmatched("a contraction kernel stores one output")
+    if stores[0].atomic:
+        raise Unmatched("split-K (atomic) stores have no variant")
+    srcs = list(dict.fromkeys(s.src_buffer for s in loads))
+    out = stores[0].dst_buffer
+    for b in (*srcs, out):
+        if b not in tensors:
+            raise Unmatched(f"unknown buffer {b!r}")
+    dtype = mmas[0].ab_dtype
+    if any(tensors[b][1] != dtype for b in (*srcs, out)):
+        raise Unmatched("operands and output must share the MMA's 16-bit dtype")
+    has_softmax = any(_kind(s) == "Assign" and s.op.name in ("exp", "exp_fast") for s in stmts)
+    if len(srcs) == 3 and has_softmax:
+        q, k, v = (tensors[b][0] for b in srcs)
+        o = tensors[out][0]
+        if not (len(q) >= 2 and q[:-2] == k[:-2] == v[:-2] == o[:-2] and k == v and q == o and q[-1] == k[-1]):
+            raise Unmatched(f"attention shapes do not agree: {q}, {k}, {v} -> {o}")
+        d = q[-1]
+        if d not in (64, 128):
+            raise Unmatched(f"attention head dim {d} has no variant (64, 128)")
+        scale = d ** -0.5
+        floats = [a for s in stmts if _kind(s) == "Assign" and s.op.name == "multiply" for a in s.args
+                  if isinstance(a, float)]
+        if floats:
+            scale = floats[0]
+        return {"variant": "attention_fwd", "inputs": srcs, "outputs": [out],
+                "params": {"dtype": dtype, "units": math.prod(q[:-2]), "seq_q": q[-2], "seq_k": k[-2], "d": d, "scale": scale}}
+    if len(srcs) != 2:
+        raise Unmatched("a GEMM reads two operand buffers")
+    a_loads = [s for s in loads if s.role == "a"]
+    b_loads = [s for s in loads if s.role == "b"]
+    if not a_loads or not b_loads:
+        raise Unmatched("a GEMM loads an `a` and a `b` fragment")
+    a_name, b_name = a_loads[0].src_buffer, b_loads[0].src_buffer
+    b_trans = bool(b_loads[0].b_trans)
+    (a_shape, _), (b_shape, _), (c_shape, _) = tensors[a_name], tensors[b_name], tensors[out]
+    if not (len(a_shape) == len(b_shape) == len(c_shape) == 2):
+        raise Unmatched("batched and broadcast matmuls have no variant yet")
+    m, k = a_shape
+    n = b_shape[0] if b_trans else b_shape[1]
+    if (b_shape[1] if b_trans else b_shape[0]) != k or c_shape != (m, n):
+        raise Unmatched(f"GEMM shapes do not agree: {a_shape} x {b_shape} -> {c_shape}")
+    if k % 8 or n % 8:
+        raise Unmatched("row pitches must be multiples of 8 elements (16-byte TMA strides)")
+    return {"variant": "gemm", "inputs": [a_name, b_name], "outputs": [out],
+            "params": {"dtype": dtype, "m": m, "n": n, "k": k, "b_trans": b_trans, "epilogue": _epilogue_name(stores[0].epilogue)}}
+
+
+def match_kernel(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
+    kinds = {_kind(s) for s in walk(kernel.body)}
+    if "MmaSyncPtx" in kinds:
+        return match_contraction(graph, kernel, launch)
+    return match_streaming(graph, kernel, launch, int_div)

@@ -1,0 +1,117 @@
+"""Run compiled kernels on the local GPU: the counterpart of the reference's `tools/run_local.py`.
+
+Same roles, same names: `init()` (`run_local.py:51-61`), `load(text, entry)` (`:64-72`) and
+`run_kernel(text, k, produced)` (`:75-113`), where `text` is what `compile.py` printed -- PTX in the
+reference, a kernel handle here -- and `k` is the kernel's entry of `meta.json`: `args` in parameter order,
+each with `name`, `dtype`, `shape` and one of `seed` (input number: `default_rng(seed).standard_normal`),
+`data`, `intermediate` (produced by an earlier kernel of the problem) or nothing (zeroed), and `output`.
+Buffers are created the way the reference's runner creates them, live in device memory for the duration of
+the call, and outputs come back as numpy arrays (bf16 widened to float32, as `from_device` does).
+"""
+from __future__ import annotations
+
+import json
+
+import numpy as np
+
+from . import runtime
+
+DTYPES = {"f32": np.float32, "f16": np.float16, "f64": np.float64, "i32": np.int32, "i64": np.int64,
+          "bool": np.bool_, "bf16": np.uint16}
+
+
+def to_device(values, dtype: str) -> np.ndarray:
+    """`values` as the host image of a `dtype` buffer; bf16 is the upper half of the fp32 bits, rounded to
+    nearest even (`tools/run_local.py:31-37`)."""
+    if dtype != "bf16":
+        return np.asarray(values).astype(DTYPES[dtype])
+    bits = np.asarray(values, dtype=np.float32).view(np.uint32)
+    return ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def from_device(raw: np.ndarray, dtype: str) -> np.ndarray:
+    return (raw.astype(np.uint32) << 16).view(np.float32) if dtype == "bf16" else raw
+
+
+def init() -> str:
+    """Make GPU 0 current and return its target name ('sm_100'); raises without a CUDA device."""
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device: the kernels have no CPU path")
+    torch.cuda.set_device(0)
+    major, minor = torch.cuda.get_device_capability(0)
+    runtime.library()
+    return f"sm_{major}{minor}"
+
+
+def load(text: str, entry: str) -> dict:
+    """Parse a kernel handle and check that it is the one for `entry`."""
+    try:
+        handle = json.loads(text)
+    except json.JSONDecodeError as e:
+        raise RuntimeError(f"not a kernel handle: {e}") from None
+    if handle.get("emmyb200_handle") != 1 or handle.get("entry") != entry:
+        raise RuntimeError(f"kernel handle is for entry {handle.get('entry')!r}, asked for {entry!r}")
+    return handle
+
+
+def _torch_view(host: np.ndarray, dtype: str):
+    import torch
+    t = torch.from_numpy(host)
+    return t.view(torch.bfloat16) if dtype == "bf16" else t
+
+
+def run_kernel(text: str, k: dict, produced: dict) -> dict:
+    """Launch one kernel of a problem; return its outputs by name."""
+    import torch
+    handle = load(text, k["entry"])
+    dev = torch.device("cuda", torch.cuda.current_device())
+    bufs, meta = {}, {}
+    for a in k["args"]:
+        if a.get("scalar"):
+            raise RuntimeError(f"scalar argument {a['name']!r}: no kernel variant takes scalars")
+        shape = a["shape"] or [1]
+        if "seed" in a:
+            host = to_device(np.random.default_rng(a["seed"]).standard_normal(shape), a["dtype"])
+        elif "data" in a:
+            host = to_device(np.asarray(a["data"]).reshape(shape), a["dtype"])
+        elif a.get("intermediate"):
+            host = to_device(np.asarray(produced[a["name"]]).reshape(shape), a["dtype"])
+        else:
+            host = np.zeros(shape, DTYPES[a["dtype"]])
+        bufs[a["name"]] = _torch_view(np.ascontiguousarray(host), a["dtype"]).to(dev)
+        meta[a["name"]] = a
+    order = [a["name"] for a in k["args"]]
+    if order != handle["arg_order"]:
+        raise RuntimeError(f"kernel arguments {order} do not match the handle's arg_order {handle['arg_order']}")
+    launch(handle, bufs)
+    torch.cuda.synchronize()
+    if runtime.device_status() != 0:
+        raise RuntimeError("a bounded device-side wait expired")
+    outputs = {}
+    for a in k["args"]:
+        if a.get("output"):
+            t = bufs[a["name"]]
+            raw = (t.view(torch.uint16) if a["dtype"] == "bf16" else t).cpu().numpy()
+            outputs[a["name"]] = from_device(raw, a["dtype"])
+    return outputs
+
+
+def launch(handle: dict, bufs: dict, stream=None) -> None:
+    """Enqueue the handle's kernel on buffers (CUDA tensors by argument name)."""
+    p, v = handle["params"], handle["variant"]
+    ins = [bufs[n] for n in handle["inputs"]]
+    out = bufs[handle["outputs"][0]]
+    if v == "pointwise_f32":
+        runtime.pointwise(p["op"], ins[0].reshape(-1), out=out.reshape(-1), stream=stream)
+    elif v == "index_gather_i32":
+        runtime.index_gather(ins[0].reshape(-1), p["mul"], p["add"], p["div"], p["shift"], p["trunc"], out=out.reshape(-1),
+                             stream=stream)
+    elif v == "gemm":
+        runtime.gemm(ins[0], ins[1], epilogue=p["epilogue"], b_is_nk=p["b_trans"], out=out, stream=stream)
+    elif v == "attention_fwd":
+        shp = (p["units"], -1, p["d"])
+        runtime.attention(ins[0].reshape(shp), ins[1].reshape(shp), ins[2].reshape(shp), scale=p["scale"],
+                          out=out.reshape(shp), stream=stream)
+    else:
+        raise RuntimeError(f"unknown kernel variant {v!r}")

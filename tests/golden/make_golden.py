@@ -1,0 +1,38 @@
+"""Golden vectors: the reference's own PTX (tests/golden/*.ref.ptx) executed on the CPU by
+oracle/ptx_interp.py on the seeded inputs of oracle/inputs.py.
+
+    python tests/golden/make_golden.py
+
+Writes tests/golden/golden.npz: for each case the input seed/size and the output the reference's kernel
+produces. Integer outputs are exact; float outputs are the reference's algorithm with its three hardware
+approximations evaluated correctly rounded (see ptx_interp.py). Regenerate only together with the .ref.ptx
+files (make_reference_ptx.py, which needs the reference checkout).
+"""
+import json
+import sys
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE.parent.parent))
+from oracle import inputs, ptx_interp  # noqa: E402
+
+manifest = json.loads((HERE / "reference_ptx_manifest.json").read_text())
+out = {}
+for name, info in manifest.items():
+    n = info["tensors"]["x"]["shape"][0]
+    if n > 2**20 or (name.startswith("c1") and n > 4096 and False):
+        continue
+    x = inputs.c2_input(n) if info["tensors"]["x"]["dtype"] == "i32" else inputs.c1_input(n)
+    y = np.zeros_like(x)
+    grid, block = info["launch"]["grid"][0], info["launch"]["block"][0]
+    ptx_interp.run_entry((HERE / f"{name}.ref.ptx").read_text(), {"x": x, "y": y}, grid, block)
+    if n > 65536:                         # keep the fixture small: a strided sample of the large cases
+        keep = np.arange(0, n, n // 4096)
+        out[f"{name}.index"] = keep.astype(np.int64)
+        y = y[keep]
+    out[f"{name}.y"] = y
+    print(name, y[:4])
+np.savez_compressed(HERE / "golden.npz", **out)
+print("wrote", HERE / "golden.npz", (HERE / "golden.npz").stat().st_size, "bytes")

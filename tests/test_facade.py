@@ -1,0 +1,129 @@
+"""The kernel-builder API (compile.py, emmyptx.kernel) on CPU: which IR matches which kernel variant.
+
+Mirrors how the reference is driven (compile.py:34-57; tools/check_torch.py:289 runs it as a subprocess on
+<entry>.ir.json next to meta.json) with the artefact being a kernel handle instead of PTX.
+"""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+from emmyptx import ir
+from emmyptx.kernel import CompileError, KernelCompiler, algorithmic_work, compile_kernel
+
+ROOT = Path(__file__).resolve().parent.parent
+COMPILE = ROOT / "emmy-ptx-compiler_b200" / "compile.py"
+
+
+def handle(built, **kw):
+    g, k, launch = built
+    return json.loads(KernelCompiler(g, k, launch, **kw).compile() if kw else compile_kernel(g, k, launch))
+
+
+def test_the_five_configurations_match_their_kernels():
+    h = handle(ir.pointwise_kernel(2**20))
+    assert (h["variant"], h["params"]) == ("pointwise_f32", {"op": "exp_sin_tanh", "n": 2**20})
+    assert algorithmic_work(h) == (8.0 * 2**20, "B")
+    h = handle(ir.index_gather_kernel(2**26))
+    assert h["variant"] == "index_gather_i32"
+    assert h["params"] == {"n": 2**26, "mul": 7919, "add": 13, "div": 3, "shift": 2, "trunc": False}
+    assert algorithmic_work(h) == (8.0 * 2**26, "B")
+    h = handle(ir.gemm_kernel(4096, 4096, 4096, "f16"))
+    assert h["params"] == {"dtype": "f16", "m": 4096, "n": 4096, "k": 4096, "b_trans": False, "epilogue": None}
+    assert algorithmic_work(h) == (2.0 * 4096**3, "flop")
+    h = handle(ir.gemm_kernel(16384, 16384, 16384, "bf16", "gelu_tanh"))
+    assert h["params"]["epilogue"] == "gelu_tanh" and h["params"]["dtype"] == "bf16"
+    h = handle(ir.attention_kernel([16, 16], 4096, 4096, 128))
+    assert h["variant"] == "attention_fwd" and h["params"]["units"] == 256 and h["params"]["d"] == 128
+    assert abs(h["params"]["scale"] - 128 ** -0.5) < 1e-12
+    assert algorithmic_work(h) == (4.0 * 256 * 4096 * 4096 * 128, "flop")
+
+
+def test_matching_is_by_meaning_not_by_spelling():
+    """The same expression arranged differently (operands commuted, tanh's argument named differently, the
+    modulus written as a mask) lands on the same variant."""
+    g, k, launch = ir.pointwise_kernel(1024)
+    body = k.body[0].body
+    body[4].args = ["v3", "v2"]            # tanh * sin
+    body[5].args = ["v4", "v1"]            # product + exp
+    assert handle((g, k, launch))["params"]["op"] == "exp_sin_tanh"
+    g, k, launch = ir.index_gather_kernel(2**12)
+    k.body[0].body[0].index[0].op = "&"
+    k.body[0].body[0].index[0].right = ir.Literal(2**12 - 1, "int")
+    assert handle((g, k, launch))["params"]["mul"] == 7919 % 2**12     # only mul mod n is observable
+    assert handle(ir.pointwise_kernel(512, "gelu_tanh"))["params"]["op"] == "gelu_tanh"
+
+
+def test_gather_parameters_are_recovered():
+    h = handle(ir.index_gather_kernel(10**6 + 3, mul=65537, add=12345, div=5, shift=4))
+    assert h["params"] == {"n": 10**6 + 3, "mul": 65537, "add": 12345, "div": 5, "shift": 4, "trunc": False}
+    assert handle(ir.index_gather_kernel(2**16), int_div="trunc")["params"]["trunc"] is True
+
+
+def test_layout_flags_and_ragged_shapes():
+    assert handle(ir.gemm_kernel(64, 512, 256, "f16", None, True))["params"]["b_trans"] is True       # m_f16_linear
+    assert handle(ir.gemm_kernel(100, 72, 200, "f16"))["params"]["m"] == 100                           # m_f16_mm_odd
+
+
+def test_unsupported_ir_is_a_compile_error():
+    with pytest.raises(CompileError, match="no float streaming variant"):
+        handle(ir.pointwise_kernel(100, "erf"))
+    g, k, launch = ir.pointwise_kernel(100, "exp")
+    k.body[0].body[1].op = ir.Op("frobnicate")
+    with pytest.raises(CompileError, match="not supported"):          # OpError surfaces as CompileError
+        handle((g, k, launch))
+    with pytest.raises(CompileError, match="sm_100a only"):
+        KernelCompiler(*ir.pointwise_kernel(64), target="sm_89")
+    with pytest.raises(CompileError, match="epilogue"):
+        handle(ir.gemm_kernel(64, 64, 64, "f16", "swish"))
+    with pytest.raises(CompileError, match="multiples of 8"):
+        handle(ir.gemm_kernel(64, 60, 64, "f16"))
+    g, k, launch = ir.gemm_kernel(64, 64, 64, "f16")
+    k.body[0].body[3].body[2].c_dtype = "f16"
+    with pytest.raises(CompileError, match="f32 accumulators"):
+        handle((g, k, launch))
+    g, k, launch = ir.pointwise_kernel(64)
+    launch["arg_order"] = ["x", "z"]
+    with pytest.raises(CompileError, match="arg_order"):
+        handle((g, k, launch))
+    g, k, launch = ir.pointwise_kernel(64)
+    k.body[0].body.append(ir.Write("y", [ir.Var("a0")], ["v1"], atomic=True))
+    with pytest.raises(CompileError, match="atomic"):
+        handle((g, k, launch))
+
+
+def test_compile_py_command_line(tmp_path):
+    g, k, launch = ir.index_gather_kernel(2**16, name="k_idx")
+    (tmp_path / "k_idx.ir.json").write_text(json.dumps(g.to_dict()))
+    (tmp_path / "meta.json").write_text(json.dumps({"kernels": [dict(launch, args=[])]}))
+    r = subprocess.run([sys.executable, str(COMPILE), str(tmp_path / "k_idx.ir.json")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    h = json.loads(r.stdout)
+    assert h["entry"] == "k_idx" and h["variant"] == "index_gather_i32" and h["arg_order"] == ["x", "y"]
+    r = subprocess.run([sys.executable, str(COMPILE), str(tmp_path / "k_idx.ir.json"), "--int-div", "trunc", "--level", "0"],
+                       capture_output=True, text=True)
+    assert json.loads(r.stdout)["params"]["trunc"] is True
+    # without meta.json the launch is guessed from the graph (compile.py:21-31)
+    (tmp_path / "meta.json").unlink()
+    r = subprocess.run([sys.executable, str(COMPILE), str(tmp_path / "k_idx.ir.json")], capture_output=True, text=True)
+    assert json.loads(r.stdout)["arg_order"] == ["x", "y"]
+    # unsupported IR: non-zero exit, message on stderr, nothing on stdout
+    g, k, launch = ir.pointwise_kernel(64, "erf", name="k_erf")
+    (tmp_path / "k_erf.ir.json").write_text(json.dumps(g.to_dict()))
+    r = subprocess.run([sys.executable, str(COMPILE), str(tmp_path / "k_erf.ir.json")], capture_output=True, text=True)
+    assert r.returncode != 0 and "compile error" in r.stderr and r.stdout == ""
+    # two kernels in one file
+    g2, k2, _ = ir.pointwise_kernel(64, "exp", name="k_exp")
+    g.nodes["k_exp"] = g2.nodes["k_exp"]
+    (tmp_path / "two.ir.json").write_text(json.dumps(g.to_dict()))
+    r = subprocess.run([sys.executable, str(COMPILE), str(tmp_path / "two.ir.json")], capture_output=True, text=True)
+    assert r.returncode != 0 and "expected one KernelOp" in r.stderr
+
+
+def test_ir_json_round_trip():
+    g, k, _ = ir.gemm_kernel(128, 256, 64, "bf16", "gelu_tanh")
+    g2 = ir.Graph.from_dict(json.loads(json.dumps(g.to_dict())))
+    assert g2.to_dict() == g.to_dict()
+    assert type(g2.nodes["k_gemm"].op).__name__ == "KernelOp"

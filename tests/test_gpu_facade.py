@@ -1,0 +1,109 @@
+"""End to end through the reference-facing API, the way the reference's harness drives it
+(tools/check_torch.py:281-295): IR file + meta.json -> `compile.py` as a subprocess -> the artefact text ->
+`run_local.run_kernel(text, k, produced)` -> compare with the float64 oracle on the same seeded inputs.
+Also: the kernels against the committed golden vectors (the reference's own output)."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from emmyptx import ir, run_local
+from oracle import inputs, reference
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+COMPILE = ROOT / "emmy-ptx-compiler_b200" / "compile.py"
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def compile_and_run(tmp_path, built, args, extra=()):
+    g, k, launch = built
+    (tmp_path / f"{k.name}.ir.json").write_text(json.dumps(g.to_dict()))
+    entry = dict(launch, args=args)
+    (tmp_path / "meta.json").write_text(json.dumps({"kernels": [entry]}))
+    r = subprocess.run([sys.executable, str(COMPILE), str(tmp_path / f"{k.name}.ir.json"), *extra], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert run_local.init() == "sm_100"
+    return run_local.run_kernel(r.stdout, entry, {})
+
+
+def seeded(seed, shape, dtype="f32"):
+    """Graph input number `seed` as the reference's runner makes it (tools/run_local.py:86-87)."""
+    return run_local.to_device(np.random.default_rng(seed).standard_normal(shape), dtype)
+
+
+def test_pointwise_through_the_facade(tmp_path, cuda):
+    n = 50_000
+    out = compile_and_run(tmp_path, ir.pointwise_kernel(n), [
+        {"name": "x", "dtype": "f32", "shape": [n], "seed": 0}, {"name": "y", "dtype": "f32", "shape": [n], "output": True}])
+    x = seeded(0, [n])
+    assert reference.compare(out["y"], reference.c1_f64(x), 1e-5, 1e-5)["ok"]
+
+
+def test_gather_through_the_facade_both_division_modes(tmp_path, cuda):
+    n = 2**18
+    x = inputs.c2_input(n)
+    args = [{"name": "x", "dtype": "i32", "shape": [n], "data": x.tolist()}, {"name": "y", "dtype": "i32", "shape": [n], "output": True}]
+    out = compile_and_run(tmp_path, ir.index_gather_kernel(n), args)
+    assert np.array_equal(out["y"], reference.c2_reference(x))
+    out = compile_and_run(tmp_path, ir.index_gather_kernel(n), args, extra=("--int-div", "trunc"))
+    assert np.array_equal(out["y"], reference.c2_reference(x, trunc=True))
+
+
+@pytest.mark.parametrize("dtype,epilogue,b_trans,tol", [("f16", None, False, (2e-2, 1e-1)), ("bf16", None, False, (5e-2, 5e-1)),
+                                                         ("f16", None, True, (2e-2, 1e-1)), ("bf16", "gelu_tanh", False, (5e-2, 5e-1))])
+def test_gemm_through_the_facade_reference_tolerances(tmp_path, cuda, dtype, epilogue, b_trans, tol):
+    """Un-normalised randn operands and the reference's tensor-core tolerances (tools/torch_cases/matmul.py:5-7)."""
+    import torch
+    m, n, k = 256, 512, 512
+    bshape = [n, k] if b_trans else [k, n]
+    out = compile_and_run(tmp_path, ir.gemm_kernel(m, n, k, dtype, epilogue, b_trans), [
+        {"name": "A", "dtype": dtype, "shape": [m, k], "seed": 0}, {"name": "B", "dtype": dtype, "shape": bshape, "seed": 1},
+        {"name": "C", "dtype": dtype, "shape": [m, n], "output": True}])
+    td = torch.float16 if dtype == "f16" else torch.bfloat16
+    a = torch.from_numpy(np.random.default_rng(0).standard_normal((m, k)).astype(np.float32)).to(td)
+    b = torch.from_numpy(np.random.default_rng(1).standard_normal(bshape).astype(np.float32)).to(td)
+    ref = reference.gemm_reference(a, b, epilogue, b_is_nk=b_trans, double=True).numpy()
+    res = reference.compare(np.asarray(out["C"], dtype=np.float64), ref, *tol)
+    assert res["ok"], res
+
+
+def test_attention_through_the_facade(tmp_path, cuda):
+    import torch
+    shp = [2, 3, 256, 128]
+    out = compile_and_run(tmp_path, ir.attention_kernel([2, 3], 256, 256, 128, "bf16"), [
+        {"name": n, "dtype": "bf16", "shape": shp, "seed": i} for i, n in enumerate("QKV")] +
+        [{"name": "O", "dtype": "bf16", "shape": shp, "output": True}])
+    q, k, v = (torch.from_numpy(np.random.default_rng(i).standard_normal(shp).astype(np.float32)).bfloat16() for i in range(3))
+    ref = reference.attention_reference(q, k, v, double=True).numpy()
+    assert reference.compare(out["O"].reshape(shp).astype(np.float64), ref, 1e-2, 1e-2)["ok"]       # HALF class
+
+
+def test_kernels_against_the_reference_golden_vectors(cuda):
+    """golden.npz is the reference's own PTX executed on these inputs. Integer kernel in the reference's
+    (truncating) mode: bit for bit. Float kernels: within the reference's tolerance class of each other."""
+    import torch
+    from emmyptx import runtime
+    g = np.load(GOLDEN / "golden.npz")
+    x = inputs.c2_input(2**16)
+    y = runtime.index_gather(torch.from_numpy(x).to(cuda), 7919, 13, 3, 2, trunc=True).cpu().numpy()
+    assert np.array_equal(y, g["c2_gather_n65536.y"])
+    x = inputs.c2_input(2**20)
+    y = runtime.index_gather(torch.from_numpy(x).to(cuda), 7919, 13, 3, 2, trunc=True).cpu().numpy()
+    assert np.array_equal(y[g["c2_gather_n1048576.index"]], g["c2_gather_n1048576.y"])
+    xf = inputs.c1_input(4096)
+    for case, op in (("c1_exp_sin_tanh_n4096", "exp_sin_tanh"), ("p_exp_n4096", "exp"), ("p_tanh_n4096", "tanh"), ("p_sin_n4096", "sin")):
+        y = runtime.pointwise(op, torch.from_numpy(xf).to(cuda)).cpu().numpy()
+        assert reference.compare(y, g[f"{case}.y"], 1e-5, 1e-5)["ok"], case
+
+
+def test_handle_for_another_entry_is_refused(cuda):
+    from emmyptx.kernel import compile_kernel
+    text = compile_kernel(*ir.pointwise_kernel(64))
+    with pytest.raises(RuntimeError, match="asked for"):
+        run_local.load(text, "some_other_entry")
+    with pytest.raises(RuntimeError, match="not a kernel handle"):
+        run_local.load(".version 8.0", "k_pointwise")
