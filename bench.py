@@ -133,12 +133,25 @@ class GemmWorkload(Workload):
         self.b = (torch.randn(k, n, device=dev, generator=g, dtype=torch.float32) / k**0.5).to(td)
         g.manual_seed(1000 + rank)
         self.a = (torch.randn(self.rows, k, device=dev, generator=g, dtype=torch.float32) / k**0.5).to(td)
-        self.c_full = torch.empty(m, n, device=dev, dtype=td)
-        self.c = self.c_full[rank * self.rows:(rank + 1) * self.rows]
         self.gather = gather and world > 1
         self.host = None
+        self.mode = os.environ.get("EMMYB200_BENCH_GATHER", "fused")       # "fused" (kernel stores to peers) or "nccl"
+        if self.gather and self.mode == "fused":
+            # The full C lives in peer-mapped memory on every rank; each rank's kernel writes its rows into all of them.
+            from emmyptx import shard
+            self.c_full, self.peers = shard.peer_mapped_empty((m, n), td, dev)
+            off = rank * self.rows * n * self.c_full.element_size()
+            own = self.c_full.data_ptr() + off
+            self.dst = [own] + [p + off for r, p in enumerate(self.peers.buffer_ptrs) if r != rank]
+        else:
+            self.c_full = torch.empty(m, n, device=dev, dtype=td)
+        self.c = self.c_full[rank * self.rows:(rank + 1) * self.rows]
 
     def step(self):
+        if self.gather and self.mode == "fused":
+            self.rt.gemm_allgather(self.a, self.b, self.dst, self.n, epilogue=self.epilogue)
+            self.peers.barrier()                # every rank's rows have landed everywhere
+            return
         self.rt.gemm(self.a, self.b, epilogue=self.epilogue, out=self.c)
         if self.gather:
             import torch.distributed as dist
@@ -146,6 +159,12 @@ class GemmWorkload(Workload):
 
     def kernel_only(self):
         self.rt.gemm(self.a, self.b, epilogue=self.epilogue, out=self.c)
+
+    @property
+    def collective(self):
+        if self.mode == "fused":
+            return "fused: the GEMM's TMA stores write each output piece to every peer's C over NVLink, then a signal barrier"
+        return "nccl all_gather of the output shards"
 
     def work_per_step(self):
         return 2.0 * self.m * self.n * self.k
@@ -268,17 +287,21 @@ class AttentionWorkload(Workload):
         self.host["o"].copy_(self.o, non_blocking=True)
 
 
-def make_workload(name, rank, world, dev):
+def make_workload(name, rank, world, dev, size=None):
+    """`size` overrides the configuration's extent (GEMM M=N=K, attention units, streaming elements): used for
+    small profiler captures of the same kernels, never for the reported line."""
     if name == "c4":
-        return GemmWorkload("c4", 16384, 16384, 16384, "bf16", "gelu_tanh", rank, world, dev)
+        s = size or 16384
+        return GemmWorkload("c4", s, s, s, "bf16", "gelu_tanh", rank, world, dev)
     if name == "c3":
-        return GemmWorkload("c3", 4096, 4096, 4096, "f16", None, rank, world, dev)
+        s = size or 4096
+        return GemmWorkload("c3", s, s, s, "f16", None, rank, world, dev)
     if name == "c5":
-        return AttentionWorkload(256, 4096, 128, rank, world, dev)
+        return AttentionWorkload(size or 256, 4096, 128, rank, world, dev)
     if name == "c1":
-        return PointwiseWorkload(2**20, rank, world, dev)
+        return PointwiseWorkload(size or 2**20, rank, world, dev)
     if name == "c2":
-        return GatherWorkload(2**26, rank, world, dev)
+        return GatherWorkload(size or 2**26, rank, world, dev)
     raise SystemExit(f"unknown workload {name!r}")
 
 
@@ -420,6 +443,8 @@ def main() -> int:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=tuple(WORKLOADS), default="c4")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads and the CPU baseline")
+    ap.add_argument("--size", type=int, default=None,
+                    help="override the workload's extent (profiler captures on a small case); the line is marked")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -441,7 +466,7 @@ def main() -> int:
     from emmyptx import runtime
     runtime.library()
 
-    wl = make_workload(args.workload, rank, world, dev)
+    wl = make_workload(args.workload, rank, world, dev, args.size)
     pk, pk_kind = peaks()
 
     # kernel-only time for the roofline (CUDA events on the launching stream, same steps)
@@ -477,9 +502,9 @@ def main() -> int:
         "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype,
         "data": "synthetic",
-        "config": {"workload": WORKLOADS[args.workload], "l2": "inputs larger than L2" if args.workload not in ("c1",) else
+        "config": {"workload": WORKLOADS[args.workload] + (f" [SIZE OVERRIDE {args.size}: not the benchmark configuration]" if args.size else ""), "l2": "inputs larger than L2" if args.workload not in ("c1",) else
                    "8 MiB working set, L2-resident by construction of the configuration", "parallelism": f"rows/{world}",
-                   "collective": "nccl all_gather of the output shards" if world > 1 else "none"},
+                   "collective": "none" if world == 1 else getattr(wl, "collective", "nccl all_gather of the output shards")},
         "roofline": {"bound": "tensor" if wl.bound == "tensor" else "hbm", "achieved": achieved, "peak": peak, "unit": roof_unit,
                      "frac": achieved / peak, "traffic": traffic, "peak_source": peak_note, "kernel_ms": k_ms},
         "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},

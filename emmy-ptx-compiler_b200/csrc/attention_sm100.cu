@@ -168,7 +168,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         float l_run = 0.0f;               // running row sum
         bool ok = true;
         for (int j = 0; j < kv_tiles && ok; ++j) {
-            if (!(ok = bounded_wait(wctx, s_full, j & 1, 0x02070000u | (j & 0xffff)))) break;
+            ok = __all_sync(0xffffffffu, bounded_wait(wctx, s_full, j & 1, 0x02070000u | (j & 0xffff)));      // warp-uniform
+            if (!ok) break;
             ptx::tc_fence_after_sync();
             const int valid = p.seq_k - j * kTileK;             // keys of this tile inside the sequence
             float m_tile = -CUDART_INF_F;
@@ -230,7 +231,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(p_full);
         }
-        if (ok && (ok = bounded_wait(wctx, o_full, 0, 0x02080000u))) {
+        if (ok && __all_sync(0xffffffffu, bounded_wait(wctx, o_full, 0, 0x02080000u))) {
             ptx::tc_fence_after_sync();
             const float inv = 1.0f / l_run;
             const int row = qt * kTileQ + quarter * 32 + lane;

@@ -14,8 +14,11 @@
 //     one of two accumulator buffers in tensor memory, and releases stages / publishes
 //     accumulators with tcgen05.commit;
 //   * warps 2-5 drain the other accumulator buffer (tcgen05.ld), apply the epilogue on the fp32
-//     values, round once to the output type and store 16-byte vectors, overlapping the next
-//     tile's main loop.
+//     values, round once to the output type, stage 128 x 64 pieces in swizzled shared memory and
+//     hand them to TMA stores, overlapping the next tile's main loop. A store goes to every
+//     destination tensor of the launch: the local C, and -- when the rows of C are sharded over
+//     several GPUs -- the same rows of each peer's C over NVLink, which is the all-gather of the
+//     output done by the kernel that produces it.
 //
 // B may be row-major K x N (an "MN-major" operand: TMA boxes of 64 N-elements per K row, and
 // the MMA told to transpose) or row-major N x K (K-major, like A).
@@ -37,16 +40,24 @@ struct GemmSmem {
     static constexpr int kBBytes = BN * kBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = (BN == 256) ? 4 : (BN == 192 ? 5 : 6);
+    static constexpr int kOutBytes = kBM * 64 * 2;                                // one 128 x 64 output piece
+    static constexpr int kOutOffset = kStages * kStageBytes;
+    static constexpr int kBarOffset = kOutOffset + 2 * kOutBytes;
     static constexpr int kBarrierBytes = 256;
-    static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;   // + alignment slack
+    static constexpr int kTotal = kBarOffset + kBarrierBytes + 1024;              // + alignment slack
 };
 
+constexpr int kMaxDst = 8;
+
 struct GemmParams {
-    void* C;
-    int64_t ldc;
     int M, N, K;
     int m_blocks, n_blocks;
+    int n_dst;              // destinations of every output piece (1 = the local C only)
     uint32_t* status;
+};
+
+struct OutMaps {
+    CUtensorMap m[kMaxDst];
 };
 
 __device__ uint32_t g_gemm_status;
@@ -84,27 +95,24 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     }
 }
 
-template <bool BF16>
-__device__ __forceinline__ void store_scalar(void* C, int64_t off, float v) {
-    if constexpr (BF16) reinterpret_cast<__nv_bfloat16*>(C)[off] = __float2bfloat16_rn(v);
-    else reinterpret_cast<__half*>(C)[off] = __float2half_rn(v);
-}
-
 template <int BN, bool BF16, int EPI, bool B_NK>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ OutMaps out, GemmParams p) {
     using S = GemmSmem<BN>;
     constexpr int kStages = S::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-    const uint32_t bar_base = smem_base + kStages * S::kStageBytes;
+    const uint32_t out_smem = smem_base + S::kOutOffset;
+    const uint32_t bar_base = smem_base + S::kBarOffset;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
     auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
     auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 2 + s); };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages * S::kStageBytes + 8 * (2 * kStages + 4));
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + S::kBarOffset + 8 * (2 * kStages + 4));
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* epi_ok = tmem_slot + 2;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (p.K + kBK - 1) / kBK;
@@ -190,50 +198,65 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ---- epilogue: 4 warps, warp w owns tensor-memory lanes 32 (w % 4) .. +32 -----------------
         const int quarter = warp & 3;
-        uint32_t acc_it = 0;
+        const int row_in_tile = quarter * 32 + lane;
+        const bool issuer = threadIdx.x == 64;                   // first epilogue thread: owns the TMA stores
+        uint32_t acc_it = 0, piece = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++acc_it) {
             int mb, nb;
             tile_coords(t, p.m_blocks, p.n_blocks, mb, nb);
             const int as = acc_it & 1;
             const uint32_t aph = (acc_it >> 1) & 1;
-            if (!(ok = bounded_wait(wctx, acc_full_bar(as), aph, 0x01040000u | as))) break;
+            // One thread waits; the outcome reaches the four warps through shared memory, so they all
+            // take the same path into the named barriers below.
+            if (issuer) *epi_ok = bounded_wait(wctx, acc_full_bar(as), aph, 0x01040000u | as) ? 1u : 0u;
+            ptx::named_barrier(1, 128);
+            ok = *epi_ok != 0;
+            if (!ok) break;
             ptx::tc_fence_after_sync();
-            const int row = mb * kBM + quarter * 32 + lane;
-            const int64_t row_off = (int64_t)row * p.ldc;
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(t_row + c, r);
-                ptx::tmem_ld_wait();
-                const int col0 = nb * BN + c;
-                if (row < p.M && col0 < p.N) {
-                    float v[32];
+            for (int c = 0; c < BN; c += 64, ++piece) {
+                const uint32_t stage = out_smem + (piece & 1) * S::kOutBytes;
+                // the stores that last read this staging buffer (two pieces ago) must be done with it
+                if (issuer) ptx::tma_store_wait_read<1>();
+                ptx::named_barrier(1, 128);
+                const uint32_t row_smem = stage + row_in_tile * 128;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float f = __uint_as_float(r[j]);
-                        v[j] = (EPI == EMMYB200_EPI_GELU_TANH) ? gelu_tanh_fast(f) : f;
-                    }
-                    if (col0 + 32 <= p.N) {
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32(t_row + c + 32 * h, r);
+                    ptx::tmem_ld_wait();
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint4 o;
-                            o.x = pack2<BF16>(v[8 * q + 0], v[8 * q + 1]);
-                            o.y = pack2<BF16>(v[8 * q + 2], v[8 * q + 3]);
-                            o.z = pack2<BF16>(v[8 * q + 4], v[8 * q + 5]);
-                            o.w = pack2<BF16>(v[8 * q + 6], v[8 * q + 7]);
-                            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.C) + row_off + col0 + 8 * q) = o;
+                    for (int q = 0; q < 4; ++q) {
+                        float v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float f = __uint_as_float(r[8 * q + j]);
+                            v[j] = (EPI == EMMYB200_EPI_GELU_TANH) ? gelu_tanh_fast(f) : f;
                         }
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.N; ++j) store_scalar<BF16>(p.C, row_off + col0 + j, v[j]);
+                        // 16-byte slot (4h + q) of the row, at its 128-byte-swizzle position
+                        const uint32_t slot = (uint32_t)(4 * h + q) ^ (uint32_t)(row_in_tile & 7);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_smem + slot * 16),
+                                     "r"(pack2<BF16>(v[0], v[1])), "r"(pack2<BF16>(v[2], v[3])),
+                                     "r"(pack2<BF16>(v[4], v[5])), "r"(pack2<BF16>(v[6], v[7]))
+                                     : "memory");
                     }
                 }
+                if (c + 64 >= BN) {                              // accumulator fully read: hand it back
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(acc_empty_bar(as));
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::named_barrier(1, 128);
+                if (issuer && nb * BN + c < p.N) {
+                    for (int d = 0; d < p.n_dst; ++d) ptx::tma_store_2d(&out.m[d], stage, nb * BN + c, mb * kBM);
+                }
+                if (issuer) ptx::tma_store_commit();
             }
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(acc_empty_bar(as));
         }
+        if (issuer) ptx::tma_store_wait<0>();
     }
 
     // ---- teardown -------------------------------------------------------------------------------
@@ -313,31 +336,37 @@ int gemm_read_status(uint32_t* out) {
 }
 
 template <int BN, bool BF16, int EPI, bool B_NK>
-static int launch_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
-                       int64_t ldc, cudaStream_t stream) {
+static int launch_gemm(const void* A, const void* B, void* const* C, int n_dst, int64_t M, int64_t N, int64_t K, int64_t lda,
+                       int64_t ldb, int64_t ldc, cudaStream_t stream) {
     using S = GemmSmem<BN>;
     CUtensorMap map_a, map_b;
+    OutMaps out;
     int rc = make_tensor_map_2d(&map_a, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBM, kBK);
     if (rc != EMMYB200_OK) return rc;
     rc = B_NK ? make_tensor_map_2d(&map_b, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, kBK)
               : make_tensor_map_2d(&map_b, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, kBK, 64);
     if (rc != EMMYB200_OK) return rc;
+    for (int d = 0; d < kMaxDst; ++d) {
+        rc = make_tensor_map_2d(&out.m[d], C[d < n_dst ? d : 0], (uint64_t)M, (uint64_t)N, (uint64_t)ldc, kBM, 64);
+        if (rc != EMMYB200_OK) return rc;
+    }
     auto kernel = gemm_tcgen05_kernel<BN, BF16, EPI, B_NK>;
     EMMY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
     GemmParams p;
-    p.C = C; p.ldc = ldc; p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.m_blocks = (int)((M + kBM - 1) / kBM);
     p.n_blocks = (int)((N + BN - 1) / BN);
+    p.n_dst = n_dst;
     EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
     const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(map_a, map_b, p);
+    kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(map_a, map_b, out, p);
     return launch_status("gemm_tcgen05_kernel");
 }
 
 template <bool BF16, int EPI, bool B_NK>
-static int pick_tile(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
-                     int64_t ldc, cudaStream_t stream) {
+static int pick_tile(const void* A, const void* B, void* const* C, int n_dst, int64_t M, int64_t N, int64_t K, int64_t lda,
+                     int64_t ldb, int64_t ldc, cudaStream_t stream) {
     // 128 x 256 tiles unless they leave most of the machine idle or the last wave mostly empty.
     const int64_t sms = sm_count();
     const int64_t mb = (M + kBM - 1) / kBM;
@@ -346,34 +375,36 @@ static int pick_tile(const void* A, const void* B, void* C, int64_t M, int64_t N
         const int64_t waves = (tiles + sms - 1) / sms;
         return (double)(waves * sms * bn) / (double)(mb * N);     // scheduled columns per useful column
     };
-    if (waste(256) <= 1.08 * waste(128)) return launch_gemm<256, BF16, EPI, B_NK>(A, B, C, M, N, K, lda, ldb, ldc, stream);
-    return launch_gemm<128, BF16, EPI, B_NK>(A, B, C, M, N, K, lda, ldb, ldc, stream);
+    if (waste(256) <= 1.08 * waste(128)) return launch_gemm<256, BF16, EPI, B_NK>(A, B, C, n_dst, M, N, K, lda, ldb, ldc, stream);
+    return launch_gemm<128, BF16, EPI, B_NK>(A, B, C, n_dst, M, N, K, lda, ldb, ldc, stream);
 }
 
-}  // namespace emmy
-
-extern "C" int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, const void* B, void* C, int64_t M,
-                             int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* cuda_stream) {
-    using namespace emmy;
+static int gemm_entry(int dtype, int epilogue, int flags, const void* A, const void* B, void* const* C, int n_dst, int64_t M,
+                      int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* cuda_stream) {
     if (dtype != EMMYB200_F16 && dtype != EMMYB200_BF16) return fail(EMMYB200_ERR_UNSUPPORTED, "gemm: dtype %d (f16 and bf16 only)", dtype);
     if (epilogue != EMMYB200_EPI_NONE && epilogue != EMMYB200_EPI_GELU_TANH) return fail(EMMYB200_ERR_ARG, "gemm: unknown epilogue %d", epilogue);
     if (flags & ~EMMYB200_GEMM_B_NK) return fail(EMMYB200_ERR_ARG, "gemm: unknown flags 0x%x", flags);
+    if (n_dst < 1 || n_dst > kMaxDst) return fail(EMMYB200_ERR_ARG, "gemm: %d destinations (1 to %d)", n_dst, kMaxDst);
     if (M < 0 || N < 0 || K < 0) return fail(EMMYB200_ERR_SHAPE, "gemm: negative extent");
     if (M == 0 || N == 0) return EMMYB200_OK;
     if (K == 0) return fail(EMMYB200_ERR_SHAPE, "gemm: K = 0 (the caller zeroes C, emmyptx/mma.py:77-79 starts accumulators at 0)");
     if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "gemm: extents must be below 2^31");
     if (A == nullptr || B == nullptr || C == nullptr) return fail(EMMYB200_ERR_ARG, "gemm: null buffer");
+    for (int d = 0; d < n_dst; ++d) {
+        if (C[d] == nullptr) return fail(EMMYB200_ERR_ARG, "gemm: null output buffer");
+        if (!aligned(C[d], 16)) return fail(EMMYB200_ERR_ALIGN, "gemm: buffers must be 16-byte aligned");
+    }
     const bool b_nk = flags & EMMYB200_GEMM_B_NK;
     if (lda < K || ldc < N || ldb < (b_nk ? K : N)) return fail(EMMYB200_ERR_SHAPE, "gemm: leading dimension smaller than the row");
     if ((lda | ldb | ldc) & 7) return fail(EMMYB200_ERR_ALIGN, "gemm: leading dimensions must be multiples of 8 elements (16 bytes)");
-    if (!aligned(A, 16) || !aligned(B, 16) || !aligned(C, 16)) return fail(EMMYB200_ERR_ALIGN, "gemm: buffers must be 16-byte aligned");
+    if (!aligned(A, 16) || !aligned(B, 16)) return fail(EMMYB200_ERR_ALIGN, "gemm: buffers must be 16-byte aligned");
     int rc = check_sm100();
     if (rc != EMMYB200_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
     const bool bf16 = dtype == EMMYB200_BF16;
     const bool gelu = epilogue == EMMYB200_EPI_GELU_TANH;
 #define EMMY_GEMM_CASE(BF, EP, NK) \
-    if (bf16 == BF && gelu == (EP == EMMYB200_EPI_GELU_TANH) && b_nk == NK) return pick_tile<BF, EP, NK>(A, B, C, M, N, K, lda, ldb, ldc, s);
+    if (bf16 == BF && gelu == (EP == EMMYB200_EPI_GELU_TANH) && b_nk == NK) return pick_tile<BF, EP, NK>(A, B, C, n_dst, M, N, K, lda, ldb, ldc, s);
     EMMY_GEMM_CASE(false, EMMYB200_EPI_NONE, false)
     EMMY_GEMM_CASE(false, EMMYB200_EPI_NONE, true)
     EMMY_GEMM_CASE(false, EMMYB200_EPI_GELU_TANH, false)
@@ -384,4 +415,20 @@ extern "C" int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, 
     EMMY_GEMM_CASE(true, EMMYB200_EPI_GELU_TANH, true)
 #undef EMMY_GEMM_CASE
     return fail(EMMYB200_ERR_UNSUPPORTED, "gemm: no kernel variant");
+}
+
+}  // namespace emmy
+
+extern "C" int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, const void* B, void* C, int64_t M,
+                             int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* cuda_stream) {
+    void* dst[1] = {C};
+    if (C == nullptr && M > 0 && N > 0) return emmy::fail(EMMYB200_ERR_ARG, "gemm: null buffer");
+    return emmy::gemm_entry(dtype, epilogue, flags, A, B, dst, 1, M, N, K, lda, ldb, ldc, cuda_stream);
+}
+
+extern "C" int emmyb200_gemm_allgather(int dtype, int epilogue, int flags, const void* A, const void* B, void* const* C_dst,
+                                       int n_dst, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                                       void* cuda_stream) {
+    if (C_dst == nullptr) return emmy::fail(EMMYB200_ERR_ARG, "gemm_allgather: null destination list");
+    return emmy::gemm_entry(dtype, epilogue, flags, A, B, C_dst, n_dst, M, N, K, lda, ldb, ldc, cuda_stream);
 }

@@ -23,9 +23,9 @@
 
 namespace emmy {
 
-struct DivConst {      // floor(m / d) for 0 <= m < 2^31 is (m * magic) >> shift
+struct DivConst {      // floor(m / d) for 0 <= m < 2^31 is (m * magic) >> (32 + hi_shift); d == 1 is the identity
     uint32_t magic;
-    int shift;
+    int hi_shift;
     int32_t d;
 };
 
@@ -33,24 +33,28 @@ static DivConst make_div(int32_t d) {
     int L = 0;
     while ((1ll << L) < d) ++L;
     DivConst c;
-    c.shift = 31 + L;
-    c.magic = (uint32_t)(((1ull << c.shift) / (uint64_t)d) + 1);
     c.d = d;
+    if (d == 1) { c.magic = 0; c.hi_shift = 0; return c; }
+    const int shift = 31 + L;                                   // >= 32 for d >= 2
+    c.magic = (uint32_t)(((1ull << shift) / (uint64_t)d) + 1);
+    c.hi_shift = shift - 32;
     return c;
 }
 
 // Floor (torch `//`) or truncating (PTX `div.s32`) division by the positive constant.
-template <bool TRUNC>
+// Floor: floor(x/d) = ~floor(~x/d) for x < 0, so the sign is folded in with one xor on each side.
+template <bool TRUNC, bool DIV1>
 __device__ __forceinline__ int32_t div_const(int32_t x, DivConst c) {
+    if constexpr (DIV1) return x;
     if constexpr (TRUNC) {
         if (x == INT32_MIN) return x / c.d;
-        uint32_t m = (uint32_t)(x < 0 ? -x : x);
-        uint32_t q = (uint32_t)(((uint64_t)m * c.magic) >> c.shift);
+        const uint32_t m = (uint32_t)(x < 0 ? -x : x);
+        const uint32_t q = __umulhi(m, c.magic) >> c.hi_shift;
         return x < 0 ? -(int32_t)q : (int32_t)q;
     } else {
-        uint32_t m = (uint32_t)(x < 0 ? ~x : x);              // floor(x/d) = ~floor(~x/d) for x < 0
-        uint32_t q = (uint32_t)(((uint64_t)m * c.magic) >> c.shift);
-        return x < 0 ? ~(int32_t)q : (int32_t)q;
+        const int32_t sign = x >> 31;
+        const uint32_t q = __umulhi((uint32_t)(x ^ sign), c.magic) >> c.hi_shift;
+        return (int32_t)q ^ sign;
     }
 }
 
@@ -67,49 +71,113 @@ struct GatherParams {
     DivConst dc;
 };
 
-constexpr int TU = 64, TV = 64, kGatherThreads = 256;
+constexpr int kGatherThreads = 256;
+// Block of the (u, v) grid one CTA turns: 128 target-run words by 32 source-run words. Measured best on B200
+// among 32..512 x 32..256 (taller blocks lengthen the write runs; narrow ones keep many CTAs in flight).
+constexpr int kTileU = 128, kTileV = 32;
+constexpr int kMinRun = 128;      // shortest matrix side the tiled kernel is used for
 
-template <bool POW2, bool TRUNC>
-__global__ void __launch_bounds__(kGatherThreads) gather_tiled_kernel(GatherParams p) {
-    __shared__ int32_t tile[TU][TV + 1];
+// One CTA per (u-block, v-block), v fastest. All index arithmetic is 32-bit: n < 2^31, so a sum of two
+// residues never wraps a uint32.
+template <int TU, int TV, int NT, bool POW2, bool TRUNC, bool DIV1>
+__global__ void __launch_bounds__(NT) gather_tiled_kernel(GatherParams p) {
+    extern __shared__ int32_t tile_raw[];
+    int32_t (*tile)[TV + 1] = reinterpret_cast<int32_t (*)[TV + 1]>(tile_raw);
     const uint32_t vb = blockIdx.x % p.v_blocks, ub = blockIdx.x / p.v_blocks;
     const uint32_t u0 = ub * TU, v0 = vb * TV;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint64_t n = p.n;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t n = p.n;
+    auto mod_n = [&](uint64_t a) { return POW2 ? (uint32_t)(a & (n - 1)) : (uint32_t)(a % n); };
+    const uint32_t rows_here = min((uint32_t)TU, p.rows - u0);      // u0 < rows by construction of the grid
+    const uint32_t cols_here = min((uint32_t)TV, p.mul - v0);       // v0 < mul likewise
+    const uint64_t last_row = (uint64_t)p.mul * (p.rows - 1);
 
     // Read: warp per source run (fixed u), lanes along v.
-#pragma unroll 4
-    for (int r = warp; r < TU; r += kGatherThreads / 32) {
-        const uint32_t u = u0 + r;
-        const uint64_t row = (uint64_t)p.mul * u;              // j' of v = 0
+    constexpr int kWarps = NT / 32;
+    const bool interior = rows_here == TU && cols_here == TV && u0 + TU < p.rows;
+    uint32_t j_base = mod_n((uint64_t)p.mul * (u0 + warp) + v0 + p.add);            // source index of (u0 + warp, v0)
+    const uint32_t step = mod_n((uint64_t)p.mul * kWarps);
+    if (interior) {
+        // Full block away from the matrix's short last row: every load is issued before the first
+        // shared-memory store, so a warp keeps TU/8 * TV/32 independent loads in flight.
+        int32_t vals[TU / kWarps][TV / 32];
 #pragma unroll
-        for (int c = lane; c < TV; c += 32) {
-            const uint32_t v = v0 + c;
-            const uint64_t jp = row + v;
-            if (u < p.rows && v < p.mul && jp < n) {
-                uint64_t j = jp + p.add;
+        for (int k = 0; k < TU / kWarps; ++k) {
+#pragma unroll
+            for (int c = 0; c < TV / 32; ++c) {
+                uint32_t j = j_base + lane + 32 * c;
                 if (j >= n) j -= n;
-                tile[r][c] = __ldg(p.x + j);
+                vals[k][c] = __ldg(p.x + j);
             }
+            j_base += step;
+            if (j_base >= n) j_base -= n;
+        }
+#pragma unroll
+        for (int k = 0; k < TU / kWarps; ++k)
+#pragma unroll
+            for (int c = 0; c < TV / 32; ++c) tile[warp + kWarps * k][lane + 32 * c] = vals[k][c];
+    } else {
+        // Edge blocks: per-element bounds. The last row of the whole matrix is short.
+        for (uint32_t r = warp; r < rows_here; r += kWarps) {
+            uint32_t limit = cols_here;
+            if (u0 + r == p.rows - 1) limit = min(limit, (uint32_t)(n - last_row > v0 ? n - last_row - v0 : 0));
+            for (uint32_t c = lane; c < TV; c += 32) {
+                if (c < limit) {
+                    uint32_t j = j_base + c;
+                    if (j >= n) j -= n;
+                    tile[r][c] = __ldg(p.x + j);
+                }
+            }
+            j_base += step;
+            if (j_base >= n) j_base -= n;
         }
     }
     __syncthreads();
     // Write: warp per target run (fixed v), lanes along u.
-#pragma unroll 4
-    for (int c = warp; c < TV; c += kGatherThreads / 32) {
-        const uint32_t v = v0 + c;
-        const uint64_t iv = POW2 ? (((uint64_t)p.inv * v) & (n - 1)) : (((uint64_t)p.inv * v) % n);
+    if (interior) {
 #pragma unroll
-        for (int r = lane; r < TU; r += 32) {
-            const uint32_t u = u0 + r;
-            const uint64_t jp = (uint64_t)p.mul * u + v;
-            if (u < p.rows && v < p.mul && jp < n) {
-                uint64_t i = iv + u;
+        for (int k = 0; k < TV / kWarps; ++k) {
+            const uint32_t c = warp + kWarps * k;
+            uint32_t i_base = mod_n((uint64_t)p.inv * (v0 + c)) + u0 + lane;
+#pragma unroll
+            for (int r = 0; r < TU / 32; ++r) {
+                uint32_t i = i_base + 32 * r;
                 if (i >= n) i -= n;
-                p.y[i] = div_const<TRUNC>(tile[r][c], p.dc) ^ (int32_t)((uint32_t)i >> p.shift);
+                p.y[i] = div_const<TRUNC, DIV1>(tile[lane + 32 * r][c], p.dc) ^ (int32_t)(i >> p.shift);
+            }
+        }
+        return;
+    }
+    for (uint32_t c = warp; c < cols_here; c += kWarps) {
+        const uint32_t v = v0 + c;
+        uint32_t i_base = mod_n((uint64_t)p.inv * v) + u0;
+        if (i_base >= n) i_base -= n;
+        // rows of this column: all of them, except that the matrix's last row may end before v
+        uint32_t limit = rows_here;
+        if (u0 + rows_here == p.rows && last_row + v >= n) limit -= 1;
+        for (uint32_t r = lane; r < TU; r += 32) {
+            if (r < limit) {
+                uint32_t i = i_base + r;
+                if (i >= n) i -= n;
+                p.y[i] = div_const<TRUNC, DIV1>(tile[r][c], p.dc) ^ (int32_t)(i >> p.shift);
             }
         }
     }
+}
+
+template <int TU, int TV, int NT = kGatherThreads>
+static int launch_tiled(GatherParams p, bool pow2, bool trunc, cudaStream_t s) {
+    p.v_blocks = (p.mul + TV - 1) / TV;
+    const uint64_t blocks = (uint64_t)p.v_blocks * ((p.rows + TU - 1) / TU);
+    if (blocks >= (1ull << 31)) return -1;
+    void (*k)(GatherParams);
+    if (p.dc.d == 1) k = pow2 ? gather_tiled_kernel<TU, TV, NT, true, false, true> : gather_tiled_kernel<TU, TV, NT, false, false, true>;
+    else k = pow2 ? (trunc ? gather_tiled_kernel<TU, TV, NT, true, true, false> : gather_tiled_kernel<TU, TV, NT, true, false, false>)
+                  : (trunc ? gather_tiled_kernel<TU, TV, NT, false, true, false> : gather_tiled_kernel<TU, TV, NT, false, false, false>);
+    const int smem = TU * (TV + 1) * 4;
+    EMMY_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    k<<<(unsigned)blocks, NT, smem, s>>>(p);
+    return launch_status("gather_tiled_kernel");
 }
 
 template <bool TRUNC>
@@ -118,7 +186,8 @@ __global__ void __launch_bounds__(kGatherThreads) gather_direct_kernel(GatherPar
     const uint64_t stride = (uint64_t)gridDim.x * kGatherThreads;
     for (uint64_t i = (uint64_t)blockIdx.x * kGatherThreads + threadIdx.x; i < n; i += stride) {
         const uint64_t j = (i * p.mul + p.add) % n;
-        p.y[i] = div_const<TRUNC>(__ldg(p.x + j), p.dc) ^ (int32_t)((uint32_t)i >> p.shift);
+        const int32_t g = __ldg(p.x + j);
+        p.y[i] = (p.dc.d == 1 ? g : div_const<TRUNC, false>(g, p.dc)) ^ (int32_t)((uint32_t)i >> p.shift);
     }
 }
 
@@ -161,17 +230,11 @@ extern "C" int emmyb200_index_gather_i32(const int32_t* x, int32_t* y, int64_t n
     const bool trunc = flags & EMMYB200_GATHER_TRUNC;
     p.inv = p.mul ? mod_inverse(p.mul, (uint64_t)n) : 0;
     p.rows = p.mul ? (uint32_t)((n - 1) / p.mul + 1) : 0;
-    const bool tiled = p.inv != 0 && p.mul >= TV && p.rows >= TU;
+    const bool tiled = p.inv != 0 && p.mul >= kMinRun && p.rows >= kMinRun;
     if (tiled) {
-        p.v_blocks = (p.mul + TV - 1) / TV;
-        const uint64_t blocks = (uint64_t)p.v_blocks * ((p.rows + TU - 1) / TU);
-        if (blocks < (1ull << 31)) {
-            const bool pow2 = (n & (n - 1)) == 0;
-            auto k = pow2 ? (trunc ? gather_tiled_kernel<true, true> : gather_tiled_kernel<true, false>)
-                          : (trunc ? gather_tiled_kernel<false, true> : gather_tiled_kernel<false, false>);
-            k<<<(unsigned)blocks, kGatherThreads, 0, s>>>(p);
-            return launch_status("gather_tiled_kernel");
-        }
+        const bool pow2 = (n & (n - 1)) == 0;
+        const int rc = launch_tiled<kTileU, kTileV>(p, pow2, trunc, s);
+        if (rc != -1) return rc;
     }
     int64_t want = (n + kGatherThreads - 1) / kGatherThreads;
     int64_t cap = (int64_t)sm_count() * 16;

@@ -8,6 +8,7 @@
 // count. The op bodies are the <= 2 ulp functions of emmy_math.cuh.
 #include "common.cuh"
 #include "emmy_math.cuh"
+#include "emmy_math_x2.cuh"
 
 namespace emmy {
 
@@ -41,6 +42,19 @@ __global__ void __launch_bounds__(kThreads) pointwise_vec4_kernel(const float4* 
             int64_t idx = base + k * stride;
             if (idx < n4) {
                 float4 r;
+                if constexpr (PackedOp<OP>::kHas) {
+                    // One range test for the four elements picks the packed straight-line path
+                    // (a NaN makes the comparison false).
+                    const float big = fmaxf(fmaxf(fabsf(v[k].x), fabsf(v[k].y)), fmaxf(fabsf(v[k].z), fabsf(v[k].w)));
+                    const float sum = (v[k].x + v[k].y) + (v[k].z + v[k].w);      // NaN if any element is
+                    if (big <= PackedOp<OP>::kBound && sum == sum) {
+                        const float2 lo = PackedOp<OP>::apply(make_float2(v[k].x, v[k].y));
+                        const float2 hi = PackedOp<OP>::apply(make_float2(v[k].z, v[k].w));
+                        r = make_float4(lo.x, lo.y, hi.x, hi.y);
+                        __stcs(y + idx, r);
+                        continue;
+                    }
+                }
                 r.x = apply_op<OP>(v[k].x);
                 r.y = apply_op<OP>(v[k].y);
                 r.z = apply_op<OP>(v[k].z);

@@ -32,6 +32,9 @@ _SIGNATURES = {
     "emmyb200_gemm": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
                                      ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                      ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),
+    "emmyb200_gemm_allgather": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                               ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
+                                               ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),
     "emmyb200_attention_fwd": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                               ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                               ctypes.c_int64, ctypes.c_float, ctypes.c_void_p]),
@@ -130,6 +133,18 @@ def gemm(a, b, epilogue: str | None = None, b_is_nk: bool = False, out=None, str
                                   b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),
                                   _stream(stream)))
     return out
+
+
+def gemm_allgather(a, b, dst_ptrs: list[int], ldc: int, epilogue: str | None = None, b_is_nk: bool = False, stream=None):
+    """epilogue(a @ b) for this rank's rows of A, every output piece stored to each address in `dst_ptrs`
+    (this rank's shard first, then where the same rows live in each peer's full C)."""
+    _need_cuda(a, b)
+    m, k = a.shape
+    n = b.shape[0] if b_is_nk else b.shape[1]
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    check(library().emmyb200_gemm_allgather(dtype_code(a), EPILOGUES[epilogue], GEMM_B_NK if b_is_nk else 0, a.data_ptr(),
+                                            b.data_ptr(), arr, len(dst_ptrs), m, n, k, a.stride(0), b.stride(0), ldc,
+                                            _stream(stream)))
 
 
 def attention(q, k, v, scale: float | None = None, out=None, stream=None):

@@ -51,3 +51,17 @@ def all_gather_ragged(full, local, total: int, align: int = 1, group=None):
     for r, (b, e) in enumerate(spans):
         full[b:e] = staged[r * rows: r * rows + (e - b)]
     return full
+
+
+def peer_mapped_empty(shape, dtype, device, group=None):
+    """A tensor of the same shape on every rank of the group, each mapped into every other rank's address
+    space (torch symmetric memory over NVLink). Returns (local tensor, handle); `handle.buffer_ptrs[r]` is rank
+    r's copy as an address valid on this GPU and `handle.barrier()` is a device-side barrier of the group.
+    Switch-side multicast is left off: plain peer stores are all the kernels use."""
+    import os
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+    t = symm_mem.empty(*shape, dtype=dtype, device=device)
+    handle = symm_mem.rendezvous(t, group if group is not None else dist.group.WORLD)
+    return t, handle

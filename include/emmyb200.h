@@ -84,6 +84,17 @@ int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, const void*
                   int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                   void* cuda_stream);
 
+/* The same GEMM on one GPU's row shard of A, with every output piece stored to n_dst destination buffers
+ * (1..8): C_dst[0] is this GPU's own C shard, the others are the addresses, valid on this GPU, of where the
+ * same rows live in each peer's copy of the full C (peer-mapped device memory). Run by every GPU of a group
+ * on its own rows, it leaves the complete C on all of them: the kernel's own TMA stores over NVLink take the
+ * place of a separate all-gather. All destinations share ldc and alignment rules. The caller synchronises
+ * the group before reading rows written by peers. No counterpart in the reference, which is single-GPU
+ * (tools/run_local.py:51-57); it serves the row-sharded configuration of the benchmark. */
+int emmyb200_gemm_allgather(int dtype, int epilogue, int flags, const void* A, const void* B, void* const* C_dst,
+                            int n_dst, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                            void* cuda_stream);
+
 /* O = softmax(Q K^T * scale) V per (batch, head) unit, fp32 softmax, non-causal: what the
  * reference emits as generic fused statements (dot-product Loops + Accum, WarpShuffle /
  * TreeHalve row reductions, `_exp`: emmyptx/kernel.py:786-797, :856-900, emmyptx/ops.py:49-77).
