@@ -110,7 +110,9 @@ __device__ __forceinline__ float2 cos2(float2 x) { return sincos2<true>(x); }
 // tanh are both odd, so their product is taken on |x|: the two sign transfers cancel exactly.
 __device__ __forceinline__ float2 exp_sin_tanh2(float2 x) {
     const float2 a = make_float2(fabsf(x.x), fabsf(x.y));
-    return add2(exp_core2(x), mul2(sincos2<false, true>(a), tanh_mag2(a)));
+    const float2 e = exp_core2(x), s = sincos2<false, true>(a), t = tanh_mag2(a);
+    // scalar product and sum: a packed mul feeding a packed add was observed to be fused into one fma
+    return make_float2(__fadd_rn(e.x, __fmul_rn(s.x, t.x)), __fadd_rn(e.y, __fmul_rn(s.y, t.y)));
 }
 
 // Largest |x| (of all lanes) for which the packed form of each op is valid; NaN fails every bound.
