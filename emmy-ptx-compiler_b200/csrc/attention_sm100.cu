@@ -12,10 +12,11 @@
 //     buffered and re-armed as soon as the MMA that read it has completed;
 //   * warp 1 (one thread): S = Q K^T as tcgen05.mma 128x128x16 from shared memory into tensor memory;
 //     O += P V with P read from tensor memory and V as an MN-major shared-memory operand;
-//   * warps 2-5: one query row per thread. Row max and exponentials on the fp32 S read with
-//     tcgen05.ld, P written back over S as packed 16-bit pairs (tcgen05.st), running row sums in
-//     registers. The running max is only raised when it grows by more than 8 (in log2 units), so the
-//     O accumulator is rescaled in tensor memory rarely; the final 1/rowsum is applied on the way out.
+//   * warps 2-9: two threads per query row, 64 keys of each tile apiece. Row max and exponentials on
+//     the fp32 S read with tcgen05.ld (one pass, values held in registers), P written back over S as
+//     packed 16-bit pairs (tcgen05.st), running row sums in registers. The running max is only raised when it grows by
+//     more than 8 (in log2 units), so the O accumulator is rescaled in tensor memory rarely; the final
+//     1/rowsum is applied on the way out.
 //
 // All waits are bounded; keys beyond seq_k are masked to -inf, rows beyond seq_q are not stored.
 #include <cuda_bf16.h>
@@ -29,7 +30,7 @@ namespace emmy {
 
 int check_sm100();
 
-constexpr int kAttThreads = 192;
+constexpr int kAttThreads = 320;     // TMA warp, MMA warp, eight softmax warps
 constexpr int kTileQ = 128, kTileK = 128;
 
 template <int D>
@@ -39,7 +40,7 @@ struct AttSmem {
     static constexpr int kVBytes = kTileK * D * 2;
     static constexpr int kBarOffset = kQBytes + kKBytes + kVBytes;
     // at least 80 KiB, so that no more than two CTAs (2 x 256 tensor-memory columns) share an SM
-    static constexpr int kTotal = (kBarOffset + 128 + 1024) > 81920 ? (kBarOffset + 128 + 1024) : 81920;
+    static constexpr int kTotal = (kBarOffset + 128 + 2048 + 1024) > 81920 ? (kBarOffset + 128 + 2048 + 1024) : 81920;
 };
 
 struct AttParams {
@@ -63,6 +64,51 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
     }
 }
 
+// Packed fp32 pairs (one issue slot for two elements), rounding spelled out.
+__device__ __forceinline__ uint64_t as_u64(float2 v) { return *reinterpret_cast<uint64_t*>(&v); }
+__device__ __forceinline__ float2 as_f2(uint64_t v) { return *reinterpret_cast<float2*>(&v); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(as_u64(a)), "l"(as_u64(b)), "l"(as_u64(c)));
+    return as_f2(d);
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(as_u64(a)), "l"(as_u64(b)));
+    return as_f2(d);
+}
+
+// The two warps that share a lane quarter publish per-row values in shared memory and then trade a flag:
+// each writes `token` to its own flag and polls the partner's, with the same time limit and abort handling
+// as every other wait in the kernel. Returns false (warp-uniformly) when the wait was given up.
+__device__ __forceinline__ bool pair_exchange(const WaitCtx& ctx, volatile uint32_t* flags, int half, int quarter, int lane,
+                                              uint32_t token, uint32_t code) {
+    __threadfence_block();
+    __syncwarp();
+    bool ok = true;
+    if (lane == 0) {
+        flags[half * 4 + quarter] = token;
+        volatile uint32_t* other = flags + (half ^ 1) * 4 + quarter;
+        uint64_t t0 = 0;
+        for (uint32_t spin = 1; *other != token; ++spin) {
+            if ((spin & 255u) == 0) {
+                if (*ctx.abort_flag) { ok = false; break; }
+                const uint64_t now = ptx::global_timer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > kWaitLimitNs) {
+                    atomicCAS(ctx.status_word, 0u, code);
+                    *ctx.abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+            }
+        }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    __threadfence_block();
+    return ok;
+}
+
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kAttThreads, 2)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -80,6 +126,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                    v_empty = bar_base + 32, s_full = bar_base + 40, p_full = bar_base + 48, o_full = bar_base + 56;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + S::kBarOffset + 64);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* pair_flags = tmem_slot + 4;                                 // [2 buffers][2 halves][4 quarters]
+    float* xchg = reinterpret_cast<float*>(smem_gen + S::kBarOffset + 128);        // [2][2][128] row maxima / sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int unit = blockIdx.x / p.q_tiles, qt = blockIdx.x % p.q_tiles;
@@ -89,7 +137,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     if (threadIdx.x == 0) {
         ptx::mbar_init(q_full, 1); ptx::mbar_init(k_full, 1); ptx::mbar_init(v_full, 1);
         ptx::mbar_init(k_empty, 1); ptx::mbar_init(v_empty, 1);
-        ptx::mbar_init(s_full, 1); ptx::mbar_init(p_full, 4); ptx::mbar_init(o_full, 1);
+        ptx::mbar_init(s_full, 1); ptx::mbar_init(p_full, 8); ptx::mbar_init(o_full, 1);
+        for (int q = 0; q < 16; ++q) pair_flags[q] = 0;
         *abort_flag = 0;
         ptx::mbar_fence_init();
         ptx::prefetch_tensormap(&map_q); ptx::prefetch_tensormap(&map_k); ptx::prefetch_tensormap(&map_v);
@@ -131,60 +180,86 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             constexpr uint32_t idesc_s = ptx::mma_idesc_f16(BF16, false, false, kTileQ, kTileK);
             constexpr uint32_t idesc_o = ptx::mma_idesc_f16(BF16, false, true, kTileQ, D);
             const uint32_t s_tmem = tmem_base, o_tmem = tmem_base + kColO;
+            // descriptors of every k-step, built once
+            uint64_t q_desc[D / 16], k_desc[D / 16], v_desc[kTileK / 16];
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t off = (kk / 4) * (kTileQ * 128) + (kk % 4) * 32;
+                q_desc[kk] = ptx::smem_desc_sw128(q_smem + off, 16, 1024);
+                k_desc[kk] = ptx::smem_desc_sw128(k_smem + off, 16, 1024);
+            }
+#pragma unroll
+            for (int kk = 0; kk < kTileK / 16; ++kk) v_desc[kk] = ptx::smem_desc_sw128(v_smem + kk * (16 * 128), kTileK * 128, 1024);
             bool ok = bounded_wait(wctx, q_full, 0, 0x02030000u);
             for (int j = 0; j < kv_tiles && ok; ++j) {
                 const uint32_t ph = j & 1;
                 if (!(ok = bounded_wait(wctx, k_full, ph, 0x02040000u | (j & 0xffff)))) break;
                 ptx::tc_fence_after_sync();
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {           // S = Q K^T, contraction over the head dim
-                    const uint32_t off = (kk / 4) * (kTileQ * 128) + (kk % 4) * 32;
-                    ptx::mma_ss(s_tmem, ptx::smem_desc_sw128(q_smem + off, 16, 1024),
-                                ptx::smem_desc_sw128(k_smem + off, 16, 1024), idesc_s, kk != 0);
-                }
+                for (int kk = 0; kk < D / 16; ++kk)             // S = Q K^T, contraction over the head dim
+                    ptx::mma_ss(s_tmem, q_desc[kk], k_desc[kk], idesc_s, kk != 0);
                 ptx::mma_commit(k_empty);
                 ptx::mma_commit(s_full);
                 if (!(ok = bounded_wait(wctx, p_full, ph, 0x02050000u | (j & 0xffff)))) break;
                 if (!(ok = bounded_wait(wctx, v_full, ph, 0x02060000u | (j & 0xffff)))) break;
                 ptx::tc_fence_after_sync();
 #pragma unroll
-                for (int kk = 0; kk < kTileK / 16; ++kk) {      // O += P V, contraction over the keys
-                    ptx::mma_ts(o_tmem, s_tmem + kk * 8,
-                                ptx::smem_desc_sw128(v_smem + kk * (16 * 128), kTileK * 128, 1024), idesc_o,
-                                (j | kk) != 0);
-                }
+                for (int kk = 0; kk < kTileK / 16; ++kk)        // O += P V, contraction over the keys
+                    ptx::mma_ts(o_tmem, s_tmem + kk * 8, v_desc[kk], idesc_o, (j | kk) != 0);
                 ptx::mma_commit(v_empty);
             }
             if (ok) ptx::mma_commit(o_full);
         }
         __syncwarp();
     } else {
-        // ---- softmax: thread = one query row ---------------------------------------------------------------
-        const int quarter = warp & 3;
+        // ---- softmax: two threads per query row, 64 keys of each tile apiece ----------------------------------
+        // Warp w reads tensor-memory lanes 32 (w % 4) .. +32; warps w and w + 4 share those rows and take the
+        // lower and upper half of the columns. They agree on the row max through shared memory (an mbarrier
+        // per lane quarter, so the wait is bounded); partial row sums are merged once, at the end.
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const int row_in_tile = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        const uint32_t s_row = tmem_base + lane_base, o_row = tmem_base + lane_base + kColO;
+        const uint32_t s_row = tmem_base + lane_base + half * (kTileK / 2);      // this thread's 64 S columns
+        const uint32_t p_row = tmem_base + lane_base + half * (kTileK / 4);      // and where its 64 P values go
+        const uint32_t o_row = tmem_base + lane_base + kColO + half * (D / 2);   // its half of the O row
         const float c = p.scale_log2;
         float m_run = -CUDART_INF_F;      // the max the exponentials are taken against (log2 units)
-        float l_run = 0.0f;               // running row sum
+        float l_run = 0.0f;               // running sum over this thread's columns
         bool ok = true;
         for (int j = 0; j < kv_tiles && ok; ++j) {
             ok = __all_sync(0xffffffffu, bounded_wait(wctx, s_full, j & 1, 0x02070000u | (j & 0xffff)));      // warp-uniform
             if (!ok) break;
             ptx::tc_fence_after_sync();
-            const int valid = p.seq_k - j * kTileK;             // keys of this tile inside the sequence
-            float m_tile = -CUDART_INF_F;
-#pragma unroll 1
-            for (int ch = 0; ch < kTileK / 32; ++ch) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(s_row + ch * 32, r);
-                ptx::tmem_ld_wait();
+            uint32_t r[kTileK / 2];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(r[i]) * c;
-                    if (ch * 32 + i >= valid) s = -CUDART_INF_F;
-                    m_tile = fmaxf(m_tile, s);
-                }
+            for (int ch = 0; ch < kTileK / 64; ++ch) ptx::tmem_ld_32x32b_x32(s_row + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[ch * 32]));
+            ptx::tmem_ld_wait();
+            const int valid = p.seq_k - j * kTileK - half * (kTileK / 2);       // of this thread's columns
+            if (valid < kTileK / 2) {                           // last, ragged tile only
+#pragma unroll
+                for (int i = 0; i < kTileK / 2; ++i)
+                    if (i >= valid) r[i] = __float_as_uint(c > 0.0f ? -CUDART_INF_F : CUDART_INF_F);
             }
+            // max of c * s = c * (max or min of s); eight independent chains for latency
+            float ext[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ext[i] = __uint_as_float(r[i]);
+            if (c > 0.0f) {
+#pragma unroll
+                for (int i = 8; i < kTileK / 2; ++i) ext[i & 7] = fmaxf(ext[i & 7], __uint_as_float(r[i]));
+                ext[0] = fmaxf(fmaxf(fmaxf(ext[0], ext[1]), fmaxf(ext[2], ext[3])), fmaxf(fmaxf(ext[4], ext[5]), fmaxf(ext[6], ext[7])));
+            } else {
+#pragma unroll
+                for (int i = 8; i < kTileK / 2; ++i) ext[i & 7] = fminf(ext[i & 7], __uint_as_float(r[i]));
+                ext[0] = fminf(fminf(fminf(ext[0], ext[1]), fminf(ext[2], ext[3])), fminf(fminf(ext[4], ext[5]), fminf(ext[6], ext[7])));
+            }
+            // exchange with the thread that owns the other half of the row (both S halves are in registers by
+            // now, so P may overwrite S afterwards)
+            volatile float* slot = xchg + (j & 1) * 256;
+            slot[half * 128 + row_in_tile] = ext[0] * c;
+            ok = pair_exchange(wctx, pair_flags + (j & 1) * 8, half, quarter, lane, (uint32_t)j + 1, 0x02090000u | (j & 0xffff));
+            if (!ok) break;
+            const float m_tile = fmaxf(ext[0] * c, slot[(half ^ 1) * 128 + row_in_tile]);
             // Raise the running max only when it would grow by more than 8: exponentials then stay
             // below 2^8, and the accumulator needs rescaling rarely.
             const bool raise = m_tile > m_run + 8.0f;
@@ -192,64 +267,67 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             if (__any_sync(0xffffffffu, raise) && j > 0) {
                 const float f = ptx::ex2_approx(m_run - m_new);     // 1 for rows that keep their max
 #pragma unroll 1
-                for (int ch = 0; ch < D / 32; ++ch) {
-                    uint32_t r[32];
-                    ptx::tmem_ld_32x32b_x32(o_row + ch * 32, r);
+                for (int col = 0; col < D / 2; col += 8) {          // few registers: the S row is still live
+                    uint32_t o[8];
+                    ptx::tmem_ld_32x32b_x8(o_row + col, o);
                     ptx::tmem_ld_wait();
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        uint32_t w[16];
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(__uint_as_float(r[16 * h + i]) * f);
-                        ptx::tmem_st_32x32b_x16(o_row + ch * 32 + h * 16, w);
-                    }
+                    for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                    ptx::tmem_st_32x32b_x8(o_row + col, o);
                 }
                 l_run *= f;
             }
             m_run = m_new;
-            float l_tile = 0.0f;
-#pragma unroll 1
-            for (int ch = 0; ch < kTileK / 32; ++ch) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(s_row + ch * 32, r);
-                ptx::tmem_ld_wait();
+            // p = 2^(c s - m): packed fma for the exponent, MUFU ex2 (moving part of the exponentials to a
+            // polynomial on the FMA pipe was measured slower at every fraction tried).
+            const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_run, -m_run);
+            float2 sum2[4] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+#pragma unroll
+            for (int ch = 0; ch < kTileK / 64; ++ch) {
                 uint32_t w[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    float e0 = ptx::ex2_approx(fmaf(__uint_as_float(r[2 * i]), c, -m_run));
-                    float e1 = ptx::ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), c, -m_run));
-                    if (ch * 32 + 2 * i >= valid) e0 = 0.0f;
-                    if (ch * 32 + 2 * i + 1 >= valid) e1 = 0.0f;
-                    l_tile += e0 + e1;
-                    w[i] = pack_pair<BF16>(e0, e1);
+                    const float2 sv = make_float2(__uint_as_float(r[ch * 32 + 2 * i]), __uint_as_float(r[ch * 32 + 2 * i + 1]));
+                    const float2 y = fma2(sv, c2, nm2);
+                    const float2 e = make_float2(ptx::ex2_approx(y.x), ptx::ex2_approx(y.y));
+                    sum2[i & 3] = add2(sum2[i & 3], e);
+                    w[i] = pack_pair<BF16>(e.x, e.y);
                 }
-                ptx::tmem_st_32x32b_x16(s_row + ch * 16, w);        // P over the consumed part of S
+                ptx::tmem_st_32x32b_x16(p_row + ch * 16, w);
             }
-            l_run += l_tile;
+            const float2 tot = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
+            l_run += tot.x + tot.y;
             ptx::tmem_st_wait();
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(p_full);
         }
+        // merge the two partial row sums, then write this thread's half of the output row
+        if (ok) {
+            volatile float* slot = xchg + (kv_tiles & 1) * 256;
+            slot[half * 128 + row_in_tile] = l_run;
+            ok = pair_exchange(wctx, pair_flags + (kv_tiles & 1) * 8, half, quarter, lane, (uint32_t)kv_tiles + 1, 0x020a0000u);
+            if (ok) l_run += slot[(half ^ 1) * 128 + row_in_tile];
+        }
         if (ok && __all_sync(0xffffffffu, bounded_wait(wctx, o_full, 0, 0x02080000u))) {
             ptx::tc_fence_after_sync();
             const float inv = 1.0f / l_run;
-            const int row = qt * kTileQ + quarter * 32 + lane;
-            uint16_t* out = reinterpret_cast<uint16_t*>(p.O) + ((int64_t)unit * p.seq_q + row) * D;
+            const int row = qt * kTileQ + row_in_tile;
+            uint16_t* out = reinterpret_cast<uint16_t*>(p.O) + ((int64_t)unit * p.seq_q + row) * D + half * (D / 2);
 #pragma unroll 1
-            for (int ch = 0; ch < D / 32; ++ch) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(o_row + ch * 32, r);
+            for (int ch = 0; ch < D / 64; ++ch) {
+                uint32_t o[32];
+                ptx::tmem_ld_32x32b_x32(o_row + ch * 32, o);
                 ptx::tmem_ld_wait();
                 if (row < p.seq_q) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        uint4 o;
-                        o.x = pack_pair<BF16>(__uint_as_float(r[8 * q + 0]) * inv, __uint_as_float(r[8 * q + 1]) * inv);
-                        o.y = pack_pair<BF16>(__uint_as_float(r[8 * q + 2]) * inv, __uint_as_float(r[8 * q + 3]) * inv);
-                        o.z = pack_pair<BF16>(__uint_as_float(r[8 * q + 4]) * inv, __uint_as_float(r[8 * q + 5]) * inv);
-                        o.w = pack_pair<BF16>(__uint_as_float(r[8 * q + 6]) * inv, __uint_as_float(r[8 * q + 7]) * inv);
-                        *reinterpret_cast<uint4*>(out + ch * 32 + q * 8) = o;
+                        uint4 v;
+                        v.x = pack_pair<BF16>(__uint_as_float(o[8 * q + 0]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
+                        v.y = pack_pair<BF16>(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
+                        v.z = pack_pair<BF16>(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
+                        v.w = pack_pair<BF16>(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
+                        *reinterpret_cast<uint4*>(out + ch * 32 + q * 8) = v;
                     }
                 }
             }

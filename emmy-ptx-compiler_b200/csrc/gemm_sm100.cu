@@ -367,15 +367,10 @@ static int launch_gemm(const void* A, const void* B, void* const* C, int n_dst, 
 template <bool BF16, int EPI, bool B_NK>
 static int pick_tile(const void* A, const void* B, void* const* C, int n_dst, int64_t M, int64_t N, int64_t K, int64_t lda,
                      int64_t ldb, int64_t ldc, cudaStream_t stream) {
-    // 128 x 256 tiles unless they leave most of the machine idle or the last wave mostly empty.
-    const int64_t sms = sm_count();
-    const int64_t mb = (M + kBM - 1) / kBM;
-    auto waste = [&](int bn) {
-        const int64_t tiles = mb * ((N + bn - 1) / bn);
-        const int64_t waves = (tiles + sms - 1) / sms;
-        return (double)(waves * sms * bn) / (double)(mb * N);     // scheduled columns per useful column
-    };
-    if (waste(256) <= 1.08 * waste(128)) return launch_gemm<256, BF16, EPI, B_NK>(A, B, C, n_dst, M, N, K, lda, ldb, ldc, stream);
+    // 128 x 256 tiles: with both operands read from shared memory by one CTA, the 128 x 128 shape is bound by
+    // shared-memory bandwidth (measured 0.6-0.7x the throughput at every size from 2048^3 to 16384^3), which
+    // costs more than the emptier last wave of the wide tile. Narrow outputs keep the narrow tile.
+    if (N > 128) return launch_gemm<256, BF16, EPI, B_NK>(A, B, C, n_dst, M, N, K, lda, ldb, ldc, stream);
     return launch_gemm<128, BF16, EPI, B_NK>(A, B, C, n_dst, M, N, K, lda, ldb, ldc, stream);
 }
 
