@@ -261,11 +261,28 @@ class AttentionWorkload(Workload):
         g.manual_seed(2000 + rank)
         mk = lambda: torch.randn(self.local, seq, d, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
         self.q, self.k, self.v = mk(), mk(), mk()
-        self.o_full = torch.empty(units, seq, d, device=dev, dtype=torch.bfloat16)
-        self.o = self.o_full[rank * self.local:(rank + 1) * self.local]
         self.gather = gather and world > 1
+        self.mode = os.environ.get("EMMYB200_BENCH_GATHER", "fused")
+        if self.gather and self.mode == "fused":
+            from emmyptx import shard
+            self.o_full, self.peers = shard.peer_mapped_empty((units, seq, d), torch.bfloat16, dev)
+            off = rank * self.local * seq * d * 2
+            self.dst = [self.o_full.data_ptr() + off] + [p + off for r, p in enumerate(self.peers.buffer_ptrs) if r != rank]
+        else:
+            self.o_full = torch.empty(units, seq, d, device=dev, dtype=torch.bfloat16)
+        self.o = self.o_full[rank * self.local:(rank + 1) * self.local]
+
+    @property
+    def collective(self):
+        if self.mode == "fused":
+            return "fused: the attention kernel's TMA stores write each output tile to every peer's O over NVLink, then a signal barrier"
+        return "nccl all_gather of the output shards"
 
     def step(self):
+        if self.gather and self.mode == "fused":
+            self.rt.attention_allgather(self.q, self.k, self.v, self.dst)
+            self.peers.barrier()
+            return
         self.rt.attention(self.q, self.k, self.v, out=self.o)
         if self.gather:
             import torch.distributed as dist

@@ -40,11 +40,17 @@ struct AttSmem {
     static constexpr int kVBytes = kTileK * D * 2;
     static constexpr int kBarOffset = kQBytes + kKBytes + kVBytes;
     // at least 80 KiB, so that no more than two CTAs (2 x 256 tensor-memory columns) share an SM
-    static constexpr int kTotal = (kBarOffset + 128 + 2048 + 1024) > 81920 ? (kBarOffset + 128 + 2048 + 1024) : 81920;
+    static constexpr int kTotal = (kBarOffset + 256 + 2048 + 1024) > 81920 ? (kBarOffset + 256 + 2048 + 1024) : 81920;
+};
+
+constexpr int kMaxDst = 8;
+
+struct AttOutMaps {
+    CUtensorMap m[kMaxDst];
 };
 
 struct AttParams {
-    void* O;
+    int n_dst;              // destinations of every output tile (1 = the local O only)
     int seq_q, seq_k;
     int q_tiles;
     float scale_log2;       // scale * log2(e)
@@ -112,7 +118,7 @@ __device__ __forceinline__ bool pair_exchange(const WaitCtx& ctx, volatile uint3
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kAttThreads, 2)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                     const __grid_constant__ CUtensorMap map_v, AttParams p) {
+                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttOutMaps out, AttParams p) {
     using S = AttSmem<D>;
     constexpr int kChunks = D / 64;                 // 64-element (128-byte) pieces of a head row
     constexpr uint32_t kTmemCols = 256;             // S / P: columns 0-127, O: 128 .. 128 + D
@@ -123,11 +129,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const uint32_t q_smem = smem_base, k_smem = smem_base + S::kQBytes, v_smem = k_smem + S::kKBytes;
     const uint32_t bar_base = smem_base + S::kBarOffset;
     const uint32_t q_full = bar_base, k_full = bar_base + 8, v_full = bar_base + 16, k_empty = bar_base + 24,
-                   v_empty = bar_base + 32, s_full = bar_base + 40, p_full = bar_base + 48, o_full = bar_base + 56;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + S::kBarOffset + 64);
+                   v_empty = bar_base + 32, s_full = bar_base + 40, p_full = bar_base + 48, o_full = bar_base + 56,
+                   o_staged = bar_base + 64;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + S::kBarOffset + 80);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     volatile uint32_t* pair_flags = tmem_slot + 4;                                 // [2 buffers][2 halves][4 quarters]
-    float* xchg = reinterpret_cast<float*>(smem_gen + S::kBarOffset + 128);        // [2][2][128] row maxima / sums
+    float* xchg = reinterpret_cast<float*>(smem_gen + S::kBarOffset + 256);        // [2][2][128] row maxima / sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int unit = blockIdx.x / p.q_tiles, qt = blockIdx.x % p.q_tiles;
@@ -137,7 +144,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     if (threadIdx.x == 0) {
         ptx::mbar_init(q_full, 1); ptx::mbar_init(k_full, 1); ptx::mbar_init(v_full, 1);
         ptx::mbar_init(k_empty, 1); ptx::mbar_init(v_empty, 1);
-        ptx::mbar_init(s_full, 1); ptx::mbar_init(p_full, 8); ptx::mbar_init(o_full, 1);
+        ptx::mbar_init(s_full, 1); ptx::mbar_init(p_full, 8); ptx::mbar_init(o_full, 1); ptx::mbar_init(o_staged, 8);
         for (int q = 0; q < 16; ++q) pair_flags[q] = 0;
         *abort_flag = 0;
         ptx::mbar_fence_init();
@@ -310,25 +317,56 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             if (ok) l_run += slot[(half ^ 1) * 128 + row_in_tile];
         }
         if (ok && __all_sync(0xffffffffu, bounded_wait(wctx, o_full, 0, 0x02080000u))) {
+            // Every MMA has completed, so the Q tile's shared memory is free: the normalised output tile is
+            // staged there in the same swizzled 128 x 64 halves and leaves through TMA stores (which drop the
+            // rows beyond seq_q), one per destination.
             ptx::tc_fence_after_sync();
             const float inv = 1.0f / l_run;
-            const int row = qt * kTileQ + row_in_tile;
-            uint16_t* out = reinterpret_cast<uint16_t*>(p.O) + ((int64_t)unit * p.seq_q + row) * D + half * (D / 2);
+            const uint32_t row_smem = q_smem + half * (kTileQ * 128) + row_in_tile * 128;
+            if constexpr (D == 128) {
 #pragma unroll 1
-            for (int ch = 0; ch < D / 64; ++ch) {
-                uint32_t o[32];
-                ptx::tmem_ld_32x32b_x32(o_row + ch * 32, o);
-                ptx::tmem_ld_wait();
-                if (row < p.seq_q) {
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t o[32];
+                    ptx::tmem_ld_32x32b_x32(o_row + ch * 32, o);
+                    ptx::tmem_ld_wait();
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        uint4 v;
-                        v.x = pack_pair<BF16>(__uint_as_float(o[8 * q + 0]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
-                        v.y = pack_pair<BF16>(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
-                        v.z = pack_pair<BF16>(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
-                        v.w = pack_pair<BF16>(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
-                        *reinterpret_cast<uint4*>(out + ch * 32 + q * 8) = v;
+                        const uint32_t slot = (uint32_t)(4 * ch + q) ^ (uint32_t)(row_in_tile & 7);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_smem + slot * 16),
+                                     "r"(pack_pair<BF16>(__uint_as_float(o[8 * q + 0]) * inv, __uint_as_float(o[8 * q + 1]) * inv)),
+                                     "r"(pack_pair<BF16>(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv)),
+                                     "r"(pack_pair<BF16>(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv)),
+                                     "r"(pack_pair<BF16>(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv))
+                                     : "memory");
                     }
+                }
+            } else {                                            // D == 64: one 128 x 64 piece, 32 columns per thread
+                uint32_t o[32];
+                ptx::tmem_ld_32x32b_x32(o_row, o);
+                ptx::tmem_ld_wait();
+                const uint32_t row64 = q_smem + row_in_tile * 128;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t slot = (uint32_t)(4 * half + q) ^ (uint32_t)(row_in_tile & 7);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row64 + slot * 16),
+                                 "r"(pack_pair<BF16>(__uint_as_float(o[8 * q + 0]) * inv, __uint_as_float(o[8 * q + 1]) * inv)),
+                                 "r"(pack_pair<BF16>(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv)),
+                                 "r"(pack_pair<BF16>(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv)),
+                                 "r"(pack_pair<BF16>(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv))
+                                 : "memory");
+                }
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(o_staged);
+            if (threadIdx.x == 64) {                            // first softmax thread: owns the stores
+                if (bounded_wait(wctx, o_staged, 0, 0x020b0000u)) {
+                    for (int d = 0; d < p.n_dst; ++d)
+#pragma unroll
+                        for (int c = 0; c < kChunks; ++c)
+                            ptx::tma_store_3d(&out.m[d], q_smem + c * (kTileQ * 128), c * 64, qt * kTileQ, unit);
+                    ptx::tma_store_commit();
+                    ptx::tma_store_wait<0>();
                 }
             }
         }
@@ -354,47 +392,68 @@ int attention_read_status(uint32_t* out) {
 }
 
 template <int D, bool BF16>
-static int launch_attention(const void* Q, const void* K, const void* V, void* O, int64_t units, int64_t seq_q,
+static int launch_attention(const void* Q, const void* K, const void* V, void* const* O, int n_dst, int64_t units, int64_t seq_q,
                             int64_t seq_k, float scale, cudaStream_t stream) {
     using S = AttSmem<D>;
     CUtensorMap mq, mk, mv;
     int rc = make_tensor_map_3d(&mq, Q, (uint64_t)units, (uint64_t)seq_q, D, kTileQ, 64);
     if (rc == EMMYB200_OK) rc = make_tensor_map_3d(&mk, K, (uint64_t)units, (uint64_t)seq_k, D, kTileK, 64);
     if (rc == EMMYB200_OK) rc = make_tensor_map_3d(&mv, V, (uint64_t)units, (uint64_t)seq_k, D, kTileK, 64);
+    AttOutMaps out;
+    for (int d = 0; d < kMaxDst && rc == EMMYB200_OK; ++d)
+        rc = make_tensor_map_3d(&out.m[d], O[d < n_dst ? d : 0], (uint64_t)units, (uint64_t)seq_q, D, kTileQ, 64);
     if (rc != EMMYB200_OK) return rc;
     auto kernel = attention_fwd_kernel<D, BF16>;
     EMMY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
     AttParams p;
-    p.O = O; p.seq_q = (int)seq_q; p.seq_k = (int)seq_k;
+    p.n_dst = n_dst; p.seq_q = (int)seq_q; p.seq_k = (int)seq_k;
     p.q_tiles = (int)((seq_q + kTileQ - 1) / kTileQ);
     p.scale_log2 = scale * 1.4426950408889634f;
     EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_att_status));
     const int64_t ctas = units * p.q_tiles;
     if (ctas >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: %lld query tiles exceed the grid limit", (long long)ctas);
-    kernel<<<(unsigned)ctas, kAttThreads, S::kTotal, stream>>>(mq, mk, mv, p);
+    kernel<<<(unsigned)ctas, kAttThreads, S::kTotal, stream>>>(mq, mk, mv, out, p);
     return launch_status("attention_fwd_kernel");
 }
 
 }  // namespace emmy
 
-extern "C" int emmyb200_attention_fwd(int dtype, const void* Q, const void* K, const void* V, void* O, int64_t units,
-                                      int64_t seq_q, int64_t seq_k, int64_t d, float scale, void* cuda_stream) {
+static int attention_entry(int dtype, const void* Q, const void* K, const void* V, void* const* O, int n_dst, int64_t units,
+                           int64_t seq_q, int64_t seq_k, int64_t d, float scale, void* cuda_stream) {
     using namespace emmy;
     if (dtype != EMMYB200_F16 && dtype != EMMYB200_BF16) return fail(EMMYB200_ERR_UNSUPPORTED, "attention_fwd: dtype %d (f16 and bf16 only)", dtype);
+    if (n_dst < 1 || n_dst > kMaxDst) return fail(EMMYB200_ERR_ARG, "attention_fwd: %d destinations (1 to %d)", n_dst, kMaxDst);
     if (units < 0 || seq_q < 0 || seq_k < 0) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: negative extent");
     if (units == 0 || seq_q == 0) return EMMYB200_OK;
     if (seq_k == 0) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: seq_k = 0 (softmax over no keys)");
     if (d != 64 && d != 128) return fail(EMMYB200_ERR_UNSUPPORTED, "attention_fwd: head dim %lld (64 and 128 only)", (long long)d);
     if (seq_q >= (1ll << 31) || seq_k >= (1ll << 31) || units >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: extents must be below 2^31");
     if (Q == nullptr || K == nullptr || V == nullptr || O == nullptr) return fail(EMMYB200_ERR_ARG, "attention_fwd: null buffer");
-    if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16)) return fail(EMMYB200_ERR_ALIGN, "attention_fwd: buffers must be 16-byte aligned");
+    for (int i = 0; i < n_dst; ++i) {
+        if (O[i] == nullptr) return fail(EMMYB200_ERR_ARG, "attention_fwd: null buffer");
+        if (!aligned(O[i], 16)) return fail(EMMYB200_ERR_ALIGN, "attention_fwd: buffers must be 16-byte aligned");
+    }
+    if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16)) return fail(EMMYB200_ERR_ALIGN, "attention_fwd: buffers must be 16-byte aligned");
     if (!(scale == scale) || scale == 0.0f) return fail(EMMYB200_ERR_ARG, "attention_fwd: scale must be a non-zero number");
     int rc = check_sm100();
     if (rc != EMMYB200_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
     const bool bf16 = dtype == EMMYB200_BF16;
-    if (d == 128) return bf16 ? launch_attention<128, true>(Q, K, V, O, units, seq_q, seq_k, scale, s)
-                              : launch_attention<128, false>(Q, K, V, O, units, seq_q, seq_k, scale, s);
-    return bf16 ? launch_attention<64, true>(Q, K, V, O, units, seq_q, seq_k, scale, s)
-                : launch_attention<64, false>(Q, K, V, O, units, seq_q, seq_k, scale, s);
+    if (d == 128) return bf16 ? launch_attention<128, true>(Q, K, V, O, n_dst, units, seq_q, seq_k, scale, s)
+                              : launch_attention<128, false>(Q, K, V, O, n_dst, units, seq_q, seq_k, scale, s);
+    return bf16 ? launch_attention<64, true>(Q, K, V, O, n_dst, units, seq_q, seq_k, scale, s)
+                : launch_attention<64, false>(Q, K, V, O, n_dst, units, seq_q, seq_k, scale, s);
+}
+
+extern "C" int emmyb200_attention_fwd(int dtype, const void* Q, const void* K, const void* V, void* O, int64_t units,
+                                      int64_t seq_q, int64_t seq_k, int64_t d, float scale, void* cuda_stream) {
+    void* dst[1] = {O};
+    return attention_entry(dtype, Q, K, V, dst, 1, units, seq_q, seq_k, d, scale, cuda_stream);
+}
+
+extern "C" int emmyb200_attention_fwd_allgather(int dtype, const void* Q, const void* K, const void* V, void* const* O_dst,
+                                                int n_dst, int64_t units, int64_t seq_q, int64_t seq_k, int64_t d, float scale,
+                                                void* cuda_stream) {
+    if (O_dst == nullptr) return emmy::fail(EMMYB200_ERR_ARG, "attention_fwd_allgather: null destination list");
+    return attention_entry(dtype, Q, K, V, O_dst, n_dst, units, seq_q, seq_k, d, scale, cuda_stream);
 }

@@ -38,6 +38,10 @@ _SIGNATURES = {
     "emmyb200_attention_fwd": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                               ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                               ctypes.c_int64, ctypes.c_float, ctypes.c_void_p]),
+    "emmyb200_attention_fwd_allgather": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                        ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int64,
+                                                        ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_float,
+                                                        ctypes.c_void_p]),
     "emmyb200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
 }
 EXPORTS = tuple(_SIGNATURES)
@@ -159,6 +163,18 @@ def attention(q, k, v, scale: float | None = None, out=None, stream=None):
     check(library().emmyb200_attention_fwd(dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), units,
                                            q.shape[-2], k.shape[-2], d, scale, _stream(stream)))
     return out
+
+
+def attention_allgather(q, k, v, dst_ptrs: list[int], scale: float | None = None, stream=None):
+    """attention() on this rank's units, every output tile stored to each address in `dst_ptrs` (this rank's slice of
+    O first, then the same slice inside each peer's full O)."""
+    _need_cuda(q, k, v)
+    d = q.shape[-1]
+    units = q.numel() // (q.shape[-2] * d)
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    scale = d ** -0.5 if scale is None else scale
+    check(library().emmyb200_attention_fwd_allgather(dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), arr, len(dst_ptrs),
+                                                     units, q.shape[-2], k.shape[-2], d, scale, _stream(stream)))
 
 
 def device_status() -> int:

@@ -104,6 +104,14 @@ int emmyb200_attention_fwd(int dtype, const void* Q, const void* K, const void* 
                            int64_t units, int64_t seq_q, int64_t seq_k, int64_t d, float scale,
                            void* cuda_stream);
 
+/* The same attention on one GPU's share of the units, every output tile stored to n_dst destinations
+ * (1..8): O_dst[0] is this GPU's own slice of O, the others the addresses, valid on this GPU, of the same
+ * slice inside each peer's full O. No counterpart in the reference (single GPU); it serves the
+ * (batch x head)-sharded configuration. The caller synchronises the group before reading peers' units. */
+int emmyb200_attention_fwd_allgather(int dtype, const void* Q, const void* K, const void* V,
+                                     void* const* O_dst, int n_dst, int64_t units, int64_t seq_q,
+                                     int64_t seq_k, int64_t d, float scale, void* cuda_stream);
+
 /* Reads (and clears) the device status word of the current device: 0 if no bounded wait has
  * expired since the last call, else a code naming kernel, role and pipeline stage.
  * Synchronises the device. */

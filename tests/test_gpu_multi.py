@@ -1,5 +1,5 @@
-"""Two-GPU path: the row-sharded GEMM whose kernel writes every output piece to both GPUs' C (TMA stores to
-peer-mapped memory), against the unsharded oracle. Skipped on a one-GPU box."""
+"""Two-GPU path: the row-sharded GEMM and the unit-sharded attention whose kernels write every output piece to both
+GPUs' copies of the result (TMA stores to peer-mapped memory), against the unsharded oracle. Skipped on a one-GPU box."""
 import os
 import socket
 
@@ -42,6 +42,21 @@ def _worker(rank: int, world: int, port: int):
         local = runtime.gemm(a[lo:hi].to(dev).contiguous(), b.to(dev), epilogue="gelu_tanh")
         gathered = shard.all_gather_rows(torch.empty(m, n, dtype=torch.bfloat16, device=dev), local)
         assert torch.equal(gathered, c_full)
+        # attention: units split over the ranks, every output tile stored to both copies of O
+        units, sq, sk, d = 4, 300, 260, 128
+        q, k, v = inputs.attention_inputs(units, sq, sk, d, "bf16")
+        ulo, uhi = shard.split_range(units, world, rank)
+        o_full, opeers = shard.peer_mapped_empty((units, sq, d), torch.bfloat16, dev)
+        o_full.zero_()
+        opeers.barrier()
+        ooff = ulo * sq * d * 2
+        odst = [o_full.data_ptr() + ooff] + [p + ooff for r, p in enumerate(opeers.buffer_ptrs) if r != rank]
+        runtime.attention_allgather(q[ulo:uhi].to(dev).contiguous(), k[ulo:uhi].to(dev).contiguous(), v[ulo:uhi].to(dev).contiguous(), odst)
+        opeers.barrier()
+        torch.cuda.synchronize()
+        assert runtime.device_status() == 0
+        ok, ratio = reference.gemm_tolerance_ok(o_full.cpu(), reference.attention_reference(q, k, v))
+        assert ok, f"rank {rank}: attention worst error {ratio:.2f}x the bound"
     finally:
         dist.destroy_process_group()
 
