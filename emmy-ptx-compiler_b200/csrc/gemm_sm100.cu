@@ -24,7 +24,6 @@
 // the MMA told to transpose) or row-major N x K (K-major, like A).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -54,8 +53,6 @@ struct GemmParams {
     int M, N, K;
     int m_blocks, n_blocks;
     int n_dst;              // destinations of every output piece (1 = the local C only)
-    int band;               // experiment hook: row-blocks per band of the tile order (0 = default)
-    int prefetch;           // k-blocks of L2 prefetch distance (0 = none)
     uint32_t* status;
 };
 
@@ -67,9 +64,8 @@ __device__ uint32_t g_gemm_status;
 
 // Tile order: bands of 16 row-blocks, column-blocks inside a band, row-blocks fastest, so CTAs that
 // run together share B column-blocks and a small set of A row-blocks.
-template <int kBandT = 16>
-__device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, int& mb, int& nb, int band_rt = 0) {
-    const int kBand = band_rt > 0 ? band_rt : kBandT;
+__device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, int& mb, int& nb) {
+    constexpr int kBand = 16;       // measured best of 2..64 at 8192^3 (1356 TFLOP/s at 2 or 64, 1473 at 16)
     const int per_band = kBand * n_blocks;
     const int band = t / per_band;
     const int first = band * kBand;
@@ -147,31 +143,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
                 int mb, nb;
-                tile_coords(t, p.m_blocks, p.n_blocks, mb, nb, p.band);
+                tile_coords(t, p.m_blocks, p.n_blocks, mb, nb);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
-                    // L2 prefetch of the operand boxes `p.prefetch` k-blocks ahead (into the next tile at the end
-                    // of this one): the ring holds about 2000 cycles of MMA work, less than a DRAM round trip.
-                    if (p.prefetch > 0) {
-                        int pk = kb + p.prefetch, pmb = mb, pnb = nb;
-                        bool valid = true;
-                        if (pk >= k_blocks) {
-                            pk -= k_blocks;
-                            const int nt = t + (int)gridDim.x;
-                            valid = nt < tiles && pk < k_blocks;
-                            if (valid) tile_coords(nt, p.m_blocks, p.n_blocks, pmb, pnb, p.band);
-                        }
-                        if (valid) {
-                            ptx::tma_prefetch_2d(&map_a, pk * kBK, pmb * kBM);
-                            if constexpr (B_NK) {
-                                ptx::tma_prefetch_2d(&map_b, pk * kBK, pnb * BN);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < BN / 64; ++j) ptx::tma_prefetch_2d(&map_b, pnb * BN + j * 64, pk * kBK);
-                            }
-                        }
-                    }
                     if (!(ok = bounded_wait(wctx, empty_bar(s), ph ^ 1, 0x01010000u | s))) break;
                     const uint32_t a_dst = smem_base + s * S::kStageBytes;
                     const uint32_t b_dst = a_dst + S::kABytes;
@@ -229,7 +204,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++acc_it) {
             int mb, nb;
-            tile_coords(t, p.m_blocks, p.n_blocks, mb, nb, p.band);
+            tile_coords(t, p.m_blocks, p.n_blocks, mb, nb);
             const int as = acc_it & 1;
             const uint32_t aph = (acc_it >> 1) & 1;
             // One thread waits; the outcome reaches the four warps through shared memory, so they all
@@ -293,208 +268,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, 512);
-    }
-}
-
-// ---- CTA-pair variant ---------------------------------------------------------------------------------
-// Two CTAs of a cluster work on one 256 x 256 tile with tcgen05.mma.cta_group::2: each CTA stages its own 128
-// rows of A and its own 128-column half of B (32 KiB a stage, six stages) and keeps the accumulators of its 128
-// rows in its own tensor memory; the even CTA of the pair issues the MMAs, which read both halves of B. Per CTA
-// the B traffic through shared memory is halved. Barriers: TMA completions of both CTAs count on the issuing
-// CTA's `full` barrier; `empty` and `acc_full` live in each CTA and get one commit each; `acc_empty` lives in
-// the issuing CTA and collects the eight epilogue warps of the pair.
-struct PairSmem {
-    static constexpr int kABytes = kBM * kBK * 2;
-    static constexpr int kBBytes = 128 * kBK * 2;
-    static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = 6;
-    static constexpr int kOutBytes = kBM * 64 * 2;
-    static constexpr int kOutOffset = kStages * kStageBytes;
-    static constexpr int kBarOffset = kOutOffset + 2 * kOutBytes;
-    static constexpr int kTotal = kBarOffset + 256 + 1024;
-};
-
-template <bool BF16, int EPI, bool B_NK>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         const __grid_constant__ OutMaps out, GemmParams p) {
-    using S = PairSmem;
-    constexpr int kStages = S::kStages;
-    constexpr int BN = 256;
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-    const uint32_t out_smem = smem_base + S::kOutOffset;
-    const uint32_t bar_base = smem_base + S::kBarOffset;
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-    auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
-    auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 2 + s); };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + S::kBarOffset + 8 * (2 * kStages + 4));
-    volatile uint32_t* abort_flag = tmem_slot + 1;
-    volatile uint32_t* epi_ok = tmem_slot + 2;
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = ptx::cluster_cta_rank();            // 0 issues the MMAs
-    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
-    const int k_blocks = (p.K + kBK - 1) / kBK;
-    const int tiles = p.m_blocks * p.n_blocks;                 // m_blocks counts 256-row blocks here
-    const WaitCtx wctx{abort_flag, p.status};
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
-        for (int s = 0; s < 2; ++s) { ptx::mbar_init(acc_full_bar(s), 1); ptx::mbar_init(acc_empty_bar(s), 8); }
-        *abort_flag = 0;
-        ptx::mbar_fence_init();
-        ptx::prefetch_tensormap(&map_a);
-        ptx::prefetch_tensormap(&map_b);
-    }
-    if (warp == 1) {
-        ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), 512);
-        ptx::tmem_relinquish_pair();
-    }
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    ptx::cluster_sync();                                       // the other CTA's barriers exist from here on
-    ptx::tc_fence_after_sync();
-    const uint32_t tmem_base = *tmem_slot;
-
-    if (warp == 0) {
-        // ---- TMA producer (both CTAs; completions count on CTA 0's barrier) -------------------------------
-        if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (int t = pair; t < tiles && ok; t += pairs) {
-                int mb, nb;
-                tile_coords<8>(t, p.m_blocks, p.n_blocks, mb, nb);
-                const int row0 = mb * 256 + (int)rank * kBM, col0 = nb * BN + (int)rank * 128;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1;
-                    if (!(ok = bounded_wait(wctx, empty_bar(s), ph ^ 1, 0x03010000u | s))) break;
-                    const uint32_t a_dst = smem_base + s * S::kStageBytes;
-                    const uint32_t b_dst = a_dst + S::kABytes;
-                    const uint32_t full0 = ptx::map_to_cta(full_bar(s), 0);
-                    if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
-                    ptx::tma_load_2d_pair(a_dst, &map_a, full0, kb * kBK, row0);
-                    if constexpr (B_NK) {
-                        ptx::tma_load_2d_pair(b_dst, &map_b, full0, kb * kBK, col0);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 2; ++j)
-                            ptx::tma_load_2d_pair(b_dst + j * (kBK * 128), &map_b, full0, col0 + j * 64, kb * kBK);
-                    }
-                }
-            }
-        }
-        __syncwarp();
-    } else if (warp == 1) {
-        // ---- MMA issuer (CTA 0 of the pair only) --------------------------------------------------------
-        if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = ptx::mma_idesc_f16(BF16, false, !B_NK, 256, BN);
-            uint32_t it = 0, acc_it = 0;
-            bool ok = true;
-            for (int t = pair; t < tiles && ok; t += pairs, ++acc_it) {
-                const int as = acc_it & 1;
-                const uint32_t aph = (acc_it >> 1) & 1;
-                if (!(ok = bounded_wait(wctx, acc_empty_bar(as), aph ^ 1, 0x03020000u | as))) break;
-                ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + as * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1;
-                    if (!(ok = bounded_wait(wctx, full_bar(s), ph, 0x03030000u | s))) break;
-                    ptx::tc_fence_after_sync();
-                    const uint32_t a_src = smem_base + s * S::kStageBytes;
-                    const uint32_t b_src = a_src + S::kABytes;
-#pragma unroll
-                    for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
-                        const uint64_t a_desc = ptx::smem_desc_sw128(a_src + kk * (kUmmaK * 2), 16, 1024);
-                        const uint64_t b_desc = B_NK ? ptx::smem_desc_sw128(b_src + kk * (kUmmaK * 2), 16, 1024)
-                                                     : ptx::smem_desc_sw128(b_src + kk * (kUmmaK * 128), kBK * 128, 1024);
-                        ptx::mma_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0);
-                    }
-                    ptx::mma_commit_pair(ptx::map_to_cta(empty_bar(s), 0));       // both producers may refill
-                    ptx::mma_commit_pair(ptx::map_to_cta(empty_bar(s), 1));
-                }
-                if (ok) {
-                    ptx::mma_commit_pair(ptx::map_to_cta(acc_full_bar(as), 0));
-                    ptx::mma_commit_pair(ptx::map_to_cta(acc_full_bar(as), 1));
-                }
-            }
-        }
-        __syncwarp();
-    } else {
-        // ---- epilogue (both CTAs, each its own 128 rows) ----------------------------------------------------
-        const int quarter = warp & 3;
-        const int row_in_tile = quarter * 32 + lane;
-        const bool issuer = threadIdx.x == 64;
-        uint32_t acc_it = 0, piece = 0;
-        bool ok = true;
-        for (int t = pair; t < tiles && ok; t += pairs, ++acc_it) {
-            int mb, nb;
-            tile_coords<8>(t, p.m_blocks, p.n_blocks, mb, nb);
-            const int row0 = mb * 256 + (int)rank * kBM;
-            const int as = acc_it & 1;
-            const uint32_t aph = (acc_it >> 1) & 1;
-            if (issuer) *epi_ok = bounded_wait(wctx, acc_full_bar(as), aph, 0x03040000u | as) ? 1u : 0u;
-            ptx::named_barrier(1, 128);
-            ok = *epi_ok != 0;
-            if (!ok) break;
-            ptx::tc_fence_after_sync();
-            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 64, ++piece) {
-                const uint32_t stage = out_smem + (piece & 1) * S::kOutBytes;
-                if (issuer) ptx::tma_store_wait_read<1>();
-                ptx::named_barrier(1, 128);
-                const uint32_t row_smem = stage + row_in_tile * 128;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    uint32_t r[32];
-                    ptx::tmem_ld_32x32b_x32(t_row + c + 32 * h, r);
-                    ptx::tmem_ld_wait();
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        float v[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float f = __uint_as_float(r[8 * q + j]);
-                            v[j] = (EPI == EMMYB200_EPI_GELU_TANH) ? gelu_tanh_fast(f) : f;
-                        }
-                        const uint32_t slot = (uint32_t)(4 * h + q) ^ (uint32_t)(row_in_tile & 7);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_smem + slot * 16),
-                                     "r"(pack2<BF16>(v[0], v[1])), "r"(pack2<BF16>(v[2], v[3])),
-                                     "r"(pack2<BF16>(v[4], v[5])), "r"(pack2<BF16>(v[6], v[7]))
-                                     : "memory");
-                    }
-                }
-                if (c + 64 >= BN) {                              // accumulator fully read: hand it back to CTA 0
-                    ptx::tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(as), 0));
-                }
-                ptx::fence_proxy_async_smem();
-                ptx::named_barrier(1, 128);
-                if (issuer && nb * BN + c < p.N && row0 < p.M) {
-                    for (int d = 0; d < p.n_dst; ++d) ptx::tma_store_2d(&out.m[d], stage, nb * BN + c, row0);
-                }
-                if (issuer) ptx::tma_store_commit();
-            }
-        }
-        if (issuer) ptx::tma_store_wait<0>();
-    }
-
-    // ---- teardown: neither CTA may leave while the other can still touch its shared or tensor memory ---------
-    if (*abort_flag) {
-        for (int i = 0; i < 64; ++i) __nanosleep(1000);
-    }
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    ptx::cluster_sync();
-    if (warp == 1) {
-        ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -584,8 +357,6 @@ static int launch_gemm(const void* A, const void* B, void* const* C, int n_dst, 
     p.m_blocks = (int)((M + kBM - 1) / kBM);
     p.n_blocks = (int)((N + BN - 1) / BN);
     p.n_dst = n_dst;
-    p.band = getenv("EMMYB200_GEMM_BAND") ? atoi(getenv("EMMYB200_GEMM_BAND")) : 0;
-    p.prefetch = getenv("EMMYB200_GEMM_PREFETCH") ? atoi(getenv("EMMYB200_GEMM_PREFETCH")) : 0;
     EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
     const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
@@ -594,56 +365,11 @@ static int launch_gemm(const void* A, const void* B, void* const* C, int n_dst, 
 }
 
 template <bool BF16, int EPI, bool B_NK>
-static int launch_gemm_pair(const void* A, const void* B, void* const* C, int n_dst, int64_t M, int64_t N, int64_t K, int64_t lda,
-                            int64_t ldb, int64_t ldc, cudaStream_t stream) {
-    using S = PairSmem;
-    CUtensorMap map_a, map_b;
-    OutMaps out;
-    int rc = make_tensor_map_2d(&map_a, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBM, kBK);
-    if (rc != EMMYB200_OK) return rc;
-    rc = B_NK ? make_tensor_map_2d(&map_b, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 128, kBK)
-              : make_tensor_map_2d(&map_b, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, kBK, 64);
-    if (rc != EMMYB200_OK) return rc;
-    for (int d = 0; d < kMaxDst; ++d) {
-        rc = make_tensor_map_2d(&out.m[d], C[d < n_dst ? d : 0], (uint64_t)M, (uint64_t)N, (uint64_t)ldc, kBM, 64);
-        if (rc != EMMYB200_OK) return rc;
-    }
-    auto kernel = gemm_tcgen05_pair_kernel<BF16, EPI, B_NK>;
-    EMMY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-    GemmParams p;
-    p.M = (int)M; p.N = (int)N; p.K = (int)K;
-    p.m_blocks = (int)((M + 255) / 256);
-    p.n_blocks = (int)((N + 255) / 256);
-    p.n_dst = n_dst;
-    p.band = 0;
-    p.prefetch = 0;
-    EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
-    const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;
-    const int64_t max_pairs = sm_count() / 2;
-    const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * pairs, 1, 1);
-    cfg.blockDim = dim3(kGemmThreads, 1, 1);
-    cfg.dynamicSmemBytes = S::kTotal;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, out, p);
-    if (e != cudaSuccess) return fail((int)e, "launch of gemm_tcgen05_pair_kernel: %s", cudaGetErrorString(e));
-    return launch_status("gemm_tcgen05_pair_kernel");
-}
-
-template <bool BF16, int EPI, bool B_NK>
 static int pick_tile(const void* A, const void* B, void* const* C, int n_dst, int64_t M, int64_t N, int64_t K, int64_t lda,
                      int64_t ldb, int64_t ldc, cudaStream_t stream) {
     // 128 x 256 tiles: with both operands read from shared memory by one CTA, the 128 x 128 shape is bound by
     // shared-memory bandwidth (measured 0.6-0.7x the throughput at every size from 2048^3 to 16384^3), which
     // costs more than the emptier last wave of the wide tile. Narrow outputs keep the narrow tile.
-    const char* mode = getenv("EMMYB200_GEMM_PAIR");            // experiment hook while the pair kernel is evaluated
-    if (mode && atoi(mode) == 1 && M > 128 && N > 128) return launch_gemm_pair<BF16, EPI, B_NK>(A, B, C, n_dst, M, N, K, lda, ldb, ldc, stream);
     if (N > 128) return launch_gemm<256, BF16, EPI, B_NK>(A, B, C, n_dst, M, N, K, lda, ldb, ldc, stream);
     return launch_gemm<128, BF16, EPI, B_NK>(A, B, C, n_dst, M, N, K, lda, ldb, ldc, stream);
 }
