@@ -19,7 +19,7 @@
 
 #if defined(__CUDACC__)
 #define EMMY_HD __host__ __device__ __forceinline__
-#define EMMY_HD_NOINLINE __host__ __device__ __noinline__
+#define EMMY_HD_NOINLINE static __host__ __device__ __noinline__
 #else
 #define EMMY_HD static inline
 #define EMMY_HD_NOINLINE static

@@ -1,0 +1,236 @@
+// General elementwise kernel: y[i] = f(x0[i], x1[i], ...) for a straight-line program of ops from the
+// reference's elementwise table (emmyptx/ops.py:212-290, `lower_op`).
+//
+// The reference prints the instructions of each `Assign` into the kernel it is compiling
+// (emmyptx/kernel.py:766-784); a precompiled library cannot, so the cell program travels as data: up to 48
+// steps `dst = op(a, b, c)` over 16 value slots, operands being slots or constants. One CTA-wide interpreter
+// loop runs it -- the control flow is the same for every thread, so there is no divergence -- with the slots
+// held per thread as float4 (four elements at a time, 128-bit global accesses, 16-bit inputs and outputs
+// widened / rounded once at the ends, as emmyptx/kernel.py:693-712 does).
+// exp, sin, cos and tanh are the library's own <= 2 ulp functions; log, erf, pow, sqrt and the divisions use
+// CUDA's device math functions (1-2 ulp), well inside the reference's 1e-5 class for these ops.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "emmy_math.cuh"
+
+namespace emmy {
+
+constexpr int kPwThreads = 256;
+constexpr int kPwSlots = EMMYB200_PW_MAX_SLOTS;
+constexpr int kPwUnroll = 2;
+
+// One scalar op; `op` is uniform across the CTA, so the switch never diverges.
+__device__ __forceinline__ float pw_apply(int op, float a, float b, float c) {
+    switch (op) {
+        case EMMYB200_PW_ADD: return __fadd_rn(a, b);
+        case EMMYB200_PW_SUB: return __fsub_rn(a, b);
+        case EMMYB200_PW_MUL: return __fmul_rn(a, b);
+        case EMMYB200_PW_DIV: return __fdiv_rn(a, b);
+        case EMMYB200_PW_MAX: return fmaxf(a, b);
+        case EMMYB200_PW_MIN: return fminf(a, b);
+        case EMMYB200_PW_RELU: return fmaxf(a, 0.0f);
+        case EMMYB200_PW_SQUARE: return __fmul_rn(a, a);
+        case EMMYB200_PW_COPY: return a;
+        case EMMYB200_PW_NEG: return -a;
+        case EMMYB200_PW_ABS: return fabsf(a);
+        case EMMYB200_PW_RCP: return __frcp_rn(a);
+        case EMMYB200_PW_SQRT: return __fsqrt_rn(a);
+        case EMMYB200_PW_RSQRT: return __frcp_rn(__fsqrt_rn(a));       // as the reference: sqrt.rn then rcp.rn (ops.py:249-252)
+        case EMMYB200_PW_EXP: return emmy_expf(a);
+        case EMMYB200_PW_LOG: return logf(a);
+        case EMMYB200_PW_SIGMOID: return __frcp_rn(__fadd_rn(1.0f, emmy_expf(-a)));
+        case EMMYB200_PW_TANH: return emmy_tanhf(a);
+        case EMMYB200_PW_ERF: return erff(a);
+        case EMMYB200_PW_SIN: return emmy_sinf(a);
+        case EMMYB200_PW_COS: return emmy_cosf(a);
+        case EMMYB200_PW_POW: return powf(a, b);
+        case EMMYB200_PW_EQ: return a == b ? 1.0f : 0.0f;
+        case EMMYB200_PW_NE: return a != b ? 1.0f : 0.0f;
+        case EMMYB200_PW_GT: return a > b ? 1.0f : 0.0f;
+        case EMMYB200_PW_LT: return a < b ? 1.0f : 0.0f;
+        case EMMYB200_PW_GE: return a >= b ? 1.0f : 0.0f;
+        case EMMYB200_PW_LE: return a <= b ? 1.0f : 0.0f;
+        case EMMYB200_PW_WHERE: return a != 0.0f ? b : c;
+        case EMMYB200_PW_AND: return (a != 0.0f && b != 0.0f) ? 1.0f : 0.0f;
+        case EMMYB200_PW_OR: return (a != 0.0f || b != 0.0f) ? 1.0f : 0.0f;
+        case EMMYB200_PW_NOT: return a == 0.0f ? 1.0f : 0.0f;
+        case EMMYB200_PW_FLOORDIV: return floorf(__fdiv_rn(a, b));
+        case EMMYB200_PW_MOD: return __fsub_rn(a, __fmul_rn(b, floorf(__fdiv_rn(a, b))));
+        default: return a;
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ float4 pw_load4(const void* base, int64_t v) {
+    if constexpr (sizeof(T) == 4) {
+        return __ldcs(reinterpret_cast<const float4*>(base) + v);
+    } else {
+        const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(base) + v);
+        if constexpr (std::is_same<T, __half>::value) {
+            const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+            const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+            return make_float4(lo.x, lo.y, hi.x, hi.y);
+        } else {
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+            return make_float4(lo.x, lo.y, hi.x, hi.y);
+        }
+    }
+}
+
+__device__ __forceinline__ float pw_load1(const void* base, int dtype, int64_t i) {
+    if (dtype == EMMYB200_F32) return reinterpret_cast<const float*>(base)[i];
+    if (dtype == EMMYB200_F16) return __half2float(reinterpret_cast<const __half*>(base)[i]);
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[i]);
+}
+
+__device__ __forceinline__ void pw_store1(void* base, int dtype, int64_t i, float v) {
+    if (dtype == EMMYB200_F32) reinterpret_cast<float*>(base)[i] = v;
+    else if (dtype == EMMYB200_F16) reinterpret_cast<__half*>(base)[i] = __float2half_rn(v);
+    else reinterpret_cast<__nv_bfloat16*>(base)[i] = __float2bfloat16_rn(v);
+}
+
+struct PwArgs {
+    const void* in[EMMYB200_PW_MAX_INPUTS];
+    void* out;
+    int64_t n;
+};
+
+// VEC: all buffers are aligned for 128-bit (fp32) / 64-bit (16-bit types) accesses of four elements.
+template <bool VEC>
+__global__ void __launch_bounds__(kPwThreads) pointwise_program_kernel(const __grid_constant__ emmyb200_pw_program prog, PwArgs args) {
+    // Per-thread value slots, indexed by the program: they live in local memory, i.e. in L1 for the few slots a
+    // program touches, and do not cap the number of resident threads the way a shared-memory file would.
+    float4 slots[kPwSlots][kPwUnroll];
+    const int tid = threadIdx.x;
+    const int64_t groups = VEC ? args.n / 4 : (args.n + 3) / 4;
+    const int64_t stride = (int64_t)gridDim.x * kPwThreads;
+    for (int64_t g0 = (int64_t)blockIdx.x * kPwThreads + tid; g0 < groups; g0 += stride * kPwUnroll) {
+        // kPwUnroll groups of four elements per thread and trip: more bytes in flight, one dispatch per step for all
+        for (int k = 0; k < prog.n_inputs; ++k) {
+#pragma unroll
+            for (int u = 0; u < kPwUnroll; ++u) {
+                const int64_t g = g0 + u * stride;
+                float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (g < groups) {
+                    if constexpr (VEC) {
+                        const int dt = prog.in_dtype[k];
+                        v = dt == EMMYB200_F32 ? pw_load4<float>(args.in[k], g)
+                          : dt == EMMYB200_F16 ? pw_load4<__half>(args.in[k], g) : pw_load4<__nv_bfloat16>(args.in[k], g);
+                    } else {
+                        const int64_t i = g * 4;
+                        v.x = pw_load1(args.in[k], prog.in_dtype[k], i);
+                        v.y = i + 1 < args.n ? pw_load1(args.in[k], prog.in_dtype[k], i + 1) : 0.0f;
+                        v.z = i + 2 < args.n ? pw_load1(args.in[k], prog.in_dtype[k], i + 2) : 0.0f;
+                        v.w = i + 3 < args.n ? pw_load1(args.in[k], prog.in_dtype[k], i + 3) : 0.0f;
+                    }
+                }
+                slots[k][u] = v;
+            }
+        }
+        for (int s = 0; s < prog.n_steps; ++s) {
+            const emmyb200_pw_step st = prog.steps[s];
+#pragma unroll
+            for (int u = 0; u < kPwUnroll; ++u) {
+                auto operand = [&](int o) {
+                    if (o >= kPwSlots) { const float c = prog.consts[o - kPwSlots]; return make_float4(c, c, c, c); }
+                    return slots[o][u];
+                };
+                const float4 a = operand(st.a), b = operand(st.b), c = operand(st.c);
+                float4 r;
+                r.x = pw_apply(st.op, a.x, b.x, c.x);
+                r.y = pw_apply(st.op, a.y, b.y, c.y);
+                r.z = pw_apply(st.op, a.z, b.z, c.z);
+                r.w = pw_apply(st.op, a.w, b.w, c.w);
+                slots[st.dst][u] = r;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kPwUnroll; ++u) {
+            const int64_t g = g0 + u * stride;
+            if (g >= groups) continue;
+            const float4 y = slots[prog.out_slot][u];
+            if constexpr (VEC) {
+                if (prog.out_dtype == EMMYB200_F32) {
+                    __stcs(reinterpret_cast<float4*>(args.out) + g, y);
+                } else if (prog.out_dtype == EMMYB200_F16) {
+                    const __half2 lo = __floats2half2_rn(y.x, y.y), hi = __floats2half2_rn(y.z, y.w);
+                    __stcs(reinterpret_cast<uint2*>(args.out) + g, make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi)));
+                } else {
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+                    __stcs(reinterpret_cast<uint2*>(args.out) + g, make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi)));
+                }
+            } else {
+                const int64_t i = g * 4;
+                pw_store1(args.out, prog.out_dtype, i, y.x);
+                if (i + 1 < args.n) pw_store1(args.out, prog.out_dtype, i + 1, y.y);
+                if (i + 2 < args.n) pw_store1(args.out, prog.out_dtype, i + 2, y.z);
+                if (i + 3 < args.n) pw_store1(args.out, prog.out_dtype, i + 3, y.w);
+            }
+        }
+    }
+    // the last n % 4 elements of the vector form: one thread, scalar accesses
+    if constexpr (VEC) {
+        const int tail = (int)(args.n & 3);
+        if (blockIdx.x == 0 && tid < tail) {
+            const int64_t i = (args.n & ~(int64_t)3) + tid;
+            float regs[kPwSlots];
+            for (int k = 0; k < prog.n_inputs; ++k) regs[k] = pw_load1(args.in[k], prog.in_dtype[k], i);
+            for (int s = 0; s < prog.n_steps; ++s) {
+                const emmyb200_pw_step st = prog.steps[s];
+                auto operand = [&](int o) { return o >= kPwSlots ? prog.consts[o - kPwSlots] : regs[o]; };
+                regs[st.dst] = pw_apply(st.op, operand(st.a), operand(st.b), operand(st.c));
+            }
+            pw_store1(args.out, prog.out_dtype, i, regs[prog.out_slot]);
+        }
+    }
+}
+
+static int elem_size(int dtype) { return dtype == EMMYB200_F32 ? 4 : 2; }
+
+}  // namespace emmy
+
+extern "C" int emmyb200_pointwise_program(const emmyb200_pw_program* prog, const void* const* inputs, void* out, int64_t n,
+                                          void* cuda_stream) {
+    using namespace emmy;
+    if (prog == nullptr) return fail(EMMYB200_ERR_ARG, "pointwise_program: null program");
+    if (prog->n_inputs < 1 || prog->n_inputs > EMMYB200_PW_MAX_INPUTS) return fail(EMMYB200_ERR_ARG, "pointwise_program: %d inputs (1 to %d)", prog->n_inputs, EMMYB200_PW_MAX_INPUTS);
+    if (prog->n_steps < 0 || prog->n_steps > EMMYB200_PW_MAX_STEPS) return fail(EMMYB200_ERR_ARG, "pointwise_program: %d steps (0 to %d)", prog->n_steps, EMMYB200_PW_MAX_STEPS);
+    if (prog->out_slot < 0 || prog->out_slot >= kPwSlots) return fail(EMMYB200_ERR_ARG, "pointwise_program: output slot %d", prog->out_slot);
+    auto dtype_ok = [](int d) { return d == EMMYB200_F32 || d == EMMYB200_F16 || d == EMMYB200_BF16; };
+    if (!dtype_ok(prog->out_dtype)) return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_program: output dtype %d", prog->out_dtype);
+    for (int k = 0; k < prog->n_inputs; ++k)
+        if (!dtype_ok(prog->in_dtype[k])) return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_program: input %d has dtype %d", k, prog->in_dtype[k]);
+    for (int s = 0; s < prog->n_steps; ++s) {
+        const emmyb200_pw_step& st = prog->steps[s];
+        if (st.op >= EMMYB200_PW_OP_COUNT) return fail(EMMYB200_ERR_ARG, "pointwise_program: step %d has unknown op %d", s, st.op);
+        if (st.dst >= kPwSlots) return fail(EMMYB200_ERR_ARG, "pointwise_program: step %d writes slot %d", s, st.dst);
+        for (int o : {st.a, st.b, st.c})
+            if (o >= kPwSlots + EMMYB200_PW_MAX_CONSTS) return fail(EMMYB200_ERR_ARG, "pointwise_program: step %d reads operand %d", s, o);
+    }
+    if (n < 0) return fail(EMMYB200_ERR_SHAPE, "pointwise_program: n = %lld is negative", (long long)n);
+    if (n == 0) return EMMYB200_OK;
+    if (inputs == nullptr || out == nullptr) return fail(EMMYB200_ERR_ARG, "pointwise_program: null buffer");
+    PwArgs args;
+    bool vec = aligned(out, 4 * elem_size(prog->out_dtype));
+    if (!aligned(out, elem_size(prog->out_dtype))) return fail(EMMYB200_ERR_ALIGN, "pointwise_program: misaligned output");
+    for (int k = 0; k < EMMYB200_PW_MAX_INPUTS; ++k) args.in[k] = nullptr;
+    for (int k = 0; k < prog->n_inputs; ++k) {
+        if (inputs[k] == nullptr) return fail(EMMYB200_ERR_ARG, "pointwise_program: null buffer");
+        if (!aligned(inputs[k], elem_size(prog->in_dtype[k]))) return fail(EMMYB200_ERR_ALIGN, "pointwise_program: misaligned input %d", k);
+        vec = vec && aligned(inputs[k], 4 * elem_size(prog->in_dtype[k]));
+        args.in[k] = inputs[k];
+    }
+    args.out = out;
+    args.n = n;
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    const int64_t groups = (n + 3) / 4;
+    const int64_t want = (groups + kPwThreads * kPwUnroll - 1) / (kPwThreads * kPwUnroll);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    const unsigned blocks = (unsigned)(want < cap ? want : cap);
+    if (vec) pointwise_program_kernel<true><<<blocks, kPwThreads, 0, s>>>(*prog, args);
+    else pointwise_program_kernel<false><<<blocks, kPwThreads, 0, s>>>(*prog, args);
+    return launch_status("pointwise_program_kernel");
+}

@@ -336,6 +336,19 @@ def pointwise_kernel(n: int, expr: str = "exp_sin_tanh", name: str = "k_pointwis
     return g, k, _launch(k, ["x", "y"], n)
 
 
+def elementwise_kernel(n: int, inputs: dict, steps: list, out_dtype: str = "f32", name: str = "k_elementwise"):
+    """A general elementwise kernel: `inputs` maps buffer name -> dtype (each of n elements); `steps` is a list of
+    (value name, op name, args) with args naming earlier values, the loaded inputs (by buffer name) or numbers;
+    the last step's value is written to `out`."""
+    a0 = Axis("a0", Dim(n))
+    body = [Load([b], b, [Var("a0")]) for b in inputs]
+    body += [Assign(v, Op(op), list(args)) for v, op, args in steps]
+    body.append(Write("out", [Var("a0")], [steps[-1][0]]))
+    k = KernelOp(name, [Tile([a0], body)])
+    g = _graph(k, [tensor(b, [n], dt) for b, dt in inputs.items()], [tensor("out", [n], out_dtype)])
+    return g, k, _launch(k, [*inputs, "out"], n)
+
+
 def index_gather_kernel(n: int, mul: int = 7919, add: int = 13, div: int = 3, shift: int = 2, name: str = "k_gather"):
     """y[i] = (x[(i*mul + add) % n] // div) ^ (i >> shift), int32."""
     a0 = Axis("a0", Dim(n))

@@ -85,6 +85,9 @@ def algorithmic_work(handle: dict) -> tuple[float, str]:
     p, v = handle["params"], handle["variant"]
     if v in ("pointwise_f32", "index_gather_i32"):
         return 8.0 * p["n"], "B"
+    if v == "pointwise_program":
+        size = {"f32": 4, "f16": 2, "bf16": 2}
+        return float(p["n"]) * (sum(size[d] for d in p["program"]["in_dtypes"]) + size[p["program"]["out_dtype"]]), "B"
     if v == "gemm":
         return 2.0 * p["m"] * p["n"] * p["k"], "flop"
     if v == "attention_fwd":

@@ -237,6 +237,70 @@ def _int_literals(kernel) -> set:
     return found
 
 
+PW_SLOTS, PW_CONSTS, PW_STEPS, PW_INPUTS = 16, 16, 48, 4
+PW_OP_NAMES = {"add", "subtract", "multiply", "divide", "maximum", "minimum", "relu", "square", "copy", "negative", "abs",
+               "reciprocal", "sqrt", "rsqrt", "exp", "exp_fast", "log", "sigmoid", "tanh", "erf", "sin", "cos", "pow", "equal",
+               "not_equal", "greater", "less", "greater_equal", "less_equal", "where", "bitwise_and", "bitwise_or",
+               "bitwise_not", "floor_divide", "mod", "remainder"}
+
+
+def build_program(tile, tensors: dict, out_name: str, out_value_name) -> dict:
+    """The tile's cell program as data for the general elementwise kernel: inputs in slots 0.., one slot per live
+    value (slots are reused once a value is dead), numeric operands in the constant table."""
+    stmts = list(tile.body)
+    inputs, slot_of = [], {}
+    for s in stmts:
+        if _kind(s) == "Load":
+            if s.input not in inputs:
+                inputs.append(s.input)
+            slot_of[s.names[0]] = inputs.index(s.input)
+    if len(inputs) > PW_INPUTS:
+        raise Unmatched(f"{len(inputs)} input buffers: the general elementwise kernel takes {PW_INPUTS}")
+    assigns = [s for s in stmts if _kind(s) == "Assign"]
+    if any(_kind(s) not in ("Load", "Assign", "Write") for s in stmts):
+        raise Unmatched("the general elementwise kernel runs Load / Assign / Write programs")
+    last_use = {}
+    for i, s in enumerate(assigns):
+        for a in s.args:
+            if isinstance(a, str):
+                last_use[a] = i
+    last_use[out_value_name] = len(assigns)
+    free = [k for k in range(PW_SLOTS - 1, len(inputs) - 1, -1)]
+    consts, steps = [], []
+    for i, s in enumerate(assigns):
+        if _dtype_name(s.dtype) in INT_DTYPES:
+            raise Unmatched("integer Assigns have no general kernel (only the index gather)")
+        if s.op.name not in PW_OP_NAMES:
+            raise OpError(f"elementwise op {s.op.name!r} is not supported")
+        ops = []
+        for a in s.args:
+            if isinstance(a, str):
+                if a not in slot_of:
+                    raise Unmatched(f"use of undefined name {a!r}")
+                ops.append(slot_of[a])
+            else:
+                v = float(a)
+                if v not in consts:
+                    consts.append(v)
+                if len(consts) > PW_CONSTS:
+                    raise Unmatched(f"more than {PW_CONSTS} distinct constants")
+                ops.append(PW_SLOTS + consts.index(v))
+        for a in set(x for x in s.args if isinstance(x, str)):          # operands that die here free their slots
+            if last_use.get(a) == i and slot_of[a] >= len(inputs):
+                free.append(slot_of[a])
+        if not free:
+            raise Unmatched(f"more than {PW_SLOTS} live values")
+        dst = free.pop()
+        slot_of[s.name] = dst
+        steps.append([s.op.name, dst, *(ops + [0, 0])[:3]])
+        if s.name not in last_use:                                      # never read: its slot is free again at once
+            free.append(dst)
+    if len(steps) > PW_STEPS:
+        raise Unmatched(f"{len(steps)} steps: the general elementwise kernel takes {PW_STEPS}")
+    return {"inputs": inputs, "in_dtypes": [tensors[b][1] for b in inputs], "out_dtype": tensors[out_name][1],
+            "out_slot": slot_of[out_value_name], "consts": consts, "steps": steps}
+
+
 def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
     tensors = tensor_table(graph)
     tiles = [s for s in kernel.body if _kind(s) == "Tile"]
@@ -262,8 +326,18 @@ def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict
     if not np.array_equal(out_idx, cells) or math.prod(tensors[out_name][0]) != n:
         raise Unmatched("streaming variants write cell i to element i")
     buffers = {b for b, _, _ in it.loads}
-    if len(buffers) != 1 or any(cnt != 1 for _, _, cnt in it.loads):
-        raise Unmatched("streaming variants read one input buffer, one element per load")
+    if any(cnt != 1 for _, _, cnt in it.loads):
+        raise Unmatched("streaming variants read one element per load")
+    float_types = ("f32", "f16", "bf16")
+    general = (tensors[out_name][1] in float_types and all(tensors[b][1] in float_types for b in buffers)
+               and all(np.array_equal(i, cells) for _, i, _ in it.loads)
+               and all(math.prod(tensors[b][0]) == n for b in buffers))
+    if general and not (len(buffers) == 1 and tensors[next(iter(buffers))][1] == "f32" and tensors[out_name][1] == "f32"):
+        prog = build_program(tile, tensors, out_name, tile.body[-1].values[0] if _kind(tile.body[-1]) == "Write" else None)
+        return {"variant": "pointwise_program", "params": {"n": n, "program": {k: v for k, v in prog.items() if k != "inputs"}},
+                "inputs": prog["inputs"], "outputs": [out_name]}
+    if len(buffers) != 1:
+        raise Unmatched("streaming variants read one input buffer")
     (src,) = buffers
     src_shape, src_dtype = tensors[src]
     out_dtype = tensors[out_name][1]
@@ -278,8 +352,10 @@ def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict
         for op, f in POINTWISE_F64.items():
             if np.allclose(got, f(x), rtol=1e-9, atol=1e-12):
                 return {"variant": "pointwise_f32", "params": {"op": op, "n": n}, "inputs": [src], "outputs": [out_name]}
-        raise Unmatched("no float streaming variant computes this expression "
-                        f"(have: {', '.join(POINTWISE_F64)})")
+        # not one of the specialised expressions: the general elementwise kernel runs the program as data
+        prog = build_program(tile, tensors, out_name, tile.body[-1].values[0])
+        return {"variant": "pointwise_program", "params": {"n": n, "program": {k: v for k, v in prog.items() if k != "inputs"}},
+                "inputs": prog["inputs"], "outputs": [out_name]}
     if src_dtype == "i32" and out_dtype == "i32":
         size = math.prod(src_shape)
         if size != n:

@@ -104,6 +104,8 @@ def launch(handle: dict, bufs: dict, stream=None) -> None:
     out = bufs[handle["outputs"][0]]
     if v == "pointwise_f32":
         runtime.pointwise(p["op"], ins[0].reshape(-1), out=out.reshape(-1), stream=stream)
+    elif v == "pointwise_program":
+        runtime.pointwise_program(p["program"], [t.reshape(-1) for t in ins], out.reshape(-1), stream=stream)
     elif v == "index_gather_i32":
         runtime.index_gather(ins[0].reshape(-1), p["mul"], p["add"], p["div"], p["shift"], p["trunc"], out=out.reshape(-1),
                              stream=stream)

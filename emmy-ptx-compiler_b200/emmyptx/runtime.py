@@ -16,6 +16,26 @@ F32, F16, BF16, I32 = 0, 1, 2, 3
 OP_EXP_SIN_TANH, OP_EXP, OP_SIN, OP_COS, OP_TANH, OP_GELU_TANH = range(6)
 POINTWISE_OPS = {"exp_sin_tanh": OP_EXP_SIN_TANH, "exp": OP_EXP, "sin": OP_SIN, "cos": OP_COS,
                  "tanh": OP_TANH, "gelu_tanh": OP_GELU_TANH}
+PW_MAX_SLOTS, PW_MAX_CONSTS, PW_MAX_STEPS, PW_MAX_INPUTS = 16, 16, 48, 4
+PW_OPS = {name: i for i, name in enumerate(
+    ["add", "subtract", "multiply", "divide", "maximum", "minimum", "relu", "square", "copy", "negative", "abs", "reciprocal",
+     "sqrt", "rsqrt", "exp", "log", "sigmoid", "tanh", "erf", "sin", "cos", "pow", "equal", "not_equal", "greater", "less",
+     "greater_equal", "less_equal", "where", "bitwise_and", "bitwise_or", "bitwise_not", "floor_divide", "mod"])}
+PW_OPS.update(exp_fast=PW_OPS["exp"], remainder=PW_OPS["mod"])
+DTYPE_CODES = {"f32": F32, "f16": F16, "bf16": BF16, "i32": I32}
+
+
+class PwStep(ctypes.Structure):
+    _fields_ = [("op", ctypes.c_uint8), ("dst", ctypes.c_uint8), ("a", ctypes.c_uint8), ("b", ctypes.c_uint8),
+                ("c", ctypes.c_uint8), ("reserved", ctypes.c_uint8 * 3)]
+
+
+class PwProgram(ctypes.Structure):
+    _fields_ = [("n_inputs", ctypes.c_int32), ("n_steps", ctypes.c_int32), ("out_slot", ctypes.c_int32),
+                ("out_dtype", ctypes.c_int32), ("in_dtype", ctypes.c_int32 * PW_MAX_INPUTS),
+                ("consts", ctypes.c_float * PW_MAX_CONSTS), ("steps", PwStep * PW_MAX_STEPS)]
+
+
 EPI_NONE, EPI_GELU_TANH = 0, 1
 EPILOGUES = {None: EPI_NONE, "none": EPI_NONE, "gelu_tanh": EPI_GELU_TANH}
 GEMM_B_NK = 1
@@ -26,6 +46,8 @@ _SIGNATURES = {
     "emmyb200_last_error": (ctypes.c_char_p, []),
     "emmyb200_pointwise_f32": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
                                               ctypes.c_void_p]),
+    "emmyb200_pointwise_program": (ctypes.c_int, [ctypes.POINTER(PwProgram), ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p,
+                                                  ctypes.c_int64, ctypes.c_void_p]),
     "emmyb200_index_gather_i32": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                                  ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                                                  ctypes.c_void_p]),
@@ -105,6 +127,30 @@ def pointwise(op: str, x, out=None, stream=None):
     out = torch.empty_like(x) if out is None else out
     _need_cuda(out)
     check(library().emmyb200_pointwise_f32(POINTWISE_OPS[op], x.data_ptr(), out.data_ptr(), x.numel(), _stream(stream)))
+    return out
+
+
+def make_program(program: dict) -> PwProgram:
+    """The C struct for a program in the form the matcher emits: {"in_dtypes": [...], "out_dtype": ..., "out_slot": k,
+    "consts": [...], "steps": [[op name, dst, a, b, c], ...]} (operands >= PW_MAX_SLOTS name constants)."""
+    p = PwProgram()
+    p.n_inputs, p.n_steps = len(program["in_dtypes"]), len(program["steps"])
+    p.out_slot, p.out_dtype = program["out_slot"], DTYPE_CODES[program["out_dtype"]]
+    for i, d in enumerate(program["in_dtypes"]):
+        p.in_dtype[i] = DTYPE_CODES[d]
+    for i, c in enumerate(program["consts"]):
+        p.consts[i] = c
+    for i, (op, dst, a, b, c) in enumerate(program["steps"]):
+        p.steps[i].op, p.steps[i].dst, p.steps[i].a, p.steps[i].b, p.steps[i].c = PW_OPS[op], dst, a, b, c
+    return p
+
+
+def pointwise_program(program: dict, inputs: list, out, stream=None):
+    """out[i] = program(inputs[0][i], inputs[1][i], ...): the general elementwise kernel."""
+    _need_cuda(out, *inputs)
+    arr = (ctypes.c_void_p * len(inputs))(*[t.data_ptr() for t in inputs])
+    prog = make_program(program)
+    check(library().emmyb200_pointwise_program(ctypes.byref(prog), arr, out.data_ptr(), out.numel(), _stream(stream)))
     return out
 
 

@@ -56,6 +56,36 @@ const char* emmyb200_last_error(void);
 #define EMMYB200_OP_GELU_TANH 5
 int emmyb200_pointwise_f32(int op, const float* x, float* y, int64_t n, void* cuda_stream);
 
+/* Any other straight-line elementwise expression over up to 4 same-sized inputs: the cell program of a
+ * one-axis `Tile` (emmyptx/kernel.py:766-784 `visit_Assign` calling emmyptx/ops.py:212 `lower_op` once per
+ * statement) handed over as data. Values are fp32 (the reference's only compute type, emmyptx/kernel.py:31-38);
+ * f16 / bf16 buffers are widened on load and rounded once on store. A step computes
+ * slot[dst] = op(operand a, b, c); an operand < EMMYB200_PW_MAX_SLOTS names a slot, otherwise constant
+ * consts[operand - EMMYB200_PW_MAX_SLOTS]. Inputs arrive in slots 0 .. n_inputs-1; `out_slot` is stored. */
+#define EMMYB200_PW_MAX_SLOTS 16
+#define EMMYB200_PW_MAX_CONSTS 16
+#define EMMYB200_PW_MAX_STEPS 48
+#define EMMYB200_PW_MAX_INPUTS 4
+enum {
+    EMMYB200_PW_ADD, EMMYB200_PW_SUB, EMMYB200_PW_MUL, EMMYB200_PW_DIV, EMMYB200_PW_MAX, EMMYB200_PW_MIN,
+    EMMYB200_PW_RELU, EMMYB200_PW_SQUARE, EMMYB200_PW_COPY, EMMYB200_PW_NEG, EMMYB200_PW_ABS, EMMYB200_PW_RCP,
+    EMMYB200_PW_SQRT, EMMYB200_PW_RSQRT, EMMYB200_PW_EXP, EMMYB200_PW_LOG, EMMYB200_PW_SIGMOID, EMMYB200_PW_TANH,
+    EMMYB200_PW_ERF, EMMYB200_PW_SIN, EMMYB200_PW_COS, EMMYB200_PW_POW, EMMYB200_PW_EQ, EMMYB200_PW_NE,
+    EMMYB200_PW_GT, EMMYB200_PW_LT, EMMYB200_PW_GE, EMMYB200_PW_LE, EMMYB200_PW_WHERE, EMMYB200_PW_AND,
+    EMMYB200_PW_OR, EMMYB200_PW_NOT, EMMYB200_PW_FLOORDIV, EMMYB200_PW_MOD, EMMYB200_PW_OP_COUNT
+};
+typedef struct {
+    uint8_t op, dst, a, b, c, reserved[3];
+} emmyb200_pw_step;
+typedef struct {
+    int32_t n_inputs, n_steps, out_slot, out_dtype;
+    int32_t in_dtype[EMMYB200_PW_MAX_INPUTS];
+    float consts[EMMYB200_PW_MAX_CONSTS];
+    emmyb200_pw_step steps[EMMYB200_PW_MAX_STEPS];
+} emmyb200_pw_program;
+int emmyb200_pointwise_program(const emmyb200_pw_program* program, const void* const* inputs, void* out,
+                               int64_t n, void* cuda_stream);
+
 /* The int32 index-math gather
  *     y[i] = (x[(i * mul + add) mod n] div d) xor (i >> shift),   0 <= i < n,
  * i.e. the s32 instruction stream of emmyptx/intmath.py:36-38, :87-117 and

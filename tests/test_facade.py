@@ -68,8 +68,11 @@ def test_layout_flags_and_ragged_shapes():
 
 
 def test_unsupported_ir_is_a_compile_error():
-    with pytest.raises(CompileError, match="no float streaming variant"):
-        handle(ir.pointwise_kernel(100, "erf"))
+    assert handle(ir.pointwise_kernel(100, "erf"))["variant"] == "pointwise_program"     # any op-table expression compiles
+    g, k, launch = ir.pointwise_kernel(100, "exp")
+    k.body[0].body.insert(1, ir.Loop(ir.Axis("r0", ir.Dim(4)), []))
+    with pytest.raises(CompileError, match="no kernel variant"):
+        handle((g, k, launch))
     g, k, launch = ir.pointwise_kernel(100, "exp")
     k.body[0].body[1].op = ir.Op("frobnicate")
     with pytest.raises(CompileError, match="not supported"):          # OpError surfaces as CompileError
@@ -110,7 +113,7 @@ def test_compile_py_command_line(tmp_path):
     r = subprocess.run([sys.executable, str(COMPILE), str(tmp_path / "k_idx.ir.json")], capture_output=True, text=True)
     assert json.loads(r.stdout)["arg_order"] == ["x", "y"]
     # unsupported IR: non-zero exit, message on stderr, nothing on stdout
-    g, k, launch = ir.pointwise_kernel(64, "erf", name="k_erf")
+    g, k, launch = ir.pointwise_kernel(64, "frobnicate", name="k_erf")
     (tmp_path / "k_erf.ir.json").write_text(json.dumps(g.to_dict()))
     r = subprocess.run([sys.executable, str(COMPILE), str(tmp_path / "k_erf.ir.json")], capture_output=True, text=True)
     assert r.returncode != 0 and "compile error" in r.stderr and r.stdout == ""

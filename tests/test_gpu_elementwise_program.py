@@ -1,0 +1,97 @@
+"""The general elementwise kernel on the reference's own pointwise and dtype cases
+(tools/torch_cases/pointwise.py:8-57, dtypes.py:5-12): each case is written once as Kernel IR (what the tracer would
+hand over: Loads, a chain of Assigns through the op table, a Write) and once as the torch expression the reference's
+checker evaluates in float64 on the same seeded inputs. Tolerances are the reference's classes
+(tools/torch_cases/__init__.py:17-21): ROUND 1e-6, TRANS 1e-5, HALF 1e-2.
+"""
+import json
+
+import numpy as np
+import pytest
+
+from emmyptx import ir, run_local
+from emmyptx.kernel import compile_kernel
+
+pytestmark = pytest.mark.gpu
+ROUND, TRANS, HALF = 1e-6, 1e-5, 1e-2
+
+# id -> (inputs, steps, torch expression over float64 tensors named like the inputs, tolerance)
+CASES = {
+    "p_abs": ({"x": "f32"}, [("a", "abs", ["x"])], "torch.abs(x)", ROUND),
+    "p_neg_sub": ({"x": "f32", "y": "f32"}, [("a", "negative", ["x"]), ("b", "subtract", ["a", "y"])], "-x - y", ROUND),
+    "p_div": ({"x": "f32", "y": "f32"}, [("a", "abs", ["y"]), ("b", "add", ["a", 0.5]), ("c", "divide", ["x", "b"])], "x / (y.abs() + 0.5)", ROUND),
+    "p_max_min": ({"x": "f32", "y": "f32"}, [("a", "maximum", ["x", "y"]), ("b", "minimum", ["x", "y"]), ("c", "add", ["a", "b"])],
+                  "torch.maximum(x, y) + torch.minimum(x, y)", ROUND),
+    "p_log": ({"x": "f32"}, [("a", "abs", ["x"]), ("b", "add", ["a", 0.5]), ("c", "log", ["b"])], "torch.log(x.abs() + 0.5)", TRANS),
+    "p_sqrt_rsqrt": ({"x": "f32"}, [("a", "abs", ["x"]), ("b", "sqrt", ["a"]), ("c", "add", ["a", 0.1]), ("d", "rsqrt", ["c"]), ("e", "add", ["b", "d"])],
+                     "torch.sqrt(x.abs()) + torch.rsqrt(x.abs() + 0.1)", TRANS),
+    "p_reciprocal": ({"x": "f32"}, [("a", "abs", ["x"]), ("b", "add", ["a", 0.5]), ("c", "reciprocal", ["b"])], "torch.reciprocal(x.abs() + 0.5)", ROUND),
+    "p_sigmoid": ({"x": "f32"}, [("a", "sigmoid", ["x"])], "torch.sigmoid(x)", TRANS),
+    "p_relu": ({"x": "f32"}, [("a", "relu", ["x"])], "torch.relu(x)", ROUND),
+    "p_gelu_erf": ({"x": "f32"}, [("a", "multiply", ["x", 0.7071067811865476]), ("b", "erf", ["a"]), ("c", "add", ["b", 1.0]),
+                                  ("d", "multiply", ["x", 0.5]), ("e", "multiply", ["d", "c"])], "F.gelu(x)", TRANS),
+    "p_silu": ({"x": "f32"}, [("a", "sigmoid", ["x"]), ("b", "multiply", ["x", "a"])], "F.silu(x)", TRANS),
+    "p_erf": ({"x": "f32"}, [("a", "erf", ["x"])], "torch.erf(x)", TRANS),
+    "p_sin_cos": ({"x": "f32"}, [("a", "multiply", ["x", 3.0]), ("b", "sin", ["a"]), ("c", "cos", ["a"]), ("d", "add", ["b", "c"])],
+                  "torch.sin(x * 3) + torch.cos(x * 3)", TRANS),
+    "p_square_cube": ({"x": "f32"}, [("a", "square", ["x"]), ("b", "multiply", ["a", "x"]), ("c", "add", ["a", "b"])], "x ** 2 + x ** 3", ROUND),
+    "p_pow_frac": ({"x": "f32"}, [("a", "abs", ["x"]), ("b", "add", ["a", 0.1]), ("c", "pow", ["b", 0.7])], "torch.pow(x.abs() + 0.1, 0.7)", TRANS),
+    "p_clamp": ({"x": "f32"}, [("a", "maximum", ["x", -0.5]), ("b", "minimum", ["a", 0.5])], "torch.clamp(x, -0.5, 0.5)", ROUND),
+    "p_where": ({"x": "f32"}, [("m", "greater", ["x", 0.0]), ("a", "multiply", ["x", 0.1]), ("b", "where", ["m", "x", "a"])],
+                "torch.where(x > 0, x, x * 0.1)", ROUND),
+    "p_cmp_to_float": ({"x": "f32", "y": "f32"}, [("m", "greater", ["x", "y"])], "(x > y).double()", ROUND),
+    "p_lerp": ({"x": "f32", "y": "f32"}, [("a", "subtract", ["y", "x"]), ("b", "multiply", ["a", 0.3]), ("c", "add", ["x", "b"])],
+               "torch.lerp(x, y, 0.3)", ROUND),
+    "p_addcmul": ({"x": "f32", "y": "f32", "z": "f32"}, [("a", "multiply", ["y", "z"]), ("b", "multiply", ["a", 0.5]), ("c", "add", ["x", "b"])],
+                  "torch.addcmul(x, y, z, value=0.5)", ROUND),
+    "p_remainder": ({"x": "f32"}, [("a", "multiply", ["x", 5.0]), ("b", "remainder", ["a", 1.5])], "torch.remainder(x * 5, 1.5)", TRANS),
+    "p_floor_divide": ({"x": "f32"}, [("a", "multiply", ["x", 5.0]), ("b", "floor_divide", ["a", 1.5])], "torch.floor_divide(x * 5, 1.5)", ROUND),
+    "d_f16_add": ({"x": "f16", "y": "f16"}, [("a", "add", ["x", "y"])], "x + y", HALF),
+    "d_bf16_add": ({"x": "bf16", "y": "bf16"}, [("a", "add", ["x", "y"])], "x + y", HALF),
+    "d_bf16_gelu": ({"x": "bf16"}, [("a", "multiply", ["x", 0.7071067811865476]), ("b", "erf", ["a"]), ("c", "add", ["b", 1.0]),
+                                    ("d", "multiply", ["x", 0.5]), ("e", "multiply", ["d", "c"])], "F.gelu(x)", HALF),
+    "d_f32_to_f16": ({"x": "f32"}, [("a", "copy", ["x"])], "x", HALF),
+}
+OUT_DTYPE = {"d_f16_add": "f16", "d_bf16_add": "bf16", "d_bf16_gelu": "bf16", "d_f32_to_f16": "f16"}
+
+
+def _expected(expr, arrays):
+    import torch
+    import torch.nn.functional as F
+    scope = {"torch": torch, "F": F, **{k: torch.from_numpy(np.asarray(v, dtype=np.float64)) for k, v in arrays.items()}}
+    return eval(expr, scope).numpy()
+
+
+@pytest.mark.parametrize("case", sorted(CASES))
+@pytest.mark.parametrize("n", [4096, 4099])
+def test_reference_pointwise_cases(case, n, cuda):
+    from oracle import reference
+    inputs, steps, expr, tol = CASES[case]
+    out_dtype = OUT_DTYPE.get(case, "f32")
+    built = ir.elementwise_kernel(n, inputs, steps, out_dtype, name=case)
+    text = compile_kernel(*built)
+    args = [{"name": b, "dtype": dt, "shape": [n], "seed": i} for i, (b, dt) in enumerate(inputs.items())]
+    args.append({"name": "out", "dtype": out_dtype, "shape": [n], "output": True})
+    run_local.init()
+    got = run_local.run_kernel(text, dict(built[2], args=args), {})["out"]
+    # graph input i is default_rng(i).standard_normal rounded to the buffer's dtype (tools/run_local.py:86-87)
+    arrays = {}
+    for i, (b, dt) in enumerate(inputs.items()):
+        host = run_local.to_device(np.random.default_rng(i).standard_normal([n]), dt)
+        arrays[b] = run_local.from_device(host, dt).astype(np.float64)
+    ref = _expected(expr, arrays)
+    res = reference.compare(np.asarray(got, dtype=np.float64), ref, tol, tol)
+    assert res["ok"], (case, res)
+
+
+def test_program_limits_are_compile_errors():
+    from emmyptx.kernel import CompileError
+    steps = [(f"v{i}", "add", ["x" if i == 0 else f"v{i-1}", float(i)]) for i in range(20)]            # 20 distinct constants
+    with pytest.raises(CompileError, match="constants"):
+        compile_kernel(*ir.elementwise_kernel(64, {"x": "f32"}, steps))
+    many = {f"x{i}": "f32" for i in range(5)}
+    with pytest.raises(CompileError, match="input buffers"):
+        compile_kernel(*ir.elementwise_kernel(64, many, [("a", "add", ["x0", "x1"])]))
+    h = json.loads(compile_kernel(*ir.elementwise_kernel(64, {"x": "f32"}, [(f"v{i}", "add", ["x" if i == 0 else f"v{i-1}", 1.0]) for i in range(40)])))
+    assert h["variant"] == "pointwise_program" and len(h["params"]["program"]["steps"]) == 40
+    assert max(s[1] for s in h["params"]["program"]["steps"]) < 16           # slots are recycled
