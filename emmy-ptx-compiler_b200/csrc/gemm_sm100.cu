@@ -52,7 +52,11 @@ constexpr int kMaxDst = 8;
 struct GemmParams {
     int M, N, K;
     int m_blocks, n_blocks;
+    int batch;              // independent products (planes of A and C; B has `batch` planes or one shared plane)
+    int b_shared;           // 1: every product reads plane 0 of B
     int n_dst;              // destinations of every output piece (1 = the local C only)
+    int epilogue;           // EMMYB200_EPI_*
+    const void* bias;       // per-column addend of the output type, or null
     uint32_t* status;
 };
 
@@ -95,7 +99,18 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     }
 }
 
-template <int BN, bool BF16, int EPI, bool B_NK>
+template <bool BF16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+    if constexpr (BF16) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+    else return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+template <bool BF16>
+__device__ __forceinline__ float unpack1(uint16_t h) {
+    if constexpr (BF16) return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&h));
+    else return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+
+template <int BN, bool BF16, bool B_NK>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ OutMaps out, GemmParams p) {
@@ -116,7 +131,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (p.K + kBK - 1) / kBK;
-    const int tiles = p.m_blocks * p.n_blocks;
+    const int plane_tiles = p.m_blocks * p.n_blocks;
+    const int tiles = plane_tiles * p.batch;
     const WaitCtx wctx{abort_flag, p.status};
 
     if (threadIdx.x == 0) {
@@ -143,7 +159,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
                 int mb, nb;
-                tile_coords(t, p.m_blocks, p.n_blocks, mb, nb);
+                const int plane = t / plane_tiles;
+                tile_coords(t - plane * plane_tiles, p.m_blocks, p.n_blocks, mb, nb);
+                const int b_plane = p.b_shared ? 0 : plane;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
@@ -151,13 +169,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t a_dst = smem_base + s * S::kStageBytes;
                     const uint32_t b_dst = a_dst + S::kABytes;
                     ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
-                    ptx::tma_load_2d(a_dst, &map_a, full_bar(s), kb * kBK, mb * kBM);
+                    ptx::tma_load_3d(a_dst, &map_a, full_bar(s), kb * kBK, mb * kBM, plane);
                     if constexpr (B_NK) {
-                        ptx::tma_load_2d(b_dst, &map_b, full_bar(s), kb * kBK, nb * BN);
+                        ptx::tma_load_3d(b_dst, &map_b, full_bar(s), kb * kBK, nb * BN, b_plane);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BN / 64; ++j)
-                            ptx::tma_load_2d(b_dst + j * (kBK * 128), &map_b, full_bar(s), nb * BN + j * 64, kb * kBK);
+                            ptx::tma_load_3d(b_dst + j * (kBK * 128), &map_b, full_bar(s), nb * BN + j * 64, kb * kBK, b_plane);
                     }
                 }
             }
@@ -204,7 +222,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++acc_it) {
             int mb, nb;
-            tile_coords(t, p.m_blocks, p.n_blocks, mb, nb);
+            const int plane = t / plane_tiles;
+            tile_coords(t - plane * plane_tiles, p.m_blocks, p.n_blocks, mb, nb);
             const int as = acc_it & 1;
             const uint32_t aph = (acc_it >> 1) & 1;
             // One thread waits; the outcome reaches the four warps through shared memory, so they all
@@ -231,9 +250,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int q = 0; q < 4; ++q) {
                         float v[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float f = __uint_as_float(r[8 * q + j]);
-                            v[j] = (EPI == EMMYB200_EPI_GELU_TANH) ? gelu_tanh_fast(f) : f;
+                        for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * q + j]);
+                        if (p.bias != nullptr) {                // eight columns' worth, the same for every row
+                            const int col = nb * BN + c + 32 * h + 8 * q;
+                            if (col + 8 <= p.N) {
+                                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col));
+                                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float2 b2 = unpack2<BF16>(w[j]);
+                                    v[2 * j] += b2.x;
+                                    v[2 * j + 1] += b2.y;
+                                }
+                            } else {
+                                for (int j = 0; j < 8 && col + j < p.N; ++j) v[j] += unpack1<BF16>(reinterpret_cast<const uint16_t*>(p.bias)[col + j]);
+                            }
+                        }
+                        if (p.epilogue == EMMYB200_EPI_GELU_TANH) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) v[j] = gelu_tanh_fast(v[j]);
+                        } else if (p.epilogue == EMMYB200_EPI_RELU) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.0f);
                         }
                         // 16-byte slot (4h + q) of the row, at its 128-byte-swizzle position
                         const uint32_t slot = (uint32_t)(4 * h + q) ^ (uint32_t)(row_in_tile & 7);
@@ -251,7 +289,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 ptx::fence_proxy_async_smem();
                 ptx::named_barrier(1, 128);
                 if (issuer && nb * BN + c < p.N) {
-                    for (int d = 0; d < p.n_dst; ++d) ptx::tma_store_2d(&out.m[d], stage, nb * BN + c, mb * kBM);
+                    for (int d = 0; d < p.n_dst; ++d) ptx::tma_store_3d(&out.m[d], stage, nb * BN + c, mb * kBM, plane);
                 }
                 if (issuer) ptx::tma_store_commit();
             }
@@ -306,10 +344,16 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64
 
 int make_tensor_map_3d(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
                        uint32_t box_rows, uint32_t box_cols) {
+    return make_tensor_map_3d_strided(out, base, planes, rows, cols, cols, rows * cols, box_rows, box_cols);
+}
+
+int make_tensor_map_3d_strided(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols, uint64_t ld,
+                               uint64_t plane_stride, uint32_t box_rows, uint32_t box_cols) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return fail(EMMYB200_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[3] = {cols, rows, planes};
-    cuuint64_t strides[2] = {cols * 2, rows * cols * 2};
+    if (planes == 1) plane_stride = rows * ld;                  // unused, but must be a valid stride
+    cuuint64_t strides[2] = {ld * 2, plane_stride * 2};
     cuuint32_t box[3] = {box_cols, box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box, estr,
@@ -335,81 +379,90 @@ int gemm_read_status(uint32_t* out) {
     return EMMYB200_OK;
 }
 
-template <int BN, bool BF16, int EPI, bool B_NK>
-static int launch_gemm(const void* A, const void* B, void* const* C, int n_dst, int64_t M, int64_t N, int64_t K, int64_t lda,
-                       int64_t ldb, int64_t ldc, cudaStream_t stream) {
+struct GemmCall {
+    int dtype, epilogue, flags;
+    const void* A; const void* B; const void* bias;
+    void* const* C; int n_dst;
+    int64_t batch, M, N, K, lda, ldb, ldc, stride_a, stride_b, stride_c;
+};
+
+template <int BN, bool BF16, bool B_NK>
+static int launch_gemm(const GemmCall& g, cudaStream_t stream) {
     using S = GemmSmem<BN>;
     CUtensorMap map_a, map_b;
     OutMaps out;
-    int rc = make_tensor_map_2d(&map_a, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBM, kBK);
+    const bool b_shared = g.stride_b == 0;
+    int rc = make_tensor_map_3d_strided(&map_a, g.A, (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda,
+                                        (uint64_t)g.stride_a, kBM, kBK);
     if (rc != EMMYB200_OK) return rc;
-    rc = B_NK ? make_tensor_map_2d(&map_b, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, kBK)
-              : make_tensor_map_2d(&map_b, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, kBK, 64);
+    const uint64_t b_planes = b_shared ? 1 : (uint64_t)g.batch;
+    rc = B_NK ? make_tensor_map_3d_strided(&map_b, g.B, b_planes, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, (uint64_t)g.stride_b, BN, kBK)
+              : make_tensor_map_3d_strided(&map_b, g.B, b_planes, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, (uint64_t)g.stride_b, kBK, 64);
     if (rc != EMMYB200_OK) return rc;
     for (int d = 0; d < kMaxDst; ++d) {
-        rc = make_tensor_map_2d(&out.m[d], C[d < n_dst ? d : 0], (uint64_t)M, (uint64_t)N, (uint64_t)ldc, kBM, 64);
+        rc = make_tensor_map_3d_strided(&out.m[d], g.C[d < g.n_dst ? d : 0], (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.N,
+                                        (uint64_t)g.ldc, (uint64_t)g.stride_c, kBM, 64);
         if (rc != EMMYB200_OK) return rc;
     }
-    auto kernel = gemm_tcgen05_kernel<BN, BF16, EPI, B_NK>;
+    auto kernel = gemm_tcgen05_kernel<BN, BF16, B_NK>;
     EMMY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
     GemmParams p;
-    p.M = (int)M; p.N = (int)N; p.K = (int)K;
-    p.m_blocks = (int)((M + kBM - 1) / kBM);
-    p.n_blocks = (int)((N + BN - 1) / BN);
-    p.n_dst = n_dst;
+    p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
+    p.m_blocks = (int)((g.M + kBM - 1) / kBM);
+    p.n_blocks = (int)((g.N + BN - 1) / BN);
+    p.batch = (int)g.batch;
+    p.b_shared = b_shared ? 1 : 0;
+    p.n_dst = g.n_dst;
+    p.epilogue = g.epilogue;
+    p.bias = g.bias;
     EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
-    const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks;
+    const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks * g.batch;
+    if (tiles >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "gemm: %lld output tiles exceed the scheduler's range", (long long)tiles);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     kernel<<<grid, kGemmThreads, S::kTotal, stream>>>(map_a, map_b, out, p);
     return launch_status("gemm_tcgen05_kernel");
 }
 
-template <bool BF16, int EPI, bool B_NK>
-static int pick_tile(const void* A, const void* B, void* const* C, int n_dst, int64_t M, int64_t N, int64_t K, int64_t lda,
-                     int64_t ldb, int64_t ldc, cudaStream_t stream) {
+template <bool BF16, bool B_NK>
+static int pick_tile(const GemmCall& g, cudaStream_t stream) {
     // 128 x 256 tiles: with both operands read from shared memory by one CTA, the 128 x 128 shape is bound by
     // shared-memory bandwidth (measured 0.6-0.7x the throughput at every size from 2048^3 to 16384^3), which
     // costs more than the emptier last wave of the wide tile. Narrow outputs keep the narrow tile.
-    if (N > 128) return launch_gemm<256, BF16, EPI, B_NK>(A, B, C, n_dst, M, N, K, lda, ldb, ldc, stream);
-    return launch_gemm<128, BF16, EPI, B_NK>(A, B, C, n_dst, M, N, K, lda, ldb, ldc, stream);
+    if (g.N > 128) return launch_gemm<256, BF16, B_NK>(g, stream);
+    return launch_gemm<128, BF16, B_NK>(g, stream);
 }
 
-static int gemm_entry(int dtype, int epilogue, int flags, const void* A, const void* B, void* const* C, int n_dst, int64_t M,
-                      int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* cuda_stream) {
-    if (dtype != EMMYB200_F16 && dtype != EMMYB200_BF16) return fail(EMMYB200_ERR_UNSUPPORTED, "gemm: dtype %d (f16 and bf16 only)", dtype);
-    if (epilogue != EMMYB200_EPI_NONE && epilogue != EMMYB200_EPI_GELU_TANH) return fail(EMMYB200_ERR_ARG, "gemm: unknown epilogue %d", epilogue);
-    if (flags & ~EMMYB200_GEMM_B_NK) return fail(EMMYB200_ERR_ARG, "gemm: unknown flags 0x%x", flags);
-    if (n_dst < 1 || n_dst > kMaxDst) return fail(EMMYB200_ERR_ARG, "gemm: %d destinations (1 to %d)", n_dst, kMaxDst);
-    if (M < 0 || N < 0 || K < 0) return fail(EMMYB200_ERR_SHAPE, "gemm: negative extent");
-    if (M == 0 || N == 0) return EMMYB200_OK;
-    if (K == 0) return fail(EMMYB200_ERR_SHAPE, "gemm: K = 0 (the caller zeroes C, emmyptx/mma.py:77-79 starts accumulators at 0)");
-    if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "gemm: extents must be below 2^31");
-    if (A == nullptr || B == nullptr || C == nullptr) return fail(EMMYB200_ERR_ARG, "gemm: null buffer");
-    for (int d = 0; d < n_dst; ++d) {
-        if (C[d] == nullptr) return fail(EMMYB200_ERR_ARG, "gemm: null output buffer");
-        if (!aligned(C[d], 16)) return fail(EMMYB200_ERR_ALIGN, "gemm: buffers must be 16-byte aligned");
+static int gemm_entry(const GemmCall& g, void* cuda_stream) {
+    if (g.dtype != EMMYB200_F16 && g.dtype != EMMYB200_BF16) return fail(EMMYB200_ERR_UNSUPPORTED, "gemm: dtype %d (f16 and bf16 only)", g.dtype);
+    if (g.epilogue != EMMYB200_EPI_NONE && g.epilogue != EMMYB200_EPI_GELU_TANH && g.epilogue != EMMYB200_EPI_RELU)
+        return fail(EMMYB200_ERR_ARG, "gemm: unknown epilogue %d", g.epilogue);
+    if (g.flags & ~EMMYB200_GEMM_B_NK) return fail(EMMYB200_ERR_ARG, "gemm: unknown flags 0x%x", g.flags);
+    if (g.n_dst < 1 || g.n_dst > kMaxDst) return fail(EMMYB200_ERR_ARG, "gemm: %d destinations (1 to %d)", g.n_dst, kMaxDst);
+    if (g.M < 0 || g.N < 0 || g.K < 0 || g.batch < 0) return fail(EMMYB200_ERR_SHAPE, "gemm: negative extent");
+    if (g.M == 0 || g.N == 0 || g.batch == 0) return EMMYB200_OK;
+    if (g.K == 0) return fail(EMMYB200_ERR_SHAPE, "gemm: K = 0 (the caller zeroes C, emmyptx/mma.py:77-79 starts accumulators at 0)");
+    if (g.M >= (1ll << 31) || g.N >= (1ll << 31) || g.K >= (1ll << 31) || g.batch >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "gemm: extents must be below 2^31");
+    if (g.A == nullptr || g.B == nullptr || g.C == nullptr) return fail(EMMYB200_ERR_ARG, "gemm: null buffer");
+    for (int d = 0; d < g.n_dst; ++d) {
+        if (g.C[d] == nullptr) return fail(EMMYB200_ERR_ARG, "gemm: null output buffer");
+        if (!aligned(g.C[d], 16)) return fail(EMMYB200_ERR_ALIGN, "gemm: buffers must be 16-byte aligned");
     }
-    const bool b_nk = flags & EMMYB200_GEMM_B_NK;
-    if (lda < K || ldc < N || ldb < (b_nk ? K : N)) return fail(EMMYB200_ERR_SHAPE, "gemm: leading dimension smaller than the row");
-    if ((lda | ldb | ldc) & 7) return fail(EMMYB200_ERR_ALIGN, "gemm: leading dimensions must be multiples of 8 elements (16 bytes)");
-    if (!aligned(A, 16) || !aligned(B, 16)) return fail(EMMYB200_ERR_ALIGN, "gemm: buffers must be 16-byte aligned");
+    const bool b_nk = g.flags & EMMYB200_GEMM_B_NK;
+    if (g.lda < g.K || g.ldc < g.N || g.ldb < (b_nk ? g.K : g.N)) return fail(EMMYB200_ERR_SHAPE, "gemm: leading dimension smaller than the row");
+    if ((g.lda | g.ldb | g.ldc) & 7) return fail(EMMYB200_ERR_ALIGN, "gemm: leading dimensions must be multiples of 8 elements (16 bytes)");
+    if (g.batch > 1) {
+        if ((g.stride_a | g.stride_b | g.stride_c) & 7) return fail(EMMYB200_ERR_ALIGN, "gemm: plane strides must be multiples of 8 elements (16 bytes)");
+        if (g.stride_a < g.M * g.lda || g.stride_c < g.M * g.ldc || (g.stride_b != 0 && g.stride_b < (b_nk ? g.N : g.K) * g.ldb))
+            return fail(EMMYB200_ERR_SHAPE, "gemm: plane stride smaller than a plane");
+    }
+    if (!aligned(g.A, 16) || !aligned(g.B, 16)) return fail(EMMYB200_ERR_ALIGN, "gemm: buffers must be 16-byte aligned");
+    if (g.bias != nullptr && !aligned(g.bias, 16)) return fail(EMMYB200_ERR_ALIGN, "gemm: bias must be 16-byte aligned");
     int rc = check_sm100();
     if (rc != EMMYB200_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
-    const bool bf16 = dtype == EMMYB200_BF16;
-    const bool gelu = epilogue == EMMYB200_EPI_GELU_TANH;
-#define EMMY_GEMM_CASE(BF, EP, NK) \
-    if (bf16 == BF && gelu == (EP == EMMYB200_EPI_GELU_TANH) && b_nk == NK) return pick_tile<BF, EP, NK>(A, B, C, n_dst, M, N, K, lda, ldb, ldc, s);
-    EMMY_GEMM_CASE(false, EMMYB200_EPI_NONE, false)
-    EMMY_GEMM_CASE(false, EMMYB200_EPI_NONE, true)
-    EMMY_GEMM_CASE(false, EMMYB200_EPI_GELU_TANH, false)
-    EMMY_GEMM_CASE(false, EMMYB200_EPI_GELU_TANH, true)
-    EMMY_GEMM_CASE(true, EMMYB200_EPI_NONE, false)
-    EMMY_GEMM_CASE(true, EMMYB200_EPI_NONE, true)
-    EMMY_GEMM_CASE(true, EMMYB200_EPI_GELU_TANH, false)
-    EMMY_GEMM_CASE(true, EMMYB200_EPI_GELU_TANH, true)
-#undef EMMY_GEMM_CASE
-    return fail(EMMYB200_ERR_UNSUPPORTED, "gemm: no kernel variant");
+    const bool bf16 = g.dtype == EMMYB200_BF16;
+    if (bf16) return b_nk ? pick_tile<true, true>(g, s) : pick_tile<true, false>(g, s);
+    return b_nk ? pick_tile<false, true>(g, s) : pick_tile<false, false>(g, s);
 }
 
 }  // namespace emmy
@@ -417,12 +470,22 @@ static int gemm_entry(int dtype, int epilogue, int flags, const void* A, const v
 extern "C" int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, const void* B, void* C, int64_t M,
                              int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* cuda_stream) {
     void* dst[1] = {C};
-    return emmy::gemm_entry(dtype, epilogue, flags, A, B, dst, 1, M, N, K, lda, ldb, ldc, cuda_stream);
+    const emmy::GemmCall g{dtype, epilogue, flags, A, B, nullptr, dst, 1, 1, M, N, K, lda, ldb, ldc, 0, 0, 0};
+    return emmy::gemm_entry(g, cuda_stream);
 }
 
 extern "C" int emmyb200_gemm_allgather(int dtype, int epilogue, int flags, const void* A, const void* B, void* const* C_dst,
                                        int n_dst, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                                        void* cuda_stream) {
     if (C_dst == nullptr) return emmy::fail(EMMYB200_ERR_ARG, "gemm_allgather: null destination list");
-    return emmy::gemm_entry(dtype, epilogue, flags, A, B, C_dst, n_dst, M, N, K, lda, ldb, ldc, cuda_stream);
+    const emmy::GemmCall g{dtype, epilogue, flags, A, B, nullptr, C_dst, n_dst, 1, M, N, K, lda, ldb, ldc, 0, 0, 0};
+    return emmy::gemm_entry(g, cuda_stream);
+}
+
+extern "C" int emmyb200_gemm_batched(int dtype, int epilogue, int flags, const void* A, const void* B, const void* bias, void* C,
+                                     int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                                     int64_t stride_a, int64_t stride_b, int64_t stride_c, void* cuda_stream) {
+    void* dst[1] = {C};
+    const emmy::GemmCall g{dtype, epilogue, flags, A, B, bias, dst, 1, batch, M, N, K, lda, ldb, ldc, stride_a, stride_b, stride_c};
+    return emmy::gemm_entry(g, cuda_stream);
 }

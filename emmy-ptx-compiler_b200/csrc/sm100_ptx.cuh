@@ -237,5 +237,8 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64
 // 3-D [planes, rows, cols], contiguous, boxes of 1 x box_rows x box_cols.
 int make_tensor_map_3d(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
                        uint32_t box_rows, uint32_t box_cols);
+// The same with a row pitch `ld` and a plane pitch `plane_stride` (both in elements).
+int make_tensor_map_3d_strided(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols, uint64_t ld,
+                               uint64_t plane_stride, uint32_t box_rows, uint32_t box_cols);
 
 }  // namespace emmy

@@ -10,6 +10,7 @@ same, because the matcher here is duck-typed in the same way.
 from __future__ import annotations
 
 import dataclasses
+import math
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -260,6 +261,7 @@ class RegStore:
     n_guard: Any = None
     atomic: bool = False
     epilogue: Any = None
+    bias: Any = None
     extra_frags: Any = None
     swizzle: str = "NONE"
     fragment_layout: str = "m16n8k16"
@@ -365,7 +367,7 @@ def index_gather_kernel(n: int, mul: int = 7919, add: int = 13, div: int = 3, sh
 
 
 def gemm_kernel(m: int, n: int, k: int, dtype: str = "f16", epilogue: str | None = None, b_trans: bool = False,
-                name: str = "k_gemm"):
+                name: str = "k_gemm", batch: tuple = (), b_batched: bool = True, bias: bool = False):
     """C = A B on mma.sync cells, as the tracer schedules a 16-bit matmul: accumulator / operand fragments, a K
     loop of fragment loads and MMAs, a fragment store (optionally with a fused epilogue, which the reference
     rejects). One warp per 16x8 cell here; the tile sizes of the real schedule do not matter to the matcher."""
@@ -378,10 +380,17 @@ def gemm_kernel(m: int, n: int, k: int, dtype: str = "f16", epilogue: str | None
             Loop(kk, [LdmatrixLoad("_a", "a", "A", [row, kof]),
                       LdmatrixLoad("_b", "b", "B", b_index, b_trans=b_trans),
                       MmaSyncPtx("_c", "_a", "_b", ab_dtype=dtype)]),
-            RegStore("_c", "C", [row, col], epilogue=epilogue)]
-    kern = KernelOp(name, [Tile([am, an], body)])
-    g = _graph(kern, [tensor("A", [m, k], dtype), tensor("B", [n, k] if b_trans else [k, n], dtype)], [tensor("C", [m, n], dtype)])
-    return g, kern, _launch(kern, ["A", "B", "C"], am.extent.value * an.extent.value * 32, block=128)
+            RegStore("_c", "C", [row, col], epilogue=epilogue, bias="bias" if bias else None)]
+    lead = list(batch)
+    axes = ([Axis("b0", Dim(math.prod(lead)))] if lead else []) + [am, an]
+    kern = KernelOp(name, [Tile(axes, body)])
+    bshape = [n, k] if b_trans else [k, n]
+    ins = [tensor("A", lead + [m, k], dtype), tensor("B", (lead if b_batched else []) + bshape, dtype)]
+    if bias:
+        ins.append(tensor("bias", [n], dtype))
+    g = _graph(kern, ins, [tensor("C", lead + [m, n], dtype)])
+    cells = math.prod(lead or [1]) * am.extent.value * an.extent.value * 32
+    return g, kern, _launch(kern, [t.name for t in ins] + ["C"], cells, block=128)
 
 
 def attention_kernel(units_shape: list[int], seq_q: int, seq_k: int, d: int, dtype: str = "bf16", scale: float | None = None,

@@ -388,7 +388,9 @@ def _epilogue_name(ep):
         return None
     if name in ("gelu_tanh", "gelu"):
         return "gelu_tanh"
-    raise Unmatched(f"store epilogue {name!r} has no fused variant (have: gelu_tanh)")
+    if name == "relu":
+        return "relu"
+    raise Unmatched(f"store epilogue {name!r} has no fused variant (have: gelu_tanh, relu)")
 
 
 def match_contraction(graph, kernel, launch: dict) -> dict:
@@ -437,16 +439,29 @@ def match_contraction(graph, kernel, launch: dict) -> dict:
     a_name, b_name = a_loads[0].src_buffer, b_loads[0].src_buffer
     b_trans = bool(b_loads[0].b_trans)
     (a_shape, _), (b_shape, _), (c_shape, _) = tensors[a_name], tensors[b_name], tensors[out]
-    if not (len(a_shape) == len(b_shape) == len(c_shape) == 2):
-        raise Unmatched("batched and broadcast matmuls have no variant yet")
-    m, k = a_shape
-    n = b_shape[0] if b_trans else b_shape[1]
-    if (b_shape[1] if b_trans else b_shape[0]) != k or c_shape != (m, n):
+    # leading axes of A are independent products (bmm); B carries the same leading axes or none (broadcast)
+    if len(a_shape) < 2 or len(b_shape) < 2 or len(c_shape) != len(a_shape):
+        raise Unmatched(f"GEMM shapes do not agree: {a_shape} x {b_shape} -> {c_shape}")
+    lead = a_shape[:-2]
+    if b_shape[:-2] not in ((), lead) or c_shape[:-2] != lead:
+        raise Unmatched(f"batched GEMM: leading axes {lead} / {b_shape[:-2]} / {c_shape[:-2]} do not line up")
+    m, k = a_shape[-2:]
+    n = b_shape[-2] if b_trans else b_shape[-1]
+    if (b_shape[-1] if b_trans else b_shape[-2]) != k or c_shape[-2:] != (m, n):
         raise Unmatched(f"GEMM shapes do not agree: {a_shape} x {b_shape} -> {c_shape}")
     if k % 8 or n % 8:
         raise Unmatched("row pitches must be multiples of 8 elements (16-byte TMA strides)")
-    return {"variant": "gemm", "inputs": [a_name, b_name], "outputs": [out],
-            "params": {"dtype": dtype, "m": m, "n": n, "k": k, "b_trans": b_trans, "epilogue": _epilogue_name(stores[0].epilogue)}}
+    bias = getattr(stores[0], "bias", None)
+    inputs = [a_name, b_name]
+    if bias is not None:
+        if bias not in tensors or math.prod(tensors[bias][0]) != n or tensors[bias][1] != dtype:
+            raise Unmatched(f"bias {bias!r} must hold N = {n} values of dtype {dtype}")
+        inputs.append(bias)
+    params = {"dtype": dtype, "m": m, "n": n, "k": k, "b_trans": b_trans, "epilogue": _epilogue_name(stores[0].epilogue)}
+    if lead or bias is not None:
+        params.update(batch=math.prod(lead), b_shared=len(b_shape) == 2, bias=bias is not None)
+        return {"variant": "gemm_batched", "inputs": inputs, "outputs": [out], "params": params}
+    return {"variant": "gemm", "inputs": inputs, "outputs": [out], "params": params}
 
 
 def match_kernel(graph, kernel, launch: dict, int_div: str = "floor") -> dict:

@@ -111,6 +111,12 @@ def launch(handle: dict, bufs: dict, stream=None) -> None:
                              stream=stream)
     elif v == "gemm":
         runtime.gemm(ins[0], ins[1], epilogue=p["epilogue"], b_is_nk=p["b_trans"], out=out, stream=stream)
+    elif v == "gemm_batched":
+        a = ins[0].reshape(p["batch"], p["m"], p["k"])
+        bshape = (p["n"], p["k"]) if p["b_trans"] else (p["k"], p["n"])
+        b = ins[1].reshape(bshape if p["b_shared"] else (p["batch"], *bshape))
+        runtime.gemm_batched(a, b, bias=ins[2].reshape(-1) if p["bias"] else None, epilogue=p["epilogue"], b_is_nk=p["b_trans"],
+                             out=out.reshape(p["batch"], p["m"], p["n"]), stream=stream)
     elif v == "attention_fwd":
         shp = (p["units"], -1, p["d"])
         runtime.attention(ins[0].reshape(shp), ins[1].reshape(shp), ins[2].reshape(shp), scale=p["scale"],

@@ -36,8 +36,8 @@ class PwProgram(ctypes.Structure):
                 ("consts", ctypes.c_float * PW_MAX_CONSTS), ("steps", PwStep * PW_MAX_STEPS)]
 
 
-EPI_NONE, EPI_GELU_TANH = 0, 1
-EPILOGUES = {None: EPI_NONE, "none": EPI_NONE, "gelu_tanh": EPI_GELU_TANH}
+EPI_NONE, EPI_GELU_TANH, EPI_RELU = 0, 1, 2
+EPILOGUES = {None: EPI_NONE, "none": EPI_NONE, "gelu_tanh": EPI_GELU_TANH, "relu": EPI_RELU}
 GEMM_B_NK = 1
 GATHER_TRUNC = 1
 
@@ -54,6 +54,8 @@ _SIGNATURES = {
     "emmyb200_gemm": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
                                      ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                      ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),
+    "emmyb200_gemm_batched": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                             ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int64] * 10 + [ctypes.c_void_p]),
     "emmyb200_gemm_allgather": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
                                                ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),
@@ -182,6 +184,29 @@ def gemm(a, b, epilogue: str | None = None, b_is_nk: bool = False, out=None, str
     check(library().emmyb200_gemm(dtype_code(a), EPILOGUES[epilogue], GEMM_B_NK if b_is_nk else 0, a.data_ptr(),
                                   b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),
                                   _stream(stream)))
+    return out
+
+
+def gemm_batched(a, b, bias=None, epilogue: str | None = None, b_is_nk: bool = False, out=None, stream=None):
+    """out[i] = epilogue(a[i] @ b[i] + bias) for 3-D a; b is 3-D (one plane per product) or 2-D (shared by all)."""
+    import torch
+    _need_cuda(a, b)
+    if a.dim() != 3 or b.dim() not in (2, 3) or a.dtype != b.dtype:
+        raise TypeError("gemm_batched: a is 3-D, b 2-D or 3-D, one 16-bit dtype")
+    batch, m, k = a.shape
+    n = b.shape[-2] if b_is_nk else b.shape[-1]
+    if (b.shape[-1] if b_is_nk else b.shape[-2]) != k or (b.dim() == 3 and b.shape[0] != batch):
+        raise ValueError(f"gemm_batched: shapes do not agree: {tuple(a.shape)} x {tuple(b.shape)}")
+    out = torch.empty((batch, m, n), dtype=a.dtype, device=a.device) if out is None else out
+    _need_cuda(out)
+    if bias is not None:
+        _need_cuda(bias)
+        if bias.dtype != a.dtype or bias.numel() != n:
+            raise ValueError("gemm_batched: bias holds N values of the operands' dtype")
+    check(library().emmyb200_gemm_batched(dtype_code(a), EPILOGUES[epilogue], GEMM_B_NK if b_is_nk else 0, a.data_ptr(),
+                                          b.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), batch, m, n, k,
+                                          a.stride(1), b.stride(-2), out.stride(1), a.stride(0), b.stride(0) if b.dim() == 3 else 0,
+                                          out.stride(0), _stream(stream)))
     return out
 
 

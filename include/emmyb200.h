@@ -109,10 +109,21 @@ int emmyb200_index_gather_i32(const int32_t* x, int32_t* y, int64_t n, int64_t m
  * leading dimensions multiples of 8 elements. */
 #define EMMYB200_EPI_NONE 0
 #define EMMYB200_EPI_GELU_TANH 1
+#define EMMYB200_EPI_RELU 2
 #define EMMYB200_GEMM_B_NK 1
 int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, const void* B, void* C,
                   int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                   void* cuda_stream);
+
+/* `batch` independent products with one launch (the reference's batched and broadcast matmul cases,
+ * tools/torch_cases/matmul.py:11-12, :31): plane b of A (stride_a elements apart) times plane b of B
+ * (stride_b apart; stride_b = 0 shares one B) into plane b of C (stride_c apart). `bias`, if not NULL, holds N
+ * values of the output type added to every row of the fp32 accumulator before the epilogue function
+ * (F.linear's bias, matmul.py:13-14); epilogues NONE, GELU_TANH, RELU. Other rules as emmyb200_gemm. */
+int emmyb200_gemm_batched(int dtype, int epilogue, int flags, const void* A, const void* B, const void* bias,
+                          void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda,
+                          int64_t ldb, int64_t ldc, int64_t stride_a, int64_t stride_b, int64_t stride_c,
+                          void* cuda_stream);
 
 /* The same GEMM on one GPU's row shard of A, with every output piece stored to n_dst destination buffers
  * (1..8): C_dst[0] is this GPU's own C shard, the others are the addresses, valid on this GPU, of where the

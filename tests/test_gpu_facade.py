@@ -107,3 +107,22 @@ def test_handle_for_another_entry_is_refused(cuda):
         run_local.load(text, "some_other_entry")
     with pytest.raises(RuntimeError, match="not a kernel handle"):
         run_local.load(".version 8.0", "k_pointwise")
+
+
+def test_batched_matmul_and_linear_bias_through_the_facade(tmp_path, cuda):
+    """m_f16_bmm (tools/torch_cases/matmul.py:31) and a 16-bit F.linear with bias and ReLU: randn operands, the
+    reference's tensor-core tolerance (rtol 2e-2, atol 1e-1) against float64."""
+    import torch
+    out = compile_and_run(tmp_path, ir.gemm_kernel(128, 96, 64, "f16", batch=(4,)), [
+        {"name": "A", "dtype": "f16", "shape": [4, 128, 64], "seed": 0}, {"name": "B", "dtype": "f16", "shape": [4, 64, 96], "seed": 1},
+        {"name": "C", "dtype": "f16", "shape": [4, 128, 96], "output": True}])
+    a = torch.from_numpy(seeded(0, [4, 128, 64], "f16")).double()
+    b = torch.from_numpy(seeded(1, [4, 64, 96], "f16")).double()
+    assert reference.compare(np.asarray(out["C"], np.float64).reshape(4, 128, 96), torch.bmm(a, b).numpy(), 2e-2, 1e-1)["ok"]
+
+    out = compile_and_run(tmp_path, ir.gemm_kernel(64, 512, 256, "f16", "relu", True, bias=True, name="k_linear"), [
+        {"name": "A", "dtype": "f16", "shape": [64, 256], "seed": 0}, {"name": "B", "dtype": "f16", "shape": [512, 256], "seed": 1},
+        {"name": "bias", "dtype": "f16", "shape": [512], "seed": 2}, {"name": "C", "dtype": "f16", "shape": [64, 512], "output": True}])
+    x, w, bias = (torch.from_numpy(seeded(i, shp, "f16")).double() for i, shp in enumerate(([64, 256], [512, 256], [512])))
+    ref = torch.relu(torch.nn.functional.linear(x, w, bias)).numpy()
+    assert reference.compare(np.asarray(out["C"], np.float64).reshape(64, 512), ref, 2e-2, 1e-1)["ok"]

@@ -120,3 +120,45 @@ def test_rejects_bad_arguments(cuda, lib):
     assert g(1, 0, 0, p + 2, p, p, 64, 64, 64, 64, 64, 64, None) == -3      # misaligned pointer
     assert g(1, 0, 0, p, p, p, 0, 64, 64, 64, 64, 64, None) == 0            # empty
     assert g(1, 0, 0, p, p, p, 64, 64, 0, 64, 64, 64, None) == -2           # K = 0
+
+
+@pytest.mark.parametrize("batch,m,n,k,shared", [(4, 128, 96, 64, False),      # m_f16_bmm (matmul.py:31)
+                                                 (4, 64, 48, 32, True),        # m_bcast_matmul's shape, 16-bit
+                                                 (3, 100, 72, 200, False), (5, 300, 264, 136, True)])
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_batched_and_broadcast(batch, m, n, k, shared, dtype, cuda):
+    import torch
+    from emmyptx import runtime
+    td = torch.float16 if dtype == "f16" else torch.bfloat16
+    a = torch.from_numpy(np.random.default_rng(0).standard_normal((batch, m, k)).astype(np.float32) / k**0.5).to(td)
+    b = torch.from_numpy(np.random.default_rng(1).standard_normal((k, n) if shared else (batch, k, n)).astype(np.float32) / k**0.5).to(td)
+    got = runtime.gemm_batched(a.to(cuda), b.to(cuda)).cpu()
+    torch.cuda.synchronize()
+    assert runtime.device_status() == 0
+    ref = torch.matmul(a.float(), b.float())
+    ok, ratio = reference.gemm_tolerance_ok(got, ref)
+    assert ok, f"worst error {ratio:.2f}x the bound"
+
+
+@pytest.mark.parametrize("epilogue", [None, "relu", "gelu_tanh"])
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_bias_and_relu_epilogue(epilogue, dtype, cuda):
+    """F.linear(x, w, b) with the weight stored N x K (m_linear_bias / m_f16_linear shapes), bias added to the fp32
+    accumulator, then the activation, one rounding."""
+    import torch
+    from emmyptx import runtime
+    td = torch.float16 if dtype == "f16" else torch.bfloat16
+    m, n, k = 64, 520, 256
+    x = torch.from_numpy(np.random.default_rng(0).standard_normal((1, m, k)).astype(np.float32)).to(td)
+    w = torch.from_numpy(np.random.default_rng(1).standard_normal((n, k)).astype(np.float32) / k**0.5).to(td)
+    bias = torch.from_numpy(np.random.default_rng(2).standard_normal(n).astype(np.float32)).to(td)
+    got = runtime.gemm_batched(x.to(cuda), w.to(cuda), bias=bias.to(cuda), epilogue=epilogue, b_is_nk=True).cpu()[0]
+    ref = x[0].float() @ w.float().t() + bias.float()
+    if epilogue == "relu":
+        ref = torch.relu(ref)
+    elif epilogue == "gelu_tanh":
+        ref = torch.nn.functional.gelu(ref, approximate="tanh")
+    ok, ratio = reference.gemm_tolerance_ok(got, ref)
+    assert ok, f"worst error {ratio:.2f}x the bound"
+    if epilogue == "relu":
+        assert (got >= 0).all()
