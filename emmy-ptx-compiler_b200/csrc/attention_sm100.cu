@@ -18,7 +18,8 @@
 //     more than 8 (in log2 units), so the O accumulator is rescaled in tensor memory rarely; the final
 //     1/rowsum is applied on the way out.
 //
-// All waits are bounded; keys beyond seq_k are masked to -inf, rows beyond seq_q are not stored.
+// All waits are bounded; keys beyond seq_k (and, with the causal flag, keys after the query) are masked to -inf,
+// rows beyond seq_q are not stored.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math_constants.h>
@@ -51,6 +52,7 @@ struct AttOutMaps {
 
 struct AttParams {
     int n_dst;              // destinations of every output tile (1 = the local O only)
+    int causal;             // 1: query i sees keys 0 .. i only
     int seq_q, seq_k;
     int q_tiles;
     float scale_log2;       // scale * log2(e)
@@ -137,8 +139,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     float* xchg = reinterpret_cast<float*>(smem_gen + S::kBarOffset + 256);        // [2][2][128] row maxima / sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int unit = blockIdx.x / p.q_tiles, qt = blockIdx.x % p.q_tiles;
-    const int kv_tiles = (p.seq_k + kTileK - 1) / kTileK;
+    // Causal tiles differ in length (tile qt runs qt + 1 key tiles): the longest of each unit are launched first.
+    const int unit = blockIdx.x / p.q_tiles;
+    const int qt = p.causal ? p.q_tiles - 1 - (int)(blockIdx.x % p.q_tiles) : (int)(blockIdx.x % p.q_tiles);
+    // Causal: keys beyond the tile's last query are never seen, so the tiles past the diagonal are skipped.
+    const int kv_all = (p.seq_k + kTileK - 1) / kTileK;
+    const int kv_tiles = p.causal ? min(kv_all, (qt * kTileQ + kTileQ + kTileK - 1) / kTileK) : kv_all;
     const WaitCtx wctx{abort_flag, p.status};
 
     if (threadIdx.x == 0) {
@@ -241,8 +247,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
             for (int ch = 0; ch < kTileK / 64; ++ch) ptx::tmem_ld_32x32b_x32(s_row + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[ch * 32]));
             ptx::tmem_ld_wait();
-            const int valid = p.seq_k - j * kTileK - half * (kTileK / 2);       // of this thread's columns
-            if (valid < kTileK / 2) {                           // last, ragged tile only
+            int valid = p.seq_k - j * kTileK - half * (kTileK / 2);             // of this thread's columns
+            if (p.causal) valid = min(valid, qt * kTileQ + row_in_tile - j * kTileK - half * (kTileK / 2) + 1);
+            if (valid < kTileK / 2) {                           // ragged last tile, or the causal diagonal
 #pragma unroll
                 for (int i = 0; i < kTileK / 2; ++i)
                     if (i >= valid) r[i] = __float_as_uint(c > 0.0f ? -CUDART_INF_F : CUDART_INF_F);
@@ -392,8 +399,8 @@ int attention_read_status(uint32_t* out) {
 }
 
 template <int D, bool BF16>
-static int launch_attention(const void* Q, const void* K, const void* V, void* const* O, int n_dst, int64_t units, int64_t seq_q,
-                            int64_t seq_k, float scale, cudaStream_t stream) {
+static int launch_attention(const void* Q, const void* K, const void* V, void* const* O, int n_dst, bool causal, int64_t units,
+                            int64_t seq_q, int64_t seq_k, float scale, cudaStream_t stream) {
     using S = AttSmem<D>;
     CUtensorMap mq, mk, mv;
     int rc = make_tensor_map_3d(&mq, Q, (uint64_t)units, (uint64_t)seq_q, D, kTileQ, 64);
@@ -406,7 +413,7 @@ static int launch_attention(const void* Q, const void* K, const void* V, void* c
     auto kernel = attention_fwd_kernel<D, BF16>;
     EMMY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
     AttParams p;
-    p.n_dst = n_dst; p.seq_q = (int)seq_q; p.seq_k = (int)seq_k;
+    p.n_dst = n_dst; p.causal = causal ? 1 : 0; p.seq_q = (int)seq_q; p.seq_k = (int)seq_k;
     p.q_tiles = (int)((seq_q + kTileQ - 1) / kTileQ);
     p.scale_log2 = scale * 1.4426950408889634f;
     EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_att_status));
@@ -418,10 +425,12 @@ static int launch_attention(const void* Q, const void* K, const void* V, void* c
 
 }  // namespace emmy
 
-static int attention_entry(int dtype, const void* Q, const void* K, const void* V, void* const* O, int n_dst, int64_t units,
+static int attention_entry(int dtype, int flags, const void* Q, const void* K, const void* V, void* const* O, int n_dst, int64_t units,
                            int64_t seq_q, int64_t seq_k, int64_t d, float scale, void* cuda_stream) {
     using namespace emmy;
     if (dtype != EMMYB200_F16 && dtype != EMMYB200_BF16) return fail(EMMYB200_ERR_UNSUPPORTED, "attention_fwd: dtype %d (f16 and bf16 only)", dtype);
+    if (flags & ~EMMYB200_ATT_CAUSAL) return fail(EMMYB200_ERR_ARG, "attention_fwd: unknown flags 0x%x", flags);
+    const bool causal = flags & EMMYB200_ATT_CAUSAL;
     if (n_dst < 1 || n_dst > kMaxDst) return fail(EMMYB200_ERR_ARG, "attention_fwd: %d destinations (1 to %d)", n_dst, kMaxDst);
     if (units < 0 || seq_q < 0 || seq_k < 0) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: negative extent");
     if (units == 0 || seq_q == 0) return EMMYB200_OK;
@@ -439,21 +448,21 @@ static int attention_entry(int dtype, const void* Q, const void* K, const void* 
     if (rc != EMMYB200_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
     const bool bf16 = dtype == EMMYB200_BF16;
-    if (d == 128) return bf16 ? launch_attention<128, true>(Q, K, V, O, n_dst, units, seq_q, seq_k, scale, s)
-                              : launch_attention<128, false>(Q, K, V, O, n_dst, units, seq_q, seq_k, scale, s);
-    return bf16 ? launch_attention<64, true>(Q, K, V, O, n_dst, units, seq_q, seq_k, scale, s)
-                : launch_attention<64, false>(Q, K, V, O, n_dst, units, seq_q, seq_k, scale, s);
+    if (d == 128) return bf16 ? launch_attention<128, true>(Q, K, V, O, n_dst, causal, units, seq_q, seq_k, scale, s)
+                              : launch_attention<128, false>(Q, K, V, O, n_dst, causal, units, seq_q, seq_k, scale, s);
+    return bf16 ? launch_attention<64, true>(Q, K, V, O, n_dst, causal, units, seq_q, seq_k, scale, s)
+                : launch_attention<64, false>(Q, K, V, O, n_dst, causal, units, seq_q, seq_k, scale, s);
 }
 
-extern "C" int emmyb200_attention_fwd(int dtype, const void* Q, const void* K, const void* V, void* O, int64_t units,
+extern "C" int emmyb200_attention_fwd(int dtype, int flags, const void* Q, const void* K, const void* V, void* O, int64_t units,
                                       int64_t seq_q, int64_t seq_k, int64_t d, float scale, void* cuda_stream) {
     void* dst[1] = {O};
-    return attention_entry(dtype, Q, K, V, dst, 1, units, seq_q, seq_k, d, scale, cuda_stream);
+    return attention_entry(dtype, flags, Q, K, V, dst, 1, units, seq_q, seq_k, d, scale, cuda_stream);
 }
 
-extern "C" int emmyb200_attention_fwd_allgather(int dtype, const void* Q, const void* K, const void* V, void* const* O_dst,
+extern "C" int emmyb200_attention_fwd_allgather(int dtype, int flags, const void* Q, const void* K, const void* V, void* const* O_dst,
                                                 int n_dst, int64_t units, int64_t seq_q, int64_t seq_k, int64_t d, float scale,
                                                 void* cuda_stream) {
     if (O_dst == nullptr) return emmy::fail(EMMYB200_ERR_ARG, "attention_fwd_allgather: null destination list");
-    return attention_entry(dtype, Q, K, V, O_dst, n_dst, units, seq_q, seq_k, d, scale, cuda_stream);
+    return attention_entry(dtype, flags, Q, K, V, O_dst, n_dst, units, seq_q, seq_k, d, scale, cuda_stream);
 }

@@ -394,10 +394,13 @@ def gemm_kernel(m: int, n: int, k: int, dtype: str = "f16", epilogue: str | None
 
 
 def attention_kernel(units_shape: list[int], seq_q: int, seq_k: int, d: int, dtype: str = "bf16", scale: float | None = None,
-                     name: str = "k_sdpa"):
+                     name: str = "k_sdpa", causal: bool = False):
     """softmax(Q K^T * scale) V as fused generic statements: two MMA groups with an exp and a row reduction between
-    them. Only the features the matcher keys on are spelled out."""
+    them. Only the features the matcher keys on are spelled out. `causal` adds the lower-triangular mask the way the
+    tracer lowers `masked_fill(~tril, -inf)`: a comparison of the key index with the query index feeding a `where`."""
     scale = d ** -0.5 if scale is None else scale
+    mask = [Assign("keep", Op("le"), [Var("j0"), Var("q0")]),
+            Assign("t0", Op("where"), ["keep", "t0", float("-inf")])] if causal else []
     u = 1
     for s in units_shape:
         u *= s
@@ -408,7 +411,7 @@ def attention_kernel(units_shape: list[int], seq_q: int, seq_k: int, d: int, dty
                 LdmatrixLoad("_q", "a", "Q", [Var("u0"), Var("q0"), Literal(0, "int")]),
                 LdmatrixLoad("_k", "b", "K", [Var("u0"), Var("j0"), Literal(0, "int")], b_trans=True),
                 MmaSyncPtx("_s", "_q", "_k", ab_dtype=dtype),
-                Assign("t0", Op("multiply"), ["_s", scale]),
+                Assign("t0", Op("multiply"), ["_s", scale]), *mask,
                 WarpShuffle(["mx"], ["mx_b"], [Assign("mx", Op("maximum"), ["mx", "mx_b"])], 4),
                 Assign("t1", Op("subtract"), ["t0", "mx"]), Assign("p", Op("exp"), ["t1"]),
                 WarpShuffle(["sm"], ["sm_b"], [Assign("sm", Op("add"), ["sm", "sm_b"])], 4),

@@ -93,5 +93,11 @@ def algorithmic_work(handle: dict) -> tuple[float, str]:
     if v == "gemm_batched":
         return 2.0 * p["batch"] * p["m"] * p["n"] * p["k"], "flop"
     if v == "attention_fwd":
-        return 4.0 * p["units"] * p["seq_q"] * p["seq_k"] * p["d"], "flop"
+        sq, sk = p["seq_q"], p["seq_k"]
+        pairs = sq * sk
+        if p.get("causal"):                       # query i meets keys 0 .. min(i, sk - 1)
+            full = max(0, sq - sk)
+            tri = min(sq, sk)
+            pairs = tri * (tri + 1) // 2 + full * sk
+        return 4.0 * p["units"] * pairs * p["d"], "flop"
     raise CompileError(f"unknown variant {v!r}")

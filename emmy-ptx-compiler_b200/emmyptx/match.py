@@ -428,8 +428,15 @@ def match_contraction(graph, kernel, launch: dict) -> dict:
                   if isinstance(a, float)]
         if floats:
             scale = floats[0]
+        # a `where` that fills -inf under an index comparison is the lower-triangular mask (tools/torch_cases/fused.py:31-36)
+        assigns = [s for s in stmts if _kind(s) == "Assign"]
+        fills = [s for s in assigns if s.op.name == "where" and any(isinstance(a, float) and a == float("-inf") for a in s.args)]
+        causal = bool(fills) and any(s.op.name in ("le", "ge", "lt", "gt") for s in assigns)
+        if fills and not causal:
+            raise Unmatched("a masked softmax other than the lower-triangular one has no variant")
         return {"variant": "attention_fwd", "inputs": srcs, "outputs": [out],
-                "params": {"dtype": dtype, "units": math.prod(q[:-2]), "seq_q": q[-2], "seq_k": k[-2], "d": d, "scale": scale}}
+                "params": {"dtype": dtype, "units": math.prod(q[:-2]), "seq_q": q[-2], "seq_k": k[-2], "d": d, "scale": scale,
+                           "causal": causal}}
     if len(srcs) != 2:
         raise Unmatched("a GEMM reads two operand buffers")
     a_loads = [s for s in loads if s.role == "a"]

@@ -120,6 +120,6 @@ def launch(handle: dict, bufs: dict, stream=None) -> None:
     elif v == "attention_fwd":
         shp = (p["units"], -1, p["d"])
         runtime.attention(ins[0].reshape(shp), ins[1].reshape(shp), ins[2].reshape(shp), scale=p["scale"],
-                          out=out.reshape(shp), stream=stream)
+                          causal=p.get("causal", False), out=out.reshape(shp), stream=stream)
     else:
         raise RuntimeError(f"unknown kernel variant {v!r}")

@@ -39,6 +39,7 @@ class PwProgram(ctypes.Structure):
 EPI_NONE, EPI_GELU_TANH, EPI_RELU = 0, 1, 2
 EPILOGUES = {None: EPI_NONE, "none": EPI_NONE, "gelu_tanh": EPI_GELU_TANH, "relu": EPI_RELU}
 GEMM_B_NK = 1
+ATT_CAUSAL = 1
 GATHER_TRUNC = 1
 
 _SIGNATURES = {
@@ -59,10 +60,10 @@ _SIGNATURES = {
     "emmyb200_gemm_allgather": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
                                                ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),
-    "emmyb200_attention_fwd": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+    "emmyb200_attention_fwd": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                               ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                               ctypes.c_int64, ctypes.c_float, ctypes.c_void_p]),
-    "emmyb200_attention_fwd_allgather": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+    "emmyb200_attention_fwd_allgather": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                         ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int64,
                                                         ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_float,
                                                         ctypes.c_void_p]),
@@ -222,8 +223,9 @@ def gemm_allgather(a, b, dst_ptrs: list[int], ldc: int, epilogue: str | None = N
                                             _stream(stream)))
 
 
-def attention(q, k, v, scale: float | None = None, out=None, stream=None):
-    """softmax(q k^T * scale) v over the last two axes; leading axes are independent units."""
+def attention(q, k, v, scale: float | None = None, causal: bool = False, out=None, stream=None):
+    """softmax(q k^T * scale) v over the last two axes; leading axes are independent units. `causal`: query i sees
+    keys 0..i only."""
     import torch
     _need_cuda(q, k, v)
     d = q.shape[-1]
@@ -231,12 +233,12 @@ def attention(q, k, v, scale: float | None = None, out=None, stream=None):
     out = torch.empty_like(q) if out is None else out
     _need_cuda(out)
     scale = d ** -0.5 if scale is None else scale
-    check(library().emmyb200_attention_fwd(dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), units,
+    check(library().emmyb200_attention_fwd(dtype_code(q), ATT_CAUSAL if causal else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), units,
                                            q.shape[-2], k.shape[-2], d, scale, _stream(stream)))
     return out
 
 
-def attention_allgather(q, k, v, dst_ptrs: list[int], scale: float | None = None, stream=None):
+def attention_allgather(q, k, v, dst_ptrs: list[int], scale: float | None = None, causal: bool = False, stream=None):
     """attention() on this rank's units, every output tile stored to each address in `dst_ptrs` (this rank's slice of
     O first, then the same slice inside each peer's full O)."""
     _need_cuda(q, k, v)
@@ -244,7 +246,7 @@ def attention_allgather(q, k, v, dst_ptrs: list[int], scale: float | None = None
     units = q.numel() // (q.shape[-2] * d)
     arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
     scale = d ** -0.5 if scale is None else scale
-    check(library().emmyb200_attention_fwd_allgather(dtype_code(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), arr, len(dst_ptrs),
+    check(library().emmyb200_attention_fwd_allgather(dtype_code(q), ATT_CAUSAL if causal else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), arr, len(dst_ptrs),
                                                      units, q.shape[-2], k.shape[-2], d, scale, _stream(stream)))
 
 

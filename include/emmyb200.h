@@ -140,8 +140,10 @@ int emmyb200_gemm_allgather(int dtype, int epilogue, int flags, const void* A, c
  * reference emits as generic fused statements (dot-product Loops + Accum, WarpShuffle /
  * TreeHalve row reductions, `_exp`: emmyptx/kernel.py:786-797, :856-900, emmyptx/ops.py:49-77).
  * Q, O: [units, seq_q, d]; K, V: [units, seq_k, d]; contiguous, dtype F16 or BF16, d = 128
- * or 64, any seq_q, seq_k >= 1. */
-int emmyb200_attention_fwd(int dtype, const void* Q, const void* K, const void* V, void* O,
+ * or 64, any seq_q, seq_k >= 1. EMMYB200_ATT_CAUSAL: query i attends to keys 0..i only (the lower-triangular
+ * mask of tools/torch_cases/models.py:17-19, fused.py:31-36). */
+#define EMMYB200_ATT_CAUSAL 1
+int emmyb200_attention_fwd(int dtype, int flags, const void* Q, const void* K, const void* V, void* O,
                            int64_t units, int64_t seq_q, int64_t seq_k, int64_t d, float scale,
                            void* cuda_stream);
 
@@ -149,7 +151,7 @@ int emmyb200_attention_fwd(int dtype, const void* Q, const void* K, const void* 
  * (1..8): O_dst[0] is this GPU's own slice of O, the others the addresses, valid on this GPU, of the same
  * slice inside each peer's full O. No counterpart in the reference (single GPU); it serves the
  * (batch x head)-sharded configuration. The caller synchronises the group before reading peers' units. */
-int emmyb200_attention_fwd_allgather(int dtype, const void* Q, const void* K, const void* V,
+int emmyb200_attention_fwd_allgather(int dtype, int flags, const void* Q, const void* K, const void* V,
                                      void* const* O_dst, int n_dst, int64_t units, int64_t seq_q,
                                      int64_t seq_k, int64_t d, float scale, void* cuda_stream);
 

@@ -40,8 +40,8 @@ def test_argument_checks_need_no_device(lib):
     assert lib.emmyb200_index_gather_i32(None, None, 16, 1, 0, 3, 2, 0, None) == -1
     assert lib.emmyb200_gemm(0, 0, 0, None, None, None, 8, 8, 8, 8, 8, 8, None) == -4
     assert lib.emmyb200_gemm(1, 0, 0, None, None, None, 8, 8, 8, 8, 8, 8, None) == -1
-    assert lib.emmyb200_attention_fwd(2, None, None, None, None, 1, 8, 8, 96, 1.0, None) == -4
-    assert lib.emmyb200_attention_fwd(2, None, None, None, None, 1, 8, 8, 128, 1.0, None) == -1
+    assert lib.emmyb200_attention_fwd(2, 0, None, None, None, None, 1, 8, 8, 96, 1.0, None) == -4
+    assert lib.emmyb200_attention_fwd(2, 0, None, None, None, None, 1, 8, 8, 128, 1.0, None) == -1
 
 
 def test_python_binding_refuses_cpu_tensors():

@@ -39,6 +39,8 @@ def test_the_five_configurations_match_their_kernels():
     assert h["variant"] == "attention_fwd" and h["params"]["units"] == 256 and h["params"]["d"] == 128
     assert abs(h["params"]["scale"] - 128 ** -0.5) < 1e-12
     assert algorithmic_work(h) == (4.0 * 256 * 4096 * 4096 * 128, "flop")
+    assert h["params"]["causal"] is False
+    assert handle(ir.attention_kernel([2], 512, 512, 64, "f16", causal=True))["params"]["causal"] is True
 
 
 def test_matching_is_by_meaning_not_by_spelling():

@@ -74,13 +74,46 @@ def test_rows_sum_property(cuda):
     assert (a.float() - b.float()).abs().max() <= 1e-2 * a.float().std() + 1e-2 * a.float().abs().max()
 
 
+@pytest.mark.parametrize("units,s,d", [(2, 256, 128), (3, 300, 128), (2, 64, 32 * 2), (1, 1000, 128), (2, 129, 64)])
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_causal(units, s, d, dtype, cuda):
+    """t_causal_sdpa / f_masked_attn_manual (tools/torch_cases/models.py:17-19, fused.py:31-36): lower-triangular mask.
+
+    The absolute floor of the bound is taken per query row (1e-2 of the row's rms) rather than over the whole
+    output: early rows average a handful of values and are O(1) while late rows average thousands and are small,
+    so one global std would hold the early rows' 16-bit probabilities to a tighter class than 1e-2."""
+    import torch
+    q, k, v = inputs.attention_inputs(units, s, s, d, dtype)
+    got = _attn(q, k, v, cuda, causal=True)
+    scores = torch.matmul(q.double(), k.double().transpose(-1, -2)) * d ** -0.5
+    mask = torch.ones(s, s, dtype=torch.bool).tril()
+    ref = torch.matmul(torch.softmax(scores.masked_fill(~mask, float("-inf")), -1), v.double())
+    bound = 1e-2 * ref.abs() + 1e-2 * ref.pow(2).mean(-1, keepdim=True).sqrt()
+    ratio = float(((got.double() - ref).abs() / bound).max())
+    assert ratio <= 1.0, f"worst error {ratio:.2f}x the bound"
+    assert torch.equal(got[:, 0].float(), v[:, 0].float())        # the first query sees one key: O = V[0] exactly
+
+
+def test_causal_skips_tiles_past_the_diagonal(cuda):
+    """Keys after the query must not influence the result at all: poisoning them with NaN changes nothing."""
+    import torch
+    q, k, v = inputs.attention_inputs(2, 384, 384, 128, "bf16")
+    a = _attn(q, k, v, cuda, causal=True)
+    k2, v2 = k.clone(), v.clone()
+    k2[:, 256:] = float("nan")
+    v2[:, 256:] = float("nan")
+    b = _attn(q, k2, v2, cuda, causal=True)
+    assert torch.equal(a[:, :256], b[:, :256])
+
+
 def test_rejects_bad_arguments(cuda, lib):
     import torch
     x = torch.zeros(2 * 128 * 128, dtype=torch.bfloat16, device=cuda)
     p = x.data_ptr()
     f = lib.emmyb200_attention_fwd
-    assert f(2, p, p, p, p, 2, 128, 128, 96, 0.1, None) == -4      # head dim
-    assert f(0, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -4     # f32
-    assert f(2, p, p, p, p, 2, 128, 0, 128, 0.1, None) == -2       # no keys
-    assert f(2, p, p, p, p, 0, 128, 128, 128, 0.1, None) == 0      # no units
-    assert f(2, None, p, p, p, 2, 128, 128, 128, 0.1, None) == -1
+    assert f(2, 0, p, p, p, p, 2, 128, 128, 96, 0.1, None) == -4      # head dim
+    assert f(0, 0, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -4     # f32
+    assert f(2, 0, p, p, p, p, 2, 128, 0, 128, 0.1, None) == -2       # no keys
+    assert f(2, 0, p, p, p, p, 0, 128, 128, 128, 0.1, None) == 0      # no units
+    assert f(2, 8, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -1     # unknown flag
+    assert f(2, 0, None, p, p, p, 2, 128, 128, 128, 0.1, None) == -1

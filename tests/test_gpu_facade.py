@@ -82,6 +82,19 @@ def test_attention_through_the_facade(tmp_path, cuda):
     assert reference.compare(out["O"].reshape(shp).astype(np.float64), ref, 1e-2, 1e-2)["ok"]       # HALF class
 
 
+def test_causal_attention_through_the_facade(tmp_path, cuda):
+    import torch
+    shp = [4, 200, 64]
+    out = compile_and_run(tmp_path, ir.attention_kernel([4], 200, 200, 64, "f16", causal=True), [
+        {"name": n, "dtype": "f16", "shape": shp, "seed": i} for i, n in enumerate("QKV")] +
+        [{"name": "O", "dtype": "f16", "shape": shp, "output": True}])
+    q, k, v = (torch.from_numpy(np.random.default_rng(i).standard_normal(shp).astype(np.float32)).half().double() for i in range(3))
+    scores = (q @ k.transpose(-1, -2)) * 64 ** -0.5
+    scores = scores.masked_fill(~torch.ones(200, 200, dtype=torch.bool).tril(), float("-inf"))
+    ref = (torch.softmax(scores, -1) @ v).numpy()
+    assert reference.compare(out["O"].reshape(shp).astype(np.float64), ref, 1e-2, 1e-2)["ok"]       # HALF class
+
+
 def test_kernels_against_the_reference_golden_vectors(cuda):
     """golden.npz is the reference's own PTX executed on these inputs. Integer kernel in the reference's
     (truncating) mode: bit for bit. Float kernels: within the reference's tolerance class of each other."""
