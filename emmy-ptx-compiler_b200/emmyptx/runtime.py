@@ -41,6 +41,9 @@ EPILOGUES = {None: EPI_NONE, "none": EPI_NONE, "gelu_tanh": EPI_GELU_TANH, "relu
 GEMM_B_NK = 1
 ATT_CAUSAL = 1
 GATHER_TRUNC = 1
+ROW_OPS = {"sum": 0, "mean": 1, "amax": 2, "amin": 3, "prod": 4, "var": 5, "std": 6, "norm2": 7, "logsumexp": 8, "argmax": 9,
+           "softmax": 16, "log_softmax": 17, "layer_norm": 18, "rms_norm": 19, "normalize": 20}
+ROW_MAP_FIRST = 16            # ops from here on write [rows, cols]
 
 _SIGNATURES = {
     "emmyb200_version": (ctypes.c_int, []),
@@ -67,6 +70,10 @@ _SIGNATURES = {
                                                         ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int64,
                                                         ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_float,
                                                         ctypes.c_void_p]),
+    "emmyb200_rowwise_workspace_bytes": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64]),
+    "emmyb200_rowwise_f32": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                            ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_int64,
+                                            ctypes.c_void_p]),
     "emmyb200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
 }
 EXPORTS = tuple(_SIGNATURES)
@@ -248,6 +255,37 @@ def attention_allgather(q, k, v, dst_ptrs: list[int], scale: float | None = None
     scale = d ** -0.5 if scale is None else scale
     check(library().emmyb200_attention_fwd_allgather(dtype_code(q), ATT_CAUSAL if causal else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), arr, len(dst_ptrs),
                                                      units, q.shape[-2], k.shape[-2], d, scale, _stream(stream)))
+
+
+def rowwise(op: str, x, weight=None, bias=None, eps: float = 0.0, out=None, workspace=None, stream=None):
+    """Reduce (or normalise) the last axis of a contiguous float32 CUDA tensor; `op` is a key of ROW_OPS. Reducing ops
+    return x.shape[:-1] (int64 for argmax), the others x.shape. Long rows need workspace memory, taken from torch's
+    allocator unless a uint8 tensor is passed."""
+    import torch
+    _need_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() < 1:
+        raise TypeError("rowwise: a contiguous float32 tensor with at least one axis")
+    code = ROW_OPS[op]
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    if out is None:
+        out = (torch.empty_like(x) if code >= ROW_MAP_FIRST else
+               torch.empty(x.shape[:-1], dtype=torch.int64 if op == "argmax" else torch.float32, device=x.device))
+    _need_cuda(out)
+    for t in (weight, bias):
+        if t is not None:
+            _need_cuda(t)
+            if t.dtype != torch.float32 or t.numel() != cols or not t.is_contiguous():
+                raise TypeError("rowwise: weight / bias are contiguous float32 vectors of the row length")
+    lib = library()
+    need = lib.emmyb200_rowwise_workspace_bytes(code, rows, cols)
+    if need > 0 and (workspace is None or workspace.numel() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    check(lib.emmyb200_rowwise_f32(code, x.data_ptr(), weight.data_ptr() if weight is not None else None,
+                                   bias.data_ptr() if bias is not None else None, out.data_ptr(), rows, cols, eps,
+                                   workspace.data_ptr() if workspace is not None else None,
+                                   workspace.numel() if workspace is not None else 0, _stream(stream)))
+    return out
 
 
 def device_status() -> int:

@@ -155,6 +155,37 @@ int emmyb200_attention_fwd_allgather(int dtype, int flags, const void* Q, const 
                                      void* const* O_dst, int n_dst, int64_t units, int64_t seq_q,
                                      int64_t seq_k, int64_t d, float scale, void* cuda_stream);
 
+/* Reductions over the last axis of a contiguous fp32 [rows, cols] array and the normalisations built on them:
+ * the kernels the reference assembles from per-thread `Accum` loops, `WarpShuffle` butterflies and `TreeHalve`
+ * shared-memory trees (emmyptx/kernel.py:786-797, :856-900) for the cases of tools/torch_cases/reductions.py:6-19
+ * and fused.py:6-13. Ops below EMMYB200_ROW_SOFTMAX store one value per row (y: float[rows]; ARGMAX:
+ * int64_t[rows], first index of the maximum, NaN counting as the largest, as torch); the others store
+ * y: float[rows, cols]. VAR and STD are the unbiased estimates (torch's default). LAYER_NORM is
+ * (x - mean) / sqrt(biased var + eps) * weight + bias and RMS_NORM x / sqrt(mean(x^2) + eps) * weight, `weight`
+ * and `bias` being float[cols] or NULL; NORMALIZE is x / max(||x||_2, eps). Other ops take NULL for both.
+ * Rows of more than 65536 elements are reduced in pieces by several thread blocks, which needs
+ * emmyb200_rowwise_workspace_bytes(op, rows, cols) bytes of 256-byte-aligned device memory (contents
+ * irrelevant before, undefined after; 0 for shorter rows, -1 for arguments the call would reject); results do
+ * not depend on the order in which blocks finish. rows >= 0, 1 <= cols < 2^31. */
+#define EMMYB200_ROW_SUM 0
+#define EMMYB200_ROW_MEAN 1
+#define EMMYB200_ROW_AMAX 2
+#define EMMYB200_ROW_AMIN 3
+#define EMMYB200_ROW_PROD 4
+#define EMMYB200_ROW_VAR 5
+#define EMMYB200_ROW_STD 6
+#define EMMYB200_ROW_NORM2 7
+#define EMMYB200_ROW_LOGSUMEXP 8
+#define EMMYB200_ROW_ARGMAX 9
+#define EMMYB200_ROW_SOFTMAX 16
+#define EMMYB200_ROW_LOG_SOFTMAX 17
+#define EMMYB200_ROW_LAYER_NORM 18
+#define EMMYB200_ROW_RMS_NORM 19
+#define EMMYB200_ROW_NORMALIZE 20
+int64_t emmyb200_rowwise_workspace_bytes(int op, int64_t rows, int64_t cols);
+int emmyb200_rowwise_f32(int op, const float* x, const float* weight, const float* bias, void* y, int64_t rows,
+                         int64_t cols, float eps, void* workspace, int64_t workspace_bytes, void* cuda_stream);
+
 /* Reads (and clears) the device status word of the current device: 0 if no bounded wait has
  * expired since the last call, else a code naming kernel, role and pipeline stage.
  * Synchronises the device. */

@@ -108,6 +108,35 @@ def attention_reference(q, k, v, scale: float | None = None, double: bool = Fals
     return torch.matmul(torch.softmax(s, dim=-1), v)
 
 
+# ---- row reductions and normalisations (tools/torch_cases/reductions.py:6-19, fused.py:6-13) ----------------------
+def rowwise_reference(op: str, x, weight=None, bias=None, eps: float = 0.0):
+    """float64 torch evaluation of one row op on float32 data, as tools/check_torch.py:194-237 defines truth."""
+    import torch
+    import torch.nn.functional as F
+    x = x.double()
+    w = None if weight is None else weight.double()
+    b = None if bias is None else bias.double()
+    n = x.shape[-1]
+    if op == "sum": return x.sum(-1)
+    if op == "mean": return x.mean(-1)
+    if op == "amax": return x.amax(-1)
+    if op == "amin": return x.amin(-1)
+    if op == "prod": return x.prod(-1)
+    if op == "var": return x.var(-1)
+    if op == "std": return x.std(-1)
+    if op == "norm2": return torch.linalg.vector_norm(x, dim=-1)
+    if op == "logsumexp": return torch.logsumexp(x, -1)
+    if op == "argmax": return x.argmax(-1)
+    if op == "softmax": return torch.softmax(x, -1)
+    if op == "log_softmax": return torch.log_softmax(x, -1)
+    if op == "layer_norm": return F.layer_norm(x, (n,), w, b, eps)
+    if op == "rms_norm":
+        y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+        return y if w is None else y * w
+    if op == "normalize": return F.normalize(x, dim=-1, eps=eps)
+    raise KeyError(op)
+
+
 # ---- the reference harness's comparison -----------------------------------------------------------------
 def compare(got: np.ndarray, ref: np.ndarray, rtol: float, atol: float) -> dict:
     """`tools/check_torch.py:260-278`: isclose with equal NaNs, plus the vacuity check (an all-zero
