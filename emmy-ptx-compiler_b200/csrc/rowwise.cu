@@ -6,7 +6,7 @@
 // (:868-900); the combine step is an ordinary Assign program. The cases are those of
 // tools/torch_cases/reductions.py:6-19 and fused.py:6-13. Here the same three levels are fixed in CUDA:
 //
-//   * rowwise_cached_kernel: a row is held in registers by a group of G threads (8, 32 or 256, by row length) or,
+//   * rowwise_cached_kernel: a row is held in registers by a group of G threads (8 to 256, by row length) or,
 //     beyond 8192 elements, by the 2, 4 or 8 CTAs of a thread-block cluster, which exchange their partial
 //     results through distributed shared memory; so the array is read once and written at most once, with
 //     128-bit accesses; the grid is a multiple of the SM count and walks the rows.
@@ -164,8 +164,10 @@ __device__ __forceinline__ St group_allreduce(St s, ReduceSlabs* slabs, int& rou
         ++round;
         St* slab = slabs->warp + buf * 32;
         if (lane == 0) slab[threadIdx.x >> 5] = s;
-        __syncthreads();
-        s = lane < G / 32 ? slab[lane] : st_identity<K>();
+        const int first_warp = (threadIdx.x / G) * (G / 32);    // of this group
+        if constexpr (G == 256) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"r"(1 + (int)threadIdx.x / G), "n"(G) : "memory");      // the group only
+        s = lane < G / 32 ? slab[first_warp + lane] : st_identity<K>();
         s = warp_allreduce<K>(s, 32, lane);                     // identities in the upper lanes: every lane gets the result
         if (csize > 1) {
             if (threadIdx.x == 0) slabs->cta[buf] = s;
@@ -269,6 +271,9 @@ __global__ void __launch_bounds__(256) rowwise_cached_kernel(RowArgs a) {
         // squared deviations from the mean; max, then exponentials against it; max, then the first column equal to it.
         constexpr int K1 = K == K_MOM ? K_ADD : ((K == K_LSE || K == K_ARG) ? K_MAX : K);
         St s = st_identity<K1>();
+        // Extrema go through the one-instruction hardware max / min, which drops NaNs; a sum of x * 2^-120 on the FMA
+        // pipe (NaN iff the values hold a NaN, or infinities of both signs) tells when the careful version is needed.
+        float nan_probe = 0.0f;
 #pragma unroll
         for (int i = 0; i < kIter; ++i) {
             if (slice_end + i * G * VEC >= cols) break;
@@ -279,20 +284,38 @@ __global__ void __launch_bounds__(256) rowwise_cached_kernel(RowArgs a) {
                     const float x = v[VEC * i + e];
                     if constexpr (K1 == K_ADD) s.a += x;
                     else if constexpr (K1 == K_SQ) s.a = fmaf(x, x, s.a);
-                    else if constexpr (K1 == K_MAX) s.a = nan_max(s.a, x);
-                    else if constexpr (K1 == K_MIN) s.a = nan_min(s.a, x);
+                    else if constexpr (K1 == K_MAX) { s.a = fmaxf(s.a, x); nan_probe = fmaf(x, 0x1p-120f, nan_probe); }
+                    else if constexpr (K1 == K_MIN) { s.a = fminf(s.a, x); nan_probe = fmaf(x, 0x1p-120f, nan_probe); }
                     else s.a *= x;
                 }
             }
         }
+        if constexpr (K1 == K_MAX || K1 == K_MIN) {
+            if (nan_probe != nan_probe) {
+#pragma unroll
+                for (int i = 0; i < kIter; ++i) {
+                    if (slice_end + i * G * VEC >= cols) break;
+                    const int c = (first + i * G) * VEC;
+                    if (live && c < cols) {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) s.a = K1 == K_MAX ? nan_max(s.a, v[VEC * i + e]) : nan_min(s.a, v[VEC * i + e]);
+                    }
+                }
+            }
+        }
+        const float own = s.a;                                  // this thread's extremum (argmax looks only where it is the row's)
         s = group_allreduce<K1, G>(s, &slabs, round, csize);
         if constexpr (K == K_MOM || K == K_LSE || K == K_ARG) {
             const float centre = K == K_MOM ? s.a / (float)cols : s.a;      // the mean, or the max
             const bool max_is_nan = centre != centre;
+            int hit = INT_MAX;
             St s2 = st_identity<K == K_ARG ? K_MIN : K_ADD>();
 #pragma unroll
             for (int i = kIter - 1; i >= 0; --i) {                          // downwards: the lowest matching column is kept
                 const int c = (first + i * G) * VEC;
+                if constexpr (K == K_ARG) {
+                    if (!(own == centre || max_is_nan)) break;               // the maximum is not among this thread's values
+                }
                 if (slice_end + i * G * VEC < cols && live && c < cols) {
 #pragma unroll
                     for (int e = VEC - 1; e >= 0; --e) {
@@ -305,11 +328,13 @@ __global__ void __launch_bounds__(256) rowwise_cached_kernel(RowArgs a) {
                             s2.a += p;
                             if constexpr (OP == EMMYB200_ROW_SOFTMAX) v[VEC * i + e] = p;
                         } else {
-                            if (max_is_nan ? x != x : x == centre) s2.a = (float)(c + e);      // columns < 2^24: exact
+                            if (x == centre || (max_is_nan && x != x)) hit = i * G * VEC + e;      // a constant: no index registers
                         }
                     }
                 }
             }
+            // columns < 2^24 are exact as floats; INT_MAX stands for "none here"
+            if constexpr (K == K_ARG) s2.a = hit == INT_MAX ? (float)INT_MAX : (float)(hit + first * VEC);
             s2 = group_allreduce<K == K_ARG ? K_MIN : K_ADD, G>(s2, &slabs, round, csize);
             if constexpr (K == K_MOM) s = {(float)cols, centre, s2.a};
             else if constexpr (K == K_LSE) s = {centre, s2.a, 0.0f};
@@ -554,7 +579,10 @@ int launch_op(const RowArgs& a, void* ws, cudaStream_t s) {
     if (a.cols <= kMaxCachedCols) {
         constexpr int kIter = kPerThread / VEC;
         if (per <= 8 * kIter) return launch_cached<OP, 8, VEC>(a, 1, s);
+        if (per <= 16 * kIter) return launch_cached<OP, 16, VEC>(a, 1, s);
         if (per <= 32 * kIter) return launch_cached<OP, 32, VEC>(a, 1, s);
+        if (per <= 64 * kIter) return launch_cached<OP, 64, VEC>(a, 1, s);
+        if (per <= 128 * kIter) return launch_cached<OP, 128, VEC>(a, 1, s);
         const int64_t slices = (per + 256 * kIter - 1) / (256 * kIter);
         return launch_cached<OP, 256, VEC>(a, slices <= 1 ? 1 : (slices <= 2 ? 2 : (slices <= 4 ? 4 : 8)), s);
     }

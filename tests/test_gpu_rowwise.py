@@ -87,7 +87,7 @@ def test_reference_cases(op, rows, cols, rtol, atol, cuda):
 
 
 # ---- every group width, ragged and unaligned rows ----------------------------------------------------------------
-@pytest.mark.parametrize("cols", [1, 3, 4, 5, 31, 64, 127, 256, 257, 1000, 1024, 1028, 4099, 8192,      # one CTA or less per row
+@pytest.mark.parametrize("cols", [1, 3, 4, 5, 31, 64, 127, 256, 257, 500, 1000, 1024, 1028, 2048, 3000, 4096, 4099, 8192,      # one CTA or less per row
                                   8196, 16384, 20001, 32768, 40000, 65536])                             # clusters of 2, 4, 8
 @pytest.mark.parametrize("op", REDUCING + MAPPING)
 def test_cached_rows(op, cols, cuda):
