@@ -578,6 +578,25 @@ def other_workloads(torch, dist, dev, pk, skip: str) -> dict:
                              "frac_of_peak": 8.0 * n / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
     except Exception as e:  # noqa: BLE001
         out["c1_at_2^28"] = {"error": str(e)[:200]}
+    # the rows built after the five configurations: row kernels (256 MiB of fp32, larger than L2) and causal attention
+    try:
+        from emmyptx import runtime
+        x = torch.randn(65536, 1024, device=dev)
+        for op in ("sum", "softmax", "layer_norm"):
+            y = runtime.rowwise(op, x)
+            ms = timed(torch, dist, 1, lambda: runtime.rowwise(op, x, out=y), 5, 3) / 5
+            byts = 4.0 * (x.numel() + y.numel())
+            out[f"row_{op}_65536x1024"] = {"value": byts / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms": ms,
+                                           "frac_of_peak": byts / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+        del x, y
+        q, k, v = (torch.randn(64, 4096, 128, device=dev).to(torch.bfloat16) for _ in range(3))
+        o = torch.empty_like(q)
+        ms = timed(torch, dist, 1, lambda: runtime.attention(q, k, v, causal=True, out=o), 5, 3) / 5
+        flop = 4.0 * 64 * 128 * (4096 * 4097 / 2)
+        out["attention_causal_64x4096x128"] = {"value": flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": ms,
+                                               "frac_of_peak": flop / (ms * 1e-3) / 1e12 / pk.get("bf16_tflops", 1.0)}
+    except Exception as e:  # noqa: BLE001
+        out["next_rows"] = {"error": str(e)[:200]}
     return out
 
 

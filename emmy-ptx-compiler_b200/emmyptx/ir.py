@@ -366,6 +366,73 @@ def index_gather_kernel(n: int, mul: int = 7919, add: int = 13, div: int = 3, sh
     return g, k, _launch(k, ["x", "y"], n)
 
 
+def rowwise_kernel(op: str, rows: int, cols: int, eps: float = 1e-5, name: str = "k_rowwise"):
+    """A reduction over the last axis of X[rows, cols] (or a normalisation built on one) in the statement shapes the
+    reference lowers (emmyptx/kernel.py:786-797 `Accum` inside a `Loop`, :856-866 `WarpShuffle` to merge lanes): one tile
+    cell per row, a loop per pass over the row."""
+    r0, c0 = Axis("r0", Dim(rows)), Axis("c0", Dim(cols))
+    ld = lambda: Load(["x"], "X", [Var("r0"), Var("c0")])
+    shuffle = lambda st, o: WarpShuffle([st], [st + "_b"], [Assign(st, Op(o), [st, st + "_b"])], 32)
+    fold = lambda st, o, pre=(): [Loop(c0, [ld(), *pre, Accum(st, None, pre[-1].name if pre else "x", Op(o))]), shuffle(st, o)]
+    inputs, body, out, is_map = [tensor("X", [rows, cols], "f32")], [], None, False
+    if op in ("sum", "mean", "amax", "amin", "prod"):
+        body = fold("acc", {"sum": "add", "mean": "add", "amax": "maximum", "amin": "minimum", "prod": "multiply"}[op])
+        out = "acc"
+        if op == "mean":
+            body.append(Assign("m", Op("multiply"), ["acc", 1.0 / cols]))
+            out = "m"
+    elif op == "norm2":
+        body = fold("acc", "add", [Assign("sq", Op("multiply"), ["x", "x"])]) + [Assign("n", Op("sqrt"), ["acc"])]
+        out = "n"
+    elif op in ("var", "std", "layer_norm"):
+        body = fold("acc", "add") + [Assign("mean", Op("multiply"), ["acc", 1.0 / cols])]
+        body += fold("acc2", "add", [Assign("d", Op("subtract"), ["x", "mean"]), Assign("d2", Op("multiply"), ["d", "d"])])
+        body.append(Assign("var", Op("multiply"), ["acc2", 1.0 / (cols if op == "layer_norm" else cols - 1)]))
+        out = "var"
+        if op == "std":
+            body.append(Assign("sd", Op("sqrt"), ["var"]))
+            out = "sd"
+        if op == "layer_norm":
+            inputs += [tensor("W", [cols], "f32"), tensor("B", [cols], "f32")]
+            body += [Assign("ve", Op("add"), ["var", float(eps)]), Assign("rs", Op("rsqrt"), ["ve"]),
+                     Loop(c0, [ld(), Load(["w"], "W", [Var("c0")]), Load(["b"], "B", [Var("c0")]),
+                               Assign("d", Op("subtract"), ["x", "mean"]), Assign("n", Op("multiply"), ["d", "rs"]),
+                               Assign("s", Op("multiply"), ["n", "w"]), Assign("o", Op("add"), ["s", "b"]),
+                               Write("Y", [Var("r0"), Var("c0")], ["o"])])]
+            is_map = True
+    elif op in ("logsumexp", "softmax", "log_softmax"):
+        body = fold("mx", "maximum")
+        body += fold("se", "add", [Assign("d", Op("subtract"), ["x", "mx"]), Assign("e", Op("exp"), ["d"])])
+        if op == "logsumexp":
+            body += [Assign("l", Op("log"), ["se"]), Assign("o", Op("add"), ["l", "mx"])]
+            out = "o"
+        else:
+            tail = ([Assign("o", Op("divide"), ["e", "se"])] if op == "softmax" else
+                    [Assign("l", Op("log"), ["se"]), Assign("o", Op("subtract"), ["d", "l"])])
+            body.append(Loop(c0, [ld(), Assign("d", Op("subtract"), ["x", "mx"]), Assign("e", Op("exp"), ["d"]), *tail,
+                                  Write("Y", [Var("r0"), Var("c0")], ["o"])]))
+            is_map = True
+    elif op in ("rms_norm", "normalize"):
+        body = fold("acc", "add", [Assign("sq", Op("multiply"), ["x", "x"])])
+        if op == "rms_norm":
+            inputs.append(tensor("W", [cols], "f32"))
+            body += [Assign("ms", Op("multiply"), ["acc", 1.0 / cols]), Assign("ve", Op("add"), ["ms", float(eps)]),
+                     Assign("rs", Op("rsqrt"), ["ve"]),
+                     Loop(c0, [ld(), Load(["w"], "W", [Var("c0")]), Assign("n", Op("multiply"), ["x", "rs"]),
+                               Assign("o", Op("multiply"), ["n", "w"]), Write("Y", [Var("r0"), Var("c0")], ["o"])])]
+        else:
+            body += [Assign("nrm", Op("sqrt"), ["acc"]), Assign("den", Op("maximum"), ["nrm", float(eps)]),
+                     Loop(c0, [ld(), Assign("o", Op("divide"), ["x", "den"]), Write("Y", [Var("r0"), Var("c0")], ["o"])])]
+        is_map = True
+    else:
+        raise KeyError(op)
+    if not is_map:
+        body.append(Write("Y", [Var("r0")], [out]))
+    kern = KernelOp(name, [Tile([r0], body)])
+    g = _graph(kern, inputs, [tensor("Y", [rows, cols] if is_map else [rows], "f32")])
+    return g, kern, _launch(kern, [t.name for t in inputs] + ["Y"], rows * 32)
+
+
 def gemm_kernel(m: int, n: int, k: int, dtype: str = "f16", epilogue: str | None = None, b_trans: bool = False,
                 name: str = "k_gemm", batch: tuple = (), b_batched: bool = True, bias: bool = False):
     """C = A B on mma.sync cells, as the tracer schedules a 16-bit matmul: accumulator / operand fragments, a K

@@ -100,4 +100,7 @@ def algorithmic_work(handle: dict) -> tuple[float, str]:
             tri = min(sq, sk)
             pairs = tri * (tri + 1) // 2 + full * sk
         return 4.0 * p["units"] * pairs * p["d"], "flop"
+    if v == "rowwise_f32":
+        is_map = p["op"] in ("softmax", "log_softmax", "layer_norm", "rms_norm", "normalize")
+        return 4.0 * p["rows"] * (p["cols"] * (2 if is_map else 1) + (0 if is_map else 1)), "B"
     raise CompileError(f"unknown variant {v!r}")

@@ -10,7 +10,8 @@ in float64 / exact integers over synthetic buffer contents, and compared with wh
 computes for the same cells. Two programs that mean the same thing match the same kernel, however the
 tracer happened to arrange them. Contractions are recognised by their tensor-core statements
 (`RegFragment` / `LdmatrixLoad` / `MmaSyncPtx` / `RegStore`, `emmyptx/mma.py`), whose buffers, layout flags
-and epilogue give the GEMM's parameters; the tile sizes the tracer chose are irrelevant here.
+and epilogue give the GEMM's parameters; the tile sizes the tracer chose are irrelevant here. Row reductions
+(`Loop` / `Accum` under a tile over the rows) are recognised by behaviour too, a few probe rows at a time.
 """
 from __future__ import annotations
 
@@ -471,8 +472,132 @@ def match_contraction(graph, kernel, launch: dict) -> dict:
     return {"variant": "gemm", "inputs": inputs, "outputs": [out], "params": params}
 
 
+# ---- row reductions and normalisations --------------------------------------------------------------------------
+_ACCUM = {"add": np.sum, "maximum": np.max, "minimum": np.min, "multiply": np.prod}
+
+
+def _softmax64(x):
+    e = np.exp(x - x.max(-1, keepdims=True))
+    return e / e.sum(-1, keepdims=True)
+
+
+def _moments(x):
+    m = x.mean(-1, keepdims=True)
+    return m, ((x - m) ** 2).sum(-1, keepdims=True)
+
+
+# op -> f(x, w, b, eps) in float64; reducing ops return [rows, 1]
+ROWWISE_F64 = {
+    "sum": lambda x, w, b, e: x.sum(-1, keepdims=True),
+    "mean": lambda x, w, b, e: x.mean(-1, keepdims=True),
+    "amax": lambda x, w, b, e: x.max(-1, keepdims=True),
+    "amin": lambda x, w, b, e: x.min(-1, keepdims=True),
+    "prod": lambda x, w, b, e: x.prod(-1, keepdims=True),
+    "var": lambda x, w, b, e: _moments(x)[1] / (x.shape[-1] - 1),
+    "std": lambda x, w, b, e: np.sqrt(_moments(x)[1] / (x.shape[-1] - 1)),
+    "norm2": lambda x, w, b, e: np.sqrt((x * x).sum(-1, keepdims=True)),
+    "logsumexp": lambda x, w, b, e: np.log(np.exp(x - x.max(-1, keepdims=True)).sum(-1, keepdims=True)) + x.max(-1, keepdims=True),
+    "softmax": lambda x, w, b, e: _softmax64(x),
+    "log_softmax": lambda x, w, b, e: np.log(_softmax64(x)),
+    "layer_norm": lambda x, w, b, e: (x - _moments(x)[0]) / np.sqrt(_moments(x)[1] / x.shape[-1] + e) * w + b,
+    "rms_norm": lambda x, w, b, e: x / np.sqrt((x * x).mean(-1, keepdims=True) + e) * w,
+    "normalize": lambda x, w, b, e: x / np.maximum(np.sqrt((x * x).sum(-1, keepdims=True)), e),
+}
+ROWWISE_MAPS = ("softmax", "log_softmax", "layer_norm", "rms_norm", "normalize")
+
+
+class RowInterpreter(CellInterpreter):
+    """Runs a row-reduction kernel on a few probe rows, every value a [rows, cols] float64 array (row-level
+    values are constant along a row). A `Loop` over the row's columns runs its body once on whole rows; an `Accum`
+    (emmyptx/kernel.py:786-797) reduces along the row; the `WarpShuffle` / `TreeHalve` that merge the lanes' partial
+    states (:856-900) change nothing once a row is reduced whole, and are skipped."""
+
+    def __init__(self, tensors: dict, rows: np.ndarray, cols: int) -> None:
+        super().__init__(tensors, np.zeros((len(rows), cols), dtype=np.int64), INT_OPS)
+        self.cols = cols
+
+    def run(self, stmts) -> None:
+        for s in stmts:
+            k = _kind(s)
+            if k in ("Loop", "StridedLoop"):
+                if int(s.axis.extent.as_static()) != self.cols:
+                    raise Unmatched("a row kernel loops over the whole row")
+                self.env[s.axis.name] = np.broadcast_to(np.arange(self.cols, dtype=np.int64), self.cells.shape)
+                self.run(s.body)
+            elif k == "Accum":
+                if s.op.name not in _ACCUM:
+                    raise Unmatched(f"no row reduction folds with {s.op.name!r}")
+                red = _ACCUM[s.op.name](np.asarray(self.lookup(s.value), np.float64), axis=1, keepdims=True)
+                base = s.base if s.base is not None else (s.name if s.name in self.env else None)
+                if base is not None:
+                    red = FLOAT_OPS[s.op.name][1](np.asarray(self.lookup(base), np.float64)[:, :1], red)
+                self.env[s.name] = np.broadcast_to(red, self.cells.shape)
+            elif k in ("WarpShuffle", "TreeHalve", "Sync", "Smem", "Init"):
+                continue
+            elif k == "Assign":
+                args = [np.asarray(self.lookup(a), np.float64) for a in s.args]
+                if s.op.name not in FLOAT_OPS:
+                    raise OpError(f"elementwise op {s.op.name!r} is not supported")
+                self.env[s.name] = np.broadcast_to(FLOAT_OPS[s.op.name][1](*args), self.cells.shape)
+            else:
+                super().run([s])
+
+
+def match_rowwise(graph, kernel, launch: dict) -> dict:
+    tensors = tensor_table(graph)
+    tiles = [s for s in kernel.body if _kind(s) == "Tile"]
+    if len(kernel.body) != 1 or len(tiles) != 1:
+        raise Unmatched("a row kernel is one Tile")
+    tile = tiles[0]
+    loops = [s for s in walk(tile.body) if _kind(s) in ("Loop", "StridedLoop")]
+    cols = int(loops[0].axis.extent.as_static())
+    rows = math.prod(int(a.extent.as_static()) for a in tile.axes)
+    probe = np.unique([0, rows // 2, rows - 1]).astype(np.int64)
+    it = RowInterpreter(tensors, probe, cols)
+    rem = np.broadcast_to(probe[:, None], it.cells.shape).copy()
+    for a in reversed(tile.axes):
+        e = int(a.extent.as_static())
+        it.env[a.name] = rem % e
+        rem = rem // e
+    it.run(tile.body)
+    if len(it.writes) != 1 or len(it.writes[0][2]) != 1:
+        raise Unmatched("row kernels write one value to one buffer")
+    out_name, out_idx, (value,) = it.writes[0]
+    # the input is the buffer read as X[row, col]; vectors read as V[col] are weight and bias, in load order
+    element = probe[:, None] * cols + np.arange(cols)[None, :]
+    src = [b for b, i, _ in it.loads if math.prod(tensors[b][0]) == rows * cols and np.array_equal(i, element)]
+    vecs = list(dict.fromkeys(b for b, i, _ in it.loads if math.prod(tensors[b][0]) == cols and b not in src
+                              and np.array_equal(i, np.broadcast_to(np.arange(cols), i.shape))))
+    if len(set(src)) != 1 or len(set(b for b, _, _ in it.loads)) != 1 + len(vecs) or len(vecs) > 2:
+        raise Unmatched("a row kernel reads one [rows, cols] buffer and at most a weight and a bias vector")
+    if any(tensors[b][1] != "f32" for b in (src[0], out_name, *vecs)):
+        raise Unmatched("row kernels are float32")
+    x = probe_values(src[0], "f32", element)
+    w = probe_values(vecs[0], "f32", np.arange(cols))[None, :] if vecs else np.ones((1, cols))
+    b = probe_values(vecs[1], "f32", np.arange(cols))[None, :] if len(vecs) > 1 else np.zeros((1, cols))
+    is_map = math.prod(tensors[out_name][0]) == rows * cols and cols > 1
+    want_idx = element if is_map else np.broadcast_to(probe[:, None], element.shape)
+    if not np.array_equal(out_idx, want_idx):
+        raise Unmatched("a row kernel writes Y[row] or Y[row, col]")
+    got = np.asarray(value, np.float64)
+    literals = sorted({float(a) for s in walk(tile.body) if _kind(s) == "Assign" for a in s.args
+                       if isinstance(a, float) and 0.0 < a < 1e-2}, reverse=True)
+    for op, f in ROWWISE_F64.items():
+        if (op in ROWWISE_MAPS) != is_map or (vecs and op not in ("layer_norm", "rms_norm")) or (len(vecs) > 1 and op != "layer_norm"):
+            continue
+        for eps in (literals + [0.0] if op in ("layer_norm", "rms_norm", "normalize") else [0.0]):
+            with np.errstate(all="ignore"):
+                ref = np.broadcast_to(f(x, w, b, eps), got.shape)
+            if np.allclose(got, ref, rtol=1e-9, atol=1e-12):
+                return {"variant": "rowwise_f32", "inputs": [src[0], *vecs], "outputs": [out_name],
+                        "params": {"op": op, "rows": rows, "cols": cols, "eps": eps, "weight": len(vecs) > 0, "bias": len(vecs) > 1}}
+    raise Unmatched("the row program is none of the reductions or normalisations the library has")
+
+
 def match_kernel(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
     kinds = {_kind(s) for s in walk(kernel.body)}
     if "MmaSyncPtx" in kinds:
         return match_contraction(graph, kernel, launch)
+    if "Accum" in kinds:
+        return match_rowwise(graph, kernel, launch)
     return match_streaming(graph, kernel, launch, int_div)

@@ -121,5 +121,10 @@ def launch(handle: dict, bufs: dict, stream=None) -> None:
         shp = (p["units"], -1, p["d"])
         runtime.attention(ins[0].reshape(shp), ins[1].reshape(shp), ins[2].reshape(shp), scale=p["scale"],
                           causal=p.get("causal", False), out=out.reshape(shp), stream=stream)
+    elif v == "rowwise_f32":
+        x = ins[0].reshape(p["rows"], p["cols"])
+        runtime.rowwise(p["op"], x, ins[1].reshape(-1) if p["weight"] else None, ins[2].reshape(-1) if p["bias"] else None,
+                        p["eps"], out=out.reshape(x.shape if p["op"] in ("softmax", "log_softmax", "layer_norm", "rms_norm", "normalize")
+                                                  else (p["rows"],)), stream=stream)
     else:
         raise RuntimeError(f"unknown kernel variant {v!r}")

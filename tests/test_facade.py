@@ -132,3 +132,34 @@ def test_ir_json_round_trip():
     g2 = ir.Graph.from_dict(json.loads(json.dumps(g.to_dict())))
     assert g2.to_dict() == g.to_dict()
     assert type(g2.nodes["k_gemm"].op).__name__ == "KernelOp"
+
+
+def test_row_reductions_are_matched_by_behaviour():
+    """Every row op the builder can spell is recognised, with its extents and epsilon; a differently arranged program
+    with the same meaning (mean as a division, the variance through E[x^2] - E[x]^2) matches the same kernel."""
+    from emmyptx.ir import Accum, Assign, Axis, Dim, KernelOp, Load, Loop, Op, Tile, Var, Write, _graph, _launch, tensor
+    for op in ("sum", "mean", "amax", "amin", "prod", "var", "std", "norm2", "logsumexp", "softmax", "log_softmax",
+               "layer_norm", "rms_norm", "normalize"):
+        h = handle(ir.rowwise_kernel(op, 48, 256, eps=1e-6))
+        assert h["variant"] == "rowwise_f32" and h["params"]["op"] == op, op
+        assert (h["params"]["rows"], h["params"]["cols"]) == (48, 256)
+    assert handle(ir.rowwise_kernel("layer_norm", 8, 64, eps=1e-3))["params"]["eps"] == 1e-3
+    assert handle(ir.rowwise_kernel("layer_norm", 8, 64))["inputs"] == ["X", "W", "B"]
+    assert algorithmic_work(handle(ir.rowwise_kernel("softmax", 64, 1000))) == (8.0 * 64 * 1000, "B")
+
+    rows, cols = 10, 96
+    r0, c0 = Axis("r0", Dim(rows)), Axis("c0", Dim(cols))
+    ld = Load(["x"], "X", [Var("r0"), Var("c0")])
+    body = [Loop(c0, [ld, Accum("s1", None, "x", Op("add")), Assign("xx", Op("square"), ["x"]), Accum("s2", None, "xx", Op("add"))]),
+            Assign("m", Op("divide"), ["s1", float(cols)]), Assign("mm", Op("multiply"), ["m", "s1"]),
+            Assign("num", Op("subtract"), ["s2", "mm"]), Assign("v", Op("divide"), ["num", float(cols - 1)]),
+            Write("Y", [Var("r0")], ["v"])]
+    k = KernelOp("k_var2", [Tile([r0], body)])
+    g = _graph(k, [tensor("X", [rows, cols], "f32")], [tensor("Y", [rows], "f32")])
+    assert handle((g, k, _launch(k, ["X", "Y"], rows)))["params"]["op"] == "var"
+    # a reduction the library does not have is refused, not approximated
+    body = [Loop(c0, [ld, Assign("a", Op("abs"), ["x"]), Accum("s", None, "a", Op("add"))]), Write("Y", [Var("r0")], ["s"])]
+    k = KernelOp("k_l1", [Tile([r0], body)])
+    g = _graph(k, [tensor("X", [rows, cols], "f32")], [tensor("Y", [rows], "f32")])
+    with pytest.raises(CompileError):
+        handle((g, k, _launch(k, ["X", "Y"], rows)))

@@ -95,6 +95,24 @@ def test_causal_attention_through_the_facade(tmp_path, cuda):
     assert reference.compare(out["O"].reshape(shp).astype(np.float64), ref, 1e-2, 1e-2)["ok"]       # HALF class
 
 
+@pytest.mark.parametrize("op,rows,cols,rtol,atol", [
+    ("mean", 128, 300, 1e-4, 1e-4), ("var", 64, 512, 1e-4, 1e-4), ("logsumexp", 64, 512, 1e-4, 1e-4),
+    ("softmax", 64, 1000, 1e-3, 1e-5), ("layer_norm", 64, 768, 1e-3, 1e-4), ("rms_norm", 32, 512, 1e-3, 1e-4)])
+def test_row_kernels_through_the_facade(tmp_path, cuda, op, rows, cols, rtol, atol):
+    """r_mean_rows, r_var_std, r_logsumexp, f_softmax, f_layer_norm_affine, f_rms_norm (tools/torch_cases/reductions.py,
+    fused.py) at the reference's tolerances."""
+    import torch
+    built = ir.rowwise_kernel(op, rows, cols, eps=1e-5)
+    names = [t for t in built[2]["arg_order"] if t != "Y"]
+    shapes = {"X": [rows, cols], "W": [cols], "B": [cols]}
+    is_map = op in ("softmax", "layer_norm", "rms_norm")
+    out = compile_and_run(tmp_path, built, [{"name": n, "dtype": "f32", "shape": shapes[n], "seed": i} for i, n in enumerate(names)] +
+                          [{"name": "Y", "dtype": "f32", "shape": [rows, cols] if is_map else [rows], "output": True}])
+    t = {n: torch.from_numpy(seeded(i, shapes[n])) for i, n in enumerate(names)}
+    ref = reference.rowwise_reference(op, t["X"], t.get("W"), t.get("B"), 1e-5).numpy()
+    assert reference.compare(out["Y"], ref, rtol, atol)["ok"]
+
+
 def test_kernels_against_the_reference_golden_vectors(cuda):
     """golden.npz is the reference's own PTX executed on these inputs. Integer kernel in the reference's
     (truncating) mode: bit for bit. Float kernels: within the reference's tolerance class of each other."""
