@@ -22,6 +22,8 @@
 #include <limits.h>
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "emmy_math.cuh"
 
@@ -655,4 +657,43 @@ extern "C" int emmyb200_rowwise_f32(int op, const float* x, const float* weight,
     const bool vec = cols % 4 == 0 && aligned(x, 16) && (!is_map(op) || aligned(y, 16)) &&
                      (weight == nullptr || aligned(weight, 16)) && (bias == nullptr || aligned(bias, 16));
     return vec ? dispatch<4>(op, a, workspace, s) : dispatch<1>(op, a, workspace, s);
+}
+
+// ---- the same call with the library's own scratch memory -----------------------------------------------------------
+// Piece states, tickets and row statistics of the split path live in a fixed array in the library's device image
+// instead of caller memory. Its address is looked up once per device; nothing is allocated or freed, here or later.
+namespace emmy {
+namespace {
+constexpr int64_t kStaticScratchBytes = 1 << 20;
+static __device__ __align__(256) unsigned char g_row_scratch[kStaticScratchBytes];
+
+int static_scratch(void** out) {
+    static void* cached[64];
+    static std::mutex lock;
+    int dev = 0;
+    EMMY_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(EMMYB200_ERR_DEVICE, "rowwise_static: device index %d out of range", dev);
+    std::lock_guard<std::mutex> guard(lock);
+    if (cached[dev] == nullptr) EMMY_CUDA(cudaGetSymbolAddress(&cached[dev], g_row_scratch));
+    *out = cached[dev];
+    return EMMYB200_OK;
+}
+}  // namespace
+}  // namespace emmy
+
+extern "C" int64_t emmyb200_rowwise_static_capacity(void) { return emmy::kStaticScratchBytes; }
+
+extern "C" int emmyb200_rowwise_f32_static(int op, const float* x, const float* weight, const float* bias, void* y, int64_t rows,
+                                           int64_t cols, float eps, void* cuda_stream) {
+    using namespace emmy;
+    const int64_t need = emmyb200_rowwise_workspace_bytes(op, rows, cols);
+    if (need > kStaticScratchBytes)
+        return fail(EMMYB200_ERR_SHAPE, "rowwise_static: %lld rows of %lld elements need %lld bytes of scratch, the library holds %lld",
+                    (long long)rows, (long long)cols, (long long)need, (long long)kStaticScratchBytes);
+    void* scratch = nullptr;
+    if (need > 0) {
+        const int rc = static_scratch(&scratch);
+        if (rc != EMMYB200_OK) return rc;
+    }
+    return emmyb200_rowwise_f32(op, x, weight, bias, y, rows, cols, eps, scratch, need > 0 ? kStaticScratchBytes : 0, cuda_stream);
 }

@@ -74,6 +74,9 @@ _SIGNATURES = {
     "emmyb200_rowwise_f32": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                             ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_int64,
                                             ctypes.c_void_p]),
+    "emmyb200_rowwise_static_capacity": (ctypes.c_int64, []),
+    "emmyb200_rowwise_f32_static": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                   ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p]),
     "emmyb200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
 }
 EXPORTS = tuple(_SIGNATURES)

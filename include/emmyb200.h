@@ -186,6 +186,16 @@ int64_t emmyb200_rowwise_workspace_bytes(int op, int64_t rows, int64_t cols);
 int emmyb200_rowwise_f32(int op, const float* x, const float* weight, const float* bias, void* y, int64_t rows,
                          int64_t cols, float eps, void* workspace, int64_t workspace_bytes, void* cuda_stream);
 
+/* emmyb200_rowwise_f32 without a workspace argument and without any allocation: the scratch memory of long rows is
+ * a fixed array inside the library's device image (emmyb200_rowwise_static_capacity() bytes per device). Shapes
+ * whose emmyb200_rowwise_workspace_bytes() exceeds the capacity are rejected with EMMYB200_ERR_SHAPE; all others
+ * behave exactly as emmyb200_rowwise_f32. Calls on one device share the array, so they must be ordered (one
+ * stream, or events between streams). These two entry points have no counterpart in the reference, whose kernels
+ * never use scratch memory beyond their own shared memory. */
+int64_t emmyb200_rowwise_static_capacity(void);
+int emmyb200_rowwise_f32_static(int op, const float* x, const float* weight, const float* bias, void* y, int64_t rows,
+                                int64_t cols, float eps, void* cuda_stream);
+
 /* Reads (and clears) the device status word of the current device: 0 if no bounded wait has
  * expired since the last call, else a code naming kernel, role and pipeline stage.
  * Synchronises the device. */
