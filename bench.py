@@ -578,6 +578,13 @@ def other_workloads(torch, dist, dev, pk, skip: str) -> dict:
                              "frac_of_peak": 8.0 * n / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
     except Exception as e:  # noqa: BLE001
         out["c1_at_2^28"] = {"error": str(e)[:200]}
+    # the reference's own kernels (its compiler's PTX for C1 and C2, committed as text fixtures) JIT-loaded on this GPU
+    # and timed next to ours on the same buffers. The GEMM and attention configurations are left out: their PTX
+    # depends on a schedule (tiling, staging) that the reference's tracer chooses and that is not available here.
+    try:
+        out["reference_ptx_on_this_gpu"] = reference_ptx_timings(torch, dist, dev)
+    except Exception as e:  # noqa: BLE001
+        out["reference_ptx_on_this_gpu"] = {"error": f"{type(e).__name__}: {e}"[:200]}
     # the rows built after the five configurations: row kernels (256 MiB of fp32, larger than L2) and causal attention
     try:
         from emmyptx import runtime
@@ -598,6 +605,37 @@ def other_workloads(torch, dist, dev, pk, skip: str) -> dict:
     except Exception as e:  # noqa: BLE001
         out["next_rows"] = {"error": str(e)[:200]}
     return out
+
+
+def reference_ptx_timings(torch, dist, dev) -> dict:
+    import json as _json
+    from emmyptx import runtime
+    from emmyptx.ptx_driver import PtxModule
+    golden = ROOT / "tests" / "golden"
+    manifest = _json.loads((golden / "reference_ptx_manifest.json").read_text())
+    res = {}
+    cases = [("c1_2^20", "c1_exp_sin_tanh_n1048576", torch.float32, lambda x, y: runtime.pointwise("exp_sin_tanh", x, out=y)),
+             ("c1_2^28", "c1_exp_sin_tanh_n268435456", torch.float32, lambda x, y: runtime.pointwise("exp_sin_tanh", x, out=y)),
+             ("c2_2^26", "c2_gather_n67108864", torch.int32, lambda x, y: runtime.index_gather(x, 7919, 13, 3, 2, trunc=True, out=y))]
+    for label, case, dtype, ours in cases:
+        info = manifest[case]
+        n = info["tensors"]["x"]["shape"][0]
+        x = (torch.rand(n, device=dev) * 8 - 4) if dtype == torch.float32 else torch.randint(-2**30, 2**30, (n,), device=dev, dtype=dtype)
+        y_ref, y_ours = torch.zeros_like(x), torch.zeros_like(x)
+        with PtxModule((golden / f"{case}.ref.ptx").read_text()) as m:
+            fn = m.function(info["entry"])
+            grid, block = info["launch"]["grid"][0], info["launch"]["block"][0]
+            ptrs = [x.data_ptr(), y_ref.data_ptr()]
+            ref = lambda: m.launch(fn, ptrs, grid, block, stream=torch.cuda.current_stream().cuda_stream)
+            # kernels of a few microseconds: both sides inside a CUDA graph, so that neither host path is measured
+            ms_ref = graph_timed(torch, ref, 50) if n <= 2**22 else timed(torch, dist, 1, ref, 5, 3) / 5
+        ms_ours = graph_timed(torch, lambda: ours(x, y_ours), 50) if n <= 2**22 else timed(torch, dist, 1, lambda: ours(x, y_ours), 5, 3) / 5
+        same = bool(torch.equal(y_ref, y_ours)) if dtype == torch.int32 else bool(torch.allclose(y_ref, y_ours, rtol=1e-5, atol=1e-5))
+        res[label] = {"reference_kernel_ms": ms_ref, "this_library_ms": ms_ours, "speedup": ms_ref / ms_ours,
+                      "reference_GBps": 8.0 * n / (ms_ref * 1e-3) / 1e9, "outputs_agree": same}
+        del x, y_ref, y_ours
+        torch.cuda.empty_cache()
+    return res
 
 
 if __name__ == "__main__":

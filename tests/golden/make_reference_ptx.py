@@ -32,6 +32,9 @@ CASES = {
     "p_sin_n4096": ir.pointwise_kernel(4096, "sin", name="p_sin_n4096"),
     "c2_gather_n65536": ir.index_gather_kernel(2**16, name="c2_gather_n65536"),
     "c2_gather_n1048576": ir.index_gather_kernel(2**20, name="c2_gather_n1048576"),
+    # full-size kernels, only ever timed on the device next to ours (no CPU golden vectors at these sizes)
+    "c2_gather_n67108864": ir.index_gather_kernel(2**26, name="c2_gather_n67108864"),
+    "c1_exp_sin_tanh_n268435456": ir.pointwise_kernel(2**28, "exp_sin_tanh", name="c1_exp_sin_tanh_n268435456"),
 }
 
 manifest = {}

@@ -5,7 +5,6 @@ JIT-loaded on this GPU through the driver API, as the reference's runner does (t
 The reference text targets sm_89; the driver JITs it forward. Only the two streaming kernels are run: straight
 line code with in-range addresses by construction (grid * block == n, indices masked to n - 1).
 """
-import ctypes
 import json
 from pathlib import Path
 
@@ -18,27 +17,11 @@ pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
-class Driver:
-    def __init__(self):
-        self.cu = ctypes.CDLL("libcuda.so.1")
-
-    def check(self, err, what):
-        if err:
-            msg = ctypes.c_char_p()
-            self.cu.cuGetErrorString(err, ctypes.byref(msg))
-            raise RuntimeError(f"{what}: {msg.value.decode() if msg.value else err}")
-
-    def run(self, ptx: str, entry: str, ptrs: list, grid: int, block: int):
-        module, fn = ctypes.c_void_p(), ctypes.c_void_p()
-        self.check(self.cu.cuModuleLoadData(ctypes.byref(module), ptx.encode() + b"\0"), "cuModuleLoadData")
-        try:
-            self.check(self.cu.cuModuleGetFunction(ctypes.byref(fn), module, entry.encode()), "cuModuleGetFunction")
-            holders = [ctypes.c_uint64(p) for p in ptrs]
-            params = (ctypes.c_void_p * len(holders))(*[ctypes.cast(ctypes.byref(h), ctypes.c_void_p) for h in holders])
-            self.check(self.cu.cuLaunchKernel(fn, grid, 1, 1, block, 1, 1, 0, None, params, None), "cuLaunchKernel")
-            self.check(self.cu.cuCtxSynchronize(), "cuCtxSynchronize")
-        finally:
-            self.cu.cuModuleUnload(module)
+def run_ptx(ptx: str, entry: str, ptrs: list, grid: int, block: int) -> None:
+    from emmyptx.ptx_driver import PtxModule
+    with PtxModule(ptx) as m:
+        m.launch(m.function(entry), ptrs, grid, block)
+        m.synchronize()
 
 
 @pytest.fixture(scope="module")
@@ -51,8 +34,8 @@ def _reference_kernel(case, manifest, x_dev, cuda):
     torch.cuda.synchronize()
     info = manifest[case]
     y = torch.zeros_like(x_dev)                      # outputs start zeroed (tools/run_local.py:92-93)
-    Driver().run((GOLDEN / f"{case}.ref.ptx").read_text(), info["entry"], [x_dev.data_ptr(), y.data_ptr()],
-                 info["launch"]["grid"][0], info["launch"]["block"][0])
+    run_ptx((GOLDEN / f"{case}.ref.ptx").read_text(), info["entry"], [x_dev.data_ptr(), y.data_ptr()],
+            info["launch"]["grid"][0], info["launch"]["block"][0])
     return y
 
 
