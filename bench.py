@@ -37,7 +37,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # under profiles/ (c4: captured at M=N=K=8192 and scaled by the 8x flops of the full size; c5: captured on 64 of the 256
 # units and scaled by 4; c2, c3: captured at full size; c1: 8 MiB working set, L2-resident, no DRAM figure).
 DRAM_TRAFFIC = {"c4": 8 * (1.026722e9 + 0.129173e9), "c5": 4 * (201.38e6 + 49.46e6), "c2": 268.97e6 + 222.76e6,
-                "c3": 83.01e6 + 14.28e6, "c1": None}
+                "c3": 83.01e6 + 14.28e6, "c1": None, "softmax": None}
 
 WORKLOADS = {
     "c1": "fp32 exp(x)+sin(x)*tanh(x), N=2^20, x~U[-4,4]",
@@ -45,6 +45,7 @@ WORKLOADS = {
     "c3": "fp16 GEMM M=N=K=4096, fp32 accumulate, fp16 out",
     "c4": "bf16 GEMM + tanh-GELU epilogue M=N=K=16384, fp32 accumulate, bf16 out, M-row shards",
     "c5": "bf16 attention fwd B16 H16 S4096 d128, non-causal, fp32 softmax, (batch x head) shards",
+    "softmax": "fp32 softmax over the last axis of [65536, 1024] (the row kernels; not one of the five configurations)",
 }
 
 
@@ -227,6 +228,25 @@ class PointwiseWorkload(Workload):
         self.host["y"].copy_(self.y, non_blocking=True)
 
 
+class RowWorkload(PointwiseWorkload):
+    """A row kernel on [rows, 1024] fp32; `n` counts elements. Rows shard across ranks like C1's chunks."""
+
+    def __init__(self, op, n, rank, world, dev):
+        import torch
+        from emmyptx import runtime
+        self.rt, self.torch, self.world = runtime, torch, world
+        self.name, self.op, self.n = op, op, n
+        g = torch.Generator(device=dev)
+        g.manual_seed(rank)
+        self.x = torch.randn(n // 1024, 1024, device=dev, generator=g)
+        self.y = torch.empty_like(self.x)
+
+    def step(self):
+        self.rt.rowwise(self.op, self.x, out=self.y)
+
+    kernel_only = step
+
+
 class GatherWorkload(PointwiseWorkload):
     dtype = "i32"
 
@@ -325,6 +345,8 @@ def make_workload(name, rank, world, dev, size=None):
         return PointwiseWorkload(size or 2**20, rank, world, dev)
     if name == "c2":
         return GatherWorkload(size or 2**26, rank, world, dev)
+    if name == "softmax":
+        return RowWorkload("softmax", size or 65536 * 1024, rank, world, dev)
     raise SystemExit(f"unknown workload {name!r}")
 
 
@@ -413,6 +435,10 @@ def cpu_reference_step(name: str, threads: int):
         x = torch.from_numpy(inputs.c2_input(n))
         fn = lambda: reference.c2_torch(x)
         return fn, 8.0 * n, 1e9, "the full 2^26 array, torch CPU int32/int64"
+    if name == "softmax":
+        x = torch.randn(65536, 1024, generator=torch.Generator().manual_seed(0))
+        fn = lambda: torch.softmax(x, -1)
+        return fn, 8.0 * x.numel(), 1e9, "the full [65536, 1024] array, torch CPU fp32"
     raise SystemExit(name)
 
 
@@ -444,11 +470,12 @@ def run_reference(args, rank: int) -> int:
     w0 = WORKLOADS[args.workload]
     value = work * args.steps / dt / scale
     unit = "TFLOP/s" if scale == 1e12 else "GB/s"
-    metric = {"c1": "elementwise_gbs", "c2": "elementwise_gbs", "c5": "attention_tflops"}.get(args.workload, "gemm_tflops")
+    metric = {"c1": "elementwise_gbs", "c2": "elementwise_gbs", "softmax": "elementwise_gbs",
+              "c5": "attention_tflops"}.get(args.workload, "gemm_tflops")
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": {"c1": "f32", "c2": "i32", "c3": "f16"}.get(args.workload, "bf16"), "data": "synthetic",
+        "vs_baseline": None, "dtype": {"c1": "f32", "c2": "i32", "c3": "f16", "softmax": "f32"}.get(args.workload, "bf16"), "data": "synthetic",
         "config": {"workload": w0, "note": "each step is a bounded sample of the workload on the host cores"},
         "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "reference", "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -551,7 +578,7 @@ def other_workloads(torch, dist, dev, pk, skip: str) -> dict:
     """Short device-resident measurements of the remaining configurations (1 GPU), each with its roofline
     fraction; kernels of a few microseconds are timed inside a CUDA graph."""
     out = {}
-    for name in WORKLOADS:
+    for name in ("c1", "c2", "c3", "c4", "c5"):
         if name == skip:
             continue
         try:
