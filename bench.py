@@ -36,8 +36,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each workload's kernel, from the ncu captures summarised
 # under profiles/ (c4: captured at M=N=K=8192 and scaled by the 8x flops of the full size; c5: captured on 64 of the 256
 # units and scaled by 4; c2, c3: captured at full size; c1: 8 MiB working set, L2-resident, no DRAM figure).
-DRAM_TRAFFIC = {"c4": 8 * (1.026722e9 + 0.129173e9), "c5": 4 * (201.38e6 + 49.46e6), "c2": 268.97e6 + 222.76e6,
-                "c3": 83.01e6 + 14.28e6, "c1": None, "softmax": None}
+DRAM_TRAFFIC = {"c4": 8 * (1.018008e9 + 0.125913e9), "c5": 4 * (201.44e6 + 49.98e6), "c2": 268.97e6 + 222.76e6,
+                "c3": 83.01e6 + 14.28e6, "c1": None, "softmax": 268.46e6 + 216.40e6}
 
 WORKLOADS = {
     "c1": "fp32 exp(x)+sin(x)*tanh(x), N=2^20, x~U[-4,4]",
