@@ -366,6 +366,23 @@ def index_gather_kernel(n: int, mul: int = 7919, add: int = 13, div: int = 3, sh
     return g, k, _launch(k, ["x", "y"], n)
 
 
+def colwise_kernel(op: str, rows: int, cols: int, eps: float = 1e-12, name: str = "k_colwise"):
+    """The same statement shapes for a reduction over dim 0 of X[rows, cols]: one tile cell per column, the loop walks
+    the rows (tools/torch_cases/reductions.py:9 `x.sum(0)`, fused.py:7 `softmax(x, 0)`)."""
+    g, kern, launch = rowwise_kernel(op, cols, rows, eps, name)          # cells = columns, loop length = rows
+
+    def swap(stmts):
+        for s in stmts:
+            if isinstance(s, (Load, Write)) and len(s.index) == 2:
+                s.index = [s.index[1], s.index[0]]
+            if isinstance(s, Loop):
+                swap(s.body)
+    swap(kern.body[0].body)
+    is_map = op in ("softmax", "log_softmax", "normalize")
+    g = _graph(kern, [tensor("X", [rows, cols], "f32")], [tensor("Y", [rows, cols] if is_map else [cols], "f32")])
+    return g, kern, launch
+
+
 def rowwise_kernel(op: str, rows: int, cols: int, eps: float = 1e-5, name: str = "k_rowwise"):
     """A reduction over the last axis of X[rows, cols] (or a normalisation built on one) in the statement shapes the
     reference lowers (emmyptx/kernel.py:786-797 `Accum` inside a `Loop`, :856-866 `WarpShuffle` to merge lanes): one tile

@@ -103,4 +103,8 @@ def algorithmic_work(handle: dict) -> tuple[float, str]:
     if v == "rowwise_f32":
         is_map = p["op"] in ("softmax", "log_softmax", "layer_norm", "rms_norm", "normalize")
         return 4.0 * p["rows"] * (p["cols"] * (2 if is_map else 1) + (0 if is_map else 1)), "B"
+    if v == "colwise_f32":
+        is_map = p["op"] in ("softmax", "log_softmax", "normalize")
+        n = p["outer"] * p["rows"] * p["cols"]
+        return 4.0 * (n * (2 if is_map else 1) + (0 if is_map else p["outer"] * p["cols"])), "B"
     raise CompileError(f"unknown variant {v!r}")

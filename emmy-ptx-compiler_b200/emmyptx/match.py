@@ -563,32 +563,44 @@ def match_rowwise(graph, kernel, launch: dict) -> dict:
     if len(it.writes) != 1 or len(it.writes[0][2]) != 1:
         raise Unmatched("row kernels write one value to one buffer")
     out_name, out_idx, (value,) = it.writes[0]
-    # the input is the buffer read as X[row, col]; vectors read as V[col] are weight and bias, in load order
-    element = probe[:, None] * cols + np.arange(cols)[None, :]
-    src = [b for b, i, _ in it.loads if math.prod(tensors[b][0]) == rows * cols and np.array_equal(i, element)]
+    # The input is read either as X[cell, k] (a reduction over the last axis) or as X[k, cell] (over dim 0), k being the
+    # loop variable; vectors read as V[k] are weight and bias, in load order (last-axis form only).
+    along_last = probe[:, None] * cols + np.arange(cols)[None, :]
+    along_first = np.arange(cols)[None, :] * rows + probe[:, None]
+    big = [(b, i) for b, i, _ in it.loads if math.prod(tensors[b][0]) == rows * cols]
+    if not big:
+        raise Unmatched("a reduction kernel reads one buffer of cells x loop-length elements")
+    over_dim0 = rows > 1 and all(np.array_equal(i, along_first) for _, i in big)
+    element = along_first if over_dim0 else along_last
+    src = [b for b, i in big if np.array_equal(i, element)]
     vecs = list(dict.fromkeys(b for b, i, _ in it.loads if math.prod(tensors[b][0]) == cols and b not in src
                               and np.array_equal(i, np.broadcast_to(np.arange(cols), i.shape))))
-    if len(set(src)) != 1 or len(set(b for b, _, _ in it.loads)) != 1 + len(vecs) or len(vecs) > 2:
-        raise Unmatched("a row kernel reads one [rows, cols] buffer and at most a weight and a bias vector")
+    if len(set(src)) != 1 or len(set(b for b, _, _ in it.loads)) != 1 + len(vecs) or len(vecs) > 2 or (vecs and over_dim0):
+        raise Unmatched("a reduction kernel reads one buffer and, over the last axis, at most a weight and a bias vector")
     if any(tensors[b][1] != "f32" for b in (src[0], out_name, *vecs)):
-        raise Unmatched("row kernels are float32")
+        raise Unmatched("reduction kernels are float32")
     x = probe_values(src[0], "f32", element)
     w = probe_values(vecs[0], "f32", np.arange(cols))[None, :] if vecs else np.ones((1, cols))
     b = probe_values(vecs[1], "f32", np.arange(cols))[None, :] if len(vecs) > 1 else np.zeros((1, cols))
     is_map = math.prod(tensors[out_name][0]) == rows * cols and cols > 1
     want_idx = element if is_map else np.broadcast_to(probe[:, None], element.shape)
     if not np.array_equal(out_idx, want_idx):
-        raise Unmatched("a row kernel writes Y[row] or Y[row, col]")
+        raise Unmatched("a reduction kernel writes one value per cell, or one per element in the input's layout")
     got = np.asarray(value, np.float64)
     literals = sorted({float(a) for s in walk(tile.body) if _kind(s) == "Assign" for a in s.args
                        if isinstance(a, float) and 0.0 < a < 1e-2}, reverse=True)
     for op, f in ROWWISE_F64.items():
         if (op in ROWWISE_MAPS) != is_map or (vecs and op not in ("layer_norm", "rms_norm")) or (len(vecs) > 1 and op != "layer_norm"):
             continue
+        if over_dim0 and op in ("layer_norm", "rms_norm"):
+            continue
         for eps in (literals + [0.0] if op in ("layer_norm", "rms_norm", "normalize") else [0.0]):
             with np.errstate(all="ignore"):
                 ref = np.broadcast_to(f(x, w, b, eps), got.shape)
             if np.allclose(got, ref, rtol=1e-9, atol=1e-12):
+                if over_dim0:
+                    return {"variant": "colwise_f32", "inputs": [src[0]], "outputs": [out_name],
+                            "params": {"op": op, "outer": 1, "rows": cols, "cols": rows, "eps": eps}}
                 return {"variant": "rowwise_f32", "inputs": [src[0], *vecs], "outputs": [out_name],
                         "params": {"op": op, "rows": rows, "cols": cols, "eps": eps, "weight": len(vecs) > 0, "bias": len(vecs) > 1}}
     raise Unmatched("the row program is none of the reductions or normalisations the library has")

@@ -126,5 +126,9 @@ def launch(handle: dict, bufs: dict, stream=None) -> None:
         runtime.rowwise(p["op"], x, ins[1].reshape(-1) if p["weight"] else None, ins[2].reshape(-1) if p["bias"] else None,
                         p["eps"], out=out.reshape(x.shape if p["op"] in ("softmax", "log_softmax", "layer_norm", "rms_norm", "normalize")
                                                   else (p["rows"],)), stream=stream)
+    elif v == "colwise_f32":
+        x = ins[0].reshape(p["outer"], p["rows"], p["cols"])
+        is_map = p["op"] in ("softmax", "log_softmax", "normalize")
+        runtime.colwise(p["op"], x, p["eps"], out=out.reshape(x.shape if is_map else (p["outer"], p["cols"])), stream=stream)
     else:
         raise RuntimeError(f"unknown kernel variant {v!r}")

@@ -74,6 +74,10 @@ _SIGNATURES = {
     "emmyb200_rowwise_f32": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                             ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_int64,
                                             ctypes.c_void_p]),
+    "emmyb200_colwise_workspace_bytes": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64]),
+    "emmyb200_colwise_f32": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                            ctypes.c_float, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]),
+    "emmyb200_cumsum_f32": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),
     "emmyb200_rowwise_static_capacity": (ctypes.c_int64, []),
     "emmyb200_rowwise_f32_static": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                    ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p]),
@@ -288,6 +292,48 @@ def rowwise(op: str, x, weight=None, bias=None, eps: float = 0.0, out=None, work
                                    bias.data_ptr() if bias is not None else None, out.data_ptr(), rows, cols, eps,
                                    workspace.data_ptr() if workspace is not None else None,
                                    workspace.numel() if workspace is not None else 0, _stream(stream)))
+    return out
+
+
+COL_OPS = ("sum", "mean", "amax", "amin", "prod", "var", "std", "norm2", "logsumexp", "argmax", "softmax", "log_softmax", "normalize")
+
+
+def colwise(op: str, x, eps: float = 0.0, out=None, workspace=None, stream=None):
+    """Reduce (or normalise) axis -2 of a contiguous float32 CUDA tensor of 2 or more axes: a [rows, cols] matrix over
+    dim 0, a [..., rows, cols] stack plane by plane. `op` is one of COL_OPS."""
+    import torch
+    _need_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() < 2:
+        raise TypeError("colwise: a contiguous float32 tensor with at least two axes")
+    if op not in COL_OPS:
+        raise KeyError(op)
+    code = ROW_OPS[op]
+    rows, cols = x.shape[-2], x.shape[-1]
+    outer = x.numel() // (rows * cols) if rows * cols else 0
+    if out is None:
+        out = (torch.empty_like(x) if code >= ROW_MAP_FIRST else
+               torch.empty((*x.shape[:-2], cols), dtype=torch.int64 if op == "argmax" else torch.float32, device=x.device))
+    _need_cuda(out)
+    lib = library()
+    need = lib.emmyb200_colwise_workspace_bytes(code, outer, rows, cols)
+    if need > 0 and (workspace is None or workspace.numel() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    check(lib.emmyb200_colwise_f32(code, x.data_ptr(), out.data_ptr(), outer, rows, cols, eps,
+                                   workspace.data_ptr() if workspace is not None else None,
+                                   workspace.numel() if workspace is not None else 0, _stream(stream)))
+    return out
+
+
+def cumsum(x, out=None, stream=None):
+    """Running sum along the last axis of a contiguous float32 CUDA tensor."""
+    import torch
+    _need_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() < 1:
+        raise TypeError("cumsum: a contiguous float32 tensor with at least one axis")
+    out = torch.empty_like(x) if out is None else out
+    _need_cuda(out)
+    cols = x.shape[-1]
+    check(library().emmyb200_cumsum_f32(x.data_ptr(), out.data_ptr(), x.numel() // cols if cols else 0, cols, _stream(stream)))
     return out
 
 

@@ -186,6 +186,21 @@ int64_t emmyb200_rowwise_workspace_bytes(int op, int64_t rows, int64_t cols);
 int emmyb200_rowwise_f32(int op, const float* x, const float* weight, const float* bias, void* y, int64_t rows,
                          int64_t cols, float eps, void* workspace, int64_t workspace_bytes, void* cuda_stream);
 
+/* The same reductions over the middle axis of a contiguous fp32 [outer, rows, cols] array (outer = 1: over dim 0 of a
+ * matrix, tools/torch_cases/reductions.py:9, fused.py:7; a sum over several axes is a row pass followed by this
+ * one, reductions.py:10). Ops: the reducing ones (y: float[outer, cols]; ARGMAX: int64_t[outer, cols], the row
+ * index) and SOFTMAX, LOG_SOFTMAX, NORMALIZE (y: float[outer, rows, cols]). Tall arrays are cut into row slices
+ * handled by different thread blocks, and mapping ops keep per-column statistics: both need
+ * emmyb200_colwise_workspace_bytes(op, outer, rows, cols) bytes of 256-byte-aligned device memory (possibly 0;
+ * -1 for arguments the call would reject). outer <= 65535, 1 <= rows, cols < 2^31. */
+int64_t emmyb200_colwise_workspace_bytes(int op, int64_t outer, int64_t rows, int64_t cols);
+int emmyb200_colwise_f32(int op, const float* x, void* y, int64_t outer, int64_t rows, int64_t cols, float eps,
+                         void* workspace, int64_t workspace_bytes, void* cuda_stream);
+
+/* y[r, c] = x[r, 0] + ... + x[r, c] over a contiguous fp32 [rows, cols] array (torch.cumsum(x, -1),
+ * tools/torch_cases/reductions.py:18). x and y may be the same buffer. */
+int emmyb200_cumsum_f32(const float* x, float* y, int64_t rows, int64_t cols, void* cuda_stream);
+
 /* emmyb200_rowwise_f32 without a workspace argument and without any allocation: the scratch memory of long rows is
  * a fixed array inside the library's device image (emmyb200_rowwise_static_capacity() bytes per device). Shapes
  * whose emmyb200_rowwise_workspace_bytes() exceeds the capacity are rejected with EMMYB200_ERR_SHAPE; all others

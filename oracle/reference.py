@@ -137,6 +137,19 @@ def rowwise_reference(op: str, x, weight=None, bias=None, eps: float = 0.0):
     raise KeyError(op)
 
 
+def colwise_reference(op: str, x, eps: float = 0.0):
+    """The same ops over axis -2 (dim 0 of a matrix; tools/torch_cases/reductions.py:9, fused.py:7), float64."""
+    import torch
+    y = rowwise_reference(op, x.transpose(-1, -2), eps=eps)
+    return y.transpose(-1, -2) if y.dim() == x.dim() else y
+
+
+def cumsum_reference(x):
+    """torch.cumsum(x, -1) in float64 (tools/torch_cases/reductions.py:18)."""
+    import torch
+    return torch.cumsum(x.double(), -1)
+
+
 # ---- the reference harness's comparison -----------------------------------------------------------------
 def compare(got: np.ndarray, ref: np.ndarray, rtol: float, atol: float) -> dict:
     """`tools/check_torch.py:260-278`: isclose with equal NaNs, plus the vacuity check (an all-zero

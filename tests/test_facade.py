@@ -147,6 +147,12 @@ def test_row_reductions_are_matched_by_behaviour():
     assert handle(ir.rowwise_kernel("layer_norm", 8, 64))["inputs"] == ["X", "W", "B"]
     assert algorithmic_work(handle(ir.rowwise_kernel("softmax", 64, 1000))) == (8.0 * 64 * 1000, "B")
 
+    # the same programs walking dim 0 instead of the last axis go to the column kernels
+    for op in ("sum", "amax", "var", "logsumexp", "softmax", "normalize"):
+        h = handle(ir.colwise_kernel(op, 256, 64))
+        assert h["variant"] == "colwise_f32" and h["params"]["op"] == op, op
+        assert (h["params"]["outer"], h["params"]["rows"], h["params"]["cols"]) == (1, 256, 64)
+
     rows, cols = 10, 96
     r0, c0 = Axis("r0", Dim(rows)), Axis("c0", Dim(cols))
     ld = Load(["x"], "X", [Var("r0"), Var("c0")])

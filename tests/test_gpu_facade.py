@@ -113,6 +113,18 @@ def test_row_kernels_through_the_facade(tmp_path, cuda, op, rows, cols, rtol, at
     assert reference.compare(out["Y"], ref, rtol, atol)["ok"]
 
 
+@pytest.mark.parametrize("op,rtol,atol", [("sum", 1e-4, 1e-4), ("softmax", 1e-3, 1e-5)])
+def test_dim0_kernels_through_the_facade(tmp_path, cuda, op, rtol, atol):
+    """r_sum_dim0 and f_softmax_dim0 (tools/torch_cases/reductions.py:9, fused.py:7)."""
+    import torch
+    rows, cols = 256, 64
+    out_shape = [rows, cols] if op == "softmax" else [cols]
+    out = compile_and_run(tmp_path, ir.colwise_kernel(op, rows, cols), [
+        {"name": "X", "dtype": "f32", "shape": [rows, cols], "seed": 0}, {"name": "Y", "dtype": "f32", "shape": out_shape, "output": True}])
+    x = torch.from_numpy(seeded(0, [rows, cols]))
+    assert reference.compare(out["Y"], reference.colwise_reference(op, x).numpy(), rtol, atol)["ok"]
+
+
 def test_kernels_against_the_reference_golden_vectors(cuda):
     """golden.npz is the reference's own PTX executed on these inputs. Integer kernel in the reference's
     (truncating) mode: bit for bit. Float kernels: within the reference's tolerance class of each other."""
