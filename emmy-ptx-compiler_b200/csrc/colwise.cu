@@ -8,7 +8,7 @@
 //   * colwise_kernel: a CTA is 32 column lanes (one 128-bit load each, so a warp reads 512 contiguous bytes of a row)
 //     by 8 row lanes; it folds a slice of the rows for 128 columns, the 8 row lanes merge through shared memory, and
 //     when the rows were split over several CTAs the slice states go to workspace memory and the CTA that draws the
-//     last ticket of its column tile merges them in slice order (no CTA waits for another; the result does not
+//     last ticket of its column tile merges them in a fixed order (no CTA waits for another; the result does not
 //     depend on block scheduling). The states are those of the row kernels (reduce_state.cuh).
 //   * colwise_map_kernel: the second pass of softmax / log-softmax / normalise over that axis.
 //   * cumsum_kernel: a group of 32 or 256 threads streams a row slab by slab (128-bit accesses), scanning inside a
@@ -30,7 +30,7 @@ __device__ __forceinline__ void st_push(St& s, float x, int idx, float shift) {
     else if constexpr (K == K_MAX) s.a = nan_max(s.a, x);
     else if constexpr (K == K_MIN) s.a = nan_min(s.a, x);
     else if constexpr (K == K_MUL) s.a *= x;
-    else if constexpr (K == K_MOM) { const float d = x - shift; s.a += 1.0f; s.b += d; s.c = fmaf(d, d, s.c); }
+    else if constexpr (K == K_MOM) { const float d = x - shift; s.b += d; s.c = fmaf(d, d, s.c); }      // the count is set by the caller
     else if constexpr (K == K_LSE) {
         if (x > s.a || x != x) {                            // a new maximum: rescale what was summed so far
             s.b = (s.a == -CUDART_INF_F ? 0.0f : s.b * exp_le0(s.a - x)) + exp_le0(x - x);      // 1, or NaN for an infinity, as torch
@@ -87,28 +87,33 @@ __global__ void __launch_bounds__(kColThreads) colwise_kernel(ColArgs a, float4*
     }
     if (in_cols) {
         constexpr int kTrip = 4;                                // rows in flight per thread
-        for (int64_t r = r_begin + ry; r < r_end; r += kRowLanes * kTrip) {
+        const int rb = (int)r_begin, re = (int)r_end;           // rows < 2^31
+        for (int r = rb + ry; r < re; r += kRowLanes * kTrip) {
             float v[kTrip][VEC];
+            const float* row = base + (int64_t)r * a.cols;
 #pragma unroll
             for (int k = 0; k < kTrip; ++k) {
-                const int64_t rr = r + k * kRowLanes;
-                if (rr < r_end) {
+                if (r + k * kRowLanes < re) {
                     if constexpr (VEC == 4) {
-                        const float4 q = __ldcs(reinterpret_cast<const float4*>(base + rr * a.cols));
+                        const float4 q = __ldcs(reinterpret_cast<const float4*>(row + (int64_t)k * kRowLanes * a.cols));
                         v[k][0] = q.x; v[k][1] = q.y; v[k][2] = q.z; v[k][3] = q.w;
                     } else {
-                        v[k][0] = __ldcs(base + rr * a.cols);
+                        v[k][0] = __ldcs(row + (int64_t)k * kRowLanes * a.cols);
                     }
                 }
             }
 #pragma unroll
             for (int k = 0; k < kTrip; ++k) {
-                const int64_t rr = r + k * kRowLanes;
-                if (rr < r_end) {
+                if (r + k * kRowLanes < re) {
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) st_push<K>(s[e], v[k][e], (int)rr, shift[e]);
+                    for (int e = 0; e < VEC; ++e) st_push<K>(s[e], v[k][e], r + k * kRowLanes, shift[e]);
                 }
             }
+        }
+        if constexpr (K == K_MOM) {                             // rows rb + ry, rb + ry + 8, ... below re
+            const int mine = re - rb > ry ? (re - rb - ry + kRowLanes - 1) / kRowLanes : 0;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) s[e].a = (float)mine;
         }
     }
     // the 8 row lanes of a column merge in lane order (lane ry holds rows ry, ry + 8, ...: for argmax the merge
@@ -146,13 +151,30 @@ __global__ void __launch_bounds__(kColThreads) colwise_kernel(ColArgs a, float4*
         __syncthreads();
         if (!is_last) return;
         __threadfence();
-        if (ry == 0 && in_cols) {
+        // The slices are merged in a fixed order whichever CTA does it: row lane ry folds slices ry, ry + 8, ..., then
+        // the eight lanes fold through shared memory as above.
+        St t[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) t[e] = st_identity<K>();
+        if (in_cols) {
+            for (int sp = ry; sp < a.splits; sp += kRowLanes) {
+                const float4* src = partials + (o * a.splits + sp) * a.cols + col0;
+                float4 f[VEC];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) f[e] = __ldcg(src + e);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) t[e] = st_merge<K>(t[e], St{f[e].x, f[e].y, f[e].z});
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) slab[ry][cx * VEC + e] = make_float4(t[e].a, t[e].b, t[e].c, 0.0f);
+        __syncthreads();
+        if (ry == 0) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
-                m[e] = st_identity<K>();
-                if constexpr (K == K_MOM) m[e] = St{0.0f, 0.0f, 0.0f};
-                for (int sp = 0; sp < a.splits; ++sp) {
-                    const float4 f = __ldcg(partials + (o * a.splits + sp) * a.cols + col0 + e);
+                m[e] = St{slab[0][cx * VEC + e].x, slab[0][cx * VEC + e].y, slab[0][cx * VEC + e].z};
+                for (int l = 1; l < kRowLanes; ++l) {
+                    const float4 f = slab[l][cx * VEC + e];
                     m[e] = st_merge<K>(m[e], St{f.x, f.y, f.z});
                 }
             }
@@ -265,10 +287,10 @@ ColPlan plan_cols(int op, int64_t outer, int64_t rows, int64_t cols, int vec) {
     ColPlan p;
     p.col_tiles = (cols + kColLanes * vec - 1) / (kColLanes * vec);
     const int64_t ctas = p.col_tiles * outer;
-    int64_t want = (4 * (int64_t)sm_count() + ctas - 1) / ctas;          // enough CTAs to fill the GPU a few times
+    int64_t want = (6 * (int64_t)sm_count() + ctas - 1) / ctas;          // enough CTAs to fill the GPU a few times
     const int64_t most = rows / 64 > 0 ? rows / 64 : 1;                   // at least 64 rows per slice
     if (want > most) want = most;
-    if (want > 256) want = 256;
+    if (want > 1024) want = 1024;
     if (want < 1) want = 1;
     p.rows_per_split = (rows + want - 1) / want;
     p.splits = (int)((rows + p.rows_per_split - 1) / p.rows_per_split);

@@ -110,7 +110,13 @@ __device__ __forceinline__ float unpack1(uint16_t h) {
     else return __half2float(*reinterpret_cast<const __half*>(&h));
 }
 
-template <int BN, bool BF16, bool B_NK>
+// F32: fp32-accurate products on the bf16 tensor-core path. Each fp32 operand arrives as three bf16 planes
+// x = x1 + x2 + x3 (8 mantissa bits each, made by split3_kernel); the k-loop runs six times over K, one pass per
+// pair (a_i, b_j) with i + j <= 4, smallest terms first, all into the same fp32 accumulator; the three dropped
+// pairs are below 2^-24 of the product. The output is stored as fp32 (32-column pieces instead of 64).
+constexpr uint32_t kSplitPlaneA = 0x001012, kSplitPlaneB = 0x010210;      // pair p -> plane of A / of B, 4 bits each
+
+template <int BN, bool BF16, bool B_NK, bool F32 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ OutMaps out, GemmParams p) {
@@ -131,6 +137,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (p.K + kBK - 1) / kBK;
+    const int k_total = F32 ? 6 * k_blocks : k_blocks;          // k-blocks the accumulator of one tile receives
     const int plane_tiles = p.m_blocks * p.n_blocks;
     const int tiles = plane_tiles * p.batch;
     const WaitCtx wctx{abort_flag, p.status};
@@ -162,20 +169,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int plane = t / plane_tiles;
                 tile_coords(t - plane * plane_tiles, p.m_blocks, p.n_blocks, mb, nb);
                 const int b_plane = p.b_shared ? 0 : plane;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kq = 0; kq < k_total; ++kq, ++it) {
+                    int kb = kq, a_plane = plane, bb_plane = b_plane;
+                    if constexpr (F32) {
+                        const int pair = kq / k_blocks;
+                        kb = kq - pair * k_blocks;
+                        a_plane = plane * 3 + (int)((kSplitPlaneA >> (4 * pair)) & 15u);
+                        bb_plane = b_plane * 3 + (int)((kSplitPlaneB >> (4 * pair)) & 15u);
+                    }
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
                     if (!(ok = bounded_wait(wctx, empty_bar(s), ph ^ 1, 0x01010000u | s))) break;
                     const uint32_t a_dst = smem_base + s * S::kStageBytes;
                     const uint32_t b_dst = a_dst + S::kABytes;
                     ptx::mbar_arrive_expect_tx(full_bar(s), S::kStageBytes);
-                    ptx::tma_load_3d(a_dst, &map_a, full_bar(s), kb * kBK, mb * kBM, plane);
+                    ptx::tma_load_3d(a_dst, &map_a, full_bar(s), kb * kBK, mb * kBM, a_plane);
                     if constexpr (B_NK) {
-                        ptx::tma_load_3d(b_dst, &map_b, full_bar(s), kb * kBK, nb * BN, b_plane);
+                        ptx::tma_load_3d(b_dst, &map_b, full_bar(s), kb * kBK, nb * BN, bb_plane);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BN / 64; ++j)
-                            ptx::tma_load_3d(b_dst + j * (kBK * 128), &map_b, full_bar(s), nb * BN + j * 64, kb * kBK, b_plane);
+                            ptx::tma_load_3d(b_dst + j * (kBK * 128), &map_b, full_bar(s), nb * BN + j * 64, kb * kBK, bb_plane);
                     }
                 }
             }
@@ -193,7 +207,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (!(ok = bounded_wait(wctx, acc_empty_bar(as), aph ^ 1, 0x01020000u | as))) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + as * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = 0; kb < k_total; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
                     if (!(ok = bounded_wait(wctx, full_bar(s), ph, 0x01030000u | s))) break;
@@ -234,15 +248,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (!ok) break;
             ptx::tc_fence_after_sync();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
+            constexpr int kPiece = F32 ? 32 : 64;                 // columns of one 128-byte-wide output piece
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 64, ++piece) {
+            for (int c = 0; c < BN; c += kPiece, ++piece) {
                 const uint32_t stage = out_smem + (piece & 1) * S::kOutBytes;
                 // the stores that last read this staging buffer (two pieces ago) must be done with it
                 if (issuer) ptx::tma_store_wait_read<1>();
                 ptx::named_barrier(1, 128);
                 const uint32_t row_smem = stage + row_in_tile * 128;
+                if constexpr (F32) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32(t_row + c, r);
+                    ptx::tmem_ld_wait();
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
+                    for (int q = 0; q < 8; ++q) {
+                        float v[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) v[j] = __uint_as_float(r[4 * q + j]);
+                        if (p.bias != nullptr) {
+                            const int col = nb * BN + c + 4 * q;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (col + j < p.N) v[j] += __ldg(reinterpret_cast<const float*>(p.bias) + col + j);
+                        }
+                        if (p.epilogue == EMMYB200_EPI_GELU_TANH) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) v[j] = gelu_tanh_fast(v[j]);
+                        } else if (p.epilogue == EMMYB200_EPI_RELU) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) v[j] = fmaxf(v[j], 0.0f);
+                        }
+                        const uint32_t slot = (uint32_t)q ^ (uint32_t)(row_in_tile & 7);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_smem + slot * 16), "r"(__float_as_uint(v[0])),
+                                     "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3]))
+                                     : "memory");
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < (F32 ? 0 : 2); ++h) {
                     uint32_t r[32];
                     ptx::tmem_ld_32x32b_x32(t_row + c + 32 * h, r);
                     ptx::tmem_ld_wait();
@@ -281,7 +324,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                      : "memory");
                     }
                 }
-                if (c + 64 >= BN) {                              // accumulator fully read: hand it back
+                if (c + kPiece >= BN) {                          // accumulator fully read: hand it back
                     ptx::tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(acc_empty_bar(as));
@@ -363,6 +406,23 @@ int make_tensor_map_3d_strided(CUtensorMap* out, const void* base, uint64_t plan
     return EMMYB200_OK;
 }
 
+// The fp32 output of the split-precision GEMM: 32-column (128-byte) boxes.
+int make_tensor_map_3d_f32(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols, uint64_t ld,
+                           uint64_t plane_stride, uint32_t box_rows, uint32_t box_cols) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return fail(EMMYB200_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {cols, rows, planes};
+    if (planes == 1) plane_stride = rows * ld;
+    cuuint64_t strides[2] = {ld * 4, plane_stride * 4};
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(EMMYB200_ERR_ARG, "cuTensorMapEncodeTiled (3-D fp32) failed: %d", (int)r);
+    return EMMYB200_OK;
+}
+
 int check_sm100() {
     int dev = 0, major = 0;
     EMMY_CUDA(cudaGetDevice(&dev));
@@ -384,27 +444,31 @@ struct GemmCall {
     const void* A; const void* B; const void* bias;
     void* const* C; int n_dst;
     int64_t batch, M, N, K, lda, ldb, ldc, stride_a, stride_b, stride_c;
+    bool b_shared_split = false;    // split-precision path: one B for every product (stride_b then is the split-plane stride)
 };
 
-template <int BN, bool BF16, bool B_NK>
+template <int BN, bool BF16, bool B_NK, bool F32 = false>
 static int launch_gemm(const GemmCall& g, cudaStream_t stream) {
     using S = GemmSmem<BN>;
     CUtensorMap map_a, map_b;
     OutMaps out;
-    const bool b_shared = g.stride_b == 0;
-    int rc = make_tensor_map_3d_strided(&map_a, g.A, (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda,
+    const bool b_shared = g.stride_b == 0 || g.b_shared_split;
+    constexpr uint64_t kSplit = F32 ? 3 : 1;                    // operand planes per product (see split3_kernel)
+    int rc = make_tensor_map_3d_strided(&map_a, g.A, (uint64_t)g.batch * kSplit, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda,
                                         (uint64_t)g.stride_a, kBM, kBK);
     if (rc != EMMYB200_OK) return rc;
-    const uint64_t b_planes = b_shared ? 1 : (uint64_t)g.batch;
+    const uint64_t b_planes = (b_shared ? 1 : (uint64_t)g.batch) * kSplit;
     rc = B_NK ? make_tensor_map_3d_strided(&map_b, g.B, b_planes, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, (uint64_t)g.stride_b, BN, kBK)
               : make_tensor_map_3d_strided(&map_b, g.B, b_planes, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, (uint64_t)g.stride_b, kBK, 64);
     if (rc != EMMYB200_OK) return rc;
     for (int d = 0; d < kMaxDst; ++d) {
-        rc = make_tensor_map_3d_strided(&out.m[d], g.C[d < g.n_dst ? d : 0], (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.N,
-                                        (uint64_t)g.ldc, (uint64_t)g.stride_c, kBM, 64);
+        rc = F32 ? make_tensor_map_3d_f32(&out.m[d], g.C[d < g.n_dst ? d : 0], (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.N,
+                                          (uint64_t)g.ldc, (uint64_t)g.stride_c, kBM, 32)
+                 : make_tensor_map_3d_strided(&out.m[d], g.C[d < g.n_dst ? d : 0], (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.N,
+                                              (uint64_t)g.ldc, (uint64_t)g.stride_c, kBM, 64);
         if (rc != EMMYB200_OK) return rc;
     }
-    auto kernel = gemm_tcgen05_kernel<BN, BF16, B_NK>;
+    auto kernel = gemm_tcgen05_kernel<BN, BF16, B_NK, F32>;
     EMMY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
     GemmParams p;
     p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
@@ -465,7 +529,113 @@ static int gemm_entry(const GemmCall& g, void* cuda_stream) {
     return b_nk ? pick_tile<false, true>(g, s) : pick_tile<false, false>(g, s);
 }
 
+// ---- fp32-accurate products: operands split into three bf16 planes --------------------------------------------------
+// src: `planes` matrices of rows x cols fp32 (leading dimension ld, plane_stride apart). dst: for every matrix three
+// bf16 planes of rows x pitch (pitch a multiple of 8, columns beyond cols zero): x1 = bf16(x), x2 = bf16(x - x1),
+// x3 = bf16(x - x1 - x2). A non-finite x keeps its value in x1 and zeros in x2, x3.
+__global__ void __launch_bounds__(256) split3_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t planes,
+                                                     int64_t rows, int64_t cols, int64_t ld, int64_t plane_stride, int64_t pitch) {
+    const int64_t groups_per_row = pitch / 8;
+    const int64_t total = planes * rows * groups_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+        const int64_t c0 = (i % groups_per_row) * 8;
+        const int64_t r = (i / groups_per_row) % rows;
+        const int64_t pl = i / (groups_per_row * rows);
+        const float* in = src + pl * plane_stride + r * ld + c0;
+        __align__(16) __nv_bfloat16 h[3][8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float x = c0 + j < cols ? __ldg(in + j) : 0.0f;
+            const __nv_bfloat16 h1 = __float2bfloat16_rn(x);
+            const float f1 = __bfloat162float(h1);
+            const bool finite = fabsf(f1) <= 3.3895314e38f;
+            const float r1 = finite ? x - f1 : 0.0f;
+            const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);
+            const float r2 = r1 - __bfloat162float(h2);
+            h[0][j] = h1; h[1][j] = h2; h[2][j] = __float2bfloat16_rn(r2);
+        }
+#pragma unroll
+        for (int sidx = 0; sidx < 3; ++sidx) {
+            __nv_bfloat16* out = dst + ((pl * 3 + sidx) * rows + r) * pitch + c0;
+            *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(h[sidx]);
+        }
+    }
+}
+
+static int64_t pad8(int64_t v) { return (v + 7) / 8 * 8; }
+
+struct SplitPlan {
+    int64_t a_pitch, b_rows, b_cols, b_pitch, b_planes;
+    size_t a_bytes, b_bytes;
+};
+
+static SplitPlan plan_split3(int flags, int64_t batch, int64_t M, int64_t N, int64_t K, bool b_shared) {
+    SplitPlan p;
+    const bool b_nk = flags & EMMYB200_GEMM_B_NK;
+    p.a_pitch = pad8(K);
+    p.b_rows = b_nk ? N : K;
+    p.b_cols = b_nk ? K : N;
+    p.b_pitch = pad8(p.b_cols);
+    p.b_planes = b_shared ? 1 : batch;
+    p.a_bytes = ((size_t)batch * 3 * M * p.a_pitch * 2 + 255) / 256 * 256;
+    p.b_bytes = ((size_t)p.b_planes * 3 * p.b_rows * p.b_pitch * 2 + 255) / 256 * 256;
+    return p;
+}
+
 }  // namespace emmy
+
+extern "C" int64_t emmyb200_gemm_f32_workspace_bytes(int flags, int64_t batch, int64_t M, int64_t N, int64_t K, int b_shared) {
+    using namespace emmy;
+    if ((flags & ~EMMYB200_GEMM_B_NK) || batch < 0 || M < 0 || N < 0 || K < 1) return -1;
+    if (batch == 0 || M == 0 || N == 0) return 0;
+    const SplitPlan p = plan_split3(flags, batch, M, N, K, b_shared != 0);
+    return (int64_t)(p.a_bytes + p.b_bytes);
+}
+
+extern "C" int emmyb200_gemm_f32(int epilogue, int flags, const float* A, const float* B, const float* bias, float* C, int64_t batch,
+                                 int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t stride_a,
+                                 int64_t stride_b, int64_t stride_c, void* workspace, int64_t workspace_bytes, void* cuda_stream) {
+    using namespace emmy;
+    if (epilogue != EMMYB200_EPI_NONE && epilogue != EMMYB200_EPI_GELU_TANH && epilogue != EMMYB200_EPI_RELU)
+        return fail(EMMYB200_ERR_ARG, "gemm_f32: unknown epilogue %d", epilogue);
+    if (flags & ~EMMYB200_GEMM_B_NK) return fail(EMMYB200_ERR_ARG, "gemm_f32: unknown flags 0x%x", flags);
+    if (M < 0 || N < 0 || K < 0 || batch < 0) return fail(EMMYB200_ERR_SHAPE, "gemm_f32: negative extent");
+    if (M == 0 || N == 0 || batch == 0) return EMMYB200_OK;
+    if (K == 0) return fail(EMMYB200_ERR_SHAPE, "gemm_f32: K = 0");
+    if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31) || batch * 3 >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "gemm_f32: extents must be below 2^31");
+    if (A == nullptr || B == nullptr || C == nullptr) return fail(EMMYB200_ERR_ARG, "gemm_f32: null buffer");
+    const bool b_nk = flags & EMMYB200_GEMM_B_NK;
+    if (lda < K || ldc < N || ldb < (b_nk ? K : N)) return fail(EMMYB200_ERR_SHAPE, "gemm_f32: leading dimension smaller than the row");
+    if (!aligned(A, 4) || !aligned(B, 4) || (bias != nullptr && !aligned(bias, 4))) return fail(EMMYB200_ERR_ALIGN, "gemm_f32: operands must be 4-byte aligned");
+    if (!aligned(C, 16) || (ldc & 3) || (batch > 1 && (stride_c & 3)))
+        return fail(EMMYB200_ERR_ALIGN, "gemm_f32: C must be 16-byte aligned with a leading dimension (and plane stride) that is a multiple of 4 elements");
+    const bool b_shared = stride_b == 0 || batch == 1;
+    if (batch > 1 && (stride_a < M * lda || stride_c < M * ldc || (!b_shared && stride_b < (b_nk ? N : K) * ldb)))
+        return fail(EMMYB200_ERR_SHAPE, "gemm_f32: plane stride smaller than a plane");
+    const SplitPlan sp = plan_split3(flags, batch, M, N, K, b_shared);
+    if (workspace == nullptr || workspace_bytes < (int64_t)(sp.a_bytes + sp.b_bytes))
+        return fail(EMMYB200_ERR_ARG, "gemm_f32: the split operands need %lld bytes of workspace", (long long)(sp.a_bytes + sp.b_bytes));
+    if (!aligned(workspace, 256)) return fail(EMMYB200_ERR_ALIGN, "gemm_f32: the workspace must be 256-byte aligned");
+    int rc = check_sm100();
+    if (rc != EMMYB200_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    __nv_bfloat16* a3 = static_cast<__nv_bfloat16*>(workspace);
+    __nv_bfloat16* b3 = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(workspace) + sp.a_bytes);
+    const int64_t cap = (int64_t)sm_count() * 16;
+    auto blocks = [&](int64_t groups) { const int64_t b = (groups + 255) / 256; return (unsigned)(b < cap ? b : cap); };
+    split3_kernel<<<blocks(batch * M * sp.a_pitch / 8), 256, 0, s>>>(A, a3, batch, M, K, lda, stride_a, sp.a_pitch);
+    rc = launch_status("split3_kernel");
+    if (rc != EMMYB200_OK) return rc;
+    split3_kernel<<<blocks(sp.b_planes * sp.b_rows * sp.b_pitch / 8), 256, 0, s>>>(B, b3, sp.b_planes, sp.b_rows, sp.b_cols, ldb, stride_b, sp.b_pitch);
+    rc = launch_status("split3_kernel");
+    if (rc != EMMYB200_OK) return rc;
+    void* dst[1] = {C};
+    GemmCall g{EMMYB200_BF16, epilogue, flags, a3, b3, bias, dst, 1, batch, M, N, K, sp.a_pitch, sp.b_pitch, ldc,
+               M * sp.a_pitch, sp.b_rows * sp.b_pitch, stride_c};
+    g.b_shared_split = b_shared;
+    if (N > 128) return b_nk ? launch_gemm<256, true, true, true>(g, s) : launch_gemm<256, true, false, true>(g, s);
+    return b_nk ? launch_gemm<128, true, true, true>(g, s) : launch_gemm<128, true, false, true>(g, s);
+}
 
 extern "C" int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, const void* B, void* C, int64_t M,
                              int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* cuda_stream) {

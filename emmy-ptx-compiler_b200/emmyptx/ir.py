@@ -366,6 +366,33 @@ def index_gather_kernel(n: int, mul: int = 7919, add: int = 13, div: int = 3, sh
     return g, k, _launch(k, ["x", "y"], n)
 
 
+def matmul_f32_kernel(m: int, n: int, k: int, batch: int = 1, b_trans: bool = False, b_batched: bool = True, bias: bool = False,
+                      relu: bool = False, name: str = "k_mm_f32"):
+    """A float32 product the way the reference lowers it without tensor-core statements: one tile cell per output
+    element, a loop over K folding a * b into an accumulator (emmyptx/kernel.py:786-797; the fma is formed from the
+    multiply feeding the Accum), then the optional bias and ReLU, then the store."""
+    axes = ([Axis("b0", Dim(batch))] if batch > 1 else []) + [Axis("m0", Dim(m)), Axis("n0", Dim(n))]
+    lead = [Var("b0")] if batch > 1 else []
+    b_lead = lead if (b_batched and batch > 1) else []
+    b_index = b_lead + ([Var("n0"), Var("k0")] if b_trans else [Var("k0"), Var("n0")])
+    body = [Loop(Axis("k0", Dim(k)), [Load(["a"], "A", lead + [Var("m0"), Var("k0")]), Load(["b"], "B", b_index),
+                                      Assign("p", Op("multiply"), ["a", "b"]), Accum("acc", None, "p", Op("add"))])]
+    out = "acc"
+    ins = [tensor("A", ([batch] if batch > 1 else []) + [m, k], "f32"),
+           tensor("B", ([batch] if b_lead else []) + ([n, k] if b_trans else [k, n]), "f32")]
+    if bias:
+        ins.append(tensor("bias", [n], "f32"))
+        body += [Load(["bv"], "bias", [Var("n0")]), Assign("s", Op("add"), [out, "bv"])]
+        out = "s"
+    if relu:
+        body.append(Assign("r", Op("relu"), [out]))
+        out = "r"
+    body.append(Write("C", lead + [Var("m0"), Var("n0")], [out]))
+    kern = KernelOp(name, [Tile(axes, body)])
+    g = _graph(kern, ins, [tensor("C", ([batch] if batch > 1 else []) + [m, n], "f32")])
+    return g, kern, _launch(kern, [t.name for t in ins] + ["C"], batch * m * n)
+
+
 def colwise_kernel(op: str, rows: int, cols: int, eps: float = 1e-12, name: str = "k_colwise"):
     """The same statement shapes for a reduction over dim 0 of X[rows, cols]: one tile cell per column, the loop walks
     the rows (tools/torch_cases/reductions.py:9 `x.sum(0)`, fused.py:7 `softmax(x, 0)`)."""

@@ -90,6 +90,8 @@ def algorithmic_work(handle: dict) -> tuple[float, str]:
         return float(p["n"]) * (sum(size[d] for d in p["program"]["in_dtypes"]) + size[p["program"]["out_dtype"]]), "B"
     if v == "gemm":
         return 2.0 * p["m"] * p["n"] * p["k"], "flop"
+    if v == "gemm_f32":
+        return 2.0 * p["batch"] * p["m"] * p["n"] * p["k"], "flop"
     if v == "gemm_batched":
         return 2.0 * p["batch"] * p["m"] * p["n"] * p["k"], "flop"
     if v == "attention_fwd":

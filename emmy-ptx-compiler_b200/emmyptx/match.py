@@ -606,10 +606,81 @@ def match_rowwise(graph, kernel, launch: dict) -> dict:
     raise Unmatched("the row program is none of the reductions or normalisations the library has")
 
 
+def match_dot(graph, kernel, launch: dict) -> dict:
+    """A float32 matrix product written as scalar loops (one tile cell per output element, a `Loop` over K folding
+    a[m, k] * b[k, n] with an `Accum`; tools/torch_cases/matmul.py:10-14): recognised by running a few output cells
+    and comparing with the product of the probe buffers. Batched A, a B shared by the batch or one per product, B as
+    K x N or N x K, an optional bias vector and ReLU are told apart by the buffers' index patterns and the values."""
+    tensors = tensor_table(graph)
+    tiles = [s for s in kernel.body if _kind(s) == "Tile"]
+    if len(kernel.body) != 1 or len(tiles) != 1:
+        raise Unmatched("a product kernel is one Tile")
+    tile = tiles[0]
+    loops = [s for s in walk(tile.body) if _kind(s) in ("Loop", "StridedLoop")]
+    if len(loops) != 1:
+        raise Unmatched("a product kernel has one loop over K")
+    k = int(loops[0].axis.extent.as_static())
+    cells = math.prod(int(a.extent.as_static()) for a in tile.axes)
+    probe = np.unique(np.concatenate([[0, cells - 1], np.random.default_rng(0).integers(0, cells, 6)])).astype(np.int64)
+    it = RowInterpreter(tensors, probe, k)
+    rem = np.broadcast_to(probe[:, None], it.cells.shape).copy()
+    for a in reversed(tile.axes):
+        e = int(a.extent.as_static())
+        it.env[a.name] = rem % e
+        rem = rem // e
+    it.run(tile.body)
+    if len(it.writes) != 1 or len(it.writes[0][2]) != 1:
+        raise Unmatched("product kernels write one value to one buffer")
+    out_name, out_idx, (value,) = it.writes[0]
+    shape = tensors[out_name][0]
+    if len(shape) < 2 or math.prod(shape) != cells or not np.array_equal(out_idx[:, 0], probe):
+        raise Unmatched("a product kernel writes C[..., m, n], one cell each")
+    m, n = shape[-2], shape[-1]
+    batch = cells // (m * n)
+    bt, mi, ni = probe // (m * n), (probe // n) % m, probe % n
+    kk = np.arange(k)[None, :]
+    a_idx = (bt[:, None] * m + mi[:, None]) * k + kk
+    b_forms = {("kn", False): (bt[:, None] * k + kk) * n + ni[:, None], ("kn", True): kk * n + ni[:, None] + 0 * bt[:, None],
+               ("nk", False): (bt[:, None] * n + ni[:, None]) * k + kk, ("nk", True): ni[:, None] * k + kk + 0 * bt[:, None]}
+    names = list(dict.fromkeys(b for b, _, _ in it.loads))
+    a_name = next((b for b, i, _ in it.loads if math.prod(tensors[b][0]) == batch * m * k and np.array_equal(i, a_idx)), None)
+    b_name = layout = shared = b_idx = None
+    for bname, i, _ in it.loads:
+        if bname == a_name:
+            continue
+        for (lay, sh), idx in b_forms.items():
+            if math.prod(tensors[bname][0]) == (1 if sh else batch) * k * n and np.array_equal(i, idx):
+                b_name, layout, shared, b_idx = bname, lay, sh or batch == 1, idx
+                break
+        if b_name:
+            break
+    if a_name is None or b_name is None:
+        raise Unmatched("the loop does not read a[m, k] and b[k, n] (or b[n, k])")
+    bias = [bn for bn in names if bn not in (a_name, b_name)]
+    if len(bias) > 1 or (bias and math.prod(tensors[bias[0]][0]) != n):
+        raise Unmatched("besides the two operands a product kernel reads at most a bias vector of N elements")
+    if any(tensors[t][1] != "f32" for t in (a_name, b_name, out_name, *bias)):
+        raise Unmatched("scalar-loop products are float32 (16-bit ones use the tensor-core statements)")
+    av, bv = probe_values(a_name, "f32", a_idx), probe_values(b_name, "f32", b_idx)
+    ref = (av * bv).sum(-1)
+    if bias:
+        ref = ref + probe_values(bias[0], "f32", ni)
+    got = np.asarray(value, np.float64)[:, 0]
+    for epilogue, f in ((None, lambda r: r), ("relu", lambda r: np.maximum(r, 0.0))):
+        if np.allclose(got, f(ref), rtol=1e-9, atol=1e-12):
+            return {"variant": "gemm_f32", "inputs": [a_name, b_name, *bias], "outputs": [out_name],
+                    "params": {"batch": batch, "m": m, "n": n, "k": k, "b_trans": layout == "nk", "b_shared": bool(shared),
+                               "bias": bool(bias), "epilogue": epilogue}}
+    raise Unmatched("the loop is not a plain product (optionally plus a bias vector, optionally through ReLU)")
+
+
 def match_kernel(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
     kinds = {_kind(s) for s in walk(kernel.body)}
     if "MmaSyncPtx" in kinds:
         return match_contraction(graph, kernel, launch)
     if "Accum" in kinds:
-        return match_rowwise(graph, kernel, launch)
+        try:
+            return match_dot(graph, kernel, launch)
+        except Unmatched:
+            return match_rowwise(graph, kernel, launch)
     return match_streaming(graph, kernel, launch, int_div)

@@ -126,6 +126,12 @@ def launch(handle: dict, bufs: dict, stream=None) -> None:
         runtime.rowwise(p["op"], x, ins[1].reshape(-1) if p["weight"] else None, ins[2].reshape(-1) if p["bias"] else None,
                         p["eps"], out=out.reshape(x.shape if p["op"] in ("softmax", "log_softmax", "layer_norm", "rms_norm", "normalize")
                                                   else (p["rows"],)), stream=stream)
+    elif v == "gemm_f32":
+        a = ins[0].reshape(p["batch"], p["m"], p["k"])
+        bshape = (p["n"], p["k"]) if p["b_trans"] else (p["k"], p["n"])
+        b = ins[1].reshape(bshape if p["b_shared"] else (p["batch"], *bshape))
+        runtime.gemm_f32(a, b, bias=ins[2].reshape(-1) if p["bias"] else None, epilogue=p["epilogue"], b_is_nk=p["b_trans"],
+                         out=out.reshape(p["batch"], p["m"], p["n"]), stream=stream)
     elif v == "colwise_f32":
         x = ins[0].reshape(p["outer"], p["rows"], p["cols"])
         is_map = p["op"] in ("softmax", "log_softmax", "normalize")

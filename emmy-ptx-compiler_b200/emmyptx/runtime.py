@@ -60,6 +60,9 @@ _SIGNATURES = {
                                      ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),
     "emmyb200_gemm_batched": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
                                              ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int64] * 10 + [ctypes.c_void_p]),
+    "emmyb200_gemm_f32_workspace_bytes": (ctypes.c_int64, [ctypes.c_int] + [ctypes.c_int64] * 4 + [ctypes.c_int]),
+    "emmyb200_gemm_f32": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+                          + [ctypes.c_int64] * 10 + [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]),
     "emmyb200_gemm_allgather": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
                                                ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),
@@ -122,11 +125,11 @@ def _stream(stream) -> int:
     return (torch.cuda.current_stream() if stream is None else stream).cuda_stream
 
 
-def _need_cuda(*tensors) -> None:
+def _need_cuda(*tensors, strided: bool = False) -> None:
     for t in tensors:
         if not t.is_cuda:
             raise RuntimeError("emmyb200 kernels take CUDA tensors only (there is no CPU path)")
-        if not t.is_contiguous():
+        if not strided and not t.is_contiguous():
             raise RuntimeError("emmyb200 kernels take contiguous tensors")
 
 
@@ -222,6 +225,45 @@ def gemm_batched(a, b, bias=None, epilogue: str | None = None, b_is_nk: bool = F
                                           b.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), batch, m, n, k,
                                           a.stride(1), b.stride(-2), out.stride(1), a.stride(0), b.stride(0) if b.dim() == 3 else 0,
                                           out.stride(0), _stream(stream)))
+    return out
+
+
+def gemm_f32(a, b, bias=None, epilogue: str | None = None, b_is_nk: bool = False, out=None, workspace=None, stream=None):
+    """float32 matmul with float32 accuracy on the tensor cores. a: [M, K] or [batch, M, K]; b: [K, N] ([N, K] with
+    b_is_nk), shared by every product, or [batch, K, N]; bias: [N] or None. Last axes must be contiguous."""
+    import torch
+    _need_cuda(a, b, strided=True)              # row-pitched views are fine: the split reads element by element
+    if a.dtype != torch.float32 or b.dtype != torch.float32:
+        raise TypeError("gemm_f32: float32 operands")
+    squeeze = a.dim() == 2
+    a3 = a.unsqueeze(0) if squeeze else a
+    if a3.dim() != 3 or b.dim() not in (2, 3) or a3.stride(-1) != 1 or b.stride(-1) != 1:
+        raise TypeError("gemm_f32: [batch,] M x K and [batch,] K x N operands with contiguous last axes")
+    batch, m, k = a3.shape
+    n = b.shape[-2] if b_is_nk else b.shape[-1]
+    if (b.shape[-1] if b_is_nk else b.shape[-2]) != k or (b.dim() == 3 and b.shape[0] != batch):
+        raise ValueError("gemm_f32: operand shapes do not agree")
+    if out is None:
+        out = torch.empty((batch, m, n), dtype=torch.float32, device=a.device)
+        if squeeze:
+            out = out[0]
+    _need_cuda(out, strided=True)
+    o3 = out.unsqueeze(0) if out.dim() == 2 else out
+    stride_b = b.stride(0) if b.dim() == 3 and batch > 1 else 0
+    lib = library()
+    flags = GEMM_B_NK if b_is_nk else 0
+    need = lib.emmyb200_gemm_f32_workspace_bytes(flags, batch, m, n, k, 1 if stride_b == 0 else 0)
+    if need > 0 and (workspace is None or workspace.numel() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+    if bias is not None:
+        _need_cuda(bias)
+        if bias.dtype != torch.float32 or bias.numel() != n or not bias.is_contiguous():
+            raise TypeError("gemm_f32: bias is a contiguous float32 vector of N elements")
+    check(lib.emmyb200_gemm_f32(EPILOGUES[epilogue], flags, a3.data_ptr(), b.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                o3.data_ptr(), batch, m, n, k, a3.stride(1), b.stride(-2), o3.stride(1),
+                                a3.stride(0) if batch > 1 else 0, stride_b, o3.stride(0) if batch > 1 else 0,
+                                workspace.data_ptr() if workspace is not None else None,
+                                workspace.numel() if workspace is not None else 0, _stream(stream)))
     return out
 
 

@@ -125,6 +125,21 @@ int emmyb200_gemm_batched(int dtype, int epilogue, int flags, const void* A, con
                           int64_t ldb, int64_t ldc, int64_t stride_a, int64_t stride_b, int64_t stride_c,
                           void* cuda_stream);
 
+/* fp32 in, fp32 out, fp32-accurate: the reference's float32 matmul cases (tools/torch_cases/matmul.py:10-16: mm, bmm,
+ * broadcast, F.linear with bias, einsum), which it lowers to scalar FMA loops (emmyptx/kernel.py:786-797). Here each
+ * operand is split into three bf16 planes (x = x1 + x2 + x3, 24 mantissa bits together) in `workspace`, and the six
+ * products a_i b_j with i + j <= 4 run on the bf16 tensor-core path into one fp32 accumulator; the dropped terms
+ * are below 2^-24 of a product, and the accumulator truncates once per 16-deep block, so the error is bounded by
+ * about 2^-23 (8 + K / 16) sum_k |a_k b_k| (measured: 1e-7 .. 8e-7 of that sum for operands of random sign). Arguments as emmyb200_gemm_batched with float buffers (`bias`: N floats or NULL);
+ * lda / ldb / strides of A and B are unrestricted, C must be 16-byte aligned with ldc (and stride_c) a multiple
+ * of 4. `workspace`: emmyb200_gemm_f32_workspace_bytes(flags, batch, M, N, K, b_shared) bytes, 256-byte aligned
+ * (b_shared = 1 when stride_b is 0 or batch is 1). No counterpart for the split itself in the reference. */
+int64_t emmyb200_gemm_f32_workspace_bytes(int flags, int64_t batch, int64_t M, int64_t N, int64_t K, int b_shared);
+int emmyb200_gemm_f32(int epilogue, int flags, const float* A, const float* B, const float* bias, float* C,
+                      int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                      int64_t stride_a, int64_t stride_b, int64_t stride_c, void* workspace, int64_t workspace_bytes,
+                      void* cuda_stream);
+
 /* The same GEMM on one GPU's row shard of A, with every output piece stored to n_dst destination buffers
  * (1..8): C_dst[0] is this GPU's own C shard, the others are the addresses, valid on this GPU, of where the
  * same rows live in each peer's copy of the full C (peer-mapped device memory). Run by every GPU of a group

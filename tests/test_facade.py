@@ -169,3 +169,16 @@ def test_row_reductions_are_matched_by_behaviour():
     g = _graph(k, [tensor("X", [rows, cols], "f32")], [tensor("Y", [rows], "f32")])
     with pytest.raises(CompileError):
         handle((g, k, _launch(k, ["X", "Y"], rows)))
+
+
+def test_float32_products_written_as_loops_match_the_split_precision_gemm():
+    """m_mm, m_bmm, m_bcast_matmul, m_linear_bias (tools/torch_cases/matmul.py:10-14) as the scalar-loop IR."""
+    h = handle(ir.matmul_f32_kernel(128, 80, 96))
+    assert h["variant"] == "gemm_f32" and h["params"] == {"batch": 1, "m": 128, "n": 80, "k": 96, "b_trans": False, "b_shared": True,
+                                                           "bias": False, "epilogue": None}
+    assert algorithmic_work(h) == (2.0 * 128 * 80 * 96, "flop")
+    assert handle(ir.matmul_f32_kernel(64, 48, 32, batch=4))["params"]["b_shared"] is False
+    assert handle(ir.matmul_f32_kernel(64, 48, 32, batch=4, b_batched=False))["params"]["b_shared"] is True
+    p = handle(ir.matmul_f32_kernel(64, 96, 128, b_trans=True, bias=True))
+    assert p["params"]["b_trans"] and p["params"]["bias"] and p["inputs"] == ["A", "B", "bias"]
+    assert handle(ir.matmul_f32_kernel(32, 256, 128, b_trans=True, bias=True, relu=True))["params"]["epilogue"] == "relu"

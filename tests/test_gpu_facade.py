@@ -125,6 +125,22 @@ def test_dim0_kernels_through_the_facade(tmp_path, cuda, op, rtol, atol):
     assert reference.compare(out["Y"], reference.colwise_reference(op, x).numpy(), rtol, atol)["ok"]
 
 
+@pytest.mark.parametrize("kw", [dict(m=128, n=80, k=96), dict(m=64, n=48, k=32, batch=4), dict(m=64, n=48, k=32, batch=4, b_batched=False),
+                                dict(m=64, n=96, k=128, b_trans=True, bias=True)])
+def test_float32_matmul_through_the_facade(tmp_path, cuda, kw):
+    """m_mm, m_bmm, m_bcast_matmul, m_linear_bias at the reference's MM class (rtol = atol = 1e-3)."""
+    import torch
+    built = ir.matmul_f32_kernel(**kw)
+    tensors = {t.name: [int(d.as_static()) for d in t.shape] for node in built[0].nodes.values() for t in node.outputs}
+    names = [nm for nm in built[2]["arg_order"] if nm != "C"]
+    out = compile_and_run(tmp_path, built, [{"name": nm, "dtype": "f32", "shape": tensors[nm], "seed": i} for i, nm in enumerate(names)] +
+                          [{"name": "C", "dtype": "f32", "shape": tensors["C"], "output": True}])
+    t = {nm: torch.from_numpy(seeded(i, tensors[nm])).double() for i, nm in enumerate(names)}
+    b = t["B"].transpose(-1, -2) if kw.get("b_trans") else t["B"]
+    ref = t["A"] @ b + (t["bias"] if "bias" in t else 0.0)
+    assert reference.compare(out["C"].reshape(ref.shape), ref.numpy(), 1e-3, 1e-3)["ok"]
+
+
 def test_kernels_against_the_reference_golden_vectors(cuda):
     """golden.npz is the reference's own PTX executed on these inputs. Integer kernel in the reference's
     (truncating) mode: bit for bit. Float kernels: within the reference's tolerance class of each other."""
