@@ -140,7 +140,8 @@ def test_cumsum(cols, cuda):
     assert torch.equal(xd, expect)
     flat = torch.zeros(rows * cols + 1, device=cuda)                        # a view off the 16-byte grid
     flat[1:] = x.reshape(-1).to(cuda)
-    assert torch.allclose(runtime.cumsum(flat[1:].view(rows, cols)), expect, rtol=1e-5, atol=1e-4)
+    off = runtime.cumsum(flat[1:].view(rows, cols)).cpu()                  # scalar accesses, other slab size: other rounding
+    assert reference.compare(off.numpy(), reference.cumsum_reference(x).numpy(), 1e-4, 1e-4 + 2e-6 * cols ** 0.5)["ok"]
 
 
 def test_cumsum_of_integers_is_exact(cuda):
