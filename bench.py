@@ -107,6 +107,15 @@ class ClockSampler:
 
 
 # ---- the five workloads -------------------------------------------------------------------------------
+def group_has_multicast(address: int, dev) -> bool:
+    """True if every rank got a multicast address for the buffer (the ranks must take the same path)."""
+    import torch
+    import torch.distributed as dist
+    flag = torch.tensor([1 if address else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(flag.item())
+
+
 class Workload:
     """One configuration: device-resident inputs for this rank, the step, its algorithmic work."""
 
@@ -142,21 +151,27 @@ class GemmWorkload(Workload):
         self.a = (torch.randn(self.rows, k, device=dev, generator=g, dtype=torch.float32) / k**0.5).to(td)
         self.gather = gather and world > 1
         self.host = None
-        self.mode = os.environ.get("EMMYB200_BENCH_GATHER", "fused")       # "fused" (kernel stores to peers) or "nccl"
-        if self.gather and self.mode == "fused":
+        # "multicast" (one multimem.st per piece, replicated by the NVSwitch), "fused" (one TMA store per peer) or "nccl"
+        self.mode = os.environ.get("EMMYB200_BENCH_GATHER", "multicast")
+        if self.gather and self.mode in ("fused", "multicast"):
             # The full C lives in peer-mapped memory on every rank; each rank's kernel writes its rows into all of them.
             from emmyptx import shard
-            self.c_full, self.peers = shard.peer_mapped_empty((m, n), td, dev)
+            self.c_full, self.peers = shard.peer_mapped_empty((m, n), td, dev, multicast=self.mode == "multicast")
             off = rank * self.rows * n * self.c_full.element_size()
             own = self.c_full.data_ptr() + off
-            self.dst = [own] + [p + off for r, p in enumerate(self.peers.buffer_ptrs) if r != rank]
+            if self.mode == "multicast" and not group_has_multicast(shard.multicast_address(self.peers), dev):
+                self.mode = "fused"                                       # no multicast object on this fabric
+            if self.mode == "multicast":
+                self.dst = [shard.multicast_address(self.peers) + off]
+            else:
+                self.dst = [own] + [p + off for r, p in enumerate(self.peers.buffer_ptrs) if r != rank]
         else:
             self.c_full = torch.empty(m, n, device=dev, dtype=td)
         self.c = self.c_full[rank * self.rows:(rank + 1) * self.rows]
 
     def step(self):
-        if self.gather and self.mode == "fused":
-            self.rt.gemm_allgather(self.a, self.b, self.dst, self.n, epilogue=self.epilogue)
+        if self.gather and self.mode in ("fused", "multicast"):
+            self.rt.gemm_allgather(self.a, self.b, self.dst, self.n, epilogue=self.epilogue, multicast=self.mode == "multicast")
             self.peers.barrier()                # every rank's rows have landed everywhere
             return
         self.rt.gemm(self.a, self.b, epilogue=self.epilogue, out=self.c)
@@ -169,6 +184,8 @@ class GemmWorkload(Workload):
 
     @property
     def collective(self):
+        if self.mode == "multicast":
+            return "fused: the GEMM stores each output piece once through the NVSwitch multicast mapping of C (multimem.st), then a signal barrier"
         if self.mode == "fused":
             return "fused: the GEMM's TMA stores write each output piece to every peer's C over NVLink, then a signal barrier"
         return "nccl all_gather of the output shards"
@@ -282,25 +299,32 @@ class AttentionWorkload(Workload):
         mk = lambda: torch.randn(self.local, seq, d, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
         self.q, self.k, self.v = mk(), mk(), mk()
         self.gather = gather and world > 1
-        self.mode = os.environ.get("EMMYB200_BENCH_GATHER", "fused")
-        if self.gather and self.mode == "fused":
+        self.mode = os.environ.get("EMMYB200_BENCH_GATHER", "multicast")
+        if self.gather and self.mode in ("fused", "multicast"):
             from emmyptx import shard
-            self.o_full, self.peers = shard.peer_mapped_empty((units, seq, d), torch.bfloat16, dev)
+            self.o_full, self.peers = shard.peer_mapped_empty((units, seq, d), torch.bfloat16, dev, multicast=self.mode == "multicast")
             off = rank * self.local * seq * d * 2
-            self.dst = [self.o_full.data_ptr() + off] + [p + off for r, p in enumerate(self.peers.buffer_ptrs) if r != rank]
+            if self.mode == "multicast" and not group_has_multicast(shard.multicast_address(self.peers), dev):
+                self.mode = "fused"
+            if self.mode == "multicast":
+                self.dst = [shard.multicast_address(self.peers) + off]
+            else:
+                self.dst = [self.o_full.data_ptr() + off] + [p + off for r, p in enumerate(self.peers.buffer_ptrs) if r != rank]
         else:
             self.o_full = torch.empty(units, seq, d, device=dev, dtype=torch.bfloat16)
         self.o = self.o_full[rank * self.local:(rank + 1) * self.local]
 
     @property
     def collective(self):
+        if self.mode == "multicast":
+            return "fused: the attention kernel stores each output tile once through the NVSwitch multicast mapping of O (multimem.st), then a signal barrier"
         if self.mode == "fused":
             return "fused: the attention kernel's TMA stores write each output tile to every peer's O over NVLink, then a signal barrier"
         return "nccl all_gather of the output shards"
 
     def step(self):
-        if self.gather and self.mode == "fused":
-            self.rt.attention_allgather(self.q, self.k, self.v, self.dst)
+        if self.gather and self.mode in ("fused", "multicast"):
+            self.rt.attention_allgather(self.q, self.k, self.v, self.dst, multicast=self.mode == "multicast")
             self.peers.barrier()
             return
         self.rt.attention(self.q, self.k, self.v, out=self.o)

@@ -53,6 +53,7 @@ struct AttOutMaps {
 struct AttParams {
     int n_dst;              // destinations of every output tile (1 = the local O only)
     int causal;             // 1: query i sees keys 0 .. i only
+    unsigned long long mc_base;     // != 0: O as a multicast address, written once with multimem.st for every GPU
     int seq_q, seq_k;
     int q_tiles;
     float scale_log2;       // scale * log2(e)
@@ -366,7 +367,25 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(o_staged);
-            if (threadIdx.x == 64) {                            // first softmax thread: owns the stores
+            if (p.mc_base != 0) {
+                // every softmax thread waits for the staged tile, then the 256 of them copy it out: 16 (d = 128) or 8
+                // (d = 64) threads per row, so each multicast store of a warp covers whole rows
+                if (__all_sync(0xffffffffu, bounded_wait(wctx, o_staged, 0, 0x020b0000u))) {
+                    constexpr int kSlots = D / 8;                   // 16-byte slots per output row
+                    const int tt = (int)threadIdx.x - 64, slot = tt % kSlots;
+                    const uint32_t chunk_smem = q_smem + (slot >> 3) * (kTileQ * 128);
+#pragma unroll
+                    for (int i = 0; i < kTileQ * kSlots / 256; ++i) {
+                        const int r = tt / kSlots + (256 / kSlots) * i;
+                        if (qt * kTileQ + r < p.seq_q) {
+                            uint32_t w0, w1, w2, w3;
+                            ptx::ld_shared_16B(chunk_smem + r * 128 + (((slot & 7) ^ (r & 7)) << 4), w0, w1, w2, w3);
+                            const unsigned long long elem = ((unsigned long long)unit * p.seq_q + qt * kTileQ + r) * D + slot * 8;
+                            ptx::multimem_st_16B(p.mc_base + elem * 2ull, w0, w1, w2, w3);
+                        }
+                    }
+                }
+            } else if (threadIdx.x == 64) {                     // first softmax thread: owns the stores
                 if (bounded_wait(wctx, o_staged, 0, 0x020b0000u)) {
                     for (int d = 0; d < p.n_dst; ++d)
 #pragma unroll
@@ -399,7 +418,7 @@ int attention_read_status(uint32_t* out) {
 }
 
 template <int D, bool BF16>
-static int launch_attention(const void* Q, const void* K, const void* V, void* const* O, int n_dst, bool causal, int64_t units,
+static int launch_attention(const void* Q, const void* K, const void* V, void* const* O, int n_dst, bool causal, bool multicast, int64_t units,
                             int64_t seq_q, int64_t seq_k, float scale, cudaStream_t stream) {
     using S = AttSmem<D>;
     CUtensorMap mq, mk, mv;
@@ -407,13 +426,16 @@ static int launch_attention(const void* Q, const void* K, const void* V, void* c
     if (rc == EMMYB200_OK) rc = make_tensor_map_3d(&mk, K, (uint64_t)units, (uint64_t)seq_k, D, kTileK, 64);
     if (rc == EMMYB200_OK) rc = make_tensor_map_3d(&mv, V, (uint64_t)units, (uint64_t)seq_k, D, kTileK, 64);
     AttOutMaps out;
-    for (int d = 0; d < kMaxDst && rc == EMMYB200_OK; ++d)
-        rc = make_tensor_map_3d(&out.m[d], O[d < n_dst ? d : 0], (uint64_t)units, (uint64_t)seq_q, D, kTileQ, 64);
+    for (int d = 0; d < kMaxDst && rc == EMMYB200_OK; ++d) {
+        if (multicast) out.m[d] = mq;                               // unused: the stores go through multimem.st
+        else rc = make_tensor_map_3d(&out.m[d], O[d < n_dst ? d : 0], (uint64_t)units, (uint64_t)seq_q, D, kTileQ, 64);
+    }
     if (rc != EMMYB200_OK) return rc;
     auto kernel = attention_fwd_kernel<D, BF16>;
     EMMY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
     AttParams p;
     p.n_dst = n_dst; p.causal = causal ? 1 : 0; p.seq_q = (int)seq_q; p.seq_k = (int)seq_k;
+    p.mc_base = multicast ? (unsigned long long)(uintptr_t)O[0] : 0ull;
     p.q_tiles = (int)((seq_q + kTileQ - 1) / kTileQ);
     p.scale_log2 = scale * 1.4426950408889634f;
     EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_att_status));
@@ -429,8 +451,10 @@ static int attention_entry(int dtype, int flags, const void* Q, const void* K, c
                            int64_t seq_q, int64_t seq_k, int64_t d, float scale, void* cuda_stream) {
     using namespace emmy;
     if (dtype != EMMYB200_F16 && dtype != EMMYB200_BF16) return fail(EMMYB200_ERR_UNSUPPORTED, "attention_fwd: dtype %d (f16 and bf16 only)", dtype);
-    if (flags & ~EMMYB200_ATT_CAUSAL) return fail(EMMYB200_ERR_ARG, "attention_fwd: unknown flags 0x%x", flags);
+    if (flags & ~(EMMYB200_ATT_CAUSAL | EMMYB200_ATT_DST_MULTICAST)) return fail(EMMYB200_ERR_ARG, "attention_fwd: unknown flags 0x%x", flags);
     const bool causal = flags & EMMYB200_ATT_CAUSAL;
+    const bool multicast = flags & EMMYB200_ATT_DST_MULTICAST;
+    if (multicast && n_dst != 1) return fail(EMMYB200_ERR_ARG, "attention_fwd: a multicast destination is a single address");
     if (n_dst < 1 || n_dst > kMaxDst) return fail(EMMYB200_ERR_ARG, "attention_fwd: %d destinations (1 to %d)", n_dst, kMaxDst);
     if (units < 0 || seq_q < 0 || seq_k < 0) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: negative extent");
     if (units == 0 || seq_q == 0) return EMMYB200_OK;
@@ -448,15 +472,16 @@ static int attention_entry(int dtype, int flags, const void* Q, const void* K, c
     if (rc != EMMYB200_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
     const bool bf16 = dtype == EMMYB200_BF16;
-    if (d == 128) return bf16 ? launch_attention<128, true>(Q, K, V, O, n_dst, causal, units, seq_q, seq_k, scale, s)
-                              : launch_attention<128, false>(Q, K, V, O, n_dst, causal, units, seq_q, seq_k, scale, s);
-    return bf16 ? launch_attention<64, true>(Q, K, V, O, n_dst, causal, units, seq_q, seq_k, scale, s)
-                : launch_attention<64, false>(Q, K, V, O, n_dst, causal, units, seq_q, seq_k, scale, s);
+    if (d == 128) return bf16 ? launch_attention<128, true>(Q, K, V, O, n_dst, causal, multicast, units, seq_q, seq_k, scale, s)
+                              : launch_attention<128, false>(Q, K, V, O, n_dst, causal, multicast, units, seq_q, seq_k, scale, s);
+    return bf16 ? launch_attention<64, true>(Q, K, V, O, n_dst, causal, multicast, units, seq_q, seq_k, scale, s)
+                : launch_attention<64, false>(Q, K, V, O, n_dst, causal, multicast, units, seq_q, seq_k, scale, s);
 }
 
 extern "C" int emmyb200_attention_fwd(int dtype, int flags, const void* Q, const void* K, const void* V, void* O, int64_t units,
                                       int64_t seq_q, int64_t seq_k, int64_t d, float scale, void* cuda_stream) {
     void* dst[1] = {O};
+    if (flags & EMMYB200_ATT_DST_MULTICAST) return emmy::fail(EMMYB200_ERR_ARG, "attention_fwd: the multicast flag belongs to emmyb200_attention_fwd_allgather");
     return attention_entry(dtype, flags, Q, K, V, dst, 1, units, seq_q, seq_k, d, scale, cuda_stream);
 }
 

@@ -57,6 +57,8 @@ struct GemmParams {
     int n_dst;              // destinations of every output piece (1 = the local C only)
     int epilogue;           // EMMYB200_EPI_*
     const void* bias;       // per-column addend of the output type, or null
+    unsigned long long mc_base;     // != 0: C as a multicast address (stores go out through multimem.st, once, to every GPU)
+    long long ldc, stride_c;        // of C, in elements (multicast mode only; the TMA path has them in its tensor maps)
     uint32_t* status;
 };
 
@@ -331,13 +333,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 ptx::fence_proxy_async_smem();
                 ptx::named_barrier(1, 128);
-                if (issuer && nb * BN + c < p.N) {
-                    for (int d = 0; d < p.n_dst; ++d) ptx::tma_store_3d(&out.m[d], stage, nb * BN + c, mb * kBM, plane);
+                if (p.mc_base != 0) {
+                    if constexpr (!F32) {
+                        // 128 threads copy the 128 x 128-byte piece: 8 threads per row, 16 rows per pass, so every
+                        // multicast store instruction of a warp covers four full 128-byte rows
+                        const int tt = (int)threadIdx.x - 64, s16 = tt & 7;
+                        const int col = nb * BN + c + s16 * 8;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = (tt >> 3) + 16 * i;
+                            const int grow = mb * kBM + r;
+                            if (grow < p.M && col < p.N) {
+                                uint32_t w0, w1, w2, w3;
+                                ptx::ld_shared_16B(stage + r * 128 + ((s16 ^ (r & 7)) << 4), w0, w1, w2, w3);
+                                const long long elem = (long long)plane * p.stride_c + (long long)grow * p.ldc + col;
+                                ptx::multimem_st_16B(p.mc_base + (unsigned long long)elem * 2ull, w0, w1, w2, w3);
+                            }
+                        }
+                    }
+                } else {
+                    if (issuer && nb * BN + c < p.N) {
+                        for (int d = 0; d < p.n_dst; ++d) ptx::tma_store_3d(&out.m[d], stage, nb * BN + c, mb * kBM, plane);
+                    }
+                    if (issuer) ptx::tma_store_commit();
                 }
-                if (issuer) ptx::tma_store_commit();
             }
         }
         if (issuer) ptx::tma_store_wait<0>();
+        if (p.mc_base != 0) __threadfence_system();
     }
 
     // ---- teardown -------------------------------------------------------------------------------
@@ -442,7 +465,7 @@ int gemm_read_status(uint32_t* out) {
 struct GemmCall {
     int dtype, epilogue, flags;
     const void* A; const void* B; const void* bias;
-    void* const* C; int n_dst;
+    void* const* C; int n_dst;      // with EMMYB200_GEMM_DST_MULTICAST: C[0] is a multicast address, n_dst = 1
     int64_t batch, M, N, K, lda, ldb, ldc, stride_a, stride_b, stride_c;
     bool b_shared_split = false;    // split-precision path: one B for every product (stride_b then is the split-plane stride)
 };
@@ -462,6 +485,7 @@ static int launch_gemm(const GemmCall& g, cudaStream_t stream) {
               : make_tensor_map_3d_strided(&map_b, g.B, b_planes, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, (uint64_t)g.stride_b, kBK, 64);
     if (rc != EMMYB200_OK) return rc;
     for (int d = 0; d < kMaxDst; ++d) {
+        if (g.flags & EMMYB200_GEMM_DST_MULTICAST) { out.m[d] = map_a; continue; }      // unused: stores go through multimem.st
         rc = F32 ? make_tensor_map_3d_f32(&out.m[d], g.C[d < g.n_dst ? d : 0], (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.N,
                                           (uint64_t)g.ldc, (uint64_t)g.stride_c, kBM, 32)
                  : make_tensor_map_3d_strided(&out.m[d], g.C[d < g.n_dst ? d : 0], (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.N,
@@ -479,6 +503,10 @@ static int launch_gemm(const GemmCall& g, cudaStream_t stream) {
     p.n_dst = g.n_dst;
     p.epilogue = g.epilogue;
     p.bias = g.bias;
+    const bool multicast = g.flags & EMMYB200_GEMM_DST_MULTICAST;
+    p.mc_base = multicast ? (unsigned long long)(uintptr_t)g.C[0] : 0ull;
+    p.ldc = g.ldc;
+    p.stride_c = g.stride_c;
     EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
     const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks * g.batch;
     if (tiles >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "gemm: %lld output tiles exceed the scheduler's range", (long long)tiles);
@@ -500,7 +528,11 @@ static int gemm_entry(const GemmCall& g, void* cuda_stream) {
     if (g.dtype != EMMYB200_F16 && g.dtype != EMMYB200_BF16) return fail(EMMYB200_ERR_UNSUPPORTED, "gemm: dtype %d (f16 and bf16 only)", g.dtype);
     if (g.epilogue != EMMYB200_EPI_NONE && g.epilogue != EMMYB200_EPI_GELU_TANH && g.epilogue != EMMYB200_EPI_RELU)
         return fail(EMMYB200_ERR_ARG, "gemm: unknown epilogue %d", g.epilogue);
-    if (g.flags & ~EMMYB200_GEMM_B_NK) return fail(EMMYB200_ERR_ARG, "gemm: unknown flags 0x%x", g.flags);
+    if (g.flags & ~(EMMYB200_GEMM_B_NK | EMMYB200_GEMM_DST_MULTICAST)) return fail(EMMYB200_ERR_ARG, "gemm: unknown flags 0x%x", g.flags);
+    if (g.flags & EMMYB200_GEMM_DST_MULTICAST) {
+        if (g.n_dst != 1) return fail(EMMYB200_ERR_ARG, "gemm: a multicast destination is a single address");
+        if (g.N % 8 != 0) return fail(EMMYB200_ERR_SHAPE, "gemm: multicast stores move 8 columns at a time (N = %lld)", (long long)g.N);
+    }
     if (g.n_dst < 1 || g.n_dst > kMaxDst) return fail(EMMYB200_ERR_ARG, "gemm: %d destinations (1 to %d)", g.n_dst, kMaxDst);
     if (g.M < 0 || g.N < 0 || g.K < 0 || g.batch < 0) return fail(EMMYB200_ERR_SHAPE, "gemm: negative extent");
     if (g.M == 0 || g.N == 0 || g.batch == 0) return EMMYB200_OK;
@@ -640,6 +672,7 @@ extern "C" int emmyb200_gemm_f32(int epilogue, int flags, const float* A, const 
 extern "C" int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, const void* B, void* C, int64_t M,
                              int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* cuda_stream) {
     void* dst[1] = {C};
+    if (flags & EMMYB200_GEMM_DST_MULTICAST) return emmy::fail(EMMYB200_ERR_ARG, "gemm: the multicast flag belongs to emmyb200_gemm_allgather");
     const emmy::GemmCall g{dtype, epilogue, flags, A, B, nullptr, dst, 1, 1, M, N, K, lda, ldb, ldc, 0, 0, 0};
     return emmy::gemm_entry(g, cuda_stream);
 }
@@ -655,6 +688,7 @@ extern "C" int emmyb200_gemm_allgather(int dtype, int epilogue, int flags, const
 extern "C" int emmyb200_gemm_batched(int dtype, int epilogue, int flags, const void* A, const void* B, const void* bias, void* C,
                                      int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                                      int64_t stride_a, int64_t stride_b, int64_t stride_c, void* cuda_stream) {
+    if (flags & EMMYB200_GEMM_DST_MULTICAST) return emmy::fail(EMMYB200_ERR_ARG, "gemm: the multicast flag belongs to emmyb200_gemm_allgather");
     void* dst[1] = {C};
     const emmy::GemmCall g{dtype, epilogue, flags, A, B, bias, dst, 1, batch, M, N, K, lda, ldb, ldc, stride_a, stride_b, stride_c};
     return emmy::gemm_entry(g, cuda_stream);

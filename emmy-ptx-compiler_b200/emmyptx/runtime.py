@@ -39,7 +39,9 @@ class PwProgram(ctypes.Structure):
 EPI_NONE, EPI_GELU_TANH, EPI_RELU = 0, 1, 2
 EPILOGUES = {None: EPI_NONE, "none": EPI_NONE, "gelu_tanh": EPI_GELU_TANH, "relu": EPI_RELU}
 GEMM_B_NK = 1
+GEMM_DST_MULTICAST = 2
 ATT_CAUSAL = 1
+ATT_DST_MULTICAST = 2
 GATHER_TRUNC = 1
 ROW_OPS = {"sum": 0, "mean": 1, "amax": 2, "amin": 3, "prod": 4, "var": 5, "std": 6, "norm2": 7, "logsumexp": 8, "argmax": 9,
            "softmax": 16, "log_softmax": 17, "layer_norm": 18, "rms_norm": 19, "normalize": 20}
@@ -267,14 +269,17 @@ def gemm_f32(a, b, bias=None, epilogue: str | None = None, b_is_nk: bool = False
     return out
 
 
-def gemm_allgather(a, b, dst_ptrs: list[int], ldc: int, epilogue: str | None = None, b_is_nk: bool = False, stream=None):
+def gemm_allgather(a, b, dst_ptrs: list[int], ldc: int, epilogue: str | None = None, b_is_nk: bool = False, multicast: bool = False,
+                   stream=None):
     """epilogue(a @ b) for this rank's rows of A, every output piece stored to each address in `dst_ptrs`
-    (this rank's shard first, then where the same rows live in each peer's full C)."""
+    (this rank's shard first, then where the same rows live in each peer's full C). With `multicast`, `dst_ptrs` is the
+    one address of the shard inside a multicast mapping of C, and the switch replicates every store."""
     _need_cuda(a, b)
     m, k = a.shape
     n = b.shape[0] if b_is_nk else b.shape[1]
     arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
-    check(library().emmyb200_gemm_allgather(dtype_code(a), EPILOGUES[epilogue], GEMM_B_NK if b_is_nk else 0, a.data_ptr(),
+    check(library().emmyb200_gemm_allgather(dtype_code(a), EPILOGUES[epilogue],
+                                            (GEMM_B_NK if b_is_nk else 0) | (GEMM_DST_MULTICAST if multicast else 0), a.data_ptr(),
                                             b.data_ptr(), arr, len(dst_ptrs), m, n, k, a.stride(0), b.stride(0), ldc,
                                             _stream(stream)))
 
@@ -294,15 +299,17 @@ def attention(q, k, v, scale: float | None = None, causal: bool = False, out=Non
     return out
 
 
-def attention_allgather(q, k, v, dst_ptrs: list[int], scale: float | None = None, causal: bool = False, stream=None):
+def attention_allgather(q, k, v, dst_ptrs: list[int], scale: float | None = None, causal: bool = False, multicast: bool = False,
+                        stream=None):
     """attention() on this rank's units, every output tile stored to each address in `dst_ptrs` (this rank's slice of
-    O first, then the same slice inside each peer's full O)."""
+    O first, then the same slice inside each peer's full O; with `multicast`, the slice's one multicast address)."""
     _need_cuda(q, k, v)
     d = q.shape[-1]
     units = q.numel() // (q.shape[-2] * d)
     arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
     scale = d ** -0.5 if scale is None else scale
-    check(library().emmyb200_attention_fwd_allgather(dtype_code(q), ATT_CAUSAL if causal else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), arr, len(dst_ptrs),
+    check(library().emmyb200_attention_fwd_allgather(dtype_code(q), (ATT_CAUSAL if causal else 0) | (ATT_DST_MULTICAST if multicast else 0),
+                                                     q.data_ptr(), k.data_ptr(), v.data_ptr(), arr, len(dst_ptrs),
                                                      units, q.shape[-2], k.shape[-2], d, scale, _stream(stream)))
 
 

@@ -53,15 +53,26 @@ def all_gather_ragged(full, local, total: int, align: int = 1, group=None):
     return full
 
 
-def peer_mapped_empty(shape, dtype, device, group=None):
+def peer_mapped_empty(shape, dtype, device, group=None, multicast: bool = False):
     """A tensor of the same shape on every rank of the group, each mapped into every other rank's address
     space (torch symmetric memory over NVLink). Returns (local tensor, handle); `handle.buffer_ptrs[r]` is rank
     r's copy as an address valid on this GPU and `handle.barrier()` is a device-side barrier of the group.
-    Switch-side multicast is left off: plain peer stores are all the kernels use."""
+    With `multicast`, the copies are also bound to one NVSwitch multicast object where the fabric supports it:
+    `multicast_address(handle)` is then the address through which one `multimem.st` reaches every copy (0 if not).
+    The choice is made by the first call in a process (torch reads the switch once)."""
     import os
-    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    if not multicast:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     import torch.distributed as dist
     import torch.distributed._symmetric_memory as symm_mem
     t = symm_mem.empty(*shape, dtype=dtype, device=device)
     handle = symm_mem.rendezvous(t, group if group is not None else dist.group.WORLD)
     return t, handle
+
+
+def multicast_address(handle) -> int:
+    """The multicast address of a `peer_mapped_empty(..., multicast=True)` buffer, or 0 when the group has none."""
+    try:
+        return int(getattr(handle, "multicast_ptr", 0) or 0)
+    except Exception:  # noqa: BLE001 - an unsupported fabric is not an error here
+        return 0

@@ -111,6 +111,7 @@ int emmyb200_index_gather_i32(const int32_t* x, int32_t* y, int64_t n, int64_t m
 #define EMMYB200_EPI_GELU_TANH 1
 #define EMMYB200_EPI_RELU 2
 #define EMMYB200_GEMM_B_NK 1
+#define EMMYB200_GEMM_DST_MULTICAST 2   /* emmyb200_gemm_allgather only, see there */
 int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, const void* B, void* C,
                   int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                   void* cuda_stream);
@@ -145,8 +146,11 @@ int emmyb200_gemm_f32(int epilogue, int flags, const float* A, const float* B, c
  * same rows live in each peer's copy of the full C (peer-mapped device memory). Run by every GPU of a group
  * on its own rows, it leaves the complete C on all of them: the kernel's own TMA stores over NVLink take the
  * place of a separate all-gather. All destinations share ldc and alignment rules. The caller synchronises
- * the group before reading rows written by peers. No counterpart in the reference, which is single-GPU
- * (tools/run_local.py:51-57); it serves the row-sharded configuration of the benchmark. */
+ * the group before reading rows written by peers. With EMMYB200_GEMM_DST_MULTICAST, n_dst is 1 and C_dst[0] is the
+ * address of this GPU's rows inside an NVSwitch multicast mapping of C (N a multiple of 8): every piece is then
+ * stored once with multimem.st and the switch delivers it to all GPUs of the group, this one included, so the
+ * GPU's outgoing NVLink traffic is its own shard instead of one copy per peer. No counterpart in the reference,
+ * which is single-GPU (tools/run_local.py:51-57); it serves the row-sharded configuration of the benchmark. */
 int emmyb200_gemm_allgather(int dtype, int epilogue, int flags, const void* A, const void* B, void* const* C_dst,
                             int n_dst, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                             void* cuda_stream);
@@ -158,6 +162,7 @@ int emmyb200_gemm_allgather(int dtype, int epilogue, int flags, const void* A, c
  * or 64, any seq_q, seq_k >= 1. EMMYB200_ATT_CAUSAL: query i attends to keys 0..i only (the lower-triangular
  * mask of tools/torch_cases/models.py:17-19, fused.py:31-36). */
 #define EMMYB200_ATT_CAUSAL 1
+#define EMMYB200_ATT_DST_MULTICAST 2    /* emmyb200_attention_fwd_allgather only, see there */
 int emmyb200_attention_fwd(int dtype, int flags, const void* Q, const void* K, const void* V, void* O,
                            int64_t units, int64_t seq_q, int64_t seq_k, int64_t d, float scale,
                            void* cuda_stream);
@@ -165,7 +170,8 @@ int emmyb200_attention_fwd(int dtype, int flags, const void* Q, const void* K, c
 /* The same attention on one GPU's share of the units, every output tile stored to n_dst destinations
  * (1..8): O_dst[0] is this GPU's own slice of O, the others the addresses, valid on this GPU, of the same
  * slice inside each peer's full O. No counterpart in the reference (single GPU); it serves the
- * (batch x head)-sharded configuration. The caller synchronises the group before reading peers' units. */
+ * (batch x head)-sharded configuration. The caller synchronises the group before reading peers' units.
+ * EMMYB200_ATT_DST_MULTICAST: n_dst = 1 and O_dst[0] is the multicast address of the slice (as for the GEMM). */
 int emmyb200_attention_fwd_allgather(int dtype, int flags, const void* Q, const void* K, const void* V,
                                      void* const* O_dst, int n_dst, int64_t units, int64_t seq_q,
                                      int64_t seq_k, int64_t d, float scale, void* cuda_stream);

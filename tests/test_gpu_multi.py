@@ -14,6 +14,58 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
+def _worker_multicast(rank: int, world: int, port: int):
+    """The same two kernels storing through the NVSwitch multicast mapping (one multimem.st per 16 bytes reaches both
+    copies). Where the fabric has no multicast the mapping's address is 0 and the case is skipped."""
+    import torch
+    import torch.distributed as dist
+    from emmyptx import runtime, shard
+    from oracle import inputs, reference
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        m, n, k = 1024, 768, 512
+        a, b = inputs.gemm_inputs(m, n, k, "bf16")
+        lo, hi = shard.split_range(m, world, rank, 128)
+        c_full, peers = shard.peer_mapped_empty((m, n), torch.bfloat16, dev, multicast=True)
+        mc = shard.multicast_address(peers)
+        flag = torch.tensor([1 if mc else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if flag.item() == 0:
+            print("no multicast mapping on this fabric: skipped")
+            return
+        c_full.zero_()
+        peers.barrier()
+        runtime.gemm_allgather(a[lo:hi].to(dev).contiguous(), b.to(dev), [mc + lo * n * 2], n, epilogue="gelu_tanh", multicast=True)
+        peers.barrier()
+        torch.cuda.synchronize()
+        assert runtime.device_status() == 0
+        local = runtime.gemm(a[lo:hi].to(dev).contiguous(), b.to(dev), epilogue="gelu_tanh")
+        gathered = shard.all_gather_rows(torch.empty(m, n, dtype=torch.bfloat16, device=dev), local)
+        assert torch.equal(gathered, c_full), f"rank {rank}: multicast GEMM differs from the gathered shards"
+        units, sq, sk, d = 4, 300, 260, 128
+        q, k, v = inputs.attention_inputs(units, sq, sk, d, "bf16")
+        ulo, uhi = shard.split_range(units, world, rank)
+        o_full, opeers = shard.peer_mapped_empty((units, sq, d), torch.bfloat16, dev, multicast=True)
+        omc = shard.multicast_address(opeers)
+        assert omc != 0
+        o_full.zero_()
+        opeers.barrier()
+        runtime.attention_allgather(q[ulo:uhi].to(dev).contiguous(), k[ulo:uhi].to(dev).contiguous(), v[ulo:uhi].to(dev).contiguous(),
+                                    [omc + ulo * sq * d * 2], multicast=True)
+        opeers.barrier()
+        torch.cuda.synchronize()
+        assert runtime.device_status() == 0
+        ok, ratio = reference.gemm_tolerance_ok(o_full.cpu(), reference.attention_reference(q, k, v))
+        assert ok, f"rank {rank}: multicast attention worst error {ratio:.2f}x the bound"
+        plain = runtime.attention(q.to(dev), k.to(dev), v.to(dev))
+        assert torch.equal(plain, o_full)
+    finally:
+        dist.destroy_process_group()
+
+
 def _worker(rank: int, world: int, port: int):
     import torch
     import torch.distributed as dist
@@ -67,3 +119,11 @@ def test_fused_gemm_allgather_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def test_multicast_stores_two_gpus():
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mp.spawn(_worker_multicast, args=(2, _free_port()), nprocs=2, join=True)
