@@ -44,6 +44,29 @@ def test_argument_checks_need_no_device(lib):
     assert lib.emmyb200_attention_fwd(2, 0, None, None, None, None, 1, 8, 8, 128, 1.0, None) == -1
 
 
+def test_newer_entry_points_check_their_arguments_without_a_device(lib):
+    """Row / column reductions, cumsum, the float32 product and the multicast flag: all rejected (or accepted as empty)
+    before any CUDA call."""
+    p = ctypes.c_void_p(4096)                                                  # never dereferenced
+    assert lib.emmyb200_rowwise_f32(0, None, None, None, None, 0, 8, 0.0, None, 0, None) == 0
+    assert lib.emmyb200_rowwise_f32(0, None, None, None, None, 4, 8, 0.0, None, 0, None) == -1
+    assert lib.emmyb200_rowwise_f32(12, p, None, None, p, 4, 8, 0.0, None, 0, None) == -1
+    assert lib.emmyb200_rowwise_workspace_bytes(16, 4, 1 << 20) > 0 and lib.emmyb200_rowwise_workspace_bytes(16, 4, 4096) == 0
+    assert lib.emmyb200_colwise_f32(19, p, p, 1, 4, 8, 0.0, None, 0, None) == -1  # rms_norm is a row op only
+    assert lib.emmyb200_colwise_f32(0, None, None, 0, 4, 8, 0.0, None, 0, None) == 0
+    assert lib.emmyb200_cumsum_f32(None, None, 4, 0, None) == 0
+    assert lib.emmyb200_cumsum_f32(None, None, 4, 8, None) == -1
+    assert lib.emmyb200_gemm_f32_workspace_bytes(0, 1, 128, 128, 128, 1) == 2 * 3 * 128 * 128 * 2
+    assert lib.emmyb200_gemm_f32(0, 0, p, p, None, p, 1, 8, 8, 8, 8, 8, 8, 0, 0, 0, None, 0, None) == -1 and b"workspace" in lib.emmyb200_last_error()
+    assert lib.emmyb200_gemm(2, 0, 2, p, p, p, 8, 8, 8, 8, 8, 8, None) == -1     # the multicast flag is for the allgather entry
+    dst = (ctypes.c_void_p * 2)(4096, 8192)
+    assert lib.emmyb200_gemm_allgather(2, 0, 2, p, p, dst, 2, 8, 8, 8, 8, 8, 8, None) == -1      # one multicast address, not two
+    assert lib.emmyb200_gemm_allgather(2, 0, 2, p, p, dst, 1, 8, 12, 8, 8, 16, 16, None) == -2    # N must be a multiple of 8
+    assert lib.emmyb200_attention_fwd(2, 2, p, p, p, p, 1, 8, 8, 128, 1.0, None) == -1
+    assert lib.emmyb200_attention_fwd_allgather(2, 2, p, p, p, dst, 2, 1, 8, 8, 128, 1.0, None) == -1
+    assert lib.emmyb200_rowwise_static_capacity() == 1 << 20
+
+
 def test_python_binding_refuses_cpu_tensors():
     import torch
     from emmyptx import runtime
