@@ -79,7 +79,7 @@ __device__ __forceinline__ St st_merge(St x, St y) {
     else if constexpr (K == K_MOM) {
         const float n = x.a + y.a;
         if (n == 0.0f) return x;
-        const float d = y.b - x.b, f = y.a / n;
+        const float d = y.b - x.b, f = __fdividef(y.a, n);      // counts are small integers: 2 ulp is plenty
         return {n, x.b + d * f, x.c + y.c + d * d * x.a * f};
     } else if constexpr (K == K_LSE) {
         const float m = nan_max(x.a, y.a);
@@ -106,7 +106,9 @@ template <int K>
 __device__ __forceinline__ St warp_allreduce(St s, int width, int lane) {
     for (int off = 1; off < width; off <<= 1) {
         const St o = st_shfl_xor<K>(s, off);
-        s = (lane & off) ? st_merge<K>(o, s) : st_merge<K>(s, o);
+        const bool upper = lane & off;
+        const St lo = upper ? o : s, hi = upper ? s : o;        // one merge per level, operands in lane order
+        s = st_merge<K>(lo, hi);
     }
     return s;
 }

@@ -59,7 +59,7 @@ struct ReduceSlabs {
 // All-reduce over a group of G consecutive threads (a part of a warp, a warp, or the whole CTA) and then, if the
 // CTA belongs to a cluster, over the CTAs of the cluster in rank order. Every thread returns the same bits.
 template <int K, int G>
-__device__ __forceinline__ St group_allreduce(St s, ReduceSlabs* slabs, int& round, uint32_t csize = 1) {
+__device__ __forceinline__ St group_allreduce(St s, ReduceSlabs* slabs, int& round) {
     const int lane = threadIdx.x & 31;
     s = warp_allreduce<K>(s, G < 32 ? G : 32, lane);
     if constexpr (G > 32) {
@@ -72,21 +72,29 @@ __device__ __forceinline__ St group_allreduce(St s, ReduceSlabs* slabs, int& rou
         else asm volatile("bar.sync %0, %1;" ::"r"(1 + (int)threadIdx.x / G), "n"(G) : "memory");      // the group only
         s = lane < G / 32 ? slab[first_warp + lane] : st_identity<K>();
         s = warp_allreduce<K>(s, 32, lane);                     // identities in the upper lanes: every lane gets the result
-        if (csize > 1) {
-            if (threadIdx.x == 0) slabs->cta[buf] = s;
-            cluster_barrier();
-            St o = st_identity<K>();
-            if ((uint32_t)lane < csize) {
-                o.a = peer_shared_load(&slabs->cta[buf].a, lane);
-                if constexpr (K == K_MOM || K == K_LSE) o.b = peer_shared_load(&slabs->cta[buf].b, lane);
-                if constexpr (K == K_MOM || K == K_ARG) o.c = peer_shared_load(&slabs->cta[buf].c, lane);
-            }
-            s = warp_allreduce<K>(o, 8, lane);                  // at most 8 CTAs, in lanes 0-7
-            s.a = __shfl_sync(0xffffffffu, s.a, 0);
-            if constexpr (K == K_MOM || K == K_LSE) s.b = __shfl_sync(0xffffffffu, s.b, 0);
-            if constexpr (K == K_MOM || K == K_ARG) s.c = __shfl_sync(0xffffffffu, s.c, 0);
-        }
     }
+    return s;
+}
+
+// All-reduce of per-CTA states (every thread of a CTA holding its CTA's) over the cluster, in rank order: one
+// hardware barrier, then each CTA reads its peers' states through distributed shared memory.
+template <int K>
+__device__ __forceinline__ St cluster_allreduce(St s, ReduceSlabs* slabs, int& cround, uint32_t csize) {
+    const int lane = threadIdx.x & 31;
+    const int buf = cround & 1;
+    ++cround;
+    if (threadIdx.x == 0) slabs->cta[buf] = s;
+    cluster_barrier();
+    St o = st_identity<K>();
+    if ((uint32_t)lane < csize) {
+        o.a = peer_shared_load(&slabs->cta[buf].a, lane);
+        if constexpr (K == K_MOM || K == K_LSE) o.b = peer_shared_load(&slabs->cta[buf].b, lane);
+        if constexpr (K == K_MOM || K == K_ARG) o.c = peer_shared_load(&slabs->cta[buf].c, lane);
+    }
+    s = warp_allreduce<K>(o, 8, lane);                          // at most 8 CTAs, in lanes 0-7
+    s.a = __shfl_sync(0xffffffffu, s.a, 0);
+    if constexpr (K == K_MOM || K == K_LSE) s.b = __shfl_sync(0xffffffffu, s.b, 0);
+    if constexpr (K == K_MOM || K == K_ARG) s.c = __shfl_sync(0xffffffffu, s.c, 0);
     return s;
 }
 
@@ -112,7 +120,7 @@ __global__ void __launch_bounds__(256) rowwise_cached_kernel(RowArgs a) {
     constexpr int kRowsPerBlock = 256 / G;
     constexpr int kIter = kPerThread / VEC;
     __shared__ ReduceSlabs slabs;
-    int round = 0;
+    int round = 0, cround = 0;
     const uint32_t csize = G == 256 ? cluster_size() : 1u;
     const uint32_t crank = G == 256 ? cluster_rank() : 0u;
     const int t = threadIdx.x % G, g = threadIdx.x / G;
@@ -177,9 +185,11 @@ __global__ void __launch_bounds__(256) rowwise_cached_kernel(RowArgs a) {
             }
         }
         const float own = s.a;                                  // this thread's extremum (argmax looks only where it is the row's)
-        s = group_allreduce<K1, G>(s, &slabs, round, csize);
+        s = group_allreduce<K1, G>(s, &slabs, round);           // over the row, or over this CTA's slice of it
         if constexpr (K == K_MOM || K == K_LSE || K == K_ARG) {
-            const float centre = K == K_MOM ? s.a / (float)cols : s.a;      // the mean, or the max
+            // of the slice this CTA holds (the whole row without a cluster): its mean, or its max
+            const int held = min(cols - slice_end, kIter * G * VEC);
+            const float centre = K == K_MOM ? (held > 0 ? s.a / (float)held : 0.0f) : s.a;
             const bool max_is_nan = centre != centre;
             int hit = INT_MAX;
             St s2 = st_identity<K == K_ARG ? K_MIN : K_ADD>();
@@ -197,7 +207,7 @@ __global__ void __launch_bounds__(256) rowwise_cached_kernel(RowArgs a) {
                             const float d = x - centre;
                             s2.a = fmaf(d, d, s2.a);
                         } else if constexpr (K == K_LSE) {
-                            const float p = exp_le0(x - centre);
+                            const float p = centre == -CUDART_INF_F ? 0.0f : exp_le0(x - centre);
                             s2.a += p;
                             if constexpr (OP == EMMYB200_ROW_SOFTMAX) v[VEC * i + e] = p;
                         } else {
@@ -208,10 +218,14 @@ __global__ void __launch_bounds__(256) rowwise_cached_kernel(RowArgs a) {
             }
             // columns < 2^24 are exact as floats; INT_MAX stands for "none here"
             if constexpr (K == K_ARG) s2.a = hit == INT_MAX ? (float)INT_MAX : (float)(hit + first * VEC);
-            s2 = group_allreduce<K == K_ARG ? K_MIN : K_ADD, G>(s2, &slabs, round, csize);
-            if constexpr (K == K_MOM) s = {(float)cols, centre, s2.a};
+            s2 = group_allreduce<K == K_ARG ? K_MIN : K_ADD, G>(s2, &slabs, round);
+            if constexpr (K == K_MOM) s = {(float)max(held, 0), centre, s2.a};
             else if constexpr (K == K_LSE) s = {centre, s2.a, 0.0f};
             else s = {centre, 0.0f, __int_as_float((int)s2.a)};
+        }
+        const float own_centre = s.a;                           // softmax: the max the held exponentials were taken against
+        if constexpr (G == 256) {
+            if (csize > 1) s = cluster_allreduce<K>(s, &slabs, cround, csize);      // one exchange of whole states per row
         }
         const float2 r = row_finish<OP>(s, (float)cols, a.eps);
 
@@ -219,6 +233,11 @@ __global__ void __launch_bounds__(256) rowwise_cached_kernel(RowArgs a) {
             if (live && t == 0 && crank == 0) store_reduced<OP>(a.y, row, s, r);
         } else {
             float* yr = static_cast<float*>(a.y) + row * a.cols;
+            // softmax: exp(x - row max) / sum = the held exp(x - slice max) * exp(slice max - row max) / sum
+            float soft = r.y;
+            if constexpr (OP == EMMYB200_ROW_SOFTMAX && G == 256) {
+                if (csize > 1) soft = exp_le0(own_centre - r.x) * r.y;
+            }
 #pragma unroll
             for (int i = 0; i < kIter; ++i) {
                 if (slice_end + i * G * VEC >= cols) break;
@@ -238,7 +257,7 @@ __global__ void __launch_bounds__(256) rowwise_cached_kernel(RowArgs a) {
                     }
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) {
-                        if constexpr (OP == EMMYB200_ROW_SOFTMAX) o[e] = v[VEC * i + e] * r.y;      // the exponential is held
+                        if constexpr (OP == EMMYB200_ROW_SOFTMAX) o[e] = v[VEC * i + e] * soft;     // the exponential is held
                         else o[e] = row_map<OP>(v[VEC * i + e], r, wv[e], bv[e]);
                     }
                     if constexpr (VEC == 4) __stcs(reinterpret_cast<float4*>(yr + c), make_float4(o[0], o[1], o[2], o[3]));
