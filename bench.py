@@ -156,7 +156,12 @@ class GemmWorkload(Workload):
         if self.gather and self.mode in ("fused", "multicast"):
             # The full C lives in peer-mapped memory on every rank; each rank's kernel writes its rows into all of them.
             from emmyptx import shard
-            self.c_full, self.peers = shard.peer_mapped_empty((m, n), td, dev, multicast=self.mode == "multicast")
+            try:
+                self.c_full, self.peers = shard.peer_mapped_empty((m, n), td, dev, multicast=self.mode == "multicast")
+            except Exception as e:  # noqa: BLE001 - no peer mapping on this box: gather with NCCL instead
+                print(f"[bench] peer-mapped memory unavailable ({type(e).__name__}: {e}); gathering with NCCL", file=sys.stderr)
+                self.mode = "nccl"
+        if self.gather and self.mode in ("fused", "multicast"):
             off = rank * self.rows * n * self.c_full.element_size()
             own = self.c_full.data_ptr() + off
             if self.mode == "multicast" and not group_has_multicast(shard.multicast_address(self.peers), dev):
@@ -302,7 +307,12 @@ class AttentionWorkload(Workload):
         self.mode = os.environ.get("EMMYB200_BENCH_GATHER", "multicast")
         if self.gather and self.mode in ("fused", "multicast"):
             from emmyptx import shard
-            self.o_full, self.peers = shard.peer_mapped_empty((units, seq, d), torch.bfloat16, dev, multicast=self.mode == "multicast")
+            try:
+                self.o_full, self.peers = shard.peer_mapped_empty((units, seq, d), torch.bfloat16, dev, multicast=self.mode == "multicast")
+            except Exception as e:  # noqa: BLE001
+                print(f"[bench] peer-mapped memory unavailable ({type(e).__name__}: {e}); gathering with NCCL", file=sys.stderr)
+                self.mode = "nccl"
+        if self.gather and self.mode in ("fused", "multicast"):
             off = rank * self.local * seq * d * 2
             if self.mode == "multicast" and not group_has_multicast(shard.multicast_address(self.peers), dev):
                 self.mode = "fused"
