@@ -230,6 +230,50 @@ def gemm_batched(a, b, bias=None, epilogue: str | None = None, b_is_nk: bool = F
     return out
 
 
+class HostGemm:
+    """epilogue(A @ B) with A, B and C in pinned host memory: B is copied to the device once per call, A in row chunks
+    on a copy stream, and each chunk's product is copied back on a third stream while the next chunk is on its way
+    in and being multiplied, so that a call costs about as long as the larger of its host-to-device copies and its
+    arithmetic instead of their sum. Device buffers are allocated once, in the constructor."""
+
+    def __init__(self, m: int, n: int, k: int, dtype, device, epilogue: str | None = None, chunks: int = 16):
+        import torch
+        while chunks > 1 and (m % chunks or (m // chunks) % 128):
+            chunks -= 1                                                        # whole row blocks per chunk
+        self.m, self.n, self.k, self.epilogue, self.chunks, self.rows = m, n, k, epilogue, chunks, m // chunks
+        self.a = torch.empty(m, k, dtype=dtype, device=device)
+        self.b = torch.empty(k, n, dtype=dtype, device=device)
+        self.c = torch.empty(m, n, dtype=dtype, device=device)
+        self.copy_in, self.copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        self.ev_in = [torch.cuda.Event() for _ in range(chunks + 1)]
+        self.ev_done = [torch.cuda.Event() for _ in range(chunks)]
+
+    def __call__(self, a_host, b_host, c_host, stream=None):
+        """Enqueue the whole call; `c_host` is complete when `stream` (default: the current one) has caught up."""
+        import torch
+        main = torch.cuda.current_stream() if stream is None else stream
+        self.copy_in.wait_stream(main)                                         # the buffers may still be in use by earlier work
+        self.copy_out.wait_stream(main)
+        with torch.cuda.stream(self.copy_in):
+            self.b.copy_(b_host, non_blocking=True)
+            self.ev_in[0].record()
+            for i in range(self.chunks):
+                rows = slice(i * self.rows, (i + 1) * self.rows)
+                self.a[rows].copy_(a_host[rows], non_blocking=True)
+                self.ev_in[i + 1].record()
+        main.wait_event(self.ev_in[0])
+        for i in range(self.chunks):
+            rows = slice(i * self.rows, (i + 1) * self.rows)
+            main.wait_event(self.ev_in[i + 1])
+            gemm(self.a[rows], self.b, epilogue=self.epilogue, out=self.c[rows], stream=main)
+            self.ev_done[i].record(main)
+            with torch.cuda.stream(self.copy_out):
+                self.copy_out.wait_event(self.ev_done[i])
+                c_host[rows].copy_(self.c[rows], non_blocking=True)
+        main.wait_stream(self.copy_out)
+        return c_host
+
+
 def gemm_f32(a, b, bias=None, epilogue: str | None = None, b_is_nk: bool = False, out=None, workspace=None, stream=None):
     """float32 matmul with float32 accuracy on the tensor cores. a: [M, K] or [batch, M, K]; b: [K, N] ([N, K] with
     b_is_nk), shared by every product, or [batch, K, N]; bias: [N] or None. Last axes must be contiguous."""

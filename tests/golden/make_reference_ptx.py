@@ -1,6 +1,6 @@
 """Generate the reference's own PTX for the two streaming configurations (and a small GEMM), as fixtures.
 
-    python tests/golden/make_reference_ptx.py [/root/reference]
+    python tests/golden/make_reference_ptx.py <path to a checkout of the reference>
 
 Needs the reference checkout (read-only) and nothing else: its `KernelCompiler` dispatches on class *names*, so
 the stand-in IR classes of `emmy-ptx-compiler_b200/emmyptx/ir.py` drive it. The PTX text it prints is the
@@ -15,7 +15,9 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) != 2:
+    sys.exit(__doc__)
+ref = Path(sys.argv[1])
 sys.path.insert(0, str(ref))
 from emmyptx.kernel import compile_kernel  # noqa: E402  (the reference's)
 

@@ -162,3 +162,21 @@ def test_bias_and_relu_epilogue(epilogue, dtype, cuda):
     assert ok, f"worst error {ratio:.2f}x the bound"
     if epilogue == "relu":
         assert (got >= 0).all()
+
+
+def test_host_buffer_call_overlaps_copies_and_matches_the_device_call(cuda):
+    """runtime.HostGemm: pinned host A, B in, C out, in row chunks on three streams; same bits as one device call."""
+    import torch
+    from emmyptx import runtime
+    m, n, k = 1024, 384, 256
+    a, b = inputs.gemm_inputs(m, n, k, "bf16")
+    a_h, b_h = a.pin_memory(), b.pin_memory()
+    c_h = torch.zeros(m, n, dtype=torch.bfloat16).pin_memory()
+    call = runtime.HostGemm(m, n, k, torch.bfloat16, cuda, epilogue="gelu_tanh", chunks=4)
+    assert call.chunks == 4 and call.rows == 256
+    for _ in range(2):                                   # twice: the second call must wait for the first one's buffers
+        call(a_h, b_h, c_h)
+    torch.cuda.synchronize()
+    expect = runtime.gemm(a.to(cuda), b.to(cuda), epilogue="gelu_tanh").cpu()
+    assert torch.equal(c_h, expect)
+    assert runtime.HostGemm(300, 64, 64, torch.bfloat16, cuda, chunks=8).chunks == 1     # no whole-block split: one chunk
