@@ -37,7 +37,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # under profiles/ (c4: captured at M=N=K=8192 and scaled by the 8x flops of the full size; c5: captured on 64 of the 256
 # units and scaled by 4; c2, c3: captured at full size; c1: 8 MiB working set, L2-resident, no DRAM figure).
 DRAM_TRAFFIC = {"c4": 8 * (1.018008e9 + 0.125913e9), "c5": 4 * (201.44e6 + 49.98e6), "c2": 268.97e6 + 222.76e6,
-                "c3": 83.01e6 + 14.28e6, "c1": None, "softmax": 268.46e6 + 216.40e6}
+                "c3": 83.01e6 + 14.28e6, "c1": None, "softmax": 268.46e6 + 216.40e6, "f32mm": None}
 
 WORKLOADS = {
     "c1": "fp32 exp(x)+sin(x)*tanh(x), N=2^20, x~U[-4,4]",
@@ -45,6 +45,7 @@ WORKLOADS = {
     "c3": "fp16 GEMM M=N=K=4096, fp32 accumulate, fp16 out",
     "c4": "bf16 GEMM + tanh-GELU epilogue M=N=K=16384, fp32 accumulate, bf16 out, M-row shards",
     "c5": "bf16 attention fwd B16 H16 S4096 d128, non-causal, fp32 softmax, (batch x head) shards",
+    "f32mm": "fp32 matmul M=N=K=4096 with fp32 accuracy (three-way bf16 split on the tensor cores; not one of the five configurations)",
     "softmax": "fp32 softmax over the last axis of [65536, 1024] (the row kernels; not one of the five configurations)",
 }
 
@@ -256,6 +257,47 @@ class PointwiseWorkload(Workload):
         self.host["y"].copy_(self.y, non_blocking=True)
 
 
+class GemmF32Workload(Workload):
+    """emmyb200_gemm_f32 on square fp32 operands; one step = split kernels + the six-pass GEMM."""
+    metric, unit, bound, dtype = "gemm_tflops", "TFLOP/s", "tensor", "f32"
+
+    def __init__(self, s, rank, world, dev):
+        import torch
+        from emmyptx import runtime
+        self.rt, self.torch, self.world, self.s, self.name = runtime, torch, world, s, "f32mm"
+        g = torch.Generator(device=dev)
+        g.manual_seed(rank)
+        self.a = torch.randn(s, s, device=dev, generator=g) / s**0.5
+        self.b = torch.randn(s, s, device=dev, generator=g) / s**0.5
+        self.c = torch.empty(s, s, device=dev)
+        need = runtime.library().emmyb200_gemm_f32_workspace_bytes(0, 1, s, s, s, 1)
+        self.ws = torch.empty(need, dtype=torch.uint8, device=dev)
+
+    def step(self):
+        self.rt.gemm_f32(self.a, self.b, out=self.c, workspace=self.ws)
+
+    kernel_only = step
+
+    def launches_per_step(self):
+        return 3
+
+    def work_per_step(self):
+        return 2.0 * self.s**3 * self.world
+
+    def kernel_work_per_launch(self):
+        return 2.0 * self.s**3
+
+    def e2e_setup(self):
+        self.host = {"a": self.a.cpu().pin_memory(), "b": self.b.cpu().pin_memory(), "c": self.c.cpu().pin_memory()}
+        return 2 * self.s * self.s * 4, self.s * self.s * 4
+
+    def e2e_step(self):
+        self.a.copy_(self.host["a"], non_blocking=True)
+        self.b.copy_(self.host["b"], non_blocking=True)
+        self.step()
+        self.host["c"].copy_(self.c, non_blocking=True)
+
+
 class RowWorkload(PointwiseWorkload):
     """A row kernel on [rows, 1024] fp32; `n` counts elements. Rows shard across ranks like C1's chunks."""
 
@@ -387,6 +429,8 @@ def make_workload(name, rank, world, dev, size=None):
         return GatherWorkload(size or 2**26, rank, world, dev)
     if name == "softmax":
         return RowWorkload("softmax", size or 65536 * 1024, rank, world, dev)
+    if name == "f32mm":
+        return GemmF32Workload(size or 4096, rank, world, dev)
     raise SystemExit(f"unknown workload {name!r}")
 
 
@@ -475,6 +519,10 @@ def cpu_reference_step(name: str, threads: int):
         x = torch.from_numpy(inputs.c2_input(n))
         fn = lambda: reference.c2_torch(x)
         return fn, 8.0 * n, 1e9, "the full 2^26 array, torch CPU int32/int64"
+    if name == "f32mm":
+        g = torch.Generator().manual_seed(0)
+        a, b = torch.randn(4096, 4096, generator=g), torch.randn(4096, 4096, generator=g)
+        return (lambda: a @ b), 2.0 * 4096**3, 1e12, "the full 4096^3 product, torch CPU fp32"
     if name == "softmax":
         x = torch.randn(65536, 1024, generator=torch.Generator().manual_seed(0))
         fn = lambda: torch.softmax(x, -1)
@@ -515,7 +563,7 @@ def run_reference(args, rank: int) -> int:
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": {"c1": "f32", "c2": "i32", "c3": "f16", "softmax": "f32"}.get(args.workload, "bf16"), "data": "synthetic",
+        "vs_baseline": None, "dtype": {"c1": "f32", "c2": "i32", "c3": "f16", "softmax": "f32", "f32mm": "f32"}.get(args.workload, "bf16"), "data": "synthetic",
         "config": {"workload": w0, "note": "each step is a bounded sample of the workload on the host cores"},
         "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "reference", "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
