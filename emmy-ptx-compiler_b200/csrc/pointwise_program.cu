@@ -82,6 +82,7 @@ __device__ __forceinline__ float4 pw_load4(const void* base, int64_t v) {
 
 __device__ __forceinline__ float pw_load1(const void* base, int dtype, int64_t i) {
     if (dtype == EMMYB200_F32) return reinterpret_cast<const float*>(base)[i];
+    if (dtype == EMMYB200_U8) return reinterpret_cast<const uint8_t*>(base)[i] ? 1.0f : 0.0f;
     if (dtype == EMMYB200_F16) return __half2float(reinterpret_cast<const __half*>(base)[i]);
     return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[i]);
 }
@@ -117,8 +118,13 @@ __global__ void __launch_bounds__(kPwThreads) pointwise_program_kernel(const __g
                 if (g < groups) {
                     if constexpr (VEC) {
                         const int dt = prog.in_dtype[k];
-                        v = dt == EMMYB200_F32 ? pw_load4<float>(args.in[k], g)
-                          : dt == EMMYB200_F16 ? pw_load4<__half>(args.in[k], g) : pw_load4<__nv_bfloat16>(args.in[k], g);
+                        if (dt == EMMYB200_U8) {
+                            const uchar4 m = __ldcs(reinterpret_cast<const uchar4*>(args.in[k]) + g);
+                            v = make_float4(m.x ? 1.0f : 0.0f, m.y ? 1.0f : 0.0f, m.z ? 1.0f : 0.0f, m.w ? 1.0f : 0.0f);
+                        } else {
+                            v = dt == EMMYB200_F32 ? pw_load4<float>(args.in[k], g)
+                              : dt == EMMYB200_F16 ? pw_load4<__half>(args.in[k], g) : pw_load4<__nv_bfloat16>(args.in[k], g);
+                        }
                     } else {
                         const int64_t i = g * 4;
                         v.x = pw_load1(args.in[k], prog.in_dtype[k], i);
@@ -188,7 +194,73 @@ __global__ void __launch_bounds__(kPwThreads) pointwise_program_kernel(const __g
     }
 }
 
-static int elem_size(int dtype) { return dtype == EMMYB200_F32 ? 4 : 2; }
+// ---- integer programs: 32-bit two's complement values, one element per thread and trip ----------------------------
+__device__ __forceinline__ int pw_apply_int(int op, int a, int b, int c, int trunc) {
+    const unsigned ua = (unsigned)a, ub = (unsigned)b;
+    switch (op) {
+        case EMMYB200_PW_ADD: return (int)(ua + ub);
+        case EMMYB200_PW_SUB: return (int)(ua - ub);
+        case EMMYB200_PW_MUL: return (int)(ua * ub);
+        case EMMYB200_PW_MAX: return max(a, b);
+        case EMMYB200_PW_MIN: return min(a, b);
+        case EMMYB200_PW_RELU: return max(a, 0);
+        case EMMYB200_PW_SQUARE: return (int)(ua * ua);
+        case EMMYB200_PW_NEG: return (int)(0u - ua);
+        case EMMYB200_PW_ABS: return a < 0 ? (int)(0u - ua) : a;
+        case EMMYB200_PW_EQ: return a == b;
+        case EMMYB200_PW_NE: return a != b;
+        case EMMYB200_PW_GT: return a > b;
+        case EMMYB200_PW_LT: return a < b;
+        case EMMYB200_PW_GE: return a >= b;
+        case EMMYB200_PW_LE: return a <= b;
+        case EMMYB200_PW_WHERE: return a != 0 ? b : c;
+        case EMMYB200_PW_AND: return a & b;
+        case EMMYB200_PW_OR: return a | b;
+        case EMMYB200_PW_NOT: return ~a;
+        case EMMYB200_PW_XOR: return a ^ b;
+        case EMMYB200_PW_SHL: return (int)(ua << (ub & 31u));
+        case EMMYB200_PW_SHR: return a >> (ub & 31u);
+        case EMMYB200_PW_DIV:
+        case EMMYB200_PW_FLOORDIV: {
+            if (b == 0) return 0;
+            if (b == -1) return (int)(0u - ua);                 // INT_MIN / -1 wraps
+            int q = a / b;
+            if (!trunc && (a % b != 0) && ((a < 0) != (b < 0))) --q;
+            return q;
+        }
+        case EMMYB200_PW_MOD: {
+            if (b == 0 || b == -1) return 0;
+            int r = a % b;
+            if (!trunc && r != 0 && ((r < 0) != (b < 0))) r += b;
+            return r;
+        }
+        default: return a;                                      // COPY
+    }
+}
+
+__device__ __forceinline__ int pw_load_int(const void* base, int dtype, int64_t i) {
+    return dtype == EMMYB200_I32 ? reinterpret_cast<const int*>(base)[i] : (int)reinterpret_cast<const long long*>(base)[i];
+}
+
+__global__ void __launch_bounds__(kPwThreads) pointwise_program_int_kernel(const __grid_constant__ emmyb200_pw_program prog, PwArgs args) {
+    const int64_t stride = (int64_t)gridDim.x * kPwThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kPwThreads + threadIdx.x; i < args.n; i += stride) {
+        int regs[kPwSlots];
+        for (int k = 0; k < prog.n_inputs; ++k) regs[k] = pw_load_int(args.in[k], prog.in_dtype[k], i);
+        for (int s = 0; s < prog.n_steps; ++s) {
+            const emmyb200_pw_step st = prog.steps[s];
+            auto operand = [&](int o) { return o >= kPwSlots ? (int)prog.consts[o - kPwSlots] : regs[o]; };
+            regs[st.dst] = pw_apply_int(st.op, operand(st.a), operand(st.b), operand(st.c), st.reserved[0]);
+        }
+        const int y = regs[prog.out_slot];
+        if (prog.out_dtype == EMMYB200_I32) reinterpret_cast<int*>(args.out)[i] = y;
+        else reinterpret_cast<long long*>(args.out)[i] = (long long)y;
+    }
+}
+
+static int elem_size(int dtype) {
+    return dtype == EMMYB200_F32 || dtype == EMMYB200_I32 ? 4 : (dtype == EMMYB200_I64 ? 8 : (dtype == EMMYB200_U8 ? 1 : 2));
+}
 
 }  // namespace emmy
 
@@ -199,10 +271,15 @@ extern "C" int emmyb200_pointwise_program(const emmyb200_pw_program* prog, const
     if (prog->n_inputs < 1 || prog->n_inputs > EMMYB200_PW_MAX_INPUTS) return fail(EMMYB200_ERR_ARG, "pointwise_program: %d inputs (1 to %d)", prog->n_inputs, EMMYB200_PW_MAX_INPUTS);
     if (prog->n_steps < 0 || prog->n_steps > EMMYB200_PW_MAX_STEPS) return fail(EMMYB200_ERR_ARG, "pointwise_program: %d steps (0 to %d)", prog->n_steps, EMMYB200_PW_MAX_STEPS);
     if (prog->out_slot < 0 || prog->out_slot >= kPwSlots) return fail(EMMYB200_ERR_ARG, "pointwise_program: output slot %d", prog->out_slot);
-    auto dtype_ok = [](int d) { return d == EMMYB200_F32 || d == EMMYB200_F16 || d == EMMYB200_BF16; };
-    if (!dtype_ok(prog->out_dtype)) return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_program: output dtype %d", prog->out_dtype);
-    for (int k = 0; k < prog->n_inputs; ++k)
-        if (!dtype_ok(prog->in_dtype[k])) return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_program: input %d has dtype %d", k, prog->in_dtype[k]);
+    const bool int_program = prog->out_dtype == EMMYB200_I32 || prog->out_dtype == EMMYB200_I64;
+    auto float_ok = [](int d) { return d == EMMYB200_F32 || d == EMMYB200_F16 || d == EMMYB200_BF16; };
+    auto int_ok = [](int d) { return d == EMMYB200_I32 || d == EMMYB200_I64; };
+    if (!int_program && !float_ok(prog->out_dtype)) return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_program: output dtype %d", prog->out_dtype);
+    for (int k = 0; k < prog->n_inputs; ++k) {
+        const int d = prog->in_dtype[k];
+        if (int_program ? !int_ok(d) : !(float_ok(d) || d == EMMYB200_U8))
+            return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_program: input %d has dtype %d (%s program)", k, d, int_program ? "an integer" : "a float");
+    }
     for (int s = 0; s < prog->n_steps; ++s) {
         const emmyb200_pw_step& st = prog->steps[s];
         if (st.op >= EMMYB200_PW_OP_COUNT) return fail(EMMYB200_ERR_ARG, "pointwise_program: step %d has unknown op %d", s, st.op);
@@ -230,6 +307,11 @@ extern "C" int emmyb200_pointwise_program(const emmyb200_pw_program* prog, const
     const int64_t want = (groups + kPwThreads * kPwUnroll - 1) / (kPwThreads * kPwUnroll);
     const int64_t cap = (int64_t)sm_count() * 8;
     const unsigned blocks = (unsigned)(want < cap ? want : cap);
+    if (int_program) {
+        const int64_t want_i = (n + kPwThreads - 1) / kPwThreads;
+        pointwise_program_int_kernel<<<(unsigned)(want_i < cap ? want_i : cap), kPwThreads, 0, s>>>(*prog, args);
+        return launch_status("pointwise_program_int_kernel");
+    }
     if (vec) pointwise_program_kernel<true><<<blocks, kPwThreads, 0, s>>>(*prog, args);
     else pointwise_program_kernel<false><<<blocks, kPwThreads, 0, s>>>(*prog, args);
     return launch_status("pointwise_program_kernel");

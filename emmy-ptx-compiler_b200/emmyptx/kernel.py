@@ -86,7 +86,7 @@ def algorithmic_work(handle: dict) -> tuple[float, str]:
     if v in ("pointwise_f32", "index_gather_i32"):
         return 8.0 * p["n"], "B"
     if v == "pointwise_program":
-        size = {"f32": 4, "f16": 2, "bf16": 2}
+        size = {"f32": 4, "f16": 2, "bf16": 2, "i32": 4, "int": 4, "i64": 8, "bool": 1, "u8": 1}
         return float(p["n"]) * (sum(size[d] for d in p["program"]["in_dtypes"]) + size[p["program"]["out_dtype"]]), "B"
     if v == "gemm":
         return 2.0 * p["m"] * p["n"] * p["k"], "flop"

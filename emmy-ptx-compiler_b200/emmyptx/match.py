@@ -245,9 +245,10 @@ PW_OP_NAMES = {"add", "subtract", "multiply", "divide", "maximum", "minimum", "r
                "bitwise_not", "floor_divide", "mod", "remainder"}
 
 
-def build_program(tile, tensors: dict, out_name: str, out_value_name) -> dict:
+def build_program(tile, tensors: dict, out_name: str, out_value_name, integer: bool = False) -> dict:
     """The tile's cell program as data for the general elementwise kernel: inputs in slots 0.., one slot per live
-    value (slots are reused once a value is dead), numeric operands in the constant table."""
+    value (slots are reused once a value is dead), numeric operands in the constant table. `integer`: an s32 program
+    (every Assign integer-typed, ops from the integer table, constants whole numbers)."""
     stmts = list(tile.body)
     inputs, slot_of = [], {}
     for s in stmts:
@@ -269,9 +270,11 @@ def build_program(tile, tensors: dict, out_name: str, out_value_name) -> dict:
     free = [k for k in range(PW_SLOTS - 1, len(inputs) - 1, -1)]
     consts, steps = [], []
     for i, s in enumerate(assigns):
-        if _dtype_name(s.dtype) in INT_DTYPES:
-            raise Unmatched("integer Assigns have no general kernel (only the index gather)")
-        if s.op.name not in PW_OP_NAMES:
+        if (_dtype_name(s.dtype) in INT_DTYPES) != integer:
+            raise Unmatched("a cell program mixing integer and float Assigns has no kernel")
+        if integer and s.op.name not in INT_OPS:
+            raise OpError(f"integer elementwise op {s.op.name!r} is not supported")
+        if not integer and s.op.name not in PW_OP_NAMES:
             raise OpError(f"elementwise op {s.op.name!r} is not supported")
         ops = []
         for a in s.args:
@@ -281,6 +284,8 @@ def build_program(tile, tensors: dict, out_name: str, out_value_name) -> dict:
                 ops.append(slot_of[a])
             else:
                 v = float(a)
+                if integer and (v != int(v) or abs(v) >= 2**24):
+                    raise Unmatched(f"integer constant {a!r} does not fit the program's constant table")
                 if v not in consts:
                     consts.append(v)
                 if len(consts) > PW_CONSTS:
@@ -330,7 +335,15 @@ def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict
     if any(cnt != 1 for _, _, cnt in it.loads):
         raise Unmatched("streaming variants read one element per load")
     float_types = ("f32", "f16", "bf16")
-    general = (tensors[out_name][1] in float_types and all(tensors[b][1] in float_types for b in buffers)
+    int_types = ("i32", "i64", "int")
+    identity = all(np.array_equal(i, cells) for _, i, _ in it.loads) and all(math.prod(tensors[b][0]) == n for b in buffers)
+    if identity and tensors[out_name][1] in int_types and all(tensors[b][1] in int_types for b in buffers) and buffers:
+        # an integer expression of element i of every buffer: the s32 program kernel (the gather is the other integer kernel)
+        prog = build_program(tile, tensors, out_name, tile.body[-1].values[0] if _kind(tile.body[-1]) == "Write" else None, integer=True)
+        prog["int_div"] = int_div
+        return {"variant": "pointwise_program", "params": {"n": n, "program": {k: v for k, v in prog.items() if k != "inputs"}},
+                "inputs": prog["inputs"], "outputs": [out_name]}
+    general = (tensors[out_name][1] in float_types and all(tensors[b][1] in float_types + ("bool", "u8") for b in buffers)
                and all(np.array_equal(i, cells) for _, i, _ in it.loads)
                and all(math.prod(tensors[b][0]) == n for b in buffers))
     if general and not (len(buffers) == 1 and tensors[next(iter(buffers))][1] == "f32" and tensors[out_name][1] == "f32"):

@@ -21,8 +21,10 @@ PW_OPS = {name: i for i, name in enumerate(
     ["add", "subtract", "multiply", "divide", "maximum", "minimum", "relu", "square", "copy", "negative", "abs", "reciprocal",
      "sqrt", "rsqrt", "exp", "log", "sigmoid", "tanh", "erf", "sin", "cos", "pow", "equal", "not_equal", "greater", "less",
      "greater_equal", "less_equal", "where", "bitwise_and", "bitwise_or", "bitwise_not", "floor_divide", "mod"])}
+PW_OPS.update(bitwise_xor=len(PW_OPS), left_shift=len(PW_OPS) + 1, right_shift=len(PW_OPS) + 2)
 PW_OPS.update(exp_fast=PW_OPS["exp"], remainder=PW_OPS["mod"])
-DTYPE_CODES = {"f32": F32, "f16": F16, "bf16": BF16, "i32": I32}
+I64, U8 = 4, 5
+DTYPE_CODES = {"f32": F32, "f16": F16, "bf16": BF16, "i32": I32, "i64": I64, "int": I32, "bool": U8, "u8": U8}
 
 
 class PwStep(ctypes.Structure):
@@ -154,7 +156,8 @@ def pointwise(op: str, x, out=None, stream=None):
 
 def make_program(program: dict) -> PwProgram:
     """The C struct for a program in the form the matcher emits: {"in_dtypes": [...], "out_dtype": ..., "out_slot": k,
-    "consts": [...], "steps": [[op name, dst, a, b, c], ...]} (operands >= PW_MAX_SLOTS name constants)."""
+    "consts": [...], "steps": [[op name, dst, a, b, c], ...]} (operands >= PW_MAX_SLOTS name constants). An integer
+    program (output i32 / i64) may carry "int_div": "trunc" to round `//` and `%` toward zero."""
     p = PwProgram()
     p.n_inputs, p.n_steps = len(program["in_dtypes"]), len(program["steps"])
     p.out_slot, p.out_dtype = program["out_slot"], DTYPE_CODES[program["out_dtype"]]
@@ -164,6 +167,7 @@ def make_program(program: dict) -> PwProgram:
         p.consts[i] = c
     for i, (op, dst, a, b, c) in enumerate(program["steps"]):
         p.steps[i].op, p.steps[i].dst, p.steps[i].a, p.steps[i].b, p.steps[i].c = PW_OPS[op], dst, a, b, c
+        p.steps[i].reserved[0] = 1 if program.get("int_div") == "trunc" else 0
     return p
 
 

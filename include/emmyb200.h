@@ -38,6 +38,8 @@ extern "C" {
 #define EMMYB200_F16 1
 #define EMMYB200_BF16 2
 #define EMMYB200_I32 3
+#define EMMYB200_I64 4   /* integer programs only: computed in 32 bits, as the reference does (emmyptx/kernel.py:41) */
+#define EMMYB200_U8 5    /* a bool / byte input of a float program: 0 or 1 */
 
 int emmyb200_version(void);
 
@@ -61,7 +63,12 @@ int emmyb200_pointwise_f32(int op, const float* x, float* y, int64_t n, void* cu
  * statement) handed over as data. Values are fp32 (the reference's only compute type, emmyptx/kernel.py:31-38);
  * f16 / bf16 buffers are widened on load and rounded once on store. A step computes
  * slot[dst] = op(operand a, b, c); an operand < EMMYB200_PW_MAX_SLOTS names a slot, otherwise constant
- * consts[operand - EMMYB200_PW_MAX_SLOTS]. Inputs arrive in slots 0 .. n_inputs-1; `out_slot` is stored. */
+ * consts[operand - EMMYB200_PW_MAX_SLOTS]. Inputs arrive in slots 0 .. n_inputs-1; `out_slot` is stored.
+ * Float programs may also read U8 buffers (bool masks, as 0 / 1). A program whose output is I32 or I64 is an integer
+ * program (the s32 table of emmyptx/ops.py:294-309 and emmyptx/intmath.py): every buffer is I32 or I64, values are
+ * 32-bit two's complement, AND / OR / NOT / XOR are bitwise, SHL / SHR shift (SHR arithmetically), constants are
+ * the integers held in `consts`, and FLOORDIV / MOD round toward minus infinity unless the step's reserved[0] is 1
+ * (toward zero, the reference's div.s32 / rem.s32). */
 #define EMMYB200_PW_MAX_SLOTS 16
 #define EMMYB200_PW_MAX_CONSTS 16
 #define EMMYB200_PW_MAX_STEPS 48
@@ -72,7 +79,8 @@ enum {
     EMMYB200_PW_SQRT, EMMYB200_PW_RSQRT, EMMYB200_PW_EXP, EMMYB200_PW_LOG, EMMYB200_PW_SIGMOID, EMMYB200_PW_TANH,
     EMMYB200_PW_ERF, EMMYB200_PW_SIN, EMMYB200_PW_COS, EMMYB200_PW_POW, EMMYB200_PW_EQ, EMMYB200_PW_NE,
     EMMYB200_PW_GT, EMMYB200_PW_LT, EMMYB200_PW_GE, EMMYB200_PW_LE, EMMYB200_PW_WHERE, EMMYB200_PW_AND,
-    EMMYB200_PW_OR, EMMYB200_PW_NOT, EMMYB200_PW_FLOORDIV, EMMYB200_PW_MOD, EMMYB200_PW_OP_COUNT
+    EMMYB200_PW_OR, EMMYB200_PW_NOT, EMMYB200_PW_FLOORDIV, EMMYB200_PW_MOD, EMMYB200_PW_XOR, EMMYB200_PW_SHL,
+    EMMYB200_PW_SHR, EMMYB200_PW_OP_COUNT
 };
 typedef struct {
     uint8_t op, dst, a, b, c, reserved[3];

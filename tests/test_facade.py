@@ -182,3 +182,31 @@ def test_float32_products_written_as_loops_match_the_split_precision_gemm():
     p = handle(ir.matmul_f32_kernel(64, 96, 128, b_trans=True, bias=True))
     assert p["params"]["b_trans"] and p["params"]["bias"] and p["inputs"] == ["A", "B", "bias"]
     assert handle(ir.matmul_f32_kernel(32, 256, 128, b_trans=True, bias=True, relu=True))["params"]["epilogue"] == "relu"
+
+
+def test_integer_and_bool_programs_match_the_program_kernel():
+    """d_i32_arith / d_i32_floordiv_mod / d_bool_in (tools/torch_cases/dtypes.py:11-16): integer-typed Assigns become an
+    integer program (with the division mode of the compile), a bool buffer is a legal input of a float program, and
+    a program mixing integer and float Assigns is refused."""
+    from emmyptx.ir import Assign, Axis, DType, Dim, KernelOp, Load, Op, Tile, Var, Write, _graph, _launch, tensor
+
+    def int_kernel(steps, mixed=False):
+        a0 = Axis("a0", Dim(1024))
+        body = [Load(["a"], "a", [Var("a0")])]
+        body += [Assign(v, Op(op), list(args), None if (mixed and i == 0) else DType("int")) for i, (v, op, args) in enumerate(steps)]
+        body.append(Write("out", [Var("a0")], [steps[-1][0]]))
+        k = KernelOp("k_int", [Tile([a0], body)])
+        return _graph(k, [tensor("a", [1024], "i32")], [tensor("out", [1024], "i32")]), k, _launch(k, ["a", "out"], 1024)
+
+    steps = [("q", "floor_divide", ["a", 3]), ("r", "mod", ["a", 3]), ("s", "multiply", ["r", 100]), ("u", "add", ["q", "s"])]
+    h = handle(int_kernel(steps))
+    assert h["variant"] == "pointwise_program" and h["params"]["program"]["out_dtype"] == "i32"
+    assert h["params"]["program"]["int_div"] == "floor" and len(h["params"]["program"]["steps"]) == 4
+    assert handle(int_kernel(steps), int_div="trunc")["params"]["program"]["int_div"] == "trunc"
+    assert algorithmic_work(h) == (8.0 * 1024, "B")
+    with pytest.raises(CompileError):
+        handle(int_kernel(steps, mixed=True))
+    with pytest.raises(CompileError):
+        handle(int_kernel([("t", "multiply", ["a", 2.5])]))                 # not a whole number
+    h = handle(ir.elementwise_kernel(1024, {"x": "f32", "m": "bool"}, [("nx", "negative", ["x"]), ("y", "where", ["m", "x", "nx"])]))
+    assert h["params"]["program"]["in_dtypes"] == ["f32", "bool"]

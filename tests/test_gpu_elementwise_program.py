@@ -95,3 +95,80 @@ def test_program_limits_are_compile_errors():
     h = json.loads(compile_kernel(*ir.elementwise_kernel(64, {"x": "f32"}, [(f"v{i}", "add", ["x" if i == 0 else f"v{i-1}", 1.0]) for i in range(40)])))
     assert h["variant"] == "pointwise_program" and len(h["params"]["program"]["steps"]) == 40
     assert max(s[1] for s in h["params"]["program"]["steps"]) < 16           # slots are recycled
+
+
+# ---- integer programs and bool inputs (tools/torch_cases/dtypes.py:11-16) -----------------------------------------
+def _int_kernel(n, steps, in_dt="i32", out_dt="i32", ins=("a",)):
+    """Kernel IR of an integer cell program: integer-typed Assigns over the s32 op table (emmyptx/ops.py:294-309)."""
+    from emmyptx.ir import Assign, Axis, DType, Dim, KernelOp, Load, Op, Tile, Var, Write, _graph, _launch, tensor
+    a0 = Axis("a0", Dim(n))
+    body = [Load([b], b, [Var("a0")]) for b in ins]
+    body += [Assign(v, Op(op), list(args), DType("int")) for v, op, args in steps]
+    body.append(Write("out", [Var("a0")], [steps[-1][0]]))
+    k = KernelOp("k_int", [Tile([a0], body)])
+    g = _graph(k, [tensor(b, [n], in_dt) for b in ins], [tensor("out", [n], out_dt)])
+    return g, k, _launch(k, [*ins, "out"], n)
+
+
+def _run_built(built, arrays, out_dtype, n, **kw):
+    import torch
+    from emmyptx.kernel import KernelCompiler
+    g, k, launch = built
+    handle = json.loads(KernelCompiler(g, k, launch, **kw).compile())
+    assert handle["variant"] == "pointwise_program"
+    run_local.init()
+    dev = torch.device("cuda:0")
+    bufs = {name: torch.from_numpy(a).to(dev) for name, a in arrays.items()}
+    bufs["out"] = torch.zeros(n, dtype=out_dtype, device=dev)
+    run_local.launch(handle, bufs)
+    torch.cuda.synchronize()
+    return bufs["out"].cpu().numpy()
+
+
+@pytest.mark.parametrize("n", [1024, 4099])
+def test_integer_cases_are_bit_exact(n, cuda):
+    import torch
+    rng = np.random.default_rng(n)
+    a = rng.integers(-8, 8, n).astype(np.int32)
+    got = _run_built(_int_kernel(n, [("t", "multiply", ["a", 3]), ("u", "add", ["t", 1])]), {"a": a}, torch.int32, n)
+    assert np.array_equal(got, a * 3 + 1)                                                           # d_i32_arith
+    steps = [("q", "floor_divide", ["a", 3]), ("r", "mod", ["a", 3]), ("s", "multiply", ["r", 100]), ("u", "add", ["q", "s"])]
+    got = _run_built(_int_kernel(n, steps), {"a": a}, torch.int32, n)
+    assert np.array_equal(got, a // 3 + (a % 3) * 100)                                              # d_i32_floordiv_mod (torch floors)
+    got = _run_built(_int_kernel(n, steps), {"a": a}, torch.int32, n, int_div="trunc")              # the reference's div.s32 / rem.s32
+    q = np.trunc(a / 3).astype(np.int32)
+    assert np.array_equal(got, q + (a - 3 * q) * 100)
+    a64 = rng.integers(-4, 4, n).astype(np.int64)
+    got = _run_built(_int_kernel(n, [("t", "multiply", ["a", 3]), ("u", "add", ["t", 1])], "i64", "i64"), {"a": a64}, torch.int64, n)
+    assert np.array_equal(got, a64 * 3 + 1)                                                         # d_i64_arith
+
+
+def test_integer_ops_wrap_and_shift_as_s32(cuda):
+    import torch
+    n = 2048
+    rng = np.random.default_rng(3)
+    a = rng.integers(-2**31, 2**31, n).astype(np.int32)
+    b = rng.integers(-2**31, 2**31, n).astype(np.int32)
+    a[:4] = [np.iinfo(np.int32).min, np.iinfo(np.int32).max, -1, 0]
+    steps = [("m", "multiply", ["a", "b"]), ("x", "bitwise_xor", ["m", "a"]), ("s", "right_shift", ["x", 3]), ("t", "left_shift", ["b", 5]),
+             ("o", "bitwise_or", ["s", "t"]), ("n", "bitwise_and", ["o", 16777215]), ("d", "subtract", ["n", "a"]), ("z", "maximum", ["d", "b"])]
+    got = _run_built(_int_kernel(n, steps, ins=("a", "b")), {"a": a, "b": b}, torch.int32, n)
+    a64, b64 = a.astype(np.int64), b.astype(np.int64)
+    wrap = lambda v: ((v + 2**31) % 2**32 - 2**31)
+    m = wrap(a64 * b64)
+    x = m ^ a64
+    o = (x >> 3) | wrap(b64 << 5)
+    d = wrap((o & 16777215) - a64)
+    assert np.array_equal(got, np.maximum(d, b64).astype(np.int32))
+
+
+@pytest.mark.parametrize("n", [1024, 4099])
+def test_bool_mask_input(n, cuda):
+    """d_bool_in: torch.where(m, x, -x) with a bool buffer as a graph input."""
+    import torch
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal(n).astype(np.float32)
+    m = rng.standard_normal(n) > 0
+    built = ir.elementwise_kernel(n, {"x": "f32", "m": "bool"}, [("nx", "negative", ["x"]), ("y", "where", ["m", "x", "nx"])])
+    got = _run_built(built, {"x": x, "m": m}, torch.float32, n)
+    assert np.array_equal(got, np.where(m, x, -x))
