@@ -15,7 +15,7 @@ enum Kind { K_ADD, K_SQ, K_MAX, K_MIN, K_MUL, K_MOM, K_LSE, K_ARG };
 
 constexpr int kind_of(int op) {
     switch (op) {
-        case EMMYB200_ROW_SUM: case EMMYB200_ROW_MEAN: return K_ADD;
+        case EMMYB200_ROW_SUM: case EMMYB200_ROW_MEAN: case EMMYB200_ROW_DOT: return K_ADD;
         case EMMYB200_ROW_NORM2: case EMMYB200_ROW_RMS_NORM: case EMMYB200_ROW_NORMALIZE: return K_SQ;
         case EMMYB200_ROW_AMAX: return K_MAX;
         case EMMYB200_ROW_AMIN: return K_MIN;

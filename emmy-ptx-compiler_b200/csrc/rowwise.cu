@@ -143,8 +143,13 @@ __global__ void __launch_bounds__(256) rowwise_cached_kernel(RowArgs a) {
                 if constexpr (VEC == 4) {
                     const float4 q = __ldcs(reinterpret_cast<const float4*>(xr + c));
                     v[4 * i] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
+                    if constexpr (OP == EMMYB200_ROW_DOT) {     // the products with the vector are what is summed
+                        const float4 wq = __ldg(reinterpret_cast<const float4*>(a.w + c));
+                        v[4 * i] *= wq.x; v[4 * i + 1] *= wq.y; v[4 * i + 2] *= wq.z; v[4 * i + 3] *= wq.w;
+                    }
                 } else {
                     v[i] = __ldcs(xr + c);
+                    if constexpr (OP == EMMYB200_ROW_DOT) v[i] *= __ldg(a.w + c);
                 }
             }
         }
@@ -274,7 +279,7 @@ constexpr int kSplitThreads = 256;
 
 // Folds elements [c0, c1) of one row into a state, kSplitThreads threads together; every thread returns it.
 template <int K, int VEC>
-__device__ __forceinline__ St piece_state(const float* xr, int64_t c0, int64_t c1, ReduceSlabs* slabs, int& round) {
+__device__ __forceinline__ St piece_state(const float* xr, const float* w, int64_t c0, int64_t c1, ReduceSlabs* slabs, int& round) {
     St s = st_identity<K>();
     float shift = 0.0f, s1 = 0.0f, s2 = 0.0f, cnt = 0.0f;
     if constexpr (K == K_MOM) shift = __ldg(xr + c0);          // sums are taken about a sample of the piece
@@ -291,6 +296,10 @@ __device__ __forceinline__ St piece_state(const float* xr, int64_t c0, int64_t c
                     v[k][0] = q.x; v[k][1] = q.y; v[k][2] = q.z; v[k][3] = q.w;
                 } else {
                     v[k][0] = __ldcs(xr + c);
+                }
+                if (w != nullptr) {                             // dot product: fold x * w (uniform over the grid)
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) v[k][e] *= __ldg(w + c + e);
                 }
             }
         }
@@ -349,7 +358,7 @@ __global__ void __launch_bounds__(kSplitThreads) rowwise_split_kernel(RowArgs a,
     const float* xr = a.x + row * a.cols;
     const int64_t c0 = (int64_t)piece * piece_len;
     const int64_t c1 = c0 + piece_len < a.cols ? c0 + piece_len : a.cols;
-    St s = piece_state<K, VEC>(xr, c0, c1, &slabs, round);
+    St s = piece_state<K, VEC>(xr, OP == EMMYB200_ROW_DOT ? a.w : nullptr, c0, c1, &slabs, round);
     if (pieces > 1) {
         if (threadIdx.x == 0) {
             partials[row * pieces + piece] = make_float4(s.a, s.b, s.c, 0.0f);
@@ -501,7 +510,7 @@ int dispatch(int op, const RowArgs& a, void* ws, cudaStream_t s) {
     switch (op) {
 #define EMMY_ROW_CASE(name) case EMMYB200_ROW_##name: return launch_op<EMMYB200_ROW_##name, VEC>(a, ws, s);
         EMMY_ROW_CASE(SUM) EMMY_ROW_CASE(MEAN) EMMY_ROW_CASE(AMAX) EMMY_ROW_CASE(AMIN) EMMY_ROW_CASE(PROD)
-        EMMY_ROW_CASE(VAR) EMMY_ROW_CASE(STD) EMMY_ROW_CASE(NORM2) EMMY_ROW_CASE(LOGSUMEXP) EMMY_ROW_CASE(ARGMAX)
+        EMMY_ROW_CASE(VAR) EMMY_ROW_CASE(STD) EMMY_ROW_CASE(NORM2) EMMY_ROW_CASE(LOGSUMEXP) EMMY_ROW_CASE(ARGMAX) EMMY_ROW_CASE(DOT)
         EMMY_ROW_CASE(SOFTMAX) EMMY_ROW_CASE(LOG_SOFTMAX) EMMY_ROW_CASE(LAYER_NORM) EMMY_ROW_CASE(RMS_NORM)
         EMMY_ROW_CASE(NORMALIZE)
 #undef EMMY_ROW_CASE
@@ -509,7 +518,7 @@ int dispatch(int op, const RowArgs& a, void* ws, cudaStream_t s) {
     return fail(EMMYB200_ERR_ARG, "rowwise: unknown op %d", op);
 }
 
-bool known_op(int op) { return (op >= EMMYB200_ROW_SUM && op <= EMMYB200_ROW_ARGMAX) || (op >= EMMYB200_ROW_SOFTMAX && op <= EMMYB200_ROW_NORMALIZE); }
+bool known_op(int op) { return (op >= EMMYB200_ROW_SUM && op <= EMMYB200_ROW_DOT) || (op >= EMMYB200_ROW_SOFTMAX && op <= EMMYB200_ROW_NORMALIZE); }
 
 }  // namespace
 }  // namespace emmy
@@ -531,7 +540,11 @@ extern "C" int emmyb200_rowwise_f32(int op, const float* x, const float* weight,
     if (cols >= ((int64_t)1 << 31) || rows >= ((int64_t)1 << 31)) return fail(EMMYB200_ERR_SHAPE, "rowwise: extents are limited to 2^31 - 1");
     if (x == nullptr || y == nullptr) return fail(EMMYB200_ERR_ARG, "rowwise: null buffer");
     const bool affine = op == EMMYB200_ROW_LAYER_NORM || op == EMMYB200_ROW_RMS_NORM;
-    if (!affine && (weight != nullptr || bias != nullptr)) return fail(EMMYB200_ERR_ARG, "rowwise: only layer_norm and rms_norm take a weight or bias");
+    if (op == EMMYB200_ROW_DOT) {
+        if (weight == nullptr || bias != nullptr) return fail(EMMYB200_ERR_ARG, "rowwise: dot takes the vector as `weight` and no bias");
+    } else if (!affine && (weight != nullptr || bias != nullptr)) {
+        return fail(EMMYB200_ERR_ARG, "rowwise: only layer_norm, rms_norm and dot take a weight or bias");
+    }
     if (op == EMMYB200_ROW_RMS_NORM && bias != nullptr) return fail(EMMYB200_ERR_ARG, "rowwise: rms_norm has no bias");
     if (!aligned(x, 4) || !aligned(y, is_map(op) ? 4 : (op == EMMYB200_ROW_ARGMAX ? 8 : 4)))
         return fail(EMMYB200_ERR_ALIGN, "rowwise: buffers must be aligned to their element size");

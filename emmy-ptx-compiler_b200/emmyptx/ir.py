@@ -428,6 +428,11 @@ def rowwise_kernel(op: str, rows: int, cols: int, eps: float = 1e-5, name: str =
     elif op == "norm2":
         body = fold("acc", "add", [Assign("sq", Op("multiply"), ["x", "x"])]) + [Assign("n", Op("sqrt"), ["acc"])]
         out = "n"
+    elif op == "dot":                                   # a matrix-vector product: the vector is the second input
+        inputs.append(tensor("W", [cols], "f32"))
+        body = [Loop(c0, [ld(), Load(["w"], "W", [Var("c0")]), Assign("p", Op("multiply"), ["x", "w"]), Accum("acc", None, "p", Op("add"))]),
+                shuffle("acc", "add")]
+        out = "acc"
     elif op in ("var", "std", "layer_norm"):
         body = fold("acc", "add") + [Assign("mean", Op("multiply"), ["acc", 1.0 / cols])]
         body += fold("acc2", "add", [Assign("d", Op("subtract"), ["x", "mean"]), Assign("d2", Op("multiply"), ["d", "d"])])

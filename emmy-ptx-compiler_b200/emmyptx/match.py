@@ -509,6 +509,7 @@ ROWWISE_F64 = {
     "var": lambda x, w, b, e: _moments(x)[1] / (x.shape[-1] - 1),
     "std": lambda x, w, b, e: np.sqrt(_moments(x)[1] / (x.shape[-1] - 1)),
     "norm2": lambda x, w, b, e: np.sqrt((x * x).sum(-1, keepdims=True)),
+    "dot": lambda x, w, b, e: (x * w).sum(-1, keepdims=True),
     "logsumexp": lambda x, w, b, e: np.log(np.exp(x - x.max(-1, keepdims=True)).sum(-1, keepdims=True)) + x.max(-1, keepdims=True),
     "softmax": lambda x, w, b, e: _softmax64(x),
     "log_softmax": lambda x, w, b, e: np.log(_softmax64(x)),
@@ -603,9 +604,11 @@ def match_rowwise(graph, kernel, launch: dict) -> dict:
     literals = sorted({float(a) for s in walk(tile.body) if _kind(s) == "Assign" for a in s.args
                        if isinstance(a, float) and 0.0 < a < 1e-2}, reverse=True)
     for op, f in ROWWISE_F64.items():
-        if (op in ROWWISE_MAPS) != is_map or (vecs and op not in ("layer_norm", "rms_norm")) or (len(vecs) > 1 and op != "layer_norm"):
+        if (op in ROWWISE_MAPS) != is_map or (vecs and op not in ("layer_norm", "rms_norm", "dot")) or (len(vecs) > 1 and op != "layer_norm"):
             continue
-        if over_dim0 and op in ("layer_norm", "rms_norm"):
+        if (op == "dot") != (len(vecs) == 1 and not is_map):
+            continue
+        if over_dim0 and op in ("layer_norm", "rms_norm", "dot"):
             continue
         for eps in (literals + [0.0] if op in ("layer_norm", "rms_norm", "normalize") else [0.0]):
             with np.errstate(all="ignore"):

@@ -45,7 +45,7 @@ GEMM_DST_MULTICAST = 2
 ATT_CAUSAL = 1
 ATT_DST_MULTICAST = 2
 GATHER_TRUNC = 1
-ROW_OPS = {"sum": 0, "mean": 1, "amax": 2, "amin": 3, "prod": 4, "var": 5, "std": 6, "norm2": 7, "logsumexp": 8, "argmax": 9,
+ROW_OPS = {"sum": 0, "mean": 1, "amax": 2, "amin": 3, "prod": 4, "var": 5, "std": 6, "norm2": 7, "logsumexp": 8, "argmax": 9, "dot": 10,
            "softmax": 16, "log_softmax": 17, "layer_norm": 18, "rms_norm": 19, "normalize": 20}
 ROW_MAP_FIRST = 16            # ops from here on write [rows, cols]
 

@@ -191,7 +191,8 @@ int emmyb200_attention_fwd_allgather(int dtype, int flags, const void* Q, const 
  * int64_t[rows], first index of the maximum, NaN counting as the largest, as torch); the others store
  * y: float[rows, cols]. VAR and STD are the unbiased estimates (torch's default). LAYER_NORM is
  * (x - mean) / sqrt(biased var + eps) * weight + bias and RMS_NORM x / sqrt(mean(x^2) + eps) * weight, `weight`
- * and `bias` being float[cols] or NULL; NORMALIZE is x / max(||x||_2, eps). Other ops take NULL for both.
+ * and `bias` being float[cols] or NULL; NORMALIZE is x / max(||x||_2, eps); DOT needs `weight` (the vector). Other ops
+ * take NULL for both.
  * Rows of more than 65536 elements are reduced in pieces by several thread blocks, which needs
  * emmyb200_rowwise_workspace_bytes(op, rows, cols) bytes of 256-byte-aligned device memory (contents
  * irrelevant before, undefined after; 0 for shorter rows, -1 for arguments the call would reject); results do
@@ -206,6 +207,7 @@ int emmyb200_attention_fwd_allgather(int dtype, int flags, const void* Q, const 
 #define EMMYB200_ROW_NORM2 7
 #define EMMYB200_ROW_LOGSUMEXP 8
 #define EMMYB200_ROW_ARGMAX 9
+#define EMMYB200_ROW_DOT 10      /* y[r] = sum_c x[r, c] * weight[c]: a matrix-vector product (tools/torch_cases/matmul.py:22) */
 #define EMMYB200_ROW_SOFTMAX 16
 #define EMMYB200_ROW_LOG_SOFTMAX 17
 #define EMMYB200_ROW_LAYER_NORM 18

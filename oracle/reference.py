@@ -127,6 +127,7 @@ def rowwise_reference(op: str, x, weight=None, bias=None, eps: float = 0.0):
     if op == "norm2": return torch.linalg.vector_norm(x, dim=-1)
     if op == "logsumexp": return torch.logsumexp(x, -1)
     if op == "argmax": return x.argmax(-1)
+    if op == "dot": return x @ w
     if op == "softmax": return torch.softmax(x, -1)
     if op == "log_softmax": return torch.log_softmax(x, -1)
     if op == "layer_norm": return F.layer_norm(x, (n,), w, b, eps)

@@ -138,7 +138,7 @@ def test_row_reductions_are_matched_by_behaviour():
     """Every row op the builder can spell is recognised, with its extents and epsilon; a differently arranged program
     with the same meaning (mean as a division, the variance through E[x^2] - E[x]^2) matches the same kernel."""
     from emmyptx.ir import Accum, Assign, Axis, Dim, KernelOp, Load, Loop, Op, Tile, Var, Write, _graph, _launch, tensor
-    for op in ("sum", "mean", "amax", "amin", "prod", "var", "std", "norm2", "logsumexp", "softmax", "log_softmax",
+    for op in ("sum", "mean", "amax", "amin", "prod", "var", "std", "norm2", "logsumexp", "dot", "softmax", "log_softmax",
                "layer_norm", "rms_norm", "normalize"):
         h = handle(ir.rowwise_kernel(op, 48, 256, eps=1e-6))
         assert h["variant"] == "rowwise_f32" and h["params"]["op"] == op, op

@@ -13,7 +13,7 @@ from oracle import reference
 
 pytestmark = pytest.mark.gpu
 
-REDUCING = ["sum", "mean", "amax", "amin", "prod", "var", "std", "norm2", "logsumexp", "argmax"]
+REDUCING = ["sum", "mean", "amax", "amin", "prod", "var", "std", "norm2", "logsumexp", "argmax", "dot"]
 MAPPING = ["softmax", "log_softmax", "layer_norm", "rms_norm", "normalize"]
 
 
@@ -31,7 +31,7 @@ def _data(op, rows, cols, seed=0):
         x[u < 1e-4] = 2.0
         x[(u >= 1e-4) & (u < 2e-4)] = 0.5
         x[u > 0.99] = -1.0
-    w = torch.randn(cols, generator=g) if op in ("layer_norm", "rms_norm") else None
+    w = torch.randn(cols, generator=g) if op in ("layer_norm", "rms_norm", "dot") else None
     b = torch.randn(cols, generator=g) if op == "layer_norm" else None
     eps = {"layer_norm": 1e-5, "rms_norm": 1e-6, "normalize": 1e-12}.get(op, 0.0)
     return x, w, b, eps
@@ -52,7 +52,7 @@ def _check(op, got, ref, cols, rtol=1e-4, atol=1e-4):
         return
     if op in ("amax", "amin"):
         rtol = atol = 1e-6
-    elif op in ("sum", "norm2", "logsumexp", "log_softmax"):
+    elif op in ("sum", "dot", "norm2", "logsumexp", "log_softmax"):
         atol = atol + 1e-6 * cols ** 0.5
     res = reference.compare(got.numpy(), ref.numpy(), rtol, atol)
     assert res["ok"], (op, cols, res)
@@ -69,6 +69,7 @@ def _check(op, got, ref, cols, rtol=1e-4, atol=1e-4):
     ("norm2", 64, 512, 1e-4, 1e-4),          # r_vector_norm
     ("logsumexp", 64, 512, 1e-4, 1e-4),      # r_logsumexp
     ("argmax", 64, 512, 0, 0),               # r_argmax, r_max_with_idx
+    ("dot", 256, 128, 1e-3, 1e-3),           # m_matvec (tools/torch_cases/matmul.py:22), the matmul class
     ("softmax", 64, 1000, 1e-3, 1e-5),       # f_softmax
     ("log_softmax", 48, 256, 1e-3, 1e-4),    # f_log_softmax
     ("layer_norm", 64, 768, 1e-3, 1e-4),     # f_layer_norm_affine
