@@ -93,6 +93,13 @@ __device__ __forceinline__ void pw_store1(void* base, int dtype, int64_t i, floa
     else reinterpret_cast<__nv_bfloat16*>(base)[i] = __float2bfloat16_rn(v);
 }
 
+// Index of the element input k supplies for output element i.
+__device__ __forceinline__ int64_t pw_index(const emmyb200_pw_program& prog, int k, int64_t i) {
+    if (prog.in_div[k] > 0) i /= prog.in_div[k];
+    if (prog.in_mod[k] > 0) i %= prog.in_mod[k];
+    return i;
+}
+
 struct PwArgs {
     const void* in[EMMYB200_PW_MAX_INPUTS];
     void* out;
@@ -115,7 +122,13 @@ __global__ void __launch_bounds__(kPwThreads) pointwise_program_kernel(const __g
             for (int u = 0; u < kPwUnroll; ++u) {
                 const int64_t g = g0 + u * stride;
                 float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (g < groups) {
+                if (g < groups && (prog.in_div[k] | prog.in_mod[k]) != 0) {     // a broadcast input: four gathered loads
+                    const int64_t i = g * 4;
+                    v.x = pw_load1(args.in[k], prog.in_dtype[k], pw_index(prog, k, i));
+                    v.y = i + 1 < args.n ? pw_load1(args.in[k], prog.in_dtype[k], pw_index(prog, k, i + 1)) : 0.0f;
+                    v.z = i + 2 < args.n ? pw_load1(args.in[k], prog.in_dtype[k], pw_index(prog, k, i + 2)) : 0.0f;
+                    v.w = i + 3 < args.n ? pw_load1(args.in[k], prog.in_dtype[k], pw_index(prog, k, i + 3)) : 0.0f;
+                } else if (g < groups) {
                     if constexpr (VEC) {
                         const int dt = prog.in_dtype[k];
                         if (dt == EMMYB200_U8) {
@@ -183,7 +196,7 @@ __global__ void __launch_bounds__(kPwThreads) pointwise_program_kernel(const __g
         if (blockIdx.x == 0 && tid < tail) {
             const int64_t i = (args.n & ~(int64_t)3) + tid;
             float regs[kPwSlots];
-            for (int k = 0; k < prog.n_inputs; ++k) regs[k] = pw_load1(args.in[k], prog.in_dtype[k], i);
+            for (int k = 0; k < prog.n_inputs; ++k) regs[k] = pw_load1(args.in[k], prog.in_dtype[k], pw_index(prog, k, i));
             for (int s = 0; s < prog.n_steps; ++s) {
                 const emmyb200_pw_step st = prog.steps[s];
                 auto operand = [&](int o) { return o >= kPwSlots ? prog.consts[o - kPwSlots] : regs[o]; };
@@ -246,7 +259,7 @@ __global__ void __launch_bounds__(kPwThreads) pointwise_program_int_kernel(const
     const int64_t stride = (int64_t)gridDim.x * kPwThreads;
     for (int64_t i = (int64_t)blockIdx.x * kPwThreads + threadIdx.x; i < args.n; i += stride) {
         int regs[kPwSlots];
-        for (int k = 0; k < prog.n_inputs; ++k) regs[k] = pw_load_int(args.in[k], prog.in_dtype[k], i);
+        for (int k = 0; k < prog.n_inputs; ++k) regs[k] = pw_load_int(args.in[k], prog.in_dtype[k], pw_index(prog, k, i));
         for (int s = 0; s < prog.n_steps; ++s) {
             const emmyb200_pw_step st = prog.steps[s];
             auto operand = [&](int o) { return o >= kPwSlots ? (int)prog.consts[o - kPwSlots] : regs[o]; };
@@ -297,7 +310,8 @@ extern "C" int emmyb200_pointwise_program(const emmyb200_pw_program* prog, const
     for (int k = 0; k < prog->n_inputs; ++k) {
         if (inputs[k] == nullptr) return fail(EMMYB200_ERR_ARG, "pointwise_program: null buffer");
         if (!aligned(inputs[k], elem_size(prog->in_dtype[k]))) return fail(EMMYB200_ERR_ALIGN, "pointwise_program: misaligned input %d", k);
-        vec = vec && aligned(inputs[k], 4 * elem_size(prog->in_dtype[k]));
+        if (prog->in_div[k] < 0 || prog->in_mod[k] < 0) return fail(EMMYB200_ERR_ARG, "pointwise_program: negative broadcast extent for input %d", k);
+        if ((prog->in_div[k] | prog->in_mod[k]) == 0) vec = vec && aligned(inputs[k], 4 * elem_size(prog->in_dtype[k]));
         args.in[k] = inputs[k];
     }
     args.out = out;

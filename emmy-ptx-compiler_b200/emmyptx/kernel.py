@@ -87,7 +87,10 @@ def algorithmic_work(handle: dict) -> tuple[float, str]:
         return 8.0 * p["n"], "B"
     if v == "pointwise_program":
         size = {"f32": 4, "f16": 2, "bf16": 2, "i32": 4, "int": 4, "i64": 8, "bool": 1, "u8": 1}
-        return float(p["n"]) * (sum(size[d] for d in p["program"]["in_dtypes"]) + size[p["program"]["out_dtype"]]), "B"
+        prog, n = p["program"], p["n"]
+        div, mod = prog.get("in_div", [0] * 4), prog.get("in_mod", [0] * 4)
+        read = sum(size[d] * (mod[k] or (n // div[k] if div[k] else n)) for k, d in enumerate(prog["in_dtypes"]))      # broadcast inputs are small
+        return float(read + n * size[prog["out_dtype"]]), "B"
     if v == "gemm":
         return 2.0 * p["m"] * p["n"] * p["k"], "flop"
     if v == "gemm_f32":

@@ -337,17 +337,33 @@ def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict
     float_types = ("f32", "f16", "bf16")
     int_types = ("i32", "i64", "int")
     identity = all(np.array_equal(i, cells) for _, i, _ in it.loads) and all(math.prod(tensors[b][0]) == n for b in buffers)
-    if identity and tensors[out_name][1] in int_types and all(tensors[b][1] in int_types for b in buffers) and buffers:
+    # Broadcast reads: element (i // div) % mod of a smaller buffer (a row vector over a matrix, a column vector, ...).
+    # The divisors tried are the products of the output's trailing extents.
+    out_shape = tensors[out_name][0]
+    divisors = sorted({math.prod(out_shape[j:]) for j in range(len(out_shape) + 1)})
+    pattern = {}
+    for b, i, _ in it.loads:
+        size = math.prod(tensors[b][0])
+        found = next(((d if d > 1 else 0, 0 if (d == 1 and size == n) else size) for d in divisors
+                      if np.array_equal(i, (cells // d) % size)), None)
+        if found is None or pattern.setdefault(b, found) != found:
+            pattern = None
+            break
+    broadcast = pattern is not None and not identity
+    if (identity or broadcast) and tensors[out_name][1] in int_types and all(tensors[b][1] in int_types for b in buffers) and buffers:
         # an integer expression of element i of every buffer: the s32 program kernel (the gather is the other integer kernel)
         prog = build_program(tile, tensors, out_name, tile.body[-1].values[0] if _kind(tile.body[-1]) == "Write" else None, integer=True)
         prog["int_div"] = int_div
+        if broadcast:
+            prog["in_div"], prog["in_mod"] = [pattern[b][0] for b in prog["inputs"]], [pattern[b][1] for b in prog["inputs"]]
         return {"variant": "pointwise_program", "params": {"n": n, "program": {k: v for k, v in prog.items() if k != "inputs"}},
                 "inputs": prog["inputs"], "outputs": [out_name]}
     general = (tensors[out_name][1] in float_types and all(tensors[b][1] in float_types + ("bool", "u8") for b in buffers)
-               and all(np.array_equal(i, cells) for _, i, _ in it.loads)
-               and all(math.prod(tensors[b][0]) == n for b in buffers))
-    if general and not (len(buffers) == 1 and tensors[next(iter(buffers))][1] == "f32" and tensors[out_name][1] == "f32"):
+               and (identity or broadcast) and bool(buffers))
+    if general and (broadcast or not (len(buffers) == 1 and tensors[next(iter(buffers))][1] == "f32" and tensors[out_name][1] == "f32")):
         prog = build_program(tile, tensors, out_name, tile.body[-1].values[0] if _kind(tile.body[-1]) == "Write" else None)
+        if broadcast:
+            prog["in_div"], prog["in_mod"] = [pattern[b][0] for b in prog["inputs"]], [pattern[b][1] for b in prog["inputs"]]
         return {"variant": "pointwise_program", "params": {"n": n, "program": {k: v for k, v in prog.items() if k != "inputs"}},
                 "inputs": prog["inputs"], "outputs": [out_name]}
     if len(buffers) != 1:

@@ -35,7 +35,8 @@ class PwStep(ctypes.Structure):
 class PwProgram(ctypes.Structure):
     _fields_ = [("n_inputs", ctypes.c_int32), ("n_steps", ctypes.c_int32), ("out_slot", ctypes.c_int32),
                 ("out_dtype", ctypes.c_int32), ("in_dtype", ctypes.c_int32 * PW_MAX_INPUTS),
-                ("consts", ctypes.c_float * PW_MAX_CONSTS), ("steps", PwStep * PW_MAX_STEPS)]
+                ("consts", ctypes.c_float * PW_MAX_CONSTS), ("steps", PwStep * PW_MAX_STEPS),
+                ("in_div", ctypes.c_int64 * PW_MAX_INPUTS), ("in_mod", ctypes.c_int64 * PW_MAX_INPUTS)]
 
 
 EPI_NONE, EPI_GELU_TANH, EPI_RELU = 0, 1, 2
@@ -163,6 +164,8 @@ def make_program(program: dict) -> PwProgram:
     p.out_slot, p.out_dtype = program["out_slot"], DTYPE_CODES[program["out_dtype"]]
     for i, d in enumerate(program["in_dtypes"]):
         p.in_dtype[i] = DTYPE_CODES[d]
+        p.in_div[i] = program.get("in_div", [0] * PW_MAX_INPUTS)[i]            # broadcast inputs: element (i // div) % mod
+        p.in_mod[i] = program.get("in_mod", [0] * PW_MAX_INPUTS)[i]
     for i, c in enumerate(program["consts"]):
         p.consts[i] = c
     for i, (op, dst, a, b, c) in enumerate(program["steps"]):

@@ -90,6 +90,11 @@ typedef struct {
     int32_t in_dtype[EMMYB200_PW_MAX_INPUTS];
     float consts[EMMYB200_PW_MAX_CONSTS];
     emmyb200_pw_step steps[EMMYB200_PW_MAX_STEPS];
+    /* Broadcast inputs: element i of the output reads element (i / in_div[k]) % in_mod[k] of input k (0 = that
+     * step is skipped; both 0: element i, the default). in_mod = cols gives a row vector broadcast over a
+     * [rows, cols] output (a bias, batch-norm statistics); in_div = cols a column vector (an outer product). */
+    int64_t in_div[EMMYB200_PW_MAX_INPUTS];
+    int64_t in_mod[EMMYB200_PW_MAX_INPUTS];
 } emmyb200_pw_program;
 int emmyb200_pointwise_program(const emmyb200_pw_program* program, const void* const* inputs, void* out,
                                int64_t n, void* cuda_stream);

@@ -210,3 +210,22 @@ def test_integer_and_bool_programs_match_the_program_kernel():
         handle(int_kernel([("t", "multiply", ["a", 2.5])]))                 # not a whole number
     h = handle(ir.elementwise_kernel(1024, {"x": "f32", "m": "bool"}, [("nx", "negative", ["x"]), ("y", "where", ["m", "x", "nx"])]))
     assert h["params"]["program"]["in_dtypes"] == ["f32", "bool"]
+
+
+def test_broadcast_reads_become_program_inputs_with_an_index_map():
+    """A row vector over a matrix (bias, batch-norm statistics), a column vector (outer product): the reads are matched as
+    element (i // div) % mod of the smaller buffer; any other index map is refused."""
+    from emmyptx.ir import Assign, Axis, BinaryExpr, Dim, KernelOp, Literal, Load, Op, Tile, Var, Write, _graph, _launch, tensor
+    r0, c0 = Axis("r0", Dim(64)), Axis("c0", Dim(96))
+
+    def build(a_index, a_shape):
+        body = [Load(["a"], "A", a_index), Load(["b"], "B", [Var("c0")]), Assign("o", Op("multiply"), ["a", "b"]),
+                Write("Y", [Var("r0"), Var("c0")], ["o"])]
+        k = KernelOp("k_outer", [Tile([r0, c0], body)])
+        return _graph(k, [tensor("A", a_shape, "f32"), tensor("B", [96], "f32")], [tensor("Y", [64, 96], "f32")]), k, _launch(k, ["A", "B", "Y"], 64 * 96)
+
+    prog = handle(build([Var("r0")], [64]))["params"]["program"]
+    assert (prog["in_div"], prog["in_mod"]) == ([96, 0], [64, 96])
+    assert algorithmic_work(handle(build([Var("r0")], [64]))) == (4.0 * (64 + 96 + 64 * 96), "B")
+    with pytest.raises(CompileError):                                        # a reversed read is not a broadcast
+        handle(build([BinaryExpr("-", Literal(63, "int"), Var("r0"))], [64]))

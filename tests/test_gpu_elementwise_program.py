@@ -172,3 +172,38 @@ def test_bool_mask_input(n, cuda):
     built = ir.elementwise_kernel(n, {"x": "f32", "m": "bool"}, [("nx", "negative", ["x"]), ("y", "where", ["m", "x", "nx"])])
     got = _run_built(built, {"x": x, "m": m}, torch.float32, n)
     assert np.array_equal(got, np.where(m, x, -x))
+
+
+# ---- broadcast inputs (f_batch_norm_eval, m_outer, s_expand: tools/torch_cases/fused.py:18-20, matmul.py:23, shapes.py) ----
+def _tile2(rows, cols, loads, steps, ins, out_shape):
+    from emmyptx.ir import Assign, Axis, Dim, KernelOp, Load, Op, Tile, Var, Write, _graph, _launch, tensor
+    r0, c0 = Axis("r0", Dim(rows)), Axis("c0", Dim(cols))
+    body = [Load([v], buf, [Var(a) for a in axes]) for v, buf, axes in loads]
+    body += [Assign(v, Op(op), list(args)) for v, op, args in steps]
+    body.append(Write("out", [Var("r0"), Var("c0")], [steps[-1][0]]))
+    k = KernelOp("k_bcast", [Tile([r0, c0], body)])
+    g = _graph(k, [tensor(nm, shp, "f32") for nm, shp in ins.items()], [tensor("out", out_shape, "f32")])
+    return g, k, _launch(k, [*ins, "out"], rows * cols)
+
+
+@pytest.mark.parametrize("rows,cols", [(32, 64), (33, 61)])
+def test_broadcast_inputs(rows, cols, cuda):
+    import torch
+    rng = np.random.default_rng(rows)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    m, w, b = (rng.standard_normal(cols).astype(np.float32) for _ in range(3))
+    # batch norm in eval mode with the per-channel scale folded: (x - m) * w + b, three row vectors over a matrix
+    built = _tile2(rows, cols, [("x", "X", ("r0", "c0")), ("m", "M", ("c0",)), ("w", "W", ("c0",)), ("b", "B", ("c0",))],
+                   [("d", "subtract", ["x", "m"]), ("s", "multiply", ["d", "w"]), ("o", "add", ["s", "b"])],
+                   {"X": [rows, cols], "M": [cols], "W": [cols], "B": [cols]}, [rows, cols])
+    got = _run_built(built, {"X": x.reshape(-1), "M": m, "W": w, "B": b}, torch.float32, rows * cols)
+    assert np.array_equal(got.reshape(rows, cols), (x - m) * w + b)
+    # outer product: a column vector and a row vector
+    a, v = rng.standard_normal(rows).astype(np.float32), rng.standard_normal(cols).astype(np.float32)
+    built = _tile2(rows, cols, [("a", "A", ("r0",)), ("v", "V", ("c0",))], [("o", "multiply", ["a", "v"])], {"A": [rows], "V": [cols]}, [rows, cols])
+    got = _run_built(built, {"A": a, "V": v}, torch.float32, rows * cols)
+    assert np.array_equal(got.reshape(rows, cols), np.outer(a, v))
+    # expand: one row repeated
+    built = _tile2(rows, cols, [("v", "V", ("c0",))], [("o", "add", ["v", 0.0])], {"V": [cols]}, [rows, cols])
+    got = _run_built(built, {"V": v}, torch.float32, rows * cols)
+    assert np.array_equal(got.reshape(rows, cols), np.broadcast_to(v, (rows, cols)))
