@@ -209,12 +209,37 @@ class GemmWorkload(Workload):
         if self.world == 1:
             # the library's host-buffer call: chunked copies overlapped with the kernel (emmyptx.runtime.HostGemm)
             self.host_gemm = self.rt.HostGemm(self.m, self.n, self.k, self.a.dtype, self.a.device, self.epilogue)
+        else:
+            step = 1024 if self.rows % 1024 == 0 else self.rows
+            self.chunks = [(lo, lo + step) for lo in range(0, self.rows, step)]
+            self.copy_in = t.cuda.Stream(self.a.device)
+            self.ev_in = [t.cuda.Event() for _ in range(len(self.chunks) + 1)]
         return self.host["a"].numel() * 2 + self.host["b"].numel() * 2, self.host["c"].numel() * 2
 
     def e2e_step(self):
         h = self.host
         if self.world == 1:
             self.host_gemm(h["a"], h["b"], h["c"])
+            return
+        if self.gather and self.mode in ("fused", "multicast"):
+            # the same overlap across ranks: B once, this rank's rows of A in chunks on a copy stream, one fused
+            # GEMM + gather per chunk as it lands; the group barrier, then this rank's rows of C back
+            t = self.torch
+            main = t.cuda.current_stream()
+            self.copy_in.wait_stream(main)
+            with t.cuda.stream(self.copy_in):
+                self.b.copy_(h["b"], non_blocking=True)
+                self.ev_in[0].record()
+                for i, (lo, hi) in enumerate(self.chunks):
+                    self.a[lo:hi].copy_(h["a"][lo:hi], non_blocking=True)
+                    self.ev_in[i + 1].record()
+            main.wait_event(self.ev_in[0])
+            for i, (lo, hi) in enumerate(self.chunks):
+                main.wait_event(self.ev_in[i + 1])
+                dst = [d + lo * self.n * 2 for d in self.dst]
+                self.rt.gemm_allgather(self.a[lo:hi], self.b, dst, self.n, epilogue=self.epilogue, multicast=self.mode == "multicast")
+            self.peers.barrier()
+            h["c"].copy_(self.c, non_blocking=True)
             return
         self.a.copy_(h["a"], non_blocking=True)
         self.b.copy_(h["b"], non_blocking=True)
