@@ -214,6 +214,10 @@ class GemmWorkload(Workload):
             self.chunks = [(lo, lo + step) for lo in range(0, self.rows, step)]
             self.copy_in = t.cuda.Stream(self.a.device)
             self.ev_in = [t.cuda.Event() for _ in range(len(self.chunks) + 1)]
+            kb = self.k // self.world
+            self.b_rows = (self.rank * kb, (self.rank + 1) * kb)
+            if self.gather and self.mode in ("fused", "multicast"):     # bytes of the whole job: A and B once in, C once out
+                return (self.host["a"].numel() + self.b[self.b_rows[0]:self.b_rows[1]].numel()) * 2 * self.world, self.host["c"].numel() * 2 * self.world
         return self.host["a"].numel() * 2 + self.host["b"].numel() * 2, self.host["c"].numel() * 2
 
     def e2e_step(self):
@@ -228,12 +232,16 @@ class GemmWorkload(Workload):
             main = t.cuda.current_stream()
             self.copy_in.wait_stream(main)
             with t.cuda.stream(self.copy_in):
-                self.b.copy_(h["b"], non_blocking=True)
+                # B is replicated on the devices but crosses the host link once: every rank copies its K / world rows
+                # and the ranks exchange them over NVLink (NCCL all-gather, in place)
+                self.b[self.b_rows[0]:self.b_rows[1]].copy_(h["b"][self.b_rows[0]:self.b_rows[1]], non_blocking=True)
                 self.ev_in[0].record()
                 for i, (lo, hi) in enumerate(self.chunks):
                     self.a[lo:hi].copy_(h["a"][lo:hi], non_blocking=True)
                     self.ev_in[i + 1].record()
             main.wait_event(self.ev_in[0])
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(self.b, self.b[self.b_rows[0]:self.b_rows[1]])
             for i, (lo, hi) in enumerate(self.chunks):
                 main.wait_event(self.ev_in[i + 1])
                 dst = [d + lo * self.n * 2 for d in self.dst]
