@@ -31,8 +31,7 @@
 namespace emmy {
 
 constexpr int kBM = 128, kBK = 64, kUmmaK = 16;
-constexpr int kGemmThreads = 192;
-constexpr int kEpiWarp0 = 2;
+constexpr int kGemmThreads = 192;          // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
 
 template <int BN>
 struct GemmSmem {
