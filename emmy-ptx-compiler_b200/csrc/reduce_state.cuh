@@ -11,7 +11,7 @@
 namespace emmy {
 namespace {
 
-enum Kind { K_ADD, K_SQ, K_MAX, K_MIN, K_MUL, K_MOM, K_LSE, K_ARG };
+enum Kind { K_ADD, K_SQ, K_MAX, K_MIN, K_MUL, K_MOM, K_LSE, K_ARG, K_DOT3 };
 
 constexpr int kind_of(int op) {
     switch (op) {
@@ -22,6 +22,7 @@ constexpr int kind_of(int op) {
         case EMMYB200_ROW_PROD: return K_MUL;
         case EMMYB200_ROW_VAR: case EMMYB200_ROW_STD: case EMMYB200_ROW_LAYER_NORM: return K_MOM;
         case EMMYB200_ROW_LOGSUMEXP: case EMMYB200_ROW_SOFTMAX: case EMMYB200_ROW_LOG_SOFTMAX: return K_LSE;
+        case EMMYB200_ROW_COSINE: return K_DOT3;
         default: return K_ARG;
     }
 }
@@ -73,6 +74,7 @@ __device__ __forceinline__ void arg_push(St& s, float x, int idx) {
 template <int K>
 __device__ __forceinline__ St st_merge(St x, St y) {
     if constexpr (K == K_ADD || K == K_SQ) return {x.a + y.a, 0.0f, 0.0f};
+    else if constexpr (K == K_DOT3) return {x.a + y.a, x.b + y.b, x.c + y.c};      // sum of x w, of x^2, of w^2
     else if constexpr (K == K_MAX) return {nan_max(x.a, y.a), 0.0f, 0.0f};
     else if constexpr (K == K_MIN) return {nan_min(x.a, y.a), 0.0f, 0.0f};
     else if constexpr (K == K_MUL) return {x.a * y.a, 0.0f, 0.0f};
@@ -95,8 +97,8 @@ template <int K>
 __device__ __forceinline__ St st_shfl_xor(St s, int off) {
     St o = s;
     o.a = __shfl_xor_sync(0xffffffffu, s.a, off);
-    if constexpr (K == K_MOM || K == K_LSE) o.b = __shfl_xor_sync(0xffffffffu, s.b, off);
-    if constexpr (K == K_MOM || K == K_ARG) o.c = __shfl_xor_sync(0xffffffffu, s.c, off);
+    if constexpr (K == K_MOM || K == K_LSE || K == K_DOT3) o.b = __shfl_xor_sync(0xffffffffu, s.b, off);
+    if constexpr (K == K_MOM || K == K_ARG || K == K_DOT3) o.c = __shfl_xor_sync(0xffffffffu, s.c, off);
     return o;
 }
 
@@ -125,6 +127,7 @@ __device__ __forceinline__ float2 row_finish(St s, float cols, float eps) {
     else if constexpr (OP == EMMYB200_ROW_LAYER_NORM) return {s.b, 1.0f / sqrtf(s.c / cols + eps)};
     else if constexpr (OP == EMMYB200_ROW_RMS_NORM) return {0.0f, 1.0f / sqrtf(s.a / cols + eps)};
     else if constexpr (OP == EMMYB200_ROW_NORMALIZE) return {0.0f, 1.0f / fmaxf(sqrtf(s.a), eps)};
+    else if constexpr (OP == EMMYB200_ROW_COSINE) return {s.a / fmaxf(sqrtf(s.b) * sqrtf(s.c), eps), 0.0f};
     else return {s.a, 0.0f};      // SUM, AMAX, AMIN, PROD (ARGMAX stores s.c)
 }
 

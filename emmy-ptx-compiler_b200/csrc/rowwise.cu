@@ -88,13 +88,13 @@ __device__ __forceinline__ St cluster_allreduce(St s, ReduceSlabs* slabs, int& c
     St o = st_identity<K>();
     if ((uint32_t)lane < csize) {
         o.a = peer_shared_load(&slabs->cta[buf].a, lane);
-        if constexpr (K == K_MOM || K == K_LSE) o.b = peer_shared_load(&slabs->cta[buf].b, lane);
-        if constexpr (K == K_MOM || K == K_ARG) o.c = peer_shared_load(&slabs->cta[buf].c, lane);
+        if constexpr (K == K_MOM || K == K_LSE || K == K_DOT3) o.b = peer_shared_load(&slabs->cta[buf].b, lane);
+        if constexpr (K == K_MOM || K == K_ARG || K == K_DOT3) o.c = peer_shared_load(&slabs->cta[buf].c, lane);
     }
     s = warp_allreduce<K>(o, 8, lane);                          // at most 8 CTAs, in lanes 0-7
     s.a = __shfl_sync(0xffffffffu, s.a, 0);
-    if constexpr (K == K_MOM || K == K_LSE) s.b = __shfl_sync(0xffffffffu, s.b, 0);
-    if constexpr (K == K_MOM || K == K_ARG) s.c = __shfl_sync(0xffffffffu, s.c, 0);
+    if constexpr (K == K_MOM || K == K_LSE || K == K_DOT3) s.b = __shfl_sync(0xffffffffu, s.b, 0);
+    if constexpr (K == K_MOM || K == K_ARG || K == K_DOT3) s.c = __shfl_sync(0xffffffffu, s.c, 0);
     return s;
 }
 
@@ -166,9 +166,17 @@ __global__ void __launch_bounds__(256) rowwise_cached_kernel(RowArgs a) {
             const int c = (first + i * G) * VEC;
             if (live && c < cols) {
 #pragma unroll
+                float wv[VEC];
+                if constexpr (K1 == K_DOT3) {                   // the second matrix streams by: it is not needed again
+                    const float* wr = a.w + row * a.cols + c;
+                    if constexpr (VEC == 4) { const float4 q = __ldcs(reinterpret_cast<const float4*>(wr)); wv[0] = q.x; wv[1] = q.y; wv[2] = q.z; wv[3] = q.w; }
+                    else wv[0] = __ldcs(wr);
+                }
+#pragma unroll
                 for (int e = 0; e < VEC; ++e) {
                     const float x = v[VEC * i + e];
-                    if constexpr (K1 == K_ADD) s.a += x;
+                    if constexpr (K1 == K_DOT3) { s.a = fmaf(x, wv[e], s.a); s.b = fmaf(x, x, s.b); s.c = fmaf(wv[e], wv[e], s.c); }
+                    else if constexpr (K1 == K_ADD) s.a += x;
                     else if constexpr (K1 == K_SQ) s.a = fmaf(x, x, s.a);
                     else if constexpr (K1 == K_MAX) { s.a = fmaxf(s.a, x); nan_probe = fmaf(x, 0x1p-120f, nan_probe); }
                     else if constexpr (K1 == K_MIN) { s.a = fminf(s.a, x); nan_probe = fmaf(x, 0x1p-120f, nan_probe); }
@@ -287,6 +295,7 @@ __device__ __forceinline__ St piece_state(const float* xr, const float* w, int64
     const int64_t step = (int64_t)kSplitThreads * VEC;
     for (int64_t base = c0 + (int64_t)threadIdx.x * VEC; base < c1; base += step * kTrip) {
         float v[kTrip][VEC];
+        float wv[K == K_DOT3 ? kTrip : 1][VEC];
 #pragma unroll
         for (int k = 0; k < kTrip; ++k) {
             const int64_t c = base + k * step;
@@ -297,7 +306,10 @@ __device__ __forceinline__ St piece_state(const float* xr, const float* w, int64
                 } else {
                     v[k][0] = __ldcs(xr + c);
                 }
-                if (w != nullptr) {                             // dot product: fold x * w (uniform over the grid)
+                if constexpr (K == K_DOT3) {                    // cosine: w is the same row of the second matrix
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) wv[k][e] = __ldcs(w + c + e);
+                } else if (w != nullptr) {                      // dot product: fold x * w (uniform over the grid)
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) v[k][e] *= __ldg(w + c + e);
                 }
@@ -323,7 +335,8 @@ __device__ __forceinline__ St piece_state(const float* xr, const float* w, int64
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) {
                     const float x = v[k][e];
-                    if constexpr (K == K_ADD) s.a += x;
+                    if constexpr (K == K_DOT3) { const float y = wv[k][e]; s.a = fmaf(x, y, s.a); s.b = fmaf(x, x, s.b); s.c = fmaf(y, y, s.c); }
+                    else if constexpr (K == K_ADD) s.a += x;
                     else if constexpr (K == K_SQ) s.a = fmaf(x, x, s.a);
                     else if constexpr (K == K_MAX) s.a = nan_max(s.a, x);
                     else if constexpr (K == K_MIN) s.a = nan_min(s.a, x);
@@ -358,7 +371,7 @@ __global__ void __launch_bounds__(kSplitThreads) rowwise_split_kernel(RowArgs a,
     const float* xr = a.x + row * a.cols;
     const int64_t c0 = (int64_t)piece * piece_len;
     const int64_t c1 = c0 + piece_len < a.cols ? c0 + piece_len : a.cols;
-    St s = piece_state<K, VEC>(xr, OP == EMMYB200_ROW_DOT ? a.w : nullptr, c0, c1, &slabs, round);
+    St s = piece_state<K, VEC>(xr, OP == EMMYB200_ROW_DOT ? a.w : (OP == EMMYB200_ROW_COSINE ? a.w + row * a.cols : nullptr), c0, c1, &slabs, round);
     if (pieces > 1) {
         if (threadIdx.x == 0) {
             partials[row * pieces + piece] = make_float4(s.a, s.b, s.c, 0.0f);
@@ -510,7 +523,7 @@ int dispatch(int op, const RowArgs& a, void* ws, cudaStream_t s) {
     switch (op) {
 #define EMMY_ROW_CASE(name) case EMMYB200_ROW_##name: return launch_op<EMMYB200_ROW_##name, VEC>(a, ws, s);
         EMMY_ROW_CASE(SUM) EMMY_ROW_CASE(MEAN) EMMY_ROW_CASE(AMAX) EMMY_ROW_CASE(AMIN) EMMY_ROW_CASE(PROD)
-        EMMY_ROW_CASE(VAR) EMMY_ROW_CASE(STD) EMMY_ROW_CASE(NORM2) EMMY_ROW_CASE(LOGSUMEXP) EMMY_ROW_CASE(ARGMAX) EMMY_ROW_CASE(DOT)
+        EMMY_ROW_CASE(VAR) EMMY_ROW_CASE(STD) EMMY_ROW_CASE(NORM2) EMMY_ROW_CASE(LOGSUMEXP) EMMY_ROW_CASE(ARGMAX) EMMY_ROW_CASE(DOT) EMMY_ROW_CASE(COSINE)
         EMMY_ROW_CASE(SOFTMAX) EMMY_ROW_CASE(LOG_SOFTMAX) EMMY_ROW_CASE(LAYER_NORM) EMMY_ROW_CASE(RMS_NORM)
         EMMY_ROW_CASE(NORMALIZE)
 #undef EMMY_ROW_CASE
@@ -518,7 +531,7 @@ int dispatch(int op, const RowArgs& a, void* ws, cudaStream_t s) {
     return fail(EMMYB200_ERR_ARG, "rowwise: unknown op %d", op);
 }
 
-bool known_op(int op) { return (op >= EMMYB200_ROW_SUM && op <= EMMYB200_ROW_DOT) || (op >= EMMYB200_ROW_SOFTMAX && op <= EMMYB200_ROW_NORMALIZE); }
+bool known_op(int op) { return (op >= EMMYB200_ROW_SUM && op <= EMMYB200_ROW_COSINE) || (op >= EMMYB200_ROW_SOFTMAX && op <= EMMYB200_ROW_NORMALIZE); }
 
 }  // namespace
 }  // namespace emmy
@@ -540,8 +553,8 @@ extern "C" int emmyb200_rowwise_f32(int op, const float* x, const float* weight,
     if (cols >= ((int64_t)1 << 31) || rows >= ((int64_t)1 << 31)) return fail(EMMYB200_ERR_SHAPE, "rowwise: extents are limited to 2^31 - 1");
     if (x == nullptr || y == nullptr) return fail(EMMYB200_ERR_ARG, "rowwise: null buffer");
     const bool affine = op == EMMYB200_ROW_LAYER_NORM || op == EMMYB200_ROW_RMS_NORM;
-    if (op == EMMYB200_ROW_DOT) {
-        if (weight == nullptr || bias != nullptr) return fail(EMMYB200_ERR_ARG, "rowwise: dot takes the vector as `weight` and no bias");
+    if (op == EMMYB200_ROW_DOT || op == EMMYB200_ROW_COSINE) {
+        if (weight == nullptr || bias != nullptr) return fail(EMMYB200_ERR_ARG, "rowwise: dot and cosine take their second operand as `weight` and no bias");
     } else if (!affine && (weight != nullptr || bias != nullptr)) {
         return fail(EMMYB200_ERR_ARG, "rowwise: only layer_norm, rms_norm and dot take a weight or bias");
     }

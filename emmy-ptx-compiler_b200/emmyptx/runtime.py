@@ -46,7 +46,7 @@ GEMM_DST_MULTICAST = 2
 ATT_CAUSAL = 1
 ATT_DST_MULTICAST = 2
 GATHER_TRUNC = 1
-ROW_OPS = {"sum": 0, "mean": 1, "amax": 2, "amin": 3, "prod": 4, "var": 5, "std": 6, "norm2": 7, "logsumexp": 8, "argmax": 9, "dot": 10,
+ROW_OPS = {"sum": 0, "mean": 1, "amax": 2, "amin": 3, "prod": 4, "var": 5, "std": 6, "norm2": 7, "logsumexp": 8, "argmax": 9, "dot": 10, "cosine": 11,
            "softmax": 16, "log_softmax": 17, "layer_norm": 18, "rms_norm": 19, "normalize": 20}
 ROW_MAP_FIRST = 16            # ops from here on write [rows, cols]
 
@@ -382,8 +382,9 @@ def rowwise(op: str, x, weight=None, bias=None, eps: float = 0.0, out=None, work
     for t in (weight, bias):
         if t is not None:
             _need_cuda(t)
-            if t.dtype != torch.float32 or t.numel() != cols or not t.is_contiguous():
-                raise TypeError("rowwise: weight / bias are contiguous float32 vectors of the row length")
+            want = x.numel() if op == "cosine" else cols               # cosine: the second matrix, same shape as x
+            if t.dtype != torch.float32 or t.numel() != want or not t.is_contiguous():
+                raise TypeError("rowwise: weight / bias are contiguous float32 vectors of the row length (cosine: a second array like x)")
     lib = library()
     need = lib.emmyb200_rowwise_workspace_bytes(code, rows, cols)
     if need > 0 and (workspace is None or workspace.numel() < need):

@@ -212,6 +212,7 @@ int emmyb200_attention_fwd_allgather(int dtype, int flags, const void* Q, const 
 #define EMMYB200_ROW_NORM2 7
 #define EMMYB200_ROW_LOGSUMEXP 8
 #define EMMYB200_ROW_ARGMAX 9
+#define EMMYB200_ROW_COSINE 11   /* y[r] = x[r] . w[r] / max(||x[r]|| ||w[r]||, eps), `weight` a second float[rows, cols] (fused.py:16) */
 #define EMMYB200_ROW_DOT 10      /* y[r] = sum_c x[r, c] * weight[c]: a matrix-vector product (tools/torch_cases/matmul.py:22) */
 #define EMMYB200_ROW_SOFTMAX 16
 #define EMMYB200_ROW_LOG_SOFTMAX 17

@@ -128,6 +128,7 @@ def rowwise_reference(op: str, x, weight=None, bias=None, eps: float = 0.0):
     if op == "logsumexp": return torch.logsumexp(x, -1)
     if op == "argmax": return x.argmax(-1)
     if op == "dot": return x @ w
+    if op == "cosine": return F.cosine_similarity(x, w, dim=-1, eps=eps)
     if op == "softmax": return torch.softmax(x, -1)
     if op == "log_softmax": return torch.log_softmax(x, -1)
     if op == "layer_norm": return F.layer_norm(x, (n,), w, b, eps)

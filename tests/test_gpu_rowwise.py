@@ -13,7 +13,7 @@ from oracle import reference
 
 pytestmark = pytest.mark.gpu
 
-REDUCING = ["sum", "mean", "amax", "amin", "prod", "var", "std", "norm2", "logsumexp", "argmax", "dot"]
+REDUCING = ["sum", "mean", "amax", "amin", "prod", "var", "std", "norm2", "logsumexp", "argmax", "dot", "cosine"]
 MAPPING = ["softmax", "log_softmax", "layer_norm", "rms_norm", "normalize"]
 
 
@@ -32,8 +32,10 @@ def _data(op, rows, cols, seed=0):
         x[(u >= 1e-4) & (u < 2e-4)] = 0.5
         x[u > 0.99] = -1.0
     w = torch.randn(cols, generator=g) if op in ("layer_norm", "rms_norm", "dot") else None
+    if op == "cosine":
+        w = torch.randn(rows, cols, generator=g)
     b = torch.randn(cols, generator=g) if op == "layer_norm" else None
-    eps = {"layer_norm": 1e-5, "rms_norm": 1e-6, "normalize": 1e-12}.get(op, 0.0)
+    eps = {"layer_norm": 1e-5, "rms_norm": 1e-6, "normalize": 1e-12, "cosine": 1e-8}.get(op, 0.0)
     return x, w, b, eps
 
 
@@ -69,6 +71,7 @@ def _check(op, got, ref, cols, rtol=1e-4, atol=1e-4):
     ("norm2", 64, 512, 1e-4, 1e-4),          # r_vector_norm
     ("logsumexp", 64, 512, 1e-4, 1e-4),      # r_logsumexp
     ("argmax", 64, 512, 0, 0),               # r_argmax, r_max_with_idx
+    ("cosine", 64, 256, 1e-4, 1e-5),         # f_cosine_sim
     ("dot", 256, 128, 1e-3, 1e-3),           # m_matvec (tools/torch_cases/matmul.py:22), the matmul class
     ("softmax", 64, 1000, 1e-3, 1e-5),       # f_softmax
     ("log_softmax", 48, 256, 1e-3, 1e-4),    # f_log_softmax
