@@ -11,9 +11,15 @@ row shard followed, for N > 1, by the all-gather of the output shards. Inputs ar
 tensors of the configuration's shape and distribution, resident in HBM before the timed region
 (`value`), or staged from pinned host memory through the public Python API every step (`e2e`).
 
+The timed region is `--steps` x `inner_repeats` passes, `inner_repeats` chosen (the same on every rank) so that the
+region lasts at least half a second at every GPU count: short regions run at the boost clock, long ones under the
+power cap, and a scaling curve must not mix the two. After the timed regions the result the last pass left behind is
+checked against the torch CPU evaluation on a seeded sample of rows -- at N > 1 rows that OTHER ranks computed and
+the fused gather delivered into this rank's copy -- and reported as `parity`.
+
 `--impl reference` times the reference's CPU path for the same workload -- the torch CPU evaluation of
-the same expression (tools/check_torch.py:194-237 defines it as the truth) -- on the host cores, on a
-bounded sample of the rows.
+the same expression (tools/check_torch.py:194-237 defines it as the truth) -- on the host cores: the whole
+workload per step when the run then ends within a few minutes, else a bounded sample named in `config.sample`.
 """
 from __future__ import annotations
 
@@ -202,6 +208,39 @@ class GemmWorkload(Workload):
     def kernel_work_per_launch(self):
         return 2.0 * self.rows * self.n * self.k
 
+    def parity(self, rows_per_owner: int = 0):
+        """The C the last pass left behind against the torch CPU evaluation (fp32 product of the rounded operands, the
+        epilogue on the fp32 value, tools/check_torch.py:194-237), on a seeded sample of whole rows of every rank's
+        slab as this rank holds them after the gather: first / last rows of the slab and of 128-row tiles, the rest
+        random. Tolerance |c - ref| <= 1e-2 |ref| + 1e-2 std(ref)."""
+        t = self.torch
+        per = rows_per_owner or max(32, 256 // self.world)
+        g = t.Generator().manual_seed(77 + self.rank)
+        b32 = self.b.float().cpu()
+        worst, checked, foreign = 0.0, 0, 0
+        for owner in range(self.world):
+            if not self.gather and owner != self.rank:
+                continue
+            fixed = [0, 127, 128, self.rows // 2 - 1, self.rows // 2, self.rows - 129, self.rows - 128, self.rows - 1]
+            pick = sorted({r for r in fixed if 0 <= r < self.rows} |
+                          set(t.randint(0, self.rows, (max(per - len(fixed), 0),), generator=g).tolist()))
+            if owner == self.rank:
+                a_rows = self.a[pick]
+            else:                                   # the owner's A, regenerated from its seed
+                gd = t.Generator(device=self.a.device)
+                gd.manual_seed(1000 + owner)
+                a_rows = (t.randn(self.rows, self.k, device=self.a.device, generator=gd, dtype=t.float32) / self.k**0.5).to(self.a.dtype)[pick]
+                foreign += len(pick)
+            ref = a_rows.float().cpu() @ b32
+            if self.epilogue == "gelu_tanh":
+                ref = t.nn.functional.gelu(ref, approximate="tanh")
+            got = self.c_full[[owner * self.rows + r for r in pick]].float().cpu()
+            bound = 1e-2 * ref.abs() + 1e-2 * ref.std()
+            worst = max(worst, float(((got - ref).abs() / bound).max()))
+            checked += len(pick)
+        return {"checked_rows": checked, "rows_from_other_ranks": foreign, "worst_ratio": worst, "ok": bool(worst <= 1.0),
+                "rule": "|c-ref| <= 1e-2|ref| + 1e-2 std(ref), ref = torch CPU fp32 on the same rounded operands"}
+
     def e2e_setup(self):
         t = self.torch
         self.host = {"a": self.a.cpu().pin_memory(), "b": self.b.cpu().pin_memory(),
@@ -274,6 +313,17 @@ class PointwiseWorkload(Workload):
 
     kernel_only = step
 
+    def parity(self):
+        """The reference's own tolerance class for transcendental cases (rtol = atol = 1e-5, tools/torch_cases/__init__.py:18)
+        against the float64 torch CPU evaluation, on a strided sample of at most 2^20 elements."""
+        t = self.torch
+        idx = t.arange(0, self.n, max(1, self.n // 2**20), device=self.x.device)
+        x = self.x[idx].cpu().double()
+        ref = t.exp(x) + t.sin(x) * t.tanh(x)
+        err = (self.y[idx].cpu().double() - ref).abs() / (1e-5 + 1e-5 * ref.abs())
+        return {"checked_elements": int(idx.numel()), "worst_ratio": float(err.max()), "ok": bool(err.max() <= 1.0),
+                "rule": "isclose(rtol=1e-5, atol=1e-5) against torch CPU float64"}
+
     def work_per_step(self):
         return 8.0 * self.n * self.world
 
@@ -310,6 +360,14 @@ class GemmF32Workload(Workload):
         self.rt.gemm_f32(self.a, self.b, out=self.c, workspace=self.ws)
 
     kernel_only = step
+
+    def parity(self):
+        t = self.torch
+        rows = t.randint(0, self.s, (128,), generator=t.Generator().manual_seed(81))
+        ref = self.a[rows].cpu().double() @ self.b.cpu().double()
+        err = (self.c[rows].cpu().double() - ref).abs() / (1e-3 + 1e-3 * ref.abs())
+        return {"checked_rows": 128, "worst_ratio": float(err.max()), "ok": bool(err.max() <= 1.0),
+                "rule": "isclose(rtol=1e-3, atol=1e-3) against torch CPU float64 (tools/torch_cases/__init__.py:20)"}
 
     def launches_per_step(self):
         return 3
@@ -349,6 +407,14 @@ class RowWorkload(PointwiseWorkload):
 
     kernel_only = step
 
+    def parity(self):
+        t = self.torch
+        rows = t.randint(0, self.x.shape[0], (256,), generator=t.Generator().manual_seed(80))
+        ref = t.softmax(self.x[rows].cpu().double(), -1)
+        err = (self.y[rows].cpu().double() - ref).abs() / (1e-5 + 1e-3 * ref.abs())
+        return {"checked_rows": 256, "worst_ratio": float(err.max()), "ok": bool(err.max() <= 1.0),
+                "rule": "isclose(rtol=1e-3, atol=1e-5) against torch CPU float64 (tools/torch_cases/fused.py:6)"}
+
 
 class GatherWorkload(PointwiseWorkload):
     dtype = "i32"
@@ -368,6 +434,15 @@ class GatherWorkload(PointwiseWorkload):
         self.rt.index_gather(self.x, 7919, 13, 3, 2, out=self.y)
 
     kernel_only = step
+
+    def parity(self):
+        """Bit-exact against torch CPU (int64 index arithmetic, floor division) on a seeded sample of 2^20 positions."""
+        t = self.torch
+        i = t.randint(0, self.n, (2**20,), generator=t.Generator().manual_seed(79), dtype=t.int64)
+        x = self.x.cpu()
+        ref = t.bitwise_xor(t.div(x[(i * 7919 + 13) % self.n], 3, rounding_mode="floor"), (i >> 2).to(t.int32))
+        same = bool(t.equal(self.y.cpu()[i], ref))
+        return {"checked_elements": int(i.numel()), "worst_ratio": 0.0 if same else float("inf"), "ok": same, "rule": "bit-exact"}
 
 
 class AttentionWorkload(Workload):
@@ -431,6 +506,36 @@ class AttentionWorkload(Workload):
 
     def kernel_work_per_launch(self):
         return 4.0 * self.local * self.seq * self.seq * self.d
+
+    def parity(self, rows_per_unit: int = 64):
+        """O as the last pass left it against the torch CPU fp32 evaluation of softmax(q k^T / sqrt(d)) v, on seeded
+        query rows of the first and last unit of every rank's share as this rank holds them after the gather."""
+        t = self.torch
+        g = t.Generator().manual_seed(78 + self.rank)
+        worst, checked, foreign = 0.0, 0, 0
+        for owner in range(self.world):
+            if not self.gather and owner != self.rank:
+                continue
+            if owner == self.rank:
+                q, k, v = self.q, self.k, self.v
+            else:
+                gd = t.Generator(device=self.q.device)
+                gd.manual_seed(2000 + owner)
+                q, k, v = (t.randn(self.local, self.seq, self.d, device=self.q.device, generator=gd, dtype=t.float32).to(t.bfloat16)
+                           for _ in range(3))
+            for u in sorted({0, self.local - 1}):
+                fixed = [0, 127, 128, self.seq - 1]
+                pick = sorted(set(fixed) | set(t.randint(0, self.seq, (rows_per_unit - len(fixed),), generator=g).tolist()))
+                qs, ks, vs = q[u][pick].float().cpu(), k[u].float().cpu(), v[u].float().cpu()
+                ref = t.softmax(qs @ ks.t() * self.d ** -0.5, -1) @ vs
+                got = self.o_full[owner * self.local + u][pick].float().cpu()
+                bound = 1e-2 * ref.abs() + 1e-2 * ref.std()
+                worst = max(worst, float(((got - ref).abs() / bound).max()))
+                checked += len(pick)
+                foreign += len(pick) if owner != self.rank else 0
+            del q, k, v
+        return {"checked_rows": checked, "rows_from_other_ranks": foreign, "worst_ratio": worst, "ok": bool(worst <= 1.0),
+                "rule": "|o-ref| <= 1e-2|ref| + 1e-2 std(ref), ref = torch CPU fp32 on the same rounded operands"}
 
     def e2e_setup(self):
         t = self.torch
@@ -517,15 +622,16 @@ def graph_timed(torch, fn, launches, reps=5):
 
 
 # ---- the reference's CPU path -------------------------------------------------------------------------------
-def cpu_reference_step(name: str, threads: int):
-    """(callable running one bounded sample, work of that sample in the metric's base unit, unit scale,
-    description). The expression is the case's torch code on CPU, all host threads."""
+def cpu_reference_step(name: str, threads: int, full: bool = False):
+    """(callable running one pass or a bounded sample of it, work of that call in the metric's base unit, unit scale,
+    description of the sample). The expression is the case's torch code on CPU, all host threads. `full` asks for
+    the whole workload where the default is a sample (the two GEMM configurations and attention)."""
     import torch
     import numpy as np
     torch.set_num_threads(threads)
     if name in ("c3", "c4"):
         n = k = 16384 if name == "c4" else 4096
-        rows = 1024 if name == "c4" else 4096
+        rows = n if (full or name == "c3") else 1024
         td = torch.bfloat16 if name == "c4" else torch.float16
         g = torch.Generator().manual_seed(0)
         a = (torch.randn(rows, k, generator=g) / k**0.5).to(td)
@@ -534,9 +640,10 @@ def cpu_reference_step(name: str, threads: int):
             fn = lambda: torch.nn.functional.gelu(a @ b, approximate="tanh")
         else:
             fn = lambda: a @ b
-        return fn, 2.0 * rows * n * k, 1e12, f"{rows} of {n} rows of A against the full B, torch CPU {td}"
+        what = "the whole product" if rows == n else f"{rows} of {n} rows of A against the full B"
+        return fn, 2.0 * rows * n * k, 1e12, f"{what}, torch CPU {str(td).split('.')[-1]}"
     if name == "c5":
-        units, s, d = 4, 4096, 128
+        units, s, d = (256 if full else 4), 4096, 128
         g = torch.Generator().manual_seed(0)
         q, kk, v = (torch.randn(units, s, d, generator=g).to(torch.bfloat16) for _ in range(3))
         fn = lambda: torch.nn.functional.scaled_dot_product_attention(q, kk, v)
@@ -577,27 +684,47 @@ def time_cpu(fn, budget_s: float = 12.0, min_reps: int = 2) -> float:
     return best
 
 
+METRIC = {"c1": "elementwise_gbs", "c2": "elementwise_gbs", "softmax": "elementwise_gbs", "c5": "attention_tflops"}
+DTYPE = {"c1": "f32", "c2": "i32", "c3": "f16", "softmax": "f32", "f32mm": "f32"}
+SCALING = {"c1": "weak", "c2": "weak", "softmax": "weak", "f32mm": "weak"}
+
+
+def config_for(workload: str, world: int, size=None) -> dict:
+    """The `config` object, the same for both arms of a comparison (what differs between them is reported elsewhere:
+    `collective` and `inner_repeats` on the GPU arm, `cpu_baseline.sample` on the CPU arm)."""
+    return {"workload": WORKLOADS[workload] + (f" [SIZE OVERRIDE {size}: not the benchmark configuration]" if size else ""),
+            "l2": "8 MiB working set, L2-resident by construction of the configuration" if workload == "c1" else "inputs larger than L2",
+            "parallelism": f"rows/{world}" if workload in ("c3", "c4") else (f"units/{world}" if workload == "c5" else f"chunks/{world}")}
+
+
 def run_reference(args, rank: int) -> int:
+    """The reference arm: the torch CPU evaluation of the workload on this box's host cores (rank 0 only). Each step is
+    the whole workload when `steps + warmup` of them end within about four minutes, else a bounded sample, named."""
     if rank != 0:
         return 0
     threads = os.cpu_count() or 1
     fn, work, scale, sample = cpu_reference_step(args.workload, threads)
+    t0 = time.perf_counter()
+    fn()
+    t_sample = time.perf_counter() - t0
+    if args.workload in ("c4", "c5"):
+        full_work = 2.0 * 16384**3 if args.workload == "c4" else 4.0 * 256 * 4096 * 4096 * 128
+        if t_sample * (full_work / work) * (args.steps + args.warmup + 1) < 240.0:
+            fn, work, scale, sample = cpu_reference_step(args.workload, threads, full=True)
     for _ in range(args.warmup):
         fn()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         fn()
     dt = time.perf_counter() - t0
-    w0 = WORKLOADS[args.workload]
     value = work * args.steps / dt / scale
     unit = "TFLOP/s" if scale == 1e12 else "GB/s"
-    metric = {"c1": "elementwise_gbs", "c2": "elementwise_gbs", "softmax": "elementwise_gbs",
-              "c5": "attention_tflops"}.get(args.workload, "gemm_tflops")
+    cfg = config_for(args.workload, args.gpus, args.size)
     print(json.dumps({
-        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": {"c1": "f32", "c2": "i32", "c3": "f16", "softmax": "f32", "f32mm": "f32"}.get(args.workload, "bf16"), "data": "synthetic",
-        "config": {"workload": w0, "note": "each step is a bounded sample of the workload on the host cores"},
+        "impl": "reference", "metric": METRIC.get(args.workload, "gemm_tflops"), "value": value, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": SCALING.get(args.workload, "strong"), "vs_baseline": None, "dtype": DTYPE.get(args.workload, "bf16"), "data": "synthetic",
+        "config": cfg, "sample": sample,
         "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "reference", "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -606,6 +733,80 @@ def run_reference(args, rank: int) -> int:
 
 
 # ---- main ---------------------------------------------------------------------------------------------------
+MIN_REGION_S = 0.5
+
+
+def agree(torch, dist, world, x: float) -> float:
+    """The maximum of a host number over the ranks (so that every rank takes the same decision from it)."""
+    if world == 1:
+        return x
+    t = torch.tensor([x], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def inner_repeats(torch, dist, world, fn, steps: int) -> int:
+    """Passes per step such that `steps` steps last at least MIN_REGION_S, from a short probe; the same on every rank."""
+    probe = timed(torch, dist, world, fn, 2, 1) / 2 * 1e-3
+    return max(1, int(-(-MIN_REGION_S // max(probe * steps, 1e-9))))
+
+
+def roofline_block(wl, k_ms: float, pk: dict, pk_kind: str, traffic, clocks: dict) -> dict:
+    if wl.bound == "tensor":
+        achieved = wl.kernel_work_per_launch() / (k_ms * 1e-3) / 1e12
+        sustained, burst = pk.get("bf16_tflops_sustained", pk["bf16_tflops"]), pk["bf16_tflops"]
+        return {"bound": "tensor", "achieved": achieved, "peak": sustained, "unit": "TFLOP/s", "frac": achieved / sustained,
+                "frac_sustained": achieved / sustained, "frac_burst": achieved / burst, "peak_burst": burst,
+                "peak_source": f"{pk_kind} cuBLAS bf16: the sustained figure (the kernel is timed back to back for >= {MIN_REGION_S} s, under the power cap); frac_burst is against the burst figure",
+                "sm_mhz_during": clocks.get("sm_mhz"), "traffic": traffic, "kernel_ms": k_ms}
+    achieved = wl.kernel_work_per_launch() / (k_ms * 1e-3) / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+            "peak_source": f"{pk_kind} copy bandwidth", "sm_mhz_during": clocks.get("sm_mhz"), "traffic": traffic, "kernel_ms": k_ms}
+
+
+def measure(torch, dist, world, local_rank, wl, steps: int, warmup: int, pk, pk_kind, traffic) -> dict:
+    """Times one workload: the step (max over ranks), the kernel alone (this rank), end to end from pinned host memory."""
+    from emmyptx import runtime
+    inner = inner_repeats(torch, dist, world, wl.step, steps)
+
+    def passes(fn):
+        def run():
+            for _ in range(inner):
+                fn()
+        return run
+
+    with ClockSampler(local_rank) as clocks:
+        total_ms = timed(torch, dist, world, passes(wl.step), steps, warmup)
+    # kernel-only time for the roofline: the same number of launches, after the timed region, on the launching stream
+    with ClockSampler(local_rank) as k_clocks:
+        k_ms = timed(torch, dist, 1, passes(wl.kernel_only), steps, warmup) / (steps * inner)
+    status = runtime.device_status()
+    ms_per_step = total_ms / (steps * inner)
+    scale = 1e12 if wl.unit == "TFLOP/s" else 1e9
+    try:
+        torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
+        parity = wl.parity()                      # of the result the passes above left behind
+    except Exception as e:  # noqa: BLE001 - a failed check is reported, not hidden
+        parity = {"ok": False, "error": f"{type(e).__name__}: {e}"[:300]}
+    if world > 1:
+        flag = torch.tensor([1.0 if parity.get("ok") else 0.0, -float(parity.get("worst_ratio", float("inf")))], device="cuda", dtype=torch.float64)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        parity["ok_on_every_rank"] = bool(flag[0].item() == 1.0)
+        parity["worst_ratio_over_ranks"] = -float(flag[1].item())
+        parity["ok"] = parity["ok_on_every_rank"]
+    # end to end: pinned host inputs in, result out, through the Python API, every step
+    h2d, d2h = wl.e2e_setup()
+    e2e_steps = max(10, steps)
+    e2e_ms = timed(torch, dist, world, wl.e2e_step, e2e_steps, 3) / e2e_steps
+    return {"value": wl.work_per_step() / (ms_per_step * 1e-3) / scale, "ms_per_step": ms_per_step, "inner_repeats": inner,
+            "timed_region_s": total_ms * 1e-3, "launches": steps * inner * wl.launches_per_step(),
+            "roofline": roofline_block(wl, k_ms, pk, pk_kind, traffic, k_clocks.summary()), "clocks": clocks.summary(),
+            "e2e": {"value": wl.work_per_step() / (e2e_ms * 1e-3) / scale, "unit": wl.unit, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps, "warmup": 3,
+                    "h2d_GBps_per_rank": h2d / max(world, 1) / (e2e_ms * 1e-3) / 1e9},
+            "parity": parity, "device_status": status}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -639,47 +840,42 @@ def main() -> int:
 
     wl = make_workload(args.workload, rank, world, dev, args.size)
     pk, pk_kind = peaks()
-
-    # kernel-only time for the roofline (CUDA events on the launching stream, same steps)
-    k_ms = timed(torch, dist, 1, wl.kernel_only, args.steps, args.warmup) / args.steps
-    # the timed region proper
-    with ClockSampler(local_rank) as clocks:
-        total_ms = timed(torch, dist, world, wl.step, args.steps, args.warmup)
-    status = runtime.device_status()
-    ms_per_step = total_ms / args.steps
-    scale = 1e12 if wl.unit == "TFLOP/s" else 1e9
-    value = wl.work_per_step() / (ms_per_step * 1e-3) / scale
-
-    # end to end: pinned host inputs in, result out, through the Python API, every step
-    h2d, d2h = wl.e2e_setup()
-    e2e_steps = max(2, min(args.steps, 5))
-    e2e_ms = timed(torch, dist, world, wl.e2e_step, e2e_steps, 1) / e2e_steps
-    e2e_value = wl.work_per_step() / (e2e_ms * 1e-3) / scale
-
-    if wl.bound == "tensor":
-        achieved = wl.kernel_work_per_launch() / (k_ms * 1e-3) / 1e12
-        peak = pk.get("bf16_tflops_sustained", pk["bf16_tflops"])
-        roof_unit, peak_note = "TFLOP/s", f"{pk_kind} cuBLAS bf16, sustained"
-    else:
-        achieved = wl.kernel_work_per_launch() / (k_ms * 1e-3) / 1e9
-        peak = pk["hbm_gbs"]
-        roof_unit, peak_note = "GB/s", f"{pk_kind} copy bandwidth"
     traffic = None if (args.size or world > 1) else DRAM_TRAFFIC.get(args.workload)
+    if args.no_extras and args.size:            # a profiler capture of a small case: one plain pass per step, nothing else
+        ms = timed(torch, dist, world, wl.step, args.steps, args.warmup) / args.steps
+        if rank == 0:
+            print(json.dumps({"metric": wl.metric, "ms_per_step": ms, "config": config_for(args.workload, world, args.size), "profiling_run": True}))
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+    m = measure(torch, dist, world, local_rank, wl, args.steps, args.warmup, pk, pk_kind, traffic)
 
     line = {
-        "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype,
-        "data": "synthetic",
-        "config": {"workload": WORKLOADS[args.workload] + (f" [SIZE OVERRIDE {args.size}: not the benchmark configuration]" if args.size else ""), "l2": "inputs larger than L2" if args.workload not in ("c1",) else
-                   "8 MiB working set, L2-resident by construction of the configuration", "parallelism": f"rows/{world}",
-                   "collective": "none" if world == 1 else getattr(wl, "collective", "nccl all_gather of the output shards")},
-        "roofline": {"bound": "tensor" if wl.bound == "tensor" else "hbm", "achieved": achieved, "peak": peak, "unit": roof_unit,
-                     "frac": achieved / peak, "traffic": traffic, "peak_source": peak_note, "kernel_ms": k_ms},
-        "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-        "gpu_launches": args.steps * wl.launches_per_step(),
-        "clocks": clocks.summary(),
-        "device_status": status,
+        "metric": wl.metric, "value": m["value"], "unit": wl.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": m["ms_per_step"], "inner_repeats": m["inner_repeats"], "timed_region_s": m["timed_region_s"],
+        "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": config_for(args.workload, world, args.size),
+        "collective": "none" if world == 1 else getattr(wl, "collective", "nccl all_gather of the output shards"),
+        "roofline": m["roofline"], "e2e": m["e2e"], "parity": m["parity"], "gpu_launches": m["launches"], "clocks": m["clocks"],
+        "device_status": m["device_status"],
+        "step_definition": f"one pass of the workload; the timed region is steps x inner_repeats = {args.steps * m['inner_repeats']} passes, "
+                           "ms_per_step and value are per pass",
     }
+    if world > 1 and args.workload == "c4" and not args.no_extras:
+        # the other sharded configuration at this GPU count: unit-sharded attention with the gather fused into the kernel
+        del wl
+        torch.cuda.empty_cache()
+        try:
+            wl5 = make_workload("c5", rank, world, dev)
+            m5 = measure(torch, dist, world, local_rank, wl5, max(5, args.steps // 2), 3, pk, pk_kind, None)
+            line["other_workloads"] = {"c5": {"workload": WORKLOADS["c5"], "value": m5["value"], "unit": wl5.unit,
+                                              "ms_per_step": m5["ms_per_step"], "kernel_ms": m5["roofline"]["kernel_ms"],
+                                              "inner_repeats": m5["inner_repeats"], "collective": wl5.collective,
+                                              "roofline": m5["roofline"], "e2e": m5["e2e"], "parity": m5["parity"], "clocks": m5["clocks"],
+                                              "config": config_for("c5", world)}}
+            del wl5
+        except Exception as e:  # noqa: BLE001 - must not hide the main line
+            line["other_workloads"] = {"c5": {"error": f"{type(e).__name__}: {e}"[:300]}}
 
     if rank == 0 and world == 1 and not args.no_extras:
         threads = os.cpu_count() or 1
@@ -687,7 +883,8 @@ def main() -> int:
         best = time_cpu(fn)
         line["cpu_baseline"] = {"value": work / best / cscale, "unit": wl.unit, "cores": threads, "kind": "reference",
                                 "sample": sample}
-        line["other_workloads"] = other_workloads(torch, dist, dev, pk, args.workload)
+        del fn
+        line["other_workloads"] = other_workloads(torch, dist, dev, local_rank, pk, pk_kind, args.workload)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -695,40 +892,48 @@ def main() -> int:
     return 0
 
 
-def other_workloads(torch, dist, dev, pk, skip: str) -> dict:
-    """Short device-resident measurements of the remaining configurations (1 GPU), each with its roofline
-    fraction; kernels of a few microseconds are timed inside a CUDA graph."""
+def other_workloads(torch, dist, dev, local_rank, pk, pk_kind, skip: str) -> dict:
+    """The remaining configurations on one GPU, each measured like the main line (timed region of at least half a
+    second, kernel-only roofline with the peak named, end to end from pinned host memory, parity of the result, the
+    torch CPU baseline on this host's cores); kernels of a few microseconds are also timed inside a CUDA graph."""
     out = {}
+    threads = os.cpu_count() or 1
     for name in ("c1", "c2", "c3", "c4", "c5"):
         if name == skip:
             continue
         try:
             wl = make_workload(name, 0, 1, dev)
+            m = measure(torch, dist, 1, local_rank, wl, 5, 3, pk, pk_kind, DRAM_TRAFFIC.get(name))
+            entry = {"workload": WORKLOADS[name], "value": m["value"], "unit": wl.unit, "ms": m["ms_per_step"], "inner_repeats": m["inner_repeats"],
+                     "roofline": m["roofline"], "frac_of_peak": m["roofline"]["frac"], "peak_used": m["roofline"]["peak_source"],
+                     "e2e": m["e2e"], "parity": m["parity"], "clocks": m["clocks"]}
+            if wl.bound == "tensor":
+                entry["frac_of_burst_peak"] = m["roofline"]["frac_burst"]
             if name == "c1":
-                ms = graph_timed(torch, wl.kernel_only, 50)
-            else:
-                ms = timed(torch, dist, 1, wl.kernel_only, 5, 3) / 5
-            scale = 1e12 if wl.unit == "TFLOP/s" else 1e9
-            val = wl.kernel_work_per_launch() / (ms * 1e-3) / scale
-            peak = pk.get("bf16_tflops", 1.0) if wl.bound == "tensor" else pk["hbm_gbs"]
-            out[name] = {"workload": WORKLOADS[name], "value": val, "unit": wl.unit, "ms": ms, "frac_of_peak": val / peak}
+                g_ms = graph_timed(torch, wl.kernel_only, 50)
+                entry["cuda_graph_us_per_launch"] = g_ms * 1e3
+                entry["cuda_graph_GBps"] = wl.kernel_work_per_launch() / (g_ms * 1e-3) / 1e9
             del wl
             torch.cuda.empty_cache()
+            fn, work, cscale, sample = cpu_reference_step(name, threads)
+            best = time_cpu(fn, budget_s=3.0)
+            entry["cpu_baseline"] = {"value": work / best / cscale, "unit": entry["unit"], "cores": threads, "kind": "reference", "sample": sample}
+            del fn
+            out[name] = entry
         except Exception as e:  # noqa: BLE001 - a missing kernel must not hide the main line
             out[name] = {"workload": WORKLOADS[name], "error": f"{type(e).__name__}: {e}"[:200]}
     try:
-        from emmyptx import runtime
-        n = 2**28
-        x = torch.rand(n, device=dev) * 8 - 4
-        y = torch.empty_like(x)
-        ms = timed(torch, dist, 1, lambda: runtime.pointwise("exp_sin_tanh", x, out=y), 5, 3) / 5
-        out["c1_at_2^28"] = {"value": 8.0 * n / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms": ms,
-                             "frac_of_peak": 8.0 * n / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+        wl = PointwiseWorkload(2**28, 0, 1, dev)
+        m = measure(torch, dist, 1, local_rank, wl, 5, 3, pk, pk_kind, None)
+        out["c1_at_2^28"] = {"value": m["value"], "unit": "GB/s", "ms": m["ms_per_step"], "frac_of_peak": m["roofline"]["frac"],
+                             "peak_used": m["roofline"]["peak_source"], "parity": m["parity"], "e2e": m["e2e"]}
+        del wl
+        torch.cuda.empty_cache()
     except Exception as e:  # noqa: BLE001
         out["c1_at_2^28"] = {"error": str(e)[:200]}
-    # the reference's own kernels (its compiler's PTX for C1 and C2, committed as text fixtures) JIT-loaded on this GPU
-    # and timed next to ours on the same buffers. The GEMM and attention configurations are left out: their PTX
-    # depends on a schedule (tiling, staging) that the reference's tracer chooses and that is not available here.
+    # the reference's own kernels (its compiler's PTX, committed as text fixtures) JIT-loaded on this GPU and timed next to
+    # ours on the same buffers: the two streaming configurations, and configuration 3 as the one-warp-per-cell mma.sync
+    # kernel the stand-in IR compiles to (the tile sizes the reference's tracer would schedule are unknown: a floor).
     try:
         out["reference_ptx_on_this_gpu"] = reference_ptx_timings(torch, dist, dev)
     except Exception as e:  # noqa: BLE001
@@ -742,14 +947,16 @@ def other_workloads(torch, dist, dev, pk, skip: str) -> dict:
             ms = timed(torch, dist, 1, lambda: runtime.rowwise(op, x, out=y), 5, 3) / 5
             byts = 4.0 * (x.numel() + y.numel())
             out[f"row_{op}_65536x1024"] = {"value": byts / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms": ms,
-                                           "frac_of_peak": byts / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+                                           "frac_of_peak": byts / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "peak_used": f"{pk_kind} copy bandwidth"}
         del x, y
         q, k, v = (torch.randn(64, 4096, 128, device=dev).to(torch.bfloat16) for _ in range(3))
         o = torch.empty_like(q)
-        ms = timed(torch, dist, 1, lambda: runtime.attention(q, k, v, causal=True, out=o), 5, 3) / 5
+        ms = timed(torch, dist, 1, lambda: runtime.attention(q, k, v, causal=True, out=o), 20, 3) / 20
         flop = 4.0 * 64 * 128 * (4096 * 4097 / 2)
         out["attention_causal_64x4096x128"] = {"value": flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": ms,
-                                               "frac_of_peak": flop / (ms * 1e-3) / 1e12 / pk.get("bf16_tflops", 1.0)}
+                                               "frac_of_peak": flop / (ms * 1e-3) / 1e12 / pk.get("bf16_tflops", 1.0),
+                                               "peak_used": f"{pk_kind} cuBLAS bf16, burst"}
+        del q, k, v, o
     except Exception as e:  # noqa: BLE001
         out["next_rows"] = {"error": str(e)[:200]}
     return out
@@ -783,6 +990,28 @@ def reference_ptx_timings(torch, dist, dev) -> dict:
                       "reference_GBps": 8.0 * n / (ms_ref * 1e-3) / 1e9, "outputs_agree": same}
         del x, y_ref, y_ours
         torch.cuda.empty_cache()
+    # configuration 3 through the reference's tensor-core lowering: one warp per m16n8k16 cell, fragments read from global
+    # memory (emmyptx/mma.py:128-180). Two launches, the second timed.
+    info = manifest["c3_f16_mm_4096"]
+    g = info["gemm"]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    a = (torch.randn(g["m"], g["k"], device=dev, generator=gen) / g["k"] ** 0.5).half()
+    b = (torch.randn(g["k"], g["n"], device=dev, generator=gen) / g["k"] ** 0.5).half()
+    c_ref, c_ours = torch.zeros(g["m"], g["n"], device=dev, dtype=torch.float16), torch.zeros(g["m"], g["n"], device=dev, dtype=torch.float16)
+    with PtxModule((golden / "c3_f16_mm_4096.ref.ptx").read_text()) as m:
+        fn = m.function(info["entry"])
+        ptrs = [a.data_ptr(), b.data_ptr(), c_ref.data_ptr()]
+        ref = lambda: m.launch(fn, ptrs, info["launch"]["grid"][0], info["launch"]["block"][0], stream=torch.cuda.current_stream().cuda_stream)
+        ms_ref = timed(torch, dist, 1, ref, 1, 1)
+    ms_ours = timed(torch, dist, 1, lambda: runtime.gemm(a, b, out=c_ours), 20, 3) / 20
+    diff = (c_ref.float() - c_ours.float()).abs()
+    res["c3_4096"] = {"reference_kernel_ms": ms_ref, "this_library_ms": ms_ours, "speedup": ms_ref / ms_ours,
+                      "reference_TFLOPs": 2.0 * 4096**3 / (ms_ref * 1e-3) / 1e12,
+                      "outputs_agree": bool((diff <= 2.0 ** -9 * c_ref.float().abs() + 1e-3).all()),
+                      "outputs_identical_fraction": float((c_ref == c_ours).float().mean()),
+                      "note": "the reference kernel is its lowering of the stand-in IR (one warp per 16x8 cell, no staging): "
+                              "a floor for the reference, whose tracer's real schedule is not available"}
     return res
 
 

@@ -25,16 +25,22 @@ except ImportError:
 
 
 def find_launch(meta: dict | None, kernel, graph) -> dict:
-    """This kernel's entry in meta.json, or a best guess from the IR when there is none."""
-    if meta is not None:
-        for k in meta.get("kernels", []):
-            if k.get("entry") == kernel.name:
-                return k
-        if len(meta.get("kernels", [])) == 1:
-            return meta["kernels"][0]
-    node = next(n for n in graph.nodes.values() if n.op is kernel)
-    outputs = [t.name for t in node.outputs]
-    return {"arg_order": [*node.inputs, *outputs], "block": [256, 1, 1], "grid": [0, 1, 1], "smem_bytes": 0}
+    """The launch descriptor for `kernel` (same contract as the reference's compile.py:21-31).
+
+    Looked up in `meta["kernels"]` by entry name; a meta file that describes a single kernel is taken to mean this
+    one whatever it is called. With no usable meta the descriptor is derived from the graph: parameters are the
+    kernel node's inputs followed by its outputs, 256-thread blocks, an unknown grid (0) and no dynamic shared
+    memory -- the handle's own launch geometry does not depend on it.
+    """
+    described = (meta or {}).get("kernels", [])
+    by_name = [entry for entry in described if entry.get("entry") == kernel.name]
+    if by_name:
+        return by_name[0]
+    if len(described) == 1:
+        return described[0]
+    owner = [node for node in graph.nodes.values() if node.op is kernel][0]
+    params = list(owner.inputs) + [tensor.name for tensor in owner.outputs]
+    return {"arg_order": params, "block": [256, 1, 1], "grid": [0, 1, 1], "smem_bytes": 0}
 
 
 def main() -> int:

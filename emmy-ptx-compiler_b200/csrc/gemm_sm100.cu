@@ -563,7 +563,9 @@ static int gemm_entry(const GemmCall& g, void* cuda_stream) {
 // ---- fp32-accurate products: operands split into three bf16 planes --------------------------------------------------
 // src: `planes` matrices of rows x cols fp32 (leading dimension ld, plane_stride apart). dst: for every matrix three
 // bf16 planes of rows x pitch (pitch a multiple of 8, columns beyond cols zero): x1 = bf16(x), x2 = bf16(x - x1),
-// x3 = bf16(x - x1 - x2). A non-finite x keeps its value in x1 and zeros in x2, x3.
+// x3 = bf16(x - x1 - x2). A finite x beyond the largest bf16 (3.39e38) takes that value as x1, so the planes stay
+// finite; a non-finite x keeps its value in x1 and zeros in x2, x3 (the product passes then meet inf * 0: an
+// infinite operand gives NaN where a scalar fp32 loop gives +-inf, which the header states).
 __global__ void __launch_bounds__(256) split3_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t planes,
                                                      int64_t rows, int64_t cols, int64_t ld, int64_t plane_stride, int64_t pitch) {
     const int64_t groups_per_row = pitch / 8;
@@ -577,8 +579,12 @@ __global__ void __launch_bounds__(256) split3_kernel(const float* __restrict__ s
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float x = c0 + j < cols ? __ldg(in + j) : 0.0f;
-            const __nv_bfloat16 h1 = __float2bfloat16_rn(x);
-            const float f1 = __bfloat162float(h1);
+            __nv_bfloat16 h1 = __float2bfloat16_rn(x);
+            float f1 = __bfloat162float(h1);
+            if (fabsf(f1) > 3.3895314e38f && fabsf(x) <= 3.4028235e38f) {      // rounded up to inf: clamp to the largest bf16
+                f1 = copysignf(3.3895314e38f, x);
+                h1 = __float2bfloat16_rn(f1);
+            }
             const bool finite = fabsf(f1) <= 3.3895314e38f;
             const float r1 = finite ? x - f1 : 0.0f;
             const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);

@@ -125,6 +125,16 @@ class FuncCallExpr(_Expr):
 
 
 # ---- statements ------------------------------------------------------------------------------------------
+class _Stmt:
+    def pretty(self) -> list:
+        """Lines describing the statement, the first one its headline: the tracer's nodes have this method and
+        the reference's tensor-core lowering names a statement by it in diagnostics (emmyptx/mma.py:67, 83, 184,
+        200; emmyptx/kernel.py:479)."""
+        shown = ", ".join(f"{f.name}={getattr(self, f.name)!r}" for f in dataclasses.fields(self)
+                          if isinstance(getattr(self, f.name), (str, int, bool)))
+        return [f"{type(self).__name__}({shown})"]
+
+
 @_node
 class Op:
     name: str
@@ -210,7 +220,7 @@ class Smem:
 
 
 @_node
-class RegFragment:
+class RegFragment(_Stmt):
     name: str
     role: str
     dtype: Any
@@ -220,7 +230,7 @@ class RegFragment:
 
 
 @_node
-class LdmatrixLoad:
+class LdmatrixLoad(_Stmt):
     frag: str
     role: str
     src_buffer: str
@@ -238,7 +248,7 @@ class LdmatrixLoad:
 
 
 @_node
-class MmaSyncPtx:
+class MmaSyncPtx(_Stmt):
     c_frag: str
     a_frag: str
     b_frag: str
@@ -250,7 +260,7 @@ class MmaSyncPtx:
 
 
 @_node
-class RegStore:
+class RegStore(_Stmt):
     frag: str
     dst_buffer: str
     dst_index: list
@@ -485,49 +495,73 @@ def rowwise_kernel(op: str, rows: int, cols: int, eps: float = 1e-5, name: str =
 def gemm_kernel(m: int, n: int, k: int, dtype: str = "f16", epilogue: str | None = None, b_trans: bool = False,
                 name: str = "k_gemm", batch: tuple = (), b_batched: bool = True, bias: bool = False):
     """C = A B on mma.sync cells, as the tracer schedules a 16-bit matmul: accumulator / operand fragments, a K
-    loop of fragment loads and MMAs, a fragment store (optionally with a fused epilogue, which the reference
-    rejects). One warp per 16x8 cell here; the tile sizes of the real schedule do not matter to the matcher."""
+    loop of fragment loads straight from global memory and MMAs, a fragment store (optionally with a fused
+    epilogue, which the reference rejects, emmyptx/mma.py:201-203). One warp per 16x8 cell: the tile's axes are
+    (batch,) row cell, column cell and the 32 lanes of the warp, so that the thread-to-cell map of
+    emmyptx/kernel.py:551-626 hands every warp one cell and `mma.sync` runs warp-wide. Ragged extents carry the
+    guards of emmyptx/mma.py:128-151, 217-242 (clamped rows / columns, zero K tail, predicated stores). The
+    reference's compiler accepts this IR as it stands (without epilogue and bias); the tile sizes of the tracer's
+    real schedule are unknown and do not matter to the matcher."""
     am, an = Axis("m0", Dim(-(-m // 16))), Axis("n0", Dim(-(-n // 8)))
     kk = Axis("k0", Dim(-(-k // 16)))
-    row, col = BinaryExpr("*", Var("m0"), Literal(16, "int")), BinaryExpr("*", Var("n0"), Literal(8, "int"))
-    kof = BinaryExpr("*", Var("k0"), Literal(16, "int"))
-    b_index = [col, kof] if b_trans else [kof, col]
-    body = [RegFragment("_c", "c", DType("f32")), RegFragment("_a", "a", DType(dtype)), RegFragment("_b", "b", DType(dtype)),
-            Loop(kk, [LdmatrixLoad("_a", "a", "A", [row, kof]),
-                      LdmatrixLoad("_b", "b", "B", b_index, b_trans=b_trans),
-                      MmaSyncPtx("_c", "_a", "_b", ab_dtype=dtype)]),
-            RegStore("_c", "C", [row, col], epilogue=epilogue, bias="bias" if bias else None)]
+    lit = lambda v: Literal(int(v), "int")
+    row, col = BinaryExpr("*", Var("m0"), lit(16)), BinaryExpr("*", Var("n0"), lit(8))
+    kof = BinaryExpr("*", Var("k0"), lit(16))
     lead = list(batch)
-    axes = ([Axis("b0", Dim(math.prod(lead)))] if lead else []) + [am, an]
+    bvar = [Var("b0")] if lead else []
+    b_index = (bvar if b_batched else []) + ([col, kof] if b_trans else [kof, col])
+    rag_m, rag_n, rag_k = m % 16 != 0, n % 8 != 0, k % 16 != 0
+    a_load = LdmatrixLoad("_a", "a", "A", bvar + [row, kof], gmem_guard=(row, lit(m)) if rag_m else None,
+                          k_zero=(kof, lit(k)) if rag_k else None)
+    b_load = LdmatrixLoad("_b", "b", "B", b_index, b_trans=b_trans, gmem_guard=(col, lit(n)) if rag_n else None,
+                          k_zero=(kof, lit(k)) if rag_k else None)
+    body = [RegFragment("_c", "c", DType("f32")), RegFragment("_a", "a", DType(dtype)), RegFragment("_b", "b", DType(dtype)),
+            Loop(kk, [a_load, b_load, MmaSyncPtx("_c", "_a", "_b", ab_dtype=dtype)]),
+            RegStore("_c", "C", bvar + [row, col], epilogue=epilogue, bias="bias" if bias else None,
+                     m_guard=(row, lit(m)) if rag_m else None, n_guard=(col, lit(n)) if rag_n else None)]
+    axes = ([Axis("b0", Dim(math.prod(lead)))] if lead else []) + [am, an, Axis("lane0", Dim(32))]
     kern = KernelOp(name, [Tile(axes, body)])
     bshape = [n, k] if b_trans else [k, n]
-    ins = [tensor("A", lead + [m, k], dtype), tensor("B", (lead if b_batched else []) + bshape, dtype)]
+    flat = [math.prod(lead)] if lead else []
+    ins = [tensor("A", flat + [m, k], dtype), tensor("B", (flat if b_batched else []) + bshape, dtype)]
     if bias:
         ins.append(tensor("bias", [n], dtype))
-    g = _graph(kern, ins, [tensor("C", lead + [m, n], dtype)])
+    g = _graph(kern, ins, [tensor("C", flat + [m, n], dtype)])
     cells = math.prod(lead or [1]) * am.extent.value * an.extent.value * 32
     return g, kern, _launch(kern, [t.name for t in ins] + ["C"], cells, block=128)
 
 
 def attention_kernel(units_shape: list[int], seq_q: int, seq_k: int, d: int, dtype: str = "bf16", scale: float | None = None,
-                     name: str = "k_sdpa", causal: bool = False):
-    """softmax(Q K^T * scale) V as fused generic statements: two MMA groups with an exp and a row reduction between
-    them. Only the features the matcher keys on are spelled out. `causal` adds the lower-triangular mask the way the
-    tracer lowers `masked_fill(~tril, -inf)`: a comparison of the key index with the query index feeding a `where`."""
+                     name: str = "k_sdpa", causal: bool = False, mask: str | None = None):
+    """softmax(Q K^T * scale) V as fused statements: two MMA groups with a scaled, optionally masked exponential and
+    two row reductions between them, written per (query, key) pair -- the tile's last axis counts queries, the loop
+    keys. Only what the matcher reads is spelled out, and the softmax works on fragment names directly, which the
+    reference's compiler has no statement for (its tracer stages S through shared memory): this IR is NOT accepted
+    by the reference, unlike every other builder here. `causal` adds the lower-triangular mask the way
+    `masked_fill(~tril, -inf)` lowers: `less_equal(key, query)` feeding a `where`. `mask` selects other masks
+    ("upper", "band", "padding") that the matcher must refuse."""
     scale = d ** -0.5 if scale is None else scale
-    mask = [Assign("keep", Op("le"), [Var("j0"), Var("q0")]),
-            Assign("t0", Op("where"), ["keep", "t0", float("-inf")])] if causal else []
+    kind = mask or ("causal" if causal else None)
+    masks = {
+        None: [],
+        "causal": [Assign("keep", Op("less_equal"), [Var("j0"), Var("q0")])],
+        "upper": [Assign("keep", Op("greater_equal"), [Var("j0"), Var("q0")])],
+        "band": [Assign("lo", Op("subtract"), [Var("q0"), 16]), Assign("k1", Op("less_equal"), [Var("j0"), Var("q0")]),
+                 Assign("k2", Op("greater"), [Var("j0"), "lo"]), Assign("keep", Op("multiply"), ["k1", "k2"])],
+        "padding": [Assign("keep", Op("less"), [Var("j0"), seq_k - 8])],
+    }[kind]
+    fill = [Assign("t0", Op("where"), ["keep", "t0", float("-inf")])] if masks else []
     u = 1
     for s in units_shape:
         u *= s
-    ax = [Axis("u0", Dim(u)), Axis("q0", Dim(-(-seq_q // 16)))]
+    ax = [Axis("u0", Dim(u)), Axis("q0", Dim(seq_q))]
     body = [RegFragment("_s", "c", DType("f32")), RegFragment("_o", "c", DType("f32")),
             RegFragment("_q", "a", DType(dtype)), RegFragment("_k", "b", DType(dtype)), RegFragment("_v", "b", DType(dtype)),
-            Loop(Axis("j0", Dim(-(-seq_k // 8))), [
+            Loop(Axis("j0", Dim(seq_k)), [
                 LdmatrixLoad("_q", "a", "Q", [Var("u0"), Var("q0"), Literal(0, "int")]),
                 LdmatrixLoad("_k", "b", "K", [Var("u0"), Var("j0"), Literal(0, "int")], b_trans=True),
                 MmaSyncPtx("_s", "_q", "_k", ab_dtype=dtype),
-                Assign("t0", Op("multiply"), ["_s", scale]), *mask,
+                Assign("t0", Op("multiply"), ["_s", scale]), *masks, *fill,
                 WarpShuffle(["mx"], ["mx_b"], [Assign("mx", Op("maximum"), ["mx", "mx_b"])], 4),
                 Assign("t1", Op("subtract"), ["t0", "mx"]), Assign("p", Op("exp"), ["t1"]),
                 WarpShuffle(["sm"], ["sm_b"], [Assign("sm", Op("add"), ["sm", "sm_b"])], 4),
@@ -539,5 +573,4 @@ def attention_kernel(units_shape: list[int], seq_q: int, seq_k: int, d: int, dty
     shp = list(units_shape)
     g = _graph(kern, [tensor("Q", shp + [seq_q, d], dtype), tensor("K", shp + [seq_k, d], dtype),
                       tensor("V", shp + [seq_k, d], dtype)], [tensor("O", shp + [seq_q, d], dtype)])
-    return g, kern, _launch(kern, ["Q", "K", "V", "O"], u * ax[1].extent.value * 32, block=128)
-
+    return g, kern, _launch(kern, ["Q", "K", "V", "O"], u * -(-seq_q // 16) * 32, block=128)

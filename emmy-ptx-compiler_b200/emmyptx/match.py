@@ -423,6 +423,78 @@ def _epilogue_name(ep):
     raise Unmatched(f"store epilogue {name!r} has no fused variant (have: gelu_tanh, relu)")
 
 
+def _attention_scale(stmts, mmas, d: int) -> float:
+    """The factor on the scores: the literal of the one `multiply` whose other operand is the accumulator fragment of
+    the first MMA group (S = Q K^T); 1 when nothing scales the scores. Two candidates (a separately folded log2(e),
+    say) are ambiguous, and a scale that is not a literal cannot be passed to the kernel: both match nothing."""
+    s_frag = mmas[0].c_frag
+    cands = []
+    for st in stmts:
+        if _kind(st) == "Assign" and st.op.name == "multiply" and s_frag in [a for a in st.args if isinstance(a, str)]:
+            lits = [float(a) for a in st.args if isinstance(a, (int, float)) and not isinstance(a, bool)]
+            cands += lits
+    if len(cands) > 1:
+        raise Unmatched(f"more than one constant multiplies the scores ({cands}): which is the softmax scale is ambiguous")
+    if cands:
+        return cands[0]
+    if any(_kind(st) == "Assign" and st.op.name in ("multiply", "divide") and s_frag in [a for a in st.args if isinstance(a, str)]
+           for st in stmts):
+        raise Unmatched("the scores are scaled by something other than a literal")
+    return 1.0
+
+
+def _attention_mask(kernel, stmts, seq_q: int, seq_k: int) -> bool:
+    """False for an unmasked softmax, True for the lower-triangular (causal) mask, `Unmatched` for any other mask.
+    A mask is a `where` that fills -inf (tools/torch_cases/fused.py:31-36; models.py:17-19). Its condition is run on
+    probe (query, key) index pairs -- the tile's last axis must count queries and the loop's axis keys, one each --
+    and only `key <= query` kept / `key > query` filled is the causal variant; a padding, banded or upper-triangular
+    mask is some other function of the pair and is refused."""
+    neg_inf = lambda a: isinstance(a, float) and a == float("-inf")
+    fills = [st for st in stmts if _kind(st) == "Assign" and st.op.name == "where" and any(neg_inf(a) for a in st.args)]
+    if not fills:
+        return False
+    if len(fills) > 1:
+        raise Unmatched("more than one masking `where`")
+    tiles = [st for st in kernel.body if _kind(st) == "Tile"]
+    loops = [st for st in stmts if _kind(st) in ("Loop", "StridedLoop") and fills[0] in list(walk(st.body))]
+    if len(tiles) != 1 or not loops:
+        raise Unmatched("a masked softmax is one Tile with the mask inside the key loop")
+    q_axis, k_axis = tiles[0].axes[-1], loops[-1].axis
+    if int(q_axis.extent.as_static()) != seq_q or int(k_axis.extent.as_static()) != seq_k:
+        raise Unmatched("the mask's indices do not count single queries and keys: it cannot be checked")
+    qs = np.unique(np.clip([0, 1, 2, 7, 8, 15, 16, 17, seq_q // 2, seq_q - 2, seq_q - 1], 0, seq_q - 1))
+    ks = np.unique(np.clip([0, 1, 2, 7, 8, 15, 16, 17, seq_k // 2, seq_k - 2, seq_k - 1], 0, seq_k - 1))
+    qq, kk = (g.reshape(-1).astype(np.int64) for g in np.meshgrid(qs, ks, indexing="ij"))
+    it = CellInterpreter({}, qq, INT_OPS)
+    it.env[q_axis.name], it.env[k_axis.name] = qq, kk
+
+    def value(a):
+        return it.expr(a) if hasattr(a, "free_vars") or _kind(a) in ("Var", "Literal", "BinaryExpr") else it.lookup(a)
+
+    for st in walk(loops[-1].body):
+        if st is fills[0]:
+            break
+        if _kind(st) == "Let":
+            try:
+                it.env[st.name] = it.expr(st.value)
+            except Unmatched:
+                pass
+        elif _kind(st) == "Assign" and st.op.name in FLOAT_OPS:
+            try:
+                it.env[st.name] = FLOAT_OPS[st.op.name][1](*[np.asarray(value(a), np.float64) for a in st.args])
+            except Unmatched:                      # depends on data, not on the indices alone
+                pass
+    cond, if_true, if_false = fills[0].args
+    try:
+        c = np.asarray(value(cond), np.float64) != 0
+    except Unmatched:
+        raise Unmatched("the mask's condition is not a function of the query and key indices alone") from None
+    keep = c if neg_inf(if_false) else ~c
+    if np.array_equal(keep, kk <= qq):
+        return True
+    raise Unmatched("a masked softmax other than the lower-triangular one (key <= query) has no variant")
+
+
 def match_contraction(graph, kernel, launch: dict) -> dict:
     tensors = tensor_table(graph)
     stmts = list(walk(kernel.body))
@@ -453,17 +525,7 @@ def match_contraction(graph, kernel, launch: dict) -> dict:
         d = q[-1]
         if d not in (64, 128):
             raise Unmatched(f"attention head dim {d} has no variant (64, 128)")
-        scale = d ** -0.5
-        floats = [a for s in stmts if _kind(s) == "Assign" and s.op.name == "multiply" for a in s.args
-                  if isinstance(a, float)]
-        if floats:
-            scale = floats[0]
-        # a `where` that fills -inf under an index comparison is the lower-triangular mask (tools/torch_cases/fused.py:31-36)
-        assigns = [s for s in stmts if _kind(s) == "Assign"]
-        fills = [s for s in assigns if s.op.name == "where" and any(isinstance(a, float) and a == float("-inf") for a in s.args)]
-        causal = bool(fills) and any(s.op.name in ("le", "ge", "lt", "gt") for s in assigns)
-        if fills and not causal:
-            raise Unmatched("a masked softmax other than the lower-triangular one has no variant")
+        scale, causal = _attention_scale(stmts, mmas, d), _attention_mask(kernel, stmts, q[-2], k[-2])
         return {"variant": "attention_fwd", "inputs": srcs, "outputs": [out],
                 "params": {"dtype": dtype, "units": math.prod(q[:-2]), "seq_q": q[-2], "seq_k": k[-2], "d": d, "scale": scale,
                            "causal": causal}}
@@ -653,7 +715,10 @@ def match_dot(graph, kernel, launch: dict) -> dict:
         raise Unmatched("a product kernel has one loop over K")
     k = int(loops[0].axis.extent.as_static())
     cells = math.prod(int(a.extent.as_static()) for a in tile.axes)
-    probe = np.unique(np.concatenate([[0, cells - 1], np.random.default_rng(0).integers(0, cells, 6)])).astype(np.int64)
+    # every cell of a small output, else the corners and 62 random cells: enough of them that some pre-activation is
+    # negative, which is what tells a ReLU store from a plain one by value
+    probe = (np.arange(cells) if cells <= 64 else
+             np.unique(np.concatenate([[0, cells - 1], np.random.default_rng(0).integers(0, cells, 62)]))).astype(np.int64)
     it = RowInterpreter(tensors, probe, k)
     rem = np.broadcast_to(probe[:, None], it.cells.shape).copy()
     for a in reversed(tile.axes):
@@ -698,11 +763,27 @@ def match_dot(graph, kernel, launch: dict) -> dict:
     if bias:
         ref = ref + probe_values(bias[0], "f32", ni)
     got = np.asarray(value, np.float64)[:, 0]
-    for epilogue, f in ((None, lambda r: r), ("relu", lambda r: np.maximum(r, 0.0))):
-        if np.allclose(got, f(ref), rtol=1e-9, atol=1e-12):
-            return {"variant": "gemm_f32", "inputs": [a_name, b_name, *bias], "outputs": [out_name],
-                    "params": {"batch": batch, "m": m, "n": n, "k": k, "b_trans": layout == "nk", "b_shared": bool(shared),
-                               "bias": bool(bias), "epilogue": epilogue}}
+    # The epilogue is read off the IR -- a `relu`, or a `maximum` against a literal 0, between the fold and the store --
+    # and the values confirm it. Values alone cannot decide when no probed pre-activation is negative (tiny outputs):
+    # then the statement list must be one of the forms known here, or nothing matches.
+    after = [s for s in tile.body if _kind(s) == "Assign"]
+    is_zero = lambda a: isinstance(a, (int, float)) and not isinstance(a, bool) and float(a) == 0.0
+    relu_stmts = [s for s in after if s.op.name == "relu" or (s.op.name == "maximum" and any(is_zero(a) for a in s.args))]
+    known_forms = all(s in relu_stmts or s.op.name in ("add", "multiply", "copy") for s in after)
+    decisive = bool((ref < 0).any())
+    if not decisive and not known_forms:
+        raise Unmatched("no probed pre-activation is negative and the statements after the fold are not a known epilogue")
+    epilogue = "relu" if relu_stmts else None
+    want = np.maximum(ref, 0.0) if epilogue == "relu" else ref
+    if np.allclose(got, want, rtol=1e-9, atol=1e-12):
+        return {"variant": "gemm_f32", "inputs": [a_name, b_name, *bias], "outputs": [out_name],
+                "params": {"batch": batch, "m": m, "n": n, "k": k, "b_trans": layout == "nk", "b_shared": bool(shared),
+                           "bias": bool(bias), "epilogue": epilogue}}
+    if decisive and not relu_stmts and np.allclose(got, np.maximum(ref, 0.0), rtol=1e-9, atol=1e-12):
+        # a ReLU spelled some other way (a `where` on the sign, say): the values are unambiguous
+        return {"variant": "gemm_f32", "inputs": [a_name, b_name, *bias], "outputs": [out_name],
+                "params": {"batch": batch, "m": m, "n": n, "k": k, "b_trans": layout == "nk", "b_shared": bool(shared),
+                           "bias": bool(bias), "epilogue": "relu"}}
     raise Unmatched("the loop is not a plain product (optionally plus a bias vector, optionally through ReLU)")
 
 

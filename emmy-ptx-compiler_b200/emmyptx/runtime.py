@@ -308,6 +308,10 @@ def gemm_f32(a, b, bias=None, epilogue: str | None = None, b_is_nk: bool = False
     need = lib.emmyb200_gemm_f32_workspace_bytes(flags, batch, m, n, k, 1 if stride_b == 0 else 0)
     if need > 0 and (workspace is None or workspace.numel() < need):
         workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+        if stream is not None:
+            # a workspace made here is dropped on return while the kernels on `stream` still read it: tell the caching
+            # allocator, so that the block is not handed to other work before that stream has passed this point
+            workspace.record_stream(stream)
     if bias is not None:
         _need_cuda(bias)
         if bias.dtype != torch.float32 or bias.numel() != n or not bias.is_contiguous():

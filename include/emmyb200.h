@@ -147,7 +147,10 @@ int emmyb200_gemm_batched(int dtype, int epilogue, int flags, const void* A, con
  * about 2^-23 (8 + K / 16) sum_k |a_k b_k| (measured: 1e-7 .. 8e-7 of that sum for operands of random sign). Arguments as emmyb200_gemm_batched with float buffers (`bias`: N floats or NULL);
  * lda / ldb / strides of A and B are unrestricted, C must be 16-byte aligned with ldc (and stride_c) a multiple
  * of 4. `workspace`: emmyb200_gemm_f32_workspace_bytes(flags, batch, M, N, K, b_shared) bytes, 256-byte aligned
- * (b_shared = 1 when stride_b is 0 or batch is 1). No counterpart for the split itself in the reference. */
+ * (b_shared = 1 when stride_b is 0 or batch is 1). Non-finite operands: an infinite element of A or B makes every
+ * output element it contributes to NaN (the split meets inf * 0), where the reference's scalar fp32 loop gives +-inf;
+ * NaN operands give NaN as there. Finite operands of any magnitude are handled (values beyond the bf16 range are
+ * carried by the lower planes). No counterpart for the split itself in the reference. */
 int64_t emmyb200_gemm_f32_workspace_bytes(int flags, int64_t batch, int64_t M, int64_t N, int64_t K, int b_shared);
 int emmyb200_gemm_f32(int epilogue, int flags, const float* A, const float* B, const float* bias, float* C,
                       int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,

@@ -11,9 +11,12 @@ case's torch expression evaluated on CPU in float64 on the same seeded inputs, c
 fp32 bits (`tools/run_local.py:31-37`).
 
 Pinning: the reference ships no golden vectors (its `expected.npz` files are generated on the fly
-or come from a problem set that is not in its tree). The pins are (a) `tests/golden/`: outputs of
-the reference's own compiler -- its PTX for the two streaming configurations, executed by
-`oracle/ptx_interp.py` -- and (b) `oracle/emmy_lowering.py`, a numpy restatement of the reference's
-instruction sequences for exp / tanh / sin, both checked against this oracle within the
-reference's own tolerance classes.
+or come from a problem set that is not in its tree). The pins are the outputs of the reference's own
+compiler under `tests/golden/`: its PTX for the two streaming configurations, for the single
+transcendental ops and for its tensor-core matmul cases (`mma.sync` kernels), executed on the CPU by
+`oracle/ptx_interp.py` into `golden.npz` and JIT-loaded next to the sm_100a kernels in the GPU tests.
+This oracle is checked against those vectors within the reference's own tolerance classes
+(`tests/test_oracle_golden.py`). Attention has no reference-emitted kernel (the reference has no
+statement that carries scores from one MMA group into the next): that path is checked against this
+oracle only.
 """

@@ -29,13 +29,15 @@ def c2_input(n: int = 2**26, seed: int = 0) -> np.ndarray:
     return np.random.default_rng(seed).integers(-2**30, 2**30, n, dtype=np.int32, endpoint=True)
 
 
-def gemm_inputs(m: int, n: int, k: int, dtype: str, b_is_nk: bool = False):
-    """A[m,k], B[k,n] (or [n,k]) ~ N(0,1)/sqrt(k), rounded to `dtype` ('f16' or 'bf16').
-    Returns torch CPU tensors of that dtype."""
+def gemm_inputs(m: int, n: int, k: int, dtype: str, b_is_nk: bool = False, scaled: bool = True, batch: tuple = ()):
+    """A[m,k], B[k,n] (or [n,k]) ~ N(0,1)/sqrt(k), rounded to `dtype` ('f16' or 'bf16'); `scaled=False` gives
+    the plain N(0,1) operands of the reference's own matmul cases (tools/torch_cases/matmul.py:27-32), `batch`
+    leading axes on both. Returns torch CPU tensors of that dtype."""
     import torch
-    scale = np.float32(1.0 / np.sqrt(k))
-    a = np.random.default_rng(0).standard_normal((m, k), dtype=np.float32) * scale
-    b = np.random.default_rng(1).standard_normal((n, k) if b_is_nk else (k, n), dtype=np.float32) * scale
+    scale = np.float32(1.0 / np.sqrt(k)) if scaled else np.float32(1.0)
+    lead = tuple(batch)
+    a = np.random.default_rng(0).standard_normal(lead + (m, k), dtype=np.float32) * scale
+    b = np.random.default_rng(1).standard_normal(lead + ((n, k) if b_is_nk else (k, n)), dtype=np.float32) * scale
     td = torch.float16 if dtype == "f16" else torch.bfloat16
     return torch.from_numpy(a).to(td), torch.from_numpy(b).to(td)
 

@@ -10,7 +10,12 @@ evaluated correctly rounded, and `fma.rn.f32` goes through float64 (exact produc
 the sum in rare ties), so float outputs carry the reference's algorithm, not a particular GPU's bits.
 
 Supported: the instructions of `emmyptx/ops.py` and `emmyptx/kernel.py` for one-axis tiles with scalar
-global loads and stores, predication, and the early-exit branch to `$L_exit`. Anything else raises.
+global loads and stores, predication, and the early-exit branch to `$L_exit`; and the fully unrolled tensor-core
+kernels of `emmyptx/mma.py` (fragments read from global memory as packed 16-bit pairs, `mma.sync.m16n8k16` on
+f16 / bf16 with f32 accumulators, converted `.v2.b16` stores). `mma.sync` is evaluated per warp from the PTX
+ISA's fragment lane map (restated in emmyptx/mma.py:6-10) with exact products summed in float64 and rounded to
+f32 once per instruction: the hardware's summation order inside one instruction is unspecified, so outputs carry
+the reference's algorithm, not one GPU's low bits. Anything else (run-time loops included) raises.
 """
 from __future__ import annotations
 
@@ -27,6 +32,21 @@ class PtxError(NotImplementedError):
 
 def _f32_literal(tok: str) -> np.float32:
     return np.array([int(tok[2:], 16)], dtype=np.uint32).view(np.float32)[0]
+
+
+def _bf16_to_f32(h: np.ndarray) -> np.ndarray:
+    return (h.astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+def _f32_to_bf16(f: np.ndarray) -> np.ndarray:
+    """Round to nearest even on the upper 16 bits (tools/run_local.py:31-37 spells the same formula); NaN stays NaN."""
+    u = np.ascontiguousarray(f, dtype=np.float32).view(np.uint32)
+    r = ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+    return np.where(np.isnan(f), np.uint16(0x7FC0), r)
+
+
+def _halves_to_f32(h: np.ndarray, kind: str) -> np.ndarray:
+    return _bf16_to_f32(h) if kind == "bf16" else h.view(np.float16).astype(np.float32)
 
 
 class Interpreter:
@@ -71,7 +91,8 @@ class Interpreter:
         val = int(tok, 0)
         if ty == "f32":
             raise PtxError(f"integer immediate {tok} in a float slot")
-        dt = {"s32": np.int32, "u32": np.uint32, "b32": np.int32, "s64": np.int64, "u64": np.int64, "b64": np.int64}[ty]
+        dt = {"s32": np.int32, "u32": np.uint32, "b32": np.int32, "s64": np.int64, "u64": np.int64, "b64": np.int64,
+              "b16": np.uint16}[ty]
         return np.full(self.n, np.array(val).astype(np.int64).astype(dt), dt)
 
     @staticmethod
@@ -135,6 +156,9 @@ class Interpreter:
             self._set(ops[0], self.param_addr[ops[1].strip("[]")])
         elif name == "cvta":
             self._set(ops[0], self.reg[ops[1]])
+        elif name == "mov" and ops[1].startswith("{"):            # mov.b32 %b, {%h_lo, %h_hi}
+            lo, hi = (self.reg[t.strip()].astype(np.uint32) for t in ops[1].strip("{}").split(","))
+            self._set(ops[0], (lo | (hi << np.uint32(16))).astype(np.uint32), mask)
         elif name == "mov":
             src = ops[1]
             if src in self.special:
@@ -145,6 +169,8 @@ class Interpreter:
                 self._set(ops[0], V(src, "f32"), mask)
             else:
                 self._set(ops[0], V(src, "s32" if ty in ("b32", "u32", "s32") else ty), mask)
+        elif name == "mma":
+            self._mma(parts, ops, mask)
         elif name in ("and", "or", "xor"):
             a, b = V(ops[1], "s32"), V(ops[2], "s32")
             self._set(ops[0], {"and": np.bitwise_and, "or": np.bitwise_or, "xor": np.bitwise_xor}[name](a, b), mask)
@@ -196,23 +222,60 @@ class Interpreter:
             self._set(ops[0], np.where(self.reg[ops[3]], a, b), mask)
         elif name == "ld" and parts[1] == "global":
             buf, off = self._mem(ops[1])
-            out = np.zeros(self.n, np.float32 if ty == "f32" else np.int32)
+            dt = np.float32 if ty == "f32" else (np.uint16 if ty == "b16" else np.int32)
+            out = np.zeros(self.n, dt)
             m = self.active if mask is None else self.active & mask
             for b in np.unique(buf[m]):
                 sel = m & (buf == b)
                 arr = self.bufs[int(b)].reshape(-1)
-                out[sel] = arr.view(out.dtype)[off[sel] // 4]
+                out[sel] = arr.view(dt)[off[sel] // out.itemsize]
             self._set(ops[0], out, mask)
         elif name == "st" and parts[1] == "global":
             buf, off = self._mem(ops[0])
-            val = V(ops[1], ty)
+            width = 2 if ty == "b16" else 4
+            srcs = [t.strip() for t in ops[1].strip("{}").split(",")]        # one value, or the members of a .v2
             m = self.active if mask is None else self.active & mask
-            for b in np.unique(buf[m]):
-                sel = m & (buf == b)
-                arr = self.bufs[int(b)].reshape(-1)
-                arr.view(val.dtype)[off[sel] // 4] = val[sel]
+            for j, tok in enumerate(srcs):
+                val = self.reg[tok] if ty == "b16" else V(tok, ty)
+                for b in np.unique(buf[m]):
+                    sel = m & (buf == b)
+                    arr = self.bufs[int(b)].reshape(-1)
+                    arr.view(val.dtype)[(off[sel] + j * width) // width] = val[sel]
         else:
             raise PtxError(f"unsupported instruction {'.'.join(parts)}")
+
+    def _mma(self, parts, ops, mask) -> None:
+        """mma.sync.aligned.m16n8k16.row.col.f32.<ab>.<ab>.f32 {d}, {a}, {b}, {c}: every warp multiplies its 16x16 A by
+        its 16x8 B. Lane (g, t) = (lane / 4, lane % 4) holds a[i] = A[g + 8 (i & 1)][2t + 8 (i >> 1) + {0, 1}],
+        b[i] = B[2t + 8 i + {0, 1}][g], c[i] = C[g + 8 (i >> 1)][2t + (i & 1)], low half of a pair first."""
+        if mask is not None or not self.active.reshape(-1, 32).all(axis=1).any() or self.n % 32:
+            raise PtxError("mma.sync needs whole warps")
+        if tuple(parts[1:6]) != ("sync", "aligned", "m16n8k16", "row", "col") or parts[6] != "f32" or parts[9] != "f32":
+            raise PtxError(f"unsupported {'.'.join(parts)}")
+        kind = parts[7]
+        groups = [[t.strip() for t in o.strip("{}").split(",")] for o in ops]
+        d_regs, a_regs, b_regs, c_regs = groups
+        w = self.n // 32
+        lanes = np.arange(32)
+        g, t = lanes // 4, lanes % 4
+        A = np.zeros((w, 16, 16), np.float64)
+        B = np.zeros((w, 16, 8), np.float64)
+        C = np.zeros((w, 16, 8), np.float64)
+        for i, r in enumerate(a_regs):
+            u = self.reg[r].view(np.uint32).reshape(w, 32)
+            for j in (0, 1):
+                h = ((u >> np.uint32(16 * j)) & np.uint32(0xFFFF)).astype(np.uint16)
+                A[:, g + 8 * (i & 1), 2 * t + 8 * (i >> 1) + j] = _halves_to_f32(h, kind)
+        for i, r in enumerate(b_regs):
+            u = self.reg[r].view(np.uint32).reshape(w, 32)
+            for j in (0, 1):
+                h = ((u >> np.uint32(16 * j)) & np.uint32(0xFFFF)).astype(np.uint16)
+                B[:, 2 * t + 8 * i + j, g] = _halves_to_f32(h, kind)
+        for i, r in enumerate(c_regs):
+            C[:, g + 8 * (i >> 1), 2 * t + (i & 1)] = self._as(self.reg[r], "f32").reshape(w, 32)
+        D = (A @ B + C).astype(np.float32)
+        for i, r in enumerate(d_regs):
+            self._set(r, np.ascontiguousarray(D[:, g + 8 * (i >> 1), 2 * t + (i & 1)]).reshape(-1))
 
     def _int_arith(self, name, parts, ops, mask) -> None:
         V = self._val
@@ -260,6 +323,9 @@ class Interpreter:
             self._set(ops[0], np.clip(v, -2**31, 2**31 - 1).astype(np.int32), mask)
         elif dst_ty == "f32" and src_ty in ("s32", "u32"):
             self._set(ops[0], a.astype(np.float32), mask)
+        elif dst_ty in ("f16", "bf16") and src_ty == "f32" and rnd == "rn":
+            h = _f32_to_bf16(a) if dst_ty == "bf16" else a.astype(np.float16).view(np.uint16)
+            self._set(ops[0], h, mask)
         else:
             raise PtxError(f"unsupported conversion {'.'.join(parts)}")
 

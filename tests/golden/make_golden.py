@@ -3,8 +3,9 @@ oracle/ptx_interp.py on the seeded inputs of oracle/inputs.py.
 
     python tests/golden/make_golden.py
 
-Writes tests/golden/golden.npz: for each case the input seed/size and the output the reference's kernel
-produces. Integer outputs are exact; float outputs are the reference's algorithm with its three hardware
+Writes tests/golden/golden.npz: for each case the output the reference's kernel produces (`<case>.y`; for the
+tensor-core GEMM cases `<case>.c`, the 16-bit output as raw bit patterns, on N(0,1) operands seeded per argument
+as oracle/inputs.gemm_inputs(scaled=False) draws them). Integer outputs are exact; float outputs are the reference's algorithm with its three hardware
 approximations evaluated correctly rounded (see ptx_interp.py). Regenerate only together with the .ref.ptx
 files (make_reference_ptx.py, which needs the reference checkout).
 """
@@ -21,6 +22,22 @@ from oracle import inputs, ptx_interp  # noqa: E402
 manifest = json.loads((HERE / "reference_ptx_manifest.json").read_text())
 out = {}
 for name, info in manifest.items():
+    if "gemm" in info:
+        g = info["gemm"]
+        if g["m"] > 512:
+            continue                      # device-only timing case
+        a, b = inputs.gemm_inputs(g["m"], g["n"], g["k"], g["dtype"], g["b_trans"], scaled=False, batch=tuple(g["batch"]))
+        bufs = {"A": a.view(__import__("torch").int16).numpy().copy(), "B": b.view(__import__("torch").int16).numpy().copy(),
+                "C": np.zeros(tuple(g["batch"]) + (g["m"], g["n"]), np.int16)}
+        ptx_interp.run_entry((HERE / f"{name}.ref.ptx").read_text(), bufs, info["launch"]["grid"][0], info["launch"]["block"][0])
+        c = bufs["C"].view(np.uint16).reshape(-1, g["n"])
+        if c.shape[0] > 128:              # keep the fixture small: every fourth row of the larger cases
+            keep = np.arange(0, c.shape[0], 4)
+            out[f"{name}.rows"] = keep.astype(np.int64)
+            c = c[keep]
+        out[f"{name}.c"] = c
+        print(name, c[0, :4])
+        continue
     n = info["tensors"]["x"]["shape"][0]
     if n > 2**20 or (name.startswith("c1") and n > 4096 and False):
         continue

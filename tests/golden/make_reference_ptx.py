@@ -1,4 +1,4 @@
-"""Generate the reference's own PTX for the two streaming configurations (and a small GEMM), as fixtures.
+"""Generate the reference's own PTX for the two streaming configurations and for tensor-core GEMMs, as fixtures.
 
     python tests/golden/make_reference_ptx.py <path to a checkout of the reference>
 
@@ -7,6 +7,14 @@ the stand-in IR classes of `emmy-ptx-compiler_b200/emmyptx/ir.py` drive it. The 
 reference's output for these kernels; `oracle/ptx_interp.py` executes it on the CPU to produce the golden
 vectors (`make_golden.py`), and the GPU tests JIT the same text on the device to compare kernel against kernel.
 Targets are sm_89 (the reference's default); sm_100 devices JIT it forward.
+
+The GEMM cases are the reference's own 16-bit matmul shapes (tools/torch_cases/matmul.py:27-32) compiled from the
+stand-in contraction IR (`ir.gemm_kernel`: one warp per m16n8k16 output cell, fragments read straight from global
+memory, emmyptx/mma.py:128-180). Cases marked `device` run on a GPU; they are restricted to extents with
+M % 16 == N % 8 == K % 16 == 0, for which the IR carries no guards and every address the kernel forms is inside its
+buffer by construction -- the script works the largest element index of every fragment load and store out of the
+IR's own index expressions and stops if one is out of range. Ragged cases (clamped rows, zero-filled K tail,
+predicated stores) are only ever executed by the CPU interpreter.
 """
 import importlib.util
 import json
@@ -39,11 +47,78 @@ CASES = {
     "c1_exp_sin_tanh_n268435456": ir.pointwise_kernel(2**28, "exp_sin_tanh", name="c1_exp_sin_tanh_n268435456"),
 }
 
+GEMMS = {       # name: (m, n, k, dtype, b_trans, batch, device)
+    "m_f16_mm_32x16x32": (32, 16, 32, "f16", False, (), False),              # small: CPU golden vector
+    "m_f16_mm_odd": (100, 72, 200, "f16", False, (), False),                 # matmul.py:28, ragged: CPU only
+    "m_f16_mm": (256, 256, 256, "f16", False, (), True),                     # matmul.py:27
+    "m_bf16_mm": (512, 512, 512, "bf16", False, (), True),                   # matmul.py:30
+    "m_f16_linear": (64, 512, 256, "f16", True, (), True),                   # matmul.py:32, B stored N x K
+    "m_f16_bmm": (128, 96, 64, "f16", False, (4,), True),                    # matmul.py:31
+    "c3_f16_mm_4096": (4096, 4096, 4096, "f16", False, (), True),            # configuration 3: timed on the device only
+}
+
+
+def _max_index(e, hi: dict) -> int:
+    """Largest value of an index expression over the axis ranges `hi` (name -> largest value); the expressions the
+    builder writes are sums and products of non-negative terms, so the maximum is reached at the axes' maxima."""
+    kind = type(e).__name__
+    if kind == "Literal":
+        return int(e.value)
+    if kind == "Var":
+        return hi[e.name]
+    if kind == "BinaryExpr" and e.op in ("+", "*"):
+        a, b = _max_index(e.left, hi), _max_index(e.right, hi)
+        return a + b if e.op == "+" else a * b
+    raise SystemExit(f"unexpected index expression {e!r}")
+
+
+def assert_in_range(graph, kernel, m, n, k) -> None:
+    """Every fragment access of a guard-free GEMM stays inside its buffer: the cell's base index plus the fragment's
+    own extent (16 x 16 for A, 16 x 8 for B in either storage order, 16 x 8 for C; emmyptx/mma.py:6-10)."""
+    assert m % 16 == 0 and n % 8 == 0 and k % 16 == 0, "device cases carry no guards"
+    shapes = {t.name: [d.as_static() for d in t.shape] for nd in graph.nodes.values() for t in nd.outputs}
+    tile = kernel.body[0]
+    hi = {a.name: a.extent.as_static() - 1 for a in tile.axes}
+    for s in ir_walk(tile.body):
+        kind = type(s).__name__
+        if kind in ("Loop",):
+            hi[s.axis.name] = s.axis.extent.as_static() - 1
+    for s in ir_walk(tile.body):
+        kind = type(s).__name__
+        if kind == "LdmatrixLoad":
+            assert s.gmem_guard is None and s.k_zero is None
+            shape, idx = shapes[s.src_buffer], s.src_index
+            span = (15, 15) if s.role == "a" else ((7, 15) if s.b_trans else (15, 7))
+        elif kind == "RegStore":
+            assert s.m_guard is None and s.n_guard is None and not s.atomic
+            shape, idx, span = shapes[s.dst_buffer], s.dst_index, (15, 7)
+        else:
+            continue
+        top = [_max_index(e, hi) for e in idx]
+        top[-2] += span[0]
+        top[-1] += span[1]
+        assert len(top) == len(shape) and all(0 <= t < d for t, d in zip(top, shape)), (kind, top, shape)
+
+
+def ir_walk(body):
+    for s in body:
+        yield s
+        sub = getattr(s, "body", None)
+        if isinstance(sub, list):
+            yield from ir_walk(sub)
+
+
 manifest = {}
+for name, (m, n, k, dtype, b_trans, batch, device) in GEMMS.items():
+    graph, kernel, launch = ir.gemm_kernel(m, n, k, dtype, None, b_trans, name=name, batch=batch)
+    if device:
+        assert_in_range(graph, kernel, m, n, k)
+    CASES[name] = (graph, kernel, launch)
+
 for name, (graph, kernel, launch) in CASES.items():
     ptx = compile_kernel(graph, kernel, launch, target="sm_89")
     (HERE / f"{name}.ref.ptx").write_text(ptx)
-    manifest[name] = {"entry": kernel.name, "launch": launch,
+    manifest[name] = {"entry": kernel.name, "launch": launch, **({"gemm": dict(zip(("m", "n", "k", "dtype", "b_trans", "batch", "device"), GEMMS[name]))} if name in GEMMS else {}),
                       "tensors": {t.name: {"shape": [d.as_static() for d in t.shape], "dtype": t.dtype.name}
                                   for n in graph.nodes.values() for t in n.outputs}}
     print(f"{name}: {len(ptx.splitlines())} lines of PTX")

@@ -229,3 +229,40 @@ def test_broadcast_reads_become_program_inputs_with_an_index_map():
     assert algorithmic_work(handle(build([Var("r0")], [64]))) == (4.0 * (64 + 96 + 64 * 96), "B")
     with pytest.raises(CompileError):                                        # a reversed read is not a broadcast
         handle(build([BinaryExpr("-", Literal(63, "int"), Var("r0"))], [64]))
+
+
+def test_relu_epilogue_is_read_from_the_ir_when_no_probed_value_is_negative():
+    """Outputs so small that every probed pre-activation may be positive: the ReLU must not be dropped."""
+    for m, n, k in [(1, 2, 16), (2, 2, 8), (64, 48, 32)]:
+        assert handle(ir.matmul_f32_kernel(m, n, k, relu=True))["params"]["epilogue"] == "relu", (m, n, k)
+        assert handle(ir.matmul_f32_kernel(m, n, k, relu=False))["params"]["epilogue"] is None, (m, n, k)
+    # a ReLU spelled as maximum(x, 0) is the same epilogue
+    g, k_, launch = ir.matmul_f32_kernel(1, 2, 16, relu=True)
+    relu = next(s for s in k_.body[0].body if type(s).__name__ == "Assign" and s.op.name == "relu")
+    relu.op, relu.args = ir.Op("maximum"), [relu.args[0], 0.0]
+    assert handle((g, k_, launch))["params"]["epilogue"] == "relu"
+
+
+def test_attention_mask_and_scale_are_checked_not_guessed():
+    """Only key <= query is the causal variant; other masks, and an ambiguous scale, match nothing."""
+    for mask in ("upper", "band", "padding"):
+        with pytest.raises(CompileError, match="lower-triangular"):
+            handle(ir.attention_kernel([2], 256, 256, 64, "f16", mask=mask))
+    g, k, launch = ir.attention_kernel([2], 256, 256, 64, "f16")
+    loop = next(s for s in k.body[0].body if type(s).__name__ == "Loop")
+    at = next(i for i, s in enumerate(loop.body) if type(s).__name__ == "Assign" and s.op.name == "multiply")
+    loop.body.insert(at + 1, ir.Assign("t0", ir.Op("multiply"), ["_s", 1.4426950408889634]))
+    with pytest.raises(CompileError, match="ambiguous"):
+        handle((g, k, launch))
+    # a constant that multiplies something other than the scores is not the scale
+    g, k, launch = ir.attention_kernel([2], 256, 256, 64, "f16", scale=0.2)
+    loop = next(s for s in k.body[0].body if type(s).__name__ == "Loop")
+    loop.body.append(ir.Assign("unused", ir.Op("multiply"), ["sm", 3.0]))
+    assert handle((g, k, launch))["params"]["scale"] == 0.2
+    # masked_fill form: where(mask, -inf, s) with mask = key > query
+    g, k, launch = ir.attention_kernel([2], 256, 256, 64, "f16", causal=True)
+    loop = next(s for s in k.body[0].body if type(s).__name__ == "Loop")
+    cmp = next(s for s in loop.body if type(s).__name__ == "Assign" and s.name == "keep")
+    fill = next(s for s in loop.body if type(s).__name__ == "Assign" and s.op.name == "where")
+    cmp.op, fill.args = ir.Op("greater"), ["keep", float("-inf"), "t0"]
+    assert handle((g, k, launch))["params"]["causal"] is True

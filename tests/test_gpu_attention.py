@@ -59,6 +59,27 @@ def test_c5_sampled_units(cuda):
     assert ok, f"worst error {ratio:.2f}x the bound"
 
 
+def test_c5_full_size_sampled_rows(cuda):
+    """Configuration 5 at its own size: 256 (batch, head) units of 4096 x 128, bf16. The GPU computes all of O; the
+    oracle checks seeded query rows (tile edges included) of a seeded sample of units spread over the whole grid,
+    fp32 softmax(q k^T / sqrt(d)) v of the same rounded operands."""
+    import torch
+    from emmyptx import runtime
+    units, s, d = 256, 4096, 128
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(units, s, d, generator=g).to(torch.bfloat16) for _ in range(3))
+    o = runtime.attention(q.to(cuda), k.to(cuda), v.to(cuda))
+    torch.cuda.synchronize()
+    assert runtime.device_status() == 0
+    worst = 0.0
+    for u in sorted({0, 1, 147, 148, 255} | set(np.random.default_rng(12).integers(0, units, 7).tolist())):
+        rows = sorted({0, 127, 128, 255, 256, s - 129, s - 128, s - 1} | set(np.random.default_rng(u).integers(0, s, 56).tolist()))
+        ref = reference.attention_reference(q[u][rows], k[u], v[u])
+        ok, ratio = reference.gemm_tolerance_ok(o[u][rows].cpu(), ref)
+        worst = max(worst, ratio)
+    assert worst <= 1.0, f"worst error {worst:.2f}x the bound"
+
+
 def test_rows_sum_property(cuda):
     """Size-independent property: with V = all ones every output element is exactly 1 up to rounding
     (softmax rows sum to 1), and permuting the keys together with the values leaves O unchanged up to

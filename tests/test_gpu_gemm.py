@@ -79,6 +79,36 @@ def test_c3_full_size(cuda):
     assert ok, f"worst error {ratio:.2f}x the bound"
 
 
+def test_c4_full_size_sampled_rows(cuda):
+    """Configuration 4 at its own size: M = N = K = 16384, bf16, tanh-GELU fused into the store. The GPU computes the
+    whole product; the oracle checks a seeded sample of 256 whole rows plus the rows at the edges of 128-row output
+    tiles, of the 16-row-block bands the tile order walks, and of the matrix (fp32 product of the same rounded
+    operands, GELU on the fp32 value, one rounding to bf16 by the kernel only; comparison and vacuity check as
+    tools/check_torch.py:260-278 with the task's rule |c - ref| <= 1e-2 |ref| + 1e-2 std(ref))."""
+    import torch
+    from emmyptx import runtime
+    s = 16384
+    a, b = inputs.gemm_inputs(s, s, s, "bf16")
+    c = runtime.gemm(a.to(cuda), b.to(cuda), epilogue="gelu_tanh")
+    torch.cuda.synchronize()
+    assert runtime.device_status() == 0
+    edges = [0, 1, 127, 128, 129, 2047, 2048, 8191, 8192, 16255, 16256, s - 2, s - 1]
+    rows = sorted(set(edges) | set(np.random.default_rng(4).integers(0, s, 256).tolist()))
+    ref = reference.gemm_reference(a[rows], b, "gelu_tanh")
+    got = c[rows].cpu()
+    ok, ratio = reference.gemm_tolerance_ok(got, ref)
+    assert ok, f"worst error {ratio:.2f}x the bound"
+    assert not reference.compare(got.float().numpy(), ref.numpy(), 1e-2, 1e-2 * float(ref.std()))["vacuous"]
+    # every column block of every sampled row was written (no tile skipped): no element kept the fill value
+    fill = torch.full((8, s), float("nan"), dtype=torch.bfloat16, device=cuda)
+    runtime.gemm(a[:8].to(cuda), b.to(cuda), epilogue="gelu_tanh", out=fill)
+    assert not torch.isnan(fill).any()
+    # size-independent property: the rows of a row-permuted A give the permuted rows of C bit for bit
+    perm = torch.from_numpy(np.random.default_rng(6).permutation(s)[:1024])
+    sub = runtime.gemm(a[perm].to(cuda).contiguous(), b.to(cuda), epilogue="gelu_tanh")
+    assert torch.equal(sub, c[perm.to(cuda)])
+
+
 def test_linearity_at_size(cuda):
     """Size-independent property at a large size: (2A) B = 2 (A B) exactly (scaling by 2 is exact
     in bf16, whose exponent range keeps these outputs normal), and rows of a row-permuted A give

@@ -2,8 +2,11 @@
 JIT-loaded on this GPU through the driver API, as the reference's runner does (tools/run_local.py:64-72,
 :100-102), next to the sm_100a kernels on the same device buffers.
 
-The reference text targets sm_89; the driver JITs it forward. Only the two streaming kernels are run: straight
-line code with in-range addresses by construction (grid * block == n, indices masked to n - 1).
+The reference text targets sm_89; the driver JITs it forward. The two streaming kernels are straight-line code
+with in-range addresses by construction (grid * block == n, indices masked to n - 1). The tensor-core kernels
+(`mma.sync` on fragments read from global memory, emmyptx/mma.py:65-242) are the guard-free ones of the fixture
+set: whole m16n8k16 cells only, every address inside its buffer (checked when the fixtures are generated,
+tests/golden/make_reference_ptx.py).
 """
 import json
 from pathlib import Path
@@ -64,3 +67,47 @@ def test_pointwise_against_the_reference_kernel(manifest, cuda):
     # ours is the tighter of the two against float64
     assert np.abs(ours - ref).max() <= np.abs(theirs - ref).max()
     assert reference.c1_condition_ulp(ours, x_np).max() <= reference.c1_condition_ulp(theirs, x_np).max()
+
+
+HALF_MM, BF16_MM = dict(rtol=2e-2, atol=1e-1), dict(rtol=5e-2, atol=5e-1)      # tools/torch_cases/matmul.py:7
+
+
+@pytest.mark.parametrize("case", ["m_f16_mm", "m_bf16_mm", "m_f16_linear", "m_f16_bmm"])
+def test_gemm_against_the_reference_kernel(manifest, cuda, case):
+    """The reference's own matmul cases (tools/torch_cases/matmul.py:27-32): its mma.sync kernel and the tcgen05 kernel
+    on the same device buffers. Both must sit inside the reference's tolerance class of the float64 product; the two
+    kernels accumulate in fp32 and round once, so they agree to one unit of the output type; and ours is no further
+    from float64 than theirs. The CPU execution of the same PTX (the golden vectors) agrees with the GPU's."""
+    import torch
+    from emmyptx import runtime
+    info = manifest[case]
+    g = info["gemm"]
+    assert g["device"]
+    a, b = inputs.gemm_inputs(g["m"], g["n"], g["k"], g["dtype"], g["b_trans"], scaled=False, batch=tuple(g["batch"]))
+    a_d, b_d = a.to(cuda), b.to(cuda)
+    theirs = torch.zeros(*g["batch"], g["m"], g["n"], dtype=a.dtype, device=cuda)
+    torch.cuda.synchronize()
+    run_ptx((GOLDEN / f"{case}.ref.ptx").read_text(), info["entry"], [a_d.data_ptr(), b_d.data_ptr(), theirs.data_ptr()],
+            info["launch"]["grid"][0], info["launch"]["block"][0])
+    if g["batch"]:
+        ours = runtime.gemm_batched(a_d, b_d)
+    else:
+        ours = runtime.gemm(a_d, b_d, b_is_nk=g["b_trans"])
+    torch.cuda.synchronize()
+    bb = b.double().transpose(-1, -2) if g["b_trans"] else b.double()
+    ref = (a.double() @ bb).numpy()
+    tol = HALF_MM if g["dtype"] == "f16" else BF16_MM
+    theirs_np, ours_np = theirs.cpu().double().numpy(), ours.cpu().double().numpy()
+    assert reference.compare(theirs_np, ref, **tol)["ok"]
+    assert reference.compare(ours_np, ref, **tol)["ok"]
+    # kernel against kernel: identical after rounding except where the fp32 sums differ in their last bits
+    assert np.mean(theirs_np == ours_np) > 0.98
+    spacing = np.abs(ref) * (2.0 ** -10 if g["dtype"] == "f16" else 2.0 ** -7) + 1e-3
+    assert np.all(np.abs(theirs_np - ours_np) <= 2 * spacing)
+    assert np.abs(ours_np - ref).mean() <= np.abs(theirs_np - ref).mean() * 1.02
+    gold = np.load(GOLDEN / "golden.npz")
+    cpu = torch.from_numpy(gold[f"{case}.c"].view(np.int16)).view(a.dtype).double().numpy()
+    on_gpu, space = theirs_np.reshape(-1, g["n"]), spacing.reshape(-1, g["n"])
+    if f"{case}.rows" in gold.files:
+        on_gpu, space = on_gpu[gold[f"{case}.rows"]], space[gold[f"{case}.rows"]]
+    assert np.mean(cpu == on_gpu) > 0.98 and np.all(np.abs(cpu - on_gpu) <= 2 * space)

@@ -1,9 +1,10 @@
 """The oracle pinned against the reference's own output (CPU only).
 
-tests/golden/golden.npz holds what the reference's PTX computes for the streaming configurations (its own
-compiler's output, executed by oracle/ptx_interp.py; make_golden.py). The float64 oracle must agree with it
-within the reference's tolerance class for transcendental ops (rtol = atol = 1e-5,
-tools/torch_cases/__init__.py:18); the integer oracle, in its truncating mode, bit for bit.
+tests/golden/golden.npz holds what the reference's PTX computes for the streaming configurations and for its
+tensor-core matmul cases (its own compiler's output, executed by oracle/ptx_interp.py; make_golden.py). The float64
+oracle must agree with it within the reference's tolerance class for transcendental ops (rtol = atol = 1e-5,
+tools/torch_cases/__init__.py:18) and for 16-bit matmuls (tools/torch_cases/matmul.py:7); the integer oracle, in
+its truncating mode, bit for bit.
 """
 import json
 from pathlib import Path
@@ -82,3 +83,43 @@ def test_condition_aware_ulp_metric_on_torch_fp32():
     t32 = reference.c1_f32_torch(torch.from_numpy(x)).numpy()
     assert reference.ulp_error(t32, reference.c1_f64(x)).max() > 100
     assert reference.c1_condition_ulp(t32, x).max() < 3.0
+
+
+HALF_MM, BF16_MM = dict(rtol=2e-2, atol=1e-1), dict(rtol=5e-2, atol=5e-1)      # tools/torch_cases/matmul.py:7
+
+
+def _golden_gemm(golden, case):
+    import torch
+    info = json.loads((GOLDEN / "reference_ptx_manifest.json").read_text())[case]["gemm"]
+    a, b = inputs.gemm_inputs(info["m"], info["n"], info["k"], info["dtype"], info["b_trans"], scaled=False,
+                              batch=tuple(info["batch"]))
+    bb = b.double().transpose(-1, -2) if info["b_trans"] else b.double()
+    ref = (a.double() @ bb).reshape(-1, info["n"]).numpy()
+    td = torch.float16 if info["dtype"] == "f16" else torch.bfloat16
+    got = torch.from_numpy(golden[f"{case}.c"].view(np.int16)).view(td).double().numpy()
+    if f"{case}.rows" in golden.files:
+        ref = ref[golden[f"{case}.rows"]]
+    return got, ref, (HALF_MM if info["dtype"] == "f16" else BF16_MM), td
+
+
+@pytest.mark.parametrize("case", ["m_f16_mm_32x16x32", "m_f16_mm_odd", "m_f16_mm", "m_bf16_mm", "m_f16_linear", "m_f16_bmm"])
+def test_gemm_oracle_agrees_with_the_reference_kernel(golden, case):
+    """The reference's mma.sync kernel (fragments, K loop, converted store; emmyptx/mma.py:65-242) for its own matmul
+    cases, executed from its PTX text, against the float64 product of the same rounded operands: inside the
+    reference's tolerance class, and -- the kernel accumulating in fp32 and rounding once -- within one rounding of
+    the output type of the float64 value almost everywhere."""
+    import torch
+    got, ref, tol, td = _golden_gemm(golden, case)
+    res = reference.compare(got, ref, **tol)
+    assert res["ok"], res
+    once = torch.from_numpy(ref).to(td).double().numpy()
+    assert np.mean(got == once) > 0.98          # the rest differ by the fp32 accumulation's last bit before rounding
+
+
+def test_interpreter_reproduces_the_gemm_fixture():
+    info = json.loads((GOLDEN / "reference_ptx_manifest.json").read_text())["m_f16_mm_32x16x32"]
+    import torch
+    a, b = inputs.gemm_inputs(32, 16, 32, "f16", scaled=False)
+    bufs = {"A": a.view(torch.int16).numpy().copy(), "B": b.view(torch.int16).numpy().copy(), "C": np.zeros((32, 16), np.int16)}
+    ptx_interp.run_entry((GOLDEN / "m_f16_mm_32x16x32.ref.ptx").read_text(), bufs, info["launch"]["grid"][0], info["launch"]["block"][0])
+    assert np.array_equal(bufs["C"].view(np.uint16), np.load(GOLDEN / "golden.npz")["m_f16_mm_32x16x32.c"])
