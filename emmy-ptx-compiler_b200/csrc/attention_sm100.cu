@@ -57,6 +57,7 @@ struct AttParams {
     int seq_q, seq_k;
     int q_tiles;
     float scale_log2;       // scale * log2(e)
+    unsigned long long wait_limit_ns;       // after which a pipeline wait gives up
     uint32_t* status;
 };
 
@@ -104,7 +105,7 @@ __device__ __forceinline__ bool pair_exchange(const WaitCtx& ctx, volatile uint3
                 if (*ctx.abort_flag) { ok = false; break; }
                 const uint64_t now = ptx::global_timer_ns();
                 if (t0 == 0) t0 = now;
-                else if (now - t0 > kWaitLimitNs) {
+                else if (now - t0 > ctx.limit_ns) {
                     atomicCAS(ctx.status_word, 0u, code);
                     *ctx.abort_flag = 1;
                     ok = false;
@@ -146,7 +147,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     // Causal: keys beyond the tile's last query are never seen, so the tiles past the diagonal are skipped.
     const int kv_all = (p.seq_k + kTileK - 1) / kTileK;
     const int kv_tiles = p.causal ? min(kv_all, (qt * kTileQ + kTileQ + kTileK - 1) / kTileK) : kv_all;
-    const WaitCtx wctx{abort_flag, p.status};
+    const WaitCtx wctx{abort_flag, p.status, p.wait_limit_ns};
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(q_full, 1); ptx::mbar_init(k_full, 1); ptx::mbar_init(v_full, 1);
@@ -438,6 +439,7 @@ static int launch_attention(const void* Q, const void* K, const void* V, void* c
     p.mc_base = multicast ? (unsigned long long)(uintptr_t)O[0] : 0ull;
     p.q_tiles = (int)((seq_q + kTileQ - 1) / kTileQ);
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.wait_limit_ns = wait_limit_ns();
     EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_att_status));
     const int64_t ctas = units * p.q_tiles;
     if (ctas >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: %lld query tiles exceed the grid limit", (long long)ctas);

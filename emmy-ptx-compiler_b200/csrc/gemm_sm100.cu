@@ -58,6 +58,7 @@ struct GemmParams {
     const void* bias;       // per-column addend of the output type, or null
     unsigned long long mc_base;     // != 0: C as a multicast address (stores go out through multimem.st, once, to every GPU)
     long long ldc, stride_c;        // of C, in elements (multicast mode only; the TMA path has them in its tensor maps)
+    unsigned long long wait_limit_ns;       // after which a pipeline wait gives up
     uint32_t* status;
 };
 
@@ -141,7 +142,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int k_total = F32 ? 6 * k_blocks : k_blocks;          // k-blocks the accumulator of one tile receives
     const int plane_tiles = p.m_blocks * p.n_blocks;
     const int tiles = plane_tiles * p.batch;
-    const WaitCtx wctx{abort_flag, p.status};
+    const WaitCtx wctx{abort_flag, p.status, p.wait_limit_ns};
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
@@ -453,6 +454,34 @@ int check_sm100() {
     return EMMYB200_OK;
 }
 
+// One CTA whose first thread waits, through the same bounded_wait as every pipeline role, on an mbarrier that nothing
+// ever arrives on. The wait runs out after `limit_ns`, records its code and raises the abort flag; the other threads
+// see the flag and the kernel returns. This is the give-up path of the real kernels, made to happen on purpose without
+// a fault, a trap or an endless loop.
+__global__ void __launch_bounds__(64) wait_expiry_kernel(uint32_t* status, unsigned long long limit_ns, uint32_t* saw_abort) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        abort_flag = 0;
+        ptx::mbar_fence_init();
+    }
+    __syncthreads();
+    const WaitCtx ctx{&abort_flag, status, limit_ns};
+    bool ok = true;
+    if (threadIdx.x == 0) ok = bounded_wait(ctx, ptx::smem_u32(&bar), 0, 0x7e570001u);
+    __syncthreads();
+    if (threadIdx.x == 32 && saw_abort != nullptr) *saw_abort = abort_flag;     // another warp sees the flag, as the other roles do
+    (void)ok;
+}
+
+__device__ uint32_t g_selftest_saw_abort;
+
+int gemm_peek_status(uint32_t* out) {
+    EMMY_CUDA(cudaMemcpyFromSymbol(out, g_gemm_status, sizeof(uint32_t)));
+    return EMMYB200_OK;
+}
+
 int gemm_read_status(uint32_t* out) {
     uint32_t zero = 0;
     EMMY_CUDA(cudaDeviceSynchronize());
@@ -506,6 +535,7 @@ static int launch_gemm(const GemmCall& g, cudaStream_t stream) {
     p.mc_base = multicast ? (unsigned long long)(uintptr_t)g.C[0] : 0ull;
     p.ldc = g.ldc;
     p.stride_c = g.stride_c;
+    p.wait_limit_ns = wait_limit_ns();
     EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
     const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks * g.batch;
     if (tiles >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "gemm: %lld output tiles exceed the scheduler's range", (long long)tiles);
@@ -672,6 +702,29 @@ extern "C" int emmyb200_gemm_f32(int epilogue, int flags, const float* A, const 
     g.b_shared_split = b_shared;
     if (N > 128) return b_nk ? launch_gemm<256, true, true, true>(g, s) : launch_gemm<256, true, false, true>(g, s);
     return b_nk ? launch_gemm<128, true, true, true>(g, s) : launch_gemm<128, true, false, true>(g, s);
+}
+
+extern "C" int emmyb200_selftest_wait_expiry(uint64_t limit_ns, void* cuda_stream) {
+    using namespace emmy;
+    if (limit_ns < 1000ull || limit_ns > 1000000000ull) return fail(EMMYB200_ERR_ARG, "selftest_wait_expiry: limit between 1 us and 1 s");
+    int rc = check_sm100();
+    if (rc != EMMYB200_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    uint32_t* status = nullptr;
+    uint32_t* saw = nullptr;
+    EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_gemm_status));
+    EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&saw), g_selftest_saw_abort));
+    EMMY_CUDA(cudaMemsetAsync(saw, 0, sizeof(uint32_t), s));
+    wait_expiry_kernel<<<1, 64, 0, s>>>(status, limit_ns, saw);
+    rc = launch_status("wait_expiry_kernel");
+    if (rc != EMMYB200_OK) return rc;
+    EMMY_CUDA(cudaStreamSynchronize(s));
+    uint32_t word = 0, flag = 0;
+    rc = gemm_peek_status(&word);
+    if (rc != EMMYB200_OK) return rc;
+    EMMY_CUDA(cudaMemcpyFromSymbol(&flag, g_selftest_saw_abort, sizeof(uint32_t)));
+    if (word == 0 || flag == 0) return fail(EMMYB200_ERR_DEVICE, "selftest_wait_expiry: the wait did not give up (status 0x%08x, abort flag %u)", word, flag);
+    return fail(EMMYB200_ERR_TIMEOUT, "a bounded device-side wait expired: status 0x%08x", word);
 }
 
 extern "C" int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, const void* B, void* C, int64_t M,

@@ -211,16 +211,21 @@ __device__ __forceinline__ float rcp_approx(float x) {
 
 // ---- bounded waits ----------------------------------------------------------------------------
 // Every pipeline wait in the tensor-core kernels goes through this. It polls the barrier; every
-// 256 polls it looks at the CTA's abort flag and at the wall clock, and after `kWaitLimitNs`
-// it records `code` in the device status word, raises the abort flag and gives up. Callers
-// leave their role loop on `false`, and the kernel then tears down normally (tensor memory is
-// released, nothing traps).
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// 256 polls it looks at the CTA's abort flag and at the wall clock, and after `limit_ns` (a launch
+// parameter: wait_limit_ns() on the host, 2 s unless emmyb200_set_wait_limit_ns changed it) it
+// records `code` in the device status word, raises the abort flag and gives up. Callers leave their
+// role loop on `false`, and the kernel then tears down normally (tensor memory is released, nothing
+// traps).
+constexpr uint64_t kDefaultWaitLimitNs = 2000000000ull;
 
 struct WaitCtx {
     volatile uint32_t* abort_flag;   // shared memory
     uint32_t* status_word;           // global memory
+    uint64_t limit_ns;
 };
+
+// The limit the next launches get (host side, process-wide).
+uint64_t wait_limit_ns();
 
 __device__ __forceinline__ bool bounded_wait(const WaitCtx& ctx, uint32_t bar, uint32_t parity, uint32_t code) {
     uint64_t t0 = 0;
@@ -230,7 +235,7 @@ __device__ __forceinline__ bool bounded_wait(const WaitCtx& ctx, uint32_t bar, u
             if (*ctx.abort_flag) return false;
             uint64_t now = ptx::global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) {
+            else if (now - t0 > ctx.limit_ns) {
                 atomicCAS(ctx.status_word, 0u, code);
                 *ctx.abort_flag = 1;
                 return false;

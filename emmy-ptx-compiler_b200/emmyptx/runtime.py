@@ -90,7 +90,10 @@ _SIGNATURES = {
     "emmyb200_rowwise_f32_static": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                    ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p]),
     "emmyb200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
+    "emmyb200_set_wait_limit_ns": (ctypes.c_int, [ctypes.c_uint64]),
+    "emmyb200_selftest_wait_expiry": (ctypes.c_int, [ctypes.c_uint64, ctypes.c_void_p]),
 }
+ERR_TIMEOUT = -6
 EXPORTS = tuple(_SIGNATURES)
 
 
@@ -443,7 +446,16 @@ def cumsum(x, out=None, stream=None):
 
 
 def device_status() -> int:
-    """Reads and clears the device status word (non-zero: a bounded device-side wait expired)."""
+    """Reads and clears the device status word (non-zero: a bounded device-side wait expired). Does not raise on an
+    expired wait: `check_device()` does."""
+    word = ctypes.c_uint32(0)
+    rc = library().emmyb200_device_status(ctypes.byref(word))
+    if rc not in (0, ERR_TIMEOUT):
+        check(rc)
+    return word.value
+
+
+def check_device() -> None:
+    """Raises KernelError (status EMMYB200_ERR_TIMEOUT) if a bounded device-side wait expired since the last read."""
     word = ctypes.c_uint32(0)
     check(library().emmyb200_device_status(ctypes.byref(word)))
-    return word.value

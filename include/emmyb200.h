@@ -251,10 +251,26 @@ int64_t emmyb200_rowwise_static_capacity(void);
 int emmyb200_rowwise_f32_static(int op, const float* x, const float* weight, const float* bias, void* y, int64_t rows,
                                 int64_t cols, float eps, void* cuda_stream);
 
-/* Reads (and clears) the device status word of the current device: 0 if no bounded wait has
- * expired since the last call, else a code naming kernel, role and pipeline stage.
- * Synchronises the device. */
+/* Reads (and clears) the device status word of the current device into *status_out: 0 if no bounded wait has
+ * expired since the last call, else a code naming kernel (bits 24-31: 1 GEMM, 2 attention), wait site (16-23)
+ * and pipeline stage (0-15). Returns EMMYB200_OK with a zero word and EMMYB200_ERR_TIMEOUT with a non-zero one
+ * (the outputs of the launches since the last clean read are then not to be trusted; the device and the library
+ * stay usable). Synchronises the device. This replaces the reference's only device-side error path, a `trap`
+ * that kills the context (emmyptx/kernel.py:685-691). */
 int emmyb200_device_status(uint32_t* status_out);
+
+/* The time after which a device-side pipeline wait gives up, for the launches that follow (process-wide; default
+ * 2 s; 0 restores the default; 1 us .. 60 s). A watchdog setting: a healthy launch never waits anywhere near it.
+ * No counterpart in the reference. */
+int emmyb200_set_wait_limit_ns(uint64_t limit_ns);
+
+/* Self-test of the give-up path: launches one small CTA whose first thread waits, through the same bounded wait as
+ * every pipeline role of the tensor-core kernels, on a barrier that nothing arrives on, with `limit_ns` (1 us .. 1 s)
+ * as the limit; waits for the stream; and returns EMMYB200_ERR_TIMEOUT when -- as it must -- the wait expired, set the
+ * status word and raised the CTA's abort flag (EMMYB200_ERR_DEVICE if it did not). The status word stays set until
+ * emmyb200_device_status reads it. Nothing faults or traps; the device stays usable. No counterpart in the
+ * reference. */
+int emmyb200_selftest_wait_expiry(uint64_t limit_ns, void* cuda_stream);
 
 #ifdef __cplusplus
 }

@@ -65,6 +65,8 @@ def test_newer_entry_points_check_their_arguments_without_a_device(lib):
     assert lib.emmyb200_attention_fwd(2, 2, p, p, p, p, 1, 8, 8, 128, 1.0, None) == -1
     assert lib.emmyb200_attention_fwd_allgather(2, 2, p, p, p, dst, 2, 1, 8, 8, 128, 1.0, None) == -1
     assert lib.emmyb200_rowwise_static_capacity() == 1 << 20
+    assert lib.emmyb200_set_wait_limit_ns(1) == -1 and lib.emmyb200_set_wait_limit_ns(0) == 0
+    assert lib.emmyb200_selftest_wait_expiry(10, None) == -1 and lib.emmyb200_selftest_wait_expiry(2 * 10**9, None) == -1
 
 
 def test_python_binding_refuses_cpu_tensors():
