@@ -22,7 +22,8 @@ OBJ = HERE / "build"
 LIB = HERE / "lib" / "libemmyb200.so"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
+         *os.environ.get("EMMYB200_NVCC_EXTRA", "").split()]        # development builds only (tracing macros)
 
 
 def _newest_header() -> float:

@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math_constants.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -54,7 +55,7 @@ struct AttParams {
     int n_dst;              // destinations of every output tile (1 = the local O only)
     int causal;             // 1: query i sees keys 0 .. i only
     unsigned long long mc_base;     // != 0: O as a multicast address, written once with multimem.st for every GPU
-    int seq_q, seq_k;
+    int units, seq_q, seq_k;
     int q_tiles;
     float scale_log2;       // scale * log2(e)
     unsigned long long wait_limit_ns;       // after which a pipeline wait gives up
@@ -410,6 +411,559 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
 }
 
+
+// ---- two query tiles per CTA ------------------------------------------------------------------------------------------
+// The kernel above overlaps one CTA's softmax with the other resident CTA's MMAs; inside a CTA the score product, the
+// softmax and the value product of a key tile still run one after the other. This form keeps the tensor pipe fed from
+// within one CTA: a persistent CTA per SM owns TWO 128-query tiles of one unit (S0, S1, O0, O1 = all 512 tensor-memory
+// columns) and walks the key tiles once for both.
+//   warp 0     TMA: the two Q tiles, then K_j / V_j through a four-stage ring (32 KiB each at d = 128)
+//   warp 1     MMA issue, in the order  S0(0) S1(0) | O0+=P0 V(j)  S0(j+1)  O1+=P1 V(j)  S1(j+1) | ...  so that
+//              while one tile's probabilities are being made the tensor pipe works on the other tile
+//   warps 4-7, 8-11   softmax of tile 0 / tile 1, one thread per query row: row max, exponentials and row sum need no
+//              exchange between threads; S is read from tensor memory twice (maximum, then exponentials) in 32-column
+//              pieces so that a row's 128 scores never have to be live at once; P (16-bit pairs) overwrites S
+//   warps 12-15  correction: rescales O_i in tensor memory when a row's running maximum was raised (rare after the
+//              first tiles: it is raised only when it grows by more than 2^8), and at the end normalises O_i by the
+//              row sums, stages it in shared memory and stores it (TMA, or multimem.st for a multicast destination)
+//              while the MMA warp is already working on the next pair of tiles.
+// Work items (unit, pair of query tiles) are dealt round-robin. With the causal flag a pair's cost grows with its
+// position, so a CTA takes pairs two at a time, the k-th longest together with the k-th shortest of the same unit:
+// every such couple costs the same, and the static deal stays balanced. Every wait is bounded; the groups meet only
+// through mbarriers (no bar.sync inside the role loops), so a wait that gives up cannot strand another warp.
+#ifdef EMMY_ATT_TRACE
+// Development aid (not built by default): clock stamps of block 0's roles, [role][event index].
+__device__ long long g_att_trace[8][512];
+__device__ int g_att_trace_n[8];
+#define ATT_STAMP(role)                                                          \
+    do {                                                                         \
+        if (blockIdx.x == 0 && g_att_trace_n[role] < 512) g_att_trace[role][g_att_trace_n[role]++] = clock64(); \
+    } while (0)
+#else
+#define ATT_STAMP(role) do { } while (0)
+#endif
+
+constexpr int kPairThreads = 512;
+constexpr int kKvStages = 4;
+constexpr int kPolyOf8 = 4;         // of every eight pairs of exponentials, how many are computed on the FMA pipe
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float min3(float a, float b, float c) {
+    float d;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) {
+    uint64_t d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(as_u64(a)), "l"(as_u64(b)));
+    return as_f2(d);
+}
+// 2^y for a pair, y <= 8 or so, without the transcendental unit: y clamped at -125 (the result then underflows
+// harmlessly small), n = round(y) taken from the low mantissa bits of y + 1.5 * 2^23, f = y - n in [-1/2, 1/2],
+// 2^f by a cubic (minimax in relative error: 7.5e-5), and n added into the exponent field of the result.
+__device__ __forceinline__ float2 exp2_poly2(float2 y) {
+    const float2 magic = make_float2(12582912.0f, 12582912.0f);
+    y.x = fmaxf(y.x, -125.0f);
+    y.y = fmaxf(y.y, -125.0f);
+    const float2 t = add2(y, magic);
+    const float2 f = sub2(y, sub2(t, magic));
+    float2 q = fma2(make_float2(0.055171654f, 0.055171654f), f, make_float2(0.24261113f, 0.24261113f));
+    q = fma2(q, f, make_float2(0.69326097f, 0.69326097f));
+    q = fma2(q, f, make_float2(0.99992806f, 0.99992806f));
+    return make_float2(__uint_as_float(__float_as_uint(q.x) + (__float_as_uint(t.x) << 23)),
+                       __uint_as_float(__float_as_uint(q.y) + (__float_as_uint(t.y) << 23)));
+}
+
+template <int D>
+struct PairSmem {
+    static constexpr int kQBytes = kTileQ * D * 2;
+    static constexpr int kKvBytes = kTileK * D * 2;
+    static constexpr int kOBytes = kTileQ * D * 2;
+    static constexpr int kKvOffset = 2 * kQBytes;
+    static constexpr int kOOffset = kKvOffset + kKvStages * kKvBytes;
+    static constexpr int kBarOffset = kOOffset + kOBytes;
+    static constexpr int kFloatOffset = kBarOffset + 512;            // corr[2][128], lsum[2][128]
+    static constexpr int kTotal = kFloatOffset + 4 * 128 * 4;        // the base must be 1024-byte aligned (checked)
+};
+
+struct PairItem {
+    int unit, row0;     // unit and first query row of tile 0
+    int n[2];           // key tiles of tile 0 / tile 1 (0: the tile does not exist; n[0] == 0: nothing to do)
+};
+
+// Item `it` of this CTA. Returns false when the CTA's share is exhausted.
+__device__ __forceinline__ bool pair_item(const AttParams& p, int it, PairItem& w) {
+    const int q_pairs = (p.q_tiles + 1) >> 1;
+    int unit, pr;
+    if (!p.causal) {
+        const long long t = (long long)blockIdx.x + (long long)it * gridDim.x;
+        if (t >= (long long)p.units * q_pairs) return false;
+        unit = (int)(t / q_pairs);
+        pr = (int)(t % q_pairs);
+    } else {
+        const int couples = (q_pairs + 1) >> 1;                         // per unit
+        const long long s = (long long)blockIdx.x + (long long)(it >> 1) * gridDim.x;
+        if (s >= (long long)p.units * couples) return false;
+        unit = (int)(s / couples);
+        const int k = (int)(s % couples);
+        pr = (it & 1) ? k : q_pairs - 1 - k;                            // the long one first
+        if ((it & 1) && k == q_pairs - 1 - k) { w.unit = unit; w.row0 = 0; w.n[0] = w.n[1] = 0; return true; }   // odd count: the middle pair stands alone
+    }
+    const int kv_all = (p.seq_k + kTileK - 1) / kTileK;
+    w.unit = unit;
+    w.row0 = pr * 2 * kTileQ;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = w.row0 + i * kTileQ;
+        w.n[i] = r >= p.seq_q ? 0 : (p.causal ? min(kv_all, r / kTileK + 1) : kv_all);
+    }
+    return true;
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kPairThreads, 1)
+attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                          const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttOutMaps out, AttParams p) {
+    using S = PairSmem<D>;
+    constexpr int kChunks = D / 64;
+    constexpr uint32_t kColS = 128, kColO = 256, kColOStride = 128;     // S_i at i * 128, O_i at 256 + i * 128
+    extern __shared__ __align__(1024) uint8_t smem_pair_raw[];
+    const uint32_t smem_base = ptx::smem_u32(smem_pair_raw);
+    if (smem_base & 1023u) {                                            // the swizzled tiles need a 1024-byte aligned base
+        if (threadIdx.x == 0) atomicCAS(p.status, 0u, 0x02ff0000u);
+        return;
+    }
+    uint8_t* smem_gen = smem_pair_raw;
+    auto q_smem = [&](int i) { return smem_base + (uint32_t)i * S::kQBytes; };
+    auto kv_smem = [&](uint32_t s) { return smem_base + S::kKvOffset + s * S::kKvBytes; };
+    const uint32_t o_smem = smem_base + S::kOOffset;
+    const uint32_t bar_base = smem_base + S::kBarOffset;
+    auto bar = [&](int idx) { return bar_base + 8u * idx; };
+    // barrier indices
+    constexpr int Q_FULL = 0, Q_EMPTY = 2, KV_FULL = 4, KV_EMPTY = 8, S_FULL = 12, P_FULL = 14, O_READY = 16, O_FULL = 18, O_FREE = 20,
+                  CORR_READY = 22, L_READY = 30, STAGE_READY = 38, STAGE_FREE = 39, N_BARS = 40;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + S::kBarOffset + 8 * N_BARS);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* corr = reinterpret_cast<float*>(smem_gen + S::kFloatOffset);        // [2][128] rescale factors
+    float* lsum = corr + 256;                                                  // [2][128] final row sums
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const WaitCtx wctx{abort_flag, p.status, p.wait_limit_ns};
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(bar(Q_FULL + i), 1); ptx::mbar_init(bar(Q_EMPTY + i), 1); ptx::mbar_init(bar(S_FULL + i), 1);
+            ptx::mbar_init(bar(P_FULL + i), 4); ptx::mbar_init(bar(O_READY + i), 4); ptx::mbar_init(bar(O_FULL + i), 1);
+            ptx::mbar_init(bar(O_FREE + i), 4);
+            for (int w = 0; w < 4; ++w) { ptx::mbar_init(bar(CORR_READY + 4 * i + w), 1); ptx::mbar_init(bar(L_READY + 4 * i + w), 1); }
+        }
+        for (int s = 0; s < kKvStages; ++s) { ptx::mbar_init(bar(KV_FULL + s), 1); ptx::mbar_init(bar(KV_EMPTY + s), 1); }
+        ptx::mbar_init(bar(STAGE_READY), 4); ptx::mbar_init(bar(STAGE_FREE), p.mc_base != 0 ? 4 : 1);
+        *abort_flag = 0;
+        ptx::mbar_fence_init();
+        ptx::prefetch_tensormap(&map_q); ptx::prefetch_tensormap(&map_k); ptx::prefetch_tensormap(&map_v);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), 512);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // Registers follow the work: 512 threads start with 128 each; the softmax warps (a whole row of scores per thread)
+    // take 184, paid for by the correction warps and by the first warpgroup, whose threads mostly wait.
+    // (Each role's branch starts with its own setmaxnreg, so that the register allocator sees one limit per branch.)
+    constexpr int kRegsFirst = 64, kRegsSoftmax = 184, kRegsCorrection = 80;
+    static_assert(4 * kRegsFirst + 8 * kRegsSoftmax + 4 * kRegsCorrection == 16 * 128, "the register file is 64 K registers");
+
+    if (warp == 0) {
+        // ---- TMA producer --------------------------------------------------------------------------------------------
+        ptx::setmaxnreg_dec<kRegsFirst>();
+        if (lane == 0) {
+            uint32_t kvr = 0, cq[2] = {0, 0};
+            bool ok = true;
+            PairItem w;
+            auto load_kv = [&](const CUtensorMap* map, int j) -> bool {
+                const uint32_t s = kvr & (kKvStages - 1), ph = (kvr / kKvStages) & 1;
+                if (!bounded_wait(wctx, bar(KV_EMPTY + s), ph ^ 1, 0x03010000u | (kvr & 0xffff))) return false;
+                ptx::mbar_arrive_expect_tx(bar(KV_FULL + s), S::kKvBytes);
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c)
+                    ptx::tma_load_3d(kv_smem(s) + c * (kTileK * 128), map, bar(KV_FULL + s), c * 64, j * kTileK, w.unit);
+                ++kvr;
+                return true;
+            };
+            for (int it = 0; ok && pair_item(p, it, w); ++it) {
+                if (w.n[0] == 0) continue;
+                const int nmax = max(w.n[0], w.n[1]);
+                if (!(ok = load_kv(&map_k, 0))) break;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    if (w.n[i] == 0 || !ok) continue;
+                    if (!(ok = bounded_wait(wctx, bar(Q_EMPTY + i), (cq[i] & 1) ^ 1, 0x03020000u | i))) break;
+                    ++cq[i];
+                    ptx::mbar_arrive_expect_tx(bar(Q_FULL + i), S::kQBytes);
+#pragma unroll
+                    for (int c = 0; c < kChunks; ++c)
+                        ptx::tma_load_3d(q_smem(i) + c * (kTileQ * 128), &map_q, bar(Q_FULL + i), c * 64, w.row0 + i * kTileQ, w.unit);
+                }
+                if (!ok || !(ok = load_kv(&map_v, 0))) break;
+                for (int j = 1; j < nmax && ok; ++j) ok = load_kv(&map_k, j) && load_kv(&map_v, j);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---- MMA issuer ----------------------------------------------------------------------------------------------
+        ptx::setmaxnreg_dec<kRegsFirst>();
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = ptx::mma_idesc_f16(BF16, false, false, kTileQ, kTileK);
+            constexpr uint32_t idesc_o = ptx::mma_idesc_f16(BF16, false, true, kTileQ, D);
+            uint32_t kvr = 0, cq[2] = {0, 0}, cp[2] = {0, 0}, cor[2] = {0, 0}, cof[2] = {0, 0};
+            bool ok = true;
+            PairItem w;
+            auto kv_wait = [&](uint32_t r, uint32_t code) {
+                return bounded_wait(wctx, bar(KV_FULL + (r & (kKvStages - 1))), (r / kKvStages) & 1, code | (r & 0xffff));
+            };
+            auto issue_s = [&](int i, uint32_t r) {                      // S_i = Q_i K^T with K in ring slot r
+                const uint32_t k_base = kv_smem(r & (kKvStages - 1));
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * (kTileQ * 128) + (kk % 4) * 32;
+                    ptx::mma_ss(tmem_base + i * kColS, ptx::smem_desc_sw128(q_smem(i) + off, 16, 1024),
+                                ptx::smem_desc_sw128(k_base + off, 16, 1024), idesc_s, kk != 0);
+                }
+                ptx::mma_commit(bar(S_FULL + i));
+            };
+            auto issue_pv = [&](int i, uint32_t r, bool first) {         // O_i (+)= P_i V with V in ring slot r
+                const uint32_t v_base = kv_smem(r & (kKvStages - 1));
+#pragma unroll
+                for (int kk = 0; kk < kTileK / 16; ++kk)
+                    ptx::mma_ts(tmem_base + kColO + i * kColOStride, tmem_base + i * kColS + kk * 8,
+                                ptx::smem_desc_sw128(v_base + kk * (16 * 128), kTileK * 128, 1024), idesc_o, !(first && kk == 0));
+            };
+            for (int it = 0; ok && pair_item(p, it, w); ++it) {
+                if (w.n[0] == 0) continue;
+                const int nmax = max(w.n[0], w.n[1]);
+                if (!(ok = kv_wait(kvr, 0x03030000u))) break;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    if (w.n[i] == 0 || !ok) continue;
+                    if (!(ok = bounded_wait(wctx, bar(Q_FULL + i), cq[i] & 1, 0x03040000u | i))) break;
+                    ++cq[i];
+                    ptx::tc_fence_after_sync();
+                    issue_s(i, kvr);
+                    if (w.n[i] == 1) ptx::mma_commit(bar(Q_EMPTY + i));
+                }
+                if (!ok) break;
+                ptx::mma_commit(bar(KV_EMPTY + (kvr & (kKvStages - 1))));
+                for (int j = 0; j < nmax && ok; ++j) {
+                    const uint32_t rv = kvr + 2 * j + 1, rk = rv + 1;
+                    bool v_waited = false, k_waited = false;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        if (j >= w.n[i] || !ok) continue;
+                        ATT_STAMP(0);
+                        if (!(ok = bounded_wait(wctx, bar(P_FULL + i), cp[i] & 1, 0x03050000u | (j & 0xffff)))) break;
+                        ATT_STAMP(0);
+                        ++cp[i];
+                        if (j == 0) {
+                            if (!(ok = bounded_wait(wctx, bar(O_FREE + i), (cof[i] & 1) ^ 1, 0x03060000u | i))) break;
+                            ++cof[i];
+                        } else {
+                            if (!(ok = bounded_wait(wctx, bar(O_READY + i), cor[i] & 1, 0x03070000u | (j & 0xffff)))) break;
+                            ++cor[i];
+                        }
+                        if (!v_waited) {
+                            if (!(ok = kv_wait(rv, 0x03080000u))) break;
+                            v_waited = true;
+                        }
+                        ptx::tc_fence_after_sync();
+                        ATT_STAMP(0);
+                        issue_pv(i, rv, j == 0);
+                        if (j == w.n[i] - 1) ptx::mma_commit(bar(O_FULL + i));
+                        if (j + 1 < w.n[i]) {
+                            if (!k_waited) {
+                                if (!(ok = kv_wait(rk, 0x03090000u))) break;
+                                k_waited = true;
+                                ptx::tc_fence_after_sync();
+                            }
+                            issue_s(i, rk);
+                            ATT_STAMP(0);
+                            if (j + 2 == w.n[i]) ptx::mma_commit(bar(Q_EMPTY + i));
+                        }
+                    }
+                    if (!ok) break;
+                    ptx::mma_commit(bar(KV_EMPTY + (rv & (kKvStages - 1))));
+                    if (j + 1 < nmax) ptx::mma_commit(bar(KV_EMPTY + (rk & (kKvStages - 1))));
+                }
+                kvr += 2 * nmax;
+            }
+        }
+        __syncwarp();
+    } else if (warp < 4) {
+        ptx::setmaxnreg_dec<kRegsFirst>();                             // the two spare warps of the first warpgroup
+    } else if (warp < 12) {
+        // ---- softmax of tile g: one thread per query row ---------------------------------------------------------------
+        ptx::setmaxnreg_inc<kRegsSoftmax>();
+        const int g = (warp - 4) >> 2, wq = warp & 3;
+        const int row = wq * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+        const uint32_t s_row = tmem_base + lane_base + g * kColS;       // this row's 128 scores; P goes over their first 64 columns
+        const float c = p.scale_log2;
+        const float fill = c > 0.0f ? -CUDART_INF_F : CUDART_INF_F;
+        uint32_t cs = 0;
+        bool ok = true;
+        PairItem w;
+        for (int it = 0; ok && pair_item(p, it, w); ++it) {
+            if (w.n[g] == 0) continue;
+            const int q_row = w.row0 + g * kTileQ + row;
+            float m_run = -CUDART_INF_F, l_run = 0.0f;
+            for (int j = 0; j < w.n[g] && ok; ++j) {
+                if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
+                ok = __all_sync(0xffffffffu, bounded_wait(wctx, bar(S_FULL + g), cs & 1, 0x030a0000u | (j & 0xffff)));
+                if (!ok) break;
+                if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
+                ++cs;
+                ptx::tc_fence_after_sync();
+                int valid = p.seq_k - j * kTileK;
+                if (p.causal) valid = min(valid, q_row - j * kTileK + 1);
+                const bool ragged = valid < kTileK;
+                // the whole row of scores into registers: four loads in flight, one wait
+                uint32_t r[kTileK];
+#pragma unroll
+                for (int ch = 0; ch < kTileK / 32; ++ch) ptx::tmem_ld_32x32b_x32(s_row + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[ch * 32]));
+                ptx::tmem_ld_wait();
+                if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
+                if (ragged) {                                           // last key tile, or the causal diagonal
+#pragma unroll
+                    for (int i = 0; i < kTileK; ++i)
+                        if (i >= valid) r[i] = __float_as_uint(fill);
+                }
+                // row extremum: four chains of three-input max / min
+                float ext[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) ext[i] = __uint_as_float(r[i]);
+                if (c > 0.0f) {
+#pragma unroll
+                    for (int i = 4; i + 7 < kTileK + 4; i += 8) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int a0 = i + 2 * q, a1 = a0 + 1;
+                            if (a1 < kTileK) ext[q] = max3(ext[q], __uint_as_float(r[a0]), __uint_as_float(r[a1]));
+                            else if (a0 < kTileK) ext[q] = fmaxf(ext[q], __uint_as_float(r[a0]));
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 4; i + 7 < kTileK + 4; i += 8) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int a0 = i + 2 * q, a1 = a0 + 1;
+                            if (a1 < kTileK) ext[q] = min3(ext[q], __uint_as_float(r[a0]), __uint_as_float(r[a1]));
+                            else if (a0 < kTileK) ext[q] = fminf(ext[q], __uint_as_float(r[a0]));
+                        }
+                    }
+                }
+                const float e01 = c > 0.0f ? fmaxf(ext[0], ext[1]) : fminf(ext[0], ext[1]);
+                const float e23 = c > 0.0f ? fmaxf(ext[2], ext[3]) : fminf(ext[2], ext[3]);
+                const float m_tile = (c > 0.0f ? fmaxf(e01, e23) : fminf(e01, e23)) * c;
+                // Raise the running max only when it would grow by more than 8: exponentials then stay below 2^8, and the
+                // accumulator needs rescaling rarely.
+                const bool raise = m_tile > m_run + 8.0f;
+                const float m_new = raise ? m_tile : m_run;
+                if (j > 0) {
+                    const float f = raise ? ptx::ex2_approx(m_run - m_new) : 1.0f;
+                    l_run *= f;
+                    corr[g * 128 + row] = f;
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(bar(CORR_READY + 4 * g + wq));
+                }
+                m_run = m_new;
+                if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
+                // p = 2^(c s - m). The transcendental unit makes 16 exponentials a clock for the whole SM, which is as long
+                // as the tensor cores need for the tile's two products; so kPolyOf8 of every eight pairs go through the
+                // FMA pipe instead (round to the nearest integer n by a magic-number add, a cubic for 2^f on [-1/2, 1/2],
+                // relative error 7.5e-5 -- below the rounding of P to 16 bits --, n added into the exponent field).
+                // Tiles with masked (infinite) scores take the transcendental unit for everything.
+                const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_run, -m_run);
+                float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+#pragma unroll
+                for (int ch = 0; ch < kTileK / 32; ++ch) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int e0 = ch * 32 + 2 * i;
+                        const float2 y = fma2(make_float2(__uint_as_float(r[e0]), __uint_as_float(r[e0 + 1])), c2, nm2);
+                        float2 e;
+                        if ((i & 7) < kPolyOf8 && !ragged) e = exp2_poly2(y);
+                        else e = make_float2(ptx::ex2_approx(y.x), ptx::ex2_approx(y.y));
+                        sum2[i & 1] = add2(sum2[i & 1], e);
+                        pk[i] = pack_pair<BF16>(e.x, e.y);
+                    }
+                    ptx::tmem_st_32x32b_x16(s_row + ch * 16, pk);
+                }
+                const float2 tot = add2(sum2[0], sum2[1]);
+                l_run += tot.x + tot.y;
+                if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(bar(P_FULL + g));
+                if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
+            }
+            if (!ok) break;
+            lsum[g * 128 + row] = l_run;
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar(L_READY + 4 * g + wq));
+        }
+    } else {
+        // ---- correction and output ---------------------------------------------------------------------------------------
+        ptx::setmaxnreg_dec<kRegsCorrection>();
+        const int wq = warp & 3;
+        const int row = wq * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+        const bool issuer = threadIdx.x == 12 * 32;
+        uint32_t cc[2] = {0, 0}, cl[2] = {0, 0}, cfull[2] = {0, 0}, cstage = 0;
+        bool ok = true;
+        PairItem w;
+        for (int it = 0; ok && pair_item(p, it, w); ++it) {
+            if (w.n[0] == 0) continue;
+            const int nmax = max(w.n[0], w.n[1]);
+            for (int j = 1; j < nmax && ok; ++j) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    if (j >= w.n[i] || !ok) continue;
+                    if (issuer) ATT_STAMP(3);
+                    ok = __all_sync(0xffffffffu, bounded_wait(wctx, bar(CORR_READY + 4 * i + wq), cc[i] & 1, 0x030b0000u | (j & 0xffff)));
+                    if (!ok) break;
+                    if (issuer) ATT_STAMP(3);
+                    ++cc[i];
+                    const float f = corr[i * 128 + row];
+                    if (__any_sync(0xffffffffu, f != 1.0f)) {
+                        ptx::tc_fence_after_sync();
+                        const uint32_t o_row = tmem_base + lane_base + kColO + i * kColOStride;
+#pragma unroll 1
+                        for (int col = 0; col < D; col += 32) {
+                            uint32_t o[32];
+                            ptx::tmem_ld_32x32b_x32(o_row + col, o);
+                            ptx::tmem_ld_wait();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+                            ptx::tmem_st_32x32b_x16(o_row + col, *reinterpret_cast<uint32_t(*)[16]>(&o[0]));
+                            ptx::tmem_st_32x32b_x16(o_row + col + 16, *reinterpret_cast<uint32_t(*)[16]>(&o[16]));
+                        }
+                        ptx::tmem_st_wait();
+                    }
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(bar(O_READY + i));
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if (w.n[i] == 0 || !ok) continue;
+                ok = __all_sync(0xffffffffu, bounded_wait(wctx, bar(L_READY + 4 * i + wq), cl[i] & 1, 0x030c0000u | i));
+                if (!ok) break;
+                ++cl[i];
+                const float inv = 1.0f / lsum[i * 128 + row];
+                ok = __all_sync(0xffffffffu, bounded_wait(wctx, bar(O_FULL + i), cfull[i] & 1, 0x030d0000u | i));
+                if (!ok) break;
+                ++cfull[i];
+                // the staging tile is free once the previous tile's stores (or multicast copies) have read it
+                ok = __all_sync(0xffffffffu, bounded_wait(wctx, bar(STAGE_FREE), (cstage & 1) ^ 1, 0x030e0000u | i));
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t o_row = tmem_base + lane_base + kColO + i * kColOStride;
+#pragma unroll 1
+                for (int ch = 0; ch < D / 32; ++ch) {
+                    uint32_t o[32];
+                    ptx::tmem_ld_32x32b_x32(o_row + ch * 32, o);
+                    ptx::tmem_ld_wait();
+                    const uint32_t row_smem = o_smem + (ch >> 1) * (kTileQ * 128) + row * 128;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint32_t slot = (uint32_t)(4 * (ch & 1) + q) ^ (uint32_t)(row & 7);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_smem + slot * 16),
+                                     "r"(pack_pair<BF16>(__uint_as_float(o[8 * q + 0]) * inv, __uint_as_float(o[8 * q + 1]) * inv)),
+                                     "r"(pack_pair<BF16>(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv)),
+                                     "r"(pack_pair<BF16>(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv)),
+                                     "r"(pack_pair<BF16>(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv))
+                                     : "memory");
+                    }
+                }
+                ptx::tc_fence_before_sync();
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(bar(O_FREE + i));                  // O_i may be overwritten by the next item's first value product
+                    ptx::mbar_arrive(bar(STAGE_READY));
+                }
+                const int tile_row0 = w.row0 + i * kTileQ;
+                if (p.mc_base != 0) {
+                    ok = __all_sync(0xffffffffu, bounded_wait(wctx, bar(STAGE_READY), cstage & 1, 0x030f0000u | i));
+                    if (!ok) break;
+                    constexpr int kSlots = D / 8;                       // 16-byte slots per output row
+                    const int tt = (int)threadIdx.x - 12 * 32, slot = tt % kSlots;
+                    const uint32_t chunk_smem = o_smem + (slot >> 3) * (kTileQ * 128);
+#pragma unroll
+                    for (int e = 0; e < kTileQ * kSlots / 128; ++e) {
+                        const int r = tt / kSlots + (128 / kSlots) * e;
+                        if (tile_row0 + r < p.seq_q) {
+                            uint32_t w0, w1, w2, w3;
+                            ptx::ld_shared_16B(chunk_smem + r * 128 + (((slot & 7) ^ (r & 7)) << 4), w0, w1, w2, w3);
+                            const unsigned long long elem = ((unsigned long long)w.unit * p.seq_q + tile_row0 + r) * D + slot * 8;
+                            ptx::multimem_st_16B(p.mc_base + elem * 2ull, w0, w1, w2, w3);
+                        }
+                    }
+                    // the next tile's staging writes must come after these reads: every warp reports when it is done
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(bar(STAGE_FREE));
+                } else if (issuer) {
+                    if (bounded_wait(wctx, bar(STAGE_READY), cstage & 1, 0x030f0000u | i)) {
+                        for (int d = 0; d < p.n_dst; ++d)
+#pragma unroll
+                            for (int cc2 = 0; cc2 < kChunks; ++cc2)
+                                ptx::tma_store_3d(&out.m[d], o_smem + cc2 * (kTileQ * 128), cc2 * 64, tile_row0, w.unit);
+                        ptx::tma_store_commit();
+                        ptx::tma_store_wait_read<0>();
+                    }
+                    ptx::mbar_arrive(bar(STAGE_FREE));
+                }
+                ++cstage;
+            }
+        }
+        if (issuer) ptx::tma_store_wait<0>();
+        if (p.mc_base != 0) __threadfence_system();
+    }
+
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, 512);
+    }
+}
+
+#ifdef EMMY_ATT_TRACE
+extern "C" int emmyb200_debug_att_trace(long long* out, int* counts) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_att_trace, sizeof(long long) * 8 * 512);
+    cudaMemcpyFromSymbol(counts, g_att_trace_n, sizeof(int) * 8);
+    int zero[8] = {0};
+    cudaMemcpyToSymbol(g_att_trace_n, zero, sizeof(zero));
+    return 0;
+}
+#endif
+
 int attention_read_status(uint32_t* out) {
     uint32_t zero = 0;
     EMMY_CUDA(cudaDeviceSynchronize());
@@ -432,10 +986,8 @@ static int launch_attention(const void* Q, const void* K, const void* V, void* c
         else rc = make_tensor_map_3d(&out.m[d], O[d < n_dst ? d : 0], (uint64_t)units, (uint64_t)seq_q, D, kTileQ, 64);
     }
     if (rc != EMMYB200_OK) return rc;
-    auto kernel = attention_fwd_kernel<D, BF16>;
-    EMMY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
     AttParams p;
-    p.n_dst = n_dst; p.causal = causal ? 1 : 0; p.seq_q = (int)seq_q; p.seq_k = (int)seq_k;
+    p.n_dst = n_dst; p.causal = causal ? 1 : 0; p.units = (int)units; p.seq_q = (int)seq_q; p.seq_k = (int)seq_k;
     p.mc_base = multicast ? (unsigned long long)(uintptr_t)O[0] : 0ull;
     p.q_tiles = (int)((seq_q + kTileQ - 1) / kTileQ);
     p.scale_log2 = scale * 1.4426950408889634f;
@@ -443,6 +995,19 @@ static int launch_attention(const void* Q, const void* K, const void* V, void* c
     EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_att_status));
     const int64_t ctas = units * p.q_tiles;
     if (ctas >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: %lld query tiles exceed the grid limit", (long long)ctas);
+    const char* which = getenv("EMMYB200_ATT_KERNEL");              // experiment hook while the two forms are compared
+    if (which != nullptr && which[0] == 'p') {
+        using P = PairSmem<D>;
+        auto pair_kernel = attention_fwd_pair_kernel<D, BF16>;
+        EMMY_CUDA(cudaFuncSetAttribute(pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kTotal));
+        const int64_t q_pairs = (p.q_tiles + 1) / 2;
+        const int64_t deals = causal ? units * ((q_pairs + 1) / 2) : units * q_pairs;
+        const int grid = (int)(deals < sm_count() ? deals : sm_count());
+        pair_kernel<<<grid, kPairThreads, P::kTotal, stream>>>(mq, mk, mv, out, p);
+        return launch_status("attention_fwd_pair_kernel");
+    }
+    auto kernel = attention_fwd_kernel<D, BF16>;
+    EMMY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
     kernel<<<(unsigned)ctas, kAttThreads, S::kTotal, stream>>>(mq, mk, mv, out, p);
     return launch_status("attention_fwd_kernel");
 }
