@@ -25,6 +25,8 @@
 #include <math_constants.h>
 #include <stdlib.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -445,7 +447,9 @@ __device__ int g_att_trace_n[8];
 
 constexpr int kPairThreads = 512;
 constexpr int kKvStages = 4;
-constexpr int kPolyOf8 = 4;         // of every eight pairs of exponentials, how many are computed on the FMA pipe
+constexpr int kPolyOf8 = 4;         // of every eight pairs of exponentials, how many are computed on the FMA pipe (bf16)
+constexpr int kPolyOf8F16 = 2;      // the same for f16, whose pairs are converted on the transcendental unit in any case
+constexpr float kTruncBias = 0.0028150156f;      // log2(1 + 2^-9): centres the error of truncating an fp32 to bf16
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
@@ -786,28 +790,38 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 }
                 m_run = m_new;
                 if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
-                // p = 2^(c s - m). The transcendental unit makes 16 exponentials a clock for the whole SM, which is as long
-                // as the tensor cores need for the tile's two products; so kPolyOf8 of every eight pairs go through the
-                // FMA pipe instead (round to the nearest integer n by a magic-number add, a cubic for 2^f on [-1/2, 1/2],
-                // relative error 7.5e-5 -- below the rounding of P to 16 bits --, n added into the exponent field).
-                // Tiles with masked (infinite) scores take the transcendental unit for everything.
-                const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_run, -m_run);
+                // p = 2^(c s - m). The transcendental unit makes 16 results a clock for the whole SM -- and the conversion
+                // of a pair of floats to 16 bits runs on that same unit --, which is as long as the tensor cores need for
+                // the tile's two products. So (bf16) kPolyOf8 of every eight pairs of exponentials go through the FMA pipe
+                // (exp2_poly2), and no pair is converted: P is the upper half of the fp32 bit pattern, one byte-permute per
+                // pair. Truncation loses half a 16-bit ulp on average, so every exponent is taken kTruncBias higher
+                // (a factor 1 + 2^-9) and the row sum is scaled back once at the end. Tiles with masked (infinite)
+                // scores take the transcendental unit for everything.
+                const float shift = BF16 ? kTruncBias - m_run : -m_run;
+                const float2 c2 = make_float2(c, c), nm2 = make_float2(shift, shift);
                 float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+                auto emit = [&](auto poly_of_8) {
+                    constexpr int kPoly = decltype(poly_of_8)::value;
 #pragma unroll
-                for (int ch = 0; ch < kTileK / 32; ++ch) {
-                    uint32_t pk[16];
+                    for (int ch = 0; ch < kTileK / 32; ++ch) {
+                        uint32_t pk[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int e0 = ch * 32 + 2 * i;
-                        const float2 y = fma2(make_float2(__uint_as_float(r[e0]), __uint_as_float(r[e0 + 1])), c2, nm2);
-                        float2 e;
-                        if ((i & 7) < kPolyOf8 && !ragged) e = exp2_poly2(y);
-                        else e = make_float2(ptx::ex2_approx(y.x), ptx::ex2_approx(y.y));
-                        sum2[i & 1] = add2(sum2[i & 1], e);
-                        pk[i] = pack_pair<BF16>(e.x, e.y);
+                        for (int i = 0; i < 16; ++i) {
+                            const int e0 = ch * 32 + 2 * i;
+                            const float2 y = fma2(make_float2(__uint_as_float(r[e0]), __uint_as_float(r[e0 + 1])), c2, nm2);
+                            float2 e;
+                            if ((i & 7) < kPoly) e = exp2_poly2(y);
+                            else e = make_float2(ptx::ex2_approx(y.x), ptx::ex2_approx(y.y));
+                            sum2[i & 1] = add2(sum2[i & 1], e);
+                            if constexpr (BF16) pk[i] = __byte_perm(__float_as_uint(e.x), __float_as_uint(e.y), 0x7632);
+                            else pk[i] = pack_pair<false>(e.x, e.y);
+                        }
+                        ptx::tmem_st_32x32b_x16(s_row + ch * 16, pk);
                     }
-                    ptx::tmem_st_32x32b_x16(s_row + ch * 16, pk);
-                }
+                };
+                // (the choice is made per warp: the tensor-memory stores inside are warp-wide instructions)
+                if (__any_sync(0xffffffffu, ragged)) emit(std::integral_constant<int, 0>{});
+                else emit(std::integral_constant<int, BF16 ? kPolyOf8 : kPolyOf8F16>{});
                 const float2 tot = add2(sum2[0], sum2[1]);
                 l_run += tot.x + tot.y;
                 if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
@@ -818,7 +832,7 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
             }
             if (!ok) break;
-            lsum[g * 128 + row] = l_run;
+            lsum[g * 128 + row] = BF16 ? l_run * (1.0f / 1.001953125f) : l_run;      // the exponentials carried a factor 1 + 2^-9
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar(L_READY + 4 * g + wq));
         }

@@ -106,11 +106,25 @@ __device__ __forceinline__ float2 sincos2(float2 x) {         // |x| <= 65536
 __device__ __forceinline__ float2 sin2(float2 x) { return sincos2<false>(x); }
 __device__ __forceinline__ float2 cos2(float2 x) { return sincos2<true>(x); }
 
+// |tanh| of both lanes from a = |x| and e = e^x, as emmy_tanh_mag_from_exp: the odd polynomial below 0.65, else
+// |e^2 - 1| / (e^2 + 1), each a fused multiply-add -- the fused expression's exponential serves tanh too.
+__device__ __forceinline__ float2 tanh_mag_from_exp2(float2 a, float2 e) {
+    const float2 z = mul2(a, a);
+    float2 t = fma2(f2(EMMY_TANHT_4), z, f2(EMMY_TANHT_3));
+    t = fma2(t, z, f2(EMMY_TANHT_2));
+    t = fma2(t, z, f2(EMMY_TANHT_1));
+    t = fma2(t, z, f2(EMMY_TANHT_0));
+    const float2 small = fma2(mul2(a, z), t, a);
+    const float2 num = fma2(e, e, f2(-1.0f)), den = fma2(e, e, f2(1.0f));
+    const float2 big = mul2(make_float2(fabsf(num.x), fabsf(num.y)), make_float2(emmy_rcp(den.x), emmy_rcp(den.y)));
+    return make_float2(a.x < EMMY_TANH_SMALL ? small.x : big.x, a.y < EMMY_TANH_SMALL ? small.y : big.y);
+}
+
 // exp(x) + sin(x) * tanh(x) on a pair, product and sum rounded separately as in the scalar form. sin and
 // tanh are both odd, so their product is taken on |x|: the two sign transfers cancel exactly.
 __device__ __forceinline__ float2 exp_sin_tanh2(float2 x) {
     const float2 a = make_float2(fabsf(x.x), fabsf(x.y));
-    const float2 e = exp_core2(x), s = sincos2<false, true>(a), t = tanh_mag2(a);
+    const float2 e = exp_core2(x), s = sincos2<false, true>(a), t = tanh_mag_from_exp2(a, e);
     // scalar product and sum: a packed mul feeding a packed add was observed to be fused into one fma
     return make_float2(__fadd_rn(e.x, __fmul_rn(s.x, t.x)), __fadd_rn(e.y, __fmul_rn(s.y, t.y)));
 }
@@ -119,7 +133,7 @@ __device__ __forceinline__ float2 exp_sin_tanh2(float2 x) {
 template <int OP> struct PackedOp { static constexpr bool kHas = false; };
 template <> struct PackedOp<EMMYB200_OP_EXP_SIN_TANH> {
     static constexpr bool kHas = true;
-    static constexpr float kBound = 86.0f;
+    static constexpr float kBound = EMMY_FUSED_MAX;
     static __device__ __forceinline__ float2 apply(float2 x) { return exp_sin_tanh2(x); }
 };
 template <> struct PackedOp<EMMYB200_OP_EXP> {
