@@ -48,6 +48,7 @@ struct AttSmem {
 };
 
 constexpr int kMaxDst = 8;
+constexpr float kTruncBiasLog2 = 0.0028150156f;      // log2(1 + 2^-9): centres the error of truncating an fp32 to bf16
 
 struct AttOutMaps {
     CUtensorMap m[kMaxDst];
@@ -299,7 +300,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             m_run = m_new;
             // p = 2^(c s - m): packed fma for the exponent, MUFU ex2 (moving part of the exponentials to a
             // polynomial on the FMA pipe was measured slower at every fraction tried).
-            const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_run, -m_run);
+            // (bf16: P is the upper half of the fp32 pattern -- one byte-permute per pair instead of a conversion, which
+            // would run on the transcendental unit like the exponentials; the truncation's mean loss of half a 16-bit
+            // ulp is made up by taking every exponent kTruncBiasLog2 higher and scaling the row sum back at the end)
+            const float shift = BF16 ? kTruncBiasLog2 - m_run : -m_run;
+            const float2 c2 = make_float2(c, c), nm2 = make_float2(shift, shift);
             float2 sum2[4] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
             for (int ch = 0; ch < kTileK / 64; ++ch) {
@@ -310,7 +315,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     const float2 y = fma2(sv, c2, nm2);
                     const float2 e = make_float2(ptx::ex2_approx(y.x), ptx::ex2_approx(y.y));
                     sum2[i & 3] = add2(sum2[i & 3], e);
-                    w[i] = pack_pair<BF16>(e.x, e.y);
+                    if constexpr (BF16) w[i] = __byte_perm(__float_as_uint(e.x), __float_as_uint(e.y), 0x7632);
+                    else w[i] = pack_pair<false>(e.x, e.y);
                 }
                 ptx::tmem_st_32x32b_x16(p_row + ch * 16, w);
             }
@@ -333,7 +339,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             // staged there in the same swizzled 128 x 64 halves and leaves through TMA stores (which drop the
             // rows beyond seq_q), one per destination.
             ptx::tc_fence_after_sync();
-            const float inv = 1.0f / l_run;
+            const float inv = (BF16 ? 1.001953125f : 1.0f) / l_run;        // the bf16 exponentials carried a factor 1 + 2^-9
             const uint32_t row_smem = q_smem + half * (kTileQ * 128) + row_in_tile * 128;
             if constexpr (D == 128) {
 #pragma unroll 1
@@ -439,17 +445,18 @@ __device__ long long g_att_trace[8][512];
 __device__ int g_att_trace_n[8];
 #define ATT_STAMP(role)                                                          \
     do {                                                                         \
-        if (blockIdx.x == 0 && g_att_trace_n[role] < 512) g_att_trace[role][g_att_trace_n[role]++] = clock64(); \
+        if (blockIdx.x == 0 && trace_n < 512) g_att_trace[role][trace_n++] = clock64(); \
     } while (0)
+#define ATT_STAMP_DONE(role) do { if (blockIdx.x == 0) g_att_trace_n[role] = trace_n; } while (0)
 #else
 #define ATT_STAMP(role) do { } while (0)
+#define ATT_STAMP_DONE(role) do { } while (0)
 #endif
 
 constexpr int kPairThreads = 512;
 constexpr int kKvStages = 4;
-constexpr int kPolyOf8 = 4;         // of every eight pairs of exponentials, how many are computed on the FMA pipe (bf16)
+constexpr int kPolyOf8 = 2;         // of every eight pairs of exponentials, how many are computed on the FMA pipe (bf16)
 constexpr int kPolyOf8F16 = 2;      // the same for f16, whose pairs are converted on the transcendental unit in any case
-constexpr float kTruncBias = 0.0028150156f;      // log2(1 + 2^-9): centres the error of truncating an fp32 to bf16
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
@@ -548,12 +555,11 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     const uint32_t bar_base = smem_base + S::kBarOffset;
     auto bar = [&](int idx) { return bar_base + 8u * idx; };
     // barrier indices
-    constexpr int Q_FULL = 0, Q_EMPTY = 2, KV_FULL = 4, KV_EMPTY = 8, S_FULL = 12, P_FULL = 14, O_READY = 16, O_FULL = 18, O_FREE = 20,
-                  CORR_READY = 22, L_READY = 30, STAGE_READY = 38, STAGE_FREE = 39, N_BARS = 40;
+    constexpr int Q_FULL = 0, Q_EMPTY = 2, KV_FULL = 4, KV_EMPTY = 8, S_FULL = 12, P_FULL = 14, O_FULL = 16, O_FREE = 18,
+                  L_READY = 20, STAGE_READY = 28, STAGE_FREE = 29, N_BARS = 30;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + S::kBarOffset + 8 * N_BARS);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    float* corr = reinterpret_cast<float*>(smem_gen + S::kFloatOffset);        // [2][128] rescale factors
-    float* lsum = corr + 256;                                                  // [2][128] final row sums
+    float* lsum = reinterpret_cast<float*>(smem_gen + S::kFloatOffset);        // [2][128] final row sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const WaitCtx wctx{abort_flag, p.status, p.wait_limit_ns};
@@ -561,9 +567,9 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(bar(Q_FULL + i), 1); ptx::mbar_init(bar(Q_EMPTY + i), 1); ptx::mbar_init(bar(S_FULL + i), 1);
-            ptx::mbar_init(bar(P_FULL + i), 4); ptx::mbar_init(bar(O_READY + i), 4); ptx::mbar_init(bar(O_FULL + i), 1);
+            ptx::mbar_init(bar(P_FULL + i), 4); ptx::mbar_init(bar(O_FULL + i), 1);
             ptx::mbar_init(bar(O_FREE + i), 4);
-            for (int w = 0; w < 4; ++w) { ptx::mbar_init(bar(CORR_READY + 4 * i + w), 1); ptx::mbar_init(bar(L_READY + 4 * i + w), 1); }
+            for (int w = 0; w < 4; ++w) ptx::mbar_init(bar(L_READY + 4 * i + w), 1);
         }
         for (int s = 0; s < kKvStages; ++s) { ptx::mbar_init(bar(KV_FULL + s), 1); ptx::mbar_init(bar(KV_EMPTY + s), 1); }
         ptx::mbar_init(bar(STAGE_READY), 4); ptx::mbar_init(bar(STAGE_FREE), p.mc_base != 0 ? 4 : 1);
@@ -628,8 +634,9 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         if (lane == 0) {
             constexpr uint32_t idesc_s = ptx::mma_idesc_f16(BF16, false, false, kTileQ, kTileK);
             constexpr uint32_t idesc_o = ptx::mma_idesc_f16(BF16, false, true, kTileQ, D);
-            uint32_t kvr = 0, cq[2] = {0, 0}, cp[2] = {0, 0}, cor[2] = {0, 0}, cof[2] = {0, 0};
+            uint32_t kvr = 0, cq[2] = {0, 0}, cp[2] = {0, 0}, cof[2] = {0, 0};
             bool ok = true;
+            [[maybe_unused]] int trace_n = 0;
             PairItem w;
             auto kv_wait = [&](uint32_t r, uint32_t code) {
                 return bounded_wait(wctx, bar(KV_FULL + (r & (kKvStages - 1))), (r / kKvStages) & 1, code | (r & 0xffff));
@@ -676,12 +683,9 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                         if (!(ok = bounded_wait(wctx, bar(P_FULL + i), cp[i] & 1, 0x03050000u | (j & 0xffff)))) break;
                         ATT_STAMP(0);
                         ++cp[i];
-                        if (j == 0) {
+                        if (j == 0) {                               // the previous item's O_i has been read out
                             if (!(ok = bounded_wait(wctx, bar(O_FREE + i), (cof[i] & 1) ^ 1, 0x03060000u | i))) break;
                             ++cof[i];
-                        } else {
-                            if (!(ok = bounded_wait(wctx, bar(O_READY + i), cor[i] & 1, 0x03070000u | (j & 0xffff)))) break;
-                            ++cor[i];
                         }
                         if (!v_waited) {
                             if (!(ok = kv_wait(rv, 0x03080000u))) break;
@@ -708,6 +712,7 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 }
                 kvr += 2 * nmax;
             }
+            ATT_STAMP_DONE(0);
         }
         __syncwarp();
     } else if (warp < 4) {
@@ -723,11 +728,27 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         const float fill = c > 0.0f ? -CUDART_INF_F : CUDART_INF_F;
         uint32_t cs = 0;
         bool ok = true;
+        [[maybe_unused]] int trace_n = 0;
         PairItem w;
+        // O_g row *= f, eight columns at a time (few registers: it runs beside a live row of scores); whole warps only
+        auto rescale_o = [&](float f) {
+            ptx::tc_fence_after_sync();
+            const uint32_t o_row = tmem_base + lane_base + kColO + g * kColOStride;
+#pragma unroll 1
+            for (int col = 0; col < D; col += 8) {
+                uint32_t o[8];
+                ptx::tmem_ld_32x32b_x8(o_row + col, o);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+                ptx::tmem_st_32x32b_x8(o_row + col, o);
+            }
+            ptx::tmem_st_wait();
+        };
         for (int it = 0; ok && pair_item(p, it, w); ++it) {
             if (w.n[g] == 0) continue;
             const int q_row = w.row0 + g * kTileQ + row;
-            float m_run = -CUDART_INF_F, l_run = 0.0f;
+            float m_run = -CUDART_INF_F, m_next = -CUDART_INF_F, l_run = 0.0f, f_pend = 1.0f;
             for (int j = 0; j < w.n[g] && ok; ++j) {
                 if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
                 ok = __all_sync(0xffffffffu, bounded_wait(wctx, bar(S_FULL + g), cs & 1, 0x030a0000u | (j & 0xffff)));
@@ -738,6 +759,12 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 int valid = p.seq_k - j * kTileK;
                 if (p.causal) valid = min(valid, q_row - j * kTileK + 1);
                 const bool ragged = valid < kTileK;
+                // S_i(j) is ready, so O_i holds every product up to tile j - 1: this is where a raise of the reference
+                // decided at the previous tile is applied to the accumulator (rare) and to the running sum.
+                if (j > 0) {
+                    if (__any_sync(0xffffffffu, f_pend != 1.0f)) rescale_o(f_pend);
+                    l_run *= f_pend;
+                }
                 // the whole row of scores into registers: four loads in flight, one wait
                 uint32_t r[kTileK];
 #pragma unroll
@@ -749,23 +776,25 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                     for (int i = 0; i < kTileK; ++i)
                         if (i >= valid) r[i] = __float_as_uint(fill);
                 }
-                // row extremum: four chains of three-input max / min
-                float ext[4];
+                // c * (row extremum): four chains of three-input max / min
+                auto row_max = [&]() -> float {
+                    float ext[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) ext[i] = __uint_as_float(r[i]);
-                if (c > 0.0f) {
+                    for (int i = 0; i < 4; ++i) ext[i] = __uint_as_float(r[i]);
+                    if (c > 0.0f) {
 #pragma unroll
-                    for (int i = 4; i + 7 < kTileK + 4; i += 8) {
+                        for (int i = 4; i < kTileK; i += 8) {
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int a0 = i + 2 * q, a1 = a0 + 1;
-                            if (a1 < kTileK) ext[q] = max3(ext[q], __uint_as_float(r[a0]), __uint_as_float(r[a1]));
-                            else if (a0 < kTileK) ext[q] = fmaxf(ext[q], __uint_as_float(r[a0]));
+                            for (int q = 0; q < 4; ++q) {
+                                const int a0 = i + 2 * q, a1 = a0 + 1;
+                                if (a1 < kTileK) ext[q] = max3(ext[q], __uint_as_float(r[a0]), __uint_as_float(r[a1]));
+                                else if (a0 < kTileK) ext[q] = fmaxf(ext[q], __uint_as_float(r[a0]));
+                            }
                         }
+                        return fmaxf(fmaxf(ext[0], ext[1]), fmaxf(ext[2], ext[3])) * c;
                     }
-                } else {
 #pragma unroll
-                    for (int i = 4; i + 7 < kTileK + 4; i += 8) {
+                    for (int i = 4; i < kTileK; i += 8) {
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             const int a0 = i + 2 * q, a1 = a0 + 1;
@@ -773,35 +802,28 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                             else if (a0 < kTileK) ext[q] = fminf(ext[q], __uint_as_float(r[a0]));
                         }
                     }
-                }
-                const float e01 = c > 0.0f ? fmaxf(ext[0], ext[1]) : fminf(ext[0], ext[1]);
-                const float e23 = c > 0.0f ? fmaxf(ext[2], ext[3]) : fminf(ext[2], ext[3]);
-                const float m_tile = (c > 0.0f ? fmaxf(e01, e23) : fminf(e01, e23)) * c;
-                // Raise the running max only when it would grow by more than 8: exponentials then stay below 2^8, and the
-                // accumulator needs rescaling rarely.
-                const bool raise = m_tile > m_run + 8.0f;
-                const float m_new = raise ? m_tile : m_run;
-                if (j > 0) {
-                    const float f = raise ? ptx::ex2_approx(m_run - m_new) : 1.0f;
-                    l_run *= f;
-                    corr[g * 128 + row] = f;
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(bar(CORR_READY + 4 * g + wq));
-                }
-                m_run = m_new;
+                    return fminf(fminf(ext[0], ext[1]), fminf(ext[2], ext[3])) * c;
+                };
+                // The exponentials are taken against the reference m_run that was fixed BEFORE this tile (the first tile's
+                // own maximum, afterwards raised between tiles only): floating point does not care how far below or above
+                // 1 the values sit, so this tile's maximum is needed only to decide the next reference and to guard
+                // against overflow -- it is computed beside the exponentials, off the path from S to P.
+                float m_tile = 0.0f;
+                if (j == 0) m_run = m_tile = row_max();
                 if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
                 // p = 2^(c s - m). The transcendental unit makes 16 results a clock for the whole SM -- and the conversion
                 // of a pair of floats to 16 bits runs on that same unit --, which is as long as the tensor cores need for
                 // the tile's two products. So (bf16) kPolyOf8 of every eight pairs of exponentials go through the FMA pipe
                 // (exp2_poly2), and no pair is converted: P is the upper half of the fp32 bit pattern, one byte-permute per
-                // pair. Truncation loses half a 16-bit ulp on average, so every exponent is taken kTruncBias higher
+                // pair. Truncation loses half a 16-bit ulp on average, so every exponent is taken kTruncBiasLog2 higher
                 // (a factor 1 + 2^-9) and the row sum is scaled back once at the end. Tiles with masked (infinite)
                 // scores take the transcendental unit for everything.
-                const float shift = BF16 ? kTruncBias - m_run : -m_run;
-                const float2 c2 = make_float2(c, c), nm2 = make_float2(shift, shift);
-                float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+                float2 sum2[2];
                 auto emit = [&](auto poly_of_8) {
                     constexpr int kPoly = decltype(poly_of_8)::value;
+                    const float shift = BF16 ? kTruncBiasLog2 - m_run : -m_run;
+                    const float2 c2 = make_float2(c, c), nm2 = make_float2(shift, shift);
+                    sum2[0] = sum2[1] = make_float2(0.0f, 0.0f);
 #pragma unroll
                     for (int ch = 0; ch < kTileK / 32; ++ch) {
                         uint32_t pk[16];
@@ -822,20 +844,41 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 // (the choice is made per warp: the tensor-memory stores inside are warp-wide instructions)
                 if (__any_sync(0xffffffffu, ragged)) emit(std::integral_constant<int, 0>{});
                 else emit(std::integral_constant<int, BF16 ? kPolyOf8 : kPolyOf8F16>{});
+                if (j > 0) {
+                    m_tile = row_max();
+                    // Scores more than 2^64 above the reference could overflow: raise the reference now, bring the
+                    // accumulator and the sum along, and take this tile's exponentials again (never on ordinary data).
+                    const bool over = m_tile > m_run + 64.0f;
+                    if (__any_sync(0xffffffffu, over)) {
+                        const float f = over ? ptx::ex2_approx(m_run - m_tile) : 1.0f;
+                        rescale_o(f);
+                        l_run *= f;
+                        if (over) m_run = m_tile;
+                        emit(std::integral_constant<int, 0>{});
+                    }
+                }
                 const float2 tot = add2(sum2[0], sum2[1]);
                 l_run += tot.x + tot.y;
+                // The reference for the next tile: raised only when this tile's maximum exceeds it by more than 2^8.
+                {
+                    const bool raise = m_tile > m_run + 8.0f;
+                    f_pend = raise ? ptx::ex2_approx(m_run - m_tile) : 1.0f;
+                    m_next = raise ? m_tile : m_run;
+                }
                 if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(bar(P_FULL + g));
                 if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
+                m_run = m_next;
             }
             if (!ok) break;
             lsum[g * 128 + row] = BF16 ? l_run * (1.0f / 1.001953125f) : l_run;      // the exponentials carried a factor 1 + 2^-9
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar(L_READY + 4 * g + wq));
         }
+        if (wq == 0 && lane == 0) ATT_STAMP_DONE(1 + g);
     } else {
         // ---- correction and output ---------------------------------------------------------------------------------------
         ptx::setmaxnreg_dec<kRegsCorrection>();
@@ -843,42 +886,12 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         const int row = wq * 32 + lane;
         const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
         const bool issuer = threadIdx.x == 12 * 32;
-        uint32_t cc[2] = {0, 0}, cl[2] = {0, 0}, cfull[2] = {0, 0}, cstage = 0;
+        uint32_t cl[2] = {0, 0}, cfull[2] = {0, 0}, cstage = 0;
         bool ok = true;
+        [[maybe_unused]] int trace_n = 0;
         PairItem w;
         for (int it = 0; ok && pair_item(p, it, w); ++it) {
             if (w.n[0] == 0) continue;
-            const int nmax = max(w.n[0], w.n[1]);
-            for (int j = 1; j < nmax && ok; ++j) {
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    if (j >= w.n[i] || !ok) continue;
-                    if (issuer) ATT_STAMP(3);
-                    ok = __all_sync(0xffffffffu, bounded_wait(wctx, bar(CORR_READY + 4 * i + wq), cc[i] & 1, 0x030b0000u | (j & 0xffff)));
-                    if (!ok) break;
-                    if (issuer) ATT_STAMP(3);
-                    ++cc[i];
-                    const float f = corr[i * 128 + row];
-                    if (__any_sync(0xffffffffu, f != 1.0f)) {
-                        ptx::tc_fence_after_sync();
-                        const uint32_t o_row = tmem_base + lane_base + kColO + i * kColOStride;
-#pragma unroll 1
-                        for (int col = 0; col < D; col += 32) {
-                            uint32_t o[32];
-                            ptx::tmem_ld_32x32b_x32(o_row + col, o);
-                            ptx::tmem_ld_wait();
-#pragma unroll
-                            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
-                            ptx::tmem_st_32x32b_x16(o_row + col, *reinterpret_cast<uint32_t(*)[16]>(&o[0]));
-                            ptx::tmem_st_32x32b_x16(o_row + col + 16, *reinterpret_cast<uint32_t(*)[16]>(&o[16]));
-                        }
-                        ptx::tmem_st_wait();
-                    }
-                    ptx::tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(bar(O_READY + i));
-                }
-            }
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 if (w.n[i] == 0 || !ok) continue;
@@ -953,6 +966,7 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             }
         }
         if (issuer) ptx::tma_store_wait<0>();
+        if (issuer) ATT_STAMP_DONE(3);
         if (p.mc_base != 0) __threadfence_system();
     }
 

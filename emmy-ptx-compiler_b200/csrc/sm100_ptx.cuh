@@ -44,6 +44,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// A test without waiting.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Makes generic-proxy writes to shared memory visible to the async proxy (TMA, tcgen05.mma).
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -287,21 +300,30 @@ struct WaitCtx {
 // The limit the next launches get (host side, process-wide).
 uint64_t wait_limit_ns();
 
-__device__ __forceinline__ bool bounded_wait(const WaitCtx& ctx, uint32_t bar, uint32_t parity, uint32_t code) {
+// The polling loop behind the immediate test.
+__device__ __forceinline__ bool bounded_wait_slow(volatile uint32_t* abort_flag, uint32_t* status_word, uint64_t limit_ns, uint32_t bar,
+                                               uint32_t parity, uint32_t code) {
     uint64_t t0 = 0;
     for (uint32_t spin = 1;; ++spin) {
         if (ptx::mbar_try_wait(bar, parity)) return true;
         if ((spin & 15u) == 0) {
-            if (*ctx.abort_flag) return false;
+            if (*abort_flag) return false;
             uint64_t now = ptx::global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > ctx.limit_ns) {
-                atomicCAS(ctx.status_word, 0u, code);
-                *ctx.abort_flag = 1;
+            else if (now - t0 > limit_ns) {
+                atomicCAS(status_word, 0u, code);
+                *abort_flag = 1;
                 return false;
             }
         }
     }
+}
+
+// One immediate test of the barrier (the common case in a running pipeline: the phase has long completed), then the
+// polling loop.
+__device__ __forceinline__ bool bounded_wait(const WaitCtx& ctx, uint32_t bar, uint32_t parity, uint32_t code) {
+    if (ptx::mbar_test_wait(bar, parity)) return true;
+    return bounded_wait_slow(ctx.abort_flag, ctx.status_word, ctx.limit_ns, bar, parity, code);
 }
 
 // ---- TMA descriptors (host) -------------------------------------------------------------------
