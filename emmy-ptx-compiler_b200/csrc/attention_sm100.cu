@@ -23,9 +23,6 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math_constants.h>
-#include <stdlib.h>
-
-#include <type_traits>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -427,37 +424,24 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 // columns) and walks the key tiles once for both.
 //   warp 0     TMA: the two Q tiles, then K_j / V_j through a four-stage ring (32 KiB each at d = 128)
 //   warp 1     MMA issue, in the order  S0(0) S1(0) | O0+=P0 V(j)  S0(j+1)  O1+=P1 V(j)  S1(j+1) | ...  so that
-//              while one tile's probabilities are being made the tensor pipe works on the other tile
-//   warps 4-7, 8-11   softmax of tile 0 / tile 1, one thread per query row: row max, exponentials and row sum need no
-//              exchange between threads; S is read from tensor memory twice (maximum, then exponentials) in 32-column
-//              pieces so that a row's 128 scores never have to be live at once; P (16-bit pairs) overwrites S
-//   warps 12-15  correction: rescales O_i in tensor memory when a row's running maximum was raised (rare after the
-//              first tiles: it is raised only when it grows by more than 2^8), and at the end normalises O_i by the
-//              row sums, stages it in shared memory and stores it (TMA, or multimem.st for a multicast destination)
-//              while the MMA warp is already working on the next pair of tiles.
+//              while one tile's probabilities are being made the tensor pipe works on the other tile; descriptor
+//              words are built once and a k-step costs the thread one add
+//   warps 4-7, 8-11   softmax of tile 0 / tile 1, one thread per query row with the whole row of scores in registers
+//              (setmaxnreg moves registers to these warps): no exchange between threads anywhere. The exponentials
+//              are taken against a reference maximum fixed BEFORE the tile arrives (the first tile's own maximum,
+//              raised between tiles when a later maximum exceeds it by more than 2^8): floating point does not care
+//              how far from 1 the values sit, so the tile's own maximum is only needed for the next reference and is
+//              computed after P has been handed to the MMA warp. A tile whose sum shows scores far above the
+//              reference (2^64: never on ordinary data) is done again against a raised reference. The thread
+//              rescales its own row of O in tensor memory on the rare raise. P (16-bit pairs) overwrites S.
+//   warps 12-15  output: normalise O_i by the row sums, stage it in shared memory and store it (TMA, or multimem.st
+//              for a multicast destination) while the MMA warp is already working on the next pair of tiles.
 // Work items (unit, pair of query tiles) are dealt round-robin. With the causal flag a pair's cost grows with its
 // position, so a CTA takes pairs two at a time, the k-th longest together with the k-th shortest of the same unit:
 // every such couple costs the same, and the static deal stays balanced. Every wait is bounded; the groups meet only
 // through mbarriers (no bar.sync inside the role loops), so a wait that gives up cannot strand another warp.
-#ifdef EMMY_ATT_TRACE
-// Development aid (not built by default): clock stamps of block 0's roles, [role][event index].
-__device__ long long g_att_trace[8][512];
-__device__ int g_att_trace_n[8];
-#define ATT_STAMP(role)                                                          \
-    do {                                                                         \
-        if (blockIdx.x == 0 && trace_n < 512) g_att_trace[role][trace_n++] = clock64(); \
-    } while (0)
-#define ATT_STAMP_DONE(role) do { if (blockIdx.x == 0) g_att_trace_n[role] = trace_n; } while (0)
-#else
-#define ATT_STAMP(role) do { } while (0)
-#define ATT_STAMP_DONE(role) do { } while (0)
-#endif
-
 constexpr int kPairThreads = 512;
 constexpr int kKvStages = 4;
-constexpr int kPolyOf8 = 2;         // of every eight pairs of exponentials, how many are computed on the FMA pipe (bf16)
-constexpr int kPolyOf8F16 = 2;      // the same for f16, whose pairs are converted on the transcendental unit in any case
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -468,27 +452,6 @@ __device__ __forceinline__ float min3(float a, float b, float c) {
     asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
-__device__ __forceinline__ float2 sub2(float2 a, float2 b) {
-    uint64_t d;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(as_u64(a)), "l"(as_u64(b)));
-    return as_f2(d);
-}
-// 2^y for a pair, y <= 8 or so, without the transcendental unit: y clamped at -125 (the result then underflows
-// harmlessly small), n = round(y) taken from the low mantissa bits of y + 1.5 * 2^23, f = y - n in [-1/2, 1/2],
-// 2^f by a cubic (minimax in relative error: 7.5e-5), and n added into the exponent field of the result.
-__device__ __forceinline__ float2 exp2_poly2(float2 y) {
-    const float2 magic = make_float2(12582912.0f, 12582912.0f);
-    y.x = fmaxf(y.x, -125.0f);
-    y.y = fmaxf(y.y, -125.0f);
-    const float2 t = add2(y, magic);
-    const float2 f = sub2(y, sub2(t, magic));
-    float2 q = fma2(make_float2(0.055171654f, 0.055171654f), f, make_float2(0.24261113f, 0.24261113f));
-    q = fma2(q, f, make_float2(0.69326097f, 0.69326097f));
-    q = fma2(q, f, make_float2(0.99992806f, 0.99992806f));
-    return make_float2(__uint_as_float(__float_as_uint(q.x) + (__float_as_uint(t.x) << 23)),
-                       __uint_as_float(__float_as_uint(q.y) + (__float_as_uint(t.y) << 23)));
-}
-
 template <int D>
 struct PairSmem {
     static constexpr int kQBytes = kTileQ * D * 2;
@@ -636,27 +599,30 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             constexpr uint32_t idesc_o = ptx::mma_idesc_f16(BF16, false, true, kTileQ, D);
             uint32_t kvr = 0, cq[2] = {0, 0}, cp[2] = {0, 0}, cof[2] = {0, 0};
             bool ok = true;
-            [[maybe_unused]] int trace_n = 0;
             PairItem w;
             auto kv_wait = [&](uint32_t r, uint32_t code) {
                 return bounded_wait(wctx, bar(KV_FULL + (r & (kKvStages - 1))), (r / kKvStages) & 1, code | (r & 0xffff));
             };
+            // Descriptor words built once: per k-step the issuing thread adds a constant to a low word.
+            constexpr uint32_t kDescHi = ptx::smem_desc_sw128_hi(1024);
+            const uint32_t q_lo0 = ptx::smem_desc_sw128_lo(q_smem(0), 16), q_lo1 = ptx::smem_desc_sw128_lo(q_smem(1), 16);
+            const uint32_t k_lo = ptx::smem_desc_sw128_lo(kv_smem(0), 16), v_lo = ptx::smem_desc_sw128_lo(kv_smem(0), kTileK * 128);
             auto issue_s = [&](int i, uint32_t r) {                      // S_i = Q_i K^T with K in ring slot r
-                const uint32_t k_base = kv_smem(r & (kKvStages - 1));
+                const uint32_t kb = k_lo + (r & (kKvStages - 1)) * (S::kKvBytes >> 4), qb = i ? q_lo1 : q_lo0;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk / 4) * (kTileQ * 128) + (kk % 4) * 32;
-                    ptx::mma_ss(tmem_base + i * kColS, ptx::smem_desc_sw128(q_smem(i) + off, 16, 1024),
-                                ptx::smem_desc_sw128(k_base + off, 16, 1024), idesc_s, kk != 0);
+                    constexpr uint32_t kChunk = (kTileQ * 128) >> 4;
+                    const uint32_t off = (kk / 4) * kChunk + (kk % 4) * 2;          // in 16-byte units
+                    ptx::mma_ss_words(tmem_base + i * kColS, qb + off, kb + off, kDescHi, idesc_s, kk != 0);
                 }
                 ptx::mma_commit(bar(S_FULL + i));
             };
             auto issue_pv = [&](int i, uint32_t r, bool first) {         // O_i (+)= P_i V with V in ring slot r
-                const uint32_t v_base = kv_smem(r & (kKvStages - 1));
+                const uint32_t vb = v_lo + (r & (kKvStages - 1)) * (S::kKvBytes >> 4);
 #pragma unroll
                 for (int kk = 0; kk < kTileK / 16; ++kk)
-                    ptx::mma_ts(tmem_base + kColO + i * kColOStride, tmem_base + i * kColS + kk * 8,
-                                ptx::smem_desc_sw128(v_base + kk * (16 * 128), kTileK * 128, 1024), idesc_o, !(first && kk == 0));
+                    ptx::mma_ts_words(tmem_base + kColO + i * kColOStride, tmem_base + i * kColS + kk * 8, vb + kk * ((16 * 128) >> 4), kDescHi,
+                                      idesc_o, !(first && kk == 0));
             };
             for (int it = 0; ok && pair_item(p, it, w); ++it) {
                 if (w.n[0] == 0) continue;
@@ -679,9 +645,7 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         if (j >= w.n[i] || !ok) continue;
-                        ATT_STAMP(0);
                         if (!(ok = bounded_wait(wctx, bar(P_FULL + i), cp[i] & 1, 0x03050000u | (j & 0xffff)))) break;
-                        ATT_STAMP(0);
                         ++cp[i];
                         if (j == 0) {                               // the previous item's O_i has been read out
                             if (!(ok = bounded_wait(wctx, bar(O_FREE + i), (cof[i] & 1) ^ 1, 0x03060000u | i))) break;
@@ -692,7 +656,6 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                             v_waited = true;
                         }
                         ptx::tc_fence_after_sync();
-                        ATT_STAMP(0);
                         issue_pv(i, rv, j == 0);
                         if (j == w.n[i] - 1) ptx::mma_commit(bar(O_FULL + i));
                         if (j + 1 < w.n[i]) {
@@ -702,7 +665,6 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                                 ptx::tc_fence_after_sync();
                             }
                             issue_s(i, rk);
-                            ATT_STAMP(0);
                             if (j + 2 == w.n[i]) ptx::mma_commit(bar(Q_EMPTY + i));
                         }
                     }
@@ -712,7 +674,6 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 }
                 kvr += 2 * nmax;
             }
-            ATT_STAMP_DONE(0);
         }
         __syncwarp();
     } else if (warp < 4) {
@@ -728,7 +689,6 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         const float fill = c > 0.0f ? -CUDART_INF_F : CUDART_INF_F;
         uint32_t cs = 0;
         bool ok = true;
-        [[maybe_unused]] int trace_n = 0;
         PairItem w;
         // O_g row *= f, eight columns at a time (few registers: it runs beside a live row of scores); whole warps only
         auto rescale_o = [&](float f) {
@@ -748,12 +708,10 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         for (int it = 0; ok && pair_item(p, it, w); ++it) {
             if (w.n[g] == 0) continue;
             const int q_row = w.row0 + g * kTileQ + row;
-            float m_run = -CUDART_INF_F, m_next = -CUDART_INF_F, l_run = 0.0f, f_pend = 1.0f;
+            float m_run = -CUDART_INF_F, l_run = 0.0f, f_pend = 1.0f;
             for (int j = 0; j < w.n[g] && ok; ++j) {
-                if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
                 ok = __all_sync(0xffffffffu, bounded_wait(wctx, bar(S_FULL + g), cs & 1, 0x030a0000u | (j & 0xffff)));
                 if (!ok) break;
-                if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
                 ++cs;
                 ptx::tc_fence_after_sync();
                 int valid = p.seq_k - j * kTileK;
@@ -770,7 +728,6 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
 #pragma unroll
                 for (int ch = 0; ch < kTileK / 32; ++ch) ptx::tmem_ld_32x32b_x32(s_row + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[ch * 32]));
                 ptx::tmem_ld_wait();
-                if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
                 if (ragged) {                                           // last key tile, or the causal diagonal
 #pragma unroll
                     for (int i = 0; i < kTileK; ++i)
@@ -810,17 +767,12 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 // against overflow -- it is computed beside the exponentials, off the path from S to P.
                 float m_tile = 0.0f;
                 if (j == 0) m_run = m_tile = row_max();
-                if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
-                // p = 2^(c s - m). The transcendental unit makes 16 results a clock for the whole SM -- and the conversion
-                // of a pair of floats to 16 bits runs on that same unit --, which is as long as the tensor cores need for
-                // the tile's two products. So (bf16) kPolyOf8 of every eight pairs of exponentials go through the FMA pipe
-                // (exp2_poly2), and no pair is converted: P is the upper half of the fp32 bit pattern, one byte-permute per
-                // pair. Truncation loses half a 16-bit ulp on average, so every exponent is taken kTruncBiasLog2 higher
-                // (a factor 1 + 2^-9) and the row sum is scaled back once at the end. Tiles with masked (infinite)
-                // scores take the transcendental unit for everything.
+                // p = 2^(c s - m). bf16: P is the upper half of the fp32 bit pattern, one byte-permute per pair, because the
+                // conversion of a pair of floats to 16 bits runs on the transcendental unit like the exponentials, which
+                // is the unit this loop is bound by. Truncation loses half a 16-bit ulp on average, so every exponent is
+                // taken kTruncBiasLog2 higher (a factor 1 + 2^-9) and the row sum is scaled back once at the end.
                 float2 sum2[2];
-                auto emit = [&](auto poly_of_8) {
-                    constexpr int kPoly = decltype(poly_of_8)::value;
+                auto emit = [&]() {
                     const float shift = BF16 ? kTruncBiasLog2 - m_run : -m_run;
                     const float2 c2 = make_float2(c, c), nm2 = make_float2(shift, shift);
                     sum2[0] = sum2[1] = make_float2(0.0f, 0.0f);
@@ -831,9 +783,7 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                         for (int i = 0; i < 16; ++i) {
                             const int e0 = ch * 32 + 2 * i;
                             const float2 y = fma2(make_float2(__uint_as_float(r[e0]), __uint_as_float(r[e0 + 1])), c2, nm2);
-                            float2 e;
-                            if ((i & 7) < kPoly) e = exp2_poly2(y);
-                            else e = make_float2(ptx::ex2_approx(y.x), ptx::ex2_approx(y.y));
+                            const float2 e = make_float2(ptx::ex2_approx(y.x), ptx::ex2_approx(y.y));
                             sum2[i & 1] = add2(sum2[i & 1], e);
                             if constexpr (BF16) pk[i] = __byte_perm(__float_as_uint(e.x), __float_as_uint(e.y), 0x7632);
                             else pk[i] = pack_pair<false>(e.x, e.y);
@@ -841,44 +791,40 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                         ptx::tmem_st_32x32b_x16(s_row + ch * 16, pk);
                     }
                 };
-                // (the choice is made per warp: the tensor-memory stores inside are warp-wide instructions)
-                if (__any_sync(0xffffffffu, ragged)) emit(std::integral_constant<int, 0>{});
-                else emit(std::integral_constant<int, BF16 ? kPolyOf8 : kPolyOf8F16>{});
-                if (j > 0) {
+                emit();
+                float2 tot = add2(sum2[0], sum2[1]);
+                // Scores far above the reference show in the tile's sum: beyond 2^64 (never on ordinary data) the
+                // reference is raised now, the accumulator and the sum are brought along, and this tile's exponentials
+                // are taken again.
+                if (j > 0 && __any_sync(0xffffffffu, !(tot.x + tot.y < 1.8446744e19f))) {
                     m_tile = row_max();
-                    // Scores more than 2^64 above the reference could overflow: raise the reference now, bring the
-                    // accumulator and the sum along, and take this tile's exponentials again (never on ordinary data).
-                    const bool over = m_tile > m_run + 64.0f;
-                    if (__any_sync(0xffffffffu, over)) {
-                        const float f = over ? ptx::ex2_approx(m_run - m_tile) : 1.0f;
-                        rescale_o(f);
-                        l_run *= f;
-                        if (over) m_run = m_tile;
-                        emit(std::integral_constant<int, 0>{});
-                    }
+                    const bool over = m_tile > m_run + 32.0f;
+                    const float f = over ? ptx::ex2_approx(m_run - m_tile) : 1.0f;
+                    rescale_o(f);
+                    l_run *= f;
+                    if (over) m_run = m_tile;
+                    emit();
+                    tot = add2(sum2[0], sum2[1]);
                 }
-                const float2 tot = add2(sum2[0], sum2[1]);
                 l_run += tot.x + tot.y;
-                // The reference for the next tile: raised only when this tile's maximum exceeds it by more than 2^8.
-                {
-                    const bool raise = m_tile > m_run + 8.0f;
-                    f_pend = raise ? ptx::ex2_approx(m_run - m_tile) : 1.0f;
-                    m_next = raise ? m_tile : m_run;
-                }
-                if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(bar(P_FULL + g));
-                if (wq == 0 && lane == 0) ATT_STAMP(1 + g);
-                m_run = m_next;
+                // With P handed over, the tile's own maximum and from it the reference for the next tile: raised only
+                // when the maximum exceeds the current one by more than 2^8.
+                if (j > 0) m_tile = row_max();
+                {
+                    const bool raise = m_tile > m_run + 8.0f;
+                    f_pend = raise ? ptx::ex2_approx(m_run - m_tile) : 1.0f;
+                    m_run = raise ? m_tile : m_run;
+                }
             }
             if (!ok) break;
             lsum[g * 128 + row] = BF16 ? l_run * (1.0f / 1.001953125f) : l_run;      // the exponentials carried a factor 1 + 2^-9
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar(L_READY + 4 * g + wq));
         }
-        if (wq == 0 && lane == 0) ATT_STAMP_DONE(1 + g);
     } else {
         // ---- correction and output ---------------------------------------------------------------------------------------
         ptx::setmaxnreg_dec<kRegsCorrection>();
@@ -888,7 +834,6 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         const bool issuer = threadIdx.x == 12 * 32;
         uint32_t cl[2] = {0, 0}, cfull[2] = {0, 0}, cstage = 0;
         bool ok = true;
-        [[maybe_unused]] int trace_n = 0;
         PairItem w;
         for (int it = 0; ok && pair_item(p, it, w); ++it) {
             if (w.n[0] == 0) continue;
@@ -966,7 +911,6 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             }
         }
         if (issuer) ptx::tma_store_wait<0>();
-        if (issuer) ATT_STAMP_DONE(3);
         if (p.mc_base != 0) __threadfence_system();
     }
 
@@ -981,17 +925,6 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     }
 }
 
-#ifdef EMMY_ATT_TRACE
-extern "C" int emmyb200_debug_att_trace(long long* out, int* counts) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_att_trace, sizeof(long long) * 8 * 512);
-    cudaMemcpyFromSymbol(counts, g_att_trace_n, sizeof(int) * 8);
-    int zero[8] = {0};
-    cudaMemcpyToSymbol(g_att_trace_n, zero, sizeof(zero));
-    return 0;
-}
-#endif
-
 int attention_read_status(uint32_t* out) {
     uint32_t zero = 0;
     EMMY_CUDA(cudaDeviceSynchronize());
@@ -1001,7 +934,7 @@ int attention_read_status(uint32_t* out) {
 }
 
 template <int D, bool BF16>
-static int launch_attention(const void* Q, const void* K, const void* V, void* const* O, int n_dst, bool causal, bool multicast, int64_t units,
+static int launch_attention(const void* Q, const void* K, const void* V, void* const* O, int n_dst, bool causal, bool multicast, int form_flags, int64_t units,
                             int64_t seq_q, int64_t seq_k, float scale, cudaStream_t stream) {
     using S = AttSmem<D>;
     CUtensorMap mq, mk, mv;
@@ -1023,8 +956,11 @@ static int launch_attention(const void* Q, const void* K, const void* V, void* c
     EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_att_status));
     const int64_t ctas = units * p.q_tiles;
     if (ctas >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: %lld query tiles exceed the grid limit", (long long)ctas);
-    const char* which = getenv("EMMYB200_ATT_KERNEL");              // experiment hook while the two forms are compared
-    if (which != nullptr && which[0] == 'p') {
+    // Which form: measured on 256 units of 4096 x 128 (bf16, interleaved runs at the sustained clock), the two-tile form
+    // is 5 % faster with the causal flag (its couples of long and short tile pairs keep every SM busy to the end) and
+    // the one-tile form 5 % faster without it; a flag overrides the choice.
+    const bool two_tiles = (form_flags & EMMYB200_ATT_FORM_TWO_TILES) ? true : ((form_flags & EMMYB200_ATT_FORM_ONE_TILE) ? false : causal);
+    if (two_tiles) {
         using P = PairSmem<D>;
         auto pair_kernel = attention_fwd_pair_kernel<D, BF16>;
         EMMY_CUDA(cudaFuncSetAttribute(pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kTotal));
@@ -1046,9 +982,11 @@ static int attention_entry(int dtype, int flags, const void* Q, const void* K, c
                            int64_t seq_q, int64_t seq_k, int64_t d, float scale, void* cuda_stream) {
     using namespace emmy;
     if (dtype != EMMYB200_F16 && dtype != EMMYB200_BF16) return fail(EMMYB200_ERR_UNSUPPORTED, "attention_fwd: dtype %d (f16 and bf16 only)", dtype);
-    if (flags & ~(EMMYB200_ATT_CAUSAL | EMMYB200_ATT_DST_MULTICAST)) return fail(EMMYB200_ERR_ARG, "attention_fwd: unknown flags 0x%x", flags);
+    if (flags & ~(EMMYB200_ATT_CAUSAL | EMMYB200_ATT_DST_MULTICAST | EMMYB200_ATT_FORM_ONE_TILE | EMMYB200_ATT_FORM_TWO_TILES)) return fail(EMMYB200_ERR_ARG, "attention_fwd: unknown flags 0x%x", flags);
     const bool causal = flags & EMMYB200_ATT_CAUSAL;
     const bool multicast = flags & EMMYB200_ATT_DST_MULTICAST;
+    const int form = flags & (EMMYB200_ATT_FORM_ONE_TILE | EMMYB200_ATT_FORM_TWO_TILES);
+    if (form == (EMMYB200_ATT_FORM_ONE_TILE | EMMYB200_ATT_FORM_TWO_TILES)) return fail(EMMYB200_ERR_ARG, "attention_fwd: one form flag at most");
     if (multicast && n_dst != 1) return fail(EMMYB200_ERR_ARG, "attention_fwd: a multicast destination is a single address");
     if (n_dst < 1 || n_dst > kMaxDst) return fail(EMMYB200_ERR_ARG, "attention_fwd: %d destinations (1 to %d)", n_dst, kMaxDst);
     if (units < 0 || seq_q < 0 || seq_k < 0) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: negative extent");
@@ -1067,10 +1005,10 @@ static int attention_entry(int dtype, int flags, const void* Q, const void* K, c
     if (rc != EMMYB200_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
     const bool bf16 = dtype == EMMYB200_BF16;
-    if (d == 128) return bf16 ? launch_attention<128, true>(Q, K, V, O, n_dst, causal, multicast, units, seq_q, seq_k, scale, s)
-                              : launch_attention<128, false>(Q, K, V, O, n_dst, causal, multicast, units, seq_q, seq_k, scale, s);
-    return bf16 ? launch_attention<64, true>(Q, K, V, O, n_dst, causal, multicast, units, seq_q, seq_k, scale, s)
-                : launch_attention<64, false>(Q, K, V, O, n_dst, causal, multicast, units, seq_q, seq_k, scale, s);
+    if (d == 128) return bf16 ? launch_attention<128, true>(Q, K, V, O, n_dst, causal, multicast, form, units, seq_q, seq_k, scale, s)
+                              : launch_attention<128, false>(Q, K, V, O, n_dst, causal, multicast, form, units, seq_q, seq_k, scale, s);
+    return bf16 ? launch_attention<64, true>(Q, K, V, O, n_dst, causal, multicast, form, units, seq_q, seq_k, scale, s)
+                : launch_attention<64, false>(Q, K, V, O, n_dst, causal, multicast, form, units, seq_q, seq_k, scale, s);
 }
 
 extern "C" int emmyb200_attention_fwd(int dtype, int flags, const void* Q, const void* K, const void* V, void* O, int64_t units,

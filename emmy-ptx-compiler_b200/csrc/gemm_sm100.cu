@@ -25,8 +25,6 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -72,8 +70,8 @@ __device__ uint32_t g_gemm_status;
 
 // Tile order: bands of 16 row-blocks, column-blocks inside a band, row-blocks fastest, so CTAs that
 // run together share B column-blocks and a small set of A row-blocks.
-__device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, int& mb, int& nb, int kBand = 16) {
-    // kBand = 16 (rows of 128): measured best of 2..64 at 8192^3 (1356 TFLOP/s at 2 or 64, 1473 at 16)
+__device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, int& mb, int& nb) {
+    constexpr int kBand = 16;       // measured best of 2..64 at 8192^3 (1356 TFLOP/s at 2 or 64, 1473 at 16)
     const int per_band = kBand * n_blocks;
     const int band = t / per_band;
     const int first = band * kBand;
@@ -391,178 +389,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-// ---- CTA-pair form ------------------------------------------------------------------------------------------
-// Two CTAs of a cluster (two SMs) work on one 256 x 256 tile with tcgen05.mma.cta_group::2: each stages its own 128
-// rows of A and its own 128-column half of B (32 KiB a stage, six stages) and keeps the accumulators of its rows in
-// its own tensor memory; the first CTA of the pair issues the MMAs, which read both halves of B. Against the one-CTA
-// form, a CTA moves a third fewer operand bytes from L2 into shared memory and from shared memory into the tensor
-// core per flop -- which is what matters when the run is held at the power limit: fewer joules per flop, higher
-// sustained clock. Barriers: the TMA completions of both CTAs count on the issuing CTA's `full` barrier; `empty`
-// and `acc_full` exist in each CTA and get one commit each; `acc_empty` lives in the issuing CTA and collects the
-// eight epilogue warps of the pair. No multicast loads: the two CTAs read different boxes.
-struct PairGemmSmem {
-    static constexpr int kABytes = kBM * kBK * 2;
-    static constexpr int kBBytes = 128 * kBK * 2;
-    static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = 6;
-    static constexpr int kOutOffset = kStages * kStageBytes;
-    static constexpr int kBarOffset = kOutOffset + 2 * kOutPieceBytes;
-    static constexpr int kTotal = kBarOffset + 256 + 1024;
-};
-
-template <bool BF16, bool B_NK>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         const __grid_constant__ OutMaps out, GemmParams p) {
-    using S = PairGemmSmem;
-    constexpr int kStages = S::kStages;
-    constexpr int BN = 256;
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-    const uint32_t out_smem = smem_base + S::kOutOffset;
-    const uint32_t bar_base = smem_base + S::kBarOffset;
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-    auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
-    auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 2 + s); };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + S::kBarOffset + 8 * (2 * kStages + 4));
-    volatile uint32_t* abort_flag = tmem_slot + 1;
-    volatile uint32_t* epi_ok = tmem_slot + 2;
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = ptx::cluster_cta_rank();            // 0 issues the MMAs
-    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
-    const int k_blocks = (p.K + kBK - 1) / kBK;
-    const int plane_tiles = p.m_blocks * p.n_blocks;           // m_blocks counts 256-row blocks here
-    const int tiles = plane_tiles * p.batch;
-    const WaitCtx wctx{abort_flag, p.status, p.wait_limit_ns};
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
-        for (int s = 0; s < 2; ++s) { ptx::mbar_init(acc_full_bar(s), 1); ptx::mbar_init(acc_empty_bar(s), 8); }
-        *abort_flag = 0;
-        ptx::mbar_fence_init();
-        ptx::prefetch_tensormap(&map_a);
-        ptx::prefetch_tensormap(&map_b);
-    }
-    if (warp == 1) {
-        ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), 512);
-        ptx::tmem_relinquish_pair();
-    }
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    ptx::cluster_sync();                                       // the other CTA's barriers exist from here on
-    ptx::tc_fence_after_sync();
-    const uint32_t tmem_base = *tmem_slot;
-
-    if (warp == 0) {
-        // ---- TMA producer (both CTAs; completions count on the first CTA's barrier) -----------------------
-        if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (int t = pair; t < tiles && ok; t += pairs) {
-                int mb, nb;
-                const int plane = t / plane_tiles;
-                tile_coords(t - plane * plane_tiles, p.m_blocks, p.n_blocks, mb, nb, 8);
-                const int b_plane = p.b_shared ? 0 : plane;
-                const int row0 = mb * 256 + (int)rank * kBM, col0 = nb * BN + (int)rank * 128;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1;
-                    if (!(ok = bounded_wait(wctx, empty_bar(s), ph ^ 1, 0x04010000u | s))) break;
-                    const uint32_t a_dst = smem_base + s * S::kStageBytes;
-                    const uint32_t b_dst = a_dst + S::kABytes;
-                    const uint32_t full0 = ptx::map_to_cta(full_bar(s), 0);
-                    if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * S::kStageBytes);
-                    ptx::tma_load_3d_pair(a_dst, &map_a, full0, kb * kBK, row0, plane);
-                    if constexpr (B_NK) {
-                        ptx::tma_load_3d_pair(b_dst, &map_b, full0, kb * kBK, col0, b_plane);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 2; ++j)
-                            ptx::tma_load_3d_pair(b_dst + j * (kBK * 128), &map_b, full0, col0 + j * 64, kb * kBK, b_plane);
-                    }
-                }
-            }
-        }
-        __syncwarp();
-    } else if (warp == 1) {
-        // ---- MMA issuer (first CTA of the pair only) -------------------------------------------------------
-        if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = ptx::mma_idesc_f16(BF16, false, !B_NK, 256, BN);
-            uint32_t it = 0, acc_it = 0;
-            bool ok = true;
-            for (int t = pair; t < tiles && ok; t += pairs, ++acc_it) {
-                const int as = acc_it & 1;
-                const uint32_t aph = (acc_it >> 1) & 1;
-                if (!(ok = bounded_wait(wctx, acc_empty_bar(as), aph ^ 1, 0x04020000u | as))) break;
-                ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + as * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1;
-                    if (!(ok = bounded_wait(wctx, full_bar(s), ph, 0x04030000u | s))) break;
-                    ptx::tc_fence_after_sync();
-                    const uint32_t a_src = smem_base + s * S::kStageBytes;
-                    const uint32_t b_src = a_src + S::kABytes;
-#pragma unroll
-                    for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
-                        const uint64_t a_desc = ptx::smem_desc_sw128(a_src + kk * (kUmmaK * 2), 16, 1024);
-                        const uint64_t b_desc = B_NK ? ptx::smem_desc_sw128(b_src + kk * (kUmmaK * 2), 16, 1024)
-                                                     : ptx::smem_desc_sw128(b_src + kk * (kUmmaK * 128), kBK * 128, 1024);
-                        ptx::mma_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0);
-                    }
-                    ptx::mma_commit_pair(ptx::map_to_cta(empty_bar(s), 0));       // both producers may refill
-                    ptx::mma_commit_pair(ptx::map_to_cta(empty_bar(s), 1));
-                }
-                if (ok) {
-                    ptx::mma_commit_pair(ptx::map_to_cta(acc_full_bar(as), 0));
-                    ptx::mma_commit_pair(ptx::map_to_cta(acc_full_bar(as), 1));
-                }
-            }
-        }
-        __syncwarp();
-    } else {
-        // ---- epilogue (both CTAs, each its own 128 rows) ---------------------------------------------------
-        const int quarter = warp & 3;
-        const int row_in_tile = quarter * 32 + lane;
-        const bool issuer = threadIdx.x == 64;
-        uint32_t acc_it = 0, piece = 0;
-        bool ok = true;
-        for (int t = pair; t < tiles && ok; t += pairs, ++acc_it) {
-            int mb, nb;
-            const int plane = t / plane_tiles;
-            tile_coords(t - plane * plane_tiles, p.m_blocks, p.n_blocks, mb, nb, 8);
-            const int as = acc_it & 1;
-            const uint32_t aph = (acc_it >> 1) & 1;
-            if (issuer) *epi_ok = bounded_wait(wctx, acc_full_bar(as), aph, 0x04040000u | as) ? 1u : 0u;
-            ptx::named_barrier(1, 128);
-            ok = *epi_ok != 0;
-            if (!ok) break;
-            ptx::tc_fence_after_sync();
-            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
-            drain_accumulator<BN, BF16, false>(p, out, t_row, out_smem, piece, mb * 256 + (int)rank * kBM, nb * BN, plane, row_in_tile,
-                                               (int)threadIdx.x - 64, issuer,
-                                               [&] { if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(as), 0)); });
-        }
-        if (issuer) ptx::tma_store_wait<0>();
-        if (p.mc_base != 0) __threadfence_system();
-    }
-
-    // ---- teardown: neither CTA may leave while the other can still touch its shared or tensor memory ---------
-    if (*abort_flag) {
-        for (int i = 0; i < 64; ++i) __nanosleep(1000);
-    }
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    ptx::cluster_sync();
-    if (warp == 1) {
-        ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc_pair(tmem_base, 512);
-    }
-}
-
 // ---- host -----------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -733,63 +559,7 @@ static int launch_gemm(const GemmCall& g, cudaStream_t stream) {
 }
 
 template <bool BF16, bool B_NK>
-static int launch_gemm_pair(const GemmCall& g, cudaStream_t stream) {
-    using S = PairGemmSmem;
-    CUtensorMap map_a, map_b;
-    OutMaps out;
-    const bool b_shared = g.stride_b == 0;
-    int rc = make_tensor_map_3d_strided(&map_a, g.A, (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, (uint64_t)g.stride_a, kBM, kBK);
-    if (rc != EMMYB200_OK) return rc;
-    const uint64_t b_planes = b_shared ? 1 : (uint64_t)g.batch;
-    rc = B_NK ? make_tensor_map_3d_strided(&map_b, g.B, b_planes, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, (uint64_t)g.stride_b, 128, kBK)
-              : make_tensor_map_3d_strided(&map_b, g.B, b_planes, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, (uint64_t)g.stride_b, kBK, 64);
-    if (rc != EMMYB200_OK) return rc;
-    for (int d = 0; d < kMaxDst; ++d) {
-        if (g.flags & EMMYB200_GEMM_DST_MULTICAST) { out.m[d] = map_a; continue; }
-        rc = make_tensor_map_3d_strided(&out.m[d], g.C[d < g.n_dst ? d : 0], (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.N, (uint64_t)g.ldc,
-                                        (uint64_t)g.stride_c, kBM, 64);
-        if (rc != EMMYB200_OK) return rc;
-    }
-    auto kernel = gemm_tcgen05_pair_kernel<BF16, B_NK>;
-    EMMY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-    GemmParams p;
-    p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
-    p.m_blocks = (int)((g.M + 255) / 256);
-    p.n_blocks = (int)((g.N + 255) / 256);
-    p.batch = (int)g.batch;
-    p.b_shared = b_shared ? 1 : 0;
-    p.n_dst = g.n_dst;
-    p.epilogue = g.epilogue;
-    p.bias = g.bias;
-    const bool multicast = g.flags & EMMYB200_GEMM_DST_MULTICAST;
-    p.mc_base = multicast ? (unsigned long long)(uintptr_t)g.C[0] : 0ull;
-    p.ldc = g.ldc;
-    p.stride_c = g.stride_c;
-    p.wait_limit_ns = wait_limit_ns();
-    EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
-    const int64_t tiles = (int64_t)p.m_blocks * p.n_blocks * g.batch;
-    if (tiles >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "gemm: %lld output tiles exceed the scheduler's range", (long long)tiles);
-    const int64_t max_pairs = sm_count() / 2;
-    const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * pairs, 1, 1);
-    cfg.blockDim = dim3(kGemmThreads, 1, 1);
-    cfg.dynamicSmemBytes = S::kTotal;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, out, p);
-    if (e != cudaSuccess) return fail((int)e, "launch of gemm_tcgen05_pair_kernel: %s", cudaGetErrorString(e));
-    return launch_status("gemm_tcgen05_pair_kernel");
-}
-
-template <bool BF16, bool B_NK>
 static int pick_tile(const GemmCall& g, cudaStream_t stream) {
-    const char* mode = getenv("EMMYB200_GEMM_PAIR");            // experiment hook while the pair form is evaluated
-    if (mode != nullptr && mode[0] == '1' && g.M > 128 && g.N > 128) return launch_gemm_pair<BF16, B_NK>(g, stream);
     // 128 x 256 tiles: with both operands read from shared memory by one CTA, the 128 x 128 shape is bound by
     // shared-memory bandwidth (measured 0.6-0.7x the throughput at every size from 2048^3 to 16384^3), which
     // costs more than the emptier last wave of the wide tile. Narrow outputs keep the narrow tile.

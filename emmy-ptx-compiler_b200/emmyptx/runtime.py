@@ -45,6 +45,7 @@ GEMM_B_NK = 1
 GEMM_DST_MULTICAST = 2
 ATT_CAUSAL = 1
 ATT_DST_MULTICAST = 2
+ATT_FORMS = {None: 0, "one_tile": 4, "two_tiles": 8}
 GATHER_TRUNC = 1
 ROW_OPS = {"sum": 0, "mean": 1, "amax": 2, "amin": 3, "prod": 4, "var": 5, "std": 6, "norm2": 7, "logsumexp": 8, "argmax": 9, "dot": 10, "cosine": 11,
            "softmax": 16, "log_softmax": 17, "layer_norm": 18, "rms_norm": 19, "normalize": 20}
@@ -342,9 +343,9 @@ def gemm_allgather(a, b, dst_ptrs: list[int], ldc: int, epilogue: str | None = N
                                             _stream(stream)))
 
 
-def attention(q, k, v, scale: float | None = None, causal: bool = False, out=None, stream=None):
+def attention(q, k, v, scale: float | None = None, causal: bool = False, out=None, stream=None, form: str | None = None):
     """softmax(q k^T * scale) v over the last two axes; leading axes are independent units. `causal`: query i sees
-    keys 0..i only."""
+    keys 0..i only. `form`: "one_tile" / "two_tiles" forces a kernel form (default: the library's choice)."""
     import torch
     _need_cuda(q, k, v)
     d = q.shape[-1]
@@ -352,7 +353,7 @@ def attention(q, k, v, scale: float | None = None, causal: bool = False, out=Non
     out = torch.empty_like(q) if out is None else out
     _need_cuda(out)
     scale = d ** -0.5 if scale is None else scale
-    check(library().emmyb200_attention_fwd(dtype_code(q), ATT_CAUSAL if causal else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), units,
+    check(library().emmyb200_attention_fwd(dtype_code(q), (ATT_CAUSAL if causal else 0) | ATT_FORMS[form], q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), units,
                                            q.shape[-2], k.shape[-2], d, scale, _stream(stream)))
     return out
 

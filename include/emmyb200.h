@@ -176,9 +176,14 @@ int emmyb200_gemm_allgather(int dtype, int epilogue, int flags, const void* A, c
  * TreeHalve row reductions, `_exp`: emmyptx/kernel.py:786-797, :856-900, emmyptx/ops.py:49-77).
  * Q, O: [units, seq_q, d]; K, V: [units, seq_k, d]; contiguous, dtype F16 or BF16, d = 128
  * or 64, any seq_q, seq_k >= 1. EMMYB200_ATT_CAUSAL: query i attends to keys 0..i only (the lower-triangular
- * mask of tools/torch_cases/models.py:17-19, fused.py:31-36). */
+ * mask of tools/torch_cases/models.py:17-19, fused.py:31-36). Two kernel forms exist -- one 128-query tile per
+ * CTA with two CTAs sharing an SM, or two tiles per persistent CTA -- and the library picks by the causal flag (what
+ * was measured faster); EMMYB200_ATT_FORM_ONE_TILE / _TWO_TILES force one (tuning and tests; results agree within the
+ * rounding of P). */
 #define EMMYB200_ATT_CAUSAL 1
 #define EMMYB200_ATT_DST_MULTICAST 2    /* emmyb200_attention_fwd_allgather only, see there */
+#define EMMYB200_ATT_FORM_ONE_TILE 4
+#define EMMYB200_ATT_FORM_TWO_TILES 8
 int emmyb200_attention_fwd(int dtype, int flags, const void* Q, const void* K, const void* V, void* O,
                            int64_t units, int64_t seq_q, int64_t seq_k, int64_t d, float scale,
                            void* cuda_stream);

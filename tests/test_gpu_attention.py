@@ -13,6 +13,9 @@ from oracle import inputs, reference
 pytestmark = pytest.mark.gpu
 
 
+FORMS = ["one_tile", "two_tiles"]     # both kernel forms, forced; the default choice is exercised by the other tests
+
+
 def _attn(q, k, v, cuda, **kw):
     import torch
     from emmyptx import runtime
@@ -29,31 +32,35 @@ def _attn(q, k, v, cuda, **kw):
     (1, 2048, 2048, 128),
 ])
 @pytest.mark.parametrize("dtype", ["bf16", "f16"])
-def test_attention_matches_oracle(units, sq, sk, d, dtype, cuda):
+@pytest.mark.parametrize("form", FORMS)
+def test_attention_matches_oracle(units, sq, sk, d, dtype, form, cuda):
     q, k, v = inputs.attention_inputs(units, sq, sk, d, dtype)
-    got = _attn(q, k, v, cuda)
+    got = _attn(q, k, v, cuda, form=form)
     ref = reference.attention_reference(q, k, v)
     ok, ratio = reference.gemm_tolerance_ok(got, ref)
     assert ok, f"worst error {ratio:.2f}x the bound"
 
 
-def test_large_logits_and_scale(cuda):
+@pytest.mark.parametrize("form", FORMS)
+def test_large_logits_and_scale(form, cuda):
     """Scores spread over hundreds of log2 units: the running max must be raised (and the accumulator
-    rescaled) many times."""
+    rescaled) many times; in the two-tile form, whose exponentials are taken against the maximum of the earlier
+    tiles, the jump at key 512 also takes the overflow guard (reference raised, tile done again)."""
     import torch
     q, k, v = inputs.attention_inputs(2, 256, 1024, 128, "bf16")
     k = k.clone()
     k[:, 512:] *= 3                       # later keys dominate
-    got = _attn(q * 2, k, v, cuda, scale=1.0)
+    got = _attn(q * 2, k, v, cuda, scale=1.0, form=form)
     ref = reference.attention_reference(q * 2, k, v, scale=1.0)
     ok, ratio = reference.gemm_tolerance_ok(got, ref)
     assert ok, f"worst error {ratio:.2f}x the bound"
 
 
-def test_c5_sampled_units(cuda):
+@pytest.mark.parametrize("form", FORMS)
+def test_c5_sampled_units(form, cuda):
     """Full sequence length of C5 (4096) on a few (batch, head) units; every unit is independent."""
     q, k, v = inputs.attention_inputs(3, 4096, 4096, 128, "bf16")
-    got = _attn(q, k, v, cuda)
+    got = _attn(q, k, v, cuda, form=form)
     ref = reference.attention_reference(q, k, v)
     ok, ratio = reference.gemm_tolerance_ok(got, ref)
     assert ok, f"worst error {ratio:.2f}x the bound"
@@ -97,7 +104,8 @@ def test_rows_sum_property(cuda):
 
 @pytest.mark.parametrize("units,s,d", [(2, 256, 128), (3, 300, 128), (2, 64, 32 * 2), (1, 1000, 128), (2, 129, 64)])
 @pytest.mark.parametrize("dtype", ["bf16", "f16"])
-def test_causal(units, s, d, dtype, cuda):
+@pytest.mark.parametrize("form", FORMS)
+def test_causal(units, s, d, dtype, form, cuda):
     """t_causal_sdpa / f_masked_attn_manual (tools/torch_cases/models.py:17-19, fused.py:31-36): lower-triangular mask.
 
     The absolute floor of the bound is taken per query row (1e-2 of the row's rms) rather than over the whole
@@ -105,7 +113,7 @@ def test_causal(units, s, d, dtype, cuda):
     so one global std would hold the early rows' 16-bit probabilities to a tighter class than 1e-2."""
     import torch
     q, k, v = inputs.attention_inputs(units, s, s, d, dtype)
-    got = _attn(q, k, v, cuda, causal=True)
+    got = _attn(q, k, v, cuda, causal=True, form=form)
     scores = torch.matmul(q.double(), k.double().transpose(-1, -2)) * d ** -0.5
     mask = torch.ones(s, s, dtype=torch.bool).tril()
     ref = torch.matmul(torch.softmax(scores.masked_fill(~mask, float("-inf")), -1), v.double())
@@ -115,15 +123,16 @@ def test_causal(units, s, d, dtype, cuda):
     assert torch.equal(got[:, 0].float(), v[:, 0].float())        # the first query sees one key: O = V[0] exactly
 
 
-def test_causal_skips_tiles_past_the_diagonal(cuda):
+@pytest.mark.parametrize("form", FORMS)
+def test_causal_skips_tiles_past_the_diagonal(form, cuda):
     """Keys after the query must not influence the result at all: poisoning them with NaN changes nothing."""
     import torch
     q, k, v = inputs.attention_inputs(2, 384, 384, 128, "bf16")
-    a = _attn(q, k, v, cuda, causal=True)
+    a = _attn(q, k, v, cuda, causal=True, form=form)
     k2, v2 = k.clone(), v.clone()
     k2[:, 256:] = float("nan")
     v2[:, 256:] = float("nan")
-    b = _attn(q, k2, v2, cuda, causal=True)
+    b = _attn(q, k2, v2, cuda, causal=True, form=form)
     assert torch.equal(a[:, :256], b[:, :256])
 
 
@@ -136,5 +145,6 @@ def test_rejects_bad_arguments(cuda, lib):
     assert f(0, 0, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -4     # f32
     assert f(2, 0, p, p, p, p, 2, 128, 0, 128, 0.1, None) == -2       # no keys
     assert f(2, 0, p, p, p, p, 0, 128, 128, 128, 0.1, None) == 0      # no units
-    assert f(2, 8, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -1     # unknown flag
+    assert f(2, 16, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -1    # unknown flag
+    assert f(2, 12, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -1    # both form flags
     assert f(2, 0, None, p, p, p, 2, 128, 128, 128, 0.1, None) == -1
