@@ -348,17 +348,24 @@ def pointwise_kernel(n: int, expr: str = "exp_sin_tanh", name: str = "k_pointwis
     return g, k, _launch(k, ["x", "y"], n)
 
 
-def elementwise_kernel(n: int, inputs: dict, steps: list, out_dtype: str = "f32", name: str = "k_elementwise"):
+def elementwise_kernel(n: int, inputs: dict, steps: list, out_dtype: str = "f32", name: str = "k_elementwise",
+                       scalars: dict | None = None):
     """A general elementwise kernel: `inputs` maps buffer name -> dtype (each of n elements); `steps` is a list of
     (value name, op name, args) with args naming earlier values, the loaded inputs (by buffer name) or numbers;
-    the last step's value is written to `out`."""
+    the last step's value is written to `out`. `scalars` maps the names of by-value parameters to 'f32' / 's32':
+    they follow the buffers in `arg_order`, are described in the launch's `args` (emmyptx/kernel.py:166-178) and
+    may be named by the steps like any value."""
     a0 = Axis("a0", Dim(n))
     body = [Load([b], b, [Var("a0")]) for b in inputs]
     body += [Assign(v, Op(op), list(args)) for v, op, args in steps]
     body.append(Write("out", [Var("a0")], [steps[-1][0]]))
     k = KernelOp(name, [Tile([a0], body)])
     g = _graph(k, [tensor(b, [n], dt) for b, dt in inputs.items()], [tensor("out", [n], out_dtype)])
-    return g, k, _launch(k, [*inputs, "out"], n)
+    launch = _launch(k, [*inputs, "out", *(scalars or {})], n)
+    if scalars:
+        launch["args"] = ([{"name": b, "dtype": dt, "shape": [n]} for b, dt in inputs.items()] + [{"name": "out", "dtype": out_dtype, "shape": [n], "output": True}]
+                          + [{"name": s, "dtype": dt, "shape": [], "scalar": True} for s, dt in scalars.items()])
+    return g, k, launch
 
 
 def index_gather_kernel(n: int, mul: int = 7919, add: int = 13, div: int = 3, shift: int = 2, name: str = "k_gather"):

@@ -245,10 +245,18 @@ PW_OP_NAMES = {"add", "subtract", "multiply", "divide", "maximum", "minimum", "r
                "bitwise_not", "floor_divide", "mod", "remainder"}
 
 
-def build_program(tile, tensors: dict, out_name: str, out_value_name, integer: bool = False) -> dict:
+def scalar_args(launch: dict) -> dict:
+    """name -> 'f32' | 's32' for the launch's scalar parameters (passed by value: emmyptx/kernel.py:171-178)."""
+    return {a["name"]: ("f32" if a.get("dtype", "f32") == "f32" else "s32") for a in launch.get("args", []) if a.get("scalar")}
+
+
+def build_program(tile, tensors: dict, out_name: str, out_value_name, integer: bool = False, scalars: dict | None = None) -> dict:
     """The tile's cell program as data for the general elementwise kernel: inputs in slots 0.., one slot per live
     value (slots are reused once a value is dead), numeric operands in the constant table. `integer`: an s32 program
-    (every Assign integer-typed, ops from the integer table, constants whole numbers)."""
+    (every Assign integer-typed, ops from the integer table, constants whole numbers). A scalar parameter of the
+    launch gets a constant slot of its own, filled with its value when the kernel is launched (`scalar_consts`)."""
+    scalars = scalars or {}
+    scalar_slot: dict = {}
     stmts = list(tile.body)
     inputs, slot_of = [], {}
     for s in stmts:
@@ -278,7 +286,14 @@ def build_program(tile, tensors: dict, out_name: str, out_value_name, integer: b
             raise OpError(f"elementwise op {s.op.name!r} is not supported")
         ops = []
         for a in s.args:
-            if isinstance(a, str):
+            if isinstance(a, str) and a in scalars and a not in slot_of:
+                if a not in scalar_slot:
+                    consts.append(("scalar", a))                    # a placeholder no literal can equal
+                    scalar_slot[a] = len(consts) - 1
+                    if len(consts) > PW_CONSTS:
+                        raise Unmatched(f"more than {PW_CONSTS} distinct constants")
+                ops.append(PW_SLOTS + scalar_slot[a])
+            elif isinstance(a, str):
                 if a not in slot_of:
                     raise Unmatched(f"use of undefined name {a!r}")
                 ops.append(slot_of[a])
@@ -291,7 +306,7 @@ def build_program(tile, tensors: dict, out_name: str, out_value_name, integer: b
                 if len(consts) > PW_CONSTS:
                     raise Unmatched(f"more than {PW_CONSTS} distinct constants")
                 ops.append(PW_SLOTS + consts.index(v))
-        for a in set(x for x in s.args if isinstance(x, str)):          # operands that die here free their slots
+        for a in set(x for x in s.args if isinstance(x, str) and x in slot_of):          # operands that die here free their slots
             if last_use.get(a) == i and slot_of[a] >= len(inputs):
                 free.append(slot_of[a])
         if not free:
@@ -303,8 +318,11 @@ def build_program(tile, tensors: dict, out_name: str, out_value_name, integer: b
             free.append(dst)
     if len(steps) > PW_STEPS:
         raise Unmatched(f"{len(steps)} steps: the general elementwise kernel takes {PW_STEPS}")
-    return {"inputs": inputs, "in_dtypes": [tensors[b][1] for b in inputs], "out_dtype": tensors[out_name][1],
-            "out_slot": slot_of[out_value_name], "consts": consts, "steps": steps}
+    prog = {"inputs": inputs, "in_dtypes": [tensors[b][1] for b in inputs], "out_dtype": tensors[out_name][1],
+            "out_slot": slot_of[out_value_name], "consts": [0.0 if isinstance(c, tuple) else c for c in consts], "steps": steps}
+    if scalar_slot:
+        prog["scalar_consts"] = [[name, idx, scalars[name]] for name, idx in scalar_slot.items()]
+    return prog
 
 
 def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
@@ -319,6 +337,10 @@ def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict
     rng = np.random.default_rng(0)
     cells = np.unique(np.concatenate([np.arange(min(n, 96)), rng.integers(0, n, 160), [n - 1]])).astype(np.int64)
     it = CellInterpreter(tensors, cells, INT_OPS_TRUNC if int_div == "trunc" else INT_OPS)
+    scalars = scalar_args(launch)
+    for k, (name, ty) in enumerate(scalars.items()):        # a value no fixed-function variant's expression contains
+        it.env[name] = np.full(cells.shape, 1.3719 + 0.2113 * k) if ty == "f32" else np.full(cells.shape, 5 + 3 * k, dtype=np.int64)
+    used_scalars = {a for st in tile.body if _kind(st) == "Assign" for a in st.args if isinstance(a, str) and a in scalars}
     # axis variables: last axis fastest (emmyptx/kernel.py:587-626, without rasterisation)
     rem = cells.copy()
     for a in reversed(tile.axes):
@@ -352,7 +374,7 @@ def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict
     broadcast = pattern is not None and not identity
     if (identity or broadcast) and tensors[out_name][1] in int_types and all(tensors[b][1] in int_types for b in buffers) and buffers:
         # an integer expression of element i of every buffer: the s32 program kernel (the gather is the other integer kernel)
-        prog = build_program(tile, tensors, out_name, tile.body[-1].values[0] if _kind(tile.body[-1]) == "Write" else None, integer=True)
+        prog = build_program(tile, tensors, out_name, tile.body[-1].values[0] if _kind(tile.body[-1]) == "Write" else None, integer=True, scalars=scalars)
         prog["int_div"] = int_div
         if broadcast:
             prog["in_div"], prog["in_mod"] = [pattern[b][0] for b in prog["inputs"]], [pattern[b][1] for b in prog["inputs"]]
@@ -360,12 +382,14 @@ def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict
                 "inputs": prog["inputs"], "outputs": [out_name]}
     general = (tensors[out_name][1] in float_types and all(tensors[b][1] in float_types + ("bool", "u8") for b in buffers)
                and (identity or broadcast) and bool(buffers))
-    if general and (broadcast or not (len(buffers) == 1 and tensors[next(iter(buffers))][1] == "f32" and tensors[out_name][1] == "f32")):
-        prog = build_program(tile, tensors, out_name, tile.body[-1].values[0] if _kind(tile.body[-1]) == "Write" else None)
+    if general and (used_scalars or broadcast or not (len(buffers) == 1 and tensors[next(iter(buffers))][1] == "f32" and tensors[out_name][1] == "f32")):
+        prog = build_program(tile, tensors, out_name, tile.body[-1].values[0] if _kind(tile.body[-1]) == "Write" else None, scalars=scalars)
         if broadcast:
             prog["in_div"], prog["in_mod"] = [pattern[b][0] for b in prog["inputs"]], [pattern[b][1] for b in prog["inputs"]]
         return {"variant": "pointwise_program", "params": {"n": n, "program": {k: v for k, v in prog.items() if k != "inputs"}},
                 "inputs": prog["inputs"], "outputs": [out_name]}
+    if used_scalars:
+        raise Unmatched("scalar parameters are taken by elementwise programs over float or integer buffers only")
     if len(buffers) != 1:
         raise Unmatched("streaming variants read one input buffer")
     (src,) = buffers

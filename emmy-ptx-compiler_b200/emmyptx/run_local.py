@@ -66,10 +66,11 @@ def run_kernel(text: str, k: dict, produced: dict) -> dict:
     import torch
     handle = load(text, k["entry"])
     dev = torch.device("cuda", torch.cuda.current_device())
-    bufs, meta = {}, {}
+    bufs, meta, scalars = {}, {}, {}
     for a in k["args"]:
-        if a.get("scalar"):
-            raise RuntimeError(f"scalar argument {a['name']!r}: no kernel variant takes scalars")
+        if a.get("scalar"):                     # passed by value (tools/run_local.py:82-83)
+            scalars[a["name"]] = a["value"]
+            continue
         shape = a["shape"] or [1]
         if "seed" in a:
             host = to_device(np.random.default_rng(a["seed"]).standard_normal(shape), a["dtype"])
@@ -84,7 +85,7 @@ def run_kernel(text: str, k: dict, produced: dict) -> dict:
     order = [a["name"] for a in k["args"]]
     if order != handle["arg_order"]:
         raise RuntimeError(f"kernel arguments {order} do not match the handle's arg_order {handle['arg_order']}")
-    launch(handle, bufs)
+    launch(handle, bufs, scalars=scalars)
     torch.cuda.synchronize()
     if runtime.device_status() != 0:
         raise RuntimeError("a bounded device-side wait expired")
@@ -97,9 +98,17 @@ def run_kernel(text: str, k: dict, produced: dict) -> dict:
     return outputs
 
 
-def launch(handle: dict, bufs: dict, stream=None) -> None:
-    """Enqueue the handle's kernel on buffers (CUDA tensors by argument name)."""
+def launch(handle: dict, bufs: dict, stream=None, scalars: dict | None = None) -> None:
+    """Enqueue the handle's kernel on buffers (CUDA tensors by argument name); `scalars`: the launch's by-value
+    arguments by name."""
     p, v = handle["params"], handle["variant"]
+    if v == "pointwise_program" and p["program"].get("scalar_consts"):
+        prog = dict(p["program"], consts=list(p["program"]["consts"]))
+        for name, idx, _ in prog["scalar_consts"]:
+            if scalars is None or name not in scalars:
+                raise RuntimeError(f"scalar argument {name!r} has no value")
+            prog["consts"][idx] = float(scalars[name])
+        p = dict(p, program=prog)
     ins = [bufs[n] for n in handle["inputs"]]
     out = bufs[handle["outputs"][0]]
     if v == "pointwise_f32":

@@ -90,6 +90,9 @@ _SIGNATURES = {
     "emmyb200_rowwise_static_capacity": (ctypes.c_int64, []),
     "emmyb200_rowwise_f32_static": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                    ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p]),
+    "emmyb200_launch_workspace_bytes": (ctypes.c_int64, [ctypes.c_char_p]),
+    "emmyb200_launch": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_void_p, ctypes.c_int64,
+                                       ctypes.c_void_p]),
     "emmyb200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
     "emmyb200_set_wait_limit_ns": (ctypes.c_int, [ctypes.c_uint64]),
     "emmyb200_selftest_wait_expiry": (ctypes.c_int, [ctypes.c_uint64, ctypes.c_void_p]),

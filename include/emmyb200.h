@@ -256,6 +256,18 @@ int64_t emmyb200_rowwise_static_capacity(void);
 int emmyb200_rowwise_f32_static(int op, const float* x, const float* weight, const float* bias, void* y, int64_t rows,
                                 int64_t cols, float eps, void* cuda_stream);
 
+/* Launches the kernel a handle names, from raw device pointers: the counterpart of `cuLaunchKernel` on the PTX entry
+ * the reference prints (tools/run_local.py:94-102 builds one pointer per parameter of meta.json's `arg_order`,
+ * emmyptx/kernel.py:166-183 declares buffers as `.param .u64` and scalars as `.param .f32 / .s32`). `handle_json` is the
+ * text compile.py / compile_kernel printed; `params[i]` points at the value of the i-th name in the handle's
+ * `arg_order`: at a device pointer (a `void*`) for a buffer, at a float or an int32_t for a scalar argument; n_params
+ * must equal the length of `arg_order`. `workspace`: emmyb200_launch_workspace_bytes(handle_json) bytes of
+ * 256-byte-aligned device memory (0 for most kernels: NULL then). The handle's shapes are the ones the kernel was
+ * compiled for, as the reference bakes them into its PTX; nothing is retained; the call is asynchronous. */
+int64_t emmyb200_launch_workspace_bytes(const char* handle_json);
+int emmyb200_launch(const char* handle_json, void* const* params, int n_params, void* workspace, int64_t workspace_bytes,
+                    void* cuda_stream);
+
 /* Reads (and clears) the device status word of the current device into *status_out: 0 if no bounded wait has
  * expired since the last call, else a code naming kernel (bits 24-31: 1 GEMM, 2 attention), wait site (16-23)
  * and pipeline stage (0-15). Returns EMMYB200_OK with a zero word and EMMYB200_ERR_TIMEOUT with a non-zero one

@@ -65,6 +65,14 @@ def test_newer_entry_points_check_their_arguments_without_a_device(lib):
     assert lib.emmyb200_attention_fwd(2, 2, p, p, p, p, 1, 8, 8, 128, 1.0, None) == -1
     assert lib.emmyb200_attention_fwd_allgather(2, 2, p, p, p, dst, 2, 1, 8, 8, 128, 1.0, None) == -1
     assert lib.emmyb200_rowwise_static_capacity() == 1 << 20
+    assert lib.emmyb200_launch(b"{}", None, 0, None, 0, None) == -1 and b"handle" in lib.emmyb200_last_error()
+    assert lib.emmyb200_launch_workspace_bytes(b"[1, 2") == -1
+    handle = b'{"variant": "pointwise_f32", "params": {"op": "exp", "n": 8}, "arg_order": ["x", "y"], "inputs": ["x"], "outputs": ["y"]}'
+    assert lib.emmyb200_launch_workspace_bytes(handle) == 0
+    assert lib.emmyb200_launch(handle, None, 2, None, 0, None) == -1                  # no parameter array
+    null = ctypes.c_void_p(0)
+    params = (ctypes.c_void_p * 2)(ctypes.cast(ctypes.byref(null), ctypes.c_void_p), ctypes.cast(ctypes.byref(null), ctypes.c_void_p))
+    assert lib.emmyb200_launch(handle, params, 2, None, 0, None) == -1 and b"null" in lib.emmyb200_last_error()
     assert lib.emmyb200_set_wait_limit_ns(1) == -1 and lib.emmyb200_set_wait_limit_ns(0) == 0
     assert lib.emmyb200_selftest_wait_expiry(10, None) == -1 and lib.emmyb200_selftest_wait_expiry(2 * 10**9, None) == -1
 

@@ -266,3 +266,16 @@ def test_attention_mask_and_scale_are_checked_not_guessed():
     fill = next(s for s in loop.body if type(s).__name__ == "Assign" and s.op.name == "where")
     cmp.op, fill.args = ir.Op("greater"), ["keep", float("-inf"), "t0"]
     assert handle((g, k, launch))["params"]["causal"] is True
+
+
+def test_scalar_parameters_become_launch_time_constants():
+    """A by-value parameter of the launch (emmyptx/kernel.py:171-178) gets a constant slot that the launch fills."""
+    built = ir.elementwise_kernel(256, {"x": "f32"}, [("a", "multiply", ["x", "alpha"]), ("o", "add", ["a", "beta"])], scalars={"alpha": "f32", "beta": "f32"})
+    h = handle(built)
+    assert h["variant"] == "pointwise_program" and h["arg_order"] == ["x", "out", "alpha", "beta"]
+    prog = h["params"]["program"]
+    assert sorted(prog["scalar_consts"]) == [["alpha", 0, "f32"], ["beta", 1, "f32"]]
+    assert prog["steps"][0][2:4] == [0, 16] and prog["steps"][1][3] == 17
+    # a scalar no step uses changes nothing
+    h2 = handle(ir.elementwise_kernel(256, {"x": "f32"}, [("o", "exp", ["x"])], scalars={"unused": "f32"}))
+    assert h2["variant"] == "pointwise_f32" and h2["params"]["op"] == "exp"

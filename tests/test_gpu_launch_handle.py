@@ -1,0 +1,125 @@
+"""emmyb200_launch: a kernel handle launched from raw device pointers, the way the reference's runner launches a PTX
+entry (tools/run_local.py:80-102: one pointer per parameter of `arg_order`, buffers as device pointers, scalars by
+value). The test plays a runner that holds nothing but addresses: it compiles IR to handle text, passes the text and
+a ctypes parameter array through the C ABI, and checks the buffers against the oracle."""
+import ctypes
+import json
+
+import numpy as np
+import pytest
+
+from oracle import inputs, reference
+
+pytestmark = pytest.mark.gpu
+
+
+def launch(lib, text: str, values: list, stream=None) -> int:
+    """values: per arg_order entry a torch CUDA tensor (passed as its device pointer) or a ctypes scalar."""
+    import torch
+    holders = [ctypes.c_void_p(v.data_ptr()) if isinstance(v, torch.Tensor) else v for v in values]
+    params = (ctypes.c_void_p * len(holders))(*[ctypes.cast(ctypes.byref(h), ctypes.c_void_p) for h in holders])
+    need = lib.emmyb200_launch_workspace_bytes(text.encode())
+    assert need >= 0
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda") if need else None
+    rc = lib.emmyb200_launch(text.encode(), params, len(holders), ws.data_ptr() if ws is not None else None, need, stream)
+    torch.cuda.synchronize()
+    return rc
+
+
+def handle_text(built) -> str:
+    from emmyptx.kernel import compile_kernel
+    return compile_kernel(*built)
+
+
+def test_streaming_and_gather_handles(cuda, lib):
+    import torch
+    from emmyptx import ir
+    x = inputs.c1_input(2**16)
+    xd, yd = torch.from_numpy(x).to(cuda), torch.zeros(2**16, device=cuda)
+    assert launch(lib, handle_text(ir.pointwise_kernel(2**16)), [xd, yd]) == 0
+    assert reference.compare(yd.cpu().numpy(), reference.c1_f64(x), 1e-5, 1e-5)["ok"]
+    xi = inputs.c2_input(2**20)
+    xid, yid = torch.from_numpy(xi).to(cuda), torch.zeros(2**20, dtype=torch.int32, device=cuda)
+    assert launch(lib, handle_text(ir.index_gather_kernel(2**20)), [xid, yid]) == 0
+    assert np.array_equal(yid.cpu().numpy(), reference.c2_reference(xi))
+
+
+def test_scalar_parameters_are_passed_by_value(cuda, lib):
+    """out = (x * alpha + y) * 2 with alpha a `.param .f32`-style argument: the same handle, two values."""
+    import torch
+    from emmyptx import ir
+    n = 5000
+    built = ir.elementwise_kernel(n, {"x": "f32", "y": "f32"}, [("ax", "multiply", ["x", "alpha"]), ("s", "add", ["ax", "y"]),
+                                                                ("o", "multiply", ["s", 2.0])], scalars={"alpha": "f32"})
+    text = handle_text(built)
+    assert json.loads(text)["arg_order"] == ["x", "y", "out", "alpha"]
+    g = torch.Generator().manual_seed(0)
+    x, y = torch.randn(n, generator=g), torch.randn(n, generator=g)
+    out = torch.zeros(n, device=cuda)
+    for alpha in (0.5, -3.25):
+        assert launch(lib, text, [x.to(cuda), y.to(cuda), out, ctypes.c_float(alpha)]) == 0
+        ref = (x.double() * alpha + y.double()) * 2
+        assert reference.compare(out.cpu().numpy(), ref.numpy(), 1e-6, 1e-6)["ok"]
+    # an integer scalar in an integer program
+    built = ir.elementwise_kernel(n, {"a": "i32"}, [("t", "multiply", ["a", "k"]), ("o", "add", ["t", 7])], out_dtype="i32", scalars={"k": "s32"})
+    for st in built[1].body[0].body:
+        if type(st).__name__ == "Assign":
+            st.dtype = "i32"
+    a = torch.randint(-1000, 1000, (n,), dtype=torch.int32)
+    oi = torch.zeros(n, dtype=torch.int32, device=cuda)
+    assert launch(lib, handle_text(built), [a.to(cuda), oi, ctypes.c_int32(-11)]) == 0
+    assert torch.equal(oi.cpu(), a * -11 + 7)
+
+
+def test_contraction_handles(cuda, lib):
+    import torch
+    from emmyptx import ir
+    a, b = inputs.gemm_inputs(300, 520, 264, "bf16")
+    c = torch.zeros(300, 520, dtype=torch.bfloat16, device=cuda)
+    assert launch(lib, handle_text(ir.gemm_kernel(300, 520, 264, "bf16", "gelu_tanh")), [a.to(cuda), b.to(cuda), c]) == 0
+    ok, ratio = reference.gemm_tolerance_ok(c.cpu(), reference.gemm_reference(a, b, "gelu_tanh"))
+    assert ok, ratio
+    a, b = inputs.gemm_inputs(64, 512, 256, "f16", b_is_nk=True)
+    bias = torch.randn(512).half()
+    c = torch.zeros(64, 512, dtype=torch.float16, device=cuda)
+    text = handle_text(ir.gemm_kernel(64, 512, 256, "f16", "relu", True, bias=True, name="k_linear"))
+    assert launch(lib, text, [a.to(cuda), b.to(cuda), bias.to(cuda), c]) == 0
+    ref = torch.relu(a.float() @ b.float().t() + bias.float())
+    ok, ratio = reference.gemm_tolerance_ok(c.cpu(), ref)
+    assert ok, ratio
+    q, k, v = inputs.attention_inputs(3, 200, 328, 128, "bf16")
+    o = torch.zeros_like(q, device=cuda)
+    assert launch(lib, handle_text(ir.attention_kernel([3], 200, 328, 128, "bf16")), [q.to(cuda), k.to(cuda), v.to(cuda), o]) == 0
+    ok, ratio = reference.gemm_tolerance_ok(o.cpu(), reference.attention_reference(q, k, v))
+    assert ok, ratio
+
+
+def test_handles_that_need_a_workspace(cuda, lib):
+    import torch
+    from emmyptx import ir
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(4, 200000, generator=g)                         # rows beyond 65536 columns: split path, scratch memory
+    y = torch.zeros_like(x, device=cuda)
+    text = handle_text(ir.rowwise_kernel("softmax", 4, 200000))
+    assert lib.emmyb200_launch_workspace_bytes(text.encode()) > 0
+    assert launch(lib, text, [x.to(cuda), y]) == 0
+    assert reference.compare(y.cpu().numpy(), reference.rowwise_reference("softmax", x).numpy(), 1e-3, 1e-5)["ok"]
+    a, b = torch.randn(96, 200, generator=g), torch.randn(200, 136, generator=g)
+    c = torch.zeros(96, 136, device=cuda)
+    text = handle_text(ir.matmul_f32_kernel(96, 136, 200))
+    assert lib.emmyb200_launch_workspace_bytes(text.encode()) > 0
+    assert launch(lib, text, [a.to(cuda), b.to(cuda), c]) == 0
+    assert reference.compare(c.cpu().numpy(), (a.double() @ b.double()).numpy(), 1e-3, 1e-3)["ok"]
+
+
+def test_launch_rejects_what_it_cannot_run(cuda, lib):
+    import torch
+    from emmyptx import ir
+    text = handle_text(ir.pointwise_kernel(64))
+    x = torch.zeros(64, device=cuda)
+    assert launch(lib, text, [x]) == -1                               # one parameter short
+    assert b"arg_order" in lib.emmyb200_last_error()
+    assert lib.emmyb200_launch(b"not json", None, 0, None, 0, None) == -1
+    broken = json.loads(text)
+    broken["variant"] = "frobnicate"
+    assert launch(lib, json.dumps(broken), [x, x]) == -4
