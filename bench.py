@@ -51,6 +51,8 @@ WORKLOADS = {
     "c3": "fp16 GEMM M=N=K=4096, fp32 accumulate, fp16 out",
     "c4": "bf16 GEMM + tanh-GELU epilogue M=N=K=16384, fp32 accumulate, bf16 out, M-row shards",
     "c5": "bf16 attention fwd B16 H16 S4096 d128, non-causal, fp32 softmax, (batch x head) shards",
+    "causal": "bf16 causal attention fwd, 64 units of S4096 d128 (the two-tiles-per-CTA kernel form; not one of the five configurations)",
+    "lerp": "fp32 x + 0.3*(y - x) over 2^26 elements, two inputs, through the general elementwise kernel (program as data; not one of the five configurations)",
     "f32mm": "fp32 matmul M=N=K=4096 with fp32 accuracy (three-way bf16 split on the tensor cores; not one of the five configurations)",
     "softmax": "fp32 softmax over the last axis of [65536, 1024] (the row kernels; not one of the five configurations)",
 }
@@ -416,6 +418,56 @@ class RowWorkload(PointwiseWorkload):
                 "rule": "isclose(rtol=1e-3, atol=1e-5) against torch CPU float64 (tools/torch_cases/fused.py:6)"}
 
 
+class ProgramWorkload(PointwiseWorkload):
+    """torch.lerp(x, y, 0.3) (tools/torch_cases/pointwise.py:47 `p_lerp`) compiled from IR by the facade to a program for
+    the general elementwise kernel: 12 bytes per element (two reads, one write)."""
+
+    def __init__(self, n, rank, world, dev):
+        import json as _json
+        import torch
+        from emmyptx import ir, runtime
+        from emmyptx.kernel import compile_kernel
+        self.rt, self.torch, self.world, self.name, self.n = runtime, torch, world, "lerp", n
+        built = ir.elementwise_kernel(n, {"x": "f32", "y": "f32"}, [("d", "subtract", ["y", "x"]), ("w", "multiply", ["d", 0.3]), ("o", "add", ["x", "w"])])
+        self.handle = _json.loads(compile_kernel(*built))
+        assert self.handle["variant"] == "pointwise_program"
+        g = torch.Generator(device=dev)
+        g.manual_seed(rank)
+        self.x = torch.randn(n, device=dev, generator=g)
+        self.x2 = torch.randn(n, device=dev, generator=g)
+        self.y = torch.empty_like(self.x)
+
+    def step(self):
+        self.rt.pointwise_program(self.handle["params"]["program"], [self.x, self.x2], self.y)
+
+    kernel_only = step
+
+    def work_per_step(self):
+        return 12.0 * self.n * self.world
+
+    def kernel_work_per_launch(self):
+        return 12.0 * self.n
+
+    def e2e_setup(self):
+        self.host = {"x": self.x.cpu().pin_memory(), "x2": self.x2.cpu().pin_memory(), "y": self.torch.empty_like(self.y, device="cpu").pin_memory()}
+        return self.n * 8, self.n * 4
+
+    def e2e_step(self):
+        self.x.copy_(self.host["x"], non_blocking=True)
+        self.x2.copy_(self.host["x2"], non_blocking=True)
+        self.step()
+        self.host["y"].copy_(self.y, non_blocking=True)
+
+    def parity(self):
+        t = self.torch
+        idx = t.arange(0, self.n, max(1, self.n // 2**20), device=self.x.device)
+        x, y = self.x[idx].cpu().double(), self.x2[idx].cpu().double()
+        ref = x + 0.3 * (y - x)
+        err = (self.y[idx].cpu().double() - ref).abs() / (1e-6 + 1e-6 * ref.abs())
+        return {"checked_elements": int(idx.numel()), "worst_ratio": float(err.max()), "ok": bool(err.max() <= 1.0),
+                "rule": "isclose(rtol=1e-6, atol=1e-6) against torch CPU float64 (tools/torch_cases/__init__.py:17)"}
+
+
 class GatherWorkload(PointwiseWorkload):
     dtype = "i32"
 
@@ -448,10 +500,11 @@ class GatherWorkload(PointwiseWorkload):
 class AttentionWorkload(Workload):
     metric, unit, dtype, bound = "attention_tflops", "TFLOP/s", "bf16", "tensor"
 
-    def __init__(self, units, seq, d, rank, world, dev, gather=True):
+    def __init__(self, units, seq, d, rank, world, dev, gather=True, causal=False):
         import torch
         from emmyptx import runtime
         self.rt, self.torch = runtime, torch
+        self.causal = causal
         self.name = "c5"
         self.units, self.seq, self.d, self.world, self.rank = units, seq, d, world, rank
         self.local = units // world
@@ -493,19 +546,22 @@ class AttentionWorkload(Workload):
             self.rt.attention_allgather(self.q, self.k, self.v, self.dst, multicast=self.mode == "multicast")
             self.peers.barrier()
             return
-        self.rt.attention(self.q, self.k, self.v, out=self.o)
+        self.rt.attention(self.q, self.k, self.v, causal=self.causal, out=self.o)
         if self.gather:
             import torch.distributed as dist
             dist.all_gather_into_tensor(self.o_full, self.o)
 
     def kernel_only(self):
-        self.rt.attention(self.q, self.k, self.v, out=self.o)
+        self.rt.attention(self.q, self.k, self.v, causal=self.causal, out=self.o)
+
+    def pairs(self):
+        return self.seq * (self.seq + 1) / 2 if self.causal else float(self.seq) * self.seq
 
     def work_per_step(self):
-        return 4.0 * self.units * self.seq * self.seq * self.d
+        return 4.0 * self.units * self.pairs() * self.d
 
     def kernel_work_per_launch(self):
-        return 4.0 * self.local * self.seq * self.seq * self.d
+        return 4.0 * self.local * self.pairs() * self.d
 
     def parity(self, rows_per_unit: int = 64):
         """O as the last pass left it against the torch CPU fp32 evaluation of softmax(q k^T / sqrt(d)) v, on seeded
@@ -527,7 +583,10 @@ class AttentionWorkload(Workload):
                 fixed = [0, 127, 128, self.seq - 1]
                 pick = sorted(set(fixed) | set(t.randint(0, self.seq, (rows_per_unit - len(fixed),), generator=g).tolist()))
                 qs, ks, vs = q[u][pick].float().cpu(), k[u].float().cpu(), v[u].float().cpu()
-                ref = t.softmax(qs @ ks.t() * self.d ** -0.5, -1) @ vs
+                sc = qs @ ks.t() * self.d ** -0.5
+                if self.causal:
+                    sc = sc.masked_fill(t.arange(self.seq)[None, :] > t.tensor(pick)[:, None], float("-inf"))
+                ref = t.softmax(sc, -1) @ vs
                 got = self.o_full[owner * self.local + u][pick].float().cpu()
                 bound = 1e-2 * ref.abs() + 1e-2 * ref.std()
                 worst = max(worst, float(((got - ref).abs() / bound).max()))
@@ -565,6 +624,10 @@ def make_workload(name, rank, world, dev, size=None):
         return PointwiseWorkload(size or 2**20, rank, world, dev)
     if name == "c2":
         return GatherWorkload(size or 2**26, rank, world, dev)
+    if name == "causal":
+        return AttentionWorkload(size or 64, 4096, 128, rank, world, dev, gather=False, causal=True)
+    if name == "lerp":
+        return ProgramWorkload(size or 2**26, rank, world, dev)
     if name == "softmax":
         return RowWorkload("softmax", size or 65536 * 1024, rank, world, dev)
     if name == "f32mm":
@@ -659,6 +722,16 @@ def cpu_reference_step(name: str, threads: int, full: bool = False):
         x = torch.from_numpy(inputs.c2_input(n))
         fn = lambda: reference.c2_torch(x)
         return fn, 8.0 * n, 1e9, "the full 2^26 array, torch CPU int32/int64"
+    if name == "causal":
+        g = torch.Generator().manual_seed(0)
+        q, kk, v = (torch.randn(2, 4096, 128, generator=g).to(torch.bfloat16) for _ in range(3))
+        fn = lambda: torch.nn.functional.scaled_dot_product_attention(q, kk, v, is_causal=True)
+        return fn, 4.0 * 2 * 4096 * 4097 / 2 * 128, 1e12, "2 of 64 units, torch CPU bf16 causal SDPA"
+    if name == "lerp":
+        g = torch.Generator().manual_seed(0)
+        x, y = torch.randn(2**24, generator=g), torch.randn(2**24, generator=g)
+        fn = lambda: torch.lerp(x, y, 0.3)
+        return fn, 12.0 * x.numel(), 1e9, "2^24 of 2^26 elements, torch CPU fp32"
     if name == "f32mm":
         g = torch.Generator().manual_seed(0)
         a, b = torch.randn(4096, 4096, generator=g), torch.randn(4096, 4096, generator=g)
@@ -684,9 +757,10 @@ def time_cpu(fn, budget_s: float = 12.0, min_reps: int = 2) -> float:
     return best
 
 
-METRIC = {"c1": "elementwise_gbs", "c2": "elementwise_gbs", "softmax": "elementwise_gbs", "c5": "attention_tflops"}
-DTYPE = {"c1": "f32", "c2": "i32", "c3": "f16", "softmax": "f32", "f32mm": "f32"}
-SCALING = {"c1": "weak", "c2": "weak", "softmax": "weak", "f32mm": "weak"}
+METRIC = {"c1": "elementwise_gbs", "c2": "elementwise_gbs", "softmax": "elementwise_gbs", "lerp": "elementwise_gbs", "c5": "attention_tflops",
+          "causal": "attention_tflops"}
+DTYPE = {"c1": "f32", "c2": "i32", "c3": "f16", "softmax": "f32", "f32mm": "f32", "lerp": "f32"}
+SCALING = {"c1": "weak", "c2": "weak", "softmax": "weak", "f32mm": "weak", "lerp": "weak", "causal": "weak"}
 
 
 def config_for(workload: str, world: int, size=None) -> dict:
@@ -694,7 +768,7 @@ def config_for(workload: str, world: int, size=None) -> dict:
     `collective` and `inner_repeats` on the GPU arm, `cpu_baseline.sample` on the CPU arm)."""
     return {"workload": WORKLOADS[workload] + (f" [SIZE OVERRIDE {size}: not the benchmark configuration]" if size else ""),
             "l2": "8 MiB working set, L2-resident by construction of the configuration" if workload == "c1" else "inputs larger than L2",
-            "parallelism": f"rows/{world}" if workload in ("c3", "c4") else (f"units/{world}" if workload == "c5" else f"chunks/{world}")}
+            "parallelism": f"rows/{world}" if workload in ("c3", "c4") else (f"units/{world}" if workload in ("c5", "causal") else f"chunks/{world}")}
 
 
 def run_reference(args, rank: int) -> int:
@@ -958,14 +1032,15 @@ def other_workloads(torch, dist, dev, local_rank, pk, pk_kind, skip: str) -> dic
             out[f"row_{op}_65536x1024"] = {"value": byts / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms": ms,
                                            "frac_of_peak": byts / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "peak_used": f"{pk_kind} copy bandwidth"}
         del x, y
-        q, k, v = (torch.randn(64, 4096, 128, device=dev).to(torch.bfloat16) for _ in range(3))
-        o = torch.empty_like(q)
-        ms = timed(torch, dist, 1, lambda: runtime.attention(q, k, v, causal=True, out=o), 20, 3) / 20
-        flop = 4.0 * 64 * 128 * (4096 * 4097 / 2)
-        out["attention_causal_64x4096x128"] = {"value": flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": ms,
-                                               "frac_of_peak": flop / (ms * 1e-3) / 1e12 / pk.get("bf16_tflops", 1.0),
-                                               "peak_used": f"{pk_kind} cuBLAS bf16, burst"}
-        del q, k, v, o
+        for name in ("causal", "lerp"):
+            wl = make_workload(name, 0, 1, dev)
+            m = measure(torch, dist, 1, local_rank, wl, 5, 3, pk, pk_kind, None)
+            out[name] = {"workload": WORKLOADS[name], "value": m["value"], "unit": wl.unit, "ms": m["ms_per_step"], "roofline": m["roofline"],
+                         "frac_of_peak": m["roofline"]["frac"], "peak_used": m["roofline"]["peak_source"], "parity": m["parity"], "e2e": m["e2e"]}
+            if wl.bound == "tensor":
+                out[name]["value_burst"] = m["roofline"]["achieved_burst"]
+            del wl
+            torch.cuda.empty_cache()
     except Exception as e:  # noqa: BLE001
         out["next_rows"] = {"error": str(e)[:200]}
     return out

@@ -236,6 +236,18 @@ EMMY_HD float emmy_cosf(float x) {
     return emmy_sincos_kernel(r, q + 1);
 }
 
+// ---- sigmoid, SiLU, ReLU -------------------------------------------------------------------
+// 1 / (1 + e^-x): the exponential above, one add and the refined reciprocal; |x| > 86 is handled apart (1 above,
+// e^x below -- where 1 + e^-x would overflow -- and NaN passed through). About 2 ulp; the reference's class for these
+// cases is rtol = atol = 1e-5 (tools/torch_cases/pointwise.py:17, 23).
+EMMY_HD float emmy_sigmoidf(float x) {
+    if (fabsf(x) <= 86.0f) return emmy_rcp(emmy_add(1.0f, emmy_exp_core(-x)));
+    if (x != x) return emmy_add(x, x);
+    return x > 0.0f ? 1.0f : emmy_expf(x);
+}
+EMMY_HD float emmy_siluf(float x) { return emmy_mul(x, emmy_sigmoidf(x)); }
+EMMY_HD float emmy_reluf(float x) { return x < 0.0f ? 0.0f : x; }       // NaN stays NaN
+
 // ---- GELU, tanh form ------------------------------------------------------------------------
 // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), each step rounded to fp32 in the order torch's
 // kernel takes them (the composition the reference's case `p_gelu_tanh` traces,

@@ -129,6 +129,26 @@ __device__ __forceinline__ float2 exp_sin_tanh2(float2 x) {
     return make_float2(__fadd_rn(e.x, __fmul_rn(s.x, t.x)), __fadd_rn(e.y, __fmul_rn(s.y, t.y)));
 }
 
+// sigmoid and SiLU of both lanes, |x| <= 86 (bit-identical to emmy_sigmoidf / emmy_siluf there).
+__device__ __forceinline__ float2 sigmoid2(float2 x) {
+    const float2 e = exp_core2(make_float2(-x.x, -x.y));
+    const float2 d = add2(f2(1.0f), e);
+    return make_float2(emmy_rcp(d.x), emmy_rcp(d.y));
+}
+__device__ __forceinline__ float2 silu2(float2 x) {
+    const float2 sg = sigmoid2(x);
+    return make_float2(__fmul_rn(x.x, sg.x), __fmul_rn(x.y, sg.y));
+}
+// tanh-form GELU of both lanes, each step rounded as in emmy_gelu_tanhf (scalar products and sums where a packed
+// multiply would feed a packed add: the assembler fuses those).
+__device__ __forceinline__ float2 gelu_tanh2(float2 x) {
+    const float x3x = __fmul_rn(__fmul_rn(x.x, x.x), x.x), x3y = __fmul_rn(__fmul_rn(x.y, x.y), x.y);
+    const float ix = __fmul_rn(0.7978845608028654f, __fadd_rn(x.x, __fmul_rn(0.044715f, x3x)));
+    const float iy = __fmul_rn(0.7978845608028654f, __fadd_rn(x.y, __fmul_rn(0.044715f, x3y)));
+    const float2 t = tanh2(make_float2(ix, iy));
+    return make_float2(__fmul_rn(__fmul_rn(0.5f, x.x), __fadd_rn(1.0f, t.x)), __fmul_rn(__fmul_rn(0.5f, x.y), __fadd_rn(1.0f, t.y)));
+}
+
 // Largest |x| (of all lanes) for which the packed form of each op is valid; NaN fails every bound.
 template <int OP> struct PackedOp { static constexpr bool kHas = false; };
 template <> struct PackedOp<EMMYB200_OP_EXP_SIN_TANH> {
@@ -150,6 +170,21 @@ template <> struct PackedOp<EMMYB200_OP_COS> {
     static constexpr bool kHas = true;
     static constexpr float kBound = EMMY_TRIG_FAST_MAX;
     static __device__ __forceinline__ float2 apply(float2 x) { return cos2(x); }
+};
+template <> struct PackedOp<EMMYB200_OP_SIGMOID> {
+    static constexpr bool kHas = true;
+    static constexpr float kBound = 86.0f;
+    static __device__ __forceinline__ float2 apply(float2 x) { return sigmoid2(x); }
+};
+template <> struct PackedOp<EMMYB200_OP_SILU> {
+    static constexpr bool kHas = true;
+    static constexpr float kBound = 86.0f;
+    static __device__ __forceinline__ float2 apply(float2 x) { return silu2(x); }
+};
+template <> struct PackedOp<EMMYB200_OP_GELU_TANH> {
+    static constexpr bool kHas = true;
+    static constexpr float kBound = 1.0e12f;           // beyond it x^3 overflows: the scalar function is called
+    static __device__ __forceinline__ float2 apply(float2 x) { return gelu_tanh2(x); }
 };
 template <> struct PackedOp<EMMYB200_OP_TANH> {
     static constexpr bool kHas = true;

@@ -113,7 +113,7 @@ int code_of(const char* const* names, int count, const std::string& name) {
     return -1;
 }
 
-const char* const kPointwiseOps[] = {"exp_sin_tanh", "exp", "sin", "cos", "tanh", "gelu_tanh"};
+const char* const kPointwiseOps[] = {"exp_sin_tanh", "exp", "sin", "cos", "tanh", "gelu_tanh", "sigmoid", "silu", "relu"};
 const char* const kProgramOps[] = {"add", "subtract", "multiply", "divide", "maximum", "minimum", "relu", "square", "copy", "negative",
                                    "abs", "reciprocal", "sqrt", "rsqrt", "exp", "log", "sigmoid", "tanh", "erf", "sin", "cos", "pow",
                                    "equal", "not_equal", "greater", "less", "greater_equal", "less_equal", "where", "bitwise_and",
@@ -279,7 +279,7 @@ extern "C" int emmyb200_launch(const char* handle_json, void* const* params, int
             if (a.buffer(name.str) == nullptr) return fail(EMMYB200_ERR_ARG, "launch: buffer '%s' is null or not in arg_order", name.str.c_str());
     void* out = a.output();
     if (v == "pointwise_f32") {
-        const int op = code_of(kPointwiseOps, 6, gets(p, "op"));
+        const int op = code_of(kPointwiseOps, (int)(sizeof(kPointwiseOps) / sizeof(kPointwiseOps[0])), gets(p, "op"));
         if (op < 0) return fail(EMMYB200_ERR_ARG, "launch: unknown pointwise op");
         return emmyb200_pointwise_f32(op, (const float*)a.input(0), (float*)out, geti(p, "n"), cuda_stream);
     }

@@ -19,6 +19,9 @@ __device__ __forceinline__ float apply_op(float x) {
     else if constexpr (OP == EMMYB200_OP_SIN) return emmy_sinf(x);
     else if constexpr (OP == EMMYB200_OP_COS) return emmy_cosf(x);
     else if constexpr (OP == EMMYB200_OP_TANH) return emmy_tanhf(x);
+    else if constexpr (OP == EMMYB200_OP_SIGMOID) return emmy_sigmoidf(x);
+    else if constexpr (OP == EMMYB200_OP_SILU) return emmy_siluf(x);
+    else if constexpr (OP == EMMYB200_OP_RELU) return emmy_reluf(x);
     else return emmy_gelu_tanhf(x);
 }
 
@@ -108,6 +111,9 @@ extern "C" int emmyb200_pointwise_f32(int op, const float* x, float* y, int64_t 
         case EMMYB200_OP_COS: return launch_pointwise<EMMYB200_OP_COS>(x, y, n, s);
         case EMMYB200_OP_TANH: return launch_pointwise<EMMYB200_OP_TANH>(x, y, n, s);
         case EMMYB200_OP_GELU_TANH: return launch_pointwise<EMMYB200_OP_GELU_TANH>(x, y, n, s);
+        case EMMYB200_OP_SIGMOID: return launch_pointwise<EMMYB200_OP_SIGMOID>(x, y, n, s);
+        case EMMYB200_OP_SILU: return launch_pointwise<EMMYB200_OP_SILU>(x, y, n, s);
+        case EMMYB200_OP_RELU: return launch_pointwise<EMMYB200_OP_RELU>(x, y, n, s);
         default: return fail(EMMYB200_ERR_ARG, "pointwise: unknown op %d", op);
     }
 }

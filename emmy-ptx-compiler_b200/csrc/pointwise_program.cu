@@ -107,11 +107,19 @@ struct PwArgs {
 };
 
 // VEC: all buffers are aligned for 128-bit (fp32) / 64-bit (16-bit types) accesses of four elements.
-template <bool VEC>
-__global__ void __launch_bounds__(kPwThreads) pointwise_program_kernel(const __grid_constant__ emmyb200_pw_program prog, PwArgs args) {
+// FAST: no step writes an input's slot, so inputs and forwarded results may stay in registers (see below).
+constexpr uint8_t kPwStore = 1;       // step.reserved[1]: the result must also go to its slot
+template <bool VEC, bool FAST>
+__global__ void __launch_bounds__(kPwThreads, 3) pointwise_program_kernel(const __grid_constant__ emmyb200_pw_program prog, PwArgs args) {
     // Per-thread value slots, indexed by the program: they live in local memory, i.e. in L1 for the few slots a
-    // program touches, and do not cap the number of resident threads the way a shared-memory file would.
+    // program touches, and do not cap the number of resident threads the way a shared-memory file would. L1 traffic
+    // is what bounds a naive interpreter (every step reads two or three slots and writes one), so values bypass the
+    // slot file wherever the program's shape allows: the inputs stay in registers (picked by a uniform switch), the
+    // result of a step is forwarded to the next step in registers, and a result is written to its slot only when a
+    // later step (other than the next) or the output needs it -- the host marks those steps (kPwStore). A chain of
+    // unary / binary ops, the usual shape of an activation function, then touches no local memory at all.
     float4 slots[kPwSlots][kPwUnroll];
+    float4 in0[kPwUnroll], in1[kPwUnroll], in2[kPwUnroll], in3[kPwUnroll], acc[kPwUnroll];
     const int tid = threadIdx.x;
     const int64_t groups = VEC ? args.n / 4 : (args.n + 3) / 4;
     const int64_t stride = (int64_t)gridDim.x * kPwThreads;
@@ -146,15 +154,24 @@ __global__ void __launch_bounds__(kPwThreads) pointwise_program_kernel(const __g
                         v.w = i + 3 < args.n ? pw_load1(args.in[k], prog.in_dtype[k], i + 3) : 0.0f;
                     }
                 }
-                slots[k][u] = v;
+                if (k == 0) in0[u] = v;
+                else if (k == 1) in1[u] = v;
+                else if (k == 2) in2[u] = v;
+                else in3[u] = v;
+                if (!FAST) slots[k][u] = v;
             }
         }
+        int prev_dst = -1;
         for (int s = 0; s < prog.n_steps; ++s) {
             const emmyb200_pw_step st = prog.steps[s];
 #pragma unroll
             for (int u = 0; u < kPwUnroll; ++u) {
                 auto operand = [&](int o) {
                     if (o >= kPwSlots) { const float c = prog.consts[o - kPwSlots]; return make_float4(c, c, c, c); }
+                    if (FAST) {
+                        if (o == prev_dst) return acc[u];
+                        if (o < prog.n_inputs) return o == 0 ? in0[u] : (o == 1 ? in1[u] : (o == 2 ? in2[u] : in3[u]));
+                    }
                     return slots[o][u];
                 };
                 const float4 a = operand(st.a), b = operand(st.b), c = operand(st.c);
@@ -163,14 +180,18 @@ __global__ void __launch_bounds__(kPwThreads) pointwise_program_kernel(const __g
                 r.y = pw_apply(st.op, a.y, b.y, c.y);
                 r.z = pw_apply(st.op, a.z, b.z, c.z);
                 r.w = pw_apply(st.op, a.w, b.w, c.w);
-                slots[st.dst][u] = r;
+                if (!FAST || (st.reserved[1] & kPwStore)) slots[st.dst][u] = r;
+                acc[u] = r;
             }
+            prev_dst = st.dst;
         }
 #pragma unroll
         for (int u = 0; u < kPwUnroll; ++u) {
             const int64_t g = g0 + u * stride;
             if (g >= groups) continue;
-            const float4 y = slots[prog.out_slot][u];
+            const int os = prog.out_slot;
+            const float4 y = !FAST ? slots[os][u]
+                                   : (os == prev_dst ? acc[u] : (os < prog.n_inputs ? (os == 0 ? in0[u] : (os == 1 ? in1[u] : (os == 2 ? in2[u] : in3[u]))) : slots[os][u]));
             if constexpr (VEC) {
                 if (prog.out_dtype == EMMYB200_F32) {
                     __stcs(reinterpret_cast<float4*>(args.out) + g, y);
@@ -326,7 +347,29 @@ extern "C" int emmyb200_pointwise_program(const emmyb200_pw_program* prog, const
         pointwise_program_int_kernel<<<(unsigned)(want_i < cap ? want_i : cap), kPwThreads, 0, s>>>(*prog, args);
         return launch_status("pointwise_program_int_kernel");
     }
-    if (vec) pointwise_program_kernel<true><<<blocks, kPwThreads, 0, s>>>(*prog, args);
-    else pointwise_program_kernel<false><<<blocks, kPwThreads, 0, s>>>(*prog, args);
+    // Which results must reach the slot file: those read by a step other than the next one before they are overwritten,
+    // or (the last definition of the output slot, unless it is the last step) by the store. Inputs stay in registers
+    // as long as no step writes their slots.
+    emmyb200_pw_program marked = *prog;
+    bool fast = true;
+    for (int i = 0; i < marked.n_steps; ++i) {
+        const int dst = marked.steps[i].dst;
+        if (dst < marked.n_inputs) fast = false;
+        bool needed = false;
+        for (int j = i + 1; j < marked.n_steps; ++j) {
+            const emmyb200_pw_step& later = marked.steps[j];
+            if (j > i + 1 && (later.a == dst || later.b == dst || later.c == dst)) needed = true;
+            if (later.dst == dst) { if (j == i + 1) {} break; }
+            if (j == marked.n_steps - 1 && dst == marked.out_slot) needed = true;
+        }
+        marked.steps[i].reserved[1] = needed ? kPwStore : 0;
+    }
+    if (vec) {
+        if (fast) pointwise_program_kernel<true, true><<<blocks, kPwThreads, 0, s>>>(marked, args);
+        else pointwise_program_kernel<true, false><<<blocks, kPwThreads, 0, s>>>(marked, args);
+    } else {
+        if (fast) pointwise_program_kernel<false, true><<<blocks, kPwThreads, 0, s>>>(marked, args);
+        else pointwise_program_kernel<false, false><<<blocks, kPwThreads, 0, s>>>(marked, args);
+    }
     return launch_status("pointwise_program_kernel");
 }

@@ -212,6 +212,7 @@ POINTWISE_F64 = {
     "exp_sin_tanh": lambda x: np.exp(x) + np.sin(x) * np.tanh(x),
     "exp": np.exp, "sin": np.sin, "cos": np.cos, "tanh": np.tanh,
     "gelu_tanh": lambda x: 0.5 * x * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * x**3))),
+    "sigmoid": lambda x: 1.0 / (1.0 + np.exp(-x)), "silu": lambda x: x / (1.0 + np.exp(-x)), "relu": lambda x: np.maximum(x, 0.0),
 }
 
 

@@ -15,7 +15,7 @@ LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libemmyb200.so"
 F32, F16, BF16, I32 = 0, 1, 2, 3
 OP_EXP_SIN_TANH, OP_EXP, OP_SIN, OP_COS, OP_TANH, OP_GELU_TANH = range(6)
 POINTWISE_OPS = {"exp_sin_tanh": OP_EXP_SIN_TANH, "exp": OP_EXP, "sin": OP_SIN, "cos": OP_COS,
-                 "tanh": OP_TANH, "gelu_tanh": OP_GELU_TANH}
+                 "tanh": OP_TANH, "gelu_tanh": OP_GELU_TANH, "sigmoid": 6, "silu": 7, "relu": 8}
 PW_MAX_SLOTS, PW_MAX_CONSTS, PW_MAX_STEPS, PW_MAX_INPUTS = 16, 16, 48, 4
 PW_OPS = {name: i for i, name in enumerate(
     ["add", "subtract", "multiply", "divide", "maximum", "minimum", "relu", "square", "copy", "negative", "abs", "reciprocal",

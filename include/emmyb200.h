@@ -56,6 +56,9 @@ const char* emmyb200_last_error(void);
 #define EMMYB200_OP_COS 3
 #define EMMYB200_OP_TANH 4
 #define EMMYB200_OP_GELU_TANH 5
+#define EMMYB200_OP_SIGMOID 6     /* 1 / (1 + exp(-x)); tools/torch_cases/pointwise.py:17 */
+#define EMMYB200_OP_SILU 7        /* x * sigmoid(x); pointwise.py:23 */
+#define EMMYB200_OP_RELU 8        /* pointwise.py:19 */
 int emmyb200_pointwise_f32(int op, const float* x, float* y, int64_t n, void* cuda_stream);
 
 /* Any other straight-line elementwise expression over up to 4 same-sized inputs: the cell program of a

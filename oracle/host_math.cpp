@@ -11,6 +11,9 @@ extern "C" void emmy_host_apply(int op, const float* x, float* y, long n) {
             case 2: y[i] = emmy_sinf(v); break;
             case 3: y[i] = emmy_cosf(v); break;
             case 4: y[i] = emmy_tanhf(v); break;
+            case 6: y[i] = emmy_sigmoidf(v); break;
+            case 7: y[i] = emmy_siluf(v); break;
+            case 8: y[i] = emmy_reluf(v); break;
             default: y[i] = emmy_gelu_tanhf(v); break;
         }
     }

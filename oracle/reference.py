@@ -24,6 +24,7 @@ UNARY_F64 = {
     "exp": np.exp, "sin": np.sin, "cos": np.cos, "tanh": np.tanh,
     "gelu_tanh": lambda x: 0.5 * x * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (x + 0.044715 * x**3))),
     "exp_sin_tanh": lambda x: np.exp(x) + np.sin(x) * np.tanh(x),
+    "sigmoid": lambda x: 1.0 / (1.0 + np.exp(-x)), "silu": lambda x: x / (1.0 + np.exp(-x)), "relu": lambda x: np.maximum(x, 0.0),
 }
 
 

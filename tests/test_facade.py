@@ -279,3 +279,13 @@ def test_scalar_parameters_become_launch_time_constants():
     # a scalar no step uses changes nothing
     h2 = handle(ir.elementwise_kernel(256, {"x": "f32"}, [("o", "exp", ["x"])], scalars={"unused": "f32"}))
     assert h2["variant"] == "pointwise_f32" and h2["params"]["op"] == "exp"
+
+
+def test_common_activations_map_to_streaming_ops():
+    """sigmoid, SiLU and ReLU however spelled land on the fixed-function streaming kernel, not on the interpreter."""
+    h = handle(ir.elementwise_kernel(4096, {"x": "f32"}, [("s", "sigmoid", ["x"]), ("y", "multiply", ["x", "s"])]))
+    assert (h["variant"], h["params"]["op"]) == ("pointwise_f32", "silu")
+    h = handle(ir.elementwise_kernel(4096, {"x": "f32"}, [("n", "negative", ["x"]), ("e", "exp", ["n"]), ("d", "add", ["e", 1.0]), ("y", "reciprocal", ["d"])]))
+    assert (h["variant"], h["params"]["op"]) == ("pointwise_f32", "sigmoid")
+    h = handle(ir.elementwise_kernel(4096, {"x": "f32"}, [("y", "maximum", ["x", 0.0])]))
+    assert (h["variant"], h["params"]["op"]) == ("pointwise_f32", "relu")

@@ -63,6 +63,28 @@ def test_c1_composite(cuda):
     assert reference.c1_condition_ulp(got, x).max() <= reference.c1_condition_ulp(t32, x).max() + 3.0
 
 
+@pytest.mark.parametrize("op", ["sigmoid", "silu", "relu"])
+def test_activation_ops(op, cuda):
+    """p_sigmoid, p_silu, p_relu (tools/torch_cases/pointwise.py:17-23) as streaming ops: the reference's class
+    (rtol = atol = 1e-5), a few ulp on normal results, NaN and infinities as torch gives them, and the packed path
+    (aligned buffer) bit-identical to the scalar one (a view 4 bytes into the allocation)."""
+    import torch
+    from emmyptx import runtime
+    x = np.concatenate([inputs.c1_input(2**18) * 5, np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 87.0, -87.0, -100.0, 1e30], np.float32)])
+    got = _run(op, x, cuda)
+    with np.errstate(all="ignore"):
+        ref = reference.UNARY_F64[op](x.astype(np.float64))
+    assert np.array_equal(np.isnan(got), np.isnan(ref))
+    fin = np.isfinite(ref) & (np.abs(ref) > 1e-30)
+    assert reference.compare(got[fin], ref[fin], 1e-5, 1e-5)["ok"]
+    assert reference.ulp_error(got[fin], ref[fin]).max() <= 4.0
+    xd = torch.from_numpy(np.concatenate([[0.0], x]).astype(np.float32)).to(cuda)
+    shifted = torch.zeros_like(xd)
+    runtime.pointwise(op, xd[1:], out=shifted[1:])
+    torch.cuda.synchronize()
+    assert np.array_equal(shifted[1:].cpu().numpy(), got, equal_nan=True)
+
+
 def test_gelu_tanh(cuda):
     x = (np.random.default_rng(0).standard_normal(2**18) * 3).astype(np.float32)
     got = _run("gelu_tanh", x, cuda)
