@@ -4,8 +4,9 @@
 
 One nvcc process per translation unit (in parallel), then one link. Objects are rebuilt when
 their source, a header they might include, or this script is newer. The library links the CUDA
-runtime statically and looks the one driver entry point it needs (cuTensorMapEncodeTiled) up at
-run time, so it loads on a machine without a GPU driver and fails only when a kernel is asked for.
+runtime statically and looks the one driver entry point it needs (cuTensorMapEncodeTiled) and the
+run-time compiler (libnvrtc, for elementwise programs) up at run time, so it loads on a machine without a
+GPU driver and fails only when a kernel is asked for.
 """
 from __future__ import annotations
 
@@ -22,8 +23,7 @@ OBJ = HERE / "build"
 LIB = HERE / "lib" / "libemmyb200.so"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
-         *os.environ.get("EMMYB200_NVCC_EXTRA", "").split()]        # development builds only (tracing macros)
+         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v", "-I", str(OBJ)]
 
 
 def _newest_header() -> float:
@@ -45,14 +45,25 @@ def _compile(src: Path, force: bool, verbose: bool) -> Path:
     return obj
 
 
+def _embed_math_header() -> None:
+    """emmy_math.cuh as a string literal: the kernels compiled at run time (pointwise_jit.cu) include it by name."""
+    text = (CSRC / "emmy_math.cuh").read_text()
+    assert ')EMMYTEXT"' not in text
+    inc = OBJ / "emmy_math_text.inc"
+    body = 'R"EMMYTEXT(' + text + ')EMMYTEXT"\n'
+    if not inc.exists() or inc.read_text() != body:
+        inc.write_text(body)
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
     OBJ.mkdir(exist_ok=True)
     LIB.parent.mkdir(exist_ok=True)
+    _embed_math_header()
     sources = sorted(CSRC.glob("*.cu"))
     with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
         objs = list(pool.map(lambda s: _compile(s, force, verbose), sources))
     if force or not LIB.exists() or LIB.stat().st_mtime < max(o.stat().st_mtime for o in objs):
-        cmd = [NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-cudart", "static"]
+        cmd = [NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-cudart", "static", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             raise RuntimeError(f"link failed:\n{r.stderr}")

@@ -1,0 +1,535 @@
+// Elementwise programs compiled at first use: the cell program of a one-axis `Tile` becomes the body of a
+// kernel specialised to it, as the reference prints the instructions of each `Assign` into the kernel it is
+// compiling (emmyptx/kernel.py:766-784, emmyptx/ops.py:212-290).
+//
+// The program (include/emmyb200.h, emmyb200_pw_program) is turned into CUDA C++ text: one straight-line
+// `cell()` function over named registers, inside a fixed streaming shell (128-bit accesses, two vectors in
+// flight per thread, grid capped at a multiple of the SM count). The text is compiled for sm_100a by NVRTC,
+// loaded through the runtime's library interface, and cached under the program's shape: op sequence, operand
+// wiring, dtypes, how each input is broadcast and which vector accesses the buffers allow. Constants and
+// broadcast extents are kernel arguments, so changing a scalar parameter does not compile again.
+//
+// Every op is spelled exactly as in the interpreter of pointwise_program.cu (explicit round-to-nearest
+// intrinsics, the functions of emmy_math.cuh, which travels inside this library as text), so the two forms give
+// the same bits (the sign and payload of a NaN aside); the interpreter remains the form used when NVRTC cannot be loaded, and for integer programs.
+#include <ctype.h>
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nvrtc.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "pointwise_jit.h"
+
+namespace emmy {
+
+static const char kMathHeader[] =
+#include "emmy_math_text.inc"
+    ;
+
+static const char kStdintStub[] =
+    "#pragma once\n"
+    "typedef signed char int8_t; typedef unsigned char uint8_t; typedef short int16_t; typedef unsigned short uint16_t;\n"
+    "typedef int int32_t; typedef unsigned int uint32_t; typedef long long int64_t; typedef unsigned long long uint64_t;\n";
+static const char kEmptyStub[] = "#pragma once\n";
+static const char kMathStub[] = "#pragma once\n#ifndef INFINITY\n#define INFINITY (__int_as_float(0x7f800000))\n#endif\n";
+
+// ---- NVRTC, looked up at run time so that the library loads where the compiler is not installed ------------
+struct Nvrtc {
+    void* handle = nullptr;
+    nvrtcResult (*CreateProgram)(nvrtcProgram*, const char*, const char*, int, const char* const*, const char* const*) = nullptr;
+    nvrtcResult (*CompileProgram)(nvrtcProgram, int, const char* const*) = nullptr;
+    nvrtcResult (*GetCUBINSize)(nvrtcProgram, size_t*) = nullptr;
+    nvrtcResult (*GetCUBIN)(nvrtcProgram, char*) = nullptr;
+    nvrtcResult (*GetProgramLogSize)(nvrtcProgram, size_t*) = nullptr;
+    nvrtcResult (*GetProgramLog)(nvrtcProgram, char*) = nullptr;
+    nvrtcResult (*DestroyProgram)(nvrtcProgram*) = nullptr;
+    const char* (*GetErrorString)(nvrtcResult) = nullptr;
+    bool ok = false;
+};
+
+static const Nvrtc& nvrtc() {
+    static Nvrtc n = [] {
+        Nvrtc r;
+        const char* env = getenv("EMMYB200_NVRTC");
+        // the toolkit this library was built with first, so that logf / erff / powf are the same device functions
+        const char* names[] = {env, "/usr/local/cuda/lib64/libnvrtc.so.12", "libnvrtc.so.12", "libnvrtc.so"};
+        for (const char* name : names) {
+            if (name == nullptr || *name == 0) continue;
+            r.handle = dlopen(name, RTLD_NOW | RTLD_LOCAL);
+            if (r.handle != nullptr) break;
+        }
+        if (r.handle == nullptr) return r;
+        auto sym = [&](const char* s) { return dlsym(r.handle, s); };
+        r.CreateProgram = reinterpret_cast<decltype(r.CreateProgram)>(sym("nvrtcCreateProgram"));
+        r.CompileProgram = reinterpret_cast<decltype(r.CompileProgram)>(sym("nvrtcCompileProgram"));
+        r.GetCUBINSize = reinterpret_cast<decltype(r.GetCUBINSize)>(sym("nvrtcGetCUBINSize"));
+        r.GetCUBIN = reinterpret_cast<decltype(r.GetCUBIN)>(sym("nvrtcGetCUBIN"));
+        r.GetProgramLogSize = reinterpret_cast<decltype(r.GetProgramLogSize)>(sym("nvrtcGetProgramLogSize"));
+        r.GetProgramLog = reinterpret_cast<decltype(r.GetProgramLog)>(sym("nvrtcGetProgramLog"));
+        r.DestroyProgram = reinterpret_cast<decltype(r.DestroyProgram)>(sym("nvrtcDestroyProgram"));
+        r.GetErrorString = reinterpret_cast<decltype(r.GetErrorString)>(sym("nvrtcGetErrorString"));
+        r.ok = r.CreateProgram && r.CompileProgram && r.GetCUBINSize && r.GetCUBIN && r.GetProgramLogSize &&
+               r.GetProgramLog && r.DestroyProgram && r.GetErrorString;
+        return r;
+    }();
+    return n;
+}
+
+static std::atomic<int> g_jit_enabled{-1};        // -1: not decided yet (the environment is read once)
+
+static bool jit_enabled() {
+    int v = g_jit_enabled.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char* env = getenv("EMMYB200_PW_JIT");
+        v = (env != nullptr && env[0] == '0') ? 0 : 1;
+        g_jit_enabled.store(v, std::memory_order_relaxed);
+    }
+    return v != 0;
+}
+
+// ---- program -> CUDA C++ -----------------------------------------------------------------------------------
+// One expression per op, written with the same intrinsics as the interpreter's pw_apply() so that the two forms
+// agree bit for bit. A, B, C stand for the operands.
+static const char* op_expr(int op) {
+    switch (op) {
+        case EMMYB200_PW_ADD: return "__fadd_rn(A, B)";
+        case EMMYB200_PW_SUB: return "__fsub_rn(A, B)";
+        case EMMYB200_PW_MUL: return "__fmul_rn(A, B)";
+        case EMMYB200_PW_DIV: return "__fdiv_rn(A, B)";
+        case EMMYB200_PW_MAX: return "fmaxf(A, B)";
+        case EMMYB200_PW_MIN: return "fminf(A, B)";
+        case EMMYB200_PW_RELU: return "fmaxf(A, 0.0f)";
+        case EMMYB200_PW_SQUARE: return "__fmul_rn(A, A)";
+        case EMMYB200_PW_COPY: return "A";
+        case EMMYB200_PW_NEG: return "(-A)";
+        case EMMYB200_PW_ABS: return "fabsf(A)";
+        case EMMYB200_PW_RCP: return "__frcp_rn(A)";
+        case EMMYB200_PW_SQRT: return "__fsqrt_rn(A)";
+        case EMMYB200_PW_RSQRT: return "__frcp_rn(__fsqrt_rn(A))";
+        case EMMYB200_PW_EXP: return "emmy_expf(A)";
+        case EMMYB200_PW_LOG: return "logf(A)";
+        case EMMYB200_PW_SIGMOID: return "__frcp_rn(__fadd_rn(1.0f, emmy_expf(-A)))";
+        case EMMYB200_PW_TANH: return "emmy_tanhf(A)";
+        case EMMYB200_PW_ERF: return "erff(A)";
+        case EMMYB200_PW_SIN: return "emmy_sinf(A)";
+        case EMMYB200_PW_COS: return "emmy_cosf(A)";
+        case EMMYB200_PW_POW: return "powf(A, B)";
+        case EMMYB200_PW_EQ: return "(A == B ? 1.0f : 0.0f)";
+        case EMMYB200_PW_NE: return "(A != B ? 1.0f : 0.0f)";
+        case EMMYB200_PW_GT: return "(A > B ? 1.0f : 0.0f)";
+        case EMMYB200_PW_LT: return "(A < B ? 1.0f : 0.0f)";
+        case EMMYB200_PW_GE: return "(A >= B ? 1.0f : 0.0f)";
+        case EMMYB200_PW_LE: return "(A <= B ? 1.0f : 0.0f)";
+        case EMMYB200_PW_WHERE: return "(A != 0.0f ? B : C)";
+        case EMMYB200_PW_AND: return "((A != 0.0f && B != 0.0f) ? 1.0f : 0.0f)";
+        case EMMYB200_PW_OR: return "((A != 0.0f || B != 0.0f) ? 1.0f : 0.0f)";
+        case EMMYB200_PW_NOT: return "(A == 0.0f ? 1.0f : 0.0f)";
+        case EMMYB200_PW_FLOORDIV: return "floorf(__fdiv_rn(A, B))";
+        case EMMYB200_PW_MOD: return "__fsub_rn(A, __fmul_rn(B, floorf(__fdiv_rn(A, B))))";
+        default: return "A";
+    }
+}
+
+static std::string operand_text(int o) {
+    char buf[24];
+    if (o >= EMMYB200_PW_MAX_SLOTS) snprintf(buf, sizeof buf, "c.v[%d]", o - EMMYB200_PW_MAX_SLOTS);
+    else snprintf(buf, sizeof buf, "s%d", o);
+    return buf;
+}
+
+static std::string expand(const char* pattern, const emmyb200_pw_step& st) {
+    std::string out;
+    for (const char* p = pattern; *p; ++p) {
+        // an operand letter stands alone: the op spellings above contain no identifier made of A, B or C only
+        const bool alone = (p == pattern || !(isalnum((unsigned char)p[-1]) || p[-1] == '_')) && !(isalnum((unsigned char)p[1]) || p[1] == '_');
+        if (alone && *p == 'A') out += operand_text(st.a);
+        else if (alone && *p == 'B') out += operand_text(st.b);
+        else if (alone && *p == 'C') out += operand_text(st.c);
+        else out += *p;
+    }
+    return out;
+}
+
+// The fixed part of every generated kernel. PW_N_IN, PW_VEC, PW_G, PW_DT0..3, PW_BC0..3 and PW_OUT_DT are defined
+// in front of it; dtype codes are those of include/emmyb200.h (0 f32, 1 f16, 2 bf16, 5 u8).
+static const char kShell[] = R"SHELL(
+// PW_G elements per thread and access group: 4 (128-bit accesses of fp32), or 8 when a 16-bit or byte buffer takes
+// part (128-bit accesses of those; two per group for an fp32 buffer). PW_VEC 0: scalar accesses, groups of 4.
+struct PwVec { float v[PW_G]; };
+template <int DT> __device__ __forceinline__ float pw_ld1(const void* p, i64 i) {
+    if (DT == 0) return reinterpret_cast<const float*>(p)[i];
+    if (DT == 5) return reinterpret_cast<const unsigned char*>(p)[i] ? 1.0f : 0.0f;
+    const unsigned short h = reinterpret_cast<const unsigned short*>(p)[i];
+    if (DT == 1) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h)); return f; }
+    return __uint_as_float((unsigned)h << 16);
+}
+__device__ __forceinline__ float pw_half_lo(unsigned w) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"((unsigned short)(w & 0xffffu))); return f; }
+__device__ __forceinline__ float pw_half_hi(unsigned w) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"((unsigned short)(w >> 16))); return f; }
+template <int DT> __device__ __forceinline__ PwVec pw_ldv(const void* p, i64 g) {
+    PwVec r;
+    if (DT == 0) {
+#pragma unroll
+        for (int q = 0; q < PW_G / 4; ++q) {
+            const float4 t = __ldcs(reinterpret_cast<const float4*>(p) + g * (PW_G / 4) + q);
+            r.v[4 * q] = t.x; r.v[4 * q + 1] = t.y; r.v[4 * q + 2] = t.z; r.v[4 * q + 3] = t.w;
+        }
+    } else if (DT == 5) {
+        unsigned w[PW_G / 4];
+#if PW_G == 4
+        w[0] = __ldcs(reinterpret_cast<const unsigned*>(p) + g);
+#else
+        const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(p) + g);
+        w[0] = raw.x; w[1] = raw.y;
+#endif
+#pragma unroll
+        for (int k = 0; k < PW_G; ++k) r.v[k] = ((w[k / 4] >> (8 * (k % 4))) & 0xffu) ? 1.0f : 0.0f;
+    } else {
+        unsigned w[PW_G / 2];
+#if PW_G == 4
+        const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(p) + g);
+        w[0] = raw.x; w[1] = raw.y;
+#else
+        const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p) + g);
+        w[0] = raw.x; w[1] = raw.y; w[2] = raw.z; w[3] = raw.w;
+#endif
+#pragma unroll
+        for (int q = 0; q < PW_G / 2; ++q) {
+            if (DT == 1) { r.v[2 * q] = pw_half_lo(w[q]); r.v[2 * q + 1] = pw_half_hi(w[q]); }
+            else { r.v[2 * q] = __uint_as_float(w[q] << 16); r.v[2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u); }
+        }
+    }
+    return r;
+}
+// Element of a broadcast input that output element i reads: (i / div) % mod, a zero extent skipping its step.
+__device__ __forceinline__ i64 pw_index(i64 i, i64 n, i64 div, i64 mod) {
+    if (n <= 0x7fffffffLL) {                       // the usual case: 32-bit division
+        unsigned j = (unsigned)i;
+        if (div > 0) j = div > 0x7fffffffLL ? 0u : j / (unsigned)div;
+        if (mod > 0 && mod <= 0x7fffffffLL) j %= (unsigned)mod;
+        return (i64)j;
+    }
+    if (div > 0) i /= div;
+    if (mod > 0) i %= mod;
+    return i;
+}
+template <int DT, int BC> __device__ __forceinline__ PwVec pw_in(const void* p, i64 g, i64 n, i64 div, i64 mod) {
+#if PW_VEC
+    if (BC == 2) return pw_ldv<DT>(p, pw_index(g * PW_G, n, 0, mod) / PW_G);      // a row vector, group by group
+#endif
+    if (BC) {
+        const i64 i = g * PW_G;
+        PwVec r;
+#pragma unroll
+        for (int k = 0; k < PW_G; ++k) r.v[k] = i + k < n ? pw_ld1<DT>(p, pw_index(i + k, n, div, mod)) : 0.0f;
+        return r;
+    }
+#if PW_VEC
+    return pw_ldv<DT>(p, g);
+#else
+    const i64 i = g * PW_G;
+    PwVec r;
+#pragma unroll
+    for (int k = 0; k < PW_G; ++k) r.v[k] = i + k < n ? pw_ld1<DT>(p, i + k) : 0.0f;
+    return r;
+#endif
+}
+__device__ __forceinline__ void pw_st1(void* p, i64 i, float v) {
+#if PW_OUT_DT == 0
+    reinterpret_cast<float*>(p)[i] = v;
+#elif PW_OUT_DT == 1
+    unsigned short h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(v)); reinterpret_cast<unsigned short*>(p)[i] = h;
+#else
+    unsigned short h; asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(v)); reinterpret_cast<unsigned short*>(p)[i] = h;
+#endif
+}
+__device__ __forceinline__ unsigned pw_pack2(float lo, float hi) {      // two values rounded to the 16-bit output type
+    unsigned w;
+#if PW_OUT_DT == 1
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi), "f"(lo));
+#else
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(hi), "f"(lo));
+#endif
+    return w;
+}
+__device__ __forceinline__ void pw_out(void* p, i64 g, i64 n, const PwVec& y) {
+#if PW_VEC
+#if PW_OUT_DT == 0
+#pragma unroll
+    for (int q = 0; q < PW_G / 4; ++q)
+        __stcs(reinterpret_cast<float4*>(p) + g * (PW_G / 4) + q, make_float4(y.v[4 * q], y.v[4 * q + 1], y.v[4 * q + 2], y.v[4 * q + 3]));
+#elif PW_G == 4
+    __stcs(reinterpret_cast<uint2*>(p) + g, make_uint2(pw_pack2(y.v[0], y.v[1]), pw_pack2(y.v[2], y.v[3])));
+#else
+    __stcs(reinterpret_cast<uint4*>(p) + g, make_uint4(pw_pack2(y.v[0], y.v[1]), pw_pack2(y.v[2], y.v[3]), pw_pack2(y.v[4], y.v[5]), pw_pack2(y.v[6], y.v[7])));
+#endif
+#else
+    const i64 i = g * PW_G;
+#pragma unroll
+    for (int k = 0; k < PW_G; ++k)
+        if (i + k < n) pw_st1(p, i + k, y.v[k]);
+#endif
+}
+
+#define PW_THREADS 256
+#define PW_UNROLL 2
+extern "C" __global__ void __launch_bounds__(PW_THREADS) pw_jit_kernel(const void* p0, const void* p1, const void* p2, const void* p3,
+                                                                       void* out, i64 n, PwConsts c, PwBcast bc) {
+    const i64 groups = PW_VEC ? n / PW_G : (n + PW_G - 1) / PW_G;
+    const i64 stride = (i64)gridDim.x * PW_THREADS;
+    for (i64 g0 = (i64)blockIdx.x * PW_THREADS + threadIdx.x; g0 < groups; g0 += stride * PW_UNROLL) {
+        PwVec x0[PW_UNROLL], x1[PW_UNROLL], x2[PW_UNROLL], x3[PW_UNROLL];
+#pragma unroll
+        for (int u = 0; u < PW_UNROLL; ++u) {               // every load of the trip is issued before the first use
+            const i64 g = g0 + u * stride;
+#pragma unroll
+            for (int k = 0; k < PW_G; ++k) x0[u].v[k] = x1[u].v[k] = x2[u].v[k] = x3[u].v[k] = 0.0f;
+            if (g < groups) {
+                x0[u] = pw_in<PW_DT0, PW_BC0>(p0, g, n, bc.div[0], bc.mod[0]);
+#if PW_N_IN > 1
+                x1[u] = pw_in<PW_DT1, PW_BC1>(p1, g, n, bc.div[1], bc.mod[1]);
+#endif
+#if PW_N_IN > 2
+                x2[u] = pw_in<PW_DT2, PW_BC2>(p2, g, n, bc.div[2], bc.mod[2]);
+#endif
+#if PW_N_IN > 3
+                x3[u] = pw_in<PW_DT3, PW_BC3>(p3, g, n, bc.div[3], bc.mod[3]);
+#endif
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < PW_UNROLL; ++u) {
+            const i64 g = g0 + u * stride;
+            if (g < groups) {
+                PwVec y;
+#pragma unroll
+                for (int k = 0; k < PW_G; ++k) y.v[k] = pw_cell(x0[u].v[k], x1[u].v[k], x2[u].v[k], x3[u].v[k], c);
+                pw_out(out, g, n, y);
+            }
+        }
+    }
+#if PW_VEC
+    // the last n % PW_G elements of the vector form: one thread each, scalar accesses
+    const int tail = (int)(n % PW_G);
+    if (blockIdx.x == 0 && (int)threadIdx.x < tail) {
+        const i64 i = n - tail + threadIdx.x;
+        float v0 = 0.0f, v1 = 0.0f, v2 = 0.0f, v3 = 0.0f;
+        v0 = pw_ld1<PW_DT0>(p0, PW_BC0 ? pw_index(i, n, bc.div[0], bc.mod[0]) : i);
+#if PW_N_IN > 1
+        v1 = pw_ld1<PW_DT1>(p1, PW_BC1 ? pw_index(i, n, bc.div[1], bc.mod[1]) : i);
+#endif
+#if PW_N_IN > 2
+        v2 = pw_ld1<PW_DT2>(p2, PW_BC2 ? pw_index(i, n, bc.div[2], bc.mod[2]) : i);
+#endif
+#if PW_N_IN > 3
+        v3 = pw_ld1<PW_DT3>(p3, PW_BC3 ? pw_index(i, n, bc.div[3], bc.mod[3]) : i);
+#endif
+        pw_st1(out, i, pw_cell(v0, v1, v2, v3, c));
+    }
+#endif
+}
+)SHELL";
+
+static bool float_program(const emmyb200_pw_program& p) {
+    return p.out_dtype == EMMYB200_F32 || p.out_dtype == EMMYB200_F16 || p.out_dtype == EMMYB200_BF16;
+}
+
+// How input k is read: 0 element i; 1 a broadcast input gathered element by element; 2 a row vector whose length is a
+// multiple of the access group (a bias over the last axis): vector accesses at the wrapped position. `base_aligned`
+// says whether the buffer itself allows those accesses.
+static int broadcast_mode(const emmyb200_pw_program& p, int k, int group, bool base_aligned) {
+    if ((p.in_div[k] | p.in_mod[k]) == 0) return 0;
+    const int per = group == 8 ? 8 : 4;
+    return (group != 0 && base_aligned && p.in_div[k] == 0 && p.in_mod[k] % per == 0) ? 2 : 1;
+}
+
+static std::string program_source(const emmyb200_pw_program& p, int group, const int* modes) {
+    std::string s;
+    char line[160];
+    snprintf(line, sizeof line, "#define PW_N_IN %d\n#define PW_VEC %d\n#define PW_G %d\n#define PW_OUT_DT %d\n", p.n_inputs, group ? 1 : 0, group == 8 ? 8 : 4, p.out_dtype);
+    s += line;
+    for (int k = 0; k < EMMYB200_PW_MAX_INPUTS; ++k) {
+        const bool used = k < p.n_inputs;
+        snprintf(line, sizeof line, "#define PW_DT%d %d\n#define PW_BC%d %d\n", k, used ? p.in_dtype[k] : 0, k, used ? modes[k] : 0);
+        s += line;
+    }
+    s += "#include \"emmy_math.cuh\"\n"
+         "typedef long long i64;\n"
+         "struct PwConsts { float v[16]; };\n"
+         "struct PwBcast { i64 div[4]; i64 mod[4]; };\n"
+         "__device__ __forceinline__ float pw_cell(float i0, float i1, float i2, float i3, const PwConsts& c) {\n"
+         "    float s0 = i0, s1 = i1, s2 = i2, s3 = i3";
+    for (int k = EMMYB200_PW_MAX_INPUTS; k < EMMYB200_PW_MAX_SLOTS; ++k) {
+        snprintf(line, sizeof line, ", s%d = 0.0f", k);
+        s += line;
+    }
+    s += ";\n";
+    for (int i = 0; i < p.n_steps; ++i) {
+        const emmyb200_pw_step& st = p.steps[i];
+        snprintf(line, sizeof line, "    s%d = ", st.dst);
+        s += line;
+        s += expand(op_expr(st.op), st);
+        s += ";\n";
+    }
+    snprintf(line, sizeof line, "    return s%d;\n}\n", p.out_slot);
+    s += line;
+    s += kShell;
+    return s;
+}
+
+// Everything the generated text depends on, and nothing else: the cache key.
+static std::string program_key(const emmyb200_pw_program& p, int group, const int* modes) {
+    std::string k;
+    auto put = [&](int v) { k.push_back((char)(v & 0xff)); };
+    put(p.n_inputs); put(p.n_steps); put(p.out_slot); put(p.out_dtype); put(group);
+    for (int i = 0; i < p.n_inputs; ++i) { put(p.in_dtype[i]); put(modes[i]); }
+    for (int i = 0; i < p.n_steps; ++i) { put(p.steps[i].op); put(p.steps[i].dst); put(p.steps[i].a); put(p.steps[i].b); put(p.steps[i].c); }
+    return k;
+}
+
+// Source text -> device code for sm_100a. No device is needed for this step.
+static int compile_source(const std::string& src, std::vector<char>* cubin) {
+    const Nvrtc& rt = nvrtc();
+    if (!rt.ok) return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_program: NVRTC is not available (%s)", rt.handle ? "symbols missing" : "libnvrtc.so.12 not found");
+    const char* header_text[] = {kMathHeader, kStdintStub, kMathStub, kEmptyStub};
+    const char* header_name[] = {"emmy_math.cuh", "stdint.h", "math.h", "string.h"};
+    nvrtcProgram prog = nullptr;
+    nvrtcResult r = rt.CreateProgram(&prog, src.c_str(), "pw_jit_kernel.cu", 4, header_text, header_name);
+    if (r != NVRTC_SUCCESS) return fail(EMMYB200_ERR_DEVICE, "nvrtcCreateProgram: %s", rt.GetErrorString(r));
+    const char* options[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-lineinfo"};
+    r = rt.CompileProgram(prog, 3, options);
+    if (r != NVRTC_SUCCESS) {
+        size_t n = 0;
+        rt.GetProgramLogSize(prog, &n);
+        std::string log(n, '\0');
+        if (n > 1) rt.GetProgramLog(prog, &log[0]);
+        rt.DestroyProgram(&prog);
+        return fail(EMMYB200_ERR_DEVICE, "pointwise_program: NVRTC (%s): %.400s", rt.GetErrorString(r), log.c_str());
+    }
+    size_t bytes = 0;
+    r = rt.GetCUBINSize(prog, &bytes);
+    if (r == NVRTC_SUCCESS && bytes > 0) {
+        cubin->resize(bytes);
+        r = rt.GetCUBIN(prog, cubin->data());
+    }
+    rt.DestroyProgram(&prog);
+    if (r != NVRTC_SUCCESS || bytes == 0) return fail(EMMYB200_ERR_DEVICE, "pointwise_program: NVRTC produced no device code (%s)", rt.GetErrorString(r));
+    return EMMYB200_OK;
+}
+
+struct JitKernel {
+    cudaLibrary_t library = nullptr;
+    cudaKernel_t kernel = nullptr;
+};
+
+static std::mutex g_jit_mutex;
+static std::map<std::string, JitKernel>& jit_cache() {
+    static std::map<std::string, JitKernel>* m = new std::map<std::string, JitKernel>();      // never destroyed: the runtime may be gone first
+    return *m;
+}
+static std::atomic<long long> g_jit_compiles{0};
+
+struct PwConstsArg { float v[16]; };
+struct PwBcastArg { long long div[4]; long long mod[4]; };
+
+int pw_jit_launch(const emmyb200_pw_program& prog, const void* const* inputs, void* out, int64_t n, int group, cudaStream_t stream) {
+    if (!jit_enabled() || !float_program(prog) || !nvrtc().ok) return kPwJitUnavailable;
+    JitKernel k;
+    int modes[EMMYB200_PW_MAX_INPUTS] = {0, 0, 0, 0};
+    for (int i = 0; i < prog.n_inputs; ++i) {
+        const int es = prog.in_dtype[i] == EMMYB200_F32 ? 4 : (prog.in_dtype[i] == EMMYB200_U8 ? 1 : 2);
+        modes[i] = broadcast_mode(prog, i, group, aligned(inputs[i], (size_t)(group == 8 ? 8 : 4) * es));
+    }
+    {
+        std::lock_guard<std::mutex> lock(g_jit_mutex);
+        const std::string key = program_key(prog, group, modes);
+        auto it = jit_cache().find(key);
+        if (it == jit_cache().end()) {
+            std::vector<char> cubin;
+            int rc = compile_source(program_source(prog, group, modes), &cubin);
+            if (rc != EMMYB200_OK) return rc;
+            cudaError_t e = cudaLibraryLoadData(&k.library, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaLibraryLoadData (specialised elementwise kernel)");
+            e = cudaLibraryGetKernel(&k.kernel, k.library, "pw_jit_kernel");
+            if (e != cudaSuccess) { cudaLibraryUnload(k.library); return cuda_fail(e, "cudaLibraryGetKernel (specialised elementwise kernel)"); }
+            g_jit_compiles.fetch_add(1);
+            it = jit_cache().emplace(key, k).first;
+        }
+        k = it->second;
+    }
+    const void* p[EMMYB200_PW_MAX_INPUTS] = {nullptr, nullptr, nullptr, nullptr};
+    PwConstsArg c;
+    PwBcastArg bc;
+    for (int i = 0; i < EMMYB200_PW_MAX_CONSTS; ++i) c.v[i] = prog.consts[i];
+    for (int i = 0; i < EMMYB200_PW_MAX_INPUTS; ++i) {
+        if (i < prog.n_inputs) p[i] = inputs[i];
+        bc.div[i] = i < prog.n_inputs ? prog.in_div[i] : 0;
+        bc.mod[i] = i < prog.n_inputs ? prog.in_mod[i] : 0;
+    }
+    long long count = n;
+    void* args[] = {&p[0], &p[1], &p[2], &p[3], &out, &count, &c, &bc};
+    const int per = group == 8 ? 8 : 4;
+    const int64_t groups = (n + per - 1) / per;
+    const int64_t want = (groups + 256 * 2 - 1) / (256 * 2);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    const unsigned blocks = (unsigned)(want < cap ? want : cap);
+    cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(k.kernel), dim3(blocks), dim3(256), args, 0, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "launch of the specialised elementwise kernel");
+    return EMMYB200_OK;
+}
+
+}  // namespace emmy
+
+extern "C" int emmyb200_set_pointwise_jit(int enabled) {
+    const bool before = emmy::jit_enabled();
+    emmy::g_jit_enabled.store(enabled ? 1 : 0, std::memory_order_relaxed);
+    return before ? 1 : 0;
+}
+
+extern "C" int emmyb200_pointwise_jit_state(int64_t* kernels_compiled) {
+    if (kernels_compiled != nullptr) *kernels_compiled = emmy::g_jit_compiles.load();
+    if (!emmy::jit_enabled()) return 0;
+    return emmy::nvrtc().ok ? 1 : -1;
+}
+
+extern "C" int64_t emmyb200_pointwise_program_source(const emmyb200_pw_program* prog, int group, char* text, int64_t capacity) {
+    using namespace emmy;
+    if (prog == nullptr || prog->n_inputs < 1 || prog->n_inputs > EMMYB200_PW_MAX_INPUTS || prog->n_steps < 0 ||
+        prog->n_steps > EMMYB200_PW_MAX_STEPS || prog->out_slot < 0 || prog->out_slot >= EMMYB200_PW_MAX_SLOTS || !float_program(*prog))
+        return fail(EMMYB200_ERR_ARG, "pointwise_program_source: not a float program");
+    for (int i = 0; i < prog->n_steps; ++i) {
+        const emmyb200_pw_step& st = prog->steps[i];
+        if (st.op >= EMMYB200_PW_OP_COUNT || st.dst >= EMMYB200_PW_MAX_SLOTS) return fail(EMMYB200_ERR_ARG, "pointwise_program_source: bad step %d", i);
+        for (int o : {st.a, st.b, st.c})
+            if (o >= EMMYB200_PW_MAX_SLOTS + EMMYB200_PW_MAX_CONSTS) return fail(EMMYB200_ERR_ARG, "pointwise_program_source: bad operand in step %d", i);
+    }
+    if (group != 0 && group != 4 && group != 8) return fail(EMMYB200_ERR_ARG, "pointwise_program_source: group %d (0, 4 or 8)", group);
+    int modes[EMMYB200_PW_MAX_INPUTS] = {0, 0, 0, 0};
+    for (int i = 0; i < prog->n_inputs; ++i) modes[i] = broadcast_mode(*prog, i, group, true);
+    const std::string s = program_source(*prog, group, modes);
+    if (text != nullptr && capacity > 0) {
+        const size_t m = (size_t)capacity - 1 < s.size() ? (size_t)capacity - 1 : s.size();
+        memcpy(text, s.data(), m);
+        text[m] = 0;
+    }
+    return (int64_t)s.size() + 1;
+}
+
+extern "C" int emmyb200_pointwise_program_compile(const emmyb200_pw_program* prog, int group, int64_t* code_bytes) {
+    using namespace emmy;
+    const int64_t need = emmyb200_pointwise_program_source(prog, group, nullptr, 0);
+    if (need < 0) return (int)need;
+    std::vector<char> cubin;
+    int modes[EMMYB200_PW_MAX_INPUTS] = {0, 0, 0, 0};
+    for (int i = 0; i < prog->n_inputs; ++i) modes[i] = broadcast_mode(*prog, i, group, true);
+    const int rc = compile_source(program_source(*prog, group, modes), &cubin);
+    if (rc == EMMYB200_OK && code_bytes != nullptr) *code_bytes = (int64_t)cubin.size();
+    return rc;
+}

@@ -58,6 +58,10 @@ _SIGNATURES = {
                                               ctypes.c_void_p]),
     "emmyb200_pointwise_program": (ctypes.c_int, [ctypes.POINTER(PwProgram), ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p,
                                                   ctypes.c_int64, ctypes.c_void_p]),
+    "emmyb200_set_pointwise_jit": (ctypes.c_int, [ctypes.c_int]),
+    "emmyb200_pointwise_jit_state": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int64)]),
+    "emmyb200_pointwise_program_source": (ctypes.c_int64, [ctypes.POINTER(PwProgram), ctypes.c_int, ctypes.c_char_p, ctypes.c_int64]),
+    "emmyb200_pointwise_program_compile": (ctypes.c_int, [ctypes.POINTER(PwProgram), ctypes.c_int, ctypes.POINTER(ctypes.c_int64)]),
     "emmyb200_index_gather_i32": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                                  ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                                                  ctypes.c_void_p]),
@@ -188,6 +192,40 @@ def pointwise_program(program: dict, inputs: list, out, stream=None):
     prog = make_program(program)
     check(library().emmyb200_pointwise_program(ctypes.byref(prog), arr, out.data_ptr(), out.numel(), _stream(stream)))
     return out
+
+
+def set_pointwise_jit(enabled: bool) -> bool:
+    """Float programs as kernels compiled at first use (True, the default) or on the interpreter kernel; returns the
+    previous setting."""
+    return bool(library().emmyb200_set_pointwise_jit(1 if enabled else 0))
+
+
+def pointwise_jit_state() -> tuple[int, int]:
+    """(state, kernels compiled so far): state 1 = compiled form in use, 0 = switched off, -1 = the run-time compiler
+    could not be loaded (programs run on the interpreter)."""
+    n = ctypes.c_int64(0)
+    return library().emmyb200_pointwise_jit_state(ctypes.byref(n)), n.value
+
+
+def program_source(program: dict, group: int = 4) -> str:
+    """The CUDA C++ text of the kernel a float program is compiled to; `group` = elements per thread and access group
+    (4, 8, or 0 for scalar accesses)."""
+    prog = make_program(program)
+    need = library().emmyb200_pointwise_program_source(ctypes.byref(prog), int(group), None, 0)
+    if need < 0:
+        check(int(need))
+    buf = ctypes.create_string_buffer(need)
+    library().emmyb200_pointwise_program_source(ctypes.byref(prog), int(group), buf, need)
+    return buf.value.decode()
+
+
+def program_compile(program: dict, group: int = 4) -> int:
+    """Compile a float program's kernel for sm_100a without launching it (works without a GPU); returns the size of
+    the device code."""
+    prog = make_program(program)
+    n = ctypes.c_int64(0)
+    check(library().emmyb200_pointwise_program_compile(ctypes.byref(prog), int(group), ctypes.byref(n)))
+    return n.value
 
 
 def index_gather(x, mul: int, add: int, div: int, shift: int, trunc: bool = False, out=None, stream=None):

@@ -102,6 +102,29 @@ typedef struct {
 int emmyb200_pointwise_program(const emmyb200_pw_program* program, const void* const* inputs, void* out,
                                int64_t n, void* cuda_stream);
 
+/* How float programs run. By default each distinct program shape (op sequence, operand wiring, dtypes, which inputs
+ * are broadcast, vector or scalar accesses) is compiled once, at its first launch, into a kernel of its own -- the
+ * counterpart of the reference printing the ops into the entry it compiles (emmyptx/kernel.py:766-784) -- by the
+ * toolkit's run-time compiler (libnvrtc.so.12, looked up when first needed; EMMYB200_NVRTC names another file).
+ * Constants and broadcast extents are launch arguments and do not compile again. The first launch of a shape takes
+ * the compile time (a fraction of a second) and cannot be part of a stream capture. With the compiler missing, or
+ * after emmyb200_set_pointwise_jit(0) (or EMMYB200_PW_JIT=0 in the environment), programs run on a precompiled
+ * interpreter kernel with the same results bit for bit (the sign and payload of a NaN aside), at a fraction of the
+ * bandwidth.
+ *   emmyb200_set_pointwise_jit      returns the previous setting (1 compiled, 0 interpreter).
+ *   emmyb200_pointwise_jit_state    1 compiled form in use, 0 switched off, -1 wanted but the compiler could not be
+ *                                   loaded; *kernels_compiled (may be NULL) counts the compilations so far.
+ *   emmyb200_pointwise_program_source   the CUDA C++ text of the kernel for `program`; group = elements per thread and
+ *                                   access: 4 (128-bit accesses of fp32), 8 (128-bit accesses of 16-bit types), 0
+ *                                   (scalar accesses, for unaligned buffers); returns the size needed including the
+ *                                   terminator, or a negative status.
+ *   emmyb200_pointwise_program_compile  compiles that text for sm_100a without launching (no device needed);
+ *                                   *code_bytes (may be NULL) receives the size of the device code. */
+int emmyb200_set_pointwise_jit(int enabled);
+int emmyb200_pointwise_jit_state(int64_t* kernels_compiled);
+int64_t emmyb200_pointwise_program_source(const emmyb200_pw_program* program, int group, char* text, int64_t capacity);
+int emmyb200_pointwise_program_compile(const emmyb200_pw_program* program, int group, int64_t* code_bytes);
+
 /* The int32 index-math gather
  *     y[i] = (x[(i * mul + add) mod n] div d) xor (i >> shift),   0 <= i < n,
  * i.e. the s32 instruction stream of emmyptx/intmath.py:36-38, :87-117 and

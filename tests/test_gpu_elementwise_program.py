@@ -15,6 +15,17 @@ from emmyptx.kernel import compile_kernel
 pytestmark = pytest.mark.gpu
 ROUND, TRANS, HALF = 1e-6, 1e-5, 1e-2
 
+
+@pytest.fixture(autouse=True, params=["compiled", "interpreter"])
+def program_form(request):
+    """Every case runs twice: as the kernel compiled for the program at first use, and on the interpreter kernel."""
+    from emmyptx import runtime
+    before = runtime.set_pointwise_jit(request.param == "compiled")
+    if request.param == "compiled":
+        assert runtime.pointwise_jit_state()[0] == 1, "the run-time compiler was not found: float programs would silently run interpreted"
+    yield request.param
+    runtime.set_pointwise_jit(before)
+
 # id -> (inputs, steps, torch expression over float64 tensors named like the inputs, tolerance)
 CASES = {
     "p_abs": ({"x": "f32"}, [("a", "abs", ["x"])], "torch.abs(x)", ROUND),
@@ -186,7 +197,7 @@ def _tile2(rows, cols, loads, steps, ins, out_shape):
     return g, k, _launch(k, [*ins, "out"], rows * cols)
 
 
-@pytest.mark.parametrize("rows,cols", [(32, 64), (33, 61)])
+@pytest.mark.parametrize("rows,cols", [(32, 64), (33, 61), (67, 1032)])
 def test_broadcast_inputs(rows, cols, cuda):
     import torch
     rng = np.random.default_rng(rows)
@@ -207,3 +218,61 @@ def test_broadcast_inputs(rows, cols, cuda):
     built = _tile2(rows, cols, [("v", "V", ("c0",))], [("o", "add", ["v", 0.0])], {"V": [cols]}, [rows, cols])
     got = _run_built(built, {"V": v}, torch.float32, rows * cols)
     assert np.array_equal(got.reshape(rows, cols), np.broadcast_to(v, (rows, cols)))
+
+
+def test_compiled_and_interpreted_forms_agree_bit_for_bit(cuda):
+    """One program through every float op of the table, on values that include zeros, infinities, NaN and subnormals;
+    f32 / f16 / bf16 / bool inputs, aligned and unaligned views, ragged lengths. The two forms must give the same bits."""
+    import torch
+    from emmyptx import runtime as rt
+    S = rt.PW_MAX_SLOTS
+    unary = ["relu", "square", "copy", "negative", "abs", "reciprocal", "sqrt", "rsqrt", "exp", "log", "sigmoid", "tanh", "erf", "sin", "cos", "bitwise_not"]
+    binary = ["add", "subtract", "multiply", "divide", "maximum", "minimum", "pow", "equal", "not_equal", "greater", "less", "greater_equal",
+              "less_equal", "bitwise_and", "bitwise_or", "floor_divide", "mod"]
+    g = torch.Generator(device="cpu").manual_seed(5)
+    special = torch.tensor([0.0, -0.0, 1.0, -1.0, float("inf"), -float("inf"), float("nan"), 1e-40, -1e-40, 88.0, -104.0, 1e5, 3.4e38, 0.5])
+    for n in (4096, 4099, 3):
+        x = torch.randn(n + 4, generator=g) * 3
+        x[1:1 + min(n, len(special))] = special[:min(n, len(special))]
+        y = torch.randn(n + 4, generator=g)
+        xs = {"f32": x.cuda(), "f16": x.half().cuda(), "bf16": x.bfloat16().cuda()}
+        ys = {"f32": y.cuda(), "f16": y.half().cuda(), "bf16": y.bfloat16().cuda()}
+        mask = (torch.randn(n + 4, generator=g) > 0).cuda()
+        for off in (0, 1, 4):           # 128-bit accesses everywhere; none; 64-bit ones for the 16-bit buffers
+            for dt_in, dt_out in (("f32", "f32"), ("f16", "bf16"), ("bf16", "f16"), ("f32", "f16")):
+                tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[dt_out]
+                for ops, arity in ((unary, 1), (binary, 2)):
+                    for op in ops:
+                        prog = {"in_dtypes": [dt_in, dt_in, "bool"], "out_dtype": dt_out, "out_slot": 5, "consts": [0.75],
+                                "steps": [[op, 4, 0, 1 if arity == 2 else 0, 0], ["where", 5, 2, 4, S + 0]]}
+                        ins = [xs[dt_in][off:off + n], ys[dt_in][off:off + n], mask[off:off + n]]
+                        outs = []
+                        for compiled in (True, False):
+                            rt.set_pointwise_jit(compiled)
+                            out = torch.full((n + 8,), 7.0, dtype=tdt, device="cuda")
+                            rt.pointwise_program(prog, ins, out[off:off + n])
+                            outs.append(out.cpu())
+                        # same bits, except that a NaN need only be a NaN in both (its sign and payload are not specified)
+                        nan = [o.float().isnan() for o in outs]
+                        assert torch.equal(nan[0], nan[1]), (op, n, off, dt_in, dt_out)
+                        a, b = (o.view(torch.int16 if tdt != torch.float32 else torch.int32)[~nan[0]] for o in outs)
+                        assert torch.equal(a, b), (op, n, off, dt_in, dt_out)
+
+
+def test_constants_and_extents_do_not_compile_again(cuda, program_form):
+    import torch
+    from emmyptx import runtime as rt
+    if program_form != "compiled":
+        pytest.skip("only the compiled form has a cache")
+    S = rt.PW_MAX_SLOTS
+    x = torch.randn(5000, device="cuda")
+    prog = {"in_dtypes": ["f32"], "out_dtype": "f32", "out_slot": 4, "consts": [1.5, -2.0], "steps": [["multiply", 4, 0, S, 0], ["add", 4, 4, S + 1, 0], ["tanh", 4, 4, 0, 0]]}
+    out = torch.empty_like(x)
+    rt.pointwise_program(prog, [x], out)
+    compiled = rt.pointwise_jit_state()[1]
+    for c in (0.25, 3.0):
+        prog["consts"] = [c, 1.0]
+        rt.pointwise_program(prog, [x], out)
+        assert torch.allclose(out, torch.tanh(x * c + 1.0), atol=1e-6)
+    rt.pointwise_program(prog, [x[:4096]], out[:4096])
+    assert rt.pointwise_jit_state()[1] == compiled

@@ -1,0 +1,51 @@
+"""The compile-at-first-use form of elementwise programs, as far as it goes without a GPU: the CUDA C++ text a program
+becomes, and that the run-time compiler turns it into sm_100a device code. The generated kernel replaces the entry the
+reference prints for a one-axis Tile (emmyptx/kernel.py:766-784 calling emmyptx/ops.py:212 once per Assign)."""
+import pytest
+
+from emmyptx import runtime as rt
+
+S = rt.PW_MAX_SLOTS
+LERP = {"in_dtypes": ["f32", "f32", "f32"], "out_dtype": "f32", "out_slot": 5, "consts": [],
+        "steps": [["subtract", 4, 1, 0, 0], ["multiply", 4, 4, 2, 0], ["add", 5, 0, 4, 0]]}
+
+
+def test_source_spells_each_step_once_in_order(lib):
+    text = rt.program_source(LERP)
+    body = text[text.index("pw_cell("):text.index("return s5;")]
+    lines = [ln.strip() for ln in body.splitlines() if ln.strip().startswith("s") and "=" in ln and not ln.strip().startswith("float")]
+    assert lines == ["s4 = __fsub_rn(s1, s0);", "s4 = __fmul_rn(s4, s2);", "s5 = __fadd_rn(s0, s4);"]
+    assert "#define PW_N_IN 3" in text and "#define PW_VEC 1" in text
+    assert "#define PW_VEC 0" in rt.program_source(LERP, group=0)
+    assert "#define PW_G 8" in rt.program_source(LERP, group=8)
+
+
+def test_constants_are_arguments_and_broadcast_is_a_flag(lib):
+    prog = {"in_dtypes": ["f16", "bool", "bf16"], "out_dtype": "bf16", "out_slot": 4, "consts": [0.5, 2.0], "in_mod": [0, 0, 7],
+            "steps": [["where", 4, 1, 0, S + 1], ["pow", 4, 4, S + 0, 0], ["maximum", 4, 4, 2, 0]]}
+    text = rt.program_source(prog)
+    assert "s4 = (s1 != 0.0f ? s0 : c.v[1]);" in text and "s4 = powf(s4, c.v[0]);" in text
+    assert "#define PW_DT0 1" in text and "#define PW_DT1 5" in text and "#define PW_DT2 2" in text
+    assert "#define PW_BC2 1" in text and "#define PW_BC0 0" in text and "#define PW_OUT_DT 2" in text
+    other = dict(prog, consts=[9.0, -1.0], in_mod=[0, 0, 13])
+    assert rt.program_source(other) == text            # same text, so the same cached kernel
+    assert "#define PW_BC2 2" in rt.program_source(dict(prog, in_mod=[0, 0, 64]))      # a row vector read with vector accesses
+
+
+def test_every_float_op_compiles_for_sm100a(lib):
+    if rt.pointwise_jit_state()[0] != 1:
+        pytest.skip("libnvrtc is not installed here")
+    names = [k for k, v in sorted(rt.PW_OPS.items(), key=lambda kv: kv[1]) if k not in ("exp_fast", "remainder")]
+    steps = []
+    for i, op in enumerate(names):                    # a chain, so that no step is dead code
+        steps.append([op, 4 + (i % 8), 4 + ((i + 7) % 8) if i else 0, 1, 2])
+    for out_dtype, vec in (("f32", 4), ("f16", 8), ("bf16", 0), ("bf16", 4), ("f32", 8)):
+        prog = {"in_dtypes": ["f32", "f16", "bf16", "bool"], "out_dtype": out_dtype, "out_slot": steps[-1][1], "consts": [1.0],
+                "in_div": [0, 3, 0, 0], "steps": steps}
+        assert rt.program_compile(prog, vec) > 1000
+
+
+def test_integer_programs_have_no_compiled_form(lib):
+    prog = {"in_dtypes": ["i32"], "out_dtype": "i32", "out_slot": 4, "consts": [3], "steps": [["add", 4, 0, S, 0]]}
+    with pytest.raises(rt.KernelError, match="float program"):
+        rt.program_source(prog)
