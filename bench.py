@@ -40,10 +40,11 @@ for _p in (str(ROOT), str(ROOT / "emmy-ptx-compiler_b200")):
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each workload's kernel, from the ncu captures summarised
-# under profiles/ (c4: captured at M=N=K=8192 and scaled by the 8x flops of the full size; c5: captured on 64 of the 256
-# units and scaled by 4; c2, c3: captured at full size; c1: 8 MiB working set, L2-resident, no DRAM figure).
-DRAM_TRAFFIC = {"c4": 8 * (1.018008e9 + 0.125913e9), "c5": 4 * (201.44e6 + 49.98e6), "c2": 268.97e6 + 222.76e6,
-                "c3": 83.01e6 + 14.28e6, "c1": None, "softmax": 268.46e6 + 216.40e6, "f32mm": None}
+# under profiles/ (c4: a one-pass capture of the two counters at the full M=N=K=16384; c5: captured on 64 of the 256
+# units and scaled by 4; c2, c3: captured at full size; c1: 8 MiB working set, L2-resident, no DRAM figure; lerp: the
+# kernel compiled for the program, at N=2^26).
+DRAM_TRAFFIC = {"c4": 8.83e9 + 0.53713e9, "c5": 4 * (201.44e6 + 49.98e6), "c2": 268.97e6 + 222.76e6,
+                "c3": 83.01e6 + 14.28e6, "c1": None, "softmax": 268.46e6 + 216.40e6, "f32mm": None, "lerp": None}
 
 WORKLOADS = {
     "c1": "fp32 exp(x)+sin(x)*tanh(x), N=2^20, x~U[-4,4]",
@@ -52,7 +53,7 @@ WORKLOADS = {
     "c4": "bf16 GEMM + tanh-GELU epilogue M=N=K=16384, fp32 accumulate, bf16 out, M-row shards",
     "c5": "bf16 attention fwd B16 H16 S4096 d128, non-causal, fp32 softmax, (batch x head) shards",
     "causal": "bf16 causal attention fwd, 64 units of S4096 d128 (the two-tiles-per-CTA kernel form; not one of the five configurations)",
-    "lerp": "fp32 x + 0.3*(y - x) over 2^26 elements, two inputs, through the general elementwise kernel (program as data; not one of the five configurations)",
+    "lerp": "fp32 x + 0.3*(y - x) over 2^26 elements, two inputs, through the general elementwise entry point (the program compiled into a kernel of its own at first use; not one of the five configurations)",
     "f32mm": "fp32 matmul M=N=K=4096 with fp32 accuracy (three-way bf16 split on the tensor cores; not one of the five configurations)",
     "softmax": "fp32 softmax over the last axis of [65536, 1024] (the row kernels; not one of the five configurations)",
 }
@@ -420,7 +421,8 @@ class RowWorkload(PointwiseWorkload):
 
 class ProgramWorkload(PointwiseWorkload):
     """torch.lerp(x, y, 0.3) (tools/torch_cases/pointwise.py:47 `p_lerp`) compiled from IR by the facade to a program for
-    the general elementwise kernel: 12 bytes per element (two reads, one write)."""
+    the general elementwise entry point, which compiles it into a kernel of its own at its first launch (a warm-up step):
+    12 bytes per element (two reads, one write)."""
 
     def __init__(self, n, rank, world, dev):
         import json as _json

@@ -978,10 +978,16 @@ static int launch_attention(const void* Q, const void* K, const void* V, void* c
 
 }  // namespace emmy
 
+namespace emmy {
+// attention_f32.cu
+int attention_cuda_cores(int dtype, bool causal, const void* Q, const void* K, const void* V, void* O, int64_t units, int64_t seq_q,
+                         int64_t seq_k, int64_t d, float scale, cudaStream_t s);
+}  // namespace emmy
+
 static int attention_entry(int dtype, int flags, const void* Q, const void* K, const void* V, void* const* O, int n_dst, int64_t units,
                            int64_t seq_q, int64_t seq_k, int64_t d, float scale, void* cuda_stream) {
     using namespace emmy;
-    if (dtype != EMMYB200_F16 && dtype != EMMYB200_BF16) return fail(EMMYB200_ERR_UNSUPPORTED, "attention_fwd: dtype %d (f16 and bf16 only)", dtype);
+    if (dtype != EMMYB200_F16 && dtype != EMMYB200_BF16 && dtype != EMMYB200_F32) return fail(EMMYB200_ERR_UNSUPPORTED, "attention_fwd: dtype %d (f32, f16 and bf16 only)", dtype);
     if (flags & ~(EMMYB200_ATT_CAUSAL | EMMYB200_ATT_DST_MULTICAST | EMMYB200_ATT_FORM_ONE_TILE | EMMYB200_ATT_FORM_TWO_TILES)) return fail(EMMYB200_ERR_ARG, "attention_fwd: unknown flags 0x%x", flags);
     const bool causal = flags & EMMYB200_ATT_CAUSAL;
     const bool multicast = flags & EMMYB200_ATT_DST_MULTICAST;
@@ -992,7 +998,10 @@ static int attention_entry(int dtype, int flags, const void* Q, const void* K, c
     if (units < 0 || seq_q < 0 || seq_k < 0) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: negative extent");
     if (units == 0 || seq_q == 0) return EMMYB200_OK;
     if (seq_k == 0) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: seq_k = 0 (softmax over no keys)");
-    if (d != 64 && d != 128) return fail(EMMYB200_ERR_UNSUPPORTED, "attention_fwd: head dim %lld (64 and 128 only)", (long long)d);
+    const bool cuda_cores = dtype == EMMYB200_F32 || (d != 64 && d != 128);        // fp32 arithmetic, or a head size the tensor-core kernels lack
+    if (cuda_cores && (d % 32 != 0 || d < 32 || d > 128)) return fail(EMMYB200_ERR_UNSUPPORTED, "attention_fwd: head dim %lld (a multiple of 32 up to 128)", (long long)d);
+    if (cuda_cores && (n_dst != 1 || multicast || form != 0))
+        return fail(EMMYB200_ERR_UNSUPPORTED, "attention_fwd: f32 buffers and head sizes other than 64 / 128 have one destination and one kernel form");
     if (seq_q >= (1ll << 31) || seq_k >= (1ll << 31) || units >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: extents must be below 2^31");
     if (Q == nullptr || K == nullptr || V == nullptr || O == nullptr) return fail(EMMYB200_ERR_ARG, "attention_fwd: null buffer");
     for (int i = 0; i < n_dst; ++i) {
@@ -1004,6 +1013,7 @@ static int attention_entry(int dtype, int flags, const void* Q, const void* K, c
     int rc = check_sm100();
     if (rc != EMMYB200_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    if (cuda_cores) return attention_cuda_cores(dtype, causal, Q, K, V, O[0], units, seq_q, seq_k, d, scale, s);
     const bool bf16 = dtype == EMMYB200_BF16;
     if (d == 128) return bf16 ? launch_attention<128, true>(Q, K, V, O, n_dst, causal, multicast, form, units, seq_q, seq_k, scale, s)
                               : launch_attention<128, false>(Q, K, V, O, n_dst, causal, multicast, form, units, seq_q, seq_k, scale, s);

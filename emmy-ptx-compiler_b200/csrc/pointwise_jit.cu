@@ -11,7 +11,8 @@
 //
 // Every op is spelled exactly as in the interpreter of pointwise_program.cu (explicit round-to-nearest
 // intrinsics, the functions of emmy_math.cuh, which travels inside this library as text), so the two forms give
-// the same bits (the sign and payload of a NaN aside); the interpreter remains the form used when NVRTC cannot be loaded, and for integer programs.
+// the same bits (the sign and payload of a NaN aside); the interpreters remain the form used when NVRTC cannot be
+// loaded. Integer programs (32-bit two's complement values in i32 / i64 buffers) are compiled the same way.
 #include <ctype.h>
 #include <cuda_runtime.h>
 #include <dlfcn.h>
@@ -138,21 +139,53 @@ static const char* op_expr(int op) {
     }
 }
 
-static std::string operand_text(int o) {
+static const char* op_expr_int(int op) {
+    switch (op) {
+        case EMMYB200_PW_ADD: return "(int)((unsigned)A + (unsigned)B)";
+        case EMMYB200_PW_SUB: return "(int)((unsigned)A - (unsigned)B)";
+        case EMMYB200_PW_MUL: return "(int)((unsigned)A * (unsigned)B)";
+        case EMMYB200_PW_MAX: return "max(A, B)";
+        case EMMYB200_PW_MIN: return "min(A, B)";
+        case EMMYB200_PW_RELU: return "max(A, 0)";
+        case EMMYB200_PW_SQUARE: return "(int)((unsigned)A * (unsigned)A)";
+        case EMMYB200_PW_NEG: return "(int)(0u - (unsigned)A)";
+        case EMMYB200_PW_ABS: return "(A < 0 ? (int)(0u - (unsigned)A) : A)";
+        case EMMYB200_PW_EQ: return "(int)(A == B)";
+        case EMMYB200_PW_NE: return "(int)(A != B)";
+        case EMMYB200_PW_GT: return "(int)(A > B)";
+        case EMMYB200_PW_LT: return "(int)(A < B)";
+        case EMMYB200_PW_GE: return "(int)(A >= B)";
+        case EMMYB200_PW_LE: return "(int)(A <= B)";
+        case EMMYB200_PW_WHERE: return "(A != 0 ? B : C)";
+        case EMMYB200_PW_AND: return "(A & B)";
+        case EMMYB200_PW_OR: return "(A | B)";
+        case EMMYB200_PW_NOT: return "(~A)";
+        case EMMYB200_PW_XOR: return "(A ^ B)";
+        case EMMYB200_PW_SHL: return "(int)((unsigned)A << ((unsigned)B & 31u))";
+        case EMMYB200_PW_SHR: return "(A >> ((unsigned)B & 31u))";
+        case EMMYB200_PW_DIV:
+        case EMMYB200_PW_FLOORDIV: return "pw_i_div(A, B, T)";
+        case EMMYB200_PW_MOD: return "pw_i_mod(A, B, T)";
+        default: return "A";                                    // COPY, and ops the s32 table does not have
+    }
+}
+
+static std::string operand_text(int o, bool ints) {
     char buf[24];
-    if (o >= EMMYB200_PW_MAX_SLOTS) snprintf(buf, sizeof buf, "c.v[%d]", o - EMMYB200_PW_MAX_SLOTS);
+    if (o >= EMMYB200_PW_MAX_SLOTS) snprintf(buf, sizeof buf, ints ? "(int)c.v[%d]" : "c.v[%d]", o - EMMYB200_PW_MAX_SLOTS);
     else snprintf(buf, sizeof buf, "s%d", o);
     return buf;
 }
 
-static std::string expand(const char* pattern, const emmyb200_pw_step& st) {
+static std::string expand(const char* pattern, const emmyb200_pw_step& st, bool ints) {
     std::string out;
     for (const char* p = pattern; *p; ++p) {
-        // an operand letter stands alone: the op spellings above contain no identifier made of A, B or C only
+        // an operand letter (or T, the step's rounding flag) stands alone: no op spelling has such an identifier
         const bool alone = (p == pattern || !(isalnum((unsigned char)p[-1]) || p[-1] == '_')) && !(isalnum((unsigned char)p[1]) || p[1] == '_');
-        if (alone && *p == 'A') out += operand_text(st.a);
-        else if (alone && *p == 'B') out += operand_text(st.b);
-        else if (alone && *p == 'C') out += operand_text(st.c);
+        if (alone && *p == 'A') out += operand_text(st.a, ints);
+        else if (alone && *p == 'B') out += operand_text(st.b, ints);
+        else if (alone && *p == 'C') out += operand_text(st.c, ints);
+        else if (alone && *p == 'T') out += st.reserved[0] ? "1" : "0";
         else out += *p;
     }
     return out;
@@ -160,10 +193,27 @@ static std::string expand(const char* pattern, const emmyb200_pw_step& st) {
 
 // The fixed part of every generated kernel. PW_N_IN, PW_VEC, PW_G, PW_DT0..3, PW_BC0..3 and PW_OUT_DT are defined
 // in front of it; dtype codes are those of include/emmyb200.h (0 f32, 1 f16, 2 bf16, 5 u8).
-static const char kShell[] = R"SHELL(
+static const char kIntOps[] = R"SHELL(// 32-bit two's complement ops of integer programs (the s32 table, emmyptx/ops.py:294-309): wrap-around arithmetic,
+// `//` and `%` toward minus infinity unless T is 1 (toward zero, the reference's div.s32 / rem.s32).
+__device__ __forceinline__ int pw_i_div(int a, int b, int trunc) {
+    if (b == 0) return 0;
+    if (b == -1) return (int)(0u - (unsigned)a);                 // INT_MIN / -1 wraps
+    int q = a / b;
+    if (!trunc && (a % b != 0) && ((a < 0) != (b < 0))) --q;
+    return q;
+}
+__device__ __forceinline__ int pw_i_mod(int a, int b, int trunc) {
+    if (b == 0 || b == -1) return 0;
+    int r = a % b;
+    if (!trunc && r != 0 && ((r < 0) != (b < 0))) r += b;
+    return r;
+}
+)SHELL";
+
+// Loads of the float programs: values are fp32, 16-bit buffers are widened, byte buffers are 0 / 1.
+static const char kFloatLoads[] = R"SHELL(
 // PW_G elements per thread and access group: 4 (128-bit accesses of fp32), or 8 when a 16-bit or byte buffer takes
 // part (128-bit accesses of those; two per group for an fp32 buffer). PW_VEC 0: scalar accesses, groups of 4.
-struct PwVec { float v[PW_G]; };
 template <int DT> __device__ __forceinline__ float pw_ld1(const void* p, i64 i) {
     if (DT == 0) return reinterpret_cast<const float*>(p)[i];
     if (DT == 5) return reinterpret_cast<const unsigned char*>(p)[i] ? 1.0f : 0.0f;
@@ -208,39 +258,9 @@ template <int DT> __device__ __forceinline__ PwVec pw_ldv(const void* p, i64 g) 
     }
     return r;
 }
-// Element of a broadcast input that output element i reads: (i / div) % mod, a zero extent skipping its step.
-__device__ __forceinline__ i64 pw_index(i64 i, i64 n, i64 div, i64 mod) {
-    if (n <= 0x7fffffffLL) {                       // the usual case: 32-bit division
-        unsigned j = (unsigned)i;
-        if (div > 0) j = div > 0x7fffffffLL ? 0u : j / (unsigned)div;
-        if (mod > 0 && mod <= 0x7fffffffLL) j %= (unsigned)mod;
-        return (i64)j;
-    }
-    if (div > 0) i /= div;
-    if (mod > 0) i %= mod;
-    return i;
-}
-template <int DT, int BC> __device__ __forceinline__ PwVec pw_in(const void* p, i64 g, i64 n, i64 div, i64 mod) {
-#if PW_VEC
-    if (BC == 2) return pw_ldv<DT>(p, pw_index(g * PW_G, n, 0, mod) / PW_G);      // a row vector, group by group
-#endif
-    if (BC) {
-        const i64 i = g * PW_G;
-        PwVec r;
-#pragma unroll
-        for (int k = 0; k < PW_G; ++k) r.v[k] = i + k < n ? pw_ld1<DT>(p, pw_index(i + k, n, div, mod)) : 0.0f;
-        return r;
-    }
-#if PW_VEC
-    return pw_ldv<DT>(p, g);
-#else
-    const i64 i = g * PW_G;
-    PwVec r;
-#pragma unroll
-    for (int k = 0; k < PW_G; ++k) r.v[k] = i + k < n ? pw_ld1<DT>(p, i + k) : 0.0f;
-    return r;
-#endif
-}
+)SHELL";
+
+static const char kFloatStores[] = R"SHELL(
 __device__ __forceinline__ void pw_st1(void* p, i64 i, float v) {
 #if PW_OUT_DT == 0
     reinterpret_cast<float*>(p)[i] = v;
@@ -278,6 +298,93 @@ __device__ __forceinline__ void pw_out(void* p, i64 g, i64 n, const PwVec& y) {
 #endif
 }
 
+)SHELL";
+
+static const char kIntLoads[] = R"SHELL(
+template <int DT> __device__ __forceinline__ int pw_ld1(const void* p, i64 i) {
+    if (DT == 3) return reinterpret_cast<const int*>(p)[i];
+    return (int)reinterpret_cast<const long long*>(p)[i];              // 64-bit buffers hold 32-bit values (emmyptx/kernel.py:41)
+}
+template <int DT> __device__ __forceinline__ PwVec pw_ldv(const void* p, i64 g) {      // PW_G is 4 for integer programs
+    PwVec r;
+    if (DT == 3) {
+        const int4 t = __ldcs(reinterpret_cast<const int4*>(p) + g);
+        r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+    } else {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const longlong2 t = __ldcs(reinterpret_cast<const longlong2*>(p) + g * 2 + q);
+            r.v[2 * q] = (int)t.x; r.v[2 * q + 1] = (int)t.y;
+        }
+    }
+    return r;
+}
+)SHELL";
+
+static const char kIntStores[] = R"SHELL(
+__device__ __forceinline__ void pw_st1(void* p, i64 i, int v) {
+#if PW_OUT_DT == 3
+    reinterpret_cast<int*>(p)[i] = v;
+#else
+    reinterpret_cast<long long*>(p)[i] = (long long)v;
+#endif
+}
+__device__ __forceinline__ void pw_out(void* p, i64 g, i64 n, const PwVec& y) {
+#if PW_VEC
+#if PW_OUT_DT == 3
+    __stcs(reinterpret_cast<int4*>(p) + g, make_int4(y.v[0], y.v[1], y.v[2], y.v[3]));
+#else
+    __stcs(reinterpret_cast<longlong2*>(p) + g * 2, make_longlong2((long long)y.v[0], (long long)y.v[1]));
+    __stcs(reinterpret_cast<longlong2*>(p) + g * 2 + 1, make_longlong2((long long)y.v[2], (long long)y.v[3]));
+#endif
+#else
+    const i64 i = g * PW_G;
+#pragma unroll
+    for (int k = 0; k < PW_G; ++k)
+        if (i + k < n) pw_st1(p, i + k, y.v[k]);
+#endif
+}
+
+)SHELL";
+
+// Shared by both kinds of program (PW_T is float or int): broadcast indexing and how an input is read.
+static const char kInputs[] = R"SHELL(
+// Element of a broadcast input that output element i reads: (i / div) % mod, a zero extent skipping its step.
+__device__ __forceinline__ i64 pw_index(i64 i, i64 n, i64 div, i64 mod) {
+    if (n <= 0x7fffffffLL) {                       // the usual case: 32-bit division
+        unsigned j = (unsigned)i;
+        if (div > 0) j = div > 0x7fffffffLL ? 0u : j / (unsigned)div;
+        if (mod > 0 && mod <= 0x7fffffffLL) j %= (unsigned)mod;
+        return (i64)j;
+    }
+    if (div > 0) i /= div;
+    if (mod > 0) i %= mod;
+    return i;
+}
+template <int DT, int BC> __device__ __forceinline__ PwVec pw_in(const void* p, i64 g, i64 n, i64 div, i64 mod) {
+#if PW_VEC
+    if (BC == 2) return pw_ldv<DT>(p, pw_index(g * PW_G, n, 0, mod) / PW_G);      // a row vector, group by group
+#endif
+    if (BC) {
+        const i64 i = g * PW_G;
+        PwVec r;
+#pragma unroll
+        for (int k = 0; k < PW_G; ++k) r.v[k] = i + k < n ? pw_ld1<DT>(p, pw_index(i + k, n, div, mod)) : (PW_T)0;
+        return r;
+    }
+#if PW_VEC
+    return pw_ldv<DT>(p, g);
+#else
+    const i64 i = g * PW_G;
+    PwVec r;
+#pragma unroll
+    for (int k = 0; k < PW_G; ++k) r.v[k] = i + k < n ? pw_ld1<DT>(p, i + k) : (PW_T)0;
+    return r;
+#endif
+}
+)SHELL";
+
+static const char kKernel[] = R"SHELL(
 #define PW_THREADS 256
 #define PW_UNROLL 2
 extern "C" __global__ void __launch_bounds__(PW_THREADS) pw_jit_kernel(const void* p0, const void* p1, const void* p2, const void* p3,
@@ -290,7 +397,7 @@ extern "C" __global__ void __launch_bounds__(PW_THREADS) pw_jit_kernel(const voi
         for (int u = 0; u < PW_UNROLL; ++u) {               // every load of the trip is issued before the first use
             const i64 g = g0 + u * stride;
 #pragma unroll
-            for (int k = 0; k < PW_G; ++k) x0[u].v[k] = x1[u].v[k] = x2[u].v[k] = x3[u].v[k] = 0.0f;
+            for (int k = 0; k < PW_G; ++k) x0[u].v[k] = x1[u].v[k] = x2[u].v[k] = x3[u].v[k] = (PW_T)0;
             if (g < groups) {
                 x0[u] = pw_in<PW_DT0, PW_BC0>(p0, g, n, bc.div[0], bc.mod[0]);
 #if PW_N_IN > 1
@@ -320,7 +427,7 @@ extern "C" __global__ void __launch_bounds__(PW_THREADS) pw_jit_kernel(const voi
     const int tail = (int)(n % PW_G);
     if (blockIdx.x == 0 && (int)threadIdx.x < tail) {
         const i64 i = n - tail + threadIdx.x;
-        float v0 = 0.0f, v1 = 0.0f, v2 = 0.0f, v3 = 0.0f;
+        PW_T v0 = (PW_T)0, v1 = (PW_T)0, v2 = (PW_T)0, v3 = (PW_T)0;
         v0 = pw_ld1<PW_DT0>(p0, PW_BC0 ? pw_index(i, n, bc.div[0], bc.mod[0]) : i);
 #if PW_N_IN > 1
         v1 = pw_ld1<PW_DT1>(p1, PW_BC1 ? pw_index(i, n, bc.div[1], bc.mod[1]) : i);
@@ -351,23 +458,29 @@ static int broadcast_mode(const emmyb200_pw_program& p, int k, int group, bool b
 }
 
 static std::string program_source(const emmyb200_pw_program& p, int group, const int* modes) {
+    const bool ints = !float_program(p);
+    const char* type = ints ? "int" : "float";
     std::string s;
-    char line[160];
-    snprintf(line, sizeof line, "#define PW_N_IN %d\n#define PW_VEC %d\n#define PW_G %d\n#define PW_OUT_DT %d\n", p.n_inputs, group ? 1 : 0, group == 8 ? 8 : 4, p.out_dtype);
+    char line[200];
+    snprintf(line, sizeof line, "#define PW_N_IN %d\n#define PW_VEC %d\n#define PW_G %d\n#define PW_OUT_DT %d\n#define PW_T %s\n", p.n_inputs,
+             group ? 1 : 0, group == 8 && !ints ? 8 : 4, p.out_dtype, type);
     s += line;
     for (int k = 0; k < EMMYB200_PW_MAX_INPUTS; ++k) {
         const bool used = k < p.n_inputs;
-        snprintf(line, sizeof line, "#define PW_DT%d %d\n#define PW_BC%d %d\n", k, used ? p.in_dtype[k] : 0, k, used ? modes[k] : 0);
+        snprintf(line, sizeof line, "#define PW_DT%d %d\n#define PW_BC%d %d\n", k, used ? p.in_dtype[k] : (ints ? EMMYB200_I32 : EMMYB200_F32), k, used ? modes[k] : 0);
         s += line;
     }
-    s += "#include \"emmy_math.cuh\"\n"
-         "typedef long long i64;\n"
+    if (!ints) s += "#include \"emmy_math.cuh\"\n";
+    s += "typedef long long i64;\n"
          "struct PwConsts { float v[16]; };\n"
          "struct PwBcast { i64 div[4]; i64 mod[4]; };\n"
-         "__device__ __forceinline__ float pw_cell(float i0, float i1, float i2, float i3, const PwConsts& c) {\n"
-         "    float s0 = i0, s1 = i1, s2 = i2, s3 = i3";
+         "struct PwVec { PW_T v[PW_G]; };\n";
+    if (ints) s += kIntOps;
+    snprintf(line, sizeof line, "__device__ __forceinline__ %s pw_cell(%s i0, %s i1, %s i2, %s i3, const PwConsts& c) {\n    %s s0 = i0, s1 = i1, s2 = i2, s3 = i3",
+             type, type, type, type, type, type);
+    s += line;
     for (int k = EMMYB200_PW_MAX_INPUTS; k < EMMYB200_PW_MAX_SLOTS; ++k) {
-        snprintf(line, sizeof line, ", s%d = 0.0f", k);
+        snprintf(line, sizeof line, ", s%d = 0", k);
         s += line;
     }
     s += ";\n";
@@ -375,12 +488,15 @@ static std::string program_source(const emmyb200_pw_program& p, int group, const
         const emmyb200_pw_step& st = p.steps[i];
         snprintf(line, sizeof line, "    s%d = ", st.dst);
         s += line;
-        s += expand(op_expr(st.op), st);
+        s += expand(ints ? op_expr_int(st.op) : op_expr(st.op), st, ints);
         s += ";\n";
     }
     snprintf(line, sizeof line, "    return s%d;\n}\n", p.out_slot);
     s += line;
-    s += kShell;
+    s += ints ? kIntLoads : kFloatLoads;
+    s += kInputs;
+    s += ints ? kIntStores : kFloatStores;
+    s += kKernel;
     return s;
 }
 
@@ -390,7 +506,7 @@ static std::string program_key(const emmyb200_pw_program& p, int group, const in
     auto put = [&](int v) { k.push_back((char)(v & 0xff)); };
     put(p.n_inputs); put(p.n_steps); put(p.out_slot); put(p.out_dtype); put(group);
     for (int i = 0; i < p.n_inputs; ++i) { put(p.in_dtype[i]); put(modes[i]); }
-    for (int i = 0; i < p.n_steps; ++i) { put(p.steps[i].op); put(p.steps[i].dst); put(p.steps[i].a); put(p.steps[i].b); put(p.steps[i].c); }
+    for (int i = 0; i < p.n_steps; ++i) { put(p.steps[i].op); put(p.steps[i].dst); put(p.steps[i].a); put(p.steps[i].b); put(p.steps[i].c); put(p.steps[i].reserved[0]); }
     return k;
 }
 
@@ -440,11 +556,12 @@ struct PwConstsArg { float v[16]; };
 struct PwBcastArg { long long div[4]; long long mod[4]; };
 
 int pw_jit_launch(const emmyb200_pw_program& prog, const void* const* inputs, void* out, int64_t n, int group, cudaStream_t stream) {
-    if (!jit_enabled() || !float_program(prog) || !nvrtc().ok) return kPwJitUnavailable;
+    if (!jit_enabled() || !nvrtc().ok) return kPwJitUnavailable;
     JitKernel k;
     int modes[EMMYB200_PW_MAX_INPUTS] = {0, 0, 0, 0};
     for (int i = 0; i < prog.n_inputs; ++i) {
-        const int es = prog.in_dtype[i] == EMMYB200_F32 ? 4 : (prog.in_dtype[i] == EMMYB200_U8 ? 1 : 2);
+        const int dt = prog.in_dtype[i];
+        const int es = dt == EMMYB200_I64 ? 8 : (dt == EMMYB200_F32 || dt == EMMYB200_I32 ? 4 : (dt == EMMYB200_U8 ? 1 : 2));
         modes[i] = broadcast_mode(prog, i, group, aligned(inputs[i], (size_t)(group == 8 ? 8 : 4) * es));
     }
     {
@@ -502,8 +619,11 @@ extern "C" int emmyb200_pointwise_jit_state(int64_t* kernels_compiled) {
 extern "C" int64_t emmyb200_pointwise_program_source(const emmyb200_pw_program* prog, int group, char* text, int64_t capacity) {
     using namespace emmy;
     if (prog == nullptr || prog->n_inputs < 1 || prog->n_inputs > EMMYB200_PW_MAX_INPUTS || prog->n_steps < 0 ||
-        prog->n_steps > EMMYB200_PW_MAX_STEPS || prog->out_slot < 0 || prog->out_slot >= EMMYB200_PW_MAX_SLOTS || !float_program(*prog))
-        return fail(EMMYB200_ERR_ARG, "pointwise_program_source: not a float program");
+        prog->n_steps > EMMYB200_PW_MAX_STEPS || prog->out_slot < 0 || prog->out_slot >= EMMYB200_PW_MAX_SLOTS)
+        return fail(EMMYB200_ERR_ARG, "pointwise_program_source: not a program (inputs, steps or output slot out of range)");
+    if (!float_program(*prog) && prog->out_dtype != EMMYB200_I32 && prog->out_dtype != EMMYB200_I64)
+        return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_program_source: output dtype %d", prog->out_dtype);
+    if (!float_program(*prog) && group == 8) return fail(EMMYB200_ERR_ARG, "pointwise_program_source: integer programs use groups of 4");
     for (int i = 0; i < prog->n_steps; ++i) {
         const emmyb200_pw_step& st = prog->steps[i];
         if (st.op >= EMMYB200_PW_OP_COUNT || st.dst >= EMMYB200_PW_MAX_SLOTS) return fail(EMMYB200_ERR_ARG, "pointwise_program_source: bad step %d", i);

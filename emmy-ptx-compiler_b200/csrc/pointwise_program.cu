@@ -3,9 +3,9 @@
 //
 // The reference prints the instructions of each `Assign` into the kernel it is compiling
 // (emmyptx/kernel.py:766-784). Here the cell program travels as data: up to 48 steps `dst = op(a, b, c)` over
-// 16 value slots, operands being slots or constants. A float program is normally compiled into a kernel of its
-// own at first use (pointwise_jit.cu); this file holds the entry point, the integer programs, and the
-// interpreter that runs a float program when the run-time compiler is not there. One CTA-wide interpreter
+// 16 value slots, operands being slots or constants. A program is normally compiled into a kernel of its own at
+// first use (pointwise_jit.cu); this file holds the entry point and the interpreters that run a program when the
+// run-time compiler is not there. One CTA-wide interpreter
 // loop runs it -- the control flow is the same for every thread, so there is no divergence -- with the slots
 // held per thread as float4 (four elements at a time, 128-bit global accesses, 16-bit inputs and outputs
 // widened / rounded once at the ends, as emmyptx/kernel.py:693-712 does).
@@ -345,12 +345,7 @@ extern "C" int emmyb200_pointwise_program(const emmyb200_pw_program* prog, const
     const int64_t want = (groups + kPwThreads * kPwUnroll - 1) / (kPwThreads * kPwUnroll);
     const int64_t cap = (int64_t)sm_count() * 8;
     const unsigned blocks = (unsigned)(want < cap ? want : cap);
-    if (int_program) {
-        const int64_t want_i = (n + kPwThreads - 1) / kPwThreads;
-        pointwise_program_int_kernel<<<(unsigned)(want_i < cap ? want_i : cap), kPwThreads, 0, s>>>(*prog, args);
-        return launch_status("pointwise_program_int_kernel");
-    }
-    // A float program runs as a kernel compiled for it (pointwise_jit.cu); the interpreter below takes over where
+    // A program runs as a kernel compiled for it (pointwise_jit.cu); the interpreters below take over where
     // that form is switched off or the run-time compiler is missing.
     {
         // groups of 8 elements when a 16-bit or byte buffer takes part and every buffer is aligned for it
@@ -362,6 +357,11 @@ extern "C" int emmyb200_pointwise_program(const emmyb200_pw_program* prog, const
         }
         const int rc = pw_jit_launch(*prog, args.in, out, n, vec ? (narrow && vec8 ? 8 : 4) : 0, s);
         if (rc != kPwJitUnavailable) return rc;
+    }
+    if (int_program) {
+        const int64_t want_i = (n + kPwThreads - 1) / kPwThreads;
+        pointwise_program_int_kernel<<<(unsigned)(want_i < cap ? want_i : cap), kPwThreads, 0, s>>>(*prog, args);
+        return launch_status("pointwise_program_int_kernel");
     }
     // Which results must reach the slot file: those read by a step other than the next one before they are overwritten,
     // or (the last definition of the output slot, unless it is the last step) by the store. Inputs stay in registers

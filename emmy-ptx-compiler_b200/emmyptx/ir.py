@@ -581,3 +581,43 @@ def attention_kernel(units_shape: list[int], seq_q: int, seq_k: int, d: int, dty
     g = _graph(kern, [tensor("Q", shp + [seq_q, d], dtype), tensor("K", shp + [seq_k, d], dtype),
                       tensor("V", shp + [seq_k, d], dtype)], [tensor("O", shp + [seq_q, d], dtype)])
     return g, kern, _launch(kern, ["Q", "K", "V", "O"], u * -(-seq_q // 16) * 32, block=128)
+
+
+def attention_scalar_kernel(units_shape: list[int], seq_q: int, seq_k: int, d: int, dtype: str = "f32", scale: float | None = None,
+                            causal: bool = False, mask: str | None = None, name: str = "k_sdpa_f32"):
+    """softmax(Q K^T * scale) V on float32 buffers the way the reference lowers a fused expression without tensor-core
+    statements (tools/torch_cases/fused.py:21-22, 31-36; models.py:17-19): one tile cell per output element, dot
+    products as a `Loop` folding q * k with an `Accum` (emmyptx/kernel.py:786-797; every loop seeds the accumulators
+    directly inside it, emmyptx/loops.py:92-102), a first pass over the keys for the row maximum and a second one for
+    the sum of exponentials and the weighted sum of V. Only statements the reference's compiler has are used, so it
+    compiles this kernel too. `causal` / `mask` as in attention_kernel."""
+    scale = d ** -0.5 if scale is None else scale
+    kind = mask or ("causal" if causal else None)
+    add, mx = Op("add", 0.0), Op("maximum", float("-inf"))
+
+    def keep(j):
+        return {None: [],
+                "causal": [Assign("keep", Op("less_equal"), [j, "q0"])],        # axis variables are names like any other
+                "upper": [Assign("keep", Op("greater_equal"), [j, "q0"])],
+                "padding": [Assign("keep", Op("less"), [j, seq_k - 8])]}[kind]
+
+    def scores(j, k, out):
+        dot = Loop(Axis(k, Dim(d)), [Load(["qv"], "Q", [Var("u0"), Var("q0"), Var(k)]), Load(["kv"], "K", [Var("u0"), Var(j), Var(k)]),
+                                    Assign("pr", Op("multiply"), ["qv", "kv"]), Accum("dot_" + out, None, "pr", add)])
+        fill = [Assign(out, Op("where"), ["keep", out, float("-inf")])] if kind else []
+        return [dot, Assign(out, Op("multiply"), ["dot_" + out, scale]), *keep(j), *fill]
+
+    u = 1
+    for s in units_shape:
+        u *= s
+    body = [Loop(Axis("j0", Dim(seq_k)), [*scores("j0", "k0", "t"), Accum("mx", None, "t", mx)]),
+            Loop(Axis("j1", Dim(seq_k)), [*scores("j1", "k1", "t2"), Assign("dl", Op("subtract"), ["t2", "mx"]), Assign("e", Op("exp"), ["dl"]),
+                                          Accum("den", None, "e", add), Load(["vv"], "V", [Var("u0"), Var("j1"), Var("c0")]),
+                                          Assign("pv", Op("multiply"), ["e", "vv"]), Accum("num", None, "pv", add)]),
+            Assign("o", Op("divide"), ["num", "den"]),
+            Write("O", [Var("u0"), Var("q0"), Var("c0")], ["o"])]
+    kern = KernelOp(name, [Tile([Axis("u0", Dim(u)), Axis("q0", Dim(seq_q)), Axis("c0", Dim(d))], body)])
+    g = _graph(kern, [tensor("Q", [u, seq_q, d], dtype), tensor("K", [u, seq_k, d], dtype), tensor("V", [u, seq_k, d], dtype)],
+               [tensor("O", [u, seq_q, d], dtype)])
+    return g, kern, _launch(kern, ["Q", "K", "V", "O"], u * seq_q * d)
+

@@ -548,8 +548,8 @@ def match_contraction(graph, kernel, launch: dict) -> dict:
         if not (len(q) >= 2 and q[:-2] == k[:-2] == v[:-2] == o[:-2] and k == v and q == o and q[-1] == k[-1]):
             raise Unmatched(f"attention shapes do not agree: {q}, {k}, {v} -> {o}")
         d = q[-1]
-        if d not in (64, 128):
-            raise Unmatched(f"attention head dim {d} has no variant (64, 128)")
+        if d % 32 or not 32 <= d <= 128:
+            raise Unmatched(f"attention head dim {d} has no variant (multiples of 32 up to 128)")
         scale, causal = _attention_scale(stmts, mmas, d), _attention_mask(kernel, stmts, q[-2], k[-2])
         return {"variant": "attention_fwd", "inputs": srcs, "outputs": [out],
                 "params": {"dtype": dtype, "units": math.prod(q[:-2]), "seq_q": q[-2], "seq_k": k[-2], "d": d, "scale": scale,
@@ -812,11 +812,156 @@ def match_dot(graph, kernel, launch: dict) -> dict:
     raise Unmatched("the loop is not a plain product (optionally plus a bias vector, optionally through ReLU)")
 
 
+class NestInterpreter(RowInterpreter):
+    """Runs a kernel whose loops nest (a dot product per key inside a loop over the keys) on a few probe cells. The
+    innermost loops run once on whole vectors, as in RowInterpreter; a loop that contains another runs iteration by
+    iteration, its own `Accum`s folding one value per trip. Every loop seeds the accumulators directly inside it with
+    the op's identity (emmyptx/loops.py:92-102). Loads are recorded at their first execution only."""
+
+    def __init__(self, tensors: dict, cells: np.ndarray, cols: int) -> None:
+        super().__init__(tensors, cells, cols)
+        self.vector = False                 # inside an innermost loop
+        self.first_loads: dict = {}         # id(statement) -> (buffer, flat index at the first execution)
+
+    def _value(self, a):
+        return self.expr(a) if hasattr(a, "free_vars") or _kind(a) in ("Var", "Literal", "BinaryExpr") else self.lookup(a)
+
+    def run(self, stmts) -> None:
+        for s in stmts:
+            k = _kind(s)
+            if k in ("Loop", "StridedLoop"):
+                extent = int(s.axis.extent.as_static())
+                if getattr(s, "seed", True):
+                    for a in s.body:
+                        if _kind(a) == "Accum":
+                            ident = getattr(a.op, "identity", None)
+                            self.env[a.name] = np.full(self.cells.shape, 0.0 if ident is None else float(ident))
+                if any(_kind(x) in ("Loop", "StridedLoop") for x in walk(s.body)):
+                    for i in range(extent):
+                        self.env[s.axis.name] = np.full(self.cells.shape, i, dtype=np.int64)
+                        self.run(s.body)
+                else:
+                    if extent != self.cols:
+                        raise Unmatched("the innermost loops of a fused attention run over the head dimension")
+                    self.env[s.axis.name] = np.broadcast_to(np.arange(self.cols, dtype=np.int64), self.cells.shape)
+                    self.vector = True
+                    try:
+                        self.run(s.body)
+                    finally:
+                        self.vector = False
+            elif k == "Accum":
+                if s.op.name not in _ACCUM:
+                    raise Unmatched(f"no reduction folds with {s.op.name!r}")
+                value = np.asarray(self.lookup(s.value), np.float64)
+                base = np.asarray(self.lookup(s.base if s.base is not None else s.name), np.float64)
+                if self.vector:
+                    value, base = _ACCUM[s.op.name](value, axis=1, keepdims=True), base[:, :1]
+                self.env[s.name] = np.broadcast_to(FLOAT_OPS[s.op.name][1](base, value), self.cells.shape)
+            elif k == "Load":
+                n_before = len(self.loads)
+                CellInterpreter.run(self, [s])
+                buf, flat, _ = self.loads.pop()
+                assert len(self.loads) == n_before
+                self.first_loads.setdefault(id(s), (buf, flat))
+            elif k == "Assign":
+                if s.op.name not in FLOAT_OPS:
+                    raise OpError(f"elementwise op {s.op.name!r} is not supported")
+                with np.errstate(all="ignore"):
+                    self.env[s.name] = np.broadcast_to(FLOAT_OPS[s.op.name][1](*[np.asarray(self._value(a), np.float64) for a in s.args]),
+                                                       self.cells.shape)
+            elif k in ("WarpShuffle", "TreeHalve", "Sync", "Smem", "Init"):
+                continue
+            else:
+                CellInterpreter.run(self, [s])
+
+
+def match_attention_scalar(graph, kernel, launch: dict) -> dict:
+    """softmax(Q K^T * scale) V written as scalar loops on float buffers (the reference's own attention cases:
+    tools/torch_cases/fused.py:21-22, 31-36; models.py:17-19): recognised by running a few output cells and comparing
+    them with the attention of the probe buffers, unmasked and lower-triangular, for every literal that could be the
+    scale. Anything else the loops might compute -- another mask, a bias on the scores -- matches nothing."""
+    tensors = tensor_table(graph)
+    tiles = [s for s in kernel.body if _kind(s) == "Tile"]
+    if len(kernel.body) != 1 or len(tiles) != 1:
+        raise Unmatched("a fused attention kernel is one Tile")
+    tile = tiles[0]
+    writes = [s for s in walk(tile.body) if _kind(s) == "Write"]
+    if len(writes) != 1 or writes[0].output not in tensors:
+        raise Unmatched("a fused attention kernel writes one buffer")
+    out_name = writes[0].output
+    o_shape, o_dtype = tensors[out_name]
+    if len(o_shape) < 2:
+        raise Unmatched("attention output is [..., queries, d]")
+    seq_q, d = int(o_shape[-2]), int(o_shape[-1])
+    units = math.prod(o_shape[:-2])
+    cells = math.prod(int(a.extent.as_static()) for a in tile.axes)
+    if cells != units * seq_q * d:
+        raise Unmatched("one tile cell per output element")
+    if o_dtype not in ("f32", "f16", "bf16"):
+        raise Unmatched("attention buffers are float")
+    if d % 32 or not 32 <= d <= 128:
+        raise Unmatched(f"attention head dim {d} has no variant (multiples of 32 up to 128)")
+    rng = np.random.default_rng(1)
+    rows = np.unique([0, 1, seq_q // 2, seq_q - 1])
+    probe = np.unique([(int(rng.integers(0, units)) * seq_q + int(r)) * d + int(rng.integers(0, d)) for r in rows for _ in range(2)]).astype(np.int64)
+    it = NestInterpreter(tensors, probe, d)
+    rem = np.broadcast_to(probe[:, None], it.cells.shape).copy()
+    for a in reversed(tile.axes):
+        e = int(a.extent.as_static())
+        it.env[a.name] = rem % e
+        rem = rem // e
+    it.run(tile.body)
+    if len(it.writes) != 1 or len(it.writes[0][2]) != 1 or not np.array_equal(it.writes[0][1][:, 0], probe):
+        raise Unmatched("a fused attention kernel writes O[unit, query, column], one cell each")
+    got = np.asarray(it.writes[0][2][0], np.float64)[:, 0]
+    un, qi, ci = probe // (seq_q * d), (probe // d) % seq_q, probe % d
+    kk = np.arange(d)[None, :]
+    loads = list(it.first_loads.values())
+    q_idx = (un[:, None] * seq_q + qi[:, None]) * d + kk
+    q_name = next((b for b, i in loads if tuple(tensors[b][0][-2:]) == (seq_q, d) and math.prod(tensors[b][0]) == units * seq_q * d
+                   and np.array_equal(i, q_idx)), None)
+    others = [(b, i) for b, i in loads if b != q_name]
+    if q_name is None or not others:
+        raise Unmatched("the loops do not read q[unit, query, :]")
+    seq_k = int(tensors[others[0][0]][0][-2])
+    k_idx0 = (un[:, None] * seq_k) * d + kk                      # key 0, all columns: the first trip of the key loop
+    v_idx0 = np.broadcast_to((un[:, None] * seq_k) * d + ci[:, None], k_idx0.shape)
+    fits = lambda b: len(tensors[b][0]) >= 2 and tuple(tensors[b][0][-2:]) == (seq_k, d) and math.prod(tensors[b][0]) == units * seq_k * d
+    k_name = next((b for b, i in others if fits(b) and np.array_equal(i, k_idx0)), None)
+    v_name = next((b for b, i in others if fits(b) and b != k_name and np.array_equal(i, v_idx0)), None)
+    if k_name is None or v_name is None or {b for b, _ in loads} != {q_name, k_name, v_name}:
+        raise Unmatched("the loops do not read k[unit, key, :] and v[unit, key, column] besides q")
+    if len({tensors[b][1] for b in (q_name, k_name, v_name, out_name)}) != 1:
+        raise Unmatched("q, k, v and the output share one dtype")
+    dt = tensors[q_name][1]
+    jj = np.arange(seq_k)
+    qv = probe_values(q_name, dt, q_idx)                                                                    # [P, d]
+    kv = probe_values(k_name, dt, ((un[:, None, None] * seq_k + jj[None, :, None]) * d + kk[None, :, :]))     # [P, seq_k, d]
+    vv = probe_values(v_name, dt, (un[:, None] * seq_k + jj[None, :]) * d + ci[:, None])                    # [P, seq_k]
+    dots = np.einsum("pd,pjd->pj", qv, kv)
+    literals = {float(a) for s in walk(tile.body) if _kind(s) == "Assign" and s.op.name in ("multiply", "divide")
+                for a in s.args if isinstance(a, (int, float)) and not isinstance(a, bool) and np.isfinite(a) and a != 0}
+    scales = sorted(literals | {1.0 / x for x in literals} | {1.0})
+    for causal in (False, True):
+        for scale in scales:
+            t = dots * scale
+            if causal:
+                t = np.where(jj[None, :] <= qi[:, None], t, -np.inf)
+            ref = (_softmax64(t) * vv).sum(-1)
+            if np.allclose(got, ref, rtol=1e-9, atol=1e-12):
+                return {"variant": "attention_fwd", "inputs": [q_name, k_name, v_name], "outputs": [out_name],
+                        "params": {"dtype": dt, "units": units, "seq_q": seq_q, "seq_k": seq_k, "d": d, "scale": scale, "causal": causal}}
+    raise Unmatched("the loops are not softmax(q k^T * scale) v, unmasked or with the lower-triangular mask")
+
+
 def match_kernel(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
     kinds = {_kind(s) for s in walk(kernel.body)}
     if "MmaSyncPtx" in kinds:
         return match_contraction(graph, kernel, launch)
     if "Accum" in kinds:
+        loops = [s for s in walk(kernel.body) if _kind(s) in ("Loop", "StridedLoop")]
+        if any(_kind(x) in ("Loop", "StridedLoop") for lp in loops for x in walk(lp.body)):
+            return match_attention_scalar(graph, kernel, launch)            # loops that nest: a dot product per key
         try:
             return match_dot(graph, kernel, launch)
         except Unmatched:

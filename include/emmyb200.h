@@ -102,20 +102,20 @@ typedef struct {
 int emmyb200_pointwise_program(const emmyb200_pw_program* program, const void* const* inputs, void* out,
                                int64_t n, void* cuda_stream);
 
-/* How float programs run. By default each distinct program shape (op sequence, operand wiring, dtypes, which inputs
+/* How programs run. By default each distinct program shape (op sequence, operand wiring, dtypes, which inputs
  * are broadcast, vector or scalar accesses) is compiled once, at its first launch, into a kernel of its own -- the
  * counterpart of the reference printing the ops into the entry it compiles (emmyptx/kernel.py:766-784) -- by the
  * toolkit's run-time compiler (libnvrtc.so.12, looked up when first needed; EMMYB200_NVRTC names another file).
  * Constants and broadcast extents are launch arguments and do not compile again. The first launch of a shape takes
  * the compile time (a fraction of a second) and cannot be part of a stream capture. With the compiler missing, or
- * after emmyb200_set_pointwise_jit(0) (or EMMYB200_PW_JIT=0 in the environment), programs run on a precompiled
- * interpreter kernel with the same results bit for bit (the sign and payload of a NaN aside), at a fraction of the
+ * after emmyb200_set_pointwise_jit(0) (or EMMYB200_PW_JIT=0 in the environment), programs run on precompiled
+ * interpreter kernels with the same results bit for bit (the sign and payload of a NaN aside), at a fraction of the
  * bandwidth.
  *   emmyb200_set_pointwise_jit      returns the previous setting (1 compiled, 0 interpreter).
  *   emmyb200_pointwise_jit_state    1 compiled form in use, 0 switched off, -1 wanted but the compiler could not be
  *                                   loaded; *kernels_compiled (may be NULL) counts the compilations so far.
  *   emmyb200_pointwise_program_source   the CUDA C++ text of the kernel for `program`; group = elements per thread and
- *                                   access: 4 (128-bit accesses of fp32), 8 (128-bit accesses of 16-bit types), 0
+ *                                   access: 4 (128-bit accesses of fp32 / i32), 8 (128-bit accesses of 16-bit types; float programs only), 0
  *                                   (scalar accesses, for unaligned buffers); returns the size needed including the
  *                                   terminator, or a negative status.
  *   emmyb200_pointwise_program_compile  compiles that text for sm_100a without launching (no device needed);
@@ -200,8 +200,11 @@ int emmyb200_gemm_allgather(int dtype, int epilogue, int flags, const void* A, c
 /* O = softmax(Q K^T * scale) V per (batch, head) unit, fp32 softmax, non-causal: what the
  * reference emits as generic fused statements (dot-product Loops + Accum, WarpShuffle /
  * TreeHalve row reductions, `_exp`: emmyptx/kernel.py:786-797, :856-900, emmyptx/ops.py:49-77).
- * Q, O: [units, seq_q, d]; K, V: [units, seq_k, d]; contiguous, dtype F16 or BF16, d = 128
- * or 64, any seq_q, seq_k >= 1. EMMYB200_ATT_CAUSAL: query i attends to keys 0..i only (the lower-triangular
+ * Q, O: [units, seq_q, d]; K, V: [units, seq_k, d]; contiguous, any seq_q, seq_k >= 1. dtype F16 or BF16 with d = 128
+ * or 64 runs on the tensor cores (the benchmark configuration). dtype F32 -- the reference's own attention cases,
+ * tools/torch_cases/fused.py:21-22, 31-36, models.py:17-19 -- and 16-bit buffers with another head size (d a
+ * multiple of 32 up to 128) run on a CUDA-core kernel that keeps every product and sum in fp32, as the reference's
+ * lowering does; it has one form, one destination and at most 65535 units. EMMYB200_ATT_CAUSAL: query i attends to keys 0..i only (the lower-triangular
  * mask of tools/torch_cases/models.py:17-19, fused.py:31-36). Two kernel forms exist -- one 128-query tile per
  * CTA with two CTAs sharing an SM, or two tiles per persistent CTA -- and the library picks by the causal flag (what
  * was measured faster); EMMYB200_ATT_FORM_ONE_TILE / _TWO_TILES force one (tuning and tests; results agree within the

@@ -42,6 +42,13 @@ def gemm_inputs(m: int, n: int, k: int, dtype: str, b_is_nk: bool = False, scale
     return torch.from_numpy(a).to(td), torch.from_numpy(b).to(td)
 
 
+def attention_inputs_f32(units: int, seq_q: int, seq_k: int, d: int):
+    """Q[units,seq_q,d], K, V[units,seq_k,d] ~ N(0,1) as float32 numpy arrays, argument i seeded with i, the way the
+    reference's runner fills graph inputs (tools/run_local.py:86-87)."""
+    return tuple(np.random.default_rng(seed).standard_normal((units, s, d)).astype(np.float32)
+                 for seed, s in ((0, seq_q), (1, seq_k), (2, seq_k)))
+
+
 def attention_inputs(units: int, seq_q: int, seq_k: int, d: int, dtype: str = "bf16"):
     """Q[units,seq_q,d], K, V[units,seq_k,d] ~ N(0,1), rounded to `dtype`; torch CPU tensors."""
     import torch

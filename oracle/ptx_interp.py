@@ -1,4 +1,4 @@
-"""A small CPU interpreter for the straight-line PTX the reference emits for streaming kernels.
+"""A small CPU interpreter for the PTX the reference emits for streaming kernels, scalar loops and tensor-core tiles.
 TEST INFRASTRUCTURE ONLY (see oracle/__init__.py).
 
 It executes a `.visible .entry` of the reference's output (tests/golden/*.ref.ptx, produced by
@@ -15,7 +15,8 @@ kernels of `emmyptx/mma.py` (fragments read from global memory as packed 16-bit 
 f16 / bf16 with f32 accumulators, converted `.v2.b16` stores). `mma.sync` is evaluated per warp from the PTX
 ISA's fragment lane map (restated in emmyptx/mma.py:6-10) with exact products summed in float64 and rounded to
 f32 once per instruction: the hardware's summation order inside one instruction is unspecified, so outputs carry
-the reference's algorithm, not one GPU's low bits. Anything else (run-time loops included) raises.
+the reference's algorithm, not one GPU's low bits. Run-time loops (emmyptx/loops.py:231-264) are followed when every
+active thread takes the same way at each branch, which holds for loops with static trip counts. Anything else raises.
 """
 from __future__ import annotations
 
@@ -73,10 +74,22 @@ class Interpreter:
         self.reg: dict = {}
         self.active = np.ones(n, dtype=bool)
         self.n = n
-        for line in self.lines:
+        labels = {line[:-1]: i for i, line in enumerate(self.lines) if line.endswith(":")}
+        self.jump = None
+        pc, executed = 0, 0
+        while pc < len(self.lines):
+            line = self.lines[pc]
+            pc += 1
             if line.endswith(":"):
                 continue
             self._exec(line)
+            executed += 1
+            if executed > 50_000_000:
+                raise PtxError("instruction budget exhausted (a loop that does not end?)")
+            if self.jump is not None:                    # a branch every active thread took (run-time loops)
+                if self.jump not in labels:
+                    raise PtxError(f"branch to unknown label {self.jump}")
+                pc, self.jump = labels[self.jump], None
 
     # ---- operands -----------------------------------------------------------------------------------
     def _val(self, tok: str, ty: str):
@@ -148,9 +161,17 @@ class Interpreter:
         if name == "ret":
             return
         if name == "bra":
-            if ops[0] != "$L_exit":
-                raise PtxError("only the early-exit branch is supported")
-            self.active = self.active & ~(np.ones(self.n, bool) if mask is None else mask)
+            taken = np.ones(self.n, bool) if mask is None else mask
+            if ops[0] == "$L_exit":
+                self.active = self.active & ~taken
+                return
+            # Any other branch belongs to a run-time loop (emmyptx/loops.py:231-264): its trip count does not depend on
+            # the thread, so either every active thread takes it or none does. Divergence is refused.
+            t = taken[self.active]
+            if t.size and t.all():
+                self.jump = ops[0]
+            elif t.any():
+                raise PtxError("a branch on which the active threads diverge is not supported")
             return
         if name == "ld" and parts[1] == "param":
             self._set(ops[0], self.param_addr[ops[1].strip("[]")])

@@ -99,13 +99,16 @@ def gemm_tolerance_ok(got, ref, rel: float = 1e-2):
 
 
 # ---- C5: attention forward ----------------------------------------------------------------------------
-def attention_reference(q, k, v, scale: float | None = None, double: bool = False):
-    """softmax(q k^T * scale) v per unit, fp32 (or fp64) throughout, on the already-rounded inputs."""
+def attention_reference(q, k, v, scale: float | None = None, double: bool = False, causal: bool = False):
+    """softmax(q k^T * scale) v per unit, fp32 (or fp64) throughout, on the already-rounded inputs. `causal`: scores of
+    keys after the query are filled with -inf (tools/torch_cases/fused.py:31-36, models.py:17-19)."""
     import torch
     dt = torch.float64 if double else torch.float32
     q, k, v = q.to(dt), k.to(dt), v.to(dt)
     scale = q.shape[-1] ** -0.5 if scale is None else scale
     s = torch.matmul(q, k.transpose(-1, -2)) * scale
+    if causal:
+        s = s.masked_fill(~torch.ones(q.shape[-2], k.shape[-2], dtype=torch.bool).tril(), float("-inf"))
     return torch.matmul(torch.softmax(s, dim=-1), v)
 
 

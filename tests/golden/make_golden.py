@@ -5,7 +5,8 @@ oracle/ptx_interp.py on the seeded inputs of oracle/inputs.py.
 
 Writes tests/golden/golden.npz: for each case the output the reference's kernel produces (`<case>.y`; for the
 tensor-core GEMM cases `<case>.c`, the 16-bit output as raw bit patterns, on N(0,1) operands seeded per argument
-as oracle/inputs.gemm_inputs(scaled=False) draws them). Integer outputs are exact; float outputs are the reference's algorithm with its three hardware
+as oracle/inputs.gemm_inputs(scaled=False) draws them; for the fp32 attention cases `<case>.o`, on the operands of
+oracle/inputs.attention_inputs_f32). Integer outputs are exact; float outputs are the reference's algorithm with its three hardware
 approximations evaluated correctly rounded (see ptx_interp.py). Regenerate only together with the .ref.ptx
 files (make_reference_ptx.py, which needs the reference checkout).
 """
@@ -37,6 +38,15 @@ for name, info in manifest.items():
             c = c[keep]
         out[f"{name}.c"] = c
         print(name, c[0, :4])
+        continue
+    if "attention" in info:
+        a = info["attention"]
+        units = int(np.prod(a["units"]))
+        q, k, v = inputs.attention_inputs_f32(units, a["seq_q"], a["seq_k"], a["d"])
+        bufs = {"Q": q.copy(), "K": k.copy(), "V": v.copy(), "O": np.zeros((units, a["seq_q"], a["d"]), np.float32)}
+        ptx_interp.run_entry((HERE / f"{name}.ref.ptx").read_text(), bufs, info["launch"]["grid"][0], info["launch"]["block"][0])
+        out[f"{name}.o"] = bufs["O"]
+        print(name, bufs["O"][0, 0, :4])
         continue
     n = info["tensors"]["x"]["shape"][0]
     if n > 2**20 or (name.startswith("c1") and n > 4096 and False):

@@ -1,4 +1,5 @@
-"""Generate the reference's own PTX for the two streaming configurations and for tensor-core GEMMs, as fixtures.
+"""Generate the reference's own PTX for the two streaming configurations, for tensor-core GEMMs and for its fp32
+attention cases, as fixtures.
 
     python tests/golden/make_reference_ptx.py <path to a checkout of the reference>
 
@@ -15,6 +16,11 @@ M % 16 == N % 8 == K % 16 == 0, for which the IR carries no guards and every add
 buffer by construction -- the script works the largest element index of every fragment load and store out of the
 IR's own index expressions and stops if one is out of range. Ragged cases (clamped rows, zero-filled K tail,
 predicated stores) are only ever executed by the CPU interpreter.
+
+The attention cases are the reference's own three (tools/torch_cases/fused.py:21-22, 31-36; models.py:17-19): fp32
+q, k, v, compiled from the scalar-loop stand-in IR (`ir.attention_scalar_kernel`: one cell per output element, nested
+loops with static trip counts, no barriers). Every buffer index is a bare tile or loop variable whose extent equals
+the buffer's extent in that position, which the script checks, and the cell count is a whole number of blocks.
 """
 import importlib.util
 import json
@@ -56,6 +62,34 @@ GEMMS = {       # name: (m, n, k, dtype, b_trans, batch, device)
     "m_f16_bmm": (128, 96, 64, "f16", False, (4,), True),                    # matmul.py:31
     "c3_f16_mm_4096": (4096, 4096, 4096, "f16", False, (), True),            # configuration 3: timed on the device only
 }
+
+
+ATTENTION = {   # name: (units shape, seq_q, seq_k, d, causal, scale)
+    "f_sdpa": ([1, 2], 64, 64, 32, False, None),                              # fused.py:21-22
+    "t_causal_sdpa": ([1, 4], 128, 128, 64, True, None),                      # models.py:17-19
+    "f_masked_attn_manual": ([1], 64, 64, 32, True, 0.17677669),              # fused.py:31-36: scores above the diagonal filled
+}
+
+
+def assert_indices_are_axes(graph, kernel) -> None:
+    """Every Load / Write index of a scalar-loop kernel is a bare axis variable with the buffer's own extent."""
+    shapes = {t.name: [d.as_static() for d in t.shape] for nd in graph.nodes.values() for t in nd.outputs}
+    tile = kernel.body[0]
+    extent = {a.name: a.extent.as_static() for a in tile.axes}
+    for s in ir_walk(tile.body):
+        if type(s).__name__ == "Loop":
+            extent[s.axis.name] = s.axis.extent.as_static()
+    cells = 1
+    for a in tile.axes:
+        cells *= a.extent.as_static()
+    assert cells % 256 == 0
+    for s in ir_walk(tile.body):
+        kind = type(s).__name__
+        if kind in ("Load", "Write"):
+            buf, idx = (s.input, s.index) if kind == "Load" else (s.output, s.index)
+            assert len(idx) == len(shapes[buf])
+            for e, dim in zip(idx, shapes[buf]):
+                assert type(e).__name__ == "Var" and extent[e.name] == dim, (kind, buf, e)
 
 
 def _max_index(e, hi: dict) -> int:
@@ -115,10 +149,16 @@ for name, (m, n, k, dtype, b_trans, batch, device) in GEMMS.items():
         assert_in_range(graph, kernel, m, n, k)
     CASES[name] = (graph, kernel, launch)
 
+for name, (units, sq, sk, d, causal, scale) in ATTENTION.items():
+    graph, kernel, launch = ir.attention_scalar_kernel(units, sq, sk, d, "f32", scale, causal, name=name)
+    assert_indices_are_axes(graph, kernel)
+    CASES[name] = (graph, kernel, launch)
+
 for name, (graph, kernel, launch) in CASES.items():
     ptx = compile_kernel(graph, kernel, launch, target="sm_89")
     (HERE / f"{name}.ref.ptx").write_text(ptx)
     manifest[name] = {"entry": kernel.name, "launch": launch, **({"gemm": dict(zip(("m", "n", "k", "dtype", "b_trans", "batch", "device"), GEMMS[name]))} if name in GEMMS else {}),
+                      **({"attention": dict(zip(("units", "seq_q", "seq_k", "d", "causal", "scale"), ATTENTION[name]))} if name in ATTENTION else {}),
                       "tensors": {t.name: {"shape": [d.as_static() for d in t.shape], "dtype": t.dtype.name}
                                   for n in graph.nodes.values() for t in n.outputs}}
     print(f"{name}: {len(ptx.splitlines())} lines of PTX")

@@ -40,7 +40,7 @@ def test_argument_checks_need_no_device(lib):
     assert lib.emmyb200_index_gather_i32(None, None, 16, 1, 0, 3, 2, 0, None) == -1
     assert lib.emmyb200_gemm(0, 0, 0, None, None, None, 8, 8, 8, 8, 8, 8, None) == -4
     assert lib.emmyb200_gemm(1, 0, 0, None, None, None, 8, 8, 8, 8, 8, 8, None) == -1
-    assert lib.emmyb200_attention_fwd(2, 0, None, None, None, None, 1, 8, 8, 96, 1.0, None) == -4
+    assert lib.emmyb200_attention_fwd(2, 0, None, None, None, None, 1, 8, 8, 80, 1.0, None) == -4
     assert lib.emmyb200_attention_fwd(2, 0, None, None, None, None, 1, 8, 8, 128, 1.0, None) == -1
 
 

@@ -289,3 +289,32 @@ def test_common_activations_map_to_streaming_ops():
     assert (h["variant"], h["params"]["op"]) == ("pointwise_f32", "sigmoid")
     h = handle(ir.elementwise_kernel(4096, {"x": "f32"}, [("y", "maximum", ["x", 0.0])]))
     assert (h["variant"], h["params"]["op"]) == ("pointwise_f32", "relu")
+
+
+
+def test_scalar_loop_attention_is_matched_by_behaviour():
+    """The reference's own attention cases are fp32 and arrive as nested scalar loops (tools/torch_cases/fused.py:21-22,
+    31-36; models.py:17-19); a few output cells are run and compared with attention of the probe buffers."""
+    h = handle(ir.attention_scalar_kernel([1, 2], 64, 64, 32))
+    assert h["variant"] == "attention_fwd" and h["inputs"] == ["Q", "K", "V"] and h["outputs"] == ["O"]
+    assert h["params"] == {"dtype": "f32", "units": 2, "seq_q": 64, "seq_k": 64, "d": 32, "scale": 32 ** -0.5, "causal": False}
+    h = handle(ir.attention_scalar_kernel([1, 4], 128, 128, 64, causal=True))
+    assert h["params"]["causal"] is True and h["params"]["scale"] == 0.125 and h["params"]["units"] == 4
+    h = handle(ir.attention_scalar_kernel([1], 64, 64, 32, scale=0.17677669, causal=True))
+    assert h["params"]["scale"] == 0.17677669 and h["params"]["causal"] is True
+    h = handle(ir.attention_scalar_kernel([3], 40, 72, 96, scale=2.0))
+    assert (h["params"]["seq_q"], h["params"]["seq_k"], h["params"]["d"], h["params"]["scale"]) == (40, 72, 96, 2.0)
+    assert algorithmic_work(h) == (4.0 * 3 * 40 * 72 * 96, "flop")
+    for mask in ("upper", "padding"):
+        with pytest.raises(CompileError, match="lower-triangular"):
+            handle(ir.attention_scalar_kernel([2], 64, 64, 32, mask=mask))
+    with pytest.raises(CompileError, match="head dim"):
+        handle(ir.attention_scalar_kernel([2], 64, 64, 48))
+    # a bias on the scores is some other function: nothing matches
+    g, k, launch = ir.attention_scalar_kernel([2], 64, 64, 32)
+    for loop in (s for s in k.body[0].body if type(s).__name__ == "Loop"):
+        at = next(i for i, s in enumerate(loop.body) if type(s).__name__ == "Assign" and s.op.name == "multiply")
+        loop.body.insert(at + 1, ir.Assign(loop.body[at].name, ir.Op("add"), [loop.body[at].name, "j0" if loop.axis.name == "j0" else "j1"]))
+    with pytest.raises(CompileError, match="not softmax"):
+        handle((g, k, launch))
+

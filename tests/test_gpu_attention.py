@@ -141,10 +141,68 @@ def test_rejects_bad_arguments(cuda, lib):
     x = torch.zeros(2 * 128 * 128, dtype=torch.bfloat16, device=cuda)
     p = x.data_ptr()
     f = lib.emmyb200_attention_fwd
-    assert f(2, 0, p, p, p, p, 2, 128, 128, 96, 0.1, None) == -4      # head dim
-    assert f(0, 0, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -4     # f32
+    assert f(2, 0, p, p, p, p, 2, 128, 128, 80, 0.1, None) == -4      # head dim: multiples of 32 up to 128
+    assert f(2, 0, p, p, p, p, 2, 128, 128, 160, 0.1, None) == -4
+    assert f(3, 0, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -4     # an integer dtype
+    assert f(0, 4, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -4     # f32 has one kernel form
+    assert f(2, 8, p, p, p, p, 2, 128, 128, 32, 0.1, None) == -4      # and so has a head size off the tensor-core kernels
     assert f(2, 0, p, p, p, p, 2, 128, 0, 128, 0.1, None) == -2       # no keys
     assert f(2, 0, p, p, p, p, 0, 128, 128, 128, 0.1, None) == 0      # no units
     assert f(2, 16, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -1    # unknown flag
     assert f(2, 12, p, p, p, p, 2, 128, 128, 128, 0.1, None) == -1    # both form flags
     assert f(2, 0, None, p, p, p, 2, 128, 128, 128, 0.1, None) == -1
+
+
+# ---- fp32 buffers, and head sizes the tensor-core kernels do not take: the CUDA-core kernel ------------------------
+def _attn_ref64(q, k, v, scale, causal):
+    import torch
+    s = torch.matmul(q.double(), k.double().transpose(-1, -2)) * scale
+    if causal:
+        s = s.masked_fill(~torch.ones(q.shape[-2], k.shape[-2], dtype=torch.bool).tril(), float("-inf"))
+    return torch.matmul(torch.softmax(s, -1), v.double())
+
+
+@pytest.mark.parametrize("units,sq,sk,d,causal,scale", [
+    (2, 64, 64, 32, False, None),            # f_sdpa: q, k, v = randn(1, 2, 64, 32)            (tools/torch_cases/fused.py:21-22)
+    (4, 128, 128, 64, True, None),           # t_causal_sdpa: randn(1, 4, 128, 64), is_causal   (models.py:17-19)
+    (1, 64, 64, 32, True, 0.17677669),       # f_masked_attn_manual: mask above the diagonal   (fused.py:31-36)
+    (3, 77, 130, 96, False, None), (2, 33, 200, 128, False, 0.3), (2, 200, 200, 128, True, None), (1, 1, 1, 32, False, None),
+    (5, 300, 45, 64, False, None),
+])
+def test_f32_attention_in_fp32_arithmetic(units, sq, sk, d, causal, scale, cuda):
+    """The reference's own attention cases are fp32 with d = 32 or 64; its tolerance class for them is MM (rtol = atol
+    = 1e-3). The kernel keeps every product in fp32, so the bound here is two orders tighter."""
+    import torch
+    g = torch.Generator().manual_seed(units * 1000 + sq)
+    q = torch.randn(units, sq, d, generator=g)
+    k, v = torch.randn(units, sk, d, generator=g), torch.randn(units, sk, d, generator=g)
+    sc = d ** -0.5 if scale is None else scale
+    got = _attn(q, k, v, cuda, causal=causal, scale=sc)
+    assert got.dtype == torch.float32
+    ref = _attn_ref64(q, k, v, sc, causal)
+    assert torch.allclose(got.double(), ref, rtol=1e-5, atol=1e-5), float((got.double() - ref).abs().max())
+    if causal:
+        assert torch.allclose(got[:, 0], v[:, 0], rtol=1e-6, atol=0)          # the first query sees one key
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("units,sq,sk,d,causal", [(2, 100, 100, 32, False), (3, 130, 130, 96, True), (1, 64, 257, 32, False)])
+def test_16_bit_attention_with_other_head_sizes(units, sq, sk, d, causal, dtype, cuda):
+    q, k, v = inputs.attention_inputs(units, sq, sk, d, dtype)
+    got = _attn(q, k, v, cuda, causal=causal)
+    ref = _attn_ref64(q, k, v, d ** -0.5, causal)
+    bound = 1e-2 * ref.abs() + 1e-2 * ref.pow(2).mean(-1, keepdim=True).sqrt()
+    assert float(((got.double() - ref).abs() / bound).max()) <= 1.0
+
+
+def test_f32_attention_large_scores(cuda):
+    """Scores hundreds of log2 units apart: the running maximum is raised many times and nothing overflows. Scores of
+    magnitude 1000 carry an absolute fp32 error of 1e-3, which is the relative error of a probability: the bound is
+    that of the arithmetic, not of the kernel."""
+    import torch
+    g = torch.Generator().manual_seed(3)
+    q, k, v = torch.randn(2, 96, 64, generator=g) * 4, torch.randn(2, 500, 64, generator=g) * 4, torch.randn(2, 500, 64, generator=g)
+    k[:, 250:] *= 3
+    got = _attn(q, k, v, cuda, scale=1.0)
+    ref = _attn_ref64(q, k, v, 1.0, False)
+    assert torch.isfinite(got).all() and torch.allclose(got.double(), ref, rtol=5e-3, atol=5e-3), float((got.double() - ref).abs().max())

@@ -111,3 +111,34 @@ def test_gemm_against_the_reference_kernel(manifest, cuda, case):
     if f"{case}.rows" in gold.files:
         on_gpu, space = on_gpu[gold[f"{case}.rows"]], space[gold[f"{case}.rows"]]
     assert np.mean(cpu == on_gpu) > 0.98 and np.all(np.abs(cpu - on_gpu) <= 2 * space)
+
+
+
+@pytest.mark.parametrize("case", ["f_sdpa", "t_causal_sdpa", "f_masked_attn_manual"])
+def test_attention_against_the_reference_kernel(manifest, cuda, case):
+    """The reference's own attention cases (fp32 q, k, v): the PTX its compiler prints for the scalar-loop kernel and
+    the CUDA-core attention kernel of this library on the same device buffers. Nested loops with static trip counts, no
+    barriers, every index a tile or loop variable with the buffer's own extent (checked when the fixture is generated).
+    Both sit inside the reference's class (MM, 1e-3) of the float64 attention, agree with each other to fp32 rounding,
+    and the CPU execution of the same PTX (the golden vector) agrees with the GPU's."""
+    import torch
+    from emmyptx import runtime
+    info = manifest[case]
+    a = info["attention"]
+    units = int(np.prod(a["units"]))
+    q, k, v = (torch.from_numpy(x).to(cuda) for x in inputs.attention_inputs_f32(units, a["seq_q"], a["seq_k"], a["d"]))
+    theirs = torch.zeros(units, a["seq_q"], a["d"], device=cuda)
+    torch.cuda.synchronize()
+    run_ptx((GOLDEN / f"{case}.ref.ptx").read_text(), info["entry"], [q.data_ptr(), k.data_ptr(), v.data_ptr(), theirs.data_ptr()],
+            info["launch"]["grid"][0], info["launch"]["block"][0])
+    ours = runtime.attention(q, k, v, scale=a["scale"], causal=a["causal"])
+    torch.cuda.synchronize()
+    ref = reference.attention_reference(q.cpu(), k.cpu(), v.cpu(), scale=a["scale"], double=True, causal=a["causal"]).numpy()
+    theirs_np, ours_np = theirs.cpu().double().numpy(), ours.cpu().double().numpy()
+    assert reference.compare(theirs_np, ref, rtol=1e-3, atol=1e-3)["ok"]
+    assert reference.compare(ours_np, ref, rtol=1e-3, atol=1e-3)["ok"]
+    assert np.allclose(ours_np, theirs_np, rtol=1e-5, atol=4e-6), float(np.abs(ours_np - theirs_np).max())
+    assert np.abs(ours_np - ref).max() <= 2 * np.abs(theirs_np - ref).max() + 1e-6
+    cpu = np.load(GOLDEN / "golden.npz")[f"{case}.o"].astype(np.float64)
+    assert np.allclose(cpu, theirs_np, rtol=1e-5, atol=4e-6)          # ex2.approx and the division differ in the last bits
+

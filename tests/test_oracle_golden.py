@@ -123,3 +123,37 @@ def test_interpreter_reproduces_the_gemm_fixture():
     bufs = {"A": a.view(torch.int16).numpy().copy(), "B": b.view(torch.int16).numpy().copy(), "C": np.zeros((32, 16), np.int16)}
     ptx_interp.run_entry((GOLDEN / "m_f16_mm_32x16x32.ref.ptx").read_text(), bufs, info["launch"]["grid"][0], info["launch"]["block"][0])
     assert np.array_equal(bufs["C"].view(np.uint16), np.load(GOLDEN / "golden.npz")["m_f16_mm_32x16x32.c"])
+
+
+
+ATTENTION_CASES = ["f_sdpa", "t_causal_sdpa", "f_masked_attn_manual"]
+
+
+def _attention_case(case):
+    import torch
+    a = json.loads((GOLDEN / "reference_ptx_manifest.json").read_text())[case]["attention"]
+    units = int(np.prod(a["units"]))
+    q, k, v = (torch.from_numpy(x) for x in inputs.attention_inputs_f32(units, a["seq_q"], a["seq_k"], a["d"]))
+    return a, q, k, v
+
+
+@pytest.mark.parametrize("case", ATTENTION_CASES)
+def test_attention_oracle_agrees_with_the_reference_kernel(golden, case):
+    """The reference's own attention cases (fp32 q, k, v; tools/torch_cases/fused.py:21-22, 31-36, models.py:17-19),
+    its compiler's PTX for the scalar-loop kernel executed on the CPU, against the oracle's float64 attention: inside
+    the reference's class for them (MM: rtol = atol = 1e-3) and, both being fp32 evaluations, two orders tighter."""
+    a, q, k, v = _attention_case(case)
+    ref = reference.attention_reference(q, k, v, scale=a["scale"], double=True, causal=a["causal"]).numpy()
+    got = golden[f"{case}.o"].astype(np.float64)
+    assert reference.compare(got, ref, rtol=1e-3, atol=1e-3)["ok"]
+    assert np.allclose(got, ref, rtol=1e-5, atol=2e-6), float(np.abs(got - ref).max())
+
+
+def test_interpreter_reproduces_the_attention_fixture():
+    """Run-time loops with static trip counts (emmyptx/loops.py:231-264) are followed by the interpreter."""
+    info = json.loads((GOLDEN / "reference_ptx_manifest.json").read_text())["f_sdpa"]
+    q, k, v = inputs.attention_inputs_f32(2, 64, 64, 32)
+    bufs = {"Q": q.copy(), "K": k.copy(), "V": v.copy(), "O": np.zeros((2, 64, 32), np.float32)}
+    ptx_interp.run_entry((GOLDEN / "f_sdpa.ref.ptx").read_text(), bufs, info["launch"]["grid"][0], info["launch"]["block"][0])
+    assert np.array_equal(bufs["O"], np.load(GOLDEN / "golden.npz")["f_sdpa.o"])
+

@@ -45,7 +45,19 @@ def test_every_float_op_compiles_for_sm100a(lib):
         assert rt.program_compile(prog, vec) > 1000
 
 
-def test_integer_programs_have_no_compiled_form(lib):
-    prog = {"in_dtypes": ["i32"], "out_dtype": "i32", "out_slot": 4, "consts": [3], "steps": [["add", 4, 0, S, 0]]}
-    with pytest.raises(rt.KernelError, match="float program"):
-        rt.program_source(prog)
+def test_integer_programs_are_compiled_too(lib):
+    prog = {"in_dtypes": ["i32", "i64"], "out_dtype": "i64", "out_slot": 5, "consts": [3], "int_div": "trunc",
+            "steps": [["add", 4, 0, S, 0], ["floor_divide", 4, 4, 1, 0], ["left_shift", 5, 4, S, 0]]}
+    text = rt.program_source(prog)
+    assert "#define PW_T int" in text and "emmy_math.cuh" not in text
+    assert "s4 = (int)((unsigned)s0 + (unsigned)(int)c.v[0]);" in text and "s4 = pw_i_div(s4, s1, 1);" in text
+    assert "pw_i_div(s4, s1, 0)" in rt.program_source({k: v for k, v in prog.items() if k != "int_div"})
+    with pytest.raises(rt.KernelError, match="groups of 4"):
+        rt.program_source(prog, group=8)
+    if rt.pointwise_jit_state()[0] == 1:
+        names = ["add", "subtract", "multiply", "maximum", "minimum", "relu", "square", "negative", "abs", "equal", "not_equal", "greater", "less",
+                 "greater_equal", "less_equal", "where", "bitwise_and", "bitwise_or", "bitwise_not", "bitwise_xor", "left_shift", "right_shift",
+                 "divide", "floor_divide", "mod", "copy"]
+        steps = [[op, 4 + (i % 8), 4 + ((i + 7) % 8) if i else 0, 1, 0] for i, op in enumerate(names)]
+        for group in (4, 0):
+            assert rt.program_compile({"in_dtypes": ["i32", "i64"], "out_dtype": "i32", "out_slot": steps[-1][1], "consts": [2], "steps": steps}, group) > 1000

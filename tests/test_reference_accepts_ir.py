@@ -4,8 +4,8 @@ The facade's matchers are exercised on IR made by the builders of `emmyptx/ir.py
 to the reference's `compile_kernel` (emmyptx/kernel.py:903): every builder whose statements the reference supports
 must compile to PTX there, so the matchers see IR of the form the reference consumes, not a private dialect. Two
 builders are outside the reference's statement set by design and must be refused by it: a tensor-core store with a
-fused epilogue (emmyptx/mma.py:201-203 -- the fusion is what the sm_100a GEMM adds), and the attention kernel, whose
-softmax between the two MMA groups is written on fragment names directly (the reference has no statement that turns
+fused epilogue (emmyptx/mma.py:201-203 -- the fusion is what the sm_100a GEMM adds), and the 16-bit attention kernel,
+whose softmax between the two MMA groups is written on fragment names directly (the reference has no statement that turns
 an accumulator fragment into an operand fragment; its tracer goes through shared memory). The checkout is looked up
 in $EMMYPTX_REFERENCE, else in a directory `reference` next to the repository; without one the test is skipped.
 """
@@ -68,6 +68,9 @@ def accepted_cases(ir):
     yield "m_mm", ir.matmul_f32_kernel(128, 80, 96)
     yield "m_bmm", ir.matmul_f32_kernel(64, 48, 32, batch=4)
     yield "m_linear_bias_relu", ir.matmul_f32_kernel(64, 96, 128, b_trans=True, bias=True, relu=True)
+    yield "f_sdpa", ir.attention_scalar_kernel([1, 2], 64, 64, 32)
+    yield "t_causal_sdpa", ir.attention_scalar_kernel([1, 4], 128, 128, 64, causal=True)
+    yield "f_masked_attn_manual", ir.attention_scalar_kernel([1], 64, 64, 32, scale=0.17677669, causal=True)
     for op in ROW_OPS:
         yield f"row_{op}", ir.rowwise_kernel(op, 64, 256)
     for op in ("sum", "amax", "softmax"):
@@ -89,7 +92,8 @@ def test_reference_output_is_the_committed_fixture(reference_compile):
     golden = ROOT / "tests" / "golden"
     for name, built in (("m_f16_mm", ir.gemm_kernel(256, 256, 256, "f16", name="m_f16_mm")),
                         ("m_f16_linear", ir.gemm_kernel(64, 512, 256, "f16", None, True, name="m_f16_linear")),
-                        ("c2_gather_n65536", ir.index_gather_kernel(2**16, name="c2_gather_n65536"))):
+                        ("c2_gather_n65536", ir.index_gather_kernel(2**16, name="c2_gather_n65536")),
+                        ("t_causal_sdpa", ir.attention_scalar_kernel([1, 4], 128, 128, 64, causal=True, name="t_causal_sdpa"))):
         assert reference_compile.compile_kernel(*built, target="sm_89") == (golden / f"{name}.ref.ptx").read_text(), name
 
 
