@@ -142,8 +142,82 @@ class Workload:
     def launches_per_step(self) -> int: return 1
 
 
+def _pipeline_note(self) -> str:
+    ring = getattr(self, "ring", None)
+    if ring is not None and ring.pipelined:
+        return " on a side stream: two copies of the output alternate, so the barrier of step k overlaps the kernel of step k+1 (step k+2 waits for it)"
+    return " in line after the kernel"
+
+
+class GatherRing:
+    """The gathered output of a sharded step, in peer-mapped memory on every rank, twice: step k writes copy k % 2.
+    The group barrier that tells a consumer "every rank's rows of step k have landed everywhere" is issued on a side
+    stream after the producing kernel, so it (and the tail of the kernel's stores through NVLink) overlaps the kernel
+    of step k + 1, which writes the other copy and needs no barrier; step k + 2 reuses copy k % 2 and therefore first
+    waits for barrier k. That is the form EMMYB200_BENCH_PIPELINE=1 selects; by default there is one copy and the barrier
+    runs in line after each kernel.
+    No kernel waits on another rank: only the barrier kernels do, and nothing that they wait for queues behind them."""
+
+    def __init__(self, torch, shape, dtype, dev, rank, shard_bytes, mode):
+        from emmyptx import shard
+        self.torch = torch
+        self.pipelined = os.environ.get("EMMYB200_BENCH_PIPELINE", "0") != "0"
+        self.mode = mode
+        self.copies = []
+        for _ in range(2 if self.pipelined else 1):
+            full, peers = shard.peer_mapped_empty(shape, dtype, dev, multicast=mode == "multicast")
+            self.copies.append([full, peers, None])
+        off = rank * shard_bytes
+        if self.mode == "multicast" and not all(group_has_multicast(shard.multicast_address(c[1]), dev) for c in self.copies):
+            self.mode = "fused"                                           # no multicast object on this fabric
+        for c in self.copies:
+            full, peers = c[0], c[1]
+            c[2] = ([shard.multicast_address(peers) + off] if self.mode == "multicast" else
+                    [full.data_ptr() + off] + [p + off for r, p in enumerate(peers.buffer_ptrs) if r != rank])
+        self.side = torch.cuda.Stream(device=dev) if self.pipelined else None
+        self.landed = [None] * len(self.copies)       # event: the barrier after the last kernel that wrote copy i
+        self.count = 0
+        self.last = 0
+
+    def begin(self):
+        """Destination addresses for the next step's kernel; called on the launching stream before the launch."""
+        i = self.count % len(self.copies)
+        self.count += 1
+        self.last = i
+        if self.pipelined and self.landed[i] is not None:
+            self.torch.cuda.current_stream().wait_event(self.landed[i])  # the copy's previous contents are no longer needed
+        return self.copies[i][2]
+
+    def end(self):
+        """After the launch: the group barrier for the copy just written."""
+        i = self.last
+        if not self.pipelined:
+            self.copies[i][1].barrier()
+            return
+        main = self.torch.cuda.current_stream()
+        done = self.torch.cuda.Event()
+        done.record(main)
+        with self.torch.cuda.stream(self.side):
+            self.side.wait_event(done)
+            self.copies[i][1].barrier()
+            ev = self.torch.cuda.Event()
+            ev.record(self.side)
+        self.landed[i] = ev
+
+    def finish(self):
+        """The launching stream waits for every barrier still in flight (end of a timed region, before reading)."""
+        for ev in self.landed:
+            if ev is not None:
+                self.torch.cuda.current_stream().wait_event(ev)
+
+    @property
+    def full(self):
+        return self.copies[self.last][0]
+
+
 class GemmWorkload(Workload):
     metric, unit, bound = "gemm_tflops", "TFLOP/s", "tensor"
+    _pipeline_note = _pipeline_note
 
     def __init__(self, name, m, n, k, dtype, epilogue, rank, world, dev, gather=True):
         import torch
@@ -163,36 +237,37 @@ class GemmWorkload(Workload):
         self.host = None
         # "multicast" (one multimem.st per piece, replicated by the NVSwitch), "fused" (one TMA store per peer) or "nccl"
         self.mode = os.environ.get("EMMYB200_BENCH_GATHER", "multicast")
+        self.ring = None
         if self.gather and self.mode in ("fused", "multicast"):
             # The full C lives in peer-mapped memory on every rank; each rank's kernel writes its rows into all of them.
-            from emmyptx import shard
             try:
-                self.c_full, self.peers = shard.peer_mapped_empty((m, n), td, dev, multicast=self.mode == "multicast")
+                self.ring = GatherRing(torch, (m, n), td, dev, rank, self.rows * n * 2, self.mode)
+                self.mode = self.ring.mode
             except Exception as e:  # noqa: BLE001 - no peer mapping on this box: gather with NCCL instead
                 print(f"[bench] peer-mapped memory unavailable ({type(e).__name__}: {e}); gathering with NCCL", file=sys.stderr)
                 self.mode = "nccl"
-        if self.gather and self.mode in ("fused", "multicast"):
-            off = rank * self.rows * n * self.c_full.element_size()
-            own = self.c_full.data_ptr() + off
-            if self.mode == "multicast" and not group_has_multicast(shard.multicast_address(self.peers), dev):
-                self.mode = "fused"                                       # no multicast object on this fabric
-            if self.mode == "multicast":
-                self.dst = [shard.multicast_address(self.peers) + off]
-            else:
-                self.dst = [own] + [p + off for r, p in enumerate(self.peers.buffer_ptrs) if r != rank]
-        else:
-            self.c_full = torch.empty(m, n, device=dev, dtype=td)
+        if self.ring is None:
+            self._c_full = torch.empty(m, n, device=dev, dtype=td)
         self.c = self.c_full[rank * self.rows:(rank + 1) * self.rows]
 
+    @property
+    def c_full(self):
+        return self.ring.full if self.ring is not None else self._c_full
+
     def step(self):
-        if self.gather and self.mode in ("fused", "multicast"):
-            self.rt.gemm_allgather(self.a, self.b, self.dst, self.n, epilogue=self.epilogue, multicast=self.mode == "multicast")
-            self.peers.barrier()                # every rank's rows have landed everywhere
+        if self.ring is not None:
+            dst = self.ring.begin()
+            self.rt.gemm_allgather(self.a, self.b, dst, self.n, epilogue=self.epilogue, multicast=self.mode == "multicast")
+            self.ring.end()                     # every rank's rows have landed everywhere once this barrier has run
             return
         self.rt.gemm(self.a, self.b, epilogue=self.epilogue, out=self.c)
         if self.gather:
             import torch.distributed as dist
             dist.all_gather_into_tensor(self.c_full, self.c)
+
+    def finish(self):
+        if self.ring is not None:
+            self.ring.finish()
 
     def kernel_only(self):
         self.rt.gemm(self.a, self.b, epilogue=self.epilogue, out=self.c)
@@ -200,9 +275,9 @@ class GemmWorkload(Workload):
     @property
     def collective(self):
         if self.mode == "multicast":
-            return "fused: the GEMM stores each output piece once through the NVSwitch multicast mapping of C (multimem.st), then a signal barrier"
+            return "fused: the GEMM stores each output piece once through the NVSwitch multicast mapping of C (multimem.st), then a signal barrier" + self._pipeline_note()
         if self.mode == "fused":
-            return "fused: the GEMM's TMA stores write each output piece to every peer's C over NVLink, then a signal barrier"
+            return "fused: the GEMM's TMA stores write each output piece to every peer's C over NVLink, then a signal barrier" + self._pipeline_note()
         return "nccl all_gather of the output shards"
 
     def work_per_step(self):
@@ -286,9 +361,9 @@ class GemmWorkload(Workload):
             dist.all_gather_into_tensor(self.b, self.b[self.b_rows[0]:self.b_rows[1]])
             for i, (lo, hi) in enumerate(self.chunks):
                 main.wait_event(self.ev_in[i + 1])
-                dst = [d + lo * self.n * 2 for d in self.dst]
+                dst = [d + lo * self.n * 2 for d in self.ring.copies[0][2]]       # copy 0, whose rows self.c views
                 self.rt.gemm_allgather(self.a[lo:hi], self.b, dst, self.n, epilogue=self.epilogue, multicast=self.mode == "multicast")
-            self.peers.barrier()
+            self.ring.copies[0][1].barrier()
             h["c"].copy_(self.c, non_blocking=True)
             return
         self.a.copy_(h["a"], non_blocking=True)
@@ -501,6 +576,7 @@ class GatherWorkload(PointwiseWorkload):
 
 class AttentionWorkload(Workload):
     metric, unit, dtype, bound = "attention_tflops", "TFLOP/s", "bf16", "tensor"
+    _pipeline_note = _pipeline_note
 
     def __init__(self, units, seq, d, rank, world, dev, gather=True, causal=False):
         import torch
@@ -516,37 +592,39 @@ class AttentionWorkload(Workload):
         self.q, self.k, self.v = mk(), mk(), mk()
         self.gather = gather and world > 1
         self.mode = os.environ.get("EMMYB200_BENCH_GATHER", "multicast")
+        self.ring = None
         if self.gather and self.mode in ("fused", "multicast"):
-            from emmyptx import shard
             try:
-                self.o_full, self.peers = shard.peer_mapped_empty((units, seq, d), torch.bfloat16, dev, multicast=self.mode == "multicast")
+                self.ring = GatherRing(torch, (units, seq, d), torch.bfloat16, dev, rank, self.local * seq * d * 2, self.mode)
+                self.mode = self.ring.mode
             except Exception as e:  # noqa: BLE001
                 print(f"[bench] peer-mapped memory unavailable ({type(e).__name__}: {e}); gathering with NCCL", file=sys.stderr)
                 self.mode = "nccl"
-        if self.gather and self.mode in ("fused", "multicast"):
-            off = rank * self.local * seq * d * 2
-            if self.mode == "multicast" and not group_has_multicast(shard.multicast_address(self.peers), dev):
-                self.mode = "fused"
-            if self.mode == "multicast":
-                self.dst = [shard.multicast_address(self.peers) + off]
-            else:
-                self.dst = [self.o_full.data_ptr() + off] + [p + off for r, p in enumerate(self.peers.buffer_ptrs) if r != rank]
-        else:
-            self.o_full = torch.empty(units, seq, d, device=dev, dtype=torch.bfloat16)
+        if self.ring is None:
+            self._o_full = torch.empty(units, seq, d, device=dev, dtype=torch.bfloat16)
         self.o = self.o_full[rank * self.local:(rank + 1) * self.local]
+
+    @property
+    def o_full(self):
+        return self.ring.full if self.ring is not None else self._o_full
+
+    def finish(self):
+        if self.ring is not None:
+            self.ring.finish()
 
     @property
     def collective(self):
         if self.mode == "multicast":
-            return "fused: the attention kernel stores each output tile once through the NVSwitch multicast mapping of O (multimem.st), then a signal barrier"
+            return "fused: the attention kernel stores each output tile once through the NVSwitch multicast mapping of O (multimem.st), then a signal barrier" + self._pipeline_note()
         if self.mode == "fused":
-            return "fused: the attention kernel's TMA stores write each output tile to every peer's O over NVLink, then a signal barrier"
+            return "fused: the attention kernel's TMA stores write each output tile to every peer's O over NVLink, then a signal barrier" + self._pipeline_note()
         return "nccl all_gather of the output shards"
 
     def step(self):
-        if self.gather and self.mode in ("fused", "multicast"):
-            self.rt.attention_allgather(self.q, self.k, self.v, self.dst, multicast=self.mode == "multicast")
-            self.peers.barrier()
+        if self.ring is not None:
+            dst = self.ring.begin()
+            self.rt.attention_allgather(self.q, self.k, self.v, dst, multicast=self.mode == "multicast")
+            self.ring.end()
             return
         self.rt.attention(self.q, self.k, self.v, causal=self.causal, out=self.o)
         if self.gather:
@@ -608,7 +686,9 @@ class AttentionWorkload(Workload):
         for n in "qkv":
             getattr(self, n).copy_(self.host[n], non_blocking=True)
         self.step()
-        self.host["o"].copy_(self.o, non_blocking=True)
+        self.finish()
+        mine = self.o_full[self.rank * self.local:(self.rank + 1) * self.local] if self.ring is not None else self.o
+        self.host["o"].copy_(mine, non_blocking=True)
 
 
 def make_workload(name, rank, world, dev, size=None):
@@ -638,10 +718,13 @@ def make_workload(name, rank, world, dev, size=None):
 
 
 # ---- timing ---------------------------------------------------------------------------------------------
-def timed(torch, dist, world, fn, steps, warmup):
-    """Device time of exactly `steps` calls of fn, max over ranks, in ms (total)."""
+def timed(torch, dist, world, fn, steps, warmup, finish=None):
+    """Device time of exactly `steps` calls of fn, max over ranks, in ms (total). `finish` (a workload's way of waiting,
+    on the launching stream, for work it put on other streams) runs inside the timed region, after the last call."""
     for _ in range(warmup):
         fn()
+    if finish is not None:
+        finish()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -650,6 +733,8 @@ def timed(torch, dist, world, fn, steps, warmup):
     e0.record()
     for _ in range(steps):
         fn()
+    if finish is not None:
+        finish()
     e1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -854,7 +939,7 @@ def measure(torch, dist, world, local_rank, wl, steps: int, warmup: int, pk, pk_
         return run
 
     with ClockSampler(local_rank) as clocks:
-        total_ms = timed(torch, dist, world, passes(wl.step), steps, warmup)
+        total_ms = timed(torch, dist, world, passes(wl.step), steps, warmup, finish=getattr(wl, "finish", None))
     # kernel-only time for the roofline: the same number of launches, after the timed region, on the launching stream
     with ClockSampler(local_rank) as k_clocks:
         k_ms = timed(torch, dist, 1, passes(wl.kernel_only), steps, warmup) / (steps * inner)
@@ -928,7 +1013,7 @@ def main() -> int:
     pk, pk_kind = peaks()
     traffic = None if (args.size or world > 1) else DRAM_TRAFFIC.get(args.workload)
     if args.no_extras and args.size:            # a profiler capture of a small case: one plain pass per step, nothing else
-        ms = timed(torch, dist, world, wl.step, args.steps, args.warmup) / args.steps
+        ms = timed(torch, dist, world, wl.step, args.steps, args.warmup, finish=getattr(wl, "finish", None)) / args.steps
         if rank == 0:
             print(json.dumps({"metric": wl.metric, "ms_per_step": ms, "config": config_for(args.workload, world, args.size), "profiling_run": True}))
         if world > 1:
