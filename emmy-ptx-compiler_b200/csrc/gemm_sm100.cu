@@ -238,7 +238,9 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const Out
 // pairs are below 2^-24 of the product. The output is stored as fp32 (32-column pieces instead of 64).
 constexpr uint32_t kSplitPlaneA = 0x001012, kSplitPlaneB = 0x010210;      // pair p -> plane of A / of B, 4 bits each
 
-template <int BN, bool BF16, bool B_NK, bool F32 = false>
+// OUT32: the output (and the bias) is fp32; on its own (16-bit operands, one pass) it is the reference's store of an
+// accumulator fragment to an f32 buffer, plain or with red.add into a zeroed C (emmyptx/mma.py:205-242).
+template <int BN, bool BF16, bool B_NK, bool F32 = false, bool OUT32 = F32>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ OutMaps out, GemmParams p) {
@@ -370,7 +372,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (!ok) break;
             ptx::tc_fence_after_sync();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
-            drain_accumulator<BN, BF16, F32>(p, out, t_row, out_smem, piece, mb * kBM, nb * BN, plane, row_in_tile, (int)threadIdx.x - 64, issuer,
+            drain_accumulator<BN, BF16, OUT32>(p, out, t_row, out_smem, piece, mb * kBM, nb * BN, plane, row_in_tile, (int)threadIdx.x - 64, issuer,
                                              [&] { if (lane == 0) ptx::mbar_arrive(acc_empty_bar(as)); });
         }
         if (issuer) ptx::tma_store_wait<0>();
@@ -512,7 +514,7 @@ struct GemmCall {
     bool b_shared_split = false;    // split-precision path: one B for every product (stride_b then is the split-plane stride)
 };
 
-template <int BN, bool BF16, bool B_NK, bool F32 = false>
+template <int BN, bool BF16, bool B_NK, bool F32 = false, bool OUT32 = F32>
 static int launch_gemm(const GemmCall& g, cudaStream_t stream) {
     using S = GemmSmem<BN>;
     CUtensorMap map_a, map_b;
@@ -528,13 +530,13 @@ static int launch_gemm(const GemmCall& g, cudaStream_t stream) {
     if (rc != EMMYB200_OK) return rc;
     for (int d = 0; d < kMaxDst; ++d) {
         if (g.flags & EMMYB200_GEMM_DST_MULTICAST) { out.m[d] = map_a; continue; }      // unused: stores go through multimem.st
-        rc = F32 ? make_tensor_map_3d_f32(&out.m[d], g.C[d < g.n_dst ? d : 0], (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.N,
+        rc = OUT32 ? make_tensor_map_3d_f32(&out.m[d], g.C[d < g.n_dst ? d : 0], (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.N,
                                           (uint64_t)g.ldc, (uint64_t)g.stride_c, kBM, 32)
                  : make_tensor_map_3d_strided(&out.m[d], g.C[d < g.n_dst ? d : 0], (uint64_t)g.batch, (uint64_t)g.M, (uint64_t)g.N,
                                               (uint64_t)g.ldc, (uint64_t)g.stride_c, kBM, 64);
         if (rc != EMMYB200_OK) return rc;
     }
-    auto kernel = gemm_tcgen05_kernel<BN, BF16, B_NK, F32>;
+    auto kernel = gemm_tcgen05_kernel<BN, BF16, B_NK, F32, OUT32>;
     EMMY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
     GemmParams p;
     p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
@@ -563,6 +565,10 @@ static int pick_tile(const GemmCall& g, cudaStream_t stream) {
     // 128 x 256 tiles: with both operands read from shared memory by one CTA, the 128 x 128 shape is bound by
     // shared-memory bandwidth (measured 0.6-0.7x the throughput at every size from 2048^3 to 16384^3), which
     // costs more than the emptier last wave of the wide tile. Narrow outputs keep the narrow tile.
+    if (g.flags & EMMYB200_GEMM_OUT_F32) {
+        if (g.N > 128) return launch_gemm<256, BF16, B_NK, false, true>(g, stream);
+        return launch_gemm<128, BF16, B_NK, false, true>(g, stream);
+    }
     if (g.N > 128) return launch_gemm<256, BF16, B_NK>(g, stream);
     return launch_gemm<128, BF16, B_NK>(g, stream);
 }
@@ -571,7 +577,9 @@ static int gemm_entry(const GemmCall& g, void* cuda_stream) {
     if (g.dtype != EMMYB200_F16 && g.dtype != EMMYB200_BF16) return fail(EMMYB200_ERR_UNSUPPORTED, "gemm: dtype %d (f16 and bf16 only)", g.dtype);
     if (g.epilogue != EMMYB200_EPI_NONE && g.epilogue != EMMYB200_EPI_GELU_TANH && g.epilogue != EMMYB200_EPI_RELU)
         return fail(EMMYB200_ERR_ARG, "gemm: unknown epilogue %d", g.epilogue);
-    if (g.flags & ~(EMMYB200_GEMM_B_NK | EMMYB200_GEMM_DST_MULTICAST)) return fail(EMMYB200_ERR_ARG, "gemm: unknown flags 0x%x", g.flags);
+    if (g.flags & ~(EMMYB200_GEMM_B_NK | EMMYB200_GEMM_DST_MULTICAST | EMMYB200_GEMM_OUT_F32)) return fail(EMMYB200_ERR_ARG, "gemm: unknown flags 0x%x", g.flags);
+    const bool out_f32 = g.flags & EMMYB200_GEMM_OUT_F32;
+    if (out_f32 && ((g.flags & EMMYB200_GEMM_DST_MULTICAST) || g.n_dst != 1)) return fail(EMMYB200_ERR_UNSUPPORTED, "gemm: an fp32 output has one plain destination");
     if (g.flags & EMMYB200_GEMM_DST_MULTICAST) {
         if (g.n_dst != 1) return fail(EMMYB200_ERR_ARG, "gemm: a multicast destination is a single address");
         if (g.N % 8 != 0) return fail(EMMYB200_ERR_SHAPE, "gemm: multicast stores move 8 columns at a time (N = %lld)", (long long)g.N);
@@ -588,9 +596,9 @@ static int gemm_entry(const GemmCall& g, void* cuda_stream) {
     }
     const bool b_nk = g.flags & EMMYB200_GEMM_B_NK;
     if (g.lda < g.K || g.ldc < g.N || g.ldb < (b_nk ? g.K : g.N)) return fail(EMMYB200_ERR_SHAPE, "gemm: leading dimension smaller than the row");
-    if ((g.lda | g.ldb | g.ldc) & 7) return fail(EMMYB200_ERR_ALIGN, "gemm: leading dimensions must be multiples of 8 elements (16 bytes)");
+    if (((g.lda | g.ldb) & 7) || (g.ldc & (out_f32 ? 3 : 7))) return fail(EMMYB200_ERR_ALIGN, "gemm: leading dimensions must be multiples of 16 bytes (8 16-bit or 4 fp32 elements)");
     if (g.batch > 1) {
-        if ((g.stride_a | g.stride_b | g.stride_c) & 7) return fail(EMMYB200_ERR_ALIGN, "gemm: plane strides must be multiples of 8 elements (16 bytes)");
+        if (((g.stride_a | g.stride_b) & 7) || (g.stride_c & (out_f32 ? 3 : 7))) return fail(EMMYB200_ERR_ALIGN, "gemm: plane strides must be multiples of 8 elements (16 bytes)");
         if (g.stride_a < g.M * g.lda || g.stride_c < g.M * g.ldc || (g.stride_b != 0 && g.stride_b < (b_nk ? g.N : g.K) * g.ldb))
             return fail(EMMYB200_ERR_SHAPE, "gemm: plane stride smaller than a plane");
     }

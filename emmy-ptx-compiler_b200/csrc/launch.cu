@@ -301,7 +301,7 @@ extern "C" int emmyb200_launch(const char* handle_json, void* const* params, int
         if (epi < 0) return fail(EMMYB200_ERR_ARG, "launch: unknown epilogue in the handle");
         const int64_t m = geti(p, "m"), n = geti(p, "n"), k = geti(p, "k"), batch = geti(p, "batch", 1);
         const bool nk = getb(p, "b_trans");
-        const int flags = nk ? EMMYB200_GEMM_B_NK : 0;
+        const int flags = (nk ? EMMYB200_GEMM_B_NK : 0) | (getb(p, "out_f32") ? EMMYB200_GEMM_OUT_F32 : 0);
         const int64_t ldb = nk ? k : n;
         if (v == "gemm") return emmyb200_gemm(dtype_code(gets(p, "dtype")), epi, flags, a.input(0), a.input(1), out, m, n, k, k, ldb, n, cuda_stream);
         const void* bias = getb(p, "bias") ? a.input(2) : nullptr;

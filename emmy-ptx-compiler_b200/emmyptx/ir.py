@@ -500,7 +500,8 @@ def rowwise_kernel(op: str, rows: int, cols: int, eps: float = 1e-5, name: str =
 
 
 def gemm_kernel(m: int, n: int, k: int, dtype: str = "f16", epilogue: str | None = None, b_trans: bool = False,
-                name: str = "k_gemm", batch: tuple = (), b_batched: bool = True, bias: bool = False):
+                name: str = "k_gemm", batch: tuple = (), b_batched: bool = True, bias: bool = False,
+                out_dtype: str | None = None, split_k: int = 1):
     """C = A B on mma.sync cells, as the tracer schedules a 16-bit matmul: accumulator / operand fragments, a K
     loop of fragment loads straight from global memory and MMAs, a fragment store (optionally with a fused
     epilogue, which the reference rejects, emmyptx/mma.py:201-203). One warp per 16x8 cell: the tile's axes are
@@ -508,12 +509,19 @@ def gemm_kernel(m: int, n: int, k: int, dtype: str = "f16", epilogue: str | None
     emmyptx/kernel.py:551-626 hands every warp one cell and `mma.sync` runs warp-wide. Ragged extents carry the
     guards of emmyptx/mma.py:128-151, 217-242 (clamped rows / columns, zero K tail, predicated stores). The
     reference's compiler accepts this IR as it stands (without epilogue and bias); the tile sizes of the tracer's
-    real schedule are unknown and do not matter to the matcher."""
+    real schedule are unknown and do not matter to the matcher. `out_dtype="f32"` stores the accumulator without
+    narrowing; `split_k` > 1 adds a tile axis that cuts the K loop into that many parts, each cell adding its partial
+    sum into a zeroed f32 C (`atomic`: red.add.f32, emmyptx/mma.py:205-242)."""
+    out_dtype = out_dtype or dtype
+    k_cells = -(-k // 16)
+    if split_k > 1 and (out_dtype != "f32" or k_cells % split_k):
+        raise ValueError("split_k needs an f32 output and a K loop it divides")
     am, an = Axis("m0", Dim(-(-m // 16))), Axis("n0", Dim(-(-n // 8)))
-    kk = Axis("k0", Dim(-(-k // 16)))
+    kk = Axis("k0", Dim(k_cells // split_k))
     lit = lambda v: Literal(int(v), "int")
     row, col = BinaryExpr("*", Var("m0"), lit(16)), BinaryExpr("*", Var("n0"), lit(8))
-    kof = BinaryExpr("*", Var("k0"), lit(16))
+    kcell = Var("k0") if split_k == 1 else BinaryExpr("+", BinaryExpr("*", Var("s0"), lit(k_cells // split_k)), Var("k0"))
+    kof = BinaryExpr("*", kcell, lit(16))
     lead = list(batch)
     bvar = [Var("b0")] if lead else []
     b_index = (bvar if b_batched else []) + ([col, kof] if b_trans else [kof, col])
@@ -524,17 +532,18 @@ def gemm_kernel(m: int, n: int, k: int, dtype: str = "f16", epilogue: str | None
                           k_zero=(kof, lit(k)) if rag_k else None)
     body = [RegFragment("_c", "c", DType("f32")), RegFragment("_a", "a", DType(dtype)), RegFragment("_b", "b", DType(dtype)),
             Loop(kk, [a_load, b_load, MmaSyncPtx("_c", "_a", "_b", ab_dtype=dtype)]),
-            RegStore("_c", "C", bvar + [row, col], epilogue=epilogue, bias="bias" if bias else None,
+            RegStore("_c", "C", bvar + [row, col], epilogue=epilogue, bias="bias" if bias else None, atomic=split_k > 1,
                      m_guard=(row, lit(m)) if rag_m else None, n_guard=(col, lit(n)) if rag_n else None)]
-    axes = ([Axis("b0", Dim(math.prod(lead)))] if lead else []) + [am, an, Axis("lane0", Dim(32))]
+    axes = (([Axis("b0", Dim(math.prod(lead)))] if lead else []) + ([Axis("s0", Dim(split_k))] if split_k > 1 else []) +
+            [am, an, Axis("lane0", Dim(32))])
     kern = KernelOp(name, [Tile(axes, body)])
     bshape = [n, k] if b_trans else [k, n]
     flat = [math.prod(lead)] if lead else []
     ins = [tensor("A", flat + [m, k], dtype), tensor("B", (flat if b_batched else []) + bshape, dtype)]
     if bias:
-        ins.append(tensor("bias", [n], dtype))
-    g = _graph(kern, ins, [tensor("C", flat + [m, n], dtype)])
-    cells = math.prod(lead or [1]) * am.extent.value * an.extent.value * 32
+        ins.append(tensor("bias", [n], out_dtype))
+    g = _graph(kern, ins, [tensor("C", flat + [m, n], out_dtype)])
+    cells = math.prod(lead or [1]) * split_k * am.extent.value * an.extent.value * 32
     return g, kern, _launch(kern, [t.name for t in ins] + ["C"], cells, block=128)
 
 

@@ -520,6 +520,35 @@ def _attention_mask(kernel, stmts, seq_q: int, seq_k: int) -> bool:
     raise Unmatched("a masked softmax other than the lower-triangular one (key <= query) has no variant")
 
 
+def _k_covered_once(kernel, a_load, k: int) -> None:
+    """The K offsets at which the kernel's cells read A -- the last index of the `a` fragment load over every value of
+    the tile and loop variables it depends on -- are 0, 16, 32, ... up to K, each exactly once. That holds for one loop
+    over K and for a split-K schedule (a tile axis times a shorter loop); a kernel that skips or repeats part of K is
+    some other computation."""
+    expr = a_load.src_index[-1]
+    extents = {}
+    for s in walk(kernel.body):
+        kind = _kind(s)
+        if kind == "Tile":
+            extents.update({a.name: int(a.extent.as_static()) for a in s.axes})
+        elif kind in ("Loop", "StridedLoop"):
+            extents[s.axis.name] = int(s.axis.extent.as_static())
+    names = sorted(expr.free_vars()) if hasattr(expr, "free_vars") else []
+    if any(nm not in extents for nm in names):
+        raise Unmatched("the K index of the A fragment depends on something other than tile and loop variables")
+    total = math.prod(extents[nm] for nm in names) if names else 1
+    if total > 1 << 20:
+        raise Unmatched("the K index of the A fragment ranges over too many cells to check")
+    grids = np.meshgrid(*[np.arange(extents[nm], dtype=np.int64) for nm in names], indexing="ij") if names else []
+    it = CellInterpreter({}, np.zeros(total, dtype=np.int64), INT_OPS)
+    for nm, g in zip(names, grids):
+        it.env[nm] = g.reshape(-1)
+    offs = np.sort(np.asarray(it.expr(expr), dtype=np.int64).reshape(-1))
+    want = np.arange(0, -(-k // 16) * 16, 16, dtype=np.int64)
+    if offs.shape != want.shape or not np.array_equal(offs, want):
+        raise Unmatched("the cells' K offsets do not cover K exactly once")
+
+
 def match_contraction(graph, kernel, launch: dict) -> dict:
     tensors = tensor_table(graph)
     stmts = list(walk(kernel.body))
@@ -531,22 +560,25 @@ def match_contraction(graph, kernel, launch: dict) -> dict:
             raise Unmatched("only f16 / bf16 operands with f32 accumulators are supported")      # emmyptx/mma.py:185-187
     if len(stores) != 1:
         raise Unmatched("a contraction kernel stores one output")
-    if stores[0].atomic:
-        raise Unmatched("split-K (atomic) stores have no variant")
     srcs = list(dict.fromkeys(s.src_buffer for s in loads))
     out = stores[0].dst_buffer
     for b in (*srcs, out):
         if b not in tensors:
             raise Unmatched(f"unknown buffer {b!r}")
     dtype = mmas[0].ab_dtype
-    if any(tensors[b][1] != dtype for b in (*srcs, out)):
-        raise Unmatched("operands and output must share the MMA's 16-bit dtype")
+    out_f32 = tensors[out][1] == "f32"
+    if any(tensors[b][1] != dtype for b in srcs) or (tensors[out][1] != dtype and not out_f32):
+        raise Unmatched("operands have the MMA's 16-bit dtype, the output that dtype or f32")
+    if stores[0].atomic and not out_f32:
+        raise Unmatched("an atomic (split-K) store adds into an f32 buffer")          # emmyptx/mma.py:205-207
     has_softmax = any(_kind(s) == "Assign" and s.op.name in ("exp", "exp_fast") for s in stmts)
     if len(srcs) == 3 and has_softmax:
         q, k, v = (tensors[b][0] for b in srcs)
         o = tensors[out][0]
         if not (len(q) >= 2 and q[:-2] == k[:-2] == v[:-2] == o[:-2] and k == v and q == o and q[-1] == k[-1]):
             raise Unmatched(f"attention shapes do not agree: {q}, {k}, {v} -> {o}")
+        if out_f32 or stores[0].atomic:
+            raise Unmatched("tensor-core attention stores the operands' 16-bit dtype")
         d = q[-1]
         if d % 32 or not 32 <= d <= 128:
             raise Unmatched(f"attention head dim {d} has no variant (multiples of 32 up to 128)")
@@ -575,13 +607,20 @@ def match_contraction(graph, kernel, launch: dict) -> dict:
         raise Unmatched(f"GEMM shapes do not agree: {a_shape} x {b_shape} -> {c_shape}")
     if k % 8 or n % 8:
         raise Unmatched("row pitches must be multiples of 8 elements (16-byte TMA strides)")
+    _k_covered_once(kernel, a_loads[0], k)
     bias = getattr(stores[0], "bias", None)
     inputs = [a_name, b_name]
     if bias is not None:
-        if bias not in tensors or math.prod(tensors[bias][0]) != n or tensors[bias][1] != dtype:
-            raise Unmatched(f"bias {bias!r} must hold N = {n} values of dtype {dtype}")
+        if bias not in tensors or math.prod(tensors[bias][0]) != n or tensors[bias][1] != tensors[out][1]:
+            raise Unmatched(f"bias {bias!r} must hold N = {n} values of the output's dtype {tensors[out][1]}")
         inputs.append(bias)
     params = {"dtype": dtype, "m": m, "n": n, "k": k, "b_trans": b_trans, "epilogue": _epilogue_name(stores[0].epilogue)}
+    if out_f32:
+        # The accumulator stored as it is. A split-K schedule (several cells adding partial sums into a zeroed C with
+        # red.add.f32) computes the same C; here one kernel covers K and overwrites C.
+        params["out_f32"] = True
+        if stores[0].atomic and stores[0].epilogue is not None:
+            raise Unmatched("an epilogue cannot be applied to partial sums")
     if lead or bias is not None:
         params.update(batch=math.prod(lead), b_shared=len(b_shape) == 2, bias=bias is not None)
         return {"variant": "gemm_batched", "inputs": inputs, "outputs": [out], "params": params}

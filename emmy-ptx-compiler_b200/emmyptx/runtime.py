@@ -241,8 +241,22 @@ def index_gather(x, mul: int, add: int, div: int, shift: int, trunc: bool = Fals
     return out
 
 
-def gemm(a, b, epilogue: str | None = None, b_is_nk: bool = False, out=None, stream=None):
-    """out = epilogue(a @ b) (or a @ b.T when `b_is_nk`), fp16 / bf16, fp32 accumulation."""
+GEMM_OUT_F32 = 4
+
+
+def _out_flag(a, out, out_f32: bool) -> int:
+    """The fp32-output flag of the 16-bit GEMM: asked for, or implied by the output tensor's dtype."""
+    import torch
+    if out is not None and out.dtype == torch.float32:
+        return GEMM_OUT_F32
+    if out is not None and out.dtype != a.dtype:
+        raise TypeError("gemm: the output has the operands' dtype or float32")
+    return GEMM_OUT_F32 if out_f32 else 0
+
+
+def gemm(a, b, epilogue: str | None = None, b_is_nk: bool = False, out=None, stream=None, out_f32: bool = False):
+    """out = epilogue(a @ b) (or a @ b.T when `b_is_nk`), fp16 / bf16, fp32 accumulation. `out_f32` (or a float32 `out`):
+    the accumulator is stored as fp32 instead of being rounded to the operands' type."""
     import torch
     _need_cuda(a, b)
     if a.dtype != b.dtype or a.dim() != 2 or b.dim() != 2:
@@ -251,16 +265,18 @@ def gemm(a, b, epilogue: str | None = None, b_is_nk: bool = False, out=None, str
     n = b.shape[0] if b_is_nk else b.shape[1]
     if (b.shape[1] if b_is_nk else b.shape[0]) != k:
         raise ValueError(f"gemm: inner extents differ: {tuple(a.shape)} x {tuple(b.shape)}")
-    out = torch.empty((m, n), dtype=a.dtype, device=a.device) if out is None else out
+    flag = _out_flag(a, out, out_f32)
+    out = torch.empty((m, n), dtype=torch.float32 if flag else a.dtype, device=a.device) if out is None else out
     _need_cuda(out)
-    check(library().emmyb200_gemm(dtype_code(a), EPILOGUES[epilogue], GEMM_B_NK if b_is_nk else 0, a.data_ptr(),
+    check(library().emmyb200_gemm(dtype_code(a), EPILOGUES[epilogue], (GEMM_B_NK if b_is_nk else 0) | flag, a.data_ptr(),
                                   b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),
                                   _stream(stream)))
     return out
 
 
-def gemm_batched(a, b, bias=None, epilogue: str | None = None, b_is_nk: bool = False, out=None, stream=None):
-    """out[i] = epilogue(a[i] @ b[i] + bias) for 3-D a; b is 3-D (one plane per product) or 2-D (shared by all)."""
+def gemm_batched(a, b, bias=None, epilogue: str | None = None, b_is_nk: bool = False, out=None, stream=None, out_f32: bool = False):
+    """out[i] = epilogue(a[i] @ b[i] + bias) for 3-D a; b is 3-D (one plane per product) or 2-D (shared by all). With
+    `out_f32` (or a float32 `out`) the output and the bias are float32."""
     import torch
     _need_cuda(a, b)
     if a.dim() != 3 or b.dim() not in (2, 3) or a.dtype != b.dtype:
@@ -269,13 +285,14 @@ def gemm_batched(a, b, bias=None, epilogue: str | None = None, b_is_nk: bool = F
     n = b.shape[-2] if b_is_nk else b.shape[-1]
     if (b.shape[-1] if b_is_nk else b.shape[-2]) != k or (b.dim() == 3 and b.shape[0] != batch):
         raise ValueError(f"gemm_batched: shapes do not agree: {tuple(a.shape)} x {tuple(b.shape)}")
-    out = torch.empty((batch, m, n), dtype=a.dtype, device=a.device) if out is None else out
+    flag = _out_flag(a, out, out_f32)
+    out = torch.empty((batch, m, n), dtype=torch.float32 if flag else a.dtype, device=a.device) if out is None else out
     _need_cuda(out)
     if bias is not None:
         _need_cuda(bias)
-        if bias.dtype != a.dtype or bias.numel() != n:
-            raise ValueError("gemm_batched: bias holds N values of the operands' dtype")
-    check(library().emmyb200_gemm_batched(dtype_code(a), EPILOGUES[epilogue], GEMM_B_NK if b_is_nk else 0, a.data_ptr(),
+        if bias.dtype != out.dtype or bias.numel() != n:
+            raise ValueError("gemm_batched: bias holds N values of the output's dtype")
+    check(library().emmyb200_gemm_batched(dtype_code(a), EPILOGUES[epilogue], (GEMM_B_NK if b_is_nk else 0) | flag, a.data_ptr(),
                                           b.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), batch, m, n, k,
                                           a.stride(1), b.stride(-2), out.stride(1), a.stride(0), b.stride(0) if b.dim() == 3 else 0,
                                           out.stride(0), _stream(stream)))

@@ -151,6 +151,10 @@ int emmyb200_index_gather_i32(const int32_t* x, int32_t* y, int64_t n, int64_t m
 #define EMMYB200_EPI_RELU 2
 #define EMMYB200_GEMM_B_NK 1
 #define EMMYB200_GEMM_DST_MULTICAST 2   /* emmyb200_gemm_allgather only, see there */
+#define EMMYB200_GEMM_OUT_F32 4         /* C (and the bias of emmyb200_gemm_batched) is fp32: the accumulator stored without
+                                         * narrowing, which is also what the reference's split-K store (red.add.f32 into a
+                                         * zeroed f32 C, emmyptx/mma.py:205-242) adds up to; C is overwritten, ldc and
+                                         * stride_c count fp32 elements (multiples of 4); one destination */
 int emmyb200_gemm(int dtype, int epilogue, int flags, const void* A, const void* B, void* C,
                   int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                   void* cuda_stream);

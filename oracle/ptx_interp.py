@@ -12,7 +12,7 @@ the sum in rare ties), so float outputs carry the reference's algorithm, not a p
 Supported: the instructions of `emmyptx/ops.py` and `emmyptx/kernel.py` for one-axis tiles with scalar
 global loads and stores, predication, and the early-exit branch to `$L_exit`; and the fully unrolled tensor-core
 kernels of `emmyptx/mma.py` (fragments read from global memory as packed 16-bit pairs, `mma.sync.m16n8k16` on
-f16 / bf16 with f32 accumulators, converted `.v2.b16` stores). `mma.sync` is evaluated per warp from the PTX
+f16 / bf16 with f32 accumulators, converted `.v2.b16` stores, f32 stores and the `red.global.add.f32` of split-K). `mma.sync` is evaluated per warp from the PTX
 ISA's fragment lane map (restated in emmyptx/mma.py:6-10) with exact products summed in float64 and rounded to
 f32 once per instruction: the hardware's summation order inside one instruction is unspecified, so outputs carry
 the reference's algorithm, not one GPU's low bits. Run-time loops (emmyptx/loops.py:231-264) are followed when every
@@ -262,6 +262,15 @@ class Interpreter:
                     sel = m & (buf == b)
                     arr = self.bufs[int(b)].reshape(-1)
                     arr.view(val.dtype)[(off[sel] + j * width) // width] = val[sel]
+        elif name == "red" and tuple(parts[1:]) == ("global", "add", "f32"):
+            # split-K partial sums (emmyptx/mma.py:239-240). The hardware adds them in no particular order; here in thread order.
+            buf, off = self._mem(ops[0])
+            val = V(ops[1], "f32")
+            m = self.active if mask is None else self.active & mask
+            for b in np.unique(buf[m]):
+                sel = m & (buf == b)
+                arr = self.bufs[int(b)].reshape(-1).view(np.float32)
+                np.add.at(arr, off[sel] // 4, val[sel])
         else:
             raise PtxError(f"unsupported instruction {'.'.join(parts)}")
 

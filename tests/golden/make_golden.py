@@ -29,8 +29,12 @@ for name, info in manifest.items():
             continue                      # device-only timing case
         a, b = inputs.gemm_inputs(g["m"], g["n"], g["k"], g["dtype"], g["b_trans"], scaled=False, batch=tuple(g["batch"]))
         bufs = {"A": a.view(__import__("torch").int16).numpy().copy(), "B": b.view(__import__("torch").int16).numpy().copy(),
-                "C": np.zeros(tuple(g["batch"]) + (g["m"], g["n"]), np.int16)}
+                "C": np.zeros(tuple(g["batch"]) + (g["m"], g["n"]), np.float32 if g.get("out_f32") else np.int16)}
         ptx_interp.run_entry((HERE / f"{name}.ref.ptx").read_text(), bufs, info["launch"]["grid"][0], info["launch"]["block"][0])
+        if g.get("out_f32"):              # the fp32 accumulator itself (a zeroed C and red.add.f32 for the split-K case)
+            out[f"{name}.c32"] = bufs["C"]
+            print(name, bufs["C"][0, :4])
+            continue
         c = bufs["C"].view(np.uint16).reshape(-1, g["n"])
         if c.shape[0] > 128:              # keep the fixture small: every fourth row of the larger cases
             keep = np.arange(0, c.shape[0], 4)

@@ -61,7 +61,10 @@ GEMMS = {       # name: (m, n, k, dtype, b_trans, batch, device)
     "m_f16_linear": (64, 512, 256, "f16", True, (), True),                   # matmul.py:32, B stored N x K
     "m_f16_bmm": (128, 96, 64, "f16", False, (4,), True),                    # matmul.py:31
     "c3_f16_mm_4096": (4096, 4096, 4096, "f16", False, (), True),            # configuration 3: timed on the device only
+    "m_f16_mm_f32out": (128, 128, 256, "f16", False, (), True),              # the accumulator stored to an f32 buffer (mma.py:205-207)
+    "m_bf16_mm_splitk4": (128, 128, 256, "bf16", False, (), True),           # four cells per output cell, red.add.f32 (mma.py:239-240)
 }
+GEMM_OUT = {"m_f16_mm_f32out": ("f32", 1), "m_bf16_mm_splitk4": ("f32", 4)}      # name: (output dtype, K splits)
 
 
 ATTENTION = {   # name: (units shape, seq_q, seq_k, d, causal, scale)
@@ -124,7 +127,7 @@ def assert_in_range(graph, kernel, m, n, k) -> None:
             shape, idx = shapes[s.src_buffer], s.src_index
             span = (15, 15) if s.role == "a" else ((7, 15) if s.b_trans else (15, 7))
         elif kind == "RegStore":
-            assert s.m_guard is None and s.n_guard is None and not s.atomic
+            assert s.m_guard is None and s.n_guard is None
             shape, idx, span = shapes[s.dst_buffer], s.dst_index, (15, 7)
         else:
             continue
@@ -144,7 +147,8 @@ def ir_walk(body):
 
 manifest = {}
 for name, (m, n, k, dtype, b_trans, batch, device) in GEMMS.items():
-    graph, kernel, launch = ir.gemm_kernel(m, n, k, dtype, None, b_trans, name=name, batch=batch)
+    out_dtype, split_k = GEMM_OUT.get(name, (None, 1))
+    graph, kernel, launch = ir.gemm_kernel(m, n, k, dtype, None, b_trans, name=name, batch=batch, out_dtype=out_dtype, split_k=split_k)
     if device:
         assert_in_range(graph, kernel, m, n, k)
     CASES[name] = (graph, kernel, launch)
@@ -157,7 +161,8 @@ for name, (units, sq, sk, d, causal, scale) in ATTENTION.items():
 for name, (graph, kernel, launch) in CASES.items():
     ptx = compile_kernel(graph, kernel, launch, target="sm_89")
     (HERE / f"{name}.ref.ptx").write_text(ptx)
-    manifest[name] = {"entry": kernel.name, "launch": launch, **({"gemm": dict(zip(("m", "n", "k", "dtype", "b_trans", "batch", "device"), GEMMS[name]))} if name in GEMMS else {}),
+    manifest[name] = {"entry": kernel.name, "launch": launch, **({"gemm": dict(zip(("m", "n", "k", "dtype", "b_trans", "batch", "device"), GEMMS[name]), out_f32=name in GEMM_OUT,
+                                       split_k=GEMM_OUT.get(name, (None, 1))[1])} if name in GEMMS else {}),
                       **({"attention": dict(zip(("units", "seq_q", "seq_k", "d", "causal", "scale"), ATTENTION[name]))} if name in ATTENTION else {}),
                       "tensors": {t.name: {"shape": [d.as_static() for d in t.shape], "dtype": t.dtype.name}
                                   for n in graph.nodes.values() for t in n.outputs}}

@@ -318,3 +318,26 @@ def test_scalar_loop_attention_is_matched_by_behaviour():
     with pytest.raises(CompileError, match="not softmax"):
         handle((g, k, launch))
 
+
+def test_f32_output_and_split_k_contractions():
+    """A fragment store to an f32 buffer (emmyptx/mma.py:205-207) and its split-K form (a tile axis over parts of K, cells
+    adding partial sums with red.add.f32, :239-240) are one kernel with an fp32 output; the cells' K offsets must cover K
+    exactly once."""
+    h = handle(ir.gemm_kernel(128, 96, 256, "bf16", out_dtype="f32"))
+    assert h["variant"] == "gemm" and h["params"]["out_f32"] is True and h["params"]["k"] == 256
+    h = handle(ir.gemm_kernel(128, 96, 256, "f16", out_dtype="f32", split_k=4))
+    assert h["variant"] == "gemm" and h["params"]["out_f32"] is True and h["params"]["k"] == 256
+    h = handle(ir.gemm_kernel(64, 96, 128, "f16", None, True, out_dtype="f32", split_k=2, batch=(3,)))
+    assert h["variant"] == "gemm_batched" and h["params"]["out_f32"] is True and h["params"]["b_trans"] is True
+    assert "out_f32" not in handle(ir.gemm_kernel(128, 96, 256, "bf16"))["params"]
+    g, k, launch = ir.gemm_kernel(128, 96, 256, "f16", out_dtype="f32", split_k=4)
+    loop = next(s for s in k.body[0].body if type(s).__name__ == "Loop")
+    loop.axis = ir.Axis("k0", ir.Dim(3))                      # each part one cell short: a quarter of K is never read
+    with pytest.raises(CompileError, match="cover K exactly once"):
+        handle((g, k, launch))
+    g, k, launch = ir.gemm_kernel(128, 96, 256, "f16")
+    store = next(s for s in k.body[0].body if type(s).__name__ == "RegStore")
+    store.atomic = True                                        # red.add needs an f32 buffer
+    with pytest.raises(CompileError, match="f32 buffer"):
+        handle((g, k, launch))
+

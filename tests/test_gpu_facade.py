@@ -185,3 +185,26 @@ def test_batched_matmul_and_linear_bias_through_the_facade(tmp_path, cuda):
     x, w, bias = (torch.from_numpy(seeded(i, shp, "f16")).double() for i, shp in enumerate(([64, 256], [512, 256], [512])))
     ref = torch.relu(torch.nn.functional.linear(x, w, bias)).numpy()
     assert reference.compare(np.asarray(out["C"], np.float64).reshape(64, 512), ref, 2e-2, 1e-1)["ok"]
+
+
+def test_split_k_and_fp32_attention_through_the_facade(tmp_path, cuda):
+    """A split-K contraction (f32 C, red.add.f32 in the reference, emmyptx/mma.py:239-240) and the reference's fp32
+    attention cases (tools/torch_cases/fused.py:21-22; models.py:17-19) from IR file to result."""
+    import torch
+    out = compile_and_run(tmp_path, ir.gemm_kernel(128, 96, 256, "bf16", out_dtype="f32", split_k=4, name="k_splitk"), [
+        {"name": "A", "dtype": "bf16", "shape": [128, 256], "seed": 0}, {"name": "B", "dtype": "bf16", "shape": [256, 96], "seed": 1},
+        {"name": "C", "dtype": "f32", "shape": [128, 96], "output": True}])
+    a = torch.from_numpy(run_local.from_device(seeded(0, [128, 256], "bf16"), "bf16")).double()
+    b = torch.from_numpy(run_local.from_device(seeded(1, [256, 96], "bf16"), "bf16")).double()
+    assert np.allclose(np.asarray(out["C"], np.float64).reshape(128, 96), (a @ b).numpy(), rtol=1e-5, atol=1e-4)
+
+    for name, units, s, d, causal in (("f_sdpa", [1, 2], 64, 32, False), ("t_causal_sdpa", [1, 4], 128, 64, True)):
+        u = int(np.prod(units))
+        out = compile_and_run(tmp_path, ir.attention_scalar_kernel(units, s, s, d, causal=causal, name=name), [
+            *[{"name": nm, "dtype": "f32", "shape": [u, s, d], "seed": i} for i, nm in enumerate("QKV")],
+            {"name": "O", "dtype": "f32", "shape": [u, s, d], "output": True}])
+        q, k, v = (torch.from_numpy(np.asarray(seeded(i, [u, s, d]), np.float32)) for i in range(3))
+        ref = reference.attention_reference(q, k, v, double=True, causal=causal).numpy()
+        assert reference.compare(np.asarray(out["O"], np.float64).reshape(u, s, d), ref, 1e-3, 1e-3)["ok"]       # MM class
+        assert np.allclose(np.asarray(out["O"], np.float64).reshape(u, s, d), ref, rtol=1e-5, atol=1e-5)
+

@@ -210,3 +210,55 @@ def test_host_buffer_call_overlaps_copies_and_matches_the_device_call(cuda):
     expect = runtime.gemm(a.to(cuda), b.to(cuda), epilogue="gelu_tanh").cpu()
     assert torch.equal(c_h, expect)
     assert runtime.HostGemm(300, 64, 64, torch.bfloat16, cuda, chunks=8).chunks == 1     # no whole-block split: one chunk
+
+
+# ---- fp32 output: the accumulator stored without narrowing (and what a split-K schedule adds up to) -----------------
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 512), (100, 200, 72), (100, 72, 200), (1, 8, 8), (300, 1000, 136), (1024, 1024, 1024)])
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("b_is_nk", [False, True])
+def test_f32_output(m, n, k, dtype, b_is_nk, cuda):
+    """emmyptx/mma.py:205-242 stores an accumulator fragment to an f32 buffer as it is, or adds it with red.add.f32. The
+    result is the fp32-accumulated product of the 16-bit operands, unrounded: the bound is that of fp32 accumulation
+    (a few 2^-24 of sum |a b|), far inside the task's 16-bit tolerance."""
+    import torch
+    a, b = inputs.gemm_inputs(m, n, k, dtype, b_is_nk=b_is_nk)
+    got = _gemm(a, b, cuda, b_is_nk=b_is_nk, out_f32=True)
+    assert got.dtype == torch.float32
+    bb = b.double().t() if b_is_nk else b.double()
+    ref = a.double() @ bb
+    scale = a.double().abs() @ bb.abs()
+    assert float(((got.double() - ref).abs() / (scale * 2.0 ** -21 + 1e-30)).max()) <= 1.0
+    # the 16-bit output of the same product is this value rounded once
+    narrow = _gemm(a, b, cuda, b_is_nk=b_is_nk)
+    assert torch.equal(narrow, got.to(narrow.dtype))
+
+
+def test_f32_output_batched_with_f32_bias_and_epilogues(cuda):
+    import torch
+    from emmyptx import runtime
+    rng = np.random.default_rng(4)
+    a = torch.from_numpy(rng.standard_normal((3, 100, 136)).astype(np.float32) / 12).to(torch.bfloat16)
+    b = torch.from_numpy(rng.standard_normal((3, 136, 264)).astype(np.float32) / 12).to(torch.bfloat16)
+    bias = torch.from_numpy(rng.standard_normal(264).astype(np.float32))
+    for epilogue in (None, "relu", "gelu_tanh"):
+        got = runtime.gemm_batched(a.to(cuda), b.to(cuda), bias=bias.to(cuda), epilogue=epilogue, out_f32=True).cpu()
+        assert got.dtype == torch.float32 and runtime.device_status() == 0
+        ref = torch.matmul(a.double(), b.double()) + bias.double()
+        ref = torch.relu(ref) if epilogue == "relu" else (torch.nn.functional.gelu(ref, approximate="tanh") if epilogue else ref)
+        tol = 2e-3 if epilogue == "gelu_tanh" else 1e-5            # the fused GELU uses the hardware exponential
+        assert torch.allclose(got.double(), ref, rtol=tol, atol=tol), (epilogue, float((got.double() - ref).abs().max()))
+    with pytest.raises(ValueError, match="output's dtype"):
+        runtime.gemm_batched(a.to(cuda), b.to(cuda), bias=bias.to(torch.bfloat16).to(cuda), out_f32=True)
+
+
+def test_f32_output_argument_checks(cuda, lib):
+    import torch
+    x = torch.zeros(256 * 256, dtype=torch.float32, device=cuda)
+    p = x.data_ptr()
+    assert lib.emmyb200_gemm(1, 0, 4, p, p, p, 64, 64, 64, 64, 64, 64, None) == 0
+    assert lib.emmyb200_gemm(1, 0, 4, p, p, p, 64, 62, 64, 64, 64, 62, None) == -3          # ldc must be a multiple of 4 fp32 elements
+    assert lib.emmyb200_gemm(1, 0, 4, p, p, p, 64, 60, 64, 64, 60, 60, None) == -3          # ldb (16-bit) must still be a multiple of 8
+    assert lib.emmyb200_gemm(1, 0, 4, p, p, p, 64, 60, 64, 64, 64, 60, None) == 0           # ldc = 60 fp32 elements is 16-byte aligned
+    assert lib.emmyb200_gemm(1, 0, 4 | 2, p, p, p, 64, 64, 64, 64, 64, 64, None) < 0        # no multicast destination in fp32
+    torch.cuda.synchronize()
+

@@ -87,6 +87,10 @@ def test_contraction_handles(cuda, lib):
     ref = torch.relu(a.float() @ b.float().t() + bias.float())
     ok, ratio = reference.gemm_tolerance_ok(c.cpu(), ref)
     assert ok, ratio
+    a, b = inputs.gemm_inputs(128, 96, 256, "f16")                      # split-K IR: one kernel with an fp32 output
+    c32 = torch.zeros(128, 96, dtype=torch.float32, device=cuda)
+    assert launch(lib, handle_text(ir.gemm_kernel(128, 96, 256, "f16", out_dtype="f32", split_k=4)), [a.to(cuda), b.to(cuda), c32]) == 0
+    assert torch.allclose(c32.cpu().double(), a.double() @ b.double(), rtol=1e-5, atol=1e-6)
     q, k, v = inputs.attention_inputs(3, 200, 328, 128, "bf16")
     o = torch.zeros_like(q, device=cuda)
     assert launch(lib, handle_text(ir.attention_kernel([3], 200, 328, 128, "bf16")), [q.to(cuda), k.to(cuda), v.to(cuda), o]) == 0

@@ -142,3 +142,31 @@ def test_attention_against_the_reference_kernel(manifest, cuda, case):
     cpu = np.load(GOLDEN / "golden.npz")[f"{case}.o"].astype(np.float64)
     assert np.allclose(cpu, theirs_np, rtol=1e-5, atol=4e-6)          # ex2.approx and the division differ in the last bits
 
+
+@pytest.mark.parametrize("case", ["m_f16_mm_f32out", "m_bf16_mm_splitk4"])
+def test_f32_output_gemm_against_the_reference_kernel(manifest, cuda, case):
+    """The reference's store of an accumulator fragment to an f32 buffer, plain and as the split-K form (four cells per
+    output cell adding partial sums into a zeroed C with red.add.f32, emmyptx/mma.py:239-240), next to the tcgen05 kernel's
+    fp32 output on the same buffers: both are fp32 accumulations of the same products and agree to a few 2^-24 of
+    sum |a b|; the CPU execution of the same PTX agrees likewise."""
+    import torch
+    from emmyptx import runtime
+    info = manifest[case]
+    g = info["gemm"]
+    assert g["device"] and g["out_f32"]
+    a, b = inputs.gemm_inputs(g["m"], g["n"], g["k"], g["dtype"], g["b_trans"], scaled=False)
+    a_d, b_d = a.to(cuda), b.to(cuda)
+    theirs = torch.zeros(g["m"], g["n"], dtype=torch.float32, device=cuda)       # zeroed: the split-K cells add into it
+    torch.cuda.synchronize()
+    run_ptx((GOLDEN / f"{case}.ref.ptx").read_text(), info["entry"], [a_d.data_ptr(), b_d.data_ptr(), theirs.data_ptr()],
+            info["launch"]["grid"][0], info["launch"]["block"][0])
+    ours = runtime.gemm(a_d, b_d, out_f32=True)
+    torch.cuda.synchronize()
+    ref = (a.double() @ b.double()).numpy()
+    scale = (a.double().abs() @ b.double().abs()).numpy() * 2.0 ** -21
+    theirs_np, ours_np = theirs.cpu().double().numpy(), ours.cpu().double().numpy()
+    assert np.all(np.abs(theirs_np - ref) <= scale) and np.all(np.abs(ours_np - ref) <= scale)
+    assert np.all(np.abs(theirs_np - ours_np) <= scale)
+    cpu = np.load(GOLDEN / "golden.npz")[f"{case}.c32"].astype(np.float64)
+    assert np.all(np.abs(cpu - theirs_np) <= scale)
+

@@ -157,3 +157,14 @@ def test_interpreter_reproduces_the_attention_fixture():
     ptx_interp.run_entry((GOLDEN / "f_sdpa.ref.ptx").read_text(), bufs, info["launch"]["grid"][0], info["launch"]["block"][0])
     assert np.array_equal(bufs["O"], np.load(GOLDEN / "golden.npz")["f_sdpa.o"])
 
+
+@pytest.mark.parametrize("case", ["m_f16_mm_f32out", "m_bf16_mm_splitk4"])
+def test_f32_output_gemm_fixture(golden, case):
+    """The accumulator stored to an f32 buffer, and the split-K form of the same product (red.add.f32 into a zeroed C):
+    both are the float64 product to within fp32 accumulation."""
+    g = json.loads((GOLDEN / "reference_ptx_manifest.json").read_text())[case]["gemm"]
+    a, b = inputs.gemm_inputs(g["m"], g["n"], g["k"], g["dtype"], g["b_trans"], scaled=False)
+    ref = (a.double() @ b.double()).numpy()
+    scale = (a.double().abs() @ b.double().abs()).numpy() * 2.0 ** -21
+    assert np.all(np.abs(golden[f"{case}.c32"].astype(np.float64) - ref) <= scale)
+

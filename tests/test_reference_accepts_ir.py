@@ -63,6 +63,8 @@ def accepted_cases(ir):
     yield "m_f16_linear", ir.gemm_kernel(64, 512, 256, "f16", None, True)
     yield "m_f16_bmm", ir.gemm_kernel(128, 96, 64, "f16", batch=(4,))
     yield "m_f16_bcast", ir.gemm_kernel(128, 96, 64, "f16", batch=(4,), b_batched=False)
+    yield "m_f16_mm_f32out", ir.gemm_kernel(128, 128, 256, "f16", out_dtype="f32")
+    yield "m_bf16_mm_splitk4", ir.gemm_kernel(128, 128, 256, "bf16", out_dtype="f32", split_k=4)
     yield "c3", ir.gemm_kernel(4096, 4096, 4096, "f16")
     yield "c4_without_epilogue", ir.gemm_kernel(16384, 16384, 16384, "bf16")
     yield "m_mm", ir.matmul_f32_kernel(128, 80, 96)
