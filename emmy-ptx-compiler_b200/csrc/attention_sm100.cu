@@ -600,8 +600,10 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             uint32_t kvr = 0, cq[2] = {0, 0}, cp[2] = {0, 0}, cof[2] = {0, 0};
             bool ok = true;
             PairItem w;
+            // This thread's waits sit on the chain P ready -> MMAs -> S ready of both tiles: it polls (bounded_spin)
+            // instead of parking in try_wait, whose resume latency would be paid twice per key tile.
             auto kv_wait = [&](uint32_t r, uint32_t code) {
-                return bounded_wait(wctx, bar(KV_FULL + (r & (kKvStages - 1))), (r / kKvStages) & 1, code | (r & 0xffff));
+                return bounded_spin(wctx, bar(KV_FULL + (r & (kKvStages - 1))), (r / kKvStages) & 1, code | (r & 0xffff));
             };
             // Descriptor words built once: per k-step the issuing thread adds a constant to a low word.
             constexpr uint32_t kDescHi = ptx::smem_desc_sw128_hi(1024);
@@ -631,7 +633,7 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     if (w.n[i] == 0 || !ok) continue;
-                    if (!(ok = bounded_wait(wctx, bar(Q_FULL + i), cq[i] & 1, 0x03040000u | i))) break;
+                    if (!(ok = bounded_spin(wctx, bar(Q_FULL + i), cq[i] & 1, 0x03040000u | i))) break;
                     ++cq[i];
                     ptx::tc_fence_after_sync();
                     issue_s(i, kvr);
@@ -645,10 +647,10 @@ attention_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         if (j >= w.n[i] || !ok) continue;
-                        if (!(ok = bounded_wait(wctx, bar(P_FULL + i), cp[i] & 1, 0x03050000u | (j & 0xffff)))) break;
+                        if (!(ok = bounded_spin(wctx, bar(P_FULL + i), cp[i] & 1, 0x03050000u | (j & 0xffff)))) break;
                         ++cp[i];
                         if (j == 0) {                               // the previous item's O_i has been read out
-                            if (!(ok = bounded_wait(wctx, bar(O_FREE + i), (cof[i] & 1) ^ 1, 0x03060000u | i))) break;
+                            if (!(ok = bounded_spin(wctx, bar(O_FREE + i), (cof[i] & 1) ^ 1, 0x03060000u | i))) break;
                             ++cof[i];
                         }
                         if (!v_waited) {
@@ -956,10 +958,14 @@ static int launch_attention(const void* Q, const void* K, const void* V, void* c
     EMMY_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_att_status));
     const int64_t ctas = units * p.q_tiles;
     if (ctas >= (1ll << 31)) return fail(EMMYB200_ERR_SHAPE, "attention_fwd: %lld query tiles exceed the grid limit", (long long)ctas);
-    // Which form: measured on 256 units of 4096 x 128 (bf16, interleaved runs at the sustained clock), the two-tile form
-    // is 5 % faster with the causal flag (its couples of long and short tile pairs keep every SM busy to the end) and
-    // the one-tile form 5 % faster without it; a flag overrides the choice.
-    const bool two_tiles = (form_flags & EMMYB200_ATT_FORM_TWO_TILES) ? true : ((form_flags & EMMYB200_ATT_FORM_ONE_TILE) ? false : causal);
+    // Which form. Measured over units x sequence length x head size, with and without the causal flag (bf16, both forms
+    // forced in the same run): the two-tile form is 2-34 % faster once a unit has eight or more key tiles and there is
+    // at least one pair of query tiles per SM (its persistent CTAs walk the keys once for two tiles, and with the causal
+    // flag its couples of long and short pairs keep every SM busy to the end); for short sequences or few work items the
+    // one-tile form, with twice as many and smaller work items, is 1-67 % faster. A flag overrides the choice.
+    const int64_t pair_items = units * ((p.q_tiles + 1) / 2);
+    const bool two_tiles = (form_flags & EMMYB200_ATT_FORM_TWO_TILES) ? true
+                         : ((form_flags & EMMYB200_ATT_FORM_ONE_TILE) ? false : (pair_items >= sm_count() && seq_k >= 8 * kTileK));
     if (two_tiles) {
         using P = PairSmem<D>;
         auto pair_kernel = attention_fwd_pair_kernel<D, BF16>;

@@ -417,7 +417,7 @@ def attention(q, k, v, scale: float | None = None, causal: bool = False, out=Non
 
 
 def attention_allgather(q, k, v, dst_ptrs: list[int], scale: float | None = None, causal: bool = False, multicast: bool = False,
-                        stream=None):
+                        stream=None, form: str | None = None):
     """attention() on this rank's units, every output tile stored to each address in `dst_ptrs` (this rank's slice of
     O first, then the same slice inside each peer's full O; with `multicast`, the slice's one multicast address)."""
     _need_cuda(q, k, v)
@@ -425,7 +425,7 @@ def attention_allgather(q, k, v, dst_ptrs: list[int], scale: float | None = None
     units = q.numel() // (q.shape[-2] * d)
     arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
     scale = d ** -0.5 if scale is None else scale
-    check(library().emmyb200_attention_fwd_allgather(dtype_code(q), (ATT_CAUSAL if causal else 0) | (ATT_DST_MULTICAST if multicast else 0),
+    check(library().emmyb200_attention_fwd_allgather(dtype_code(q), (ATT_CAUSAL if causal else 0) | (ATT_DST_MULTICAST if multicast else 0) | ATT_FORMS[form],
                                                      q.data_ptr(), k.data_ptr(), v.data_ptr(), arr, len(dst_ptrs),
                                                      units, q.shape[-2], k.shape[-2], d, scale, _stream(stream)))
 

@@ -210,8 +210,8 @@ int emmyb200_gemm_allgather(int dtype, int epilogue, int flags, const void* A, c
  * multiple of 32 up to 128) run on a CUDA-core kernel that keeps every product and sum in fp32, as the reference's
  * lowering does; it has one form, one destination and at most 65535 units. EMMYB200_ATT_CAUSAL: query i attends to keys 0..i only (the lower-triangular
  * mask of tools/torch_cases/models.py:17-19, fused.py:31-36). Two kernel forms exist -- one 128-query tile per
- * CTA with two CTAs sharing an SM, or two tiles per persistent CTA -- and the library picks by the causal flag (what
- * was measured faster); EMMYB200_ATT_FORM_ONE_TILE / _TWO_TILES force one (tuning and tests; results agree within the
+ * CTA with two CTAs sharing an SM, or two tiles per persistent CTA -- and the library picks by size (two tiles per CTA
+ * when a unit has at least eight key tiles and there is a pair of query tiles for every SM: what was measured faster); EMMYB200_ATT_FORM_ONE_TILE / _TWO_TILES force one (tuning and tests; results agree within the
  * rounding of P). */
 #define EMMYB200_ATT_CAUSAL 1
 #define EMMYB200_ATT_DST_MULTICAST 2    /* emmyb200_attention_fwd_allgather only, see there */

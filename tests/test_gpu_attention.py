@@ -206,3 +206,21 @@ def test_f32_attention_large_scores(cuda):
     got = _attn(q, k, v, cuda, scale=1.0)
     ref = _attn_ref64(q, k, v, 1.0, False)
     assert torch.isfinite(got).all() and torch.allclose(got.double(), ref, rtol=5e-3, atol=5e-3), float((got.double() - ref).abs().max())
+
+
+@pytest.mark.parametrize("form", FORMS)
+@pytest.mark.parametrize("causal", [False, True])
+def test_every_output_tile_goes_to_every_destination(form, causal, cuda):
+    """The store path of the sharded configuration on one GPU: two destinations, both local buffers. Each must hold exactly
+    what the single-destination call writes, in both kernel forms (the multicast form of the same path needs a second GPU
+    and is covered by the two-GPU tests)."""
+    import torch
+    from emmyptx import runtime
+    q, k, v = (t.to(cuda) for t in inputs.attention_inputs(3, 700, 900 if not causal else 700, 128, "bf16"))
+    plain = runtime.attention(q, k, v, causal=causal, form=form)
+    o1, o2 = torch.zeros_like(q), torch.zeros_like(q)
+    runtime.attention_allgather(q, k, v, [o1.data_ptr(), o2.data_ptr()], causal=causal, form=form)
+    torch.cuda.synchronize()
+    assert runtime.device_status() == 0
+    assert torch.equal(o1, plain) and torch.equal(o2, plain)
+

@@ -62,6 +62,17 @@ def _worker_multicast(rank: int, world: int, port: int):
         assert ok, f"rank {rank}: multicast attention worst error {ratio:.2f}x the bound"
         plain = runtime.attention(q.to(dev), k.to(dev), v.to(dev))
         assert torch.equal(plain, o_full)
+        # the same through the other kernel form (two query tiles per CTA: what long sequences run), plain and causal
+        for causal in (False, True):
+            o_full.zero_()
+            opeers.barrier()
+            runtime.attention_allgather(q[ulo:uhi].to(dev).contiguous(), k[ulo:uhi].to(dev).contiguous(), v[ulo:uhi].to(dev).contiguous(),
+                                        [omc + ulo * sq * d * 2], multicast=True, causal=causal, form="two_tiles")
+            opeers.barrier()
+            torch.cuda.synchronize()
+            assert runtime.device_status() == 0
+            plain = runtime.attention(q.to(dev), k.to(dev), v.to(dev), causal=causal, form="two_tiles")
+            assert torch.equal(plain, o_full), f"rank {rank}: two-tile multicast attention (causal={causal}) differs from the local result"
     finally:
         dist.destroy_process_group()
 
@@ -109,6 +120,14 @@ def _worker(rank: int, world: int, port: int):
         assert runtime.device_status() == 0
         ok, ratio = reference.gemm_tolerance_ok(o_full.cpu(), reference.attention_reference(q, k, v))
         assert ok, f"rank {rank}: attention worst error {ratio:.2f}x the bound"
+        o_full.zero_()
+        opeers.barrier()
+        runtime.attention_allgather(q[ulo:uhi].to(dev).contiguous(), k[ulo:uhi].to(dev).contiguous(), v[ulo:uhi].to(dev).contiguous(), odst,
+                                    form="two_tiles")
+        opeers.barrier()
+        torch.cuda.synchronize()
+        assert runtime.device_status() == 0
+        assert torch.equal(runtime.attention(q.to(dev), k.to(dev), v.to(dev), form="two_tiles"), o_full), f"rank {rank}: two-tile form"
     finally:
         dist.destroy_process_group()
 
