@@ -43,7 +43,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # under profiles/ (c4: a one-pass capture of the two counters at the full M=N=K=16384; c5: captured on 64 of the 256
 # units and scaled by 4; c2, c3: captured at full size; c1: 8 MiB working set, L2-resident, no DRAM figure; lerp: the
 # kernel compiled for the program, at N=2^26).
-DRAM_TRAFFIC = {"c4": 8.83e9 + 0.53713e9, "c5": 4 * (201.44e6 + 49.98e6), "c2": 268.97e6 + 222.76e6,
+DRAM_TRAFFIC = {"c4": 8.83e9 + 0.53713e9, "c5": 4 * (201.55e6 + 46.59e6), "c2": 268.97e6 + 222.76e6,
                 "c3": 83.01e6 + 14.28e6, "c1": None, "softmax": 268.46e6 + 216.40e6, "f32mm": None, "lerp": None}
 
 WORKLOADS = {
