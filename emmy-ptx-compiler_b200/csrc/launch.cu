@@ -293,6 +293,45 @@ extern "C" int emmyb200_launch(const char* handle_json, void* const* params, int
         for (int i = 0; i < c.n_inputs; ++i) ins[i] = a.input(i);
         return emmyb200_pointwise_program(&c, ins, out, geti(p, "n"), cuda_stream);
     }
+    if (v == "pointwise_indexed") {
+        const JVal* prog = p.get("program");
+        const JVal* im = p.get("index_map");
+        if (prog == nullptr || im == nullptr) return fail(EMMYB200_ERR_ARG, "launch: the handle has no program or no index map");
+        emmyb200_pw_program c;
+        int rc = fill_program(*prog, a, &c);
+        if (rc != EMMYB200_OK) return rc;
+        const JVal* ext = im->get("extents");
+        const JVal* srcs = im->get("inputs");
+        const JVal* dst = im->get("out");
+        if (ext == nullptr || srcs == nullptr || dst == nullptr || ext->items.empty() || ext->items.size() > EMMYB200_PW_MAX_AXES ||
+            (int)srcs->items.size() != c.n_inputs || dst->get("coef") == nullptr || dst->get("coef")->items.size() != ext->items.size())
+            return fail(EMMYB200_ERR_ARG, "launch: malformed index map");
+        emmyb200_pw_index_map m;
+        memset(&m, 0, sizeof m);
+        m.n_axes = (int)ext->items.size();
+        for (int ax = 0; ax < m.n_axes; ++ax) {
+            m.extent[ax] = ext->items[ax].as_int();
+            m.out_coef[ax] = dst->get("coef")->items[ax].as_int();
+        }
+        m.out_offset = geti(*dst, "offset");
+        const void* ins[EMMYB200_PW_MAX_INPUTS] = {nullptr, nullptr, nullptr, nullptr};
+        int next_buffer = 0;                                  // the handle's inputs are the buffer-backed sources, in program order
+        for (int k = 0; k < c.n_inputs; ++k) {
+            const JVal& src = srcs->items[k];
+            if (src.get("axis") != nullptr) {
+                m.in_kind[k] = 1;
+                m.in_axis[k] = (int)geti(src, "axis");
+                continue;
+            }
+            const JVal* coef = src.get("coef");
+            if (coef == nullptr || (int)coef->items.size() != m.n_axes) return fail(EMMYB200_ERR_ARG, "launch: malformed index map");
+            m.in_offset[k] = geti(src, "offset");
+            for (int ax = 0; ax < m.n_axes; ++ax) m.in_coef[k][ax] = coef->items[ax].as_int();
+            if (next_buffer >= (int)h.get("inputs")->items.size()) return fail(EMMYB200_ERR_ARG, "launch: the index map names more buffers than the handle has inputs");
+            ins[k] = a.input(next_buffer++);
+        }
+        return emmyb200_pointwise_indexed(&c, &m, ins, out, cuda_stream);
+    }
     if (v == "index_gather_i32")
         return emmyb200_index_gather_i32((const int32_t*)a.input(0), (int32_t*)out, geti(p, "n"), geti(p, "mul"), geti(p, "add"), (int32_t)geti(p, "div"),
                                          (int32_t)geti(p, "shift"), getb(p, "trunc") ? EMMYB200_GATHER_TRUNC : 0, cuda_stream);

@@ -444,6 +444,56 @@ extern "C" __global__ void __launch_bounds__(PW_THREADS) pw_jit_kernel(const voi
 }
 )SHELL";
 
+// The kernel of an indexed program (emmyb200_pointwise_indexed): one cell per thread and trip. The cell number is
+// split into the digits of the tile's axes (outermost first, last fastest, emmyptx/kernel.py:587-626); input k reads
+// element offset + sum coef * digit of its buffer, or IS a digit; the value goes to element out_offset + sum out_coef *
+// digit. PW_NAXES and PW_KIND0..3 (0 buffer, 1 digit) are defined in front of it. 32-bit index arithmetic whenever the
+// cell count and every buffer extent fit (the host says so through `narrow`).
+static const char kIndexedKernel[] = R"SHELL(
+struct PwIndexArg { i64 extent[6]; i64 in_offset[4]; i64 in_coef[4][6]; i64 out_offset; i64 out_coef[6]; int in_axis[4]; int narrow; };
+template <typename I> __device__ __forceinline__ void pw_ix_cell(const void* p0, const void* p1, const void* p2, const void* p3, void* out, I i,
+                                                               const PwConsts& c, const PwIndexArg& m) {
+    I d[PW_NAXES > 0 ? PW_NAXES : 1];
+    I rem = i;
+#pragma unroll
+    for (int a = PW_NAXES - 1; a >= 0; --a) {
+        const I e = (I)m.extent[a];
+        const I q = rem / e;
+        d[a] = rem - q * e;
+        rem = q;
+    }
+    I at[4], to = (I)m.out_offset;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) at[k] = (I)m.in_offset[k];
+#pragma unroll
+    for (int a = 0; a < PW_NAXES; ++a) {
+#pragma unroll
+        for (int k = 0; k < PW_N_IN; ++k) at[k] += (I)m.in_coef[k][a] * d[a];
+        to += (I)m.out_coef[a] * d[a];
+    }
+    PW_T v0 = (PW_T)0, v1 = (PW_T)0, v2 = (PW_T)0, v3 = (PW_T)0;
+    v0 = PW_KIND0 ? (PW_T)d[m.in_axis[0]] : pw_ld1<PW_DT0>(p0, (i64)at[0]);
+#if PW_N_IN > 1
+    v1 = PW_KIND1 ? (PW_T)d[m.in_axis[1]] : pw_ld1<PW_DT1>(p1, (i64)at[1]);
+#endif
+#if PW_N_IN > 2
+    v2 = PW_KIND2 ? (PW_T)d[m.in_axis[2]] : pw_ld1<PW_DT2>(p2, (i64)at[2]);
+#endif
+#if PW_N_IN > 3
+    v3 = PW_KIND3 ? (PW_T)d[m.in_axis[3]] : pw_ld1<PW_DT3>(p3, (i64)at[3]);
+#endif
+    pw_st1(out, (i64)to, pw_cell(v0, v1, v2, v3, c));
+}
+extern "C" __global__ void __launch_bounds__(256) pw_ix_kernel(const void* p0, const void* p1, const void* p2, const void* p3, void* out, i64 n,
+                                                               PwConsts c, PwIndexArg m) {
+    const i64 stride = (i64)gridDim.x * 256;
+    for (i64 i = (i64)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+        if (m.narrow) pw_ix_cell<int>(p0, p1, p2, p3, out, (int)i, c, m);
+        else pw_ix_cell<i64>(p0, p1, p2, p3, out, i, c, m);
+    }
+}
+)SHELL";
+
 static bool float_program(const emmyb200_pw_program& p) {
     return p.out_dtype == EMMYB200_F32 || p.out_dtype == EMMYB200_F16 || p.out_dtype == EMMYB200_BF16;
 }
@@ -457,7 +507,7 @@ static int broadcast_mode(const emmyb200_pw_program& p, int k, int group, bool b
     return (group != 0 && base_aligned && p.in_div[k] == 0 && p.in_mod[k] % per == 0) ? 2 : 1;
 }
 
-static std::string program_source(const emmyb200_pw_program& p, int group, const int* modes) {
+static std::string program_source(const emmyb200_pw_program& p, int group, const int* modes, const emmyb200_pw_index_map* map = nullptr) {
     const bool ints = !float_program(p);
     const char* type = ints ? "int" : "float";
     std::string s;
@@ -468,6 +518,11 @@ static std::string program_source(const emmyb200_pw_program& p, int group, const
     for (int k = 0; k < EMMYB200_PW_MAX_INPUTS; ++k) {
         const bool used = k < p.n_inputs;
         snprintf(line, sizeof line, "#define PW_DT%d %d\n#define PW_BC%d %d\n", k, used ? p.in_dtype[k] : (ints ? EMMYB200_I32 : EMMYB200_F32), k, used ? modes[k] : 0);
+        s += line;
+    }
+    if (map != nullptr) {
+        snprintf(line, sizeof line, "#define PW_NAXES %d\n#define PW_KIND0 %d\n#define PW_KIND1 %d\n#define PW_KIND2 %d\n#define PW_KIND3 %d\n", map->n_axes,
+                 map->in_kind[0], map->in_kind[1], map->in_kind[2], map->in_kind[3]);
         s += line;
     }
     if (!ints) s += "#include \"emmy_math.cuh\"\n";
@@ -494,9 +549,9 @@ static std::string program_source(const emmyb200_pw_program& p, int group, const
     snprintf(line, sizeof line, "    return s%d;\n}\n", p.out_slot);
     s += line;
     s += ints ? kIntLoads : kFloatLoads;
-    s += kInputs;
+    if (map == nullptr) s += kInputs;
     s += ints ? kIntStores : kFloatStores;
-    s += kKernel;
+    s += map == nullptr ? kKernel : kIndexedKernel;
     return s;
 }
 
@@ -602,7 +657,136 @@ int pw_jit_launch(const emmyb200_pw_program& prog, const void* const* inputs, vo
     return EMMYB200_OK;
 }
 
+static int check_program(const emmyb200_pw_program* prog, const char* who) {
+    if (prog == nullptr) return fail(EMMYB200_ERR_ARG, "%s: null program", who);
+    if (prog->n_inputs < 1 || prog->n_inputs > EMMYB200_PW_MAX_INPUTS || prog->n_steps < 0 || prog->n_steps > EMMYB200_PW_MAX_STEPS ||
+        prog->out_slot < 0 || prog->out_slot >= EMMYB200_PW_MAX_SLOTS)
+        return fail(EMMYB200_ERR_ARG, "%s: not a program (inputs, steps or output slot out of range)", who);
+    const bool ints = prog->out_dtype == EMMYB200_I32 || prog->out_dtype == EMMYB200_I64;
+    if (!float_program(*prog) && !ints) return fail(EMMYB200_ERR_UNSUPPORTED, "%s: output dtype %d", who, prog->out_dtype);
+    for (int k = 0; k < prog->n_inputs; ++k) {
+        const int d = prog->in_dtype[k];
+        const bool ok = ints ? (d == EMMYB200_I32 || d == EMMYB200_I64) : (d == EMMYB200_F32 || d == EMMYB200_F16 || d == EMMYB200_BF16 || d == EMMYB200_U8);
+        if (!ok) return fail(EMMYB200_ERR_UNSUPPORTED, "%s: input %d has dtype %d (%s program)", who, k, d, ints ? "an integer" : "a float");
+    }
+    for (int i = 0; i < prog->n_steps; ++i) {
+        const emmyb200_pw_step& st = prog->steps[i];
+        if (st.op >= EMMYB200_PW_OP_COUNT || st.dst >= EMMYB200_PW_MAX_SLOTS) return fail(EMMYB200_ERR_ARG, "%s: bad step %d", who, i);
+        for (int o : {st.a, st.b, st.c})
+            if (o >= EMMYB200_PW_MAX_SLOTS + EMMYB200_PW_MAX_CONSTS) return fail(EMMYB200_ERR_ARG, "%s: bad operand in step %d", who, i);
+    }
+    return EMMYB200_OK;
+}
+
+struct PwIndexArgHost { long long extent[6]; long long in_offset[4]; long long in_coef[4][6]; long long out_offset; long long out_coef[6]; int in_axis[4]; int narrow; };
+
 }  // namespace emmy
+
+extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const emmyb200_pw_index_map* map, const void* const* inputs, void* out,
+                                          void* cuda_stream) {
+    using namespace emmy;
+    int rc = check_program(prog, "pointwise_indexed");
+    if (rc != EMMYB200_OK) return rc;
+    if (map == nullptr) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: null index map");
+    if (map->n_axes < 1 || map->n_axes > EMMYB200_PW_MAX_AXES) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: %d axes (1 to %d)", map->n_axes, EMMYB200_PW_MAX_AXES);
+    int64_t n = 1;
+    bool narrow = true;
+    for (int a = 0; a < map->n_axes; ++a) {
+        if (map->extent[a] < 0) return fail(EMMYB200_ERR_SHAPE, "pointwise_indexed: negative extent");
+        if (map->extent[a] != 0 && n > ((int64_t)1 << 40)) return fail(EMMYB200_ERR_SHAPE, "pointwise_indexed: too many cells");
+        n *= map->extent[a];
+    }
+    if (n == 0) return EMMYB200_OK;
+    if (n > 0x7fffffffLL) narrow = false;
+    // the largest and smallest element every map reaches: for the 32-bit choice, and so that a negative index is refused
+    auto range_ok = [&](int64_t off, const int64_t* coef, const char* what) -> int {
+        int64_t lo = off, hi = off;
+        for (int a = 0; a < map->n_axes; ++a) {
+            const int64_t span = coef[a] * (map->extent[a] - 1);
+            if (span < 0) lo += span; else hi += span;
+        }
+        if (lo < 0) return fail(EMMYB200_ERR_SHAPE, "pointwise_indexed: %s reaches element %lld", what, (long long)lo);
+        if (hi > 0x7fffffffLL) narrow = false;
+        for (int a = 0; a < map->n_axes; ++a)
+            if (coef[a] > 0x7fffffffLL || coef[a] < -0x7fffffffLL) narrow = false;
+        return EMMYB200_OK;
+    };
+    if (inputs == nullptr || out == nullptr) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: null buffer");
+    for (int k = 0; k < prog->n_inputs; ++k) {
+        if (map->in_kind[k] != 0 && map->in_kind[k] != 1) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: input %d has kind %d", k, map->in_kind[k]);
+        if (map->in_kind[k] == 1) {
+            if (map->in_axis[k] < 0 || map->in_axis[k] >= map->n_axes) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: input %d names axis %d", k, map->in_axis[k]);
+            continue;
+        }
+        if (inputs[k] == nullptr) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: null buffer");
+        if ((rc = range_ok(map->in_offset[k], map->in_coef[k], "an input map")) != EMMYB200_OK) return rc;
+    }
+    if ((rc = range_ok(map->out_offset, map->out_coef, "the output map")) != EMMYB200_OK) return rc;
+    if (!nvrtc().ok) return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_indexed: needs the run-time compiler (libnvrtc.so.12 not found)");
+    emmyb200_pw_index_map key_map = *map;
+    for (int k = prog->n_inputs; k < EMMYB200_PW_MAX_INPUTS; ++k) key_map.in_kind[k] = 0;
+    JitKernel kern;
+    {
+        std::lock_guard<std::mutex> lock(g_jit_mutex);
+        const int modes[EMMYB200_PW_MAX_INPUTS] = {0, 0, 0, 0};
+        std::string key = program_key(*prog, 0, modes);
+        key.push_back('x');
+        key.push_back((char)map->n_axes);
+        for (int k = 0; k < EMMYB200_PW_MAX_INPUTS; ++k) key.push_back((char)key_map.in_kind[k]);
+        auto it = jit_cache().find(key);
+        if (it == jit_cache().end()) {
+            std::vector<char> cubin;
+            rc = compile_source(program_source(*prog, 0, modes, &key_map), &cubin);
+            if (rc != EMMYB200_OK) return rc;
+            cudaError_t e = cudaLibraryLoadData(&kern.library, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaLibraryLoadData (indexed elementwise kernel)");
+            e = cudaLibraryGetKernel(&kern.kernel, kern.library, "pw_ix_kernel");
+            if (e != cudaSuccess) { cudaLibraryUnload(kern.library); return cuda_fail(e, "cudaLibraryGetKernel (indexed elementwise kernel)"); }
+            g_jit_compiles.fetch_add(1);
+            it = jit_cache().emplace(key, kern).first;
+        }
+        kern = it->second;
+    }
+    const void* p[EMMYB200_PW_MAX_INPUTS] = {nullptr, nullptr, nullptr, nullptr};
+    PwConstsArg c;
+    PwIndexArgHost m;
+    memset(&m, 0, sizeof m);
+    for (int i = 0; i < EMMYB200_PW_MAX_CONSTS; ++i) c.v[i] = prog->consts[i];
+    for (int a = 0; a < EMMYB200_PW_MAX_AXES; ++a) {
+        m.extent[a] = a < map->n_axes ? map->extent[a] : 1;
+        m.out_coef[a] = a < map->n_axes ? map->out_coef[a] : 0;
+    }
+    m.out_offset = map->out_offset;
+    for (int k = 0; k < prog->n_inputs; ++k) {
+        p[k] = map->in_kind[k] == 0 ? inputs[k] : nullptr;
+        m.in_offset[k] = map->in_offset[k];
+        m.in_axis[k] = map->in_kind[k] == 1 ? map->in_axis[k] : 0;
+        for (int a = 0; a < map->n_axes; ++a) m.in_coef[k][a] = map->in_kind[k] == 0 ? map->in_coef[k][a] : 0;
+    }
+    m.narrow = narrow ? 1 : 0;
+    long long count = n;
+    void* args[] = {&p[0], &p[1], &p[2], &p[3], &out, &count, &c, &m};
+    const int64_t want = (n + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    const unsigned blocks = (unsigned)(want < cap ? want : cap);
+    cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(kern.kernel), dim3(blocks), dim3(256), args, 0, static_cast<cudaStream_t>(cuda_stream));
+    if (e != cudaSuccess) return cuda_fail(e, "launch of the indexed elementwise kernel");
+    return EMMYB200_OK;
+}
+
+extern "C" int emmyb200_pointwise_indexed_compile(const emmyb200_pw_program* prog, const emmyb200_pw_index_map* map, int64_t* code_bytes) {
+    using namespace emmy;
+    int rc = check_program(prog, "pointwise_indexed_compile");
+    if (rc != EMMYB200_OK) return rc;
+    if (map == nullptr || map->n_axes < 1 || map->n_axes > EMMYB200_PW_MAX_AXES) return fail(EMMYB200_ERR_ARG, "pointwise_indexed_compile: bad index map");
+    emmyb200_pw_index_map key_map = *map;
+    for (int k = 0; k < EMMYB200_PW_MAX_INPUTS; ++k) key_map.in_kind[k] = (k < prog->n_inputs && map->in_kind[k] == 1) ? 1 : 0;
+    const int modes[EMMYB200_PW_MAX_INPUTS] = {0, 0, 0, 0};
+    std::vector<char> cubin;
+    rc = compile_source(program_source(*prog, 0, modes, &key_map), &cubin);
+    if (rc == EMMYB200_OK && code_bytes != nullptr) *code_bytes = (int64_t)cubin.size();
+    return rc;
+}
 
 extern "C" int emmyb200_set_pointwise_jit(int enabled) {
     const bool before = emmy::jit_enabled();

@@ -630,3 +630,50 @@ def attention_scalar_kernel(units_shape: list[int], seq_q: int, seq_k: int, d: i
                [tensor("O", [u, seq_q, d], dtype)])
     return g, kern, _launch(kern, ["Q", "K", "V", "O"], u * seq_q * d)
 
+
+def layout_kernel(case: str, name: str | None = None):
+    """The reference's data-movement cases (tools/torch_cases/shapes.py:6-19) as one-cell-per-element tiles whose Loads and
+    Write index their buffers with expressions of the axis variables -- what a tracer hands over for a transpose, a
+    slice or a flip -- plus masks made of the axis variables themselves (tril) and a concatenation written slice by
+    slice (`s_cat_a`, `s_cat_b`: two kernels over one output). Returns (graph, kernel, launch)."""
+    lit = lambda v: Literal(int(v), "int")
+    add = lambda a, b: BinaryExpr("+", a, b)
+    mul = lambda a, b: BinaryExpr("*", a, b)
+    sub = lambda a, b: BinaryExpr("-", a, b)
+    A = lambda nm, n: Axis(nm, Dim(n))
+    cases = {
+        # name: (axes, inputs {buffer: shape}, loads [(value, buffer, index)], assigns, out shape, out index, value)
+        "s_transpose": ([A("i0", 96), A("j0", 64)], {"X": [64, 96]}, [("x", "X", [Var("j0"), Var("i0")])], [], [96, 64], [Var("i0"), Var("j0")], "x"),
+        "s_permute": ([A("a0", 32), A("b0", 8), A("c0", 16)], {"X": [8, 16, 32]}, [("x", "X", [Var("b0"), Var("c0"), Var("a0")])],
+                      [Assign("y", Op("multiply"), ["x", 2.0])], [32, 8, 16], [Var("a0"), Var("b0"), Var("c0")], "y"),
+        "s_slice": ([A("r0", 64), A("c0", 40)], {"X": [64, 128]}, [("x", "X", [Var("r0"), add(Var("c0"), lit(10))])],
+                    [Assign("y", Op("multiply"), ["x", 2.0])], [64, 40], [Var("r0"), Var("c0")], "y"),
+        "s_strided_slice": ([A("i0", 512)], {"X": [1024]}, [("x", "X", [mul(Var("i0"), lit(2))])], [Assign("y", Op("add"), ["x", 1.0])],
+                            [512], [Var("i0")], "y"),
+        "s_flip": ([A("r0", 64), A("c0", 128)], {"X": [64, 128]}, [("x", "X", [Var("r0"), sub(lit(127), Var("c0"))])], [], [64, 128],
+                   [Var("r0"), Var("c0")], "x"),
+        "s_repeat": ([A("t0", 2), A("r0", 32), A("c0", 64)], {"X": [32, 64]}, [("x", "X", [Var("r0"), Var("c0")])],
+                     [Assign("y", Op("add"), ["x", 0.0])], [64, 64], [add(mul(Var("t0"), lit(32)), Var("r0")), Var("c0")], "y"),
+        "s_stack": ([A("s0", 2), A("r0", 32), A("c0", 64)], {"A": [32, 64], "B": [32, 64]},
+                    [("a", "A", [Var("r0"), Var("c0")]), ("b", "B", [Var("r0"), Var("c0")])],
+                    [Assign("first", Op("equal"), ["s0", 0.0]), Assign("y", Op("where"), ["first", "a", "b"])], [2, 32, 64],
+                    [Var("s0"), Var("r0"), Var("c0")], "y"),
+        "s_tril": ([A("r0", 64), A("c0", 64)], {"X": [64, 64]}, [("x", "X", [Var("r0"), Var("c0")])],
+                   [Assign("keep", Op("less_equal"), ["c0", "r0"]), Assign("y", Op("where"), ["keep", "x", 0.0])], [64, 64],
+                   [Var("r0"), Var("c0")], "y"),
+        "s_cat_a": ([A("r0", 32), A("c0", 64)], {"A": [32, 64]}, [("a", "A", [Var("r0"), Var("c0")])], [], [32, 112], [Var("r0"), Var("c0")], "a"),
+        "s_cat_b": ([A("r0", 32), A("c0", 48)], {"B": [32, 48]}, [("b", "B", [Var("r0"), Var("c0")])], [], [32, 112],
+                    [Var("r0"), add(Var("c0"), lit(64))], "b"),
+        # refused on purpose: a rotation wraps around (the index is not affine in the axis variables)
+        "s_roll": ([A("r0", 64), A("c0", 128)], {"X": [64, 128]}, [("x", "X", [Var("r0"), BinaryExpr("%", add(Var("c0"), lit(125)), lit(128))])], [],
+                   [64, 128], [Var("r0"), Var("c0")], "x"),
+    }
+    axes, ins, loads, assigns, out_shape, out_index, value = cases[case]
+    body = [Load([v], buf, idx) for v, buf, idx in loads] + list(assigns) + [Write("out", out_index, [value])]
+    kern = KernelOp(name or f"k_{case}", [Tile(axes, body)])
+    cells = 1
+    for a in axes:
+        cells *= a.extent.value
+    g = _graph(kern, [tensor(b, shp, "f32") for b, shp in ins.items()], [tensor("out", out_shape, "f32")])
+    return g, kern, _launch(kern, [*ins, "out"], cells)
+

@@ -91,6 +91,18 @@ def algorithmic_work(handle: dict) -> tuple[float, str]:
         div, mod = prog.get("in_div", [0] * 4), prog.get("in_mod", [0] * 4)
         read = sum(size[d] * (mod[k] or (n // div[k] if div[k] else n)) for k, d in enumerate(prog["in_dtypes"]))      # broadcast inputs are small
         return float(read + n * size[prog["out_dtype"]]), "B"
+    if v == "pointwise_indexed":
+        size = {"f32": 4, "f16": 2, "bf16": 2, "i32": 4, "int": 4, "i64": 8, "bool": 1, "u8": 1}
+        prog, n, im = p["program"], p["n"], p["index_map"]
+        read = 0
+        for d, src in zip(prog["in_dtypes"], im["inputs"]):
+            if "axis" in src:
+                continue                                    # an axis digit: no memory behind it
+            distinct = 1
+            for c, e in zip(src["coef"], im["extents"]):    # elements the map can reach: axes it ignores repeat them
+                distinct *= e if c else 1
+            read += size[d] * distinct
+        return float(read + n * size[prog["out_dtype"]]), "B"
     if v == "gemm":
         return 2.0 * p["m"] * p["n"] * p["k"], "flop"
     if v == "gemm_f32":

@@ -326,7 +326,136 @@ def build_program(tile, tensors: dict, out_name: str, out_value_name, integer: b
     return prog
 
 
+class Load:
+    """A synthetic Load the indexed matcher puts in front of a cell program (one per source of a value)."""
+
+    def __init__(self, name: str, source: str) -> None:
+        self.names, self.input, self.index = [name], source, []
+
+
+class _Body:
+    def __init__(self, body: list) -> None:
+        self.body = body
+
+
+def _fit_affine(idx: np.ndarray, digits: list, what: str):
+    """offset and one coefficient per axis such that idx = offset + sum coef * digit on every probe cell, or Unmatched.
+    The probe cells contain cell 0 and, for every axis longer than 1, the cell whose only non-zero digit is a 1 there."""
+    zero = np.all([d == 0 for d in digits], axis=0) if digits else np.ones(idx.shape, bool)
+    off = int(idx[zero][0])
+    coef = []
+    for a, d in enumerate(digits):
+        unit = (d == 1) & np.all([dd == 0 for b, dd in enumerate(digits) if b != a], axis=0)
+        coef.append(int(idx[unit][0]) - off if unit.any() else 0)
+    want = off + sum(c * d for c, d in zip(coef, digits)) if digits else np.full(idx.shape, off)
+    if not np.array_equal(np.asarray(idx, np.int64), np.asarray(want, np.int64)):
+        raise Unmatched(f"{what} is not an affine function of the tile's axis variables")
+    return off, coef
+
+
+def _reach(off: int, coef: list, extents: list):
+    lo = hi = off
+    for c, e in zip(coef, extents):
+        lo, hi = lo + min(0, c * (e - 1)), hi + max(0, c * (e - 1))
+    return lo, hi
+
+
+def match_indexed(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
+    """A one-cell-per-element Tile whose Loads and Write address their buffers by affine functions of the axis variables,
+    and whose Assigns may use the axis variables as values: the reference's data-movement cases (transpose, permute,
+    slices, flip, stack, a concatenation written slice by slice: tools/torch_cases/shapes.py:6-17) and masks made from
+    indices (tril, :19). Every index expression is run on probe cells, fitted, checked on all of them and checked against
+    the buffers' sizes over the whole tile; the Assign chain becomes a cell program as for any elementwise kernel."""
+    tensors = tensor_table(graph)
+    tiles = [s for s in kernel.body if _kind(s) == "Tile"]
+    if len(kernel.body) != 1 or len(tiles) != 1:
+        raise Unmatched("a streaming kernel is one Tile")
+    tile = tiles[0]
+    if len(tile.axes) > 6:
+        raise Unmatched("more than 6 tile axes")
+    extents = [int(a.extent.as_static()) for a in tile.axes]
+    names = [a.name for a in tile.axes]
+    n = math.prod(extents)
+    if n > 2**31 - 1 or n < 1:
+        raise Unmatched(f"a tile of {n} cells has no indexed variant")
+    if any(_kind(s) not in ("Load", "Assign", "Write") for s in tile.body):
+        raise Unmatched("the indexed elementwise kernel runs Load / Assign / Write programs")
+    strides = [math.prod(extents[a + 1:]) for a in range(len(extents))]
+    rng = np.random.default_rng(0)
+    cells = np.unique(np.concatenate([np.arange(min(n, 64)), rng.integers(0, n, 200), [n - 1],
+                                      [st for st, e in zip(strides, extents) if e > 1]])).astype(np.int64)
+    it = CellInterpreter(tensors, cells, INT_OPS_TRUNC if int_div == "trunc" else INT_OPS)
+    digits = [(cells // st) % e for st, e in zip(strides, extents)]
+    for nm, d in zip(names, digits):
+        it.env[nm] = d
+    it.run(tile.body)
+    loads = [s for s in tile.body if _kind(s) == "Load"]
+    writes = [s for s in tile.body if _kind(s) == "Write"]
+    if len(writes) != 1 or len(it.writes) != 1 or len(it.writes[0][2]) != 1 or _kind(tile.body[-1]) != "Write":
+        raise Unmatched("indexed kernels end in one Write of one value per cell")
+    if any(cnt != 1 for _, _, cnt in it.loads) or len(it.loads) != len(loads):
+        raise Unmatched("indexed kernels read one element per Load")
+    out_name, out_idx, _ = it.writes[0]
+    out_dtype = tensors[out_name][1]
+    integer = out_dtype in ("i32", "i64", "int")
+    ok_in = ("i32", "i64", "int") if integer else ("f32", "f16", "bf16", "bool", "u8")
+    if not integer and out_dtype not in ("f32", "f16", "bf16"):
+        raise Unmatched(f"no indexed variant writes {out_dtype}")
+    # the sources of values, in program order: one per Load, one per axis variable an Assign uses as a value
+    body, sources, synthetic = [], [], dict(tensors)
+    for k, (s, (buf, idx, _)) in enumerate(zip(loads, it.loads)):
+        if tensors[buf][1] not in ok_in:
+            raise Unmatched(f"input {buf!r} of dtype {tensors[buf][1]} in {'an integer' if integer else 'a float'} program")
+        off, coef = _fit_affine(idx, digits, f"the index of {buf!r}")
+        lo, hi = _reach(off, coef, extents)
+        if lo < 0 or hi >= math.prod(tensors[buf][0]):
+            raise Unmatched(f"the index of {buf!r} leaves the buffer (elements {lo}..{hi} of {math.prod(tensors[buf][0])})")
+        name = f"__in{k}"
+        synthetic[name] = (tensors[buf][0], tensors[buf][1])
+        sources.append({"buffer": buf, "offset": off, "coef": coef})
+        body.append(Load(s.names[0], name))
+    used_axes = [nm for nm in names if any(_kind(s) == "Assign" and nm in [a for a in s.args if isinstance(a, str)] for s in tile.body)]
+    for nm in used_axes:
+        synthetic[f"__axis_{nm}"] = ((n,), "i32" if integer else "f32")
+        sources.append({"axis": names.index(nm)})
+        body.append(Load(nm, f"__axis_{nm}"))
+    if not sources:
+        raise Unmatched("an indexed kernel reads something")
+    body += [s for s in tile.body if _kind(s) != "Load"]
+    off, coef = _fit_affine(out_idx, digits, "the index of the Write")
+    lo, hi = _reach(off, coef, extents)
+    if lo < 0 or hi >= math.prod(tensors[out_name][0]):
+        raise Unmatched(f"the Write leaves its buffer (elements {lo}..{hi} of {math.prod(tensors[out_name][0])})")
+    order = sorted((abs(c), e) for c, e in zip(coef, extents) if e > 1)         # no two cells may write one element
+    span = 0
+    for c, e in order:
+        if c <= span:
+            raise Unmatched("two cells write the same element")
+        span += c * (e - 1)
+    scalars = scalar_args(launch)
+    prog = build_program(_Body(body), synthetic, out_name, writes[0].values[0], integer=integer, scalars=scalars)
+    if integer:
+        prog["int_div"] = int_div
+    by_name = {f"__in{k}": sources[k] for k in range(len(loads))}
+    by_name.update({f"__axis_{nm}": sources[len(loads) + j] for j, nm in enumerate(used_axes)})
+    ordered = [by_name[nm] for nm in prog["inputs"]]
+    index_map = {"extents": extents, "inputs": ordered, "out": {"offset": off, "coef": coef}}
+    return {"variant": "pointwise_indexed", "inputs": [src["buffer"] for src in ordered if "buffer" in src], "outputs": [out_name],
+            "params": {"n": n, "program": {k: v for k, v in prog.items() if k != "inputs"}, "index_map": index_map}}
+
+
 def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
+    try:
+        return _match_streaming(graph, kernel, launch, int_div)
+    except Unmatched as first:
+        # not element i of every buffer (or a broadcast of it): Loads and the Write may still be affine in the axis variables
+        try:
+            return match_indexed(graph, kernel, launch, int_div)
+        except (Unmatched, OpError):
+            raise first from None
+
+
+def _match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
     tensors = tensor_table(graph)
     tiles = [s for s in kernel.body if _kind(s) == "Tile"]
     if len(kernel.body) != 1 or len(tiles) != 1:

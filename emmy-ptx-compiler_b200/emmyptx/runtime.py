@@ -32,6 +32,16 @@ class PwStep(ctypes.Structure):
                 ("c", ctypes.c_uint8), ("reserved", ctypes.c_uint8 * 3)]
 
 
+PW_MAX_AXES = 6
+
+
+class PwIndexMap(ctypes.Structure):
+    _fields_ = [("n_axes", ctypes.c_int32), ("reserved", ctypes.c_int32), ("extent", ctypes.c_int64 * PW_MAX_AXES),
+                ("in_kind", ctypes.c_int32 * PW_MAX_INPUTS), ("in_axis", ctypes.c_int32 * PW_MAX_INPUTS),
+                ("in_offset", ctypes.c_int64 * PW_MAX_INPUTS), ("in_coef", (ctypes.c_int64 * PW_MAX_AXES) * PW_MAX_INPUTS),
+                ("out_offset", ctypes.c_int64), ("out_coef", ctypes.c_int64 * PW_MAX_AXES)]
+
+
 class PwProgram(ctypes.Structure):
     _fields_ = [("n_inputs", ctypes.c_int32), ("n_steps", ctypes.c_int32), ("out_slot", ctypes.c_int32),
                 ("out_dtype", ctypes.c_int32), ("in_dtype", ctypes.c_int32 * PW_MAX_INPUTS),
@@ -62,6 +72,9 @@ _SIGNATURES = {
     "emmyb200_pointwise_jit_state": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int64)]),
     "emmyb200_pointwise_program_source": (ctypes.c_int64, [ctypes.POINTER(PwProgram), ctypes.c_int, ctypes.c_char_p, ctypes.c_int64]),
     "emmyb200_pointwise_program_compile": (ctypes.c_int, [ctypes.POINTER(PwProgram), ctypes.c_int, ctypes.POINTER(ctypes.c_int64)]),
+    "emmyb200_pointwise_indexed": (ctypes.c_int, [ctypes.POINTER(PwProgram), ctypes.POINTER(PwIndexMap), ctypes.POINTER(ctypes.c_void_p),
+                                                  ctypes.c_void_p, ctypes.c_void_p]),
+    "emmyb200_pointwise_indexed_compile": (ctypes.c_int, [ctypes.POINTER(PwProgram), ctypes.POINTER(PwIndexMap), ctypes.POINTER(ctypes.c_int64)]),
     "emmyb200_index_gather_i32": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                                  ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                                                  ctypes.c_void_p]),
@@ -192,6 +205,64 @@ def pointwise_program(program: dict, inputs: list, out, stream=None):
     prog = make_program(program)
     check(library().emmyb200_pointwise_program(ctypes.byref(prog), arr, out.data_ptr(), out.numel(), _stream(stream)))
     return out
+
+
+def make_index_map(index_map: dict) -> PwIndexMap:
+    """The C struct for {"extents": [...], "inputs": [{"offset": o, "coef": [...]} | {"axis": a}, ...], "out": {"offset": o,
+    "coef": [...]}}: input k reads element offset + sum coef[a] * digit[a] of its buffer, or is the digit of axis a."""
+    m = PwIndexMap()
+    if not 1 <= len(index_map["extents"]) <= PW_MAX_AXES or len(index_map["inputs"]) > PW_MAX_INPUTS:
+        raise ValueError(f"an index map has 1 to {PW_MAX_AXES} axes and at most {PW_MAX_INPUTS} inputs")
+    m.n_axes = len(index_map["extents"])
+    for a, e in enumerate(index_map["extents"]):
+        m.extent[a] = e
+    for k, src in enumerate(index_map["inputs"]):
+        if "axis" in src:
+            m.in_kind[k], m.in_axis[k] = 1, src["axis"]
+        else:
+            m.in_offset[k] = src["offset"]
+            for a, c in enumerate(src["coef"]):
+                m.in_coef[k][a] = c
+    m.out_offset = index_map["out"]["offset"]
+    for a, c in enumerate(index_map["out"]["coef"]):
+        m.out_coef[a] = c
+    return m
+
+
+def pointwise_indexed(program: dict, index_map: dict, inputs: list, out, stream=None):
+    """One value per cell of a tile with the given axis extents; input k is an element of inputs[k] chosen by an affine
+    map of the cell's axis digits (or a digit itself: inputs[k] is then None), the value is stored through the output
+    map. Index ranges are checked against the tensors here: the C entry point cannot."""
+    import math
+    ext = index_map["extents"]
+    def reach(m):
+        lo = hi = m["offset"]
+        for c, e in zip(m["coef"], ext):
+            lo, hi = lo + min(0, c * (e - 1)), hi + max(0, c * (e - 1))
+        return lo, hi
+    real = [t for t in inputs if t is not None]
+    _need_cuda(out, *real)
+    if math.prod(ext) > 0:
+        for k, src in enumerate(index_map["inputs"]):
+            if "axis" not in src:
+                lo, hi = reach(src)
+                if lo < 0 or hi >= inputs[k].numel():
+                    raise IndexError(f"pointwise_indexed: input {k} is read at elements {lo}..{hi} of {inputs[k].numel()}")
+        lo, hi = reach(index_map["out"])
+        if lo < 0 or hi >= out.numel():
+            raise IndexError(f"pointwise_indexed: the output is written at elements {lo}..{hi} of {out.numel()}")
+    arr = (ctypes.c_void_p * len(inputs))(*[None if t is None else t.data_ptr() for t in inputs])
+    prog, m = make_program(program), make_index_map(index_map)
+    check(library().emmyb200_pointwise_indexed(ctypes.byref(prog), ctypes.byref(m), arr, out.data_ptr(), _stream(stream)))
+    return out
+
+
+def indexed_compile(program: dict, index_map: dict) -> int:
+    """Compile an indexed program's kernel for sm_100a without launching it (works without a GPU)."""
+    prog, m = make_program(program), make_index_map(index_map)
+    n = ctypes.c_int64(0)
+    check(library().emmyb200_pointwise_indexed_compile(ctypes.byref(prog), ctypes.byref(m), ctypes.byref(n)))
+    return n.value
 
 
 def set_pointwise_jit(enabled: bool) -> bool:

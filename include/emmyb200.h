@@ -125,6 +125,33 @@ int emmyb200_pointwise_jit_state(int64_t* kernels_compiled);
 int64_t emmyb200_pointwise_program_source(const emmyb200_pw_program* program, int group, char* text, int64_t capacity);
 int emmyb200_pointwise_program_compile(const emmyb200_pw_program* program, int group, int64_t* code_bytes);
 
+/* The same cell programs with index maps: a one-cell-per-element Tile whose Loads and Write address their buffers by
+ * affine functions of the tile's axis variables -- the reference's data-movement cases (tools/torch_cases/shapes.py:6-19:
+ * transpose, permute, slices, flip, repeat, expand, stack) and masks made from the axis variables themselves (tril:
+ * shapes.py:19). The cell number is split into the digits of the axes (outermost first, last fastest, as
+ * emmyptx/kernel.py:587-626 decodes `gid`); input k is element in_offset[k] + sum_a in_coef[k][a] * digit[a] of its
+ * buffer (in_kind 0), or the value of digit in_axis[k] itself with no buffer behind it (in_kind 1; inputs[k] unused); the
+ * result is stored at out_offset + sum_a out_coef[a] * digit[a]. The program's in_div / in_mod are ignored. Nothing
+ * here can check an index against a buffer's size: the caller does (the facade checks every map's range against the
+ * tensor shapes); a map that reaches a negative element is refused. Always a compiled kernel (see above); without the
+ * run-time compiler the call answers EMMYB200_ERR_UNSUPPORTED. Accesses are scalar: it is as fast as its access
+ * pattern coalesces (a contiguous map streams; a transpose reads with a stride). */
+#define EMMYB200_PW_MAX_AXES 6
+typedef struct {
+    int32_t n_axes, reserved;
+    int64_t extent[EMMYB200_PW_MAX_AXES];
+    int32_t in_kind[EMMYB200_PW_MAX_INPUTS];
+    int32_t in_axis[EMMYB200_PW_MAX_INPUTS];
+    int64_t in_offset[EMMYB200_PW_MAX_INPUTS];
+    int64_t in_coef[EMMYB200_PW_MAX_INPUTS][EMMYB200_PW_MAX_AXES];
+    int64_t out_offset;
+    int64_t out_coef[EMMYB200_PW_MAX_AXES];
+} emmyb200_pw_index_map;
+int emmyb200_pointwise_indexed(const emmyb200_pw_program* program, const emmyb200_pw_index_map* map,
+                               const void* const* inputs, void* out, void* cuda_stream);
+/* Compiles the kernel of an indexed program for sm_100a without launching it (no device needed). */
+int emmyb200_pointwise_indexed_compile(const emmyb200_pw_program* program, const emmyb200_pw_index_map* map, int64_t* code_bytes);
+
 /* The int32 index-math gather
  *     y[i] = (x[(i * mul + add) mod n] div d) xor (i >> shift),   0 <= i < n,
  * i.e. the s32 instruction stream of emmyptx/intmath.py:36-38, :87-117 and

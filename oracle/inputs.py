@@ -58,3 +58,23 @@ def attention_inputs(units: int, seq_q: int, seq_k: int, d: int, dtype: str = "b
         x = np.random.default_rng(seed).standard_normal((units, s, d), dtype=np.float32)
         out.append(torch.from_numpy(x).to(td))
     return tuple(out)
+
+
+def layout_buffers(tensors: dict, arg_order: list) -> dict:
+    """float32 buffers for a data-movement kernel: argument i ~ N(0, 1) seeded with i (tools/run_local.py:86-87); the
+    output starts as zeros (:92-93)."""
+    bufs = {}
+    for i, name in enumerate(arg_order):
+        shape = tensors[name]["shape"]
+        bufs[name] = np.zeros(shape, np.float32) if name == "out" else np.random.default_rng(i).standard_normal(shape).astype(np.float32)
+    return bufs
+
+
+LAYOUT_EXPECTED = {     # what each data-movement case computes, on the buffers of layout_buffers (numpy, exact)
+    "s_transpose": lambda b: b["X"].T, "s_permute": lambda b: b["X"].transpose(2, 0, 1) * np.float32(2), "s_slice": lambda b: b["X"][:, 10:50] * np.float32(2),
+    "s_strided_slice": lambda b: b["X"][::2] + np.float32(1), "s_flip": lambda b: b["X"][:, ::-1], "s_stack": lambda b: np.stack([b["A"], b["B"]]),
+    "s_tril": lambda b: np.tril(b["X"]), "s_repeat": lambda b: np.tile(b["X"], (2, 1)),
+    "s_cat_a": lambda b: np.concatenate([b["A"], np.zeros((32, 48), np.float32)], -1),
+    "s_cat_b": lambda b: np.concatenate([np.zeros((32, 64), np.float32), b["B"]], -1),
+}
+

@@ -52,6 +52,12 @@ for name, info in manifest.items():
         out[f"{name}.o"] = bufs["O"]
         print(name, bufs["O"][0, 0, :4])
         continue
+    if info.get("layout"):
+        bufs = inputs.layout_buffers(info["tensors"], info["launch"]["arg_order"])
+        ptx_interp.run_entry((HERE / f"{name}.ref.ptx").read_text(), bufs, info["launch"]["grid"][0], info["launch"]["block"][0])
+        out[f"{name}.out"] = bufs["out"]
+        print(name, bufs["out"].reshape(-1)[:4])
+        continue
     n = info["tensors"]["x"]["shape"][0]
     if n > 2**20 or (name.startswith("c1") and n > 4096 and False):
         continue

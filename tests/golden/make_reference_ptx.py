@@ -17,6 +17,11 @@ buffer by construction -- the script works the largest element index of every fr
 IR's own index expressions and stops if one is out of range. Ragged cases (clamped rows, zero-filled K tail,
 predicated stores) are only ever executed by the CPU interpreter.
 
+The layout cases (`ir.layout_kernel`: transpose, permute, slices, flip, stack, tril, a concatenation written in two
+kernels; tools/torch_cases/shapes.py:6-19) are one-cell-per-element tiles whose index expressions are affine in the axis
+variables; the facade's matcher checks every index range against the buffers before it accepts such a kernel, and the GPU
+test runs the reference's PTX only for kernels the matcher accepted.
+
 The attention cases are the reference's own three (tools/torch_cases/fused.py:21-22, 31-36; models.py:17-19): fp32
 q, k, v, compiled from the scalar-loop stand-in IR (`ir.attention_scalar_kernel`: one cell per output element, nested
 loops with static trip counts, no barriers). Every buffer index is a bare tile or loop variable whose extent equals
@@ -158,12 +163,19 @@ for name, (units, sq, sk, d, causal, scale) in ATTENTION.items():
     assert_indices_are_axes(graph, kernel)
     CASES[name] = (graph, kernel, launch)
 
+LAYOUT = ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_stack", "s_tril", "s_cat_a", "s_cat_b"]      # shapes.py:6-19
+for name in LAYOUT:
+    graph, kernel, launch = ir.layout_kernel(name, name=name)
+    assert launch["grid"][0] * launch["block"][0] >= 1
+    CASES[name] = (graph, kernel, launch)
+
 for name, (graph, kernel, launch) in CASES.items():
     ptx = compile_kernel(graph, kernel, launch, target="sm_89")
     (HERE / f"{name}.ref.ptx").write_text(ptx)
     manifest[name] = {"entry": kernel.name, "launch": launch, **({"gemm": dict(zip(("m", "n", "k", "dtype", "b_trans", "batch", "device"), GEMMS[name]), out_f32=name in GEMM_OUT,
                                        split_k=GEMM_OUT.get(name, (None, 1))[1])} if name in GEMMS else {}),
                       **({"attention": dict(zip(("units", "seq_q", "seq_k", "d", "causal", "scale"), ATTENTION[name]))} if name in ATTENTION else {}),
+                      **({"layout": True} if name in LAYOUT else {}),
                       "tensors": {t.name: {"shape": [d.as_static() for d in t.shape], "dtype": t.dtype.name}
                                   for n in graph.nodes.values() for t in n.outputs}}
     print(f"{name}: {len(ptx.splitlines())} lines of PTX")

@@ -214,7 +214,7 @@ def test_integer_and_bool_programs_match_the_program_kernel():
 
 def test_broadcast_reads_become_program_inputs_with_an_index_map():
     """A row vector over a matrix (bias, batch-norm statistics), a column vector (outer product): the reads are matched as
-    element (i // div) % mod of the smaller buffer; any other index map is refused."""
+    element (i // div) % mod of the smaller buffer; an index that is affine in the axis variables goes to the indexed kernel."""
     from emmyptx.ir import Assign, Axis, BinaryExpr, Dim, KernelOp, Literal, Load, Op, Tile, Var, Write, _graph, _launch, tensor
     r0, c0 = Axis("r0", Dim(64)), Axis("c0", Dim(96))
 
@@ -227,8 +227,9 @@ def test_broadcast_reads_become_program_inputs_with_an_index_map():
     prog = handle(build([Var("r0")], [64]))["params"]["program"]
     assert (prog["in_div"], prog["in_mod"]) == ([96, 0], [64, 96])
     assert algorithmic_work(handle(build([Var("r0")], [64]))) == (4.0 * (64 + 96 + 64 * 96), "B")
-    with pytest.raises(CompileError):                                        # a reversed read is not a broadcast
-        handle(build([BinaryExpr("-", Literal(63, "int"), Var("r0"))], [64]))
+    h = handle(build([BinaryExpr("-", Literal(63, "int"), Var("r0"))], [64]))            # a reversed read is not a broadcast:
+    assert h["variant"] == "pointwise_indexed"                                         # it is an affine index map
+    assert {"buffer": "A", "offset": 63, "coef": [-1, 0]} in h["params"]["index_map"]["inputs"]
 
 
 def test_relu_epilogue_is_read_from_the_ir_when_no_probed_value_is_negative():
@@ -339,5 +340,34 @@ def test_f32_output_and_split_k_contractions():
     store = next(s for s in k.body[0].body if type(s).__name__ == "RegStore")
     store.atomic = True                                        # red.add needs an f32 buffer
     with pytest.raises(CompileError, match="f32 buffer"):
+        handle((g, k, launch))
+
+
+def test_layout_kernels_become_indexed_programs():
+    """Loads and Writes whose indices are affine in the axis variables (tools/torch_cases/shapes.py:6-19), and masks made of
+    the axis variables themselves: every index is fitted on probe cells and checked against the buffers."""
+    h = handle(ir.layout_kernel("s_transpose"))
+    assert h["variant"] == "pointwise_indexed" and h["inputs"] == ["X"]
+    assert h["params"]["index_map"] == {"extents": [96, 64], "inputs": [{"buffer": "X", "offset": 0, "coef": [1, 96]}], "out": {"offset": 0, "coef": [64, 1]}}
+    assert handle(ir.layout_kernel("s_flip"))["params"]["index_map"]["inputs"][0] == {"buffer": "X", "offset": 127, "coef": [128, -1]}
+    assert handle(ir.layout_kernel("s_slice"))["params"]["index_map"]["inputs"][0] == {"buffer": "X", "offset": 10, "coef": [128, 1]}
+    assert handle(ir.layout_kernel("s_cat_b"))["params"]["index_map"]["out"] == {"offset": 64, "coef": [112, 1]}
+    h = handle(ir.layout_kernel("s_tril"))
+    assert h["params"]["index_map"]["inputs"][1:] == [{"axis": 0}, {"axis": 1}] or h["params"]["index_map"]["inputs"][1:] == [{"axis": 1}, {"axis": 0}]
+    assert [st[0] for st in h["params"]["program"]["steps"]] == ["less_equal", "where"]
+    h = handle(ir.layout_kernel("s_stack"))
+    assert h["inputs"] == ["A", "B"] and {"axis": 0} in h["params"]["index_map"]["inputs"]
+    assert handle(ir.layout_kernel("s_repeat"))["variant"] == "pointwise_program"           # a broadcast: the vectorised kernel
+    with pytest.raises(CompileError):
+        handle(ir.layout_kernel("s_roll"))                                                  # wraps around: not affine
+    g, k, launch = ir.layout_kernel("s_slice")                                              # a slice that leaves its buffer
+    load = next(s for s in k.body[0].body if type(s).__name__ == "Load")
+    load.index[1] = ir.BinaryExpr("+", ir.Var("c0"), ir.Literal(100, "int"))
+    with pytest.raises(CompileError):
+        handle((g, k, launch))
+    g, k, launch = ir.layout_kernel("s_transpose")                                          # two cells writing one element
+    write = next(s for s in k.body[0].body if type(s).__name__ == "Write")
+    write.index = [ir.Var("j0"), ir.Literal(0, "int")]
+    with pytest.raises(CompileError):
         handle((g, k, launch))
 

@@ -44,6 +44,24 @@ def test_streaming_and_gather_handles(cuda, lib):
     assert np.array_equal(yid.cpu().numpy(), reference.c2_reference(xi))
 
 
+def test_indexed_handles(cuda, lib):
+    """Data-movement kernels (tools/torch_cases/shapes.py:6-19): the handle carries the index map, the runner only pointers."""
+    import torch
+    from emmyptx import ir
+    x = torch.randn(64, 64, device=cuda)
+    out = torch.zeros(64, 64, device=cuda)
+    assert launch(lib, handle_text(ir.layout_kernel("s_tril")), [x, out]) == 0
+    assert torch.equal(out, torch.tril(x))
+    a, b = torch.randn(32, 64, device=cuda), torch.randn(32, 64, device=cuda)
+    stacked = torch.zeros(2, 32, 64, device=cuda)
+    assert launch(lib, handle_text(ir.layout_kernel("s_stack")), [a, b, stacked]) == 0
+    assert torch.equal(stacked, torch.stack([a, b]))
+    x = torch.randn(64, 96, device=cuda)
+    t = torch.zeros(96, 64, device=cuda)
+    assert launch(lib, handle_text(ir.layout_kernel("s_transpose")), [x, t]) == 0
+    assert torch.equal(t, x.t().contiguous())
+
+
 def test_scalar_parameters_are_passed_by_value(cuda, lib):
     """out = (x * alpha + y) * 2 with alpha a `.param .f32`-style argument: the same handle, two values."""
     import torch

@@ -1,0 +1,111 @@
+"""Data movement through the indexed elementwise kernel (`emmyb200_pointwise_indexed`): the reference's layout cases
+(tools/torch_cases/shapes.py:6-19) written as one-cell-per-element tiles with index expressions of the axis variables,
+from IR to result through the facade, bit for bit against numpy and against the reference compiler's own PTX for the same
+IR (run on the CPU into the golden vectors, and on this GPU next to ours)."""
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from emmyptx import ir, run_local
+from emmyptx.kernel import compile_kernel
+from oracle import inputs
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+CASES = ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_repeat", "s_stack", "s_tril", "s_cat_a", "s_cat_b"]
+
+
+def _run(case, cuda):
+    import torch
+    g, k, launch = ir.layout_kernel(case, name=case)
+    handle = json.loads(compile_kernel(g, k, launch))
+    tensors = {t.name: {"shape": [d.as_static() for d in t.shape]} for nd in g.nodes.values() for t in nd.outputs}
+    host = inputs.layout_buffers(tensors, launch["arg_order"])
+    dev = {nm: torch.from_numpy(a).to(cuda) for nm, a in host.items()}
+    run_local.init()
+    run_local.launch(handle, dev)
+    torch.cuda.synchronize()
+    return handle, host, dev, launch
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_layout_case_matches_numpy_and_the_reference_kernel(case, cuda):
+    import torch
+    from emmyptx.ptx_driver import PtxModule
+    handle, host, dev, launch = _run(case, cuda)
+    assert handle["variant"] == ("pointwise_program" if case == "s_repeat" else "pointwise_indexed")
+    want = np.ascontiguousarray(inputs.LAYOUT_EXPECTED[case](host)).astype(np.float32)
+    got = dev["out"].cpu().numpy()
+    assert np.array_equal(got, want)
+    if not (GOLDEN / f"{case}.ref.ptx").exists():
+        return
+    # the reference's PTX for the same IR: on the CPU (golden vector) and on this GPU, same buffers
+    assert np.array_equal(np.load(GOLDEN / "golden.npz")[f"{case}.out"], want)
+    theirs = torch.zeros_like(dev["out"])
+    ptrs = [dev[nm].data_ptr() if nm != "out" else theirs.data_ptr() for nm in launch["arg_order"]]
+    with PtxModule((GOLDEN / f"{case}.ref.ptx").read_text()) as m:
+        m.launch(m.function(case), ptrs, launch["grid"][0], launch["block"][0])
+        m.synchronize()
+    assert torch.equal(theirs, dev["out"])
+
+
+def test_concatenation_in_two_kernels(cuda):
+    """torch.cat([a, b], -1) (shapes.py:13) as two kernels over one output, each writing its slice through an output map."""
+    import torch
+    out = torch.zeros(32, 112, device=cuda)
+    host = {}
+    for case in ("s_cat_a", "s_cat_b"):
+        g, k, launch = ir.layout_kernel(case)
+        handle = json.loads(compile_kernel(g, k, launch))
+        tensors = {t.name: {"shape": [d.as_static() for d in t.shape]} for nd in g.nodes.values() for t in nd.outputs}
+        h = inputs.layout_buffers(tensors, launch["arg_order"])
+        src = launch["arg_order"][0]
+        host[src] = h[src]
+        run_local.launch(handle, {src: torch.from_numpy(h[src]).to(cuda), "out": out})
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), np.concatenate([host["A"], host["B"]], -1))
+
+
+def test_indexed_programs_directly(cuda):
+    """Other dtypes, negative strides, an integer program with an axis digit as a value, index ranges checked."""
+    import torch
+    from emmyptx import runtime as rt
+    S = rt.PW_MAX_SLOTS
+    x = torch.randn(40, 24, device=cuda).to(torch.bfloat16)
+    out = torch.zeros(24, 40, dtype=torch.float16, device=cuda)
+    prog = {"in_dtypes": ["bf16"], "out_dtype": "f16", "out_slot": 4, "consts": [0.5], "steps": [["multiply", 4, 0, S, 0]]}
+    imap = {"extents": [24, 40], "inputs": [{"offset": 39 * 24, "coef": [1, -24]}], "out": {"offset": 0, "coef": [40, 1]}}   # transpose + flip
+    rt.pointwise_indexed(prog, imap, [x.reshape(-1)], out.reshape(-1))
+    want = (x.float().flip(0).t() * 0.5).to(torch.float16)
+    assert torch.equal(out, want)
+    a = torch.arange(4 * 5 * 6, dtype=torch.int32, device=cuda)
+    oi = torch.zeros(4 * 5 * 6, dtype=torch.int64, device=cuda)
+    progi = {"in_dtypes": ["i32", "i32"], "out_dtype": "i64", "out_slot": 4, "consts": [100], "steps": [["multiply", 4, 1, S, 0], ["add", 4, 4, 0, 0]]}
+    imapi = {"extents": [4, 5, 6], "inputs": [{"offset": 119, "coef": [-30, -6, -1]}, {"axis": 1}], "out": {"offset": 0, "coef": [30, 6, 1]}}
+    rt.pointwise_indexed(progi, imapi, [a, None], oi)
+    i = np.arange(120)
+    assert np.array_equal(oi.cpu().numpy(), (119 - i) + 100 * ((i // 6) % 5))
+    with pytest.raises(IndexError, match="input 0"):
+        rt.pointwise_indexed(prog, dict(imap, inputs=[{"offset": 39 * 24 + 1, "coef": [1, -24]}]), [x.reshape(-1)], out.reshape(-1))
+    with pytest.raises(IndexError, match="output"):
+        rt.pointwise_indexed(prog, dict(imap, out={"offset": 1, "coef": [40, 1]}), [x.reshape(-1)], out.reshape(-1))
+    m = rt.make_index_map(dict(imap, inputs=[{"offset": 0, "coef": [1, -24]}]))           # reaches a negative element: refused by the C entry too
+    arr = (__import__("ctypes").c_void_p * 1)(x.data_ptr())
+    p = rt.make_program(prog)
+    import ctypes
+    assert rt.library().emmyb200_pointwise_indexed(ctypes.byref(p), ctypes.byref(m), arr, out.data_ptr(), None) == -2
+    assert rt.device_status() == 0
+
+
+def test_large_transpose(cuda):
+    """A transpose well beyond the reference's case: 4096 x 2048 floats, against torch."""
+    import torch
+    from emmyptx import runtime as rt
+    x = torch.randn(4096, 2048, device=cuda)
+    out = torch.empty(2048, 4096, device=cuda)
+    prog = {"in_dtypes": ["f32"], "out_dtype": "f32", "out_slot": 0, "consts": [], "steps": []}
+    rt.pointwise_indexed(prog, {"extents": [2048, 4096], "inputs": [{"offset": 0, "coef": [1, 2048]}], "out": {"offset": 0, "coef": [4096, 1]}},
+                         [x.reshape(-1)], out.reshape(-1))
+    assert torch.equal(out, x.t().contiguous())

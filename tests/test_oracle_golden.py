@@ -168,3 +168,12 @@ def test_f32_output_gemm_fixture(golden, case):
     scale = (a.double().abs() @ b.double().abs()).numpy() * 2.0 ** -21
     assert np.all(np.abs(golden[f"{case}.c32"].astype(np.float64) - ref) <= scale)
 
+
+@pytest.mark.parametrize("case", ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_stack", "s_tril", "s_cat_a", "s_cat_b"])
+def test_layout_fixture_is_what_numpy_computes(golden, case):
+    """The reference's PTX for the data-movement kernels, executed on the CPU, moves exactly the elements the torch
+    expression of the case moves (tools/torch_cases/shapes.py:6-19)."""
+    info = json.loads((GOLDEN / "reference_ptx_manifest.json").read_text())[case]
+    bufs = inputs.layout_buffers(info["tensors"], info["launch"]["arg_order"])
+    assert np.array_equal(golden[f"{case}.out"], np.ascontiguousarray(inputs.LAYOUT_EXPECTED[case](bufs)).astype(np.float32))
+

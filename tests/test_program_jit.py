@@ -61,3 +61,16 @@ def test_integer_programs_are_compiled_too(lib):
         steps = [[op, 4 + (i % 8), 4 + ((i + 7) % 8) if i else 0, 1, 0] for i, op in enumerate(names)]
         for group in (4, 0):
             assert rt.program_compile({"in_dtypes": ["i32", "i64"], "out_dtype": "i32", "out_slot": steps[-1][1], "consts": [2], "steps": steps}, group) > 1000
+
+
+def test_indexed_programs_compile_for_sm100a(lib):
+    if rt.pointwise_jit_state()[0] != 1:
+        pytest.skip("libnvrtc is not installed here")
+    prog = {"in_dtypes": ["f32", "f32", "f32"], "out_dtype": "bf16", "out_slot": 5, "consts": [0.0], "steps": [["less_equal", 4, 2, 1, 0], ["where", 5, 4, 0, S]]}
+    imap = {"extents": [64, 64], "inputs": [{"offset": 0, "coef": [64, 1]}, {"axis": 0}, {"axis": 1}], "out": {"offset": 0, "coef": [64, 1]}}
+    assert rt.indexed_compile(prog, imap) > 1000
+    progi = {"in_dtypes": ["i32", "i64"], "out_dtype": "i64", "out_slot": 4, "consts": [3], "steps": [["add", 4, 0, 1, 0]]}
+    assert rt.indexed_compile(progi, {"extents": [4, 5, 6], "inputs": [{"offset": 119, "coef": [-30, -6, -1]}, {"axis": 2}], "out": {"offset": 0, "coef": [30, 6, 1]}}) > 1000
+    with pytest.raises(ValueError):
+        rt.indexed_compile(prog, dict(imap, extents=[2] * 7, out={"offset": 0, "coef": [1] * 7}, inputs=[{"offset": 0, "coef": [1] * 7}, {"axis": 0}, {"axis": 1}]))
+
