@@ -635,7 +635,8 @@ def layout_kernel(case: str, name: str | None = None):
     """The reference's data-movement cases (tools/torch_cases/shapes.py:6-19) as one-cell-per-element tiles whose Loads and
     Write index their buffers with expressions of the axis variables -- what a tracer hands over for a transpose, a
     slice or a flip -- plus masks made of the axis variables themselves (tril) and a concatenation written slice by
-    slice (`s_cat_a`, `s_cat_b`: two kernels over one output). Returns (graph, kernel, launch)."""
+    slice (`s_cat_a`, `s_cat_b`: two kernels over one output), and the two pooling cases of tools/torch_cases/conv.py:8-9 with
+    their windows spelled out as shifted loads. Returns (graph, kernel, launch)."""
     lit = lambda v: Literal(int(v), "int")
     add = lambda a, b: BinaryExpr("+", a, b)
     mul = lambda a, b: BinaryExpr("*", a, b)
@@ -664,6 +665,16 @@ def layout_kernel(case: str, name: str | None = None):
         "s_cat_a": ([A("r0", 32), A("c0", 64)], {"A": [32, 64]}, [("a", "A", [Var("r0"), Var("c0")])], [], [32, 112], [Var("r0"), Var("c0")], "a"),
         "s_cat_b": ([A("r0", 32), A("c0", 48)], {"B": [32, 48]}, [("b", "B", [Var("r0"), Var("c0")])], [], [32, 112],
                     [Var("r0"), add(Var("c0"), lit(64))], "b"),
+        # pooling windows spelled out (tools/torch_cases/conv.py:8-9): a handful of shifted loads folded by the Assign chain
+        "c_avg_pool1d": ([A("c0", 16), A("i0", 32)], {"X": [16, 128]},
+                         [(f"x{t}", "X", [Var("c0"), add(mul(Var("i0"), lit(4)), lit(t))]) for t in range(4)],
+                         [Assign("s0_", Op("add"), ["x0", "x1"]), Assign("s1_", Op("add"), ["x2", "x3"]), Assign("s2_", Op("add"), ["s0_", "s1_"]),
+                          Assign("y", Op("multiply"), ["s2_", 0.25])], [16, 32], [Var("c0"), Var("i0")], "y"),
+        "c_max_pool2d": ([A("c0", 8), A("i0", 16), A("j0", 16)], {"X": [8, 32, 32]},
+                         [(f"x{di}{dj}", "X", [Var("c0"), add(mul(Var("i0"), lit(2)), lit(di)), add(mul(Var("j0"), lit(2)), lit(dj))])
+                          for di in range(2) for dj in range(2)],
+                         [Assign("m0_", Op("maximum"), ["x00", "x01"]), Assign("m1_", Op("maximum"), ["x10", "x11"]),
+                          Assign("y", Op("maximum"), ["m0_", "m1_"])], [8, 16, 16], [Var("c0"), Var("i0"), Var("j0")], "y"),
         # refused on purpose: a rotation wraps around (the index is not affine in the axis variables)
         "s_roll": ([A("r0", 64), A("c0", 128)], {"X": [64, 128]}, [("x", "X", [Var("r0"), BinaryExpr("%", add(Var("c0"), lit(125)), lit(128))])], [],
                    [64, 128], [Var("r0"), Var("c0")], "x"),

@@ -74,6 +74,8 @@ LAYOUT_EXPECTED = {     # what each data-movement case computes, on the buffers 
     "s_transpose": lambda b: b["X"].T, "s_permute": lambda b: b["X"].transpose(2, 0, 1) * np.float32(2), "s_slice": lambda b: b["X"][:, 10:50] * np.float32(2),
     "s_strided_slice": lambda b: b["X"][::2] + np.float32(1), "s_flip": lambda b: b["X"][:, ::-1], "s_stack": lambda b: np.stack([b["A"], b["B"]]),
     "s_tril": lambda b: np.tril(b["X"]), "s_repeat": lambda b: np.tile(b["X"], (2, 1)),
+    "c_avg_pool1d": lambda b: ((b["X"][:, 0::4] + b["X"][:, 1::4]) + (b["X"][:, 2::4] + b["X"][:, 3::4])) * np.float32(0.25),
+    "c_max_pool2d": lambda b: b["X"].reshape(8, 16, 2, 16, 2).max(axis=(2, 4)),
     "s_cat_a": lambda b: np.concatenate([b["A"], np.zeros((32, 48), np.float32)], -1),
     "s_cat_b": lambda b: np.concatenate([np.zeros((32, 64), np.float32), b["B"]], -1),
 }

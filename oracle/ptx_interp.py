@@ -244,13 +244,15 @@ class Interpreter:
         elif name == "ld" and parts[1] == "global":
             buf, off = self._mem(ops[1])
             dt = np.float32 if ty == "f32" else (np.uint16 if ty == "b16" else np.int32)
-            out = np.zeros(self.n, dt)
+            dsts = [t.strip() for t in ops[0].strip("{}").split(",")]        # one register, or the members of a .v2 / .v4
             m = self.active if mask is None else self.active & mask
-            for b in np.unique(buf[m]):
-                sel = m & (buf == b)
-                arr = self.bufs[int(b)].reshape(-1)
-                out[sel] = arr.view(dt)[off[sel] // out.itemsize]
-            self._set(ops[0], out, mask)
+            for j, dst in enumerate(dsts):                                   # (two adjacent f32 loads pair up: emmyptx/kernel.py:517-548)
+                out = np.zeros(self.n, dt)
+                for b in np.unique(buf[m]):
+                    sel = m & (buf == b)
+                    arr = self.bufs[int(b)].reshape(-1)
+                    out[sel] = arr.view(dt)[off[sel] // out.itemsize + j]
+                self._set(dst, out, mask)
         elif name == "st" and parts[1] == "global":
             buf, off = self._mem(ops[0])
             width = 2 if ty == "b16" else 4

@@ -163,7 +163,8 @@ for name, (units, sq, sk, d, causal, scale) in ATTENTION.items():
     assert_indices_are_axes(graph, kernel)
     CASES[name] = (graph, kernel, launch)
 
-LAYOUT = ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_stack", "s_tril", "s_cat_a", "s_cat_b"]      # shapes.py:6-19
+LAYOUT = ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_stack", "s_tril", "s_cat_a", "s_cat_b",      # shapes.py:6-19
+          "c_avg_pool1d", "c_max_pool2d"]                                                                              # conv.py:8-9
 for name in LAYOUT:
     graph, kernel, launch = ir.layout_kernel(name, name=name)
     assert launch["grid"][0] * launch["block"][0] >= 1

@@ -14,7 +14,8 @@ from oracle import inputs
 
 pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden"
-CASES = ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_repeat", "s_stack", "s_tril", "s_cat_a", "s_cat_b"]
+CASES = ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_repeat", "s_stack", "s_tril", "s_cat_a", "s_cat_b",
+         "c_avg_pool1d", "c_max_pool2d"]
 
 
 def _run(case, cuda):

@@ -169,7 +169,8 @@ def test_f32_output_gemm_fixture(golden, case):
     assert np.all(np.abs(golden[f"{case}.c32"].astype(np.float64) - ref) <= scale)
 
 
-@pytest.mark.parametrize("case", ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_stack", "s_tril", "s_cat_a", "s_cat_b"])
+@pytest.mark.parametrize("case", ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_stack", "s_tril", "s_cat_a", "s_cat_b",
+                                  "c_avg_pool1d", "c_max_pool2d"])
 def test_layout_fixture_is_what_numpy_computes(golden, case):
     """The reference's PTX for the data-movement kernels, executed on the CPU, moves exactly the elements the torch
     expression of the case moves (tools/torch_cases/shapes.py:6-19)."""
