@@ -60,6 +60,10 @@ def test_indexed_handles(cuda, lib):
     t = torch.zeros(96, 64, device=cuda)
     assert launch(lib, handle_text(ir.layout_kernel("s_transpose")), [x, t]) == 0
     assert torch.equal(t, x.t().contiguous())
+    x = torch.randn(64, 128, device=cuda)                               # a negative coefficient in the handle's map
+    f = torch.zeros(64, 128, device=cuda)
+    assert launch(lib, handle_text(ir.layout_kernel("s_flip")), [x, f]) == 0
+    assert torch.equal(f, x.flip(-1))
 
 
 def test_scalar_parameters_are_passed_by_value(cuda, lib):
