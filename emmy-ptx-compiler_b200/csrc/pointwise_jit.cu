@@ -279,8 +279,7 @@ __device__ __forceinline__ unsigned pw_pack2(float lo, float hi) {      // two v
 #endif
     return w;
 }
-__device__ __forceinline__ void pw_out(void* p, i64 g, i64 n, const PwVec& y) {
-#if PW_VEC
+__device__ __forceinline__ void pw_stv(void* p, i64 g, const PwVec& y) {       // group g of PW_G elements, aligned
 #if PW_OUT_DT == 0
 #pragma unroll
     for (int q = 0; q < PW_G / 4; ++q)
@@ -290,6 +289,10 @@ __device__ __forceinline__ void pw_out(void* p, i64 g, i64 n, const PwVec& y) {
 #else
     __stcs(reinterpret_cast<uint4*>(p) + g, make_uint4(pw_pack2(y.v[0], y.v[1]), pw_pack2(y.v[2], y.v[3]), pw_pack2(y.v[4], y.v[5]), pw_pack2(y.v[6], y.v[7])));
 #endif
+}
+__device__ __forceinline__ void pw_out(void* p, i64 g, i64 n, const PwVec& y) {
+#if PW_VEC
+    pw_stv(p, g, y);
 #else
     const i64 i = g * PW_G;
 #pragma unroll
@@ -329,14 +332,17 @@ __device__ __forceinline__ void pw_st1(void* p, i64 i, int v) {
     reinterpret_cast<long long*>(p)[i] = (long long)v;
 #endif
 }
-__device__ __forceinline__ void pw_out(void* p, i64 g, i64 n, const PwVec& y) {
-#if PW_VEC
+__device__ __forceinline__ void pw_stv(void* p, i64 g, const PwVec& y) {
 #if PW_OUT_DT == 3
     __stcs(reinterpret_cast<int4*>(p) + g, make_int4(y.v[0], y.v[1], y.v[2], y.v[3]));
 #else
     __stcs(reinterpret_cast<longlong2*>(p) + g * 2, make_longlong2((long long)y.v[0], (long long)y.v[1]));
     __stcs(reinterpret_cast<longlong2*>(p) + g * 2 + 1, make_longlong2((long long)y.v[2], (long long)y.v[3]));
 #endif
+}
+__device__ __forceinline__ void pw_out(void* p, i64 g, i64 n, const PwVec& y) {
+#if PW_VEC
+    pw_stv(p, g, y);
 #else
     const i64 i = g * PW_G;
 #pragma unroll
@@ -484,13 +490,148 @@ template <typename I> __device__ __forceinline__ void pw_ix_cell(const void* p0,
 #endif
     pw_st1(out, (i64)to, pw_cell(v0, v1, v2, v3, c));
 }
+// Four consecutive cells of the innermost axis per thread and trip (PW_INNER 4: the axis' extent is a multiple of 4): the
+// digits are worked out once per group, and an input (PW_IVECk) or the output (PW_OVEC) whose map advances by one
+// element per cell from a 4-aligned start is moved with one vector access.
+#if PW_INNER == 4
+template <int DT, int VEC, int KIND> __device__ __forceinline__ PwVec pw_ix_in(const void* p, i64 at, i64 step, int axis_is_last, PW_T digit) {
+    PwVec r;
+    if (KIND) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) r.v[j] = digit + (PW_T)(axis_is_last ? j : 0);
+        return r;
+    }
+    if (VEC) return pw_ldv<DT>(p, at >> 2);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) r.v[j] = pw_ld1<DT>(p, at + j * step);
+    return r;
+}
+template <typename I> __device__ __forceinline__ void pw_ix_group(const void* p0, const void* p1, const void* p2, const void* p3, void* out, I gi,
+                                                                const PwConsts& c, const PwIndexArg& m) {
+    I d[PW_NAXES > 0 ? PW_NAXES : 1];
+    I rem = gi;
+#pragma unroll
+    for (int a = PW_NAXES - 1; a >= 0; --a) {
+        const I e = a == PW_NAXES - 1 ? (I)(m.extent[a] >> 2) : (I)m.extent[a];
+        const I q = rem / e;
+        d[a] = rem - q * e;
+        rem = q;
+    }
+    d[PW_NAXES - 1] *= 4;
+    I at[4], to = (I)m.out_offset;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) at[k] = (I)m.in_offset[k];
+#pragma unroll
+    for (int a = 0; a < PW_NAXES; ++a) {
+#pragma unroll
+        for (int k = 0; k < PW_N_IN; ++k) at[k] += (I)m.in_coef[k][a] * d[a];
+        to += (I)m.out_coef[a] * d[a];
+    }
+    PwVec v0, v1, v2, v3;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v0.v[j] = v1.v[j] = v2.v[j] = v3.v[j] = (PW_T)0;
+    v0 = pw_ix_in<PW_DT0, PW_IVEC0, PW_KIND0>(p0, (i64)at[0], m.in_coef[0][PW_NAXES - 1], m.in_axis[0] == PW_NAXES - 1, (PW_T)d[m.in_axis[0]]);
+#if PW_N_IN > 1
+    v1 = pw_ix_in<PW_DT1, PW_IVEC1, PW_KIND1>(p1, (i64)at[1], m.in_coef[1][PW_NAXES - 1], m.in_axis[1] == PW_NAXES - 1, (PW_T)d[m.in_axis[1]]);
+#endif
+#if PW_N_IN > 2
+    v2 = pw_ix_in<PW_DT2, PW_IVEC2, PW_KIND2>(p2, (i64)at[2], m.in_coef[2][PW_NAXES - 1], m.in_axis[2] == PW_NAXES - 1, (PW_T)d[m.in_axis[2]]);
+#endif
+#if PW_N_IN > 3
+    v3 = pw_ix_in<PW_DT3, PW_IVEC3, PW_KIND3>(p3, (i64)at[3], m.in_coef[3][PW_NAXES - 1], m.in_axis[3] == PW_NAXES - 1, (PW_T)d[m.in_axis[3]]);
+#endif
+    PwVec y;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) y.v[j] = pw_cell(v0.v[j], v1.v[j], v2.v[j], v3.v[j], c);
+#if PW_OVEC
+    pw_stv(out, (i64)to >> 2, y);
+#else
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pw_st1(out, (i64)to + j * m.out_coef[PW_NAXES - 1], y.v[j]);
+#endif
+}
+#endif
+// A transposition between the innermost axis and axis PW_TAXIS (PW_TRANSPOSE 1): the one buffer input is contiguous along
+// PW_TAXIS, the output along the innermost axis. A CTA moves 32 x 32 tiles of those two axes through shared memory (rows
+// padded by one word), reading with the lanes along PW_TAXIS and writing with the lanes along the innermost axis, so
+// both sides are coalesced; the other axes count tiles. PW_TIN is the index of the buffer input among the inputs.
+#if PW_TRANSPOSE
+template <typename I> __device__ __forceinline__ void pw_ix_tiles(const void* p0, const void* p1, const void* p2, const void* p3, void* out,
+                                                                const PwConsts& c, const PwIndexArg& m, PW_T (*tile)[33]) {
+    const void* src = PW_TIN == 0 ? p0 : (PW_TIN == 1 ? p1 : (PW_TIN == 2 ? p2 : p3));
+    const I et = (I)m.extent[PW_TAXIS], el = (I)m.extent[PW_NAXES - 1];
+    const I tiles_t = (et + 31) / 32, tiles_l = (el + 31) / 32;
+    I batch = 1;
+#pragma unroll
+    for (int a = 0; a < PW_NAXES - 1; ++a)
+        if (a != PW_TAXIS) batch *= (I)m.extent[a];
+    const i64 work = (i64)batch * tiles_t * tiles_l;
+    const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+    for (i64 w = blockIdx.x; w < work; w += gridDim.x) {
+        I rem = (I)w;
+        const I tl = rem % tiles_l; rem /= tiles_l;
+        const I tt = rem % tiles_t; rem /= tiles_t;
+        I d[PW_NAXES > 0 ? PW_NAXES : 1];
+#pragma unroll
+        for (int a = PW_NAXES - 2; a >= 0; --a) {
+            if (a == PW_TAXIS) { d[a] = 0; continue; }
+            const I e = (I)m.extent[a];
+            const I q = rem / e;
+            d[a] = rem - q * e;
+            rem = q;
+        }
+        d[PW_NAXES - 1] = 0;
+        I at = (I)m.in_offset[PW_TIN], to = (I)m.out_offset;
+#pragma unroll
+        for (int a = 0; a < PW_NAXES; ++a) {
+            at += (I)m.in_coef[PW_TIN][a] * d[a];
+            to += (I)m.out_coef[a] * d[a];
+        }
+        const I t0 = tt * 32, l0 = tl * 32;
+        __syncthreads();                                        // the previous tile has been read out
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const I t = t0 + x, l = l0 + y + 8 * r;
+            if (t < et && l < el) tile[y + 8 * r][x] = pw_ld1<PW_TDT>(src, (i64)(at + t + (I)m.in_coef[PW_TIN][PW_NAXES - 1] * l));
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const I l = l0 + x, t = t0 + y + 8 * r;
+            if (t < et && l < el) {
+                d[PW_TAXIS] = t;
+                d[PW_NAXES - 1] = l;
+                const PW_T v = tile[x][y + 8 * r];
+                const PW_T v0 = PW_KIND0 ? (PW_T)d[m.in_axis[0]] : v;
+                const PW_T v1 = PW_N_IN > 1 ? (PW_KIND1 ? (PW_T)d[m.in_axis[1]] : v) : (PW_T)0;
+                const PW_T v2 = PW_N_IN > 2 ? (PW_KIND2 ? (PW_T)d[m.in_axis[2]] : v) : (PW_T)0;
+                const PW_T v3 = PW_N_IN > 3 ? (PW_KIND3 ? (PW_T)d[m.in_axis[3]] : v) : (PW_T)0;
+                pw_st1(out, (i64)(to + (I)m.out_coef[PW_TAXIS] * t + l), pw_cell(v0, v1, v2, v3, c));
+            }
+        }
+    }
+}
+#endif
 extern "C" __global__ void __launch_bounds__(256) pw_ix_kernel(const void* p0, const void* p1, const void* p2, const void* p3, void* out, i64 n,
                                                                PwConsts c, PwIndexArg m) {
+#if PW_TRANSPOSE
+    __shared__ PW_T tile[32][33];
+    if (m.narrow) pw_ix_tiles<int>(p0, p1, p2, p3, out, c, m, tile);
+    else pw_ix_tiles<i64>(p0, p1, p2, p3, out, c, m, tile);
+    return;
+#endif
     const i64 stride = (i64)gridDim.x * 256;
+#if PW_INNER == 4
+    for (i64 g = (i64)blockIdx.x * 256 + threadIdx.x; g < (n >> 2); g += stride) {
+        if (m.narrow) pw_ix_group<int>(p0, p1, p2, p3, out, (int)g, c, m);
+        else pw_ix_group<i64>(p0, p1, p2, p3, out, g, c, m);
+    }
+#else
     for (i64 i = (i64)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
         if (m.narrow) pw_ix_cell<int>(p0, p1, p2, p3, out, (int)i, c, m);
         else pw_ix_cell<i64>(p0, p1, p2, p3, out, i, c, m);
     }
+#endif
 }
 )SHELL";
 
@@ -507,7 +648,16 @@ static int broadcast_mode(const emmyb200_pw_program& p, int k, int group, bool b
     return (group != 0 && base_aligned && p.in_div[k] == 0 && p.in_mod[k] % per == 0) ? 2 : 1;
 }
 
-static std::string program_source(const emmyb200_pw_program& p, int group, const int* modes, const emmyb200_pw_index_map* map = nullptr) {
+struct IndexedForm {        // how the indexed kernel walks the tile (chosen on the host from extents, maps and alignment)
+    int inner = 1;          // cells of the innermost axis per thread: 1 or 4
+    int ivec[EMMYB200_PW_MAX_INPUTS] = {0, 0, 0, 0};      // input k is read with one vector access per group
+    int ovec = 0;           // the output is written with one vector access per group
+    int transpose = 0;      // 1: 32 x 32 tiles of (taxis, innermost axis) through shared memory
+    int taxis = 0, tin = 0; // the axis the buffer input is contiguous along; which input that is
+};
+
+static std::string program_source(const emmyb200_pw_program& p, int group, const int* modes, const emmyb200_pw_index_map* map = nullptr,
+                                  const IndexedForm* form = nullptr) {
     const bool ints = !float_program(p);
     const char* type = ints ? "int" : "float";
     std::string s;
@@ -523,6 +673,14 @@ static std::string program_source(const emmyb200_pw_program& p, int group, const
     if (map != nullptr) {
         snprintf(line, sizeof line, "#define PW_NAXES %d\n#define PW_KIND0 %d\n#define PW_KIND1 %d\n#define PW_KIND2 %d\n#define PW_KIND3 %d\n", map->n_axes,
                  map->in_kind[0], map->in_kind[1], map->in_kind[2], map->in_kind[3]);
+        s += line;
+        const IndexedForm plain;
+        const IndexedForm& f = form != nullptr ? *form : plain;
+        snprintf(line, sizeof line, "#define PW_INNER %d\n#define PW_IVEC0 %d\n#define PW_IVEC1 %d\n#define PW_IVEC2 %d\n#define PW_IVEC3 %d\n#define PW_OVEC %d\n",
+                 f.inner, f.ivec[0], f.ivec[1], f.ivec[2], f.ivec[3], f.ovec);
+        s += line;
+        snprintf(line, sizeof line, "#define PW_TRANSPOSE %d\n#define PW_TAXIS %d\n#define PW_TIN %d\n#define PW_TDT %d\n", f.transpose, f.taxis, f.tin,
+                 p.in_dtype[f.tin]);
         s += line;
     }
     if (!ints) s += "#include \"emmy_math.cuh\"\n";
@@ -725,6 +883,35 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
     if (!nvrtc().ok) return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_indexed: needs the run-time compiler (libnvrtc.so.12 not found)");
     emmyb200_pw_index_map key_map = *map;
     for (int k = prog->n_inputs; k < EMMYB200_PW_MAX_INPUTS; ++k) key_map.in_kind[k] = 0;
+    // groups of four cells along the innermost axis when its extent allows; vector accesses for the maps that advance by
+    // one element per cell from a start that is 4-aligned in every group (offset and the other coefficients multiples of
+    // 4, the buffer aligned for four elements)
+    IndexedForm form;
+    const int last = map->n_axes - 1;
+    auto elem_size = [](int dt) { return dt == EMMYB200_I64 ? 8 : (dt == EMMYB200_F32 || dt == EMMYB200_I32 ? 4 : (dt == EMMYB200_U8 ? 1 : 2)); };
+    auto vector_ok = [&](int64_t off, const int64_t* coef, const void* base, int dt) {
+        if (coef[last] != 1 || (off & 3) || !aligned(base, (size_t)4 * elem_size(dt))) return false;
+        for (int a = 0; a < last; ++a)
+            if (coef[a] & 3) return false;
+        return true;
+    };
+    // a transposition: one buffer input, contiguous along some other axis than the innermost, the output contiguous along
+    // the innermost axis, both axes long enough for 32 x 32 tiles
+    {
+        int buffers = 0, which = 0;
+        for (int k = 0; k < prog->n_inputs; ++k)
+            if (map->in_kind[k] == 0) { ++buffers; which = k; }
+        if (buffers == 1 && last >= 1 && map->out_coef[last] == 1 && map->in_coef[which][last] != 1 && map->extent[last] >= 32) {
+            for (int a = 0; a < last; ++a)
+                if (map->in_coef[which][a] == 1 && map->extent[a] >= 32) { form.transpose = 1; form.taxis = a; form.tin = which; break; }
+        }
+    }
+    if (!form.transpose && map->extent[last] % 4 == 0) {
+        form.inner = 4;
+        for (int k = 0; k < prog->n_inputs; ++k)
+            form.ivec[k] = map->in_kind[k] == 0 && vector_ok(map->in_offset[k], map->in_coef[k], inputs[k], prog->in_dtype[k]) ? 1 : 0;
+        form.ovec = vector_ok(map->out_offset, map->out_coef, out, prog->out_dtype) ? 1 : 0;
+    }
     JitKernel kern;
     {
         std::lock_guard<std::mutex> lock(g_jit_mutex);
@@ -732,11 +919,16 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
         std::string key = program_key(*prog, 0, modes);
         key.push_back('x');
         key.push_back((char)map->n_axes);
-        for (int k = 0; k < EMMYB200_PW_MAX_INPUTS; ++k) key.push_back((char)key_map.in_kind[k]);
+        for (int k = 0; k < EMMYB200_PW_MAX_INPUTS; ++k) { key.push_back((char)key_map.in_kind[k]); key.push_back((char)form.ivec[k]); }
+        key.push_back((char)form.inner);
+        key.push_back((char)form.ovec);
+        key.push_back((char)form.transpose);
+        key.push_back((char)form.taxis);
+        key.push_back((char)form.tin);
         auto it = jit_cache().find(key);
         if (it == jit_cache().end()) {
             std::vector<char> cubin;
-            rc = compile_source(program_source(*prog, 0, modes, &key_map), &cubin);
+            rc = compile_source(program_source(*prog, 0, modes, &key_map, &form), &cubin);
             if (rc != EMMYB200_OK) return rc;
             cudaError_t e = cudaLibraryLoadData(&kern.library, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
             if (e != cudaSuccess) return cuda_fail(e, "cudaLibraryLoadData (indexed elementwise kernel)");
@@ -766,7 +958,12 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
     m.narrow = narrow ? 1 : 0;
     long long count = n;
     void* args[] = {&p[0], &p[1], &p[2], &p[3], &out, &count, &c, &m};
-    const int64_t want = (n + 255) / 256;
+    int64_t want = (n / form.inner + 255) / 256;
+    if (form.transpose) {
+        want = ((map->extent[form.taxis] + 31) / 32) * ((map->extent[last] + 31) / 32);
+        for (int a = 0; a < last; ++a)
+            if (a != form.taxis) want *= map->extent[a];
+    }
     const int64_t cap = (int64_t)sm_count() * 16;
     const unsigned blocks = (unsigned)(want < cap ? want : cap);
     cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(kern.kernel), dim3(blocks), dim3(256), args, 0, static_cast<cudaStream_t>(cuda_stream));
@@ -784,8 +981,27 @@ extern "C" int emmyb200_pointwise_indexed_compile(const emmyb200_pw_program* pro
     const int modes[EMMYB200_PW_MAX_INPUTS] = {0, 0, 0, 0};
     std::vector<char> cubin;
     rc = compile_source(program_source(*prog, 0, modes, &key_map), &cubin);
-    if (rc == EMMYB200_OK && code_bytes != nullptr) *code_bytes = (int64_t)cubin.size();
-    return rc;
+    if (rc != EMMYB200_OK) return rc;
+    if (map->extent[map->n_axes - 1] % 4 == 0) {          // the grouped form, every buffer taken as vector-accessible
+        IndexedForm form;
+        form.inner = 4;
+        form.ovec = 1;
+        for (int k = 0; k < prog->n_inputs; ++k) form.ivec[k] = key_map.in_kind[k] == 0 ? 1 : 0;
+        std::vector<char> grouped;
+        rc = compile_source(program_source(*prog, 0, modes, &key_map, &form), &grouped);
+        if (rc != EMMYB200_OK) return rc;
+    }
+    if (map->n_axes >= 2) {                               // the tiled transposition, axis 0 against the innermost axis
+        IndexedForm form;
+        form.transpose = 1;
+        for (int k = 0; k < prog->n_inputs; ++k)
+            if (key_map.in_kind[k] == 0) form.tin = k;
+        std::vector<char> tiled;
+        rc = compile_source(program_source(*prog, 0, modes, &key_map, &form), &tiled);
+        if (rc != EMMYB200_OK) return rc;
+    }
+    if (code_bytes != nullptr) *code_bytes = (int64_t)cubin.size();
+    return EMMYB200_OK;
 }
 
 extern "C" int emmyb200_set_pointwise_jit(int enabled) {

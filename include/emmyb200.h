@@ -134,8 +134,10 @@ int emmyb200_pointwise_program_compile(const emmyb200_pw_program* program, int g
  * result is stored at out_offset + sum_a out_coef[a] * digit[a]. The program's in_div / in_mod are ignored. Nothing
  * here can check an index against a buffer's size: the caller does (the facade checks every map's range against the
  * tensor shapes); a map that reaches a negative element is refused. Always a compiled kernel (see above); without the
- * run-time compiler the call answers EMMYB200_ERR_UNSUPPORTED. Accesses are scalar: it is as fast as its access
- * pattern coalesces (a contiguous map streams; a transpose reads with a stride). */
+ * run-time compiler the call answers EMMYB200_ERR_UNSUPPORTED. The kernel takes one of three forms: 32 x 32
+ * shared-memory tiles when the one buffer input is contiguous along another axis than the innermost and the output
+ * along the innermost (a transposition: both sides coalesced); groups of four cells with 128-bit accesses where a map
+ * advances one element per cell from a 4-aligned start (slices, flips, concatenations); one cell per thread otherwise. */
 #define EMMYB200_PW_MAX_AXES 6
 typedef struct {
     int32_t n_axes, reserved;

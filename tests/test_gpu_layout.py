@@ -110,3 +110,30 @@ def test_large_transpose(cuda):
     rt.pointwise_indexed(prog, {"extents": [2048, 4096], "inputs": [{"offset": 0, "coef": [1, 2048]}], "out": {"offset": 0, "coef": [4096, 1]}},
                          [x.reshape(-1)], out.reshape(-1))
     assert torch.equal(out, x.t().contiguous())
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_batched_transposition_through_shared_memory_tiles(dtype, cuda):
+    """out[b, i, j] = x[b, j, i] * (j <= i), ragged 32 x 32 tiles, a batch axis in front, an axis digit as a value: the tiled
+    form of the indexed kernel (one buffer input contiguous along another axis than the innermost)."""
+    import torch
+    from emmyptx import runtime as rt
+    S = rt.PW_MAX_SLOTS
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    b, rows, cols = 3, 70, 45                                   # x: [b, cols, rows] -> out: [b, rows, cols]
+    x = torch.randn(b, cols, rows, device=cuda).to(td)
+    out = torch.full((b, rows, cols), 7.0, device=cuda, dtype=td)
+    prog = {"in_dtypes": [dtype, "f32", "f32"], "out_dtype": dtype, "out_slot": 5, "consts": [0.0],
+            "steps": [["less_equal", 4, 2, 1, 0], ["where", 5, 4, 0, S]]}
+    imap = {"extents": [b, rows, cols], "inputs": [{"offset": 0, "coef": [cols * rows, 1, rows]}, {"axis": 1}, {"axis": 2}],
+            "out": {"offset": 0, "coef": [rows * cols, cols, 1]}}
+    rt.pointwise_indexed(prog, imap, [x.reshape(-1), None, None], out.reshape(-1))
+    i = torch.arange(rows, device=cuda)[:, None]
+    j = torch.arange(cols, device=cuda)[None, :]
+    want = torch.where(j <= i, x.transpose(1, 2), torch.zeros((), device=cuda, dtype=td))
+    assert torch.equal(out, want)
+    # reversed along the transposed axis as well: a negative coefficient on the innermost axis
+    imap["inputs"][0] = {"offset": (cols - 1) * rows, "coef": [cols * rows, 1, -rows]}
+    rt.pointwise_indexed(prog, imap, [x.reshape(-1), None, None], out.reshape(-1))
+    assert torch.equal(out, torch.where(j <= i, x.flip(1).transpose(1, 2), torch.zeros((), device=cuda, dtype=td)))
+
