@@ -53,6 +53,7 @@ WORKLOADS = {
     "c4": "bf16 GEMM + tanh-GELU epilogue M=N=K=16384, fp32 accumulate, bf16 out, M-row shards",
     "c5": "bf16 attention fwd B16 H16 S4096 d128, non-causal, fp32 softmax, (batch x head) shards",
     "causal": "bf16 causal attention fwd, 64 units of S4096 d128 (the two-tiles-per-CTA kernel form; not one of the five configurations)",
+    "transpose": "fp32 transposition of 8192 x 8192 through the indexed elementwise kernel (shared-memory tiles, compiled at first use; not one of the five configurations)",
     "lerp": "fp32 x + 0.3*(y - x) over 2^26 elements, two inputs, through the general elementwise entry point (the program compiled into a kernel of its own at first use; not one of the five configurations)",
     "f32mm": "fp32 matmul M=N=K=4096 with fp32 accuracy (three-way bf16 split on the tensor cores; not one of the five configurations)",
     "softmax": "fp32 softmax over the last axis of [65536, 1024] (the row kernels; not one of the five configurations)",
@@ -545,6 +546,53 @@ class ProgramWorkload(PointwiseWorkload):
                 "rule": "isclose(rtol=1e-6, atol=1e-6) against torch CPU float64 (tools/torch_cases/__init__.py:17)"}
 
 
+class TransposeWorkload(PointwiseWorkload):
+    """x.t().contiguous() (tools/torch_cases/shapes.py:6 `s_transpose`, at 8192 x 8192 instead of 64 x 96) from IR through the
+    facade to the indexed elementwise kernel (shared-memory tiles): 8 bytes per element."""
+
+    def __init__(self, side, rank, world, dev):
+        import json as _json
+        import torch
+        from emmyptx import ir, runtime
+        from emmyptx.kernel import compile_kernel
+        self.rt, self.torch, self.world, self.name, self.side, self.n = runtime, torch, world, "transpose", side, side * side
+        ax = [ir.Axis("i0", ir.Dim(side)), ir.Axis("j0", ir.Dim(side))]
+        body = [ir.Load(["x"], "X", [ir.Var("j0"), ir.Var("i0")]), ir.Write("out", [ir.Var("i0"), ir.Var("j0")], ["x"])]
+        k = ir.KernelOp("k_transpose", [ir.Tile(ax, body)])
+        g = ir._graph(k, [ir.tensor("X", [side, side], "f32")], [ir.tensor("out", [side, side], "f32")])
+        self.handle = _json.loads(compile_kernel(g, k, ir._launch(k, ["X", "out"], side * side)))
+        assert self.handle["variant"] == "pointwise_indexed"
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(rank)
+        self.x = torch.randn(side, side, device=dev, generator=gen)
+        self.y = torch.empty_like(self.x)
+
+    def step(self):
+        p = self.handle["params"]
+        self.rt.pointwise_indexed(p["program"], p["index_map"], [self.x.reshape(-1)], self.y.reshape(-1))
+
+    kernel_only = step
+
+    def work_per_step(self):
+        return 8.0 * self.n * self.world
+
+    def kernel_work_per_launch(self):
+        return 8.0 * self.n
+
+    def e2e_setup(self):
+        self.host = {"x": self.x.cpu().pin_memory(), "y": self.torch.empty_like(self.y, device="cpu").pin_memory()}
+        return self.n * 4, self.n * 4
+
+    def e2e_step(self):
+        self.x.copy_(self.host["x"], non_blocking=True)
+        self.step()
+        self.host["y"].copy_(self.y, non_blocking=True)
+
+    def parity(self):
+        ok = bool(self.torch.equal(self.y, self.x.t().contiguous()))
+        return {"checked_elements": self.n, "worst_ratio": 0.0 if ok else float("inf"), "ok": ok, "rule": "bit-exact against torch's transpose"}
+
+
 class GatherWorkload(PointwiseWorkload):
     dtype = "i32"
 
@@ -710,6 +758,8 @@ def make_workload(name, rank, world, dev, size=None):
         return AttentionWorkload(size or 64, 4096, 128, rank, world, dev, gather=False, causal=True)
     if name == "lerp":
         return ProgramWorkload(size or 2**26, rank, world, dev)
+    if name == "transpose":
+        return TransposeWorkload(size or 8192, rank, world, dev)
     if name == "softmax":
         return RowWorkload("softmax", size or 65536 * 1024, rank, world, dev)
     if name == "f32mm":
@@ -819,6 +869,10 @@ def cpu_reference_step(name: str, threads: int, full: bool = False):
         x, y = torch.randn(2**24, generator=g), torch.randn(2**24, generator=g)
         fn = lambda: torch.lerp(x, y, 0.3)
         return fn, 12.0 * x.numel(), 1e9, "2^24 of 2^26 elements, torch CPU fp32"
+    if name == "transpose":
+        x = torch.randn(4096, 4096, generator=torch.Generator().manual_seed(0))
+        fn = lambda: x.t().contiguous()
+        return fn, 8.0 * x.numel(), 1e9, "4096 x 4096 of 8192 x 8192, torch CPU fp32"
     if name == "f32mm":
         g = torch.Generator().manual_seed(0)
         a, b = torch.randn(4096, 4096, generator=g), torch.randn(4096, 4096, generator=g)
@@ -844,10 +898,10 @@ def time_cpu(fn, budget_s: float = 12.0, min_reps: int = 2) -> float:
     return best
 
 
-METRIC = {"c1": "elementwise_gbs", "c2": "elementwise_gbs", "softmax": "elementwise_gbs", "lerp": "elementwise_gbs", "c5": "attention_tflops",
+METRIC = {"c1": "elementwise_gbs", "c2": "elementwise_gbs", "softmax": "elementwise_gbs", "lerp": "elementwise_gbs", "transpose": "elementwise_gbs", "c5": "attention_tflops",
           "causal": "attention_tflops"}
-DTYPE = {"c1": "f32", "c2": "i32", "c3": "f16", "softmax": "f32", "f32mm": "f32", "lerp": "f32"}
-SCALING = {"c1": "weak", "c2": "weak", "softmax": "weak", "f32mm": "weak", "lerp": "weak", "causal": "weak"}
+DTYPE = {"c1": "f32", "c2": "i32", "c3": "f16", "softmax": "f32", "f32mm": "f32", "lerp": "f32", "transpose": "f32"}
+SCALING = {"c1": "weak", "c2": "weak", "softmax": "weak", "f32mm": "weak", "lerp": "weak", "transpose": "weak", "causal": "weak"}
 
 
 def config_for(workload: str, world: int, size=None) -> dict:
@@ -1119,7 +1173,7 @@ def other_workloads(torch, dist, dev, local_rank, pk, pk_kind, skip: str) -> dic
             out[f"row_{op}_65536x1024"] = {"value": byts / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms": ms,
                                            "frac_of_peak": byts / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "peak_used": f"{pk_kind} copy bandwidth"}
         del x, y
-        for name in ("causal", "lerp"):
+        for name in ("causal", "lerp", "transpose"):
             wl = make_workload(name, 0, 1, dev)
             m = measure(torch, dist, 1, local_rank, wl, 5, 3, pk, pk_kind, None)
             out[name] = {"workload": WORKLOADS[name], "value": m["value"], "unit": wl.unit, "ms": m["ms_per_step"], "roofline": m["roofline"],
