@@ -327,6 +327,17 @@ extern "C" int emmyb200_launch(const char* handle_json, void* const* params, int
             if (coef == nullptr || (int)coef->items.size() != m.n_axes) return fail(EMMYB200_ERR_ARG, "launch: malformed index map");
             m.in_offset[k] = geti(src, "offset");
             for (int ax = 0; ax < m.n_axes; ++ax) m.in_coef[k][ax] = coef->items[ax].as_int();
+            if (const JVal* rot = src.get("rot"))
+                for (int ax = 0; ax < m.n_axes && ax < (int)rot->items.size(); ++ax) m.in_rot[k][ax] = rot->items[ax].as_int();
+            if (src.get("index_mod") != nullptr) {                  // an index source
+                m.in_kind[k] = 3;
+                m.in_index_mod[k] = geti(src, "index_mod");
+                m.in_index_abs[k] = getb(src, "index_abs") ? 1 : 0;
+            } else if (src.get("index_of") != nullptr) {            // addressed through an index source
+                m.in_kind[k] = 2;
+                m.in_index_of[k] = (int)geti(src, "index_of");
+                m.in_index_mult[k] = geti(src, "index_mult");
+            }
             if (next_buffer >= (int)h.get("inputs")->items.size()) return fail(EMMYB200_ERR_ARG, "launch: the index map names more buffers than the handle has inputs");
             ins[k] = a.input(next_buffer++);
         }

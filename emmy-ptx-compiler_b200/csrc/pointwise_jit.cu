@@ -456,7 +456,11 @@ extern "C" __global__ void __launch_bounds__(PW_THREADS) pw_jit_kernel(const voi
 // digit. PW_NAXES and PW_KIND0..3 (0 buffer, 1 digit) are defined in front of it. 32-bit index arithmetic whenever the
 // cell count and every buffer extent fit (the host says so through `narrow`).
 static const char kIndexedKernel[] = R"SHELL(
-struct PwIndexArg { i64 extent[6]; i64 in_offset[4]; i64 in_coef[4][6]; i64 out_offset; i64 out_coef[6]; int in_axis[4]; int narrow; };
+struct PwIndexArg { i64 extent[6]; i64 in_offset[4]; i64 in_coef[4][6]; i64 out_offset; i64 out_coef[6]; int in_axis[4]; int narrow;
+                    int pad; i64 in_rot[4][6]; i64 in_index_mod[4]; i64 in_index_mult[4]; };
+template <int DT> __device__ __forceinline__ i64 pw_ldi(const void* p, i64 i) {       // an index taken from an i32 / i64 buffer
+    return DT == 3 ? (i64)reinterpret_cast<const int*>(p)[i] : (i64)reinterpret_cast<const long long*>(p)[i];
+}
 template <typename I> __device__ __forceinline__ void pw_ix_cell(const void* p0, const void* p1, const void* p2, const void* p3, void* out, I i,
                                                                const PwConsts& c, const PwIndexArg& m) {
     I d[PW_NAXES > 0 ? PW_NAXES : 1];
@@ -473,11 +477,24 @@ template <typename I> __device__ __forceinline__ void pw_ix_cell(const void* p0,
     for (int k = 0; k < 4; ++k) at[k] = (I)m.in_offset[k];
 #pragma unroll
     for (int a = 0; a < PW_NAXES; ++a) {
+#if PW_SPECIAL
+        const I e = (I)m.extent[a];                     // a rotated axis enters input k's map as (digit + rot) mod extent
+#pragma unroll
+        for (int k = 0; k < PW_N_IN; ++k) {
+            I dk = d[a] + (I)m.in_rot[k][a];
+            dk -= dk >= e ? e : (I)0;
+            at[k] += (I)m.in_coef[k][a] * dk;
+        }
+#else
 #pragma unroll
         for (int k = 0; k < PW_N_IN; ++k) at[k] += (I)m.in_coef[k][a] * d[a];
+#endif
         to += (I)m.out_coef[a] * d[a];
     }
     PW_T v0 = (PW_T)0, v1 = (PW_T)0, v2 = (PW_T)0, v3 = (PW_T)0;
+#if PW_SPECIAL
+    PW_GATHER                                           // generated: index sources first, then the buffers they address
+#else
     v0 = PW_KIND0 ? (PW_T)d[m.in_axis[0]] : pw_ld1<PW_DT0>(p0, (i64)at[0]);
 #if PW_N_IN > 1
     v1 = PW_KIND1 ? (PW_T)d[m.in_axis[1]] : pw_ld1<PW_DT1>(p1, (i64)at[1]);
@@ -487,6 +504,7 @@ template <typename I> __device__ __forceinline__ void pw_ix_cell(const void* p0,
 #endif
 #if PW_N_IN > 3
     v3 = PW_KIND3 ? (PW_T)d[m.in_axis[3]] : pw_ld1<PW_DT3>(p3, (i64)at[3]);
+#endif
 #endif
     pw_st1(out, (i64)to, pw_cell(v0, v1, v2, v3, c));
 }
@@ -652,6 +670,7 @@ struct IndexedForm {        // how the indexed kernel walks the tile (chosen on 
     int inner = 1;          // cells of the innermost axis per thread: 1 or 4
     int ivec[EMMYB200_PW_MAX_INPUTS] = {0, 0, 0, 0};      // input k is read with one vector access per group
     int ovec = 0;           // the output is written with one vector access per group
+    int special = 0;        // 1: some map rotates an axis or takes an index from data: the one-cell form with spelled-out loads
     int transpose = 0;      // 1: 32 x 32 tiles of (taxis, innermost axis) through shared memory
     int taxis = 0, tin = 0; // the axis the buffer input is contiguous along; which input that is
 };
@@ -672,7 +691,7 @@ static std::string program_source(const emmyb200_pw_program& p, int group, const
     }
     if (map != nullptr) {
         snprintf(line, sizeof line, "#define PW_NAXES %d\n#define PW_KIND0 %d\n#define PW_KIND1 %d\n#define PW_KIND2 %d\n#define PW_KIND3 %d\n", map->n_axes,
-                 map->in_kind[0], map->in_kind[1], map->in_kind[2], map->in_kind[3]);
+                 map->in_kind[0] == 1, map->in_kind[1] == 1, map->in_kind[2] == 1, map->in_kind[3] == 1);
         s += line;
         const IndexedForm plain;
         const IndexedForm& f = form != nullptr ? *form : plain;
@@ -682,6 +701,29 @@ static std::string program_source(const emmyb200_pw_program& p, int group, const
         snprintf(line, sizeof line, "#define PW_TRANSPOSE %d\n#define PW_TAXIS %d\n#define PW_TIN %d\n#define PW_TDT %d\n", f.transpose, f.taxis, f.tin,
                  p.in_dtype[f.tin]);
         s += line;
+        snprintf(line, sizeof line, "#define PW_SPECIAL %d\n", f.special);
+        s += line;
+        if (f.special) {                        // the loads of the one-cell form, spelled out: index sources, then everything else
+            s += "#define PW_GATHER";
+            for (int pass = 0; pass < 2; ++pass)
+                for (int k = 0; k < p.n_inputs; ++k) {
+                    const int kind = map->in_kind[k];
+                    if ((kind == 3) != (pass == 0)) continue;
+                    const std::string K = std::to_string(k), DT = std::to_string(p.in_dtype[k]);
+                    if (kind == 3) {
+                        s += " i64 x" + K + " = pw_ldi<" + DT + ">(p" + K + ", (i64)at[" + K + "]);";
+                        if (map->in_index_abs[k]) s += " x" + K + " = x" + K + " < 0 ? -x" + K + " : x" + K + ";";
+                        s += " x" + K + " %= m.in_index_mod[" + K + "]; if (x" + K + " < 0) x" + K + " += m.in_index_mod[" + K + "];";
+                    } else if (kind == 2) {
+                        s += " v" + K + " = pw_ld1<" + DT + ">(p" + K + ", (i64)at[" + K + "] + m.in_index_mult[" + K + "] * x" + std::to_string(map->in_index_of[k]) + ");";
+                    } else if (kind == 1) {
+                        s += " v" + K + " = (PW_T)d[m.in_axis[" + K + "]];";
+                    } else {
+                        s += " v" + K + " = pw_ld1<" + DT + ">(p" + K + ", (i64)at[" + K + "]);";
+                    }
+                }
+            s += "\n";
+        }
     }
     if (!ints) s += "#include \"emmy_math.cuh\"\n";
     s += "typedef long long i64;\n"
@@ -815,7 +857,7 @@ int pw_jit_launch(const emmyb200_pw_program& prog, const void* const* inputs, vo
     return EMMYB200_OK;
 }
 
-static int check_program(const emmyb200_pw_program* prog, const char* who) {
+static int check_program(const emmyb200_pw_program* prog, const char* who, const emmyb200_pw_index_map* map = nullptr) {
     if (prog == nullptr) return fail(EMMYB200_ERR_ARG, "%s: null program", who);
     if (prog->n_inputs < 1 || prog->n_inputs > EMMYB200_PW_MAX_INPUTS || prog->n_steps < 0 || prog->n_steps > EMMYB200_PW_MAX_STEPS ||
         prog->out_slot < 0 || prog->out_slot >= EMMYB200_PW_MAX_SLOTS)
@@ -824,7 +866,9 @@ static int check_program(const emmyb200_pw_program* prog, const char* who) {
     if (!float_program(*prog) && !ints) return fail(EMMYB200_ERR_UNSUPPORTED, "%s: output dtype %d", who, prog->out_dtype);
     for (int k = 0; k < prog->n_inputs; ++k) {
         const int d = prog->in_dtype[k];
-        const bool ok = ints ? (d == EMMYB200_I32 || d == EMMYB200_I64) : (d == EMMYB200_F32 || d == EMMYB200_F16 || d == EMMYB200_BF16 || d == EMMYB200_U8);
+        const bool index_source = map != nullptr && map->in_kind[k] == 3;          // read as an integer, never as a program value
+        const bool ok = (ints || index_source) ? (d == EMMYB200_I32 || d == EMMYB200_I64)
+                                               : (d == EMMYB200_F32 || d == EMMYB200_F16 || d == EMMYB200_BF16 || d == EMMYB200_U8);
         if (!ok) return fail(EMMYB200_ERR_UNSUPPORTED, "%s: input %d has dtype %d (%s program)", who, k, d, ints ? "an integer" : "a float");
     }
     for (int i = 0; i < prog->n_steps; ++i) {
@@ -836,16 +880,17 @@ static int check_program(const emmyb200_pw_program* prog, const char* who) {
     return EMMYB200_OK;
 }
 
-struct PwIndexArgHost { long long extent[6]; long long in_offset[4]; long long in_coef[4][6]; long long out_offset; long long out_coef[6]; int in_axis[4]; int narrow; };
+struct PwIndexArgHost { long long extent[6]; long long in_offset[4]; long long in_coef[4][6]; long long out_offset; long long out_coef[6]; int in_axis[4]; int narrow;
+                        int pad; long long in_rot[4][6]; long long in_index_mod[4]; long long in_index_mult[4]; };
 
 }  // namespace emmy
 
 extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const emmyb200_pw_index_map* map, const void* const* inputs, void* out,
                                           void* cuda_stream) {
     using namespace emmy;
-    int rc = check_program(prog, "pointwise_indexed");
-    if (rc != EMMYB200_OK) return rc;
     if (map == nullptr) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: null index map");
+    int rc = check_program(prog, "pointwise_indexed", map);
+    if (rc != EMMYB200_OK) return rc;
     if (map->n_axes < 1 || map->n_axes > EMMYB200_PW_MAX_AXES) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: %d axes (1 to %d)", map->n_axes, EMMYB200_PW_MAX_AXES);
     int64_t n = 1;
     bool narrow = true;
@@ -870,15 +915,36 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
         return EMMYB200_OK;
     };
     if (inputs == nullptr || out == nullptr) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: null buffer");
+    bool special = false;
     for (int k = 0; k < prog->n_inputs; ++k) {
-        if (map->in_kind[k] != 0 && map->in_kind[k] != 1) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: input %d has kind %d", k, map->in_kind[k]);
-        if (map->in_kind[k] == 1) {
+        const int kind = map->in_kind[k];
+        if (kind < 0 || kind > 3) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: input %d has kind %d", k, kind);
+        if (kind == 1) {
             if (map->in_axis[k] < 0 || map->in_axis[k] >= map->n_axes) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: input %d names axis %d", k, map->in_axis[k]);
             continue;
         }
         if (inputs[k] == nullptr) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: null buffer");
         if ((rc = range_ok(map->in_offset[k], map->in_coef[k], "an input map")) != EMMYB200_OK) return rc;
+        for (int a = 0; a < map->n_axes; ++a) {
+            if (map->in_rot[k][a] < 0 || (map->in_rot[k][a] != 0 && map->in_rot[k][a] >= map->extent[a]))
+                return fail(EMMYB200_ERR_ARG, "pointwise_indexed: input %d rotates axis %d by %lld (0 to extent - 1)", k, a, (long long)map->in_rot[k][a]);
+            special = special || map->in_rot[k][a] != 0;
+        }
+        if (kind == 3) {
+            if (map->in_index_mod[k] < 1) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: index source %d needs a modulus (it is what bounds the index)", k);
+            special = true;
+        }
+        if (kind == 2) {
+            const int src = map->in_index_of[k];
+            if (src < 0 || src >= prog->n_inputs || map->in_kind[src] != 3) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: input %d takes its index from input %d, which is no index source", k, src);
+            if (map->in_index_mult[k] < 0) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: negative index multiplier");
+            if (map->in_offset[k] + map->in_index_mult[k] * (map->in_index_mod[src] - 1) > 0x7fffffffLL) narrow = false;
+            special = true;
+        }
     }
+    for (int st = 0; st < prog->n_steps; ++st)
+        for (int o : {prog->steps[st].a, prog->steps[st].b, prog->steps[st].c})
+            if (o < prog->n_inputs && map->in_kind[o] == 3) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: step %d reads index source %d as a value", st, o);
     if ((rc = range_ok(map->out_offset, map->out_coef, "the output map")) != EMMYB200_OK) return rc;
     if (!nvrtc().ok) return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_indexed: needs the run-time compiler (libnvrtc.so.12 not found)");
     emmyb200_pw_index_map key_map = *map;
@@ -900,13 +966,15 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
     {
         int buffers = 0, which = 0;
         for (int k = 0; k < prog->n_inputs; ++k)
-            if (map->in_kind[k] == 0) { ++buffers; which = k; }
+            if (map->in_kind[k] != 1) { ++buffers; which = k; }
         if (buffers == 1 && last >= 1 && map->out_coef[last] == 1 && map->in_coef[which][last] != 1 && map->extent[last] >= 32) {
             for (int a = 0; a < last; ++a)
                 if (map->in_coef[which][a] == 1 && map->extent[a] >= 32) { form.transpose = 1; form.taxis = a; form.tin = which; break; }
         }
     }
-    if (!form.transpose && map->extent[last] % 4 == 0) {
+    form.special = special ? 1 : 0;
+    if (special) form.transpose = 0;
+    if (!special && !form.transpose && map->extent[last] % 4 == 0) {
         form.inner = 4;
         for (int k = 0; k < prog->n_inputs; ++k)
             form.ivec[k] = map->in_kind[k] == 0 && vector_ok(map->in_offset[k], map->in_coef[k], inputs[k], prog->in_dtype[k]) ? 1 : 0;
@@ -925,6 +993,8 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
         key.push_back((char)form.transpose);
         key.push_back((char)form.taxis);
         key.push_back((char)form.tin);
+        key.push_back((char)form.special);
+        for (int k = 0; k < prog->n_inputs; ++k) { key.push_back((char)map->in_index_of[k]); key.push_back((char)(map->in_index_abs[k] != 0)); }
         auto it = jit_cache().find(key);
         if (it == jit_cache().end()) {
             std::vector<char> cubin;
@@ -950,10 +1020,15 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
     }
     m.out_offset = map->out_offset;
     for (int k = 0; k < prog->n_inputs; ++k) {
-        p[k] = map->in_kind[k] == 0 ? inputs[k] : nullptr;
+        p[k] = map->in_kind[k] != 1 ? inputs[k] : nullptr;
         m.in_offset[k] = map->in_offset[k];
         m.in_axis[k] = map->in_kind[k] == 1 ? map->in_axis[k] : 0;
-        for (int a = 0; a < map->n_axes; ++a) m.in_coef[k][a] = map->in_kind[k] == 0 ? map->in_coef[k][a] : 0;
+        for (int a = 0; a < map->n_axes; ++a) {
+            m.in_coef[k][a] = map->in_kind[k] != 1 ? map->in_coef[k][a] : 0;
+            m.in_rot[k][a] = map->in_kind[k] != 1 ? map->in_rot[k][a] : 0;
+        }
+        m.in_index_mod[k] = map->in_index_mod[k];
+        m.in_index_mult[k] = map->in_index_mult[k];
     }
     m.narrow = narrow ? 1 : 0;
     long long count = n;
@@ -973,11 +1048,27 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
 
 extern "C" int emmyb200_pointwise_indexed_compile(const emmyb200_pw_program* prog, const emmyb200_pw_index_map* map, int64_t* code_bytes) {
     using namespace emmy;
-    int rc = check_program(prog, "pointwise_indexed_compile");
-    if (rc != EMMYB200_OK) return rc;
     if (map == nullptr || map->n_axes < 1 || map->n_axes > EMMYB200_PW_MAX_AXES) return fail(EMMYB200_ERR_ARG, "pointwise_indexed_compile: bad index map");
+    int rc = check_program(prog, "pointwise_indexed_compile", map);
+    if (rc != EMMYB200_OK) return rc;
     emmyb200_pw_index_map key_map = *map;
-    for (int k = 0; k < EMMYB200_PW_MAX_INPUTS; ++k) key_map.in_kind[k] = (k < prog->n_inputs && map->in_kind[k] == 1) ? 1 : 0;
+    bool special = false;
+    for (int k = 0; k < EMMYB200_PW_MAX_INPUTS; ++k) {
+        key_map.in_kind[k] = k < prog->n_inputs ? map->in_kind[k] : 0;
+        if (k < prog->n_inputs && (map->in_kind[k] == 2 || map->in_kind[k] == 3)) special = true;
+        if (k < prog->n_inputs && map->in_kind[k] == 2 && (map->in_index_of[k] < 0 || map->in_index_of[k] >= prog->n_inputs || map->in_kind[map->in_index_of[k]] != 3))
+            return fail(EMMYB200_ERR_ARG, "pointwise_indexed_compile: input %d takes its index from no index source", k);
+        for (int a = 0; k < prog->n_inputs && a < map->n_axes; ++a) special = special || map->in_rot[k][a] != 0;
+    }
+    if (special) {
+        IndexedForm form;
+        form.special = 1;
+        const int modes0[EMMYB200_PW_MAX_INPUTS] = {0, 0, 0, 0};
+        std::vector<char> code;
+        rc = compile_source(program_source(*prog, 0, modes0, &key_map, &form), &code);
+        if (rc == EMMYB200_OK && code_bytes != nullptr) *code_bytes = (int64_t)code.size();
+        return rc;
+    }
     const int modes[EMMYB200_PW_MAX_INPUTS] = {0, 0, 0, 0};
     std::vector<char> cubin;
     rc = compile_source(program_source(*prog, 0, modes, &key_map), &cubin);

@@ -675,10 +675,24 @@ def layout_kernel(case: str, name: str | None = None):
                           for di in range(2) for dj in range(2)],
                          [Assign("m0_", Op("maximum"), ["x00", "x01"]), Assign("m1_", Op("maximum"), ["x10", "x11"]),
                           Assign("y", Op("maximum"), ["m0_", "m1_"])], [8, 16, 16], [Var("c0"), Var("i0"), Var("j0")], "y"),
-        # refused on purpose: a rotation wraps around (the index is not affine in the axis variables)
+        # a rotation: the index wraps around along one axis
         "s_roll": ([A("r0", 64), A("c0", 128)], {"X": [64, 128]}, [("x", "X", [Var("r0"), BinaryExpr("%", add(Var("c0"), lit(125)), lit(128))])], [],
                    [64, 128], [Var("r0"), Var("c0")], "x"),
     }
+    if case in ("s_embedding", "s_gather"):
+        # an index read from an integer buffer, made non-negative and reduced (`idx.abs() % n`, shapes.py:20-24), then used as
+        # a coordinate of the second Load
+        emb = case == "s_embedding"
+        axes = [A("i0", 64), A("j0", 32)] if emb else [A("r0", 32), A("k0", 8)]
+        idx_index = [Var("i0")] if emb else [Var("r0"), Var("k0")]
+        src_index = [Var("m"), Var("j0")] if emb else [Var("r0"), Var("m")]
+        body = [Load(["t"], "IDX", idx_index), Assign("a", Op("abs"), ["t"], DType("int")),
+                Assign("m", Op("mod"), ["a", 100 if emb else 64], DType("int")), Load(["v"], "SRC", src_index),
+                Write("out", [Var(axes[0].name), Var(axes[1].name)], ["v"])]
+        kern = KernelOp(name or f"k_{case}", [Tile(axes, body)])
+        g = _graph(kern, [tensor("IDX", [64] if emb else [32, 8], "i64"), tensor("SRC", [100, 32] if emb else [32, 64], "f32")],
+                   [tensor("out", [64, 32] if emb else [32, 8], "f32")])
+        return g, kern, _launch(kern, ["IDX", "SRC", "out"], axes[0].extent.value * axes[1].extent.value)
     axes, ins, loads, assigns, out_shape, out_index, value = cases[case]
     body = [Load([v], buf, idx) for v, buf, idx in loads] + list(assigns) + [Write("out", out_index, [value])]
     kern = KernelOp(name or f"k_{case}", [Tile(axes, body)])

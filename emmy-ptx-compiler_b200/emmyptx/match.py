@@ -353,6 +353,59 @@ def _fit_affine(idx: np.ndarray, digits: list, what: str):
     return off, coef
 
 
+def _fit_rotated(idx: np.ndarray, digits: list, extents: list, what: str):
+    """offset, coefficients and one rotation per axis such that idx = offset + sum coef * ((digit + rot) mod extent) on every
+    probe cell (torch.roll along one or more axes), or Unmatched. Needs the probe cells to hold, for every axis, all cells
+    whose other digits are zero."""
+    coef, rot = [], []
+    for a, (d, e) in enumerate(zip(digits, extents)):
+        line = np.all([dd == 0 for b, dd in enumerate(digits) if b != a], axis=0)
+        order = np.argsort(d[line])
+        if e == 1:
+            coef.append(0), rot.append(0)
+            continue
+        if line.sum() != e:
+            raise Unmatched(f"{what} is not an affine function of the tile's axis variables")
+        values = np.asarray(idx[line][order], np.int64)
+        steps = np.diff(values)
+        vals, counts = np.unique(steps, return_counts=True)
+        c = int(vals[np.argmax(counts)])
+        wraps = np.nonzero(steps != c)[0]
+        if len(wraps) == 0:
+            coef.append(c), rot.append(0)
+        elif len(wraps) == 1 and int(steps[wraps[0]]) == -c * (e - 1):
+            coef.append(c), rot.append(e - 1 - int(wraps[0]))
+        else:
+            raise Unmatched(f"{what} is neither affine nor a rotation along axis {a}")
+    zero = np.all([d == 0 for d in digits], axis=0)
+    off = int(idx[zero][0]) - sum(c * r for c, r in zip(coef, rot))
+    want = off + sum(c * ((d + r) % e) for c, r, d, e in zip(coef, rot, digits, extents))
+    if not np.array_equal(np.asarray(idx, np.int64), np.asarray(want, np.int64)):
+        raise Unmatched(f"{what} is neither affine nor a rotation of the tile's axis variables")
+    return off, coef, rot
+
+
+def _index_chain(tile, name: str):
+    """`name` as (load statement, abs?, modulus): the value of an integer Load, optionally through `abs`, then reduced by a
+    positive literal modulus -- the only form of a data-dependent coordinate that is bounded by construction."""
+    defs = {s.name: s for s in tile.body if _kind(s) == "Assign"}
+    loads = {s.names[0]: s for s in tile.body if _kind(s) == "Load"}
+    st = defs.get(name)
+    if st is None or st.op.name not in ("mod", "remainder") or len(st.args) != 2 or _dtype_name(st.dtype) not in INT_DTYPES:
+        raise Unmatched("a coordinate taken from data must be reduced by a literal modulus")
+    src, mod = st.args
+    if isinstance(mod, bool) or not isinstance(mod, (int, float)) or mod != int(mod) or mod < 1 or not isinstance(src, str):
+        raise Unmatched("a coordinate taken from data must be reduced by a positive literal modulus")
+    use_abs = False
+    if src in defs:
+        if defs[src].op.name != "abs" or _dtype_name(defs[src].dtype) not in INT_DTYPES or not isinstance(defs[src].args[0], str):
+            raise Unmatched("between the integer Load and the modulus only `abs` is understood")
+        use_abs, src = True, defs[src].args[0]
+    if src not in loads:
+        raise Unmatched("a coordinate taken from data starts at a Load")
+    return loads[src], use_abs, int(mod), {name, st.args[0]} if use_abs else {name}
+
+
 def _reach(off: int, coef: list, extents: list):
     lo = hi = off
     for c, e in zip(coef, extents):
@@ -382,8 +435,9 @@ def match_indexed(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
         raise Unmatched("the indexed elementwise kernel runs Load / Assign / Write programs")
     strides = [math.prod(extents[a + 1:]) for a in range(len(extents))]
     rng = np.random.default_rng(0)
+    lines = [np.arange(e) * st for st, e in zip(strides, extents) if 1 < e <= 4096]      # every cell of each axis' line through cell 0
     cells = np.unique(np.concatenate([np.arange(min(n, 64)), rng.integers(0, n, 200), [n - 1],
-                                      [st for st, e in zip(strides, extents) if e > 1]])).astype(np.int64)
+                                      [st for st, e in zip(strides, extents) if e > 1], *lines])).astype(np.int64)
     it = CellInterpreter(tensors, cells, INT_OPS_TRUNC if int_div == "trunc" else INT_OPS)
     digits = [(cells // st) % e for st, e in zip(strides, extents)]
     for nm, d in zip(names, digits):
@@ -403,17 +457,68 @@ def match_indexed(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
         raise Unmatched(f"no indexed variant writes {out_dtype}")
     # the sources of values, in program order: one per Load, one per axis variable an Assign uses as a value
     body, sources, synthetic = [], [], dict(tensors)
+    # Loads whose index uses a value that is not an axis variable: a coordinate taken from data
+    axis_names = set(names)
+    indirect, hidden, index_loads = {}, set(), {}
+    for k, s in enumerate(loads):
+        free = set()
+        for e in s.index:
+            free |= e.free_vars() if hasattr(e, "free_vars") else set()
+        extra = sorted(free - axis_names)
+        if not extra:
+            continue
+        if len(extra) != 1:
+            raise Unmatched("a Load takes at most one coordinate from data")
+        src_load, use_abs, mod, chain = _index_chain(tile, extra[0])
+        saved = it.env[extra[0]]
+        it.env[extra[0]] = np.zeros(cells.shape, np.int64)
+        base = it.flat_index(s.input, s.index)
+        it.env[extra[0]] = np.ones(cells.shape, np.int64)
+        mult = np.unique(it.flat_index(s.input, s.index) - base)
+        it.env[extra[0]] = saved
+        if len(mult) != 1 or int(mult[0]) < 0:
+            raise Unmatched("the coordinate taken from data does not enter the index linearly")
+        indirect[k] = (base, int(mult[0]), src_load, use_abs, mod)
+        hidden |= chain
+        index_loads[id(src_load)] = (use_abs, mod)
     for k, (s, (buf, idx, _)) in enumerate(zip(loads, it.loads)):
-        if tensors[buf][1] not in ok_in:
+        is_source = id(s) in index_loads
+        if is_source:
+            if tensors[buf][1] not in ("i32", "i64", "int"):
+                raise Unmatched("an index is read from an integer buffer")
+        elif tensors[buf][1] not in ok_in:
             raise Unmatched(f"input {buf!r} of dtype {tensors[buf][1]} in {'an integer' if integer else 'a float'} program")
-        off, coef = _fit_affine(idx, digits, f"the index of {buf!r}")
+        rot = None
+        fit_on = indirect[k][0] if k in indirect else idx
+        try:
+            off, coef = _fit_affine(fit_on, digits, f"the index of {buf!r}")
+        except Unmatched:
+            if k in indirect or is_source:
+                raise
+            off, coef, rot = _fit_rotated(fit_on, digits, extents, f"the index of {buf!r}")
         lo, hi = _reach(off, coef, extents)
+        if k in indirect:
+            hi += indirect[k][1] * (indirect[k][4] - 1)
         if lo < 0 or hi >= math.prod(tensors[buf][0]):
             raise Unmatched(f"the index of {buf!r} leaves the buffer (elements {lo}..{hi} of {math.prod(tensors[buf][0])})")
         name = f"__in{k}"
         synthetic[name] = (tensors[buf][0], tensors[buf][1])
-        sources.append({"buffer": buf, "offset": off, "coef": coef})
-        body.append(Load(s.names[0], name))
+        src = {"buffer": buf, "offset": off, "coef": coef}
+        if rot is not None and any(rot):
+            src["rot"] = rot
+        if is_source:
+            src["index_mod"], src["index_abs"] = index_loads[id(s)][1], index_loads[id(s)][0]
+        if k in indirect:
+            src["index_of_load"], src["index_mult"] = indirect[k][2], indirect[k][1]
+        sources.append(src)
+        if not is_source:
+            body.append(Load(s.names[0], name))
+    if index_loads:
+        used = {a for st in tile.body if _kind(st) == "Assign" and st.name not in hidden for a in st.args if isinstance(a, str)}
+        used |= {v for w in tile.body if _kind(w) == "Write" for v in w.values if isinstance(v, str)}
+        for s in loads:
+            if id(s) in index_loads and (s.names[0] in used or hidden & used):
+                raise Unmatched("a value read as an index is not also a value of the program")
     used_axes = [nm for nm in names if any(_kind(s) == "Assign" and nm in [a for a in s.args if isinstance(a, str)] for s in tile.body)]
     for nm in used_axes:
         synthetic[f"__axis_{nm}"] = ((n,), "i32" if integer else "f32")
@@ -421,7 +526,7 @@ def match_indexed(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
         body.append(Load(nm, f"__axis_{nm}"))
     if not sources:
         raise Unmatched("an indexed kernel reads something")
-    body += [s for s in tile.body if _kind(s) != "Load"]
+    body += [s for s in tile.body if _kind(s) != "Load" and not (_kind(s) == "Assign" and s.name in hidden)]
     off, coef = _fit_affine(out_idx, digits, "the index of the Write")
     lo, hi = _reach(off, coef, extents)
     if lo < 0 or hi >= math.prod(tensors[out_name][0]):
@@ -439,6 +544,17 @@ def match_indexed(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
     by_name = {f"__in{k}": sources[k] for k in range(len(loads))}
     by_name.update({f"__axis_{nm}": sources[len(loads) + j] for j, nm in enumerate(used_axes)})
     ordered = [by_name[nm] for nm in prog["inputs"]]
+    # index sources ride along as extra inputs that no step reads
+    for k, s in enumerate(loads):
+        if id(s) in index_loads:
+            ordered.append(sources[k])
+            prog["in_dtypes"].append(tensors[s.input][1])
+    if len(ordered) > PW_INPUTS:
+        raise Unmatched(f"{len(ordered)} sources: the indexed elementwise kernel takes {PW_INPUTS}")
+    for src in ordered:
+        if "index_of_load" in src:
+            target = sources[next(k for k, ld in enumerate(loads) if ld is src.pop("index_of_load"))]
+            src["index_of"] = next(j for j, o in enumerate(ordered) if o is target)
     index_map = {"extents": extents, "inputs": ordered, "out": {"offset": off, "coef": coef}}
     return {"variant": "pointwise_indexed", "inputs": [src["buffer"] for src in ordered if "buffer" in src], "outputs": [out_name],
             "params": {"n": n, "program": {k: v for k, v in prog.items() if k != "inputs"}, "index_map": index_map}}

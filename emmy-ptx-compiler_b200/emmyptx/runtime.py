@@ -39,7 +39,10 @@ class PwIndexMap(ctypes.Structure):
     _fields_ = [("n_axes", ctypes.c_int32), ("reserved", ctypes.c_int32), ("extent", ctypes.c_int64 * PW_MAX_AXES),
                 ("in_kind", ctypes.c_int32 * PW_MAX_INPUTS), ("in_axis", ctypes.c_int32 * PW_MAX_INPUTS),
                 ("in_offset", ctypes.c_int64 * PW_MAX_INPUTS), ("in_coef", (ctypes.c_int64 * PW_MAX_AXES) * PW_MAX_INPUTS),
-                ("out_offset", ctypes.c_int64), ("out_coef", ctypes.c_int64 * PW_MAX_AXES)]
+                ("out_offset", ctypes.c_int64), ("out_coef", ctypes.c_int64 * PW_MAX_AXES),
+                ("in_rot", (ctypes.c_int64 * PW_MAX_AXES) * PW_MAX_INPUTS), ("in_index_of", ctypes.c_int32 * PW_MAX_INPUTS),
+                ("in_index_abs", ctypes.c_int32 * PW_MAX_INPUTS), ("in_index_mod", ctypes.c_int64 * PW_MAX_INPUTS),
+                ("in_index_mult", ctypes.c_int64 * PW_MAX_INPUTS)]
 
 
 class PwProgram(ctypes.Structure):
@@ -223,6 +226,12 @@ def make_index_map(index_map: dict) -> PwIndexMap:
             m.in_offset[k] = src["offset"]
             for a, c in enumerate(src["coef"]):
                 m.in_coef[k][a] = c
+            for a, r in enumerate(src.get("rot", [])):              # rotation of axis a: (digit + r) mod extent
+                m.in_rot[k][a] = r
+            if "index_mod" in src:                                  # an index source: |value| (if abs) mod index_mod
+                m.in_kind[k], m.in_index_mod[k], m.in_index_abs[k] = 3, src["index_mod"], 1 if src.get("index_abs") else 0
+            elif "index_of" in src:                                 # addressed through index source index_of
+                m.in_kind[k], m.in_index_of[k], m.in_index_mult[k] = 2, src["index_of"], src["index_mult"]
     m.out_offset = index_map["out"]["offset"]
     for a, c in enumerate(index_map["out"]["coef"]):
         m.out_coef[a] = c
@@ -246,6 +255,8 @@ def pointwise_indexed(program: dict, index_map: dict, inputs: list, out, stream=
         for k, src in enumerate(index_map["inputs"]):
             if "axis" not in src:
                 lo, hi = reach(src)
+                if "index_of" in src:                               # plus the largest row the index source can name
+                    hi += src["index_mult"] * (index_map["inputs"][src["index_of"]]["index_mod"] - 1)
                 if lo < 0 or hi >= inputs[k].numel():
                     raise IndexError(f"pointwise_indexed: input {k} is read at elements {lo}..{hi} of {inputs[k].numel()}")
         lo, hi = reach(index_map["out"])

@@ -130,7 +130,8 @@ int emmyb200_pointwise_program_compile(const emmyb200_pw_program* program, int g
  * transpose, permute, slices, flip, repeat, expand, stack) and masks made from the axis variables themselves (tril:
  * shapes.py:19). The cell number is split into the digits of the axes (outermost first, last fastest, as
  * emmyptx/kernel.py:587-626 decodes `gid`); input k is element in_offset[k] + sum_a in_coef[k][a] * digit[a] of its
- * buffer (in_kind 0), or the value of digit in_axis[k] itself with no buffer behind it (in_kind 1; inputs[k] unused); the
+ * buffer (in_kind 0), or the value of digit in_axis[k] itself with no buffer behind it (in_kind 1; inputs[k] unused; kinds 2
+ * and 3, below, address a buffer through an index read from another one); the
  * result is stored at out_offset + sum_a out_coef[a] * digit[a]. The program's in_div / in_mod are ignored. Nothing
  * here can check an index against a buffer's size: the caller does (the facade checks every map's range against the
  * tensor shapes); a map that reaches a negative element is refused. Always a compiled kernel (see above); without the
@@ -148,6 +149,18 @@ typedef struct {
     int64_t in_coef[EMMYB200_PW_MAX_INPUTS][EMMYB200_PW_MAX_AXES];
     int64_t out_offset;
     int64_t out_coef[EMMYB200_PW_MAX_AXES];
+    /* Rotations (torch.roll, shapes.py:16): the digit of axis a enters input k's map as (digit + in_rot[k][a]) mod extent[a];
+     * 0 <= in_rot < extent. */
+    int64_t in_rot[EMMYB200_PW_MAX_INPUTS][EMMYB200_PW_MAX_AXES];
+    /* Indices taken from data (embedding, gather: shapes.py:20-24). An input of in_kind 3 is an index source: an I32 / I64
+     * buffer read through its own affine map, made non-negative (in_index_abs) and reduced modulo in_index_mod (required:
+     * the modulus is what bounds the index; the remainder is the non-negative one); no step may read it as a value. An
+     * input of in_kind 2 is a buffer whose element index is its affine map plus in_index_mult[k] times the value of index
+     * source in_index_of[k]. */
+    int32_t in_index_of[EMMYB200_PW_MAX_INPUTS];
+    int32_t in_index_abs[EMMYB200_PW_MAX_INPUTS];
+    int64_t in_index_mod[EMMYB200_PW_MAX_INPUTS];
+    int64_t in_index_mult[EMMYB200_PW_MAX_INPUTS];
 } emmyb200_pw_index_map;
 int emmyb200_pointwise_indexed(const emmyb200_pw_program* program, const emmyb200_pw_index_map* map,
                                const void* const* inputs, void* out, void* cuda_stream);

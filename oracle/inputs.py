@@ -61,12 +61,17 @@ def attention_inputs(units: int, seq_q: int, seq_k: int, d: int, dtype: str = "b
 
 
 def layout_buffers(tensors: dict, arg_order: list) -> dict:
-    """float32 buffers for a data-movement kernel: argument i ~ N(0, 1) seeded with i (tools/run_local.py:86-87); the
-    output starts as zeros (:92-93)."""
+    """Buffers for a data-movement kernel: float argument i ~ N(0, 1) seeded with i (tools/run_local.py:86-87), integer
+    (index) arguments uniform in [-1000, 1000); the output starts as zeros (:92-93)."""
     bufs = {}
     for i, name in enumerate(arg_order):
         shape = tensors[name]["shape"]
-        bufs[name] = np.zeros(shape, np.float32) if name == "out" else np.random.default_rng(i).standard_normal(shape).astype(np.float32)
+        if name == "out":
+            bufs[name] = np.zeros(shape, np.float32)
+        elif tensors[name].get("dtype") == "i64":               # an index buffer: either sign, beyond the table's size
+            bufs[name] = np.random.default_rng(i).integers(-1000, 1000, shape).astype(np.int64)
+        else:
+            bufs[name] = np.random.default_rng(i).standard_normal(shape).astype(np.float32)
     return bufs
 
 
@@ -74,6 +79,8 @@ LAYOUT_EXPECTED = {     # what each data-movement case computes, on the buffers 
     "s_transpose": lambda b: b["X"].T, "s_permute": lambda b: b["X"].transpose(2, 0, 1) * np.float32(2), "s_slice": lambda b: b["X"][:, 10:50] * np.float32(2),
     "s_strided_slice": lambda b: b["X"][::2] + np.float32(1), "s_flip": lambda b: b["X"][:, ::-1], "s_stack": lambda b: np.stack([b["A"], b["B"]]),
     "s_tril": lambda b: np.tril(b["X"]), "s_repeat": lambda b: np.tile(b["X"], (2, 1)),
+    "s_roll": lambda b: np.roll(b["X"], 3, -1), "s_embedding": lambda b: b["SRC"][np.abs(b["IDX"]) % 100],
+    "s_gather": lambda b: np.take_along_axis(b["SRC"], np.abs(b["IDX"]) % 64, 1),
     "c_avg_pool1d": lambda b: ((b["X"][:, 0::4] + b["X"][:, 1::4]) + (b["X"][:, 2::4] + b["X"][:, 3::4])) * np.float32(0.25),
     "c_max_pool2d": lambda b: b["X"].reshape(8, 16, 2, 16, 2).max(axis=(2, 4)),
     "s_cat_a": lambda b: np.concatenate([b["A"], np.zeros((32, 48), np.float32)], -1),

@@ -160,6 +160,11 @@ class Interpreter:
         V = self._val
         if name == "ret":
             return
+        if name == "trap":                                       # the reference's range check of an i64 value (kernel.py:691)
+            hit = self.active if mask is None else (self.active & mask)
+            if hit.any():
+                raise PtxError("the kernel trapped (a 64-bit value does not fit 32 bits)")
+            return
         if name == "bra":
             taken = np.ones(self.n, bool) if mask is None else mask
             if ops[0] == "$L_exit":
@@ -243,7 +248,7 @@ class Interpreter:
             self._set(ops[0], np.where(self.reg[ops[3]], a, b), mask)
         elif name == "ld" and parts[1] == "global":
             buf, off = self._mem(ops[1])
-            dt = np.float32 if ty == "f32" else (np.uint16 if ty == "b16" else np.int32)
+            dt = np.float32 if ty == "f32" else (np.uint16 if ty == "b16" else (np.int64 if ty in ("s64", "u64", "b64") else np.int32))
             dsts = [t.strip() for t in ops[0].strip("{}").split(",")]        # one register, or the members of a .v2 / .v4
             m = self.active if mask is None else self.active & mask
             for j, dst in enumerate(dsts):                                   # (two adjacent f32 loads pair up: emmyptx/kernel.py:517-548)
@@ -358,6 +363,10 @@ class Interpreter:
         elif dst_ty in ("f16", "bf16") and src_ty == "f32" and rnd == "rn":
             h = _f32_to_bf16(a) if dst_ty == "bf16" else a.astype(np.float16).view(np.uint16)
             self._set(ops[0], h, mask)
+        elif dst_ty == "s32" and src_ty == "s64":               # i64 buffers carry 32-bit values (emmyptx/kernel.py:41, 685-691)
+            self._set(ops[0], np.asarray(a, np.int64).astype(np.int32), mask)
+        elif dst_ty == "s64" and src_ty == "s32":
+            self._set(ops[0], np.asarray(a, np.int32).astype(np.int64), mask)
         else:
             raise PtxError(f"unsupported conversion {'.'.join(parts)}")
 

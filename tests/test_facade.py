@@ -358,8 +358,24 @@ def test_layout_kernels_become_indexed_programs():
     h = handle(ir.layout_kernel("s_stack"))
     assert h["inputs"] == ["A", "B"] and {"axis": 0} in h["params"]["index_map"]["inputs"]
     assert handle(ir.layout_kernel("s_repeat"))["variant"] == "pointwise_program"           # a broadcast: the vectorised kernel
+    h = handle(ir.layout_kernel("s_roll"))                                                  # wraps around: a rotation of axis 1
+    assert h["params"]["index_map"]["inputs"][0] == {"buffer": "X", "offset": 0, "coef": [128, 1], "rot": [0, 125]}
+    h = handle(ir.layout_kernel("s_embedding"))                                             # a row taken from data
+    srcs = h["params"]["index_map"]["inputs"]
+    assert h["inputs"] == ["SRC", "IDX"] and h["params"]["program"]["in_dtypes"] == ["f32", "i64"]
+    assert srcs[1] == {"buffer": "IDX", "offset": 0, "coef": [1, 0], "index_mod": 100, "index_abs": True}
+    assert srcs[0] == {"buffer": "SRC", "offset": 0, "coef": [0, 1], "index_mult": 32, "index_of": 1}
+    assert handle(ir.layout_kernel("s_gather"))["params"]["index_map"]["inputs"][0]["index_mult"] == 1
+    g, k, launch = ir.layout_kernel("s_embedding")                                          # without the modulus nothing bounds the row
+    body = k.body[0].body
+    load = next(s for s in body if type(s).__name__ == "Load" and s.input == "SRC")
+    load.index[0] = ir.Var("a")
     with pytest.raises(CompileError):
-        handle(ir.layout_kernel("s_roll"))                                                  # wraps around: not affine
+        handle((g, k, launch))
+    g, k, launch = ir.layout_kernel("s_embedding")                                          # a modulus larger than the table
+    next(s for s in k.body[0].body if type(s).__name__ == "Assign" and s.op.name == "mod").args[1] = 101
+    with pytest.raises(CompileError):
+        handle((g, k, launch))
     g, k, launch = ir.layout_kernel("s_slice")                                              # a slice that leaves its buffer
     load = next(s for s in k.body[0].body if type(s).__name__ == "Load")
     load.index[1] = ir.BinaryExpr("+", ir.Var("c0"), ir.Literal(100, "int"))

@@ -15,14 +15,14 @@ from oracle import inputs
 pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden"
 CASES = ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_repeat", "s_stack", "s_tril", "s_cat_a", "s_cat_b",
-         "c_avg_pool1d", "c_max_pool2d"]
+         "s_roll", "s_embedding", "s_gather", "c_avg_pool1d", "c_max_pool2d"]
 
 
 def _run(case, cuda):
     import torch
     g, k, launch = ir.layout_kernel(case, name=case)
     handle = json.loads(compile_kernel(g, k, launch))
-    tensors = {t.name: {"shape": [d.as_static() for d in t.shape]} for nd in g.nodes.values() for t in nd.outputs}
+    tensors = {t.name: {"shape": [d.as_static() for d in t.shape], "dtype": t.dtype.name} for nd in g.nodes.values() for t in nd.outputs}
     host = inputs.layout_buffers(tensors, launch["arg_order"])
     dev = {nm: torch.from_numpy(a).to(cuda) for nm, a in host.items()}
     run_local.init()
@@ -136,4 +136,30 @@ def test_batched_transposition_through_shared_memory_tiles(dtype, cuda):
     imap["inputs"][0] = {"offset": (cols - 1) * rows, "coef": [cols * rows, 1, -rows]}
     rt.pointwise_indexed(prog, imap, [x.reshape(-1), None, None], out.reshape(-1))
     assert torch.equal(out, torch.where(j <= i, x.flip(1).transpose(1, 2), torch.zeros((), device=cuda, dtype=td)))
+
+
+def test_rotation_and_data_dependent_rows_directly(cuda):
+    """A rotation along two axes at once; an embedding with int32 indices of either sign into a bf16 table with a scale in
+    the program; the range check on the largest row the modulus allows."""
+    import torch
+    from emmyptx import runtime as rt
+    S = rt.PW_MAX_SLOTS
+    x = torch.randn(37, 50, device=cuda)
+    out = torch.zeros_like(x)
+    ident = {"in_dtypes": ["f32"], "out_dtype": "f32", "out_slot": 0, "consts": [], "steps": []}
+    rt.pointwise_indexed(ident, {"extents": [37, 50], "inputs": [{"offset": 0, "coef": [50, 1], "rot": [37 - 5, 50 - 7]}], "out": {"offset": 0, "coef": [50, 1]}},
+                         [x.reshape(-1)], out.reshape(-1))
+    assert torch.equal(out, torch.roll(x, (5, 7), (0, 1)))
+    table = torch.randn(300, 48, device=cuda).to(torch.bfloat16)
+    idx = torch.randint(-5000, 5000, (1000,), device=cuda, dtype=torch.int32)
+    emb = torch.zeros(1000, 48, device=cuda, dtype=torch.bfloat16)
+    prog = {"in_dtypes": ["bf16", "i32"], "out_dtype": "bf16", "out_slot": 4, "consts": [2.0], "steps": [["multiply", 4, 0, S, 0]]}
+    imap = {"extents": [1000, 48], "inputs": [{"offset": 0, "coef": [0, 1], "index_of": 1, "index_mult": 48}, {"offset": 0, "coef": [1, 0], "index_mod": 300}],
+            "out": {"offset": 0, "coef": [48, 1]}}
+    rt.pointwise_indexed(prog, imap, [table.reshape(-1), idx], emb.reshape(-1))
+    rows = torch.remainder(idx.long(), 300)                     # the non-negative remainder, no abs
+    assert torch.equal(emb, (table[rows].float() * 2).to(torch.bfloat16))
+    with pytest.raises(IndexError, match="input 0"):
+        rt.pointwise_indexed(prog, dict(imap, inputs=[imap["inputs"][0], {"offset": 0, "coef": [1, 0], "index_mod": 301}]), [table.reshape(-1), idx], emb.reshape(-1))
+    assert rt.device_status() == 0
 
