@@ -343,6 +343,35 @@ extern "C" int emmyb200_launch(const char* handle_json, void* const* params, int
         }
         return emmyb200_pointwise_indexed(&c, &m, ins, out, cuda_stream);
     }
+    if (v == "contract_indexed") {
+        const JVal* cm = p.get("map");
+        const JVal* ext = cm ? cm->get("extents") : nullptr;
+        const JVal* loops = cm ? cm->get("loops") : nullptr;
+        const JVal* dst = cm ? cm->get("out") : nullptr;
+        if (ext == nullptr || loops == nullptr || dst == nullptr || cm->get("a") == nullptr || cm->get("b") == nullptr || ext->items.empty() ||
+            ext->items.size() > EMMYB200_PW_MAX_AXES || loops->items.empty() || loops->items.size() > EMMYB200_CT_MAX_LOOPS)
+            return fail(EMMYB200_ERR_ARG, "launch: malformed contraction map");
+        emmyb200_contraction_map m;
+        memset(&m, 0, sizeof m);
+        m.n_axes = (int)ext->items.size();
+        m.n_loops = (int)loops->items.size();
+        for (int ax = 0; ax < m.n_axes; ++ax) m.extent[ax] = ext->items[ax].as_int();
+        for (int l = 0; l < m.n_loops; ++l) m.loop_extent[l] = loops->items[l].as_int();
+        auto side = [&](const JVal& src, int64_t* offset, int64_t* coef, int64_t* loop_coef, int* dtype) -> bool {
+            const JVal* c = src.get("coef");
+            const JVal* lc = src.get("loop_coef");
+            if (c == nullptr || (int)c->items.size() != m.n_axes || (loop_coef != nullptr && (lc == nullptr || (int)lc->items.size() != m.n_loops))) return false;
+            *offset = geti(src, "offset");
+            for (int ax = 0; ax < m.n_axes; ++ax) coef[ax] = c->items[ax].as_int();
+            for (int l = 0; loop_coef != nullptr && l < m.n_loops; ++l) loop_coef[l] = lc->items[l].as_int();
+            *dtype = dtype_code(gets(src, "dtype"));
+            return true;
+        };
+        if (!side(*cm->get("a"), &m.a_offset, m.a_coef, m.a_loop_coef, &m.a_dtype) || !side(*cm->get("b"), &m.b_offset, m.b_coef, m.b_loop_coef, &m.b_dtype) ||
+            !side(*dst, &m.out_offset, m.out_coef, nullptr, &m.out_dtype))
+            return fail(EMMYB200_ERR_ARG, "launch: malformed contraction map");
+        return emmyb200_contract_indexed(&m, a.input(0), a.input(1), out, cuda_stream);
+    }
     if (v == "index_gather_i32")
         return emmyb200_index_gather_i32((const int32_t*)a.input(0), (int32_t*)out, geti(p, "n"), geti(p, "mul"), geti(p, "add"), (int32_t)geti(p, "div"),
                                          (int32_t)geti(p, "shift"), getb(p, "trunc") ? EMMYB200_GATHER_TRUNC : 0, cuda_stream);

@@ -653,6 +653,46 @@ extern "C" __global__ void __launch_bounds__(256) pw_ix_kernel(const void* p0, c
 }
 )SHELL";
 
+// The kernel of emmyb200_contract_indexed: one output cell per thread and trip; the cell's value is the sum over up to
+// three nested reduction axes of A[...] * B[...], both addressed by affine maps of the tile's and the loops' digits,
+// folded in loop order with one fused multiply-add per term (as the reference forms an FMA from the multiply feeding
+// the Accum, emmyptx/kernel.py:786-797). CT_NLOOPS, PW_NAXES, PW_DT0 (A), PW_DT1 (B) and PW_OUT_DT are defined in front.
+static const char kContractionKernel[] = R"SHELL(
+struct CtArg { i64 extent[6]; i64 loop_extent[3]; i64 a_offset; i64 a_coef[6]; i64 a_loop[3]; i64 b_offset; i64 b_coef[6]; i64 b_loop[3];
+               i64 out_offset; i64 out_coef[6]; int narrow; int pad; };
+template <typename I> __device__ __forceinline__ void ct_cell(const void* a, const void* b, void* out, I i, const CtArg& m) {
+    I rem = i, at = (I)m.a_offset, bt = (I)m.b_offset, to = (I)m.out_offset;
+#pragma unroll
+    for (int ax = PW_NAXES - 1; ax >= 0; --ax) {
+        const I e = (I)m.extent[ax];
+        const I q = rem / e;
+        const I d = rem - q * e;
+        rem = q;
+        at += (I)m.a_coef[ax] * d;
+        bt += (I)m.b_coef[ax] * d;
+        to += (I)m.out_coef[ax] * d;
+    }
+    const I n0 = (I)m.loop_extent[0], n1 = CT_NLOOPS > 1 ? (I)m.loop_extent[1] : (I)1, n2 = CT_NLOOPS > 2 ? (I)m.loop_extent[2] : (I)1;
+    const I a0 = (I)m.a_loop[0], a1 = CT_NLOOPS > 1 ? (I)m.a_loop[1] : (I)0, a2 = CT_NLOOPS > 2 ? (I)m.a_loop[2] : (I)0;
+    const I b0 = (I)m.b_loop[0], b1 = CT_NLOOPS > 1 ? (I)m.b_loop[1] : (I)0, b2 = CT_NLOOPS > 2 ? (I)m.b_loop[2] : (I)0;
+    float acc = 0.0f;
+    for (I l0 = 0; l0 < n0; ++l0)
+        for (I l1 = 0; l1 < n1; ++l1) {
+            const I ar = at + a0 * l0 + a1 * l1, br = bt + b0 * l0 + b1 * l1;
+            for (I l2 = 0; l2 < n2; ++l2)
+                acc = fmaf(pw_ld1<PW_DT0>(a, (i64)(ar + a2 * l2)), pw_ld1<PW_DT1>(b, (i64)(br + b2 * l2)), acc);
+        }
+    pw_st1(out, (i64)to, acc);
+}
+extern "C" __global__ void __launch_bounds__(256) ct_kernel(const void* a, const void* b, void* out, i64 n, CtArg m) {
+    const i64 stride = (i64)gridDim.x * 256;
+    for (i64 i = (i64)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+        if (m.narrow) ct_cell<int>(a, b, out, (int)i, m);
+        else ct_cell<i64>(a, b, out, i, m);
+    }
+}
+)SHELL";
+
 static bool float_program(const emmyb200_pw_program& p) {
     return p.out_dtype == EMMYB200_F32 || p.out_dtype == EMMYB200_F16 || p.out_dtype == EMMYB200_BF16;
 }
@@ -1044,6 +1084,126 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
     cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(kern.kernel), dim3(blocks), dim3(256), args, 0, static_cast<cudaStream_t>(cuda_stream));
     if (e != cudaSuccess) return cuda_fail(e, "launch of the indexed elementwise kernel");
     return EMMYB200_OK;
+}
+
+namespace emmy {
+
+struct CtArgHost { long long extent[6]; long long loop_extent[3]; long long a_offset; long long a_coef[6]; long long a_loop[3]; long long b_offset;
+                   long long b_coef[6]; long long b_loop[3]; long long out_offset; long long out_coef[6]; int narrow; int pad; };
+
+static std::string contraction_source(const emmyb200_contraction_map& m) {
+    char line[256];
+    snprintf(line, sizeof line,
+             "#define PW_N_IN 2\n#define PW_VEC 0\n#define PW_G 4\n#define PW_T float\n#define PW_OUT_DT %d\n#define PW_DT0 %d\n#define PW_DT1 %d\n"
+             "#define PW_NAXES %d\n#define CT_NLOOPS %d\n",
+             m.out_dtype, m.a_dtype, m.b_dtype, m.n_axes, m.n_loops);
+    std::string s = line;
+    s += "typedef long long i64;\nstruct PwVec { PW_T v[PW_G]; };\n";
+    s += kFloatLoads;
+    s += kFloatStores;
+    s += kContractionKernel;
+    return s;
+}
+
+static int check_contraction(const emmyb200_contraction_map* m, const char* who) {
+    if (m == nullptr) return fail(EMMYB200_ERR_ARG, "%s: null map", who);
+    if (m->n_axes < 1 || m->n_axes > EMMYB200_PW_MAX_AXES || m->n_loops < 1 || m->n_loops > EMMYB200_CT_MAX_LOOPS)
+        return fail(EMMYB200_ERR_ARG, "%s: %d tile axes (1 to %d), %d reduction axes (1 to %d)", who, m->n_axes, EMMYB200_PW_MAX_AXES, m->n_loops, EMMYB200_CT_MAX_LOOPS);
+    auto float_ok = [](int d) { return d == EMMYB200_F32 || d == EMMYB200_F16 || d == EMMYB200_BF16; };
+    if (!float_ok(m->a_dtype) || !float_ok(m->b_dtype) || !float_ok(m->out_dtype)) return fail(EMMYB200_ERR_UNSUPPORTED, "%s: f32 / f16 / bf16 buffers", who);
+    return EMMYB200_OK;
+}
+
+}  // namespace emmy
+
+extern "C" int emmyb200_contract_indexed(const emmyb200_contraction_map* map, const void* A, const void* B, void* out, void* cuda_stream) {
+    using namespace emmy;
+    int rc = check_contraction(map, "contract_indexed");
+    if (rc != EMMYB200_OK) return rc;
+    int64_t n = 1, terms = 1;
+    for (int a = 0; a < map->n_axes; ++a) {
+        if (map->extent[a] < 0 || (map->extent[a] != 0 && n > ((int64_t)1 << 40))) return fail(EMMYB200_ERR_SHAPE, "contract_indexed: bad extent");
+        n *= map->extent[a];
+    }
+    for (int l = 0; l < map->n_loops; ++l) {
+        if (map->loop_extent[l] < 1 || terms > ((int64_t)1 << 40)) return fail(EMMYB200_ERR_SHAPE, "contract_indexed: a reduction axis has %lld terms", (long long)map->loop_extent[l]);
+        terms *= map->loop_extent[l];
+    }
+    if (n == 0) return EMMYB200_OK;
+    if (A == nullptr || B == nullptr || out == nullptr) return fail(EMMYB200_ERR_ARG, "contract_indexed: null buffer");
+    bool narrow = n <= 0x7fffffffLL;
+    auto range_ok = [&](int64_t off, const int64_t* coef, const int64_t* loop, const char* what) -> int {
+        int64_t lo = off, hi = off;
+        for (int a = 0; a < map->n_axes; ++a) {
+            const int64_t span = coef[a] * (map->extent[a] - 1);
+            if (span < 0) lo += span; else hi += span;
+        }
+        for (int l = 0; loop != nullptr && l < map->n_loops; ++l) {
+            const int64_t span = loop[l] * (map->loop_extent[l] - 1);
+            if (span < 0) lo += span; else hi += span;
+        }
+        if (lo < 0) return fail(EMMYB200_ERR_SHAPE, "contract_indexed: %s reaches element %lld", what, (long long)lo);
+        if (hi > 0x7fffffffLL) narrow = false;
+        return EMMYB200_OK;
+    };
+    if ((rc = range_ok(map->a_offset, map->a_coef, map->a_loop_coef, "the map of A")) != EMMYB200_OK) return rc;
+    if ((rc = range_ok(map->b_offset, map->b_coef, map->b_loop_coef, "the map of B")) != EMMYB200_OK) return rc;
+    if ((rc = range_ok(map->out_offset, map->out_coef, nullptr, "the output map")) != EMMYB200_OK) return rc;
+    if (!nvrtc().ok) return fail(EMMYB200_ERR_UNSUPPORTED, "contract_indexed: needs the run-time compiler (libnvrtc.so.12 not found)");
+    JitKernel kern;
+    {
+        std::lock_guard<std::mutex> lock(g_jit_mutex);
+        std::string key = "ct";
+        for (int v : {map->n_axes, map->n_loops, map->a_dtype, map->b_dtype, map->out_dtype}) key.push_back((char)v);
+        auto it = jit_cache().find(key);
+        if (it == jit_cache().end()) {
+            std::vector<char> cubin;
+            rc = compile_source(contraction_source(*map), &cubin);
+            if (rc != EMMYB200_OK) return rc;
+            cudaError_t e = cudaLibraryLoadData(&kern.library, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaLibraryLoadData (indexed contraction kernel)");
+            e = cudaLibraryGetKernel(&kern.kernel, kern.library, "ct_kernel");
+            if (e != cudaSuccess) { cudaLibraryUnload(kern.library); return cuda_fail(e, "cudaLibraryGetKernel (indexed contraction kernel)"); }
+            g_jit_compiles.fetch_add(1);
+            it = jit_cache().emplace(key, kern).first;
+        }
+        kern = it->second;
+    }
+    CtArgHost m;
+    memset(&m, 0, sizeof m);
+    for (int a = 0; a < EMMYB200_PW_MAX_AXES; ++a) {
+        const bool live = a < map->n_axes;
+        m.extent[a] = live ? map->extent[a] : 1;
+        m.a_coef[a] = live ? map->a_coef[a] : 0;
+        m.b_coef[a] = live ? map->b_coef[a] : 0;
+        m.out_coef[a] = live ? map->out_coef[a] : 0;
+    }
+    for (int l = 0; l < EMMYB200_CT_MAX_LOOPS; ++l) {
+        const bool live = l < map->n_loops;
+        m.loop_extent[l] = live ? map->loop_extent[l] : 1;
+        m.a_loop[l] = live ? map->a_loop_coef[l] : 0;
+        m.b_loop[l] = live ? map->b_loop_coef[l] : 0;
+    }
+    m.a_offset = map->a_offset; m.b_offset = map->b_offset; m.out_offset = map->out_offset;
+    m.narrow = narrow ? 1 : 0;
+    long long count = n;
+    void* args[] = {&A, &B, &out, &count, &m};
+    const int64_t want = (n + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    const unsigned blocks = (unsigned)(want < cap ? want : cap);
+    cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(kern.kernel), dim3(blocks), dim3(256), args, 0, static_cast<cudaStream_t>(cuda_stream));
+    if (e != cudaSuccess) return cuda_fail(e, "launch of the indexed contraction kernel");
+    return EMMYB200_OK;
+}
+
+extern "C" int emmyb200_contract_indexed_compile(const emmyb200_contraction_map* map, int64_t* code_bytes) {
+    using namespace emmy;
+    int rc = check_contraction(map, "contract_indexed_compile");
+    if (rc != EMMYB200_OK) return rc;
+    std::vector<char> cubin;
+    rc = compile_source(contraction_source(*map), &cubin);
+    if (rc == EMMYB200_OK && code_bytes != nullptr) *code_bytes = (int64_t)cubin.size();
+    return rc;
 }
 
 extern "C" int emmyb200_pointwise_indexed_compile(const emmyb200_pw_program* prog, const emmyb200_pw_index_map* map, int64_t* code_bytes) {

@@ -212,6 +212,12 @@ class Accum:
 
 
 @_node
+class Init:
+    name: str
+    identity: Any = 0.0
+
+
+@_node
 class Smem:
     name: str
     dtype: str
@@ -701,4 +707,37 @@ def layout_kernel(case: str, name: str | None = None):
         cells *= a.extent.value
     g = _graph(kern, [tensor(b, shp, "f32") for b, shp in ins.items()], [tensor("out", out_shape, "f32")])
     return g, kern, _launch(kern, [*ins, "out"], cells)
+
+
+def conv_kernel(case: str = "c_conv1d", name: str | None = None):
+    """The reference's convolution cases (tools/torch_cases/conv.py:6-7) as scalar loops: one tile cell per output element,
+    nested Loops over the input channels and the taps folding w * x into an accumulator (emmyptx/kernel.py:786-797;
+    every Loop seeds the accumulators directly inside it, emmyptx/loops.py:92-102, so only the innermost body holds the
+    Accum and the accumulator is carried across the outer trips by `seed=False` on the inner Loops)."""
+    lit = lambda v: Literal(int(v), "int")
+    add = lambda a, b: BinaryExpr("+", a, b)
+    if case == "c_conv1d":              # x [1, 16, 128], w [32, 16, 3] -> [1, 32, 126]
+        axes = [Axis("o0", Dim(32)), Axis("i0", Dim(126))]
+        inner = [Load(["wv"], "W", [Var("o0"), Var("c0"), Var("t0")]), Load(["xv"], "X", [Var("c0"), add(Var("i0"), Var("t0"))]),
+                 Assign("p", Op("multiply"), ["wv", "xv"]), Accum("acc", None, "p", Op("add", 0.0))]
+        body = [Init("acc", 0.0), Loop(Axis("c0", Dim(16)), [Loop(Axis("t0", Dim(3)), inner, seed=False)], seed=False),
+                Write("out", [Var("o0"), Var("i0")], ["acc"])]
+        ins, out_shape = [tensor("X", [16, 128], "f32"), tensor("W", [32, 16, 3], "f32")], [32, 126]
+    elif case == "c_conv2d":            # x [1, 8, 32, 32], w [16, 8, 3, 3] -> [1, 16, 30, 30]
+        axes = [Axis("o0", Dim(16)), Axis("i0", Dim(30)), Axis("j0", Dim(30))]
+        inner = [Load(["wv"], "W", [Var("o0"), Var("c0"), Var("u0"), Var("v0")]),
+                 Load(["xv"], "X", [Var("c0"), add(Var("i0"), Var("u0")), add(Var("j0"), Var("v0"))]),
+                 Assign("p", Op("multiply"), ["wv", "xv"]), Accum("acc", None, "p", Op("add", 0.0))]
+        body = [Init("acc", 0.0),
+                Loop(Axis("c0", Dim(8)), [Loop(Axis("u0", Dim(3)), [Loop(Axis("v0", Dim(3)), inner, seed=False)], seed=False)], seed=False),
+                Write("out", [Var("o0"), Var("i0"), Var("j0")], ["acc"])]
+        ins, out_shape = [tensor("X", [8, 32, 32], "f32"), tensor("W", [16, 8, 3, 3], "f32")], [16, 30, 30]
+    else:
+        raise KeyError(case)
+    kern = KernelOp(name or f"k_{case}", [Tile(axes, body)])
+    cells = 1
+    for a in axes:
+        cells *= a.extent.value
+    g = _graph(kern, ins, [tensor("out", out_shape, "f32")])
+    return g, kern, _launch(kern, ["X", "W", "out"], cells)
 

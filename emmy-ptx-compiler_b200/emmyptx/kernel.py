@@ -103,6 +103,8 @@ def algorithmic_work(handle: dict) -> tuple[float, str]:
                 distinct *= e if c else 1
             read += size[d] * distinct
         return float(read + n * size[prog["out_dtype"]]), "B"
+    if v == "contract_indexed":
+        return 2.0 * p["n"] * p["terms"], "flop"
     if v == "gemm":
         return 2.0 * p["m"] * p["n"] * p["k"], "flop"
     if v == "gemm_f32":

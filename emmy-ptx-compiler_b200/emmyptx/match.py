@@ -1238,6 +1238,104 @@ def match_attention_scalar(graph, kernel, launch: dict) -> dict:
     raise Unmatched("the loops are not softmax(q k^T * scale) v, unmasked or with the lower-triangular mask")
 
 
+def match_loop_contraction(graph, kernel, launch: dict) -> dict:
+    """A Tile with one cell per output element whose nested Loops fold `a[...] * b[...]` into one accumulator with `add`:
+    the reference's convolution cases written as scalar loops (tools/torch_cases/conv.py:6-7 lowered as in
+    emmyptx/kernel.py:786-797). The statement shape is checked structurally -- a chain of up to three Loops, the
+    innermost holding Load, Load, Assign multiply, Accum add and nothing else; the accumulator seeded with zero exactly
+    once -- and the three index expressions are run on probe values of the tile's and the loops' variables, fitted as
+    affine maps, verified on every probe and checked against the buffers' sizes over the whole iteration space."""
+    tensors = tensor_table(graph)
+    tiles = [s for s in kernel.body if _kind(s) == "Tile"]
+    if len(kernel.body) != 1 or len(tiles) != 1:
+        raise Unmatched("a loop contraction is one Tile")
+    tile = tiles[0]
+    if not 1 <= len(tile.axes) <= 6:
+        raise Unmatched("1 to 6 tile axes")
+    body = [s for s in tile.body if _kind(s) not in ("Sync",)]
+    inits = [s for s in body if _kind(s) == "Init"]
+    rest = [s for s in body if _kind(s) != "Init"]
+    if len(rest) != 2 or _kind(rest[0]) not in ("Loop",) or _kind(rest[1]) != "Write" or len(inits) > 1 or (inits and body[0] is not inits[0]):
+        raise Unmatched("a loop contraction is [Init,] Loop, Write")
+    chain, node = [], rest[0]
+    while True:
+        chain.append(node)
+        if len(node.body) == 1 and _kind(node.body[0]) == "Loop":
+            node = node.body[0]
+            continue
+        break
+    if len(chain) > 3:
+        raise Unmatched("more than 3 nested reduction loops")
+    inner = chain[-1].body
+    if [_kind(s) for s in inner] != ["Load", "Load", "Assign", "Accum"]:
+        raise Unmatched("the innermost loop is Load, Load, Assign multiply, Accum add")
+    la, lb, mul, acc = inner
+    if len(la.names) != 1 or len(lb.names) != 1 or mul.op.name != "multiply" or sorted(map(str, mul.args)) != sorted([la.names[0], lb.names[0]]) \
+            or la.names[0] == lb.names[0]:
+        raise Unmatched("the product is of the two loaded values")
+    ident = getattr(acc.op, "identity", None)
+    if acc.op.name != "add" or acc.value != mul.name or acc.base not in (None, acc.name) or (ident is not None and float(ident) != 0.0):
+        raise Unmatched("the accumulator folds the product with add")
+    # seeded with zero exactly once: by an Init in front when the innermost Loop does not seed, else by a lone seeding Loop
+    inner_seeds = bool(getattr(chain[-1], "seed", True))
+    if inner_seeds and len(chain) > 1:
+        raise Unmatched("the innermost loop would reset the accumulator on every outer trip")
+    if not inner_seeds and not (inits and inits[0].name == acc.name and float(inits[0].identity) == 0.0):
+        raise Unmatched("the accumulator is not seeded with zero")
+    write = rest[1]
+    if list(write.values) != [acc.name] or write.output not in tensors:
+        raise Unmatched("the Write stores the accumulator")
+    extents = [int(a.extent.as_static()) for a in tile.axes]
+    loops = [int(lp.axis.extent.as_static()) for lp in chain]
+    names = [a.name for a in tile.axes] + [lp.axis.name for lp in chain]
+    if len(set(names)) != len(names) or min(extents + loops) < 1:
+        raise Unmatched("axis names are distinct and extents positive")
+    n = math.prod(extents)
+    if n > 2**31 - 1:
+        raise Unmatched(f"a tile of {n} cells has no contraction variant")
+    for nm in (la.input, lb.input):
+        if nm not in tensors or tensors[nm][1] not in ("f32", "f16", "bf16"):
+            raise Unmatched("contraction inputs are float buffers")
+    out_name = write.output
+    if tensors[out_name][1] not in ("f32", "f16", "bf16"):
+        raise Unmatched("the contraction writes a float buffer")
+    # probe points of the joint iteration space: the origin, every unit vector, the far corner and random points
+    all_ext = extents + loops
+    rng = np.random.default_rng(2)
+    pts = [np.zeros(len(all_ext), np.int64), np.asarray(all_ext, np.int64) - 1]
+    pts += [np.eye(len(all_ext), dtype=np.int64)[a] for a, e in enumerate(all_ext) if e > 1]
+    pts += [rng.integers(0, all_ext) for _ in range(200)]
+    pts = np.unique(np.stack(pts), axis=0)
+    digits = [pts[:, a] for a in range(len(all_ext))]
+    it = CellInterpreter(tensors, np.arange(len(pts), dtype=np.int64), INT_OPS)
+    for nm, d in zip(names, digits):
+        it.env[nm] = d
+    fits = {}
+    for key, buf, index in (("a", la.input, la.index), ("b", lb.input, lb.index), ("out", out_name, write.index)):
+        free = set()
+        for e in index:
+            free |= e.free_vars() if hasattr(e, "free_vars") else set()
+        if free - set(names) or (key == "out" and free - set(names[:len(extents)])):
+            raise Unmatched(f"the index of {buf!r} uses something other than the axis variables")
+        off, coef = _fit_affine(it.flat_index(buf, index), digits, f"the index of {buf!r}")
+        lo, hi = _reach(off, coef, all_ext)
+        if lo < 0 or hi >= math.prod(tensors[buf][0]):
+            raise Unmatched(f"the index of {buf!r} leaves the buffer (elements {lo}..{hi} of {math.prod(tensors[buf][0])})")
+        fits[key] = (off, coef)
+    o_off, o_coef = fits["out"]
+    order = sorted((abs(c), e) for c, e in zip(o_coef[:len(extents)], extents) if e > 1)       # no two cells may write one element
+    span = 0
+    for c, e in order:
+        if c <= span:
+            raise Unmatched("two cells write the same element")
+        span += c * (e - 1)
+    na = len(extents)
+    side = lambda key, buf: {"buffer": buf, "offset": fits[key][0], "coef": fits[key][1][:na], "loop_coef": fits[key][1][na:], "dtype": tensors[buf][1]}
+    cmap = {"extents": extents, "loops": loops, "a": side("a", la.input), "b": side("b", lb.input),
+            "out": {"offset": o_off, "coef": o_coef[:na], "dtype": tensors[out_name][1]}}
+    return {"variant": "contract_indexed", "inputs": [la.input, lb.input], "outputs": [out_name], "params": {"n": n, "terms": math.prod(loops), "map": cmap}}
+
+
 def match_kernel(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
     kinds = {_kind(s) for s in walk(kernel.body)}
     if "MmaSyncPtx" in kinds:
@@ -1245,7 +1343,13 @@ def match_kernel(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
     if "Accum" in kinds:
         loops = [s for s in walk(kernel.body) if _kind(s) in ("Loop", "StridedLoop")]
         if any(_kind(x) in ("Loop", "StridedLoop") for lp in loops for x in walk(lp.body)):
-            return match_attention_scalar(graph, kernel, launch)            # loops that nest: a dot product per key
+            try:
+                return match_attention_scalar(graph, kernel, launch)        # loops that nest: a dot product per key
+            except Unmatched as first:
+                try:
+                    return match_loop_contraction(graph, kernel, launch)    # or a sum of products over several axes
+                except Unmatched as second:
+                    raise Unmatched(f"{first}; {second}") from None
         try:
             return match_dot(graph, kernel, launch)
         except Unmatched:

@@ -119,6 +119,8 @@ def launch(handle: dict, bufs: dict, stream=None, scalars: dict | None = None) -
         flat = iter(t.reshape(-1) for t in ins)
         tensors = [None if "axis" in src else next(flat) for src in p["index_map"]["inputs"]]
         runtime.pointwise_indexed(p["program"], p["index_map"], tensors, out.reshape(-1), stream=stream)
+    elif v == "contract_indexed":
+        runtime.contract_indexed(p["map"], ins[0].reshape(-1), ins[1].reshape(-1), out.reshape(-1), stream=stream)
     elif v == "index_gather_i32":
         runtime.index_gather(ins[0].reshape(-1), p["mul"], p["add"], p["div"], p["shift"], p["trunc"], out=out.reshape(-1),
                              stream=stream)

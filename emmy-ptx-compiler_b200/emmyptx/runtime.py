@@ -45,6 +45,18 @@ class PwIndexMap(ctypes.Structure):
                 ("in_index_mult", ctypes.c_int64 * PW_MAX_INPUTS)]
 
 
+CT_MAX_LOOPS = 3
+
+
+class ContractionMap(ctypes.Structure):
+    _fields_ = [("n_axes", ctypes.c_int32), ("n_loops", ctypes.c_int32), ("extent", ctypes.c_int64 * PW_MAX_AXES),
+                ("loop_extent", ctypes.c_int64 * CT_MAX_LOOPS),
+                ("a_offset", ctypes.c_int64), ("a_coef", ctypes.c_int64 * PW_MAX_AXES), ("a_loop_coef", ctypes.c_int64 * CT_MAX_LOOPS),
+                ("b_offset", ctypes.c_int64), ("b_coef", ctypes.c_int64 * PW_MAX_AXES), ("b_loop_coef", ctypes.c_int64 * CT_MAX_LOOPS),
+                ("out_offset", ctypes.c_int64), ("out_coef", ctypes.c_int64 * PW_MAX_AXES),
+                ("a_dtype", ctypes.c_int32), ("b_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
 class PwProgram(ctypes.Structure):
     _fields_ = [("n_inputs", ctypes.c_int32), ("n_steps", ctypes.c_int32), ("out_slot", ctypes.c_int32),
                 ("out_dtype", ctypes.c_int32), ("in_dtype", ctypes.c_int32 * PW_MAX_INPUTS),
@@ -78,6 +90,8 @@ _SIGNATURES = {
     "emmyb200_pointwise_indexed": (ctypes.c_int, [ctypes.POINTER(PwProgram), ctypes.POINTER(PwIndexMap), ctypes.POINTER(ctypes.c_void_p),
                                                   ctypes.c_void_p, ctypes.c_void_p]),
     "emmyb200_pointwise_indexed_compile": (ctypes.c_int, [ctypes.POINTER(PwProgram), ctypes.POINTER(PwIndexMap), ctypes.POINTER(ctypes.c_int64)]),
+    "emmyb200_contract_indexed": (ctypes.c_int, [ctypes.POINTER(ContractionMap), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "emmyb200_contract_indexed_compile": (ctypes.c_int, [ctypes.POINTER(ContractionMap), ctypes.POINTER(ctypes.c_int64)]),
     "emmyb200_index_gather_i32": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                                  ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                                                  ctypes.c_void_p]),
@@ -273,6 +287,63 @@ def indexed_compile(program: dict, index_map: dict) -> int:
     prog, m = make_program(program), make_index_map(index_map)
     n = ctypes.c_int64(0)
     check(library().emmyb200_pointwise_indexed_compile(ctypes.byref(prog), ctypes.byref(m), ctypes.byref(n)))
+    return n.value
+
+
+def make_contraction_map(cmap: dict) -> ContractionMap:
+    """The C struct for {"extents": [...], "loops": [...], "a": {"offset", "coef", "loop_coef", "dtype"}, "b": {...},
+    "out": {"offset", "coef", "dtype"}}: out[cell] = sum over the loops of A[a-map] * B[b-map]."""
+    if not 1 <= len(cmap["extents"]) <= PW_MAX_AXES or not 1 <= len(cmap["loops"]) <= CT_MAX_LOOPS:
+        raise ValueError(f"a contraction has 1 to {PW_MAX_AXES} tile axes and 1 to {CT_MAX_LOOPS} reduction axes")
+    m = ContractionMap()
+    m.n_axes, m.n_loops = len(cmap["extents"]), len(cmap["loops"])
+    for a, e in enumerate(cmap["extents"]):
+        m.extent[a] = e
+    for l, e in enumerate(cmap["loops"]):
+        m.loop_extent[l] = e
+    for side in ("a", "b"):
+        src = cmap[side]
+        setattr(m, f"{side}_offset", src["offset"])
+        setattr(m, f"{side}_dtype", DTYPE_CODES[src["dtype"]])
+        for a, c in enumerate(src["coef"]):
+            getattr(m, f"{side}_coef")[a] = c
+        for l, c in enumerate(src["loop_coef"]):
+            getattr(m, f"{side}_loop_coef")[l] = c
+    m.out_offset, m.out_dtype = cmap["out"]["offset"], DTYPE_CODES[cmap["out"]["dtype"]]
+    for a, c in enumerate(cmap["out"]["coef"]):
+        m.out_coef[a] = c
+    return m
+
+
+def contract_indexed(cmap: dict, a, b, out, stream=None):
+    """out[cell] = sum over the map's reduction axes of a[...] * b[...] (fp32 fused multiply-adds in loop order), the
+    cell's digits and the loop counters addressing a and b through affine maps. Index ranges are checked against the
+    tensors here."""
+    _need_cuda(a, b, out)
+    ext, loops = cmap["extents"], cmap["loops"]
+
+    def reach(src, with_loops=True):
+        lo = hi = src["offset"]
+        terms = list(zip(src["coef"], ext)) + (list(zip(src["loop_coef"], loops)) if with_loops else [])
+        for c, e in terms:
+            lo, hi = lo + min(0, c * (e - 1)), hi + max(0, c * (e - 1))
+        return lo, hi
+    for name, t, src, wl in (("a", a, cmap["a"], True), ("b", b, cmap["b"], True), ("out", out, cmap["out"], False)):
+        if 0 in ext:
+            break                                   # an empty tile addresses nothing
+        lo, hi = reach(src, wl)
+        if lo < 0 or hi >= t.numel():
+            raise IndexError(f"contract_indexed: {name} is addressed at elements {lo}..{hi} of {t.numel()}")
+    m = make_contraction_map(cmap)
+    check(library().emmyb200_contract_indexed(ctypes.byref(m), a.data_ptr(), b.data_ptr(), out.data_ptr(), _stream(stream)))
+    return out
+
+
+def contraction_compile(cmap: dict) -> int:
+    """Compile an indexed contraction's kernel for sm_100a without launching it (works without a GPU)."""
+    m = make_contraction_map(cmap)
+    n = ctypes.c_int64(0)
+    check(library().emmyb200_contract_indexed_compile(ctypes.byref(m), ctypes.byref(n)))
     return n.value
 
 

@@ -167,6 +167,26 @@ int emmyb200_pointwise_indexed(const emmyb200_pw_program* program, const emmyb20
 /* Compiles the kernel of an indexed program for sm_100a without launching it (no device needed). */
 int emmyb200_pointwise_indexed_compile(const emmyb200_pw_program* program, const emmyb200_pw_index_map* map, int64_t* code_bytes);
 
+/* Contractions over nested loops with affine maps: a one-cell-per-output Tile whose body is up to three nested Loops
+ * folding A[...] * B[...] into an accumulator (emmyptx/kernel.py:786-797, emmyptx/loops.py:70-90) -- the reference's
+ * convolutions (tools/torch_cases/conv.py:6-7) and any other sum of products that is not a plain matrix product. The
+ * output cell's digits (as for emmyb200_pointwise_indexed) and the loops' counters address A and B through affine maps;
+ * terms are folded in loop order, one fused multiply-add each, in fp32; the result is rounded once to out_dtype and
+ * stored through the output map. One cell per thread, on the CUDA cores: sized for the reference's cases (48 to 72
+ * terms per output), not a tensor-core convolution. Always a kernel compiled at first use. */
+#define EMMYB200_CT_MAX_LOOPS 3
+typedef struct {
+    int32_t n_axes, n_loops;
+    int64_t extent[EMMYB200_PW_MAX_AXES];           /* tile axes, outermost first */
+    int64_t loop_extent[EMMYB200_CT_MAX_LOOPS];     /* reduction axes, outermost first */
+    int64_t a_offset, a_coef[EMMYB200_PW_MAX_AXES], a_loop_coef[EMMYB200_CT_MAX_LOOPS];
+    int64_t b_offset, b_coef[EMMYB200_PW_MAX_AXES], b_loop_coef[EMMYB200_CT_MAX_LOOPS];
+    int64_t out_offset, out_coef[EMMYB200_PW_MAX_AXES];
+    int32_t a_dtype, b_dtype, out_dtype, reserved;  /* EMMYB200_F32 / F16 / BF16 */
+} emmyb200_contraction_map;
+int emmyb200_contract_indexed(const emmyb200_contraction_map* map, const void* A, const void* B, void* out, void* cuda_stream);
+int emmyb200_contract_indexed_compile(const emmyb200_contraction_map* map, int64_t* code_bytes);
+
 /* The int32 index-math gather
  *     y[i] = (x[(i * mul + add) mod n] div d) xor (i >> shift),   0 <= i < n,
  * i.e. the s32 instruction stream of emmyptx/intmath.py:36-38, :87-117 and

@@ -87,3 +87,14 @@ LAYOUT_EXPECTED = {     # what each data-movement case computes, on the buffers 
     "s_cat_b": lambda b: np.concatenate([np.zeros((32, 64), np.float32), b["B"]], -1),
 }
 
+
+def conv_expected(case: str, b: dict) -> np.ndarray:
+    """The reference's convolution cases (tools/torch_cases/conv.py:6-7: stride 1, no padding, no bias, batch 1) in
+    float64 on the buffers of layout_buffers: out[o, i...] = sum over c and the taps of W[o, c, t...] * X[c, i + t...]."""
+    x, w = b["X"].astype(np.float64), b["W"].astype(np.float64)
+    taps = w.shape[2:]
+    win = np.lib.stride_tricks.sliding_window_view(x, taps, axis=tuple(range(1, x.ndim)))      # [c, i..., t...]
+    if case == "c_conv1d":
+        return np.einsum("oct,cit->oi", w, win)
+    return np.einsum("ocuv,cijuv->oij", w, win)
+

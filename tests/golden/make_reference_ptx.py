@@ -171,13 +171,17 @@ for name in LAYOUT:
     assert launch["grid"][0] * launch["block"][0] >= 1
     CASES[name] = (graph, kernel, launch)
 
+CONV = ["c_conv1d", "c_conv2d"]                                                                                         # conv.py:6-7
+for name in CONV:
+    CASES[name] = ir.conv_kernel(name, name=name)
+
 for name, (graph, kernel, launch) in CASES.items():
     ptx = compile_kernel(graph, kernel, launch, target="sm_89")
     (HERE / f"{name}.ref.ptx").write_text(ptx)
     manifest[name] = {"entry": kernel.name, "launch": launch, **({"gemm": dict(zip(("m", "n", "k", "dtype", "b_trans", "batch", "device"), GEMMS[name]), out_f32=name in GEMM_OUT,
                                        split_k=GEMM_OUT.get(name, (None, 1))[1])} if name in GEMMS else {}),
                       **({"attention": dict(zip(("units", "seq_q", "seq_k", "d", "causal", "scale"), ATTENTION[name]))} if name in ATTENTION else {}),
-                      **({"layout": True} if name in LAYOUT else {}),
+                      **({"layout": True} if name in LAYOUT or name in CONV else {}),
                       "tensors": {t.name: {"shape": [d.as_static() for d in t.shape], "dtype": t.dtype.name}
                                   for n in graph.nodes.values() for t in n.outputs}}
     print(f"{name}: {len(ptx.splitlines())} lines of PTX")

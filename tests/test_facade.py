@@ -387,3 +387,48 @@ def test_layout_kernels_become_indexed_programs():
     with pytest.raises(CompileError):
         handle((g, k, launch))
 
+
+def test_convolution_loops_become_an_indexed_contraction():
+    """Nested Loops folding w * x into one accumulator (tools/torch_cases/conv.py:6-7 as scalar loops): the three index
+    expressions are fitted over the tile's and the loops' variables and checked against the buffers."""
+    h = handle(ir.conv_kernel("c_conv1d"))
+    assert h["variant"] == "contract_indexed" and h["inputs"] == ["W", "X"] and h["outputs"] == ["out"]
+    assert h["params"]["map"] == {"extents": [32, 126], "loops": [16, 3],
+                                  "a": {"buffer": "W", "offset": 0, "coef": [48, 0], "loop_coef": [3, 1], "dtype": "f32"},
+                                  "b": {"buffer": "X", "offset": 0, "coef": [0, 1], "loop_coef": [128, 1], "dtype": "f32"},
+                                  "out": {"offset": 0, "coef": [126, 1], "dtype": "f32"}}
+    assert algorithmic_work(h) == (2.0 * 32 * 126 * 48, "flop")
+    h = handle(ir.conv_kernel("c_conv2d"))
+    assert h["params"]["map"]["b"] == {"buffer": "X", "offset": 0, "coef": [0, 32, 1], "loop_coef": [1024, 32, 1], "dtype": "f32"}
+    assert h["params"]["terms"] == 72 and h["params"]["n"] == 16 * 30 * 30
+
+    def inner(k):
+        lp = next(s for s in k.body[0].body if type(s).__name__ == "Loop")
+        while type(lp.body[0]).__name__ == "Loop":
+            lp = lp.body[0]
+        return lp
+    g, k, launch = ir.conv_kernel("c_conv1d")                       # a tap that runs past the row
+    inner(k).body[1].index[1] = ir.BinaryExpr("+", ir.BinaryExpr("+", ir.Var("i0"), ir.Var("t0")), ir.Literal(1, "int"))
+    with pytest.raises(CompileError, match="leaves the buffer"):
+        handle((g, k, launch))
+    g, k, launch = ir.conv_kernel("c_conv1d")                       # the innermost loop re-seeding the accumulator on every outer trip
+    inner(k).seed = True
+    with pytest.raises(CompileError, match="reset the accumulator"):
+        handle((g, k, launch))
+    g, k, launch = ir.conv_kernel("c_conv1d")                       # an accumulator nobody seeds
+    k.body[0].body.pop(0)
+    with pytest.raises(CompileError, match="not seeded"):
+        handle((g, k, launch))
+    g, k, launch = ir.conv_kernel("c_conv2d")                       # something other than a product
+    inner(k).body[2].op = ir.Op("add")
+    with pytest.raises(CompileError):
+        handle((g, k, launch))
+    g, k, launch = ir.conv_kernel("c_conv2d")                       # folding with max
+    inner(k).body[3].op = ir.Op("maximum")
+    with pytest.raises(CompileError):
+        handle((g, k, launch))
+    g, k, launch = ir.conv_kernel("c_conv1d")                       # an index that is not affine in the variables
+    inner(k).body[0].index[2] = ir.BinaryExpr("*", ir.Var("t0"), ir.Var("t0"))
+    with pytest.raises(CompileError):
+        handle((g, k, launch))
+

@@ -149,3 +149,19 @@ def test_launch_rejects_what_it_cannot_run(cuda, lib):
     broken = json.loads(text)
     broken["variant"] = "frobnicate"
     assert launch(lib, json.dumps(broken), [x, x]) == -4
+
+
+def test_contraction_handle(cuda, lib):
+    """A convolution written as scalar loops (tools/torch_cases/conv.py:7): the handle carries the three affine maps, the
+    runner passes X, W and out in the launch's argument order."""
+    import torch
+    from emmyptx import ir
+    built = ir.conv_kernel("c_conv2d")
+    assert built[2]["arg_order"] == ["X", "W", "out"]
+    x = torch.randn(8, 32, 32, device=cuda)
+    w = torch.randn(16, 8, 3, 3, device=cuda)
+    out = torch.zeros(16, 30, 30, device=cuda)
+    assert launch(lib, handle_text(built), [x, w, out]) == 0
+    ref = torch.nn.functional.conv2d(x.double()[None], w.double())[0]
+    assert torch.allclose(out.double(), ref, rtol=1e-5, atol=1e-4)
+

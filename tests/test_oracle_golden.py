@@ -178,3 +178,15 @@ def test_layout_fixture_is_what_numpy_computes(golden, case):
     bufs = inputs.layout_buffers(info["tensors"], info["launch"]["arg_order"])
     assert np.array_equal(golden[f"{case}.out"], np.ascontiguousarray(inputs.LAYOUT_EXPECTED[case](bufs)).astype(np.float32))
 
+
+@pytest.mark.parametrize("case", ["c_conv1d", "c_conv2d"])
+def test_convolution_fixture_is_the_float64_convolution(golden, case):
+    """The reference's PTX for its convolution cases (tools/torch_cases/conv.py:6-7), executed on the CPU, against the
+    float64 sum of the same products: within fp32 accumulation of 48 and 72 terms (the reference's own bar for this
+    category is its matmul tolerance class, tools/torch_cases/conv.py:6-7)."""
+    info = json.loads((GOLDEN / "reference_ptx_manifest.json").read_text())[case]
+    bufs = inputs.layout_buffers(info["tensors"], info["launch"]["arg_order"])
+    ref = inputs.conv_expected(case, bufs)
+    assert golden[f"{case}.out"].shape == ref.shape
+    assert np.abs(golden[f"{case}.out"].astype(np.float64) - ref).max() < 2e-5
+

@@ -74,3 +74,17 @@ def test_indexed_programs_compile_for_sm100a(lib):
     with pytest.raises(ValueError):
         rt.indexed_compile(prog, dict(imap, extents=[2] * 7, out={"offset": 0, "coef": [1] * 7}, inputs=[{"offset": 0, "coef": [1] * 7}, {"axis": 0}, {"axis": 1}]))
 
+
+def test_indexed_contractions_compile_for_sm100a(lib):
+    """The nested-loop sum of products (convolutions written as scalar loops) as a kernel compiled on this machine."""
+    cm = {"extents": [32, 126], "loops": [16, 3], "a": {"offset": 0, "coef": [48, 0], "loop_coef": [3, 1], "dtype": "f32"},
+          "b": {"offset": 0, "coef": [0, 1], "loop_coef": [128, 1], "dtype": "f32"}, "out": {"offset": 0, "coef": [126, 1], "dtype": "f32"}}
+    assert rt.contraction_compile(cm) > 1000
+    cm3 = {"extents": [16, 30, 30], "loops": [8, 3, 3], "a": {"offset": 0, "coef": [72, 0, 0], "loop_coef": [9, 3, 1], "dtype": "bf16"},
+           "b": {"offset": 0, "coef": [0, 32, 1], "loop_coef": [1024, 32, 1], "dtype": "f16"}, "out": {"offset": 0, "coef": [900, 30, 1], "dtype": "bf16"}}
+    assert rt.contraction_compile(cm3) > 1000
+    with pytest.raises(ValueError):
+        rt.contraction_compile(dict(cm, loops=[2, 2, 2, 2]))
+    with pytest.raises(rt.KernelError):
+        rt.contraction_compile(dict(cm, out={"offset": 0, "coef": [126, 1], "dtype": "i32"}))
+

@@ -76,6 +76,8 @@ def accepted_cases(ir):
     for case in ("s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_repeat", "s_stack", "s_tril", "s_cat_a", "s_cat_b", "s_roll",
                  "s_embedding", "s_gather", "c_avg_pool1d", "c_max_pool2d"):
         yield case, ir.layout_kernel(case)
+    for case in ("c_conv1d", "c_conv2d"):
+        yield case, ir.conv_kernel(case)
     for op in ROW_OPS:
         yield f"row_{op}", ir.rowwise_kernel(op, 64, 256)
     for op in ("sum", "amax", "softmax"):
