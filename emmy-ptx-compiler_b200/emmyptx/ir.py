@@ -390,7 +390,7 @@ def index_gather_kernel(n: int, mul: int = 7919, add: int = 13, div: int = 3, sh
 
 
 def matmul_f32_kernel(m: int, n: int, k: int, batch: int = 1, b_trans: bool = False, b_batched: bool = True, bias: bool = False,
-                      relu: bool = False, name: str = "k_mm_f32"):
+                      relu: bool = False, name: str = "k_mm_f32", a_trans: bool = False):
     """A float32 product the way the reference lowers it without tensor-core statements: one tile cell per output
     element, a loop over K folding a * b into an accumulator (emmyptx/kernel.py:786-797; the fma is formed from the
     multiply feeding the Accum), then the optional bias and ReLU, then the store."""
@@ -398,10 +398,11 @@ def matmul_f32_kernel(m: int, n: int, k: int, batch: int = 1, b_trans: bool = Fa
     lead = [Var("b0")] if batch > 1 else []
     b_lead = lead if (b_batched and batch > 1) else []
     b_index = b_lead + ([Var("n0"), Var("k0")] if b_trans else [Var("k0"), Var("n0")])
-    body = [Loop(Axis("k0", Dim(k)), [Load(["a"], "A", lead + [Var("m0"), Var("k0")]), Load(["b"], "B", b_index),
+    a_index = lead + ([Var("k0"), Var("m0")] if a_trans else [Var("m0"), Var("k0")])           # a.t() @ b reads A[k, m]
+    body = [Loop(Axis("k0", Dim(k)), [Load(["a"], "A", a_index), Load(["b"], "B", b_index),
                                       Assign("p", Op("multiply"), ["a", "b"]), Accum("acc", None, "p", Op("add"))])]
     out = "acc"
-    ins = [tensor("A", ([batch] if batch > 1 else []) + [m, k], "f32"),
+    ins = [tensor("A", ([batch] if batch > 1 else []) + ([k, m] if a_trans else [m, k]), "f32"),
            tensor("B", ([batch] if b_lead else []) + ([n, k] if b_trans else [k, n]), "f32")]
     if bias:
         ins.append(tensor("bias", [n], "f32"))
@@ -740,4 +741,36 @@ def conv_kernel(case: str = "c_conv1d", name: str | None = None):
         cells *= a.extent.value
     g = _graph(kern, ins, [tensor("out", out_shape, "f32")])
     return g, kern, _launch(kern, ["X", "W", "out"], cells)
+
+
+def rename_buffers(built, mapping: dict):
+    """(graph, kernel, launch) with buffers renamed old -> new everywhere they are named: tensor and node names, Load
+    and Write targets, the launch's argument order. The builders above use fixed names (A, B, C, X, Y ...); a problem
+    of several kernels passes buffers on by name (tools/run_local.py:90-91, 132-133), so its kernels need names of
+    their own."""
+    graph, kernel, launch = built
+
+    def swap(x):
+        if isinstance(x, str):
+            return mapping.get(x, x)
+        if isinstance(x, list):
+            return [swap(v) for v in x]
+        if isinstance(x, dict):
+            return {swap(k) if k != "__node__" else k: (v if k == "__node__" else swap(v)) for k, v in x.items()}
+        return x
+    value_names = {n for s in _walk_statements(kernel.body) for n in (getattr(s, "names", None) or [getattr(s, "name", None)]) if isinstance(n, str)}
+    clash = value_names & (set(mapping) | set(mapping.values()))
+    if clash:
+        raise ValueError(f"{sorted(clash)} name values inside the kernel: not buffers, or new names that would shadow them")
+    g2 = from_jsonable(swap(to_jsonable(graph)))
+    k2 = next(n.op for n in g2.nodes.values() if type(n.op).__name__ == "KernelOp")
+    return g2, k2, swap(launch)
+
+
+def _walk_statements(body):
+    for s in body:
+        yield s
+        sub = getattr(s, "body", None)
+        if isinstance(sub, list):
+            yield from _walk_statements(sub)
 

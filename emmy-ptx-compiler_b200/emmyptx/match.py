@@ -1353,5 +1353,12 @@ def match_kernel(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
         try:
             return match_dot(graph, kernel, launch)
         except Unmatched:
+            pass
+        try:
             return match_rowwise(graph, kernel, launch)
+        except Unmatched as first:
+            try:
+                return match_loop_contraction(graph, kernel, launch)        # a product with other strides: a.t() @ b
+            except Unmatched:
+                raise first from None
     return match_streaming(graph, kernel, launch, int_div)

@@ -5,16 +5,26 @@ Same roles, same names: `init()` (`run_local.py:51-61`), `load(text, entry)` (`:
 reference, a kernel handle here -- and `k` is the kernel's entry of `meta.json`: `args` in parameter order,
 each with `name`, `dtype`, `shape` and one of `seed` (input number: `default_rng(seed).standard_normal`),
 `data`, `intermediate` (produced by an earlier kernel of the problem) or nothing (zeroed), and `output`.
+`run_problem(pdir, target, level)` (`:116-141`) runs a problem folder -- `meta.json` (the kernels in launch order,
+`rtol`, `atol`), one `<entry>.ir.json` per kernel, `expected.npz` -- compiling each kernel with this package's
+`compile.py`, feeding every output forward by name and checking the ones `expected.npz` holds; `main()` is the same
+command line (`python -m emmyptx.run_local <problems folder> [--only PREFIX] [--level N]`, `:144-160`).
 Buffers are created the way the reference's runner creates them, live in device memory for the duration of
 the call, and outputs come back as numpy arrays (bf16 widened to float32, as `from_device` does).
 """
 from __future__ import annotations
 
+import argparse
 import json
+import subprocess
+import sys
+from pathlib import Path
 
 import numpy as np
 
 from . import runtime
+
+ROOT = Path(__file__).resolve().parent.parent          # the folder that holds compile.py
 
 DTYPES = {"f32": np.float32, "f16": np.float16, "f64": np.float64, "i32": np.int32, "i64": np.int64,
           "bool": np.bool_, "bf16": np.uint16}
@@ -153,3 +163,57 @@ def launch(handle: dict, bufs: dict, stream=None, scalars: dict | None = None) -
         runtime.colwise(p["op"], x, p["eps"], out=out.reshape(x.shape if is_map else (p["outer"], p["cols"])), stream=stream)
     else:
         raise RuntimeError(f"unknown kernel variant {v!r}")
+
+
+def run_problem(pdir: Path, target: str, level: int | None = None) -> tuple[bool, str]:
+    """Compile and run the kernels of one problem folder in order; (passed, one line of detail). Outputs are kept by
+    name for later kernels (`intermediate` arguments) and compared with `expected.npz` where it has them."""
+    pdir = Path(pdir)
+    meta = json.loads((pdir / "meta.json").read_text())
+    with np.load(pdir / "expected.npz") as z:
+        expected = {name: z[name] for name in z.files}
+    produced, lines = {}, []
+    for k in meta["kernels"]:
+        cmd = [sys.executable, str(ROOT / "compile.py"), str(pdir / f"{k['entry']}.ir.json"), "--target", target]
+        if level is not None:
+            cmd += ["--level", str(level)]
+        done = subprocess.run(cmd, capture_output=True, text=True)
+        if done.returncode != 0:
+            last = (done.stderr.strip().splitlines() or ["?"])[-1]
+            return False, f"compile.py failed: {last}"
+        try:
+            outputs = run_kernel(done.stdout, k, produced)
+        except RuntimeError as e:
+            return False, str(e).splitlines()[0]
+        produced.update(outputs)
+        for name, got in outputs.items():
+            if name not in expected:
+                continue
+            want = expected[name].astype(np.float64)
+            have = np.asarray(got).reshape(want.shape).astype(np.float64)
+            worst = float(np.abs(have - want).max()) if want.size else 0.0
+            if not np.allclose(have, want, rtol=meta["rtol"], atol=meta["atol"]):
+                return False, f"{name}: max abs err {worst:.3e} (rtol={meta['rtol']} atol={meta['atol']})"
+            lines.append(f"{name}: max abs err {worst:.3e}")
+    return True, "; ".join(lines)
+
+
+def main(argv: list[str] | None = None) -> int:
+    ap = argparse.ArgumentParser(description="Run every problem of a folder on the local GPU.")
+    ap.add_argument("problems", type=Path, help="a problems folder")
+    ap.add_argument("--only", default="", help="only problems whose name starts with this")
+    ap.add_argument("--level", type=int, choices=(0, 1, 2), help="accepted for compatibility; the kernels are prebuilt")
+    args = ap.parse_args(argv)
+    target = init()
+    found = sorted(p for p in args.problems.iterdir() if (p / "meta.json").exists() and p.name.startswith(args.only))
+    passed = 0
+    for p in found:
+        ok, detail = run_problem(p, target, args.level)
+        passed += bool(ok)
+        print(f"{'PASS' if ok else 'FAIL'}  {p.name:28s} {detail}", flush=True)
+    print(f"\n{passed}/{len(found)} passed on the local GPU ({target})")
+    return 0 if passed == len(found) else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -432,3 +432,17 @@ def test_convolution_loops_become_an_indexed_contraction():
     with pytest.raises(CompileError):
         handle((g, k, launch))
 
+
+def test_transposed_lhs_is_an_indexed_contraction_and_sm_100_is_a_target():
+    h = handle(ir.matmul_f32_kernel(128, 80, 96, a_trans=True))                 # a.t() @ b: A walked with stride m
+    assert h["variant"] == "contract_indexed" and h["params"]["map"]["loops"] == [96]
+    assert handle(ir.matmul_f32_kernel(128, 80, 96))["variant"] == "gemm_f32"   # the row-major product keeps its kernel
+    assert handle(ir.rowwise_kernel("dot", 64, 256))["variant"] == "rowwise_f32"
+    # a runner passes the name it derives from the device's compute capability (tools/run_local.py:57-60)
+    assert json.loads(compile_kernel(*ir.pointwise_kernel(64), target="sm_100"))["variant"] == "pointwise_f32"
+    renamed = ir.rename_buffers(ir.matmul_f32_kernel(32, 256, 128, b_trans=True, bias=True), {"A": "inp", "B": "w1", "bias": "b1", "C": "h1"})
+    h = handle(renamed)
+    assert h["inputs"] == ["inp", "w1", "b1"] and h["outputs"] == ["h1"] and h["arg_order"] == ["inp", "w1", "b1", "h1"]
+    with pytest.raises(ValueError):
+        ir.rename_buffers(ir.rowwise_kernel("rms_norm", 64, 256), {"X": "x"})    # would shadow the loaded value x
+

@@ -96,3 +96,20 @@ def test_a_larger_convolution(cuda):
     torch.cuda.synchronize()
     ref = torch.nn.functional.conv2d(x.double()[None], w.double())[0]
     assert torch.allclose(out.double(), ref, rtol=1e-5, atol=5e-4)
+
+
+def test_transposed_lhs_product(cuda):
+    """m_transpose_lhs (tools/torch_cases/matmul.py:20): a.t() @ b with a stored [k, m]. The float32 GEMM reads A row-major,
+    so the facade serves this product with the indexed contraction (one reduction axis, A walked with stride m)."""
+    import torch
+    g, k, launch = ir.matmul_f32_kernel(128, 80, 96, a_trans=True, name="m_transpose_lhs")
+    handle = json.loads(compile_kernel(g, k, launch))
+    assert handle["variant"] == "contract_indexed" and handle["params"]["map"]["a"]["loop_coef"] == [128]
+    a, b = torch.randn(96, 128, device=cuda), torch.randn(96, 80, device=cuda)
+    out = torch.zeros(128, 80, device=cuda)
+    run_local.init()
+    run_local.launch(handle, {"A": a, "B": b, "C": out})
+    torch.cuda.synchronize()
+    assert torch.allclose(out.double(), a.double().T @ b.double(), **MM)
+    assert torch.allclose(out.double(), a.double().T @ b.double(), rtol=1e-5, atol=1e-4)
+
