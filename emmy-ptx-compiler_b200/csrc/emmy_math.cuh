@@ -280,14 +280,57 @@ EMMY_HD float emmy_tanh_mag_from_exp(float a, float e) {      // a = |x|, e = e^
     return (a < EMMY_TANH_SMALL) ? small : big;
 }
 
+// On the device the fused form takes its two exponentials from the special-function unit instead of the
+// polynomial (which occupies the FP32 pipe this kernel is bound by): with t = fl(x log2 e) and
+// r = x - t ln2 (two fused multiply-adds, exact to about 2^-49 t), e^x = 2^t e^r = ex2(t) (1 + r) and
+// e^-|x| = ex2(-|t|) (1 -+ r); r is below 2^-18, so the first-order factor is exact to 2^-37. `ex2.approx` is
+// good to 2^-22, so E carries up to about 2.5 ulp. tanh(|x|) = (1 - w) / (1 + w) with w = e^{-2|x|} <= 1 -- the
+// form whose numerator loses the least (relative error of w times w / (1 - w)) -- with the reciprocal taken
+// unrefined, above |x| = 0.125; below it the three-term series a - a^3/3 + 2 a^5/15 (truncation 2e-7 relative
+// at the boundary). Both inaccuracies sit where sin(x) tanh(x) ~ x^2 is small against e^x ~ 1, so they vanish
+// in the sum: the composite is held to the same bound in ulps of its largest term as before. The host build
+// keeps the polynomial form above (no special-function unit there); the two agree to that bound, not bit for bit.
+#define EMMY_FUSED_TANH_SERIES 0.125f
+#if defined(__CUDACC__)
+__device__ __forceinline__ float emmy_ex2_approx(float t) {
+    float p;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(t));
+    return p;
+}
+__device__ __forceinline__ float emmy_rcp_approx(float a) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
+    return r;
+}
+// (e^x, tanh|x|) for |x| <= EMMY_FUSED_MAX from the quantities above; a = |x|.
+__device__ __forceinline__ void emmy_exp_tanh_mufu(float x, float a, float* e_out, float* tanh_out) {
+    const float t = emmy_mul(x, EMMY_LOG2E);
+    float r = fmaf(t, -EMMY_LN2_HI, x);
+    r = fmaf(t, -EMMY_LN2_LO, r);
+    const float p = emmy_ex2_approx(t), pn = emmy_ex2_approx(-fabsf(t));
+    *e_out = fmaf(p, r, p);
+    const float en = fmaf(pn, x > 0.0f ? -r : r, pn);                  // e^-|x|
+    const float big = emmy_mul(fmaf(-en, en, 1.0f), emmy_rcp_approx(fmaf(en, en, 1.0f)));
+    const float z = emmy_mul(a, a);
+    const float small = fmaf(emmy_mul(a, z), fmaf(z, 0.13333333f, -0.33333334f), a);
+    *tanh_out = a < EMMY_FUSED_TANH_SERIES ? small : big;
+}
+#endif
+
 EMMY_HD float emmy_exp_sin_tanh(float x) {
     float a = fabsf(x);
     if (a <= EMMY_FUSED_MAX) {
-        float e = emmy_exp_core(x);
         int32_t q;
         float r = emmy_trig_reduce(a, &q);
         float s = emmy_sincos_kernel(r, q);
+#if defined(__CUDA_ARCH__)
+        float e, th;
+        emmy_exp_tanh_mufu(x, a, &e, &th);
+        return emmy_add(e, emmy_mul(s, th));
+#else
+        float e = emmy_exp_core(x);
         return emmy_add(e, emmy_mul(s, emmy_tanh_mag_from_exp(a, e)));
+#endif
     }
     return emmy_add(emmy_expf(x), emmy_mul(emmy_sinf(x), emmy_tanhf(x)));
 }

@@ -124,7 +124,21 @@ __device__ __forceinline__ float2 tanh_mag_from_exp2(float2 a, float2 e) {
 // tanh are both odd, so their product is taken on |x|: the two sign transfers cancel exactly.
 __device__ __forceinline__ float2 exp_sin_tanh2(float2 x) {
     const float2 a = make_float2(fabsf(x.x), fabsf(x.y));
-    const float2 e = exp_core2(x), s = sincos2<false, true>(a), t = tanh_mag_from_exp2(a, e);
+    const float2 s = sincos2<false, true>(a);
+    // the exponentials from the special-function unit, step for step as emmy_exp_tanh_mufu
+    const float2 tt = mul2(x, f2(EMMY_LOG2E));
+    float2 r = fma2(tt, f2(-EMMY_LN2_HI), x);
+    r = fma2(tt, f2(-EMMY_LN2_LO), r);
+    const float2 p = make_float2(emmy_ex2_approx(tt.x), emmy_ex2_approx(tt.y));
+    const float2 pn = make_float2(emmy_ex2_approx(-fabsf(tt.x)), emmy_ex2_approx(-fabsf(tt.y)));
+    const float2 e = fma2(p, r, p);
+    const float2 en = fma2(pn, make_float2(x.x > 0.0f ? -r.x : r.x, x.y > 0.0f ? -r.y : r.y), pn);
+    const float2 nen = make_float2(-en.x, -en.y);
+    const float2 num = fma2(nen, en, f2(1.0f)), den = fma2(en, en, f2(1.0f));
+    const float2 big = mul2(num, make_float2(emmy_rcp_approx(den.x), emmy_rcp_approx(den.y)));
+    const float2 z = mul2(a, a);
+    const float2 small = fma2(mul2(a, z), fma2(z, f2(0.13333333f), f2(-0.33333334f)), a);
+    const float2 t = make_float2(a.x < EMMY_FUSED_TANH_SERIES ? small.x : big.x, a.y < EMMY_FUSED_TANH_SERIES ? small.y : big.y);
     // scalar product and sum: a packed mul feeding a packed add was observed to be fused into one fma
     return make_float2(__fadd_rn(e.x, __fmul_rn(s.x, t.x)), __fadd_rn(e.y, __fmul_rn(s.y, t.y)));
 }

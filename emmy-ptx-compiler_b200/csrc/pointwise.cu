@@ -33,13 +33,19 @@ template <int OP>
 __global__ void __launch_bounds__(kThreads) pointwise_vec4_kernel(const float4* x, float4* y, int64_t n4,
                                                                    const float* x_tail, float* y_tail, int tail) {
     const int64_t stride = (int64_t)gridDim.x * kThreads;
-    for (int64_t base = (int64_t)blockIdx.x * kThreads + threadIdx.x; base < n4; base += stride * kVecPerTrip) {
-        float4 v[kVecPerTrip];
+    int64_t base = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    // The vectors of the next trip are requested before this trip's arithmetic starts (a few hundred instructions per
+    // thread), so a warp's own work covers its memory latency instead of the other warps' alone.
+    float4 v[kVecPerTrip];
 #pragma unroll
-        for (int k = 0; k < kVecPerTrip; ++k) {
-            int64_t idx = base + k * stride;
-            if (idx < n4) v[k] = __ldcs(x + idx);
-        }
+    for (int k = 0; k < kVecPerTrip; ++k)
+        if (base + k * stride < n4) v[k] = __ldcs(x + base + k * stride);
+    for (; base < n4; base += stride * kVecPerTrip) {
+        const int64_t next = base + stride * kVecPerTrip;
+        float4 ahead[kVecPerTrip];
+#pragma unroll
+        for (int k = 0; k < kVecPerTrip; ++k)
+            if (next + k * stride < n4) ahead[k] = __ldcs(x + next + k * stride);
 #pragma unroll
         for (int k = 0; k < kVecPerTrip; ++k) {
             int64_t idx = base + k * stride;
@@ -65,6 +71,8 @@ __global__ void __launch_bounds__(kThreads) pointwise_vec4_kernel(const float4* 
                 __stcs(y + idx, r);
             }
         }
+#pragma unroll
+        for (int k = 0; k < kVecPerTrip; ++k) v[k] = ahead[k];
     }
     if (blockIdx.x == 0 && (int)threadIdx.x < tail) y_tail[threadIdx.x] = apply_op<OP>(x_tail[threadIdx.x]);
 }
@@ -77,10 +85,20 @@ __global__ void __launch_bounds__(kThreads) pointwise_scalar_kernel(const float*
     for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) y[i] = apply_op<OP>(x[i]);
 }
 
+// CTAs of a kernel that fit one SM at once (registers decide: 40 per thread leave room for 6 CTAs of 256 threads,
+// not 8). A grid-stride grid larger than what is resident runs a second, thin wave with little latency hiding.
+template <typename K>
+static int resident_ctas(K kernel) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+    return per_sm;
+}
+
 template <int OP>
 static int launch_pointwise(const float* x, float* y, int64_t n, cudaStream_t stream) {
-    const int64_t max_blocks = (int64_t)sm_count() * 8;
     if (aligned(x, 16) && aligned(y, 16)) {
+        static const int per_sm = resident_ctas(pointwise_vec4_kernel<OP>);
+        const int64_t max_blocks = (int64_t)sm_count() * per_sm;
         int64_t n4 = n / 4;
         int tail = (int)(n - n4 * 4);
         int64_t want = (n4 + (int64_t)kThreads * kVecPerTrip - 1) / ((int64_t)kThreads * kVecPerTrip);
@@ -89,6 +107,8 @@ static int launch_pointwise(const float* x, float* y, int64_t n, cudaStream_t st
             reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), n4, x + n4 * 4, y + n4 * 4, tail);
         return launch_status("pointwise_vec4_kernel");
     }
+    static const int per_sm_scalar = resident_ctas(pointwise_scalar_kernel<OP>);
+    const int64_t max_blocks = (int64_t)sm_count() * per_sm_scalar;
     int64_t want = (n + kThreads - 1) / kThreads;
     int64_t blocks = want > max_blocks ? max_blocks : want;
     pointwise_scalar_kernel<OP><<<(unsigned)blocks, kThreads, 0, stream>>>(x, y, n);

@@ -838,7 +838,17 @@ static int compile_source(const std::string& src, std::vector<char>* cubin) {
 struct JitKernel {
     cudaLibrary_t library = nullptr;
     cudaKernel_t kernel = nullptr;
+    int ctas_per_sm = 8;            // 256-thread CTAs resident per SM (the kernel's registers decide), asked once at load
 };
+
+// Grid-stride kernels are sized to what is resident at once: a grid larger than that runs a thin last wave.
+static void ask_residency(JitKernel* k) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, reinterpret_cast<const void*>(k->kernel), 256, 0) == cudaSuccess && per_sm >= 1)
+        k->ctas_per_sm = per_sm;
+    else
+        cudaGetLastError();         // an older runtime that does not take kernel handles here: keep the default
+}
 
 static std::mutex g_jit_mutex;
 static std::map<std::string, JitKernel>& jit_cache() {
@@ -871,6 +881,7 @@ int pw_jit_launch(const emmyb200_pw_program& prog, const void* const* inputs, vo
             if (e != cudaSuccess) return cuda_fail(e, "cudaLibraryLoadData (specialised elementwise kernel)");
             e = cudaLibraryGetKernel(&k.kernel, k.library, "pw_jit_kernel");
             if (e != cudaSuccess) { cudaLibraryUnload(k.library); return cuda_fail(e, "cudaLibraryGetKernel (specialised elementwise kernel)"); }
+            ask_residency(&k);
             g_jit_compiles.fetch_add(1);
             it = jit_cache().emplace(key, k).first;
         }
@@ -890,7 +901,7 @@ int pw_jit_launch(const emmyb200_pw_program& prog, const void* const* inputs, vo
     const int per = group == 8 ? 8 : 4;
     const int64_t groups = (n + per - 1) / per;
     const int64_t want = (groups + 256 * 2 - 1) / (256 * 2);
-    const int64_t cap = (int64_t)sm_count() * 8;
+    const int64_t cap = (int64_t)sm_count() * k.ctas_per_sm;
     const unsigned blocks = (unsigned)(want < cap ? want : cap);
     cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(k.kernel), dim3(blocks), dim3(256), args, 0, stream);
     if (e != cudaSuccess) return cuda_fail(e, "launch of the specialised elementwise kernel");

@@ -48,3 +48,32 @@ def test_all_inputs_within_two_ulp(op, cuda):
     print(f"{op}: worst error over all 2^32 inputs = {worst:.4f} ulp")
     assert bad == 0
     assert worst <= 2.0
+
+
+def test_fused_expression_over_its_whole_fast_range(cuda):
+    """exp(x) + sin(x) * tanh(x) on every float with 2^-20 <= |x| <= 40 -- the range the fused form (exponentials from
+    the special-function unit, tanh from e^{-2|x|}) serves -- against float64 on the same device: within 5 ulp of the
+    largest term (the sum cancels near x = -3.18, so output-ulps say nothing there) and far inside the reference's
+    class for this case, rtol = atol = 1e-5 (tools/torch_cases/pointwise.py:8-57)."""
+    import torch
+    from emmyptx import runtime
+    lo = torch.tensor(2.0 ** -20, dtype=torch.float32).view(torch.int32).item()
+    hi = torch.tensor(40.0, dtype=torch.float32).view(torch.int32).item()
+    chunk = 2 ** 26
+    worst, worst_class = 0.0, 0.0
+    for sign in (0, -2 ** 31):
+        for start in range(lo, hi + 1, chunk):
+            n = min(chunk, hi + 1 - start)
+            x = (torch.arange(n, dtype=torch.int64, device=cuda) + start + sign).to(torch.int32).view(torch.float32)
+            y = runtime.pointwise("exp_sin_tanh", x).double()
+            xd = x.double()
+            e, st = torch.exp(xd), torch.sin(xd) * torch.tanh(xd)
+            ref = e + st
+            scale = torch.maximum(torch.maximum(e.abs(), st.abs()), ref.abs()).float()
+            ulp = torch.ldexp(torch.ones_like(ref), (torch.frexp(scale).exponent.to(torch.int64) - 24).clamp(min=-149))
+            worst = max(worst, float(((y - ref).abs() / ulp).max()))
+            worst_class = max(worst_class, float(((y - ref).abs() / (1e-5 * ref.abs() + 1e-5)).max()))
+    print(f"fused expression: worst {worst:.3f} ulp of the largest term; {worst_class:.4f} of the rtol = atol = 1e-5 class")
+    assert worst <= 5.0
+    assert worst_class <= 0.1
+
