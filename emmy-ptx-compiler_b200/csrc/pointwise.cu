@@ -25,8 +25,14 @@ __device__ __forceinline__ float apply_op(float x) {
     else return emmy_gelu_tanhf(x);
 }
 
-constexpr int kThreads = 256;
-constexpr int kVecPerTrip = 2;     // float4 loads in flight per thread
+#ifndef EMMY_PW_THREADS
+#define EMMY_PW_THREADS 256
+#endif
+#ifndef EMMY_PW_VECS
+#define EMMY_PW_VECS 4
+#endif
+constexpr int kThreads = EMMY_PW_THREADS;
+constexpr int kVecPerTrip = EMMY_PW_VECS;     // float4 vectors per thread and trip (and as many again requested ahead)
 
 // x and y are not __restrict__: the op may run in place.
 template <int OP>
