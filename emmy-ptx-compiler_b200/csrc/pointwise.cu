@@ -31,12 +31,15 @@ __device__ __forceinline__ float apply_op(float x) {
 #ifndef EMMY_PW_VECS
 #define EMMY_PW_VECS 4
 #endif
+#ifndef EMMY_PW_MIN_CTAS
+#define EMMY_PW_MIN_CTAS 1
+#endif
 constexpr int kThreads = EMMY_PW_THREADS;
 constexpr int kVecPerTrip = EMMY_PW_VECS;     // float4 vectors per thread and trip (and as many again requested ahead)
 
 // x and y are not __restrict__: the op may run in place.
 template <int OP>
-__global__ void __launch_bounds__(kThreads) pointwise_vec4_kernel(const float4* x, float4* y, int64_t n4,
+__global__ void __launch_bounds__(kThreads, EMMY_PW_MIN_CTAS) pointwise_vec4_kernel(const float4* x, float4* y, int64_t n4,
                                                                    const float* x_tail, float* y_tail, int tail) {
     const int64_t stride = (int64_t)gridDim.x * kThreads;
     int64_t base = (int64_t)blockIdx.x * kThreads + threadIdx.x;
