@@ -266,9 +266,14 @@ __device__ __forceinline__ void pw_st1(void* p, i64 i, float v) {
     reinterpret_cast<float*>(p)[i] = v;
 #elif PW_OUT_DT == 1
     unsigned short h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(v)); reinterpret_cast<unsigned short*>(p)[i] = h;
+#elif PW_OUT_DT == 5
+    reinterpret_cast<unsigned char*>(p)[i] = v != 0.0f ? 1 : 0;          // a bool output: 1 where the value is non-zero
 #else
     unsigned short h; asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(v)); reinterpret_cast<unsigned short*>(p)[i] = h;
 #endif
+}
+__device__ __forceinline__ unsigned pw_pack4b(float a, float b, float c, float d) {     // four bool bytes
+    return (a != 0.0f ? 1u : 0u) | (b != 0.0f ? 0x100u : 0u) | (c != 0.0f ? 0x10000u : 0u) | (d != 0.0f ? 0x1000000u : 0u);
 }
 __device__ __forceinline__ unsigned pw_pack2(float lo, float hi) {      // two values rounded to the 16-bit output type
     unsigned w;
@@ -284,6 +289,10 @@ __device__ __forceinline__ void pw_stv(void* p, i64 g, const PwVec& y) {       /
 #pragma unroll
     for (int q = 0; q < PW_G / 4; ++q)
         __stcs(reinterpret_cast<float4*>(p) + g * (PW_G / 4) + q, make_float4(y.v[4 * q], y.v[4 * q + 1], y.v[4 * q + 2], y.v[4 * q + 3]));
+#elif PW_OUT_DT == 5 && PW_G == 4
+    __stcs(reinterpret_cast<unsigned*>(p) + g, pw_pack4b(y.v[0], y.v[1], y.v[2], y.v[3]));
+#elif PW_OUT_DT == 5
+    __stcs(reinterpret_cast<uint2*>(p) + g, make_uint2(pw_pack4b(y.v[0], y.v[1], y.v[2], y.v[3]), pw_pack4b(y.v[4], y.v[5], y.v[6], y.v[7])));
 #elif PW_G == 4
     __stcs(reinterpret_cast<uint2*>(p) + g, make_uint2(pw_pack2(y.v[0], y.v[1]), pw_pack2(y.v[2], y.v[3])));
 #else
@@ -693,8 +702,8 @@ extern "C" __global__ void __launch_bounds__(256) ct_kernel(const void* a, const
 }
 )SHELL";
 
-static bool float_program(const emmyb200_pw_program& p) {
-    return p.out_dtype == EMMYB200_F32 || p.out_dtype == EMMYB200_F16 || p.out_dtype == EMMYB200_BF16;
+static bool float_program(const emmyb200_pw_program& p) {          // computed in fp32; a byte output holds value != 0
+    return p.out_dtype == EMMYB200_F32 || p.out_dtype == EMMYB200_F16 || p.out_dtype == EMMYB200_BF16 || p.out_dtype == EMMYB200_U8;
 }
 
 // How input k is read: 0 element i; 1 a broadcast input gathered element by element; 2 a row vector whose length is a
@@ -915,6 +924,7 @@ static int check_program(const emmyb200_pw_program* prog, const char* who, const
         return fail(EMMYB200_ERR_ARG, "%s: not a program (inputs, steps or output slot out of range)", who);
     const bool ints = prog->out_dtype == EMMYB200_I32 || prog->out_dtype == EMMYB200_I64;
     if (!float_program(*prog) && !ints) return fail(EMMYB200_ERR_UNSUPPORTED, "%s: output dtype %d", who, prog->out_dtype);
+    if (map != nullptr && prog->out_dtype == EMMYB200_U8) return fail(EMMYB200_ERR_UNSUPPORTED, "%s: indexed programs write f32 / f16 / bf16 / i32 / i64", who);
     for (int k = 0; k < prog->n_inputs; ++k) {
         const int d = prog->in_dtype[k];
         const bool index_source = map != nullptr && map->in_kind[k] == 3;          // read as an integer, never as a program value

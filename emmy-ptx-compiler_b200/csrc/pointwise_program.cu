@@ -93,6 +93,7 @@ __device__ __forceinline__ float pw_load1(const void* base, int dtype, int64_t i
 __device__ __forceinline__ void pw_store1(void* base, int dtype, int64_t i, float v) {
     if (dtype == EMMYB200_F32) reinterpret_cast<float*>(base)[i] = v;
     else if (dtype == EMMYB200_F16) reinterpret_cast<__half*>(base)[i] = __float2half_rn(v);
+    else if (dtype == EMMYB200_U8) reinterpret_cast<uint8_t*>(base)[i] = v != 0.0f ? 1 : 0;          // a bool output
     else reinterpret_cast<__nv_bfloat16*>(base)[i] = __float2bfloat16_rn(v);
 }
 
@@ -201,6 +202,9 @@ __global__ void __launch_bounds__(kPwThreads, 3) pointwise_program_kernel(const 
                 } else if (prog.out_dtype == EMMYB200_F16) {
                     const __half2 lo = __floats2half2_rn(y.x, y.y), hi = __floats2half2_rn(y.z, y.w);
                     __stcs(reinterpret_cast<uint2*>(args.out) + g, make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi)));
+                } else if (prog.out_dtype == EMMYB200_U8) {
+                    const uint32_t w = (y.x != 0.0f ? 1u : 0u) | (y.y != 0.0f ? 0x100u : 0u) | (y.z != 0.0f ? 0x10000u : 0u) | (y.w != 0.0f ? 0x1000000u : 0u);
+                    __stcs(reinterpret_cast<uint32_t*>(args.out) + g, w);
                 } else {
                     const __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
                     __stcs(reinterpret_cast<uint2*>(args.out) + g, make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi)));
@@ -311,7 +315,8 @@ extern "C" int emmyb200_pointwise_program(const emmyb200_pw_program* prog, const
     const bool int_program = prog->out_dtype == EMMYB200_I32 || prog->out_dtype == EMMYB200_I64;
     auto float_ok = [](int d) { return d == EMMYB200_F32 || d == EMMYB200_F16 || d == EMMYB200_BF16; };
     auto int_ok = [](int d) { return d == EMMYB200_I32 || d == EMMYB200_I64; };
-    if (!int_program && !float_ok(prog->out_dtype)) return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_program: output dtype %d", prog->out_dtype);
+    if (!int_program && !float_ok(prog->out_dtype) && prog->out_dtype != EMMYB200_U8)
+        return fail(EMMYB200_ERR_UNSUPPORTED, "pointwise_program: output dtype %d", prog->out_dtype);
     for (int k = 0; k < prog->n_inputs; ++k) {
         const int d = prog->in_dtype[k];
         if (int_program ? !int_ok(d) : !(float_ok(d) || d == EMMYB200_U8))

@@ -13,7 +13,7 @@ from __future__ import annotations
 import json
 import math
 
-from .match import Unmatched, match_kernel
+from .match import tensor_table, Unmatched, match_kernel
 from .ops import OpError
 
 TARGET = "sm_100a"
@@ -44,6 +44,10 @@ class KernelCompiler:
 
     def match(self) -> dict:
         """The kernel variant and its parameters, as a dict."""
+        # as the reference: an f64 buffer is refused rather than silently computed in f32 (emmyptx/kernel.py:185-187)
+        for name, (_, dtype) in tensor_table(self.graph).items():
+            if dtype == "f64" and name in self.launch["arg_order"]:
+                raise CompileError(f"buffer {name!r} is f64: these kernels compute in f32, which would silently lose the f64 precision")
         try:
             m = match_kernel(self.graph, self.kernel, self.launch, self.int_div)
         except (Unmatched, OpError) as e:

@@ -626,7 +626,8 @@ def _match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dic
             prog["in_div"], prog["in_mod"] = [pattern[b][0] for b in prog["inputs"]], [pattern[b][1] for b in prog["inputs"]]
         return {"variant": "pointwise_program", "params": {"n": n, "program": {k: v for k, v in prog.items() if k != "inputs"}},
                 "inputs": prog["inputs"], "outputs": [out_name]}
-    general = (tensors[out_name][1] in float_types and all(tensors[b][1] in float_types + ("bool", "u8") for b in buffers)
+    # a bool / byte output holds 1 where the program's value is non-zero (a comparison stored as it is: `x > y`)
+    general = (tensors[out_name][1] in float_types + ("bool", "u8") and all(tensors[b][1] in float_types + ("bool", "u8") for b in buffers)
                and (identity or broadcast) and bool(buffers))
     if general and (used_scalars or broadcast or not (len(buffers) == 1 and tensors[next(iter(buffers))][1] == "f32" and tensors[out_name][1] == "f32")):
         prog = build_program(tile, tensors, out_name, tile.body[-1].values[0] if _kind(tile.body[-1]) == "Write" else None, scalars=scalars)

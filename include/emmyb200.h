@@ -39,7 +39,7 @@ extern "C" {
 #define EMMYB200_BF16 2
 #define EMMYB200_I32 3
 #define EMMYB200_I64 4   /* integer programs only: computed in 32 bits, as the reference does (emmyptx/kernel.py:41) */
-#define EMMYB200_U8 5    /* a bool / byte input of a float program: 0 or 1 */
+#define EMMYB200_U8 5    /* a bool / byte buffer of a float program: an input reads as 0 or 1, an output holds value != 0 */
 
 int emmyb200_version(void);
 

@@ -446,3 +446,13 @@ def test_transposed_lhs_is_an_indexed_contraction_and_sm_100_is_a_target():
     with pytest.raises(ValueError):
         ir.rename_buffers(ir.rowwise_kernel("rms_norm", 64, 256), {"X": "x"})    # would shadow the loaded value x
 
+
+def test_f64_buffers_are_refused_and_bool_outputs_are_programs():
+    """d_f64_add (tools/torch_cases/dtypes.py:13): the reference refuses an f64 buffer rather than compute it in f32
+    (emmyptx/kernel.py:185-187), and so does this compiler. p_cmp_bool_out (pointwise.py:50): a comparison stored to a
+    bool buffer is an elementwise program with a byte output."""
+    with pytest.raises(CompileError, match="is f64"):
+        handle(ir.elementwise_kernel(1024, {"x": "f64"}, [("a", "multiply", ["x", 2.0]), ("b", "add", ["a", 1.0])], "f64"))
+    h = handle(ir.elementwise_kernel(4096, {"x": "f32", "y": "f32"}, [("m", "greater", ["x", "y"])], "bool"))
+    assert h["variant"] == "pointwise_program" and h["params"]["program"]["out_dtype"] == "bool"
+

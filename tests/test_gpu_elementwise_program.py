@@ -101,6 +101,19 @@ CASES = {
                               ("p0", "add", ["p1m", 1.0]), ("at", "multiply", ["p0", "u"]), ("a2", "multiply", ["at", 2.0]),
                               ("big", "greater", ["ax", 1.0]), ("co", "subtract", [1.5707963267948966, "a2"]), ("r", "where", ["big", "co", "a2"]),
                               ("neg", "less", ["x", 0.0]), ("nr", "negative", ["r"]), ("out", "where", ["neg", "nr", "r"])], "torch.atan(x)", TRANS),
+    # atan2(x, y): the angle of (y, x) -- atan of min / max of the magnitudes as in p_atan (one halving, series to u^11),
+    # then pi/2 - a where |x| > |y|, pi - a where y < 0, and the sign of x
+    "p_atan2": ({"x": "f32", "y": "f32"}, [("ax", "abs", ["x"]), ("ay", "abs", ["y"]), ("lo", "minimum", ["ax", "ay"]), ("hi", "maximum", ["ax", "ay"]),
+                                           ("t", "divide", ["lo", "hi"]), ("t2", "square", ["t"]), ("q", "add", ["t2", 1.0]), ("sq", "sqrt", ["q"]),
+                                           ("dn", "add", ["sq", 1.0]), ("u", "divide", ["t", "dn"]), ("u2", "square", ["u"]),
+                                           ("p5", "multiply", ["u2", -0.09090909090909091]), ("p4", "add", ["p5", 0.1111111111111111]), ("p4m", "multiply", ["p4", "u2"]),
+                                           ("p3", "add", ["p4m", -0.14285714285714285]), ("p3m", "multiply", ["p3", "u2"]), ("p2", "add", ["p3m", 0.2]),
+                                           ("p2m", "multiply", ["p2", "u2"]), ("p1", "add", ["p2m", -0.3333333333333333]), ("p1m", "multiply", ["p1", "u2"]),
+                                           ("p0", "add", ["p1m", 1.0]), ("at", "multiply", ["p0", "u"]), ("a2", "multiply", ["at", 2.0]),
+                                           ("steep", "greater", ["ax", "ay"]), ("co", "subtract", [1.5707963267948966, "a2"]), ("r1", "where", ["steep", "co", "a2"]),
+                                           ("left", "less", ["y", 0.0]), ("su", "subtract", [3.141592653589793, "r1"]), ("r2", "where", ["left", "su", "r1"]),
+                                           ("neg", "less", ["x", 0.0]), ("nr", "negative", ["r2"]), ("out", "where", ["neg", "nr", "r2"])], "torch.atan2(x, y)", TRANS),
+    "p_cmp_bool_out": ({"x": "f32", "y": "f32"}, [("m", "greater", ["x", "y"])], "x > y", ROUND),
     "p_pow_tensor": ({"x": "f32", "y": "f32"}, [("a", "abs", ["x"]), ("b", "add", ["a", 0.1]), ("c", "pow", ["b", "y"])], "torch.pow(x.abs() + 0.1, y)", (1e-4, 1e-5)),
     "p_masked_fill": ({"x": "f32"}, [("m", "less", ["x", 0.0]), ("a", "where", ["m", 0.0, "x"])], "x.masked_fill(x < 0, 0.0)", ROUND),
     # fmod keeps the dividend's sign: a - b * trunc(a / b)
@@ -108,7 +121,7 @@ CASES = {
                               ("g", "floor_divide", ["n", 1.0]), ("c", "negative", ["g"]), ("m", "greater_equal", ["q", 0.0]), ("t", "where", ["m", "f", "c"]),
                               ("p", "multiply", ["t", 1.5]), ("r", "subtract", ["a", "p"])], "torch.fmod(x * 5, 1.5)", TRANS),
 }
-OUT_DTYPE = {"d_f16_gelu": "f16", "d_f16_add": "f16", "d_bf16_add": "bf16", "d_bf16_gelu": "bf16", "d_f32_to_f16": "f16"}
+OUT_DTYPE = {"p_cmp_bool_out": "bool", "d_f16_gelu": "f16", "d_f16_add": "f16", "d_bf16_add": "bf16", "d_bf16_gelu": "bf16", "d_f32_to_f16": "f16"}
 
 
 def _expected(expr, arrays):

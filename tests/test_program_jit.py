@@ -88,3 +88,12 @@ def test_indexed_contractions_compile_for_sm100a(lib):
     with pytest.raises(rt.KernelError):
         rt.contraction_compile(dict(cm, out={"offset": 0, "coef": [126, 1], "dtype": "i32"}))
 
+
+def test_bool_outputs_compile_in_every_group(lib):
+    """A comparison stored to a byte buffer (1 where the value is non-zero): scalar stores, four bytes and eight bytes a group."""
+    S = rt.PW_MAX_SLOTS
+    prog = {"in_dtypes": ["f32", "f32"], "out_dtype": "bool", "out_slot": 2, "consts": [], "steps": [["greater", 2, 0, 1, 0]]}
+    for group in (0, 4, 8):
+        assert "#define PW_OUT_DT 5" in rt.program_source(prog, group)
+    assert rt.program_compile(prog) > 1000
+
