@@ -402,30 +402,40 @@ template <int DT, int BC> __device__ __forceinline__ PwVec pw_in(const void* p, 
 static const char kKernel[] = R"SHELL(
 #define PW_THREADS 256
 #define PW_UNROLL 2
+// The inputs of one trip (PW_UNROLL groups, `stride` groups apart, from group g0): every load is issued before any use.
+__device__ __forceinline__ void pw_trip(PwVec* x0, PwVec* x1, PwVec* x2, PwVec* x3, const void* p0, const void* p1, const void* p2, const void* p3,
+                                        i64 g0, i64 stride, i64 groups, i64 n, const PwBcast& bc) {
+#pragma unroll
+    for (int u = 0; u < PW_UNROLL; ++u) {
+        const i64 g = g0 + u * stride;
+#pragma unroll
+        for (int k = 0; k < PW_G; ++k) x0[u].v[k] = x1[u].v[k] = x2[u].v[k] = x3[u].v[k] = (PW_T)0;
+        if (g < groups) {
+            x0[u] = pw_in<PW_DT0, PW_BC0>(p0, g, n, bc.div[0], bc.mod[0]);
+#if PW_N_IN > 1
+            x1[u] = pw_in<PW_DT1, PW_BC1>(p1, g, n, bc.div[1], bc.mod[1]);
+#endif
+#if PW_N_IN > 2
+            x2[u] = pw_in<PW_DT2, PW_BC2>(p2, g, n, bc.div[2], bc.mod[2]);
+#endif
+#if PW_N_IN > 3
+            x3[u] = pw_in<PW_DT3, PW_BC3>(p3, g, n, bc.div[3], bc.mod[3]);
+#endif
+        }
+    }
+}
 extern "C" __global__ void __launch_bounds__(PW_THREADS) pw_jit_kernel(const void* p0, const void* p1, const void* p2, const void* p3,
                                                                        void* out, i64 n, PwConsts c, PwBcast bc) {
     const i64 groups = PW_VEC ? n / PW_G : (n + PW_G - 1) / PW_G;
     const i64 stride = (i64)gridDim.x * PW_THREADS;
-    for (i64 g0 = (i64)blockIdx.x * PW_THREADS + threadIdx.x; g0 < groups; g0 += stride * PW_UNROLL) {
-        PwVec x0[PW_UNROLL], x1[PW_UNROLL], x2[PW_UNROLL], x3[PW_UNROLL];
-#pragma unroll
-        for (int u = 0; u < PW_UNROLL; ++u) {               // every load of the trip is issued before the first use
-            const i64 g = g0 + u * stride;
-#pragma unroll
-            for (int k = 0; k < PW_G; ++k) x0[u].v[k] = x1[u].v[k] = x2[u].v[k] = x3[u].v[k] = (PW_T)0;
-            if (g < groups) {
-                x0[u] = pw_in<PW_DT0, PW_BC0>(p0, g, n, bc.div[0], bc.mod[0]);
-#if PW_N_IN > 1
-                x1[u] = pw_in<PW_DT1, PW_BC1>(p1, g, n, bc.div[1], bc.mod[1]);
-#endif
-#if PW_N_IN > 2
-                x2[u] = pw_in<PW_DT2, PW_BC2>(p2, g, n, bc.div[2], bc.mod[2]);
-#endif
-#if PW_N_IN > 3
-                x3[u] = pw_in<PW_DT3, PW_BC3>(p3, g, n, bc.div[3], bc.mod[3]);
-#endif
-            }
-        }
+    i64 g0 = (i64)blockIdx.x * PW_THREADS + threadIdx.x;
+    // The next trip's inputs are requested before this trip's arithmetic starts, so a warp's own work covers its
+    // memory latency (programs with a transcendental or two would otherwise wait once per trip).
+    PwVec x0[PW_UNROLL], x1[PW_UNROLL], x2[PW_UNROLL], x3[PW_UNROLL];
+    pw_trip(x0, x1, x2, x3, p0, p1, p2, p3, g0, stride, groups, n, bc);
+    for (; g0 < groups; g0 += stride * PW_UNROLL) {
+        PwVec a0[PW_UNROLL], a1[PW_UNROLL], a2[PW_UNROLL], a3[PW_UNROLL];
+        pw_trip(a0, a1, a2, a3, p0, p1, p2, p3, g0 + stride * PW_UNROLL, stride, groups, n, bc);
 #pragma unroll
         for (int u = 0; u < PW_UNROLL; ++u) {
             const i64 g = g0 + u * stride;
@@ -436,6 +446,8 @@ extern "C" __global__ void __launch_bounds__(PW_THREADS) pw_jit_kernel(const voi
                 pw_out(out, g, n, y);
             }
         }
+#pragma unroll
+        for (int u = 0; u < PW_UNROLL; ++u) { x0[u] = a0[u]; x1[u] = a1[u]; x2[u] = a2[u]; x3[u] = a3[u]; }
     }
 #if PW_VEC
     // the last n % PW_G elements of the vector form: one thread each, scalar accesses
