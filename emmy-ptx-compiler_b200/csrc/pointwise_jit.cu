@@ -429,13 +429,20 @@ extern "C" __global__ void __launch_bounds__(PW_THREADS) pw_jit_kernel(const voi
     const i64 groups = PW_VEC ? n / PW_G : (n + PW_G - 1) / PW_G;
     const i64 stride = (i64)gridDim.x * PW_THREADS;
     i64 g0 = (i64)blockIdx.x * PW_THREADS + threadIdx.x;
-    // The next trip's inputs are requested before this trip's arithmetic starts, so a warp's own work covers its
-    // memory latency (programs with a transcendental or two would otherwise wait once per trip).
     PwVec x0[PW_UNROLL], x1[PW_UNROLL], x2[PW_UNROLL], x3[PW_UNROLL];
+#if PW_AHEAD
+    // Programs of a few cheap steps: the next trip's inputs are requested before this trip's stores go out, so loads and
+    // stores of a thread overlap (measured at 2^26 elements: abs 94 -> 87 us, add 138 -> 132). Programs with a
+    // transcendental step keep the plain loop below: the doubled register set costs them more than the overlap gives
+    // (two-input SiLU gate 126 -> 142 us, 16-bit erf-GELU 81 -> 88).
     pw_trip(x0, x1, x2, x3, p0, p1, p2, p3, g0, stride, groups, n, bc);
     for (; g0 < groups; g0 += stride * PW_UNROLL) {
         PwVec a0[PW_UNROLL], a1[PW_UNROLL], a2[PW_UNROLL], a3[PW_UNROLL];
         pw_trip(a0, a1, a2, a3, p0, p1, p2, p3, g0 + stride * PW_UNROLL, stride, groups, n, bc);
+#else
+    for (; g0 < groups; g0 += stride * PW_UNROLL) {
+        pw_trip(x0, x1, x2, x3, p0, p1, p2, p3, g0, stride, groups, n, bc);
+#endif
 #pragma unroll
         for (int u = 0; u < PW_UNROLL; ++u) {
             const i64 g = g0 + u * stride;
@@ -446,8 +453,10 @@ extern "C" __global__ void __launch_bounds__(PW_THREADS) pw_jit_kernel(const voi
                 pw_out(out, g, n, y);
             }
         }
+#if PW_AHEAD
 #pragma unroll
         for (int u = 0; u < PW_UNROLL; ++u) { x0[u] = a0[u]; x1[u] = a1[u]; x2[u] = a2[u]; x3[u] = a3[u]; }
+#endif
     }
 #if PW_VEC
     // the last n % PW_G elements of the vector form: one thread each, scalar accesses
@@ -745,6 +754,13 @@ static std::string program_source(const emmyb200_pw_program& p, int group, const
     snprintf(line, sizeof line, "#define PW_N_IN %d\n#define PW_VEC %d\n#define PW_G %d\n#define PW_OUT_DT %d\n#define PW_T %s\n", p.n_inputs,
              group ? 1 : 0, group == 8 && !ints ? 8 : 4, p.out_dtype, type);
     s += line;
+    bool heavy = false;                 // a step that costs tens of instructions: such programs do not request inputs a trip ahead
+    for (int i = 0; i < p.n_steps && !ints; ++i) {
+        const int op = p.steps[i].op;
+        heavy = heavy || op == EMMYB200_PW_EXP || op == EMMYB200_PW_LOG || op == EMMYB200_PW_SIGMOID || op == EMMYB200_PW_TANH || op == EMMYB200_PW_ERF ||
+                op == EMMYB200_PW_SIN || op == EMMYB200_PW_COS || op == EMMYB200_PW_POW;
+    }
+    s += heavy || ints ? "#define PW_AHEAD 0\n" : "#define PW_AHEAD 1\n";
     for (int k = 0; k < EMMYB200_PW_MAX_INPUTS; ++k) {
         const bool used = k < p.n_inputs;
         snprintf(line, sizeof line, "#define PW_DT%d %d\n#define PW_BC%d %d\n", k, used ? p.in_dtype[k] : (ints ? EMMYB200_I32 : EMMYB200_F32), k, used ? modes[k] : 0);
