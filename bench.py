@@ -1184,6 +1184,28 @@ def other_workloads(torch, dist, dev, local_rank, pk, pk_kind, skip: str) -> dic
             torch.cuda.empty_cache()
     except Exception as e:  # noqa: BLE001
         out["next_rows"] = {"error": str(e)[:200]}
+    # convolutions written as scalar loops (tools/torch_cases/conv.py:6-7) through the indexed contraction: the
+    # reference's own c_conv2d shape (launch-bound) and a 64-channel 3 x 3 layer over a 256 x 256 image
+    try:
+        from emmyptx import runtime
+        for label, (c, o, h) in (("conv2d_8x32x32_k3", (8, 16, 32)), ("conv2d_64x256x256_k3", (64, 32, 256))):
+            x, w = torch.randn(c, h, h, device=dev), torch.randn(o, c, 3, 3, device=dev)
+            y = torch.zeros(o, h - 2, h - 2, device=dev)
+            cm = {"extents": [o, h - 2, h - 2], "loops": [c, 3, 3], "a": {"offset": 0, "coef": [c * 9, 0, 0], "loop_coef": [9, 3, 1], "dtype": "f32"},
+                  "b": {"offset": 0, "coef": [0, h, 1], "loop_coef": [h * h, h, 1], "dtype": "f32"},
+                  "out": {"offset": 0, "coef": [(h - 2) ** 2, h - 2, 1], "dtype": "f32"}}
+            run = lambda: runtime.contract_indexed(cm, w.reshape(-1), x.reshape(-1), y.reshape(-1))
+            run()
+            ref = torch.nn.functional.conv2d(x.double()[None], w.double())[0]
+            ok = bool(torch.allclose(y.double(), ref, rtol=1e-3, atol=1e-3))
+            reps = 200 if h <= 32 else 20
+            ms = timed(torch, dist, 1, run, reps, 3) / reps
+            flop = 2.0 * o * (h - 2) ** 2 * c * 9
+            out[label] = {"value": flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": ms, "kernel": "ct_kernel (CUDA cores, fp32 fused multiply-adds in loop order)",
+                          "parity": {"ok": ok, "rule": "allclose(rtol=1e-3, atol=1e-3) against torch conv2d in float64"}}
+            del x, w, y, ref
+    except Exception as e:  # noqa: BLE001
+        out["conv"] = {"error": str(e)[:200]}
     return out
 
 
