@@ -599,62 +599,70 @@ template <typename I> __device__ __forceinline__ void pw_ix_group(const void* p0
 #endif
 }
 #endif
-// A transposition between the innermost axis and axis PW_TAXIS (PW_TRANSPOSE 1): the one buffer input is contiguous along
-// PW_TAXIS, the output along the innermost axis. A CTA moves 32 x 32 tiles of those two axes through shared memory (rows
-// padded by one word), reading with the lanes along PW_TAXIS and writing with the lanes along the innermost axis, so
-// both sides are coalesced; the other axes count tiles. PW_TIN is the index of the buffer input among the inputs.
+// A transposition (PW_TRANSPOSE 1): the one buffer input is contiguous along axis PW_RAXIS, the output along another axis
+// PW_WAXIS (one of the two is the innermost axis). A CTA moves PW_TT x PW_TT tiles (64, or 32 when an axis is shorter than
+// 64) of those two axes through shared memory (rows padded by one word), reading with the lanes along PW_RAXIS and writing
+// with the lanes along PW_WAXIS, so both sides are coalesced, in runs of PW_TT elements; the other axes count tiles.
+// PW_TIN is the index of the buffer input among the inputs.
 #if PW_TRANSPOSE
 template <typename I> __device__ __forceinline__ void pw_ix_tiles(const void* p0, const void* p1, const void* p2, const void* p3, void* out,
-                                                                const PwConsts& c, const PwIndexArg& m, PW_T (*tile)[33]) {
+                                                                const PwConsts& c, const PwIndexArg& m, PW_T (*tile)[PW_TT + 1]) {
     const void* src = PW_TIN == 0 ? p0 : (PW_TIN == 1 ? p1 : (PW_TIN == 2 ? p2 : p3));
-    const I et = (I)m.extent[PW_TAXIS], el = (I)m.extent[PW_NAXES - 1];
-    const I tiles_t = (et + 31) / 32, tiles_l = (el + 31) / 32;
+    const I er = (I)m.extent[PW_RAXIS], ew = (I)m.extent[PW_WAXIS];
+    const I tiles_r = (er + PW_TT - 1) / PW_TT, tiles_w = (ew + PW_TT - 1) / PW_TT;
     I batch = 1;
 #pragma unroll
-    for (int a = 0; a < PW_NAXES - 1; ++a)
-        if (a != PW_TAXIS) batch *= (I)m.extent[a];
-    const i64 work = (i64)batch * tiles_t * tiles_l;
+    for (int a = 0; a < PW_NAXES; ++a)
+        if (a != PW_RAXIS && a != PW_WAXIS) batch *= (I)m.extent[a];
+    const i64 work = (i64)batch * tiles_r * tiles_w;
     const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
     for (i64 w = blockIdx.x; w < work; w += gridDim.x) {
         I rem = (I)w;
-        const I tl = rem % tiles_l; rem /= tiles_l;
-        const I tt = rem % tiles_t; rem /= tiles_t;
+        const I tw = rem % tiles_w; rem /= tiles_w;
+        const I tr = rem % tiles_r; rem /= tiles_r;
         I d[PW_NAXES > 0 ? PW_NAXES : 1];
 #pragma unroll
-        for (int a = PW_NAXES - 2; a >= 0; --a) {
-            if (a == PW_TAXIS) { d[a] = 0; continue; }
+        for (int a = PW_NAXES - 1; a >= 0; --a) {
+            if (a == PW_RAXIS || a == PW_WAXIS) { d[a] = 0; continue; }
             const I e = (I)m.extent[a];
             const I q = rem / e;
             d[a] = rem - q * e;
             rem = q;
         }
-        d[PW_NAXES - 1] = 0;
         I at = (I)m.in_offset[PW_TIN], to = (I)m.out_offset;
 #pragma unroll
         for (int a = 0; a < PW_NAXES; ++a) {
             at += (I)m.in_coef[PW_TIN][a] * d[a];
             to += (I)m.out_coef[a] * d[a];
         }
-        const I t0 = tt * 32, l0 = tl * 32;
+        const I r0 = tr * PW_TT, w0 = tw * PW_TT;
         __syncthreads();                                        // the previous tile has been read out
+        PW_T got[PW_TT / 8][PW_TT / 32];                        // every load of the tile is issued before the first shared store
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const I t = t0 + x, l = l0 + y + 8 * r;
-            if (t < et && l < el) tile[y + 8 * r][x] = pw_ld1<PW_TDT>(src, (i64)(at + t + (I)m.in_coef[PW_TIN][PW_NAXES - 1] * l));
-        }
+        for (int k = 0; k < PW_TT / 8; ++k)
+#pragma unroll
+            for (int q = 0; q < PW_TT / 32; ++q) {
+                const I r = r0 + x + 32 * q, v = w0 + y + 8 * k;
+                got[k][q] = (r < er && v < ew) ? pw_ld1<PW_TDT>(src, (i64)(at + r + (I)m.in_coef[PW_TIN][PW_WAXIS] * v)) : (PW_T)0;
+            }
+#pragma unroll
+        for (int k = 0; k < PW_TT / 8; ++k)
+#pragma unroll
+            for (int q = 0; q < PW_TT / 32; ++q) tile[y + 8 * k][x + 32 * q] = got[k][q];
         __syncthreads();
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const I l = l0 + x, t = t0 + y + 8 * r;
-            if (t < et && l < el) {
-                d[PW_TAXIS] = t;
-                d[PW_NAXES - 1] = l;
-                const PW_T v = tile[x][y + 8 * r];
-                const PW_T v0 = PW_KIND0 ? (PW_T)d[m.in_axis[0]] : v;
-                const PW_T v1 = PW_N_IN > 1 ? (PW_KIND1 ? (PW_T)d[m.in_axis[1]] : v) : (PW_T)0;
-                const PW_T v2 = PW_N_IN > 2 ? (PW_KIND2 ? (PW_T)d[m.in_axis[2]] : v) : (PW_T)0;
-                const PW_T v3 = PW_N_IN > 3 ? (PW_KIND3 ? (PW_T)d[m.in_axis[3]] : v) : (PW_T)0;
-                pw_st1(out, (i64)(to + (I)m.out_coef[PW_TAXIS] * t + l), pw_cell(v0, v1, v2, v3, c));
+        for (int kq = 0; kq < (PW_TT / 8) * (PW_TT / 32); ++kq) {
+            const int k = kq / (PW_TT / 32), q = kq % (PW_TT / 32);
+            const I v = w0 + x + 32 * q, r = r0 + y + 8 * k;
+            if (r < er && v < ew) {
+                d[PW_RAXIS] = r;
+                d[PW_WAXIS] = v;
+                const PW_T val = tile[x + 32 * q][y + 8 * k];
+                const PW_T v0 = PW_KIND0 ? (PW_T)d[m.in_axis[0]] : val;
+                const PW_T v1 = PW_N_IN > 1 ? (PW_KIND1 ? (PW_T)d[m.in_axis[1]] : val) : (PW_T)0;
+                const PW_T v2 = PW_N_IN > 2 ? (PW_KIND2 ? (PW_T)d[m.in_axis[2]] : val) : (PW_T)0;
+                const PW_T v3 = PW_N_IN > 3 ? (PW_KIND3 ? (PW_T)d[m.in_axis[3]] : val) : (PW_T)0;
+                pw_st1(out, (i64)(to + (I)m.out_coef[PW_RAXIS] * r + v), pw_cell(v0, v1, v2, v3, c));
             }
         }
     }
@@ -663,7 +671,7 @@ template <typename I> __device__ __forceinline__ void pw_ix_tiles(const void* p0
 extern "C" __global__ void __launch_bounds__(256) pw_ix_kernel(const void* p0, const void* p1, const void* p2, const void* p3, void* out, i64 n,
                                                                PwConsts c, PwIndexArg m) {
 #if PW_TRANSPOSE
-    __shared__ PW_T tile[32][33];
+    __shared__ PW_T tile[PW_TT][PW_TT + 1];
     if (m.narrow) pw_ix_tiles<int>(p0, p1, p2, p3, out, c, m, tile);
     else pw_ix_tiles<i64>(p0, p1, p2, p3, out, c, m, tile);
     return;
@@ -741,8 +749,10 @@ struct IndexedForm {        // how the indexed kernel walks the tile (chosen on 
     int ivec[EMMYB200_PW_MAX_INPUTS] = {0, 0, 0, 0};      // input k is read with one vector access per group
     int ovec = 0;           // the output is written with one vector access per group
     int special = 0;        // 1: some map rotates an axis or takes an index from data: the one-cell form with spelled-out loads
-    int transpose = 0;      // 1: 32 x 32 tiles of (taxis, innermost axis) through shared memory
-    int taxis = 0, tin = 0; // the axis the buffer input is contiguous along; which input that is
+    int transpose = 0;      // 1: square tiles of (taxis, innermost axis) through shared memory
+    int ttile = 32;         // their side: 64 when both axes are at least that long
+    int taxis = 0, tin = 0; // the axis (other than the innermost) the transposition is against; which input the buffer is
+    int swapped = 0;        // 0: the input is contiguous along taxis, the output along the innermost axis; 1: the other way round
 };
 
 static std::string program_source(const emmyb200_pw_program& p, int group, const int* modes, const emmyb200_pw_index_map* map = nullptr,
@@ -775,8 +785,10 @@ static std::string program_source(const emmyb200_pw_program& p, int group, const
         snprintf(line, sizeof line, "#define PW_INNER %d\n#define PW_IVEC0 %d\n#define PW_IVEC1 %d\n#define PW_IVEC2 %d\n#define PW_IVEC3 %d\n#define PW_OVEC %d\n",
                  f.inner, f.ivec[0], f.ivec[1], f.ivec[2], f.ivec[3], f.ovec);
         s += line;
-        snprintf(line, sizeof line, "#define PW_TRANSPOSE %d\n#define PW_TAXIS %d\n#define PW_TIN %d\n#define PW_TDT %d\n", f.transpose, f.taxis, f.tin,
-                 p.in_dtype[f.tin]);
+        snprintf(line, sizeof line, "#define PW_TT %d\n", f.ttile);
+        s += line;
+        snprintf(line, sizeof line, "#define PW_TRANSPOSE %d\n#define PW_RAXIS %d\n#define PW_WAXIS %d\n#define PW_TIN %d\n#define PW_TDT %d\n", f.transpose,
+                 f.swapped ? map->n_axes - 1 : f.taxis, f.swapped ? f.taxis : map->n_axes - 1, f.tin, p.in_dtype[f.tin]);
         s += line;
         snprintf(line, sizeof line, "#define PW_SPECIAL %d\n", f.special);
         s += line;
@@ -1056,9 +1068,15 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
         int buffers = 0, which = 0;
         for (int k = 0; k < prog->n_inputs; ++k)
             if (map->in_kind[k] != 1) { ++buffers; which = k; }
-        if (buffers == 1 && last >= 1 && map->out_coef[last] == 1 && map->in_coef[which][last] != 1 && map->extent[last] >= 32) {
-            for (int a = 0; a < last; ++a)
-                if (map->in_coef[which][a] == 1 && map->extent[a] >= 32) { form.transpose = 1; form.taxis = a; form.tin = which; break; }
+        if (buffers == 1 && last >= 1 && map->extent[last] >= 32) {
+            const bool out_inner = map->out_coef[last] == 1 && map->in_coef[which][last] != 1;         // reads stride along the innermost axis
+            const bool in_inner = map->in_coef[which][last] == 1 && map->out_coef[last] != 1;          // writes do
+            for (int a = 0; a < last && (out_inner || in_inner); ++a)
+                if ((out_inner ? map->in_coef[which][a] : map->out_coef[a]) == 1 && map->extent[a] >= 32) {
+                    form.transpose = 1; form.taxis = a; form.tin = which; form.swapped = in_inner ? 1 : 0;
+                    form.ttile = map->extent[a] >= 64 && map->extent[last] >= 64 ? 64 : 32;
+                    break;
+                }
         }
     }
     form.special = special ? 1 : 0;
@@ -1081,6 +1099,8 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
         key.push_back((char)form.ovec);
         key.push_back((char)form.transpose);
         key.push_back((char)form.taxis);
+        key.push_back((char)form.ttile);
+        key.push_back((char)form.swapped);
         key.push_back((char)form.tin);
         key.push_back((char)form.special);
         for (int k = 0; k < prog->n_inputs; ++k) { key.push_back((char)map->in_index_of[k]); key.push_back((char)(map->in_index_abs[k] != 0)); }
@@ -1124,7 +1144,7 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
     void* args[] = {&p[0], &p[1], &p[2], &p[3], &out, &count, &c, &m};
     int64_t want = (n / form.inner + 255) / 256;
     if (form.transpose) {
-        want = ((map->extent[form.taxis] + 31) / 32) * ((map->extent[last] + 31) / 32);
+        want = ((map->extent[form.taxis] + form.ttile - 1) / form.ttile) * ((map->extent[last] + form.ttile - 1) / form.ttile);
         for (int a = 0; a < last; ++a)
             if (a != form.taxis) want *= map->extent[a];
     }
@@ -1291,9 +1311,11 @@ extern "C" int emmyb200_pointwise_indexed_compile(const emmyb200_pw_program* pro
         rc = compile_source(program_source(*prog, 0, modes, &key_map, &form), &grouped);
         if (rc != EMMYB200_OK) return rc;
     }
-    if (map->n_axes >= 2) {                               // the tiled transposition, axis 0 against the innermost axis
+    for (int variant = 0; variant < 4 && map->n_axes >= 2; ++variant) {    // the tiled transposition, axis 0 against the innermost axis
         IndexedForm form;
         form.transpose = 1;
+        form.ttile = variant & 1 ? 64 : 32;
+        form.swapped = variant >> 1;
         for (int k = 0; k < prog->n_inputs; ++k)
             if (key_map.in_kind[k] == 0) form.tin = k;
         std::vector<char> tiled;

@@ -163,3 +163,34 @@ def test_rotation_and_data_dependent_rows_directly(cuda):
         rt.pointwise_indexed(prog, dict(imap, inputs=[imap["inputs"][0], {"offset": 0, "coef": [1, 0], "index_mod": 301}]), [table.reshape(-1), idx], emb.reshape(-1))
     assert rt.device_status() == 0
 
+
+@pytest.mark.parametrize("shape", [(96, 64), (100, 70), (257, 130), (64, 4096), (3, 65, 200), (2, 129, 64)])
+def test_transpositions_either_way(shape, cuda):
+    """The shared-memory tiled form with the tile laid out in output order (strided reads) and in input order (strided
+    writes), 32- and 64-wide tiles, ragged edges, a leading batch axis, f32 and bf16, against torch's transpose."""
+    import torch
+    from emmyptx import runtime as rt
+    *lead, r, c = shape
+    b = lead[0] if lead else 1
+    for dt, name in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+        x = torch.randn(b, r, c, device=cuda).to(dt)
+        want = x.transpose(1, 2).contiguous()
+        prog = {"in_dtypes": [name], "out_dtype": name, "out_slot": 0, "consts": [], "steps": []}
+        # cells in output order [b, c, r]: the input is read with stride c along the innermost axis
+        out = torch.zeros(b, c, r, device=cuda, dtype=dt)
+        m = {"extents": [b, c, r], "inputs": [{"offset": 0, "coef": [r * c, 1, c]}], "out": {"offset": 0, "coef": [r * c, r, 1]}}
+        rt.pointwise_indexed(prog, m, [x.reshape(-1)], out.reshape(-1))
+        assert torch.equal(out, want)
+        # cells in input order [b, r, c]: the output is written with stride r along the innermost axis
+        out2 = torch.zeros(b, c, r, device=cuda, dtype=dt)
+        m2 = {"extents": [b, r, c], "inputs": [{"offset": 0, "coef": [r * c, c, 1]}], "out": {"offset": 0, "coef": [r * c, 1, r]}}
+        rt.pointwise_indexed(prog, m2, [x.reshape(-1)], out2.reshape(-1))
+        assert torch.equal(out2, want)
+    # a program on the way: 2 x + 1 while transposing, cells in input order
+    x = torch.randn(r, c, device=cuda)
+    S = rt.PW_MAX_SLOTS
+    prog = {"in_dtypes": ["f32"], "out_dtype": "f32", "out_slot": 2, "consts": [2.0, 1.0], "steps": [["multiply", 1, 0, S, 0], ["add", 2, 1, S + 1, 0]]}
+    out = torch.zeros(c, r, device=cuda)
+    rt.pointwise_indexed(prog, {"extents": [r, c], "inputs": [{"offset": 0, "coef": [c, 1]}], "out": {"offset": 0, "coef": [1, r]}}, [x.reshape(-1)], out.reshape(-1))
+    assert torch.equal(out, (x * 2 + 1).t().contiguous())
+
