@@ -19,7 +19,7 @@ import math
 
 import numpy as np
 
-from .ops import FLOAT_OPS, INT_OPS, INT_OPS_TRUNC, OpError, Program, lower_int_op, lower_op
+from .ops import FLOAT_OPS, INT_OPS, INT_OPS_TRUNC, MOVE_OPS, OpError, Program, lower_int_op, lower_op
 
 INT_DTYPES = {"int", "i32", "i64", "int32", "int64", "u32", "u8", "i8"}      # emmyptx/kernel.py:41
 _FUNC_ALIASES = {"fmax": "maximum", "fmin": "minimum", "fabs": "abs"}       # emmyptx/kernel.py:55
@@ -243,7 +243,7 @@ PW_SLOTS, PW_CONSTS, PW_STEPS, PW_INPUTS = 16, 16, 48, 4
 PW_OP_NAMES = {"add", "subtract", "multiply", "divide", "maximum", "minimum", "relu", "square", "copy", "negative", "abs",
                "reciprocal", "sqrt", "rsqrt", "exp", "exp_fast", "log", "sigmoid", "tanh", "erf", "sin", "cos", "pow", "equal",
                "not_equal", "greater", "less", "greater_equal", "less_equal", "where", "bitwise_and", "bitwise_or",
-               "bitwise_not", "floor_divide", "mod", "remainder"}
+               "bitwise_not", "floor_divide", "mod", "remainder", *MOVE_OPS}
 
 
 def scalar_args(launch: dict) -> dict:
@@ -314,7 +314,7 @@ def build_program(tile, tensors: dict, out_name: str, out_value_name, integer: b
             raise Unmatched(f"more than {PW_SLOTS} live values")
         dst = free.pop()
         slot_of[s.name] = dst
-        steps.append([s.op.name, dst, *(ops + [0, 0])[:3]])
+        steps.append(["copy" if s.op.name in MOVE_OPS else s.op.name, dst, *(ops + [0, 0])[:3]])
         if s.name not in last_use:                                      # never read: its slot is free again at once
             free.append(dst)
     if len(steps) > PW_STEPS:

@@ -36,6 +36,10 @@ def _trunc_div_int(a, b):
     return _wrap32(np.where((a < 0) != (b < 0), -q, q))
 
 
+# Names the reference lowers as a plain register move (emmyptx/ops.py:236-237: the value is already fp32 in a register,
+# the narrowing or widening happened at the load or happens at the store).
+MOVE_OPS = ("pad", "from_f8e4m3", "from_f8e5m2", "to_f8e4m3", "to_f8e5m2")
+
 # name -> (arity, float64 meaning). Comparisons give 1.0 / 0.0 masks (the reference's convention, ops.py:116-120).
 FLOAT_OPS = {
     "add": (2, np.add), "subtract": (2, np.subtract), "multiply": (2, np.multiply), "divide": (2, np.divide),
@@ -51,6 +55,7 @@ FLOAT_OPS = {
     "floor_divide": (2, lambda a, b: np.floor(a / b)), "mod": (2, lambda a, b: a - b * np.floor(a / b)),
     "remainder": (2, lambda a, b: a - b * np.floor(a / b)),
 }
+FLOAT_OPS.update({name: FLOAT_OPS["copy"] for name in MOVE_OPS})
 
 # Integer ops work on wrapped int32 values. `floor_divide` / `mod` follow torch (round toward minus
 # infinity), the semantics the reference's cases are checked against (tools/torch_cases/dtypes.py:17-19);

@@ -456,3 +456,11 @@ def test_f64_buffers_are_refused_and_bool_outputs_are_programs():
     h = handle(ir.elementwise_kernel(4096, {"x": "f32", "y": "f32"}, [("m", "greater", ["x", "y"])], "bool"))
     assert h["variant"] == "pointwise_program" and h["params"]["program"]["out_dtype"] == "bool"
 
+
+def test_move_only_op_names_are_copies():
+    """`pad` and the f8 conversion names are plain register moves in the reference's op table (emmyptx/ops.py:236-237);
+    here they become `copy` steps of an elementwise program."""
+    for name in ("pad", "from_f8e4m3", "to_f8e5m2"):
+        h = handle(ir.elementwise_kernel(4096, {"x": "f16"}, [("a", name, ["x"]), ("b", "add", ["a", 1.0])], "f16"))
+        assert h["variant"] == "pointwise_program" and [st[0] for st in h["params"]["program"]["steps"]] == ["copy", "add"]
+
