@@ -196,6 +196,19 @@ class Let:
 
 
 @_node
+class Branch:
+    select: Any             # the predicate (an expression of axis variables and earlier values); unused in the last branch
+    value: Any              # a value name or a number
+
+
+@_node
+class Select:
+    """`name = v0 when p0, v1 when p1, ..., v_last otherwise` (emmyptx/kernel.py:812-822)."""
+    name: str
+    branches: list
+
+
+@_node
 class Loop:
     axis: Any
     body: list
@@ -682,6 +695,15 @@ def layout_kernel(case: str, name: str | None = None):
                           for di in range(2) for dj in range(2)],
                          [Assign("m0_", Op("maximum"), ["x00", "x01"]), Assign("m1_", Op("maximum"), ["x10", "x11"]),
                           Assign("y", Op("maximum"), ["m0_", "m1_"])], [8, 16, 16], [Var("c0"), Var("i0"), Var("j0")], "y"),
+        # the same mask as s_tril spelled as a Select on the axis variables (emmyptx/kernel.py:812-822), and a window of
+        # columns kept through a Let of a compound predicate (`F.pad`-like masking; emmyptx/kernel.py:344-369)
+        "s_tril_select": ([A("r0", 64), A("c0", 64)], {"X": [64, 64]}, [("x", "X", [Var("r0"), Var("c0")])],
+                          [Select("y", [Branch(BinaryExpr("<=", Var("c0"), Var("r0")), "x"), Branch(None, 0.0)])], [64, 64],
+                          [Var("r0"), Var("c0")], "y"),
+        "s_window_let": ([A("r0", 64), A("c0", 128)], {"X": [64, 128]}, [("x", "X", [Var("r0"), Var("c0")])],
+                         [Let("inside", BinaryExpr("&&", BinaryExpr(">=", Var("c0"), lit(3)), BinaryExpr("<", Var("c0"), lit(120)))),
+                          Assign("m", Op("where"), ["inside", "x", 0.0]), Assign("y", Op("multiply"), ["m", 2.0])], [64, 128],
+                         [Var("r0"), Var("c0")], "y"),
         # a rotation: the index wraps around along one axis
         "s_roll": ([A("r0", 64), A("c0", 128)], {"X": [64, 128]}, [("x", "X", [Var("r0"), BinaryExpr("%", add(Var("c0"), lit(125)), lit(128))])], [],
                    [64, 128], [Var("r0"), Var("c0")], "x"),

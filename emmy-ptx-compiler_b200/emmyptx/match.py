@@ -560,6 +560,101 @@ def match_indexed(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
             "params": {"n": n, "program": {k: v for k, v in prog.items() if k != "inputs"}, "index_map": index_map}}
 
 
+# ---- Let and Select as Assigns ---------------------------------------------------------------------------------
+_EXPR_OPS = {"+": "add", "-": "subtract", "*": "multiply", "/": "divide", "<": "less", "<=": "less_equal", ">": "greater",
+             ">=": "greater_equal", "==": "equal", "!=": "not_equal", "&&": "bitwise_and", "||": "bitwise_or"}
+
+
+class _Op:
+    def __init__(self, name: str) -> None:
+        self.name, self.identity = name, None
+
+
+class Assign:
+    """A synthetic Assign (what the desugaring below writes in place of a Let or a Select)."""
+
+    def __init__(self, name: str, op: str, args: list) -> None:
+        self.name, self.op, self.args, self.dtype = name, _Op(op), args, None
+
+
+def desugar_float_body(body: list) -> list:
+    """The statement list with every float `Let` (name = expression) and `Select` (name = v0 when p0, ... ,
+    emmyptx/kernel.py:812-822) rewritten as Assigns over the op table, so that the cell-program builders see
+    Load / Assign / Write only. Expressions may use axis variables, earlier values, literals, arithmetic, comparisons,
+    `&&` / `||` (masks are 1.0 / 0.0, as the reference's comparisons are: emmyptx/ops.py:116-120), the ternary and calls of
+    ops by name. Integer expressions (shifts, `//`, `%`, casts to int) are not rewritten: Unmatched."""
+    out, counter = [], [0]
+
+    def fresh() -> str:
+        counter[0] += 1
+        return f"__e{counter[0]}"
+
+    def operand(e):
+        k = _kind(e)
+        if isinstance(e, (int, float)) and not isinstance(e, bool):
+            return float(e)
+        if isinstance(e, bool):
+            return 1.0 if e else 0.0
+        if isinstance(e, str):
+            return e
+        if k == "Literal":
+            return (1.0 if e.value else 0.0) if isinstance(e.value, bool) else float(e.value)
+        if k == "Var":
+            return e.name
+        if k == "BinaryExpr":
+            if e.op not in _EXPR_OPS:
+                raise Unmatched(f"operator {e.op!r} in a float expression has no elementwise op")
+            name = fresh()
+            out.append(Assign(name, _EXPR_OPS[e.op], [operand(e.left), operand(e.right)]))
+            return name
+        if k == "TernaryExpr":
+            name = fresh()
+            out.append(Assign(name, "where", [operand(e.cond), operand(e.if_true), operand(e.if_false)]))
+            return name
+        if k == "CastExpr":
+            if e.dtype in INT_DTYPES:
+                raise Unmatched("a cast to an integer inside a float expression")
+            return operand(e.expr)
+        if k == "FuncCallExpr":
+            name = fresh()
+            out.append(Assign(name, _FUNC_ALIASES.get(e.name, e.name), [operand(a) for a in e.args]))
+            return name
+        raise Unmatched(f"unsupported expression {k}")
+
+    for s in body:
+        k = _kind(s)
+        if k == "Let":
+            if _dtype_name(getattr(s, "dtype", None)) in INT_DTYPES:
+                raise Unmatched("an integer Let in a float cell program")
+            out.append(Assign(s.name, "copy", [operand(s.value)]))
+        elif k == "Select":
+            branches = list(s.branches)
+            if not branches:
+                raise Unmatched("a Select without branches")
+            result = operand(branches[-1].value)
+            for b in reversed(branches[:-1]):
+                pred = operand(b.select)
+                name = fresh()
+                out.append(Assign(name, "where", [pred, operand(b.value), result]))
+                result = name
+            out.append(Assign(s.name, "copy", [result]))
+        else:
+            out.append(s)
+    return out
+
+
+class Tile:
+    """A Tile with another body (the matchers tell statements by class name, hence the name)."""
+
+    def __init__(self, tile, body: list) -> None:
+        self.axes, self.body = tile.axes, body
+
+
+class KernelOp:
+    def __init__(self, kernel, body: list) -> None:
+        self.name, self.body = kernel.name, body
+
+
 def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
     try:
         return _match_streaming(graph, kernel, launch, int_div)
@@ -568,7 +663,19 @@ def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict
         try:
             return match_indexed(graph, kernel, launch, int_div)
         except (Unmatched, OpError):
-            raise first from None
+            pass
+        # float Lets and Selects spelled out as Assigns, then the same two matchers
+        tiles = [s for s in kernel.body if _kind(s) == "Tile"]
+        if len(kernel.body) == 1 and len(tiles) == 1 and any(_kind(s) in ("Let", "Select") for s in tiles[0].body):
+            try:
+                plain = KernelOp(kernel, [Tile(tiles[0], desugar_float_body(tiles[0].body))])
+                try:
+                    return _match_streaming(graph, plain, launch, int_div)
+                except Unmatched:
+                    return match_indexed(graph, plain, launch, int_div)
+            except (Unmatched, OpError):
+                pass
+        raise first from None
 
 
 def _match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict:

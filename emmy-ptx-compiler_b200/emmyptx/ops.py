@@ -54,6 +54,9 @@ FLOAT_OPS = {
     "where": (3, lambda c, a, b: np.where(c != 0, a, b)),
     "floor_divide": (2, lambda a, b: np.floor(a / b)), "mod": (2, lambda a, b: a - b * np.floor(a / b)),
     "remainder": (2, lambda a, b: a - b * np.floor(a / b)),
+    # logical and / or / not of 1.0 / 0.0 masks (emmyptx/ops.py:274-279)
+    "bitwise_and": (2, lambda a, b: ((a != 0) & (b != 0)) * 1.0), "bitwise_or": (2, lambda a, b: ((a != 0) | (b != 0)) * 1.0),
+    "bitwise_not": (1, lambda a: (a == 0) * 1.0),
 }
 FLOAT_OPS.update({name: FLOAT_OPS["copy"] for name in MOVE_OPS})
 

@@ -78,7 +78,8 @@ def layout_buffers(tensors: dict, arg_order: list) -> dict:
 LAYOUT_EXPECTED = {     # what each data-movement case computes, on the buffers of layout_buffers (numpy, exact)
     "s_transpose": lambda b: b["X"].T, "s_permute": lambda b: b["X"].transpose(2, 0, 1) * np.float32(2), "s_slice": lambda b: b["X"][:, 10:50] * np.float32(2),
     "s_strided_slice": lambda b: b["X"][::2] + np.float32(1), "s_flip": lambda b: b["X"][:, ::-1], "s_stack": lambda b: np.stack([b["A"], b["B"]]),
-    "s_tril": lambda b: np.tril(b["X"]), "s_repeat": lambda b: np.tile(b["X"], (2, 1)),
+    "s_tril": lambda b: np.tril(b["X"]), "s_tril_select": lambda b: np.tril(b["X"]),
+    "s_window_let": lambda b: np.where((np.arange(128) >= 3) & (np.arange(128) < 120), b["X"], np.float32(0)) * np.float32(2), "s_repeat": lambda b: np.tile(b["X"], (2, 1)),
     "s_roll": lambda b: np.roll(b["X"], 3, -1), "s_embedding": lambda b: b["SRC"][np.abs(b["IDX"]) % 100],
     "s_gather": lambda b: np.take_along_axis(b["SRC"], np.abs(b["IDX"]) % 64, 1),
     "c_avg_pool1d": lambda b: ((b["X"][:, 0::4] + b["X"][:, 1::4]) + (b["X"][:, 2::4] + b["X"][:, 3::4])) * np.float32(0.25),

@@ -197,6 +197,9 @@ class Interpreter:
                 self._set(ops[0], V(src, "s32" if ty in ("b32", "u32", "s32") else ty), mask)
         elif name == "mma":
             self._mma(parts, ops, mask)
+        elif name in ("and", "or", "xor") and ty == "pred":     # and.pred %p, %p1, %p2: predicates are boolean arrays here
+            a, b = self.reg[ops[1]].astype(bool), self.reg[ops[2]].astype(bool)
+            self._set(ops[0], {"and": np.logical_and, "or": np.logical_or, "xor": np.logical_xor}[name](a, b), mask)
         elif name in ("and", "or", "xor"):
             a, b = V(ops[1], "s32"), V(ops[2], "s32")
             self._set(ops[0], {"and": np.bitwise_and, "or": np.bitwise_or, "xor": np.bitwise_xor}[name](a, b), mask)

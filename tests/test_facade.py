@@ -464,3 +464,19 @@ def test_move_only_op_names_are_copies():
         h = handle(ir.elementwise_kernel(4096, {"x": "f16"}, [("a", name, ["x"]), ("b", "add", ["a", 1.0])], "f16"))
         assert h["variant"] == "pointwise_program" and [st[0] for st in h["params"]["program"]["steps"]] == ["copy", "add"]
 
+
+def test_let_and_select_become_assigns():
+    """A mask written as a Select on the axis variables (emmyptx/kernel.py:812-822) or kept in a Let of a compound predicate
+    is spelled out as comparison / logical / where steps of an indexed program; integer expressions are not rewritten."""
+    h = handle(ir.layout_kernel("s_tril_select"))
+    assert h["variant"] == "pointwise_indexed"
+    assert [st[0] for st in h["params"]["program"]["steps"]] == ["less_equal", "where", "copy"]
+    assert h["params"]["index_map"]["inputs"][1:] in ([{"axis": 0}, {"axis": 1}], [{"axis": 1}, {"axis": 0}])
+    h = handle(ir.layout_kernel("s_window_let"))
+    assert [st[0] for st in h["params"]["program"]["steps"]] == ["greater_equal", "less", "bitwise_and", "copy", "where", "multiply"]
+    g, k, launch = ir.layout_kernel("s_window_let")
+    k.body[0].body[1] = ir.Let("inside", ir.BinaryExpr(">>", ir.Var("c0"), ir.Literal(2, "int")))      # a shift has no float op
+    with pytest.raises(CompileError):
+        handle((g, k, launch))
+    assert handle(ir.index_gather_kernel(2**16))["variant"] == "index_gather_i32"                        # the integer Let of the gather is untouched
+
