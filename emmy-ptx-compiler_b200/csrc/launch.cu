@@ -337,6 +337,9 @@ extern "C" int emmyb200_launch(const char* handle_json, void* const* params, int
                 m.in_kind[k] = 2;
                 m.in_index_of[k] = (int)geti(src, "index_of");
                 m.in_index_mult[k] = geti(src, "index_mult");
+            } else if (src.get("clamp") != nullptr) {               // a guarded read, clamped into the buffer
+                m.in_kind[k] = 4;
+                m.in_index_mod[k] = geti(src, "clamp");
             }
             if (next_buffer >= (int)h.get("inputs")->items.size()) return fail(EMMYB200_ERR_ARG, "launch: the index map names more buffers than the handle has inputs");
             ins[k] = a.input(next_buffer++);

@@ -807,6 +807,9 @@ static std::string program_source(const emmyb200_pw_program& p, int group, const
                         s += " v" + K + " = pw_ld1<" + DT + ">(p" + K + ", (i64)at[" + K + "] + m.in_index_mult[" + K + "] * x" + std::to_string(map->in_index_of[k]) + ");";
                     } else if (kind == 1) {
                         s += " v" + K + " = (PW_T)d[m.in_axis[" + K + "]];";
+                    } else if (kind == 4) {
+                        s += " { i64 g = (i64)at[" + K + "]; g = g < 0 ? 0 : (g >= m.in_index_mod[" + K + "] ? m.in_index_mod[" + K + "] - 1 : g); v" + K +
+                             " = pw_ld1<" + DT + ">(p" + K + ", g); }";
                     } else {
                         s += " v" + K + " = pw_ld1<" + DT + ">(p" + K + ", (i64)at[" + K + "]);";
                     }
@@ -1019,12 +1022,18 @@ extern "C" int emmyb200_pointwise_indexed(const emmyb200_pw_program* prog, const
     bool special = false;
     for (int k = 0; k < prog->n_inputs; ++k) {
         const int kind = map->in_kind[k];
-        if (kind < 0 || kind > 3) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: input %d has kind %d", k, kind);
+        if (kind < 0 || kind > 4) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: input %d has kind %d", k, kind);
         if (kind == 1) {
             if (map->in_axis[k] < 0 || map->in_axis[k] >= map->n_axes) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: input %d names axis %d", k, map->in_axis[k]);
             continue;
         }
         if (inputs[k] == nullptr) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: null buffer");
+        if (kind == 4) {                // a guarded read: the index is clamped into the buffer, the map may leave it
+            if (map->in_index_mod[k] < 1) return fail(EMMYB200_ERR_ARG, "pointwise_indexed: guarded input %d needs its buffer's element count", k);
+            narrow = false;
+            special = true;
+            continue;
+        }
         if ((rc = range_ok(map->in_offset[k], map->in_coef[k], "an input map")) != EMMYB200_OK) return rc;
         for (int a = 0; a < map->n_axes; ++a) {
             if (map->in_rot[k][a] < 0 || (map->in_rot[k][a] != 0 && map->in_rot[k][a] >= map->extent[a]))
@@ -1284,7 +1293,7 @@ extern "C" int emmyb200_pointwise_indexed_compile(const emmyb200_pw_program* pro
     bool special = false;
     for (int k = 0; k < EMMYB200_PW_MAX_INPUTS; ++k) {
         key_map.in_kind[k] = k < prog->n_inputs ? map->in_kind[k] : 0;
-        if (k < prog->n_inputs && (map->in_kind[k] == 2 || map->in_kind[k] == 3)) special = true;
+        if (k < prog->n_inputs && (map->in_kind[k] == 2 || map->in_kind[k] == 3 || map->in_kind[k] == 4)) special = true;
         if (k < prog->n_inputs && map->in_kind[k] == 2 && (map->in_index_of[k] < 0 || map->in_index_of[k] >= prog->n_inputs || map->in_kind[map->in_index_of[k]] != 3))
             return fail(EMMYB200_ERR_ARG, "pointwise_indexed_compile: input %d takes its index from no index source", k);
         for (int a = 0; k < prog->n_inputs && a < map->n_axes; ++a) special = special || map->in_rot[k][a] != 0;

@@ -209,6 +209,14 @@ class Select:
 
 
 @_node
+class Cond:
+    """`if cond: body else: else_body` on an expression of the axis variables (emmyptx/kernel.py:825-840)."""
+    cond: Any
+    body: list
+    else_body: list
+
+
+@_node
 class Loop:
     axis: Any
     body: list
@@ -704,6 +712,12 @@ def layout_kernel(case: str, name: str | None = None):
                          [Let("inside", BinaryExpr("&&", BinaryExpr(">=", Var("c0"), lit(3)), BinaryExpr("<", Var("c0"), lit(120)))),
                           Assign("m", Op("where"), ["inside", "x", 0.0]), Assign("y", Op("multiply"), ["m", 2.0])], [64, 128],
                          [Var("r0"), Var("c0")], "y"),
+        # torch.cat([a, b], -1) (shapes.py:13) as one kernel: a Cond on the column picks the source (emmyptx/kernel.py:825-840)
+        "s_cat_cond": ([A("r0", 32), A("c0", 112)], {"A": [32, 64], "B": [32, 48]}, [],
+                       [Cond(BinaryExpr("<", Var("c0"), lit(64)),
+                             [Load(["a"], "A", [Var("r0"), Var("c0")]), Write("out", [Var("r0"), Var("c0")], ["a"])],
+                             [Load(["b"], "B", [Var("r0"), sub(Var("c0"), lit(64))]), Write("out", [Var("r0"), Var("c0")], ["b"])])],
+                       [32, 112], None, None),
         # a rotation: the index wraps around along one axis
         "s_roll": ([A("r0", 64), A("c0", 128)], {"X": [64, 128]}, [("x", "X", [Var("r0"), BinaryExpr("%", add(Var("c0"), lit(125)), lit(128))])], [],
                    [64, 128], [Var("r0"), Var("c0")], "x"),
@@ -723,7 +737,7 @@ def layout_kernel(case: str, name: str | None = None):
                    [tensor("out", [64, 32] if emb else [32, 8], "f32")])
         return g, kern, _launch(kern, ["IDX", "SRC", "out"], axes[0].extent.value * axes[1].extent.value)
     axes, ins, loads, assigns, out_shape, out_index, value = cases[case]
-    body = [Load([v], buf, idx) for v, buf, idx in loads] + list(assigns) + [Write("out", out_index, [value])]
+    body = [Load([v], buf, idx) for v, buf, idx in loads] + list(assigns) + ([Write("out", out_index, [value])] if out_index is not None else [])
     kern = KernelOp(name or f"k_{case}", [Tile(axes, body)])
     cells = 1
     for a in axes:

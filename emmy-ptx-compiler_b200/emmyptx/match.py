@@ -499,11 +499,16 @@ def match_indexed(graph, kernel, launch: dict, int_div: str = "floor") -> dict:
         lo, hi = _reach(off, coef, extents)
         if k in indirect:
             hi += indirect[k][1] * (indirect[k][4] - 1)
-        if lo < 0 or hi >= math.prod(tensors[buf][0]):
+        guarded = bool(getattr(s, "guarded", False))            # hoisted out of a Cond: the kernel clamps the index
+        if guarded and (rot is not None or k in indirect or is_source):
+            raise Unmatched("a Load inside a Cond is addressed by a plain affine index")
+        if not guarded and (lo < 0 or hi >= math.prod(tensors[buf][0])):
             raise Unmatched(f"the index of {buf!r} leaves the buffer (elements {lo}..{hi} of {math.prod(tensors[buf][0])})")
         name = f"__in{k}"
         synthetic[name] = (tensors[buf][0], tensors[buf][1])
         src = {"buffer": buf, "offset": off, "coef": coef}
+        if guarded and (lo < 0 or hi >= math.prod(tensors[buf][0])):
+            src["clamp"] = math.prod(tensors[buf][0])
         if rot is not None and any(rot):
             src["rot"] = rot
         if is_source:
@@ -577,12 +582,43 @@ class Assign:
         self.name, self.op, self.args, self.dtype = name, _Op(op), args, None
 
 
+class _Var:
+    def __init__(self, name: str) -> None:
+        self.name = name
+
+    def free_vars(self) -> set:
+        return {self.name}
+
+
+_Var.__name__ = "Var"
+
+
+def guarded_load(names: list, buffer: str, index: list):
+    """A Load hoisted out of a Cond: it runs in every cell, so the kernel clamps its index into the buffer."""
+    ld = object.__new__(Load)
+    ld.names, ld.input, ld.index, ld.guarded = names, buffer, index, True
+    return ld
+
+
+class Write:
+    def __init__(self, output: str, index: list, values: list) -> None:
+        self.output, self.index, self.values, self.atomic = output, index, values, False
+
+
+def merged_write(output: str, index: list, values: list):
+    return Write(output, index, values)
+
+
 def desugar_float_body(body: list) -> list:
     """The statement list with every float `Let` (name = expression) and `Select` (name = v0 when p0, ... ,
     emmyptx/kernel.py:812-822) rewritten as Assigns over the op table, so that the cell-program builders see
     Load / Assign / Write only. Expressions may use axis variables, earlier values, literals, arithmetic, comparisons,
     `&&` / `||` (masks are 1.0 / 0.0, as the reference's comparisons are: emmyptx/ops.py:116-120), the ternary and calls of
-    ops by name. Integer expressions (shifts, `//`, `%`, casts to int) are not rewritten: Unmatched."""
+    ops by name. Integer expressions (shifts, `//`, `%`, casts to int) are not rewritten: Unmatched.
+    A `Cond` on such an expression (emmyptx/kernel.py:825-840) is flattened: the Loads of both arms run in every cell as
+    guarded Loads (the kernel clamps their indices into the buffers), values are renamed per arm, and what both arms
+    define or write to the same element is merged with `where` on the predicate -- the two halves of a concatenation, a
+    padded border. Arms that write different elements (or only one of which writes) have no kernel variant."""
     out, counter = [], [0]
 
     def fresh() -> str:
@@ -621,9 +657,74 @@ def desugar_float_body(body: list) -> list:
             return name
         raise Unmatched(f"unsupported expression {k}")
 
+    def same_expr(a, b) -> bool:
+        if _kind(a) != _kind(b):
+            return False
+        if not hasattr(a, "__dict__"):
+            return a == b
+        fields = [f for f in vars(a) if not f.startswith("_")]
+        return all(same_expr(getattr(a, f), getattr(b, f, None)) if not isinstance(getattr(a, f), (list, tuple)) else
+                   (isinstance(getattr(b, f, None), (list, tuple)) and len(getattr(a, f)) == len(getattr(b, f)) and
+                    all(same_expr(x, y) for x, y in zip(getattr(a, f), getattr(b, f)))) for f in fields)
+
+    def rename_expr(e, names: dict):
+        """The expression with value names replaced (axis variables and untouched names stay)."""
+        k = _kind(e)
+        if isinstance(e, str):
+            return names.get(e, e)
+        if k == "Var":
+            return _Var(names.get(e.name, e.name))
+        if k in ("BinaryExpr", "TernaryExpr", "CastExpr", "FuncCallExpr"):
+            copy = object.__new__(type(e))
+            for f, v in vars(e).items():
+                setattr(copy, f, [rename_expr(x, names) for x in v] if isinstance(v, (list, tuple)) else
+                        (rename_expr(v, names) if hasattr(v, "__dict__") else v))
+            return copy
+        return e
+
+    def branch(stmts, tag: str):
+        """One arm of a Cond, flattened: Loads become guarded Loads of renamed values, Assigns / Lets / Selects are renamed,
+        Writes are collected. Returns (statements, {original name: renamed}, writes)."""
+        names, flat, writes = {}, [], []
+        for t in stmts:
+            k = _kind(t)
+            if k == "Load":
+                for nm in t.names:
+                    names[nm] = f"{nm}__{tag}"
+                flat.append(guarded_load([names[nm] for nm in t.names], t.input, [rename_expr(e, names) for e in t.index]))
+            elif k == "Assign":
+                args = [names.get(a, a) if isinstance(a, str) else a for a in t.args]
+                names[t.name] = f"{t.name}__{tag}"
+                a2 = Assign(names[t.name], t.op.name, args)
+                a2.dtype = t.dtype
+                flat.append(a2)
+            elif k == "Write":
+                writes.append((t.output, list(t.index), [names.get(v, v) if isinstance(v, str) else v for v in t.values], bool(getattr(t, "atomic", False))))
+            else:
+                raise Unmatched(f"statement {k} inside a Cond has no kernel variant")
+        return flat, names, writes
+
     for s in body:
         k = _kind(s)
-        if k == "Let":
+        if k == "Cond":
+            counter[0] += 1
+            pred = operand(s.cond)
+            then_flat, then_names, then_writes = branch(list(s.body), f"t{counter[0]}")
+            else_flat, else_names, else_writes = branch(list(getattr(s, "else_body", None) or []), f"e{counter[0]}")
+            out.extend(then_flat)
+            out.extend(else_flat)
+            for nm in then_names:                                       # a value both arms define lives on after the Cond
+                if nm in else_names:
+                    out.append(Assign(nm, "where", [pred, then_names[nm], else_names[nm]]))
+            if len(then_writes) != len(else_writes):
+                raise Unmatched("the two arms of a Cond must write the same elements (a cell that writes nothing has no kernel variant)")
+            for (o1, i1, v1, at1), (o2, i2, v2, at2) in zip(then_writes, else_writes):
+                if o1 != o2 or at1 or at2 or len(v1) != 1 or len(v2) != 1 or len(i1) != len(i2) or not all(same_expr(x, y) for x, y in zip(i1, i2)):
+                    raise Unmatched("the two arms of a Cond must write the same elements")
+                name = fresh()
+                out.append(Assign(name, "where", [pred, v1[0], v2[0]]))
+                out.append(merged_write(o1, i1, [name]))
+        elif k == "Let":
             if _dtype_name(getattr(s, "dtype", None)) in INT_DTYPES:
                 raise Unmatched("an integer Let in a float cell program")
             out.append(Assign(s.name, "copy", [operand(s.value)]))
@@ -666,7 +767,7 @@ def match_streaming(graph, kernel, launch: dict, int_div: str = "floor") -> dict
             pass
         # float Lets and Selects spelled out as Assigns, then the same two matchers
         tiles = [s for s in kernel.body if _kind(s) == "Tile"]
-        if len(kernel.body) == 1 and len(tiles) == 1 and any(_kind(s) in ("Let", "Select") for s in tiles[0].body):
+        if len(kernel.body) == 1 and len(tiles) == 1 and any(_kind(s) in ("Let", "Select", "Cond") for s in tiles[0].body):
             try:
                 plain = KernelOp(kernel, [Tile(tiles[0], desugar_float_body(tiles[0].body))])
                 try:

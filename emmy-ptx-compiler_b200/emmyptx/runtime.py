@@ -226,7 +226,9 @@ def pointwise_program(program: dict, inputs: list, out, stream=None):
 
 def make_index_map(index_map: dict) -> PwIndexMap:
     """The C struct for {"extents": [...], "inputs": [{"offset": o, "coef": [...]} | {"axis": a}, ...], "out": {"offset": o,
-    "coef": [...]}}: input k reads element offset + sum coef[a] * digit[a] of its buffer, or is the digit of axis a."""
+    "coef": [...]}}: input k reads element offset + sum coef[a] * digit[a] of its buffer, or is the digit of axis a. A buffer
+    input may carry "rot" (rotations), "index_mod" / "index_abs" (an index source), "index_of" / "index_mult" (addressed
+    through one) or "clamp" (a guarded read: the index is clamped into [0, clamp))."""
     m = PwIndexMap()
     if not 1 <= len(index_map["extents"]) <= PW_MAX_AXES or len(index_map["inputs"]) > PW_MAX_INPUTS:
         raise ValueError(f"an index map has 1 to {PW_MAX_AXES} axes and at most {PW_MAX_INPUTS} inputs")
@@ -246,6 +248,8 @@ def make_index_map(index_map: dict) -> PwIndexMap:
                 m.in_kind[k], m.in_index_mod[k], m.in_index_abs[k] = 3, src["index_mod"], 1 if src.get("index_abs") else 0
             elif "index_of" in src:                                 # addressed through index source index_of
                 m.in_kind[k], m.in_index_of[k], m.in_index_mult[k] = 2, src["index_of"], src["index_mult"]
+            elif "clamp" in src:                                    # a guarded read: the index is clamped into [0, clamp)
+                m.in_kind[k], m.in_index_mod[k] = 4, src["clamp"]
     m.out_offset = index_map["out"]["offset"]
     for a, c in enumerate(index_map["out"]["coef"]):
         m.out_coef[a] = c
@@ -267,7 +271,10 @@ def pointwise_indexed(program: dict, index_map: dict, inputs: list, out, stream=
     _need_cuda(out, *real)
     if math.prod(ext) > 0:
         for k, src in enumerate(index_map["inputs"]):
-            if "axis" not in src:
+            if "clamp" in src:                                      # a guarded read: clamped into the buffer by the kernel
+                if not 1 <= src["clamp"] <= inputs[k].numel():
+                    raise IndexError(f"pointwise_indexed: input {k} is clamped to {src['clamp']} elements of {inputs[k].numel()}")
+            elif "axis" not in src:
                 lo, hi = reach(src)
                 if "index_of" in src:                               # plus the largest row the index source can name
                     hi += src["index_mult"] * (index_map["inputs"][src["index_of"]]["index_mod"] - 1)

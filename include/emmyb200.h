@@ -156,7 +156,10 @@ typedef struct {
      * buffer read through its own affine map, made non-negative (in_index_abs) and reduced modulo in_index_mod (required:
      * the modulus is what bounds the index; the remainder is the non-negative one); no step may read it as a value. An
      * input of in_kind 2 is a buffer whose element index is its affine map plus in_index_mult[k] times the value of index
-     * source in_index_of[k]. */
+     * source in_index_of[k].
+     * An input of in_kind 4 is a guarded read (a Load inside a `Cond` on the axis variables, emmyptx/kernel.py:825-840: the
+     * two halves of a concatenation, a padded border): its affine index is clamped into [0, in_index_mod[k]) -- the
+     * buffer's element count -- so the map may leave the buffer in cells whose value the program does not select. */
     int32_t in_index_of[EMMYB200_PW_MAX_INPUTS];
     int32_t in_index_abs[EMMYB200_PW_MAX_INPUTS];
     int64_t in_index_mod[EMMYB200_PW_MAX_INPUTS];

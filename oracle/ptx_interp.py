@@ -75,12 +75,17 @@ class Interpreter:
         self.active = np.ones(n, dtype=bool)
         self.n = n
         labels = {line[:-1]: i for i, line in enumerate(self.lines) if line.endswith(":")}
+        self.labels, self.parked = labels, {}
         self.jump = None
         pc, executed = 0, 0
         while pc < len(self.lines):
             line = self.lines[pc]
+            self.pc = pc
             pc += 1
             if line.endswith(":"):
+                waiting = self.parked.pop(line[:-1], None)           # threads that branched forward to this label rejoin
+                if waiting is not None:
+                    self.active = self.active | waiting
                 continue
             self._exec(line)
             executed += 1
@@ -170,13 +175,21 @@ class Interpreter:
             if ops[0] == "$L_exit":
                 self.active = self.active & ~taken
                 return
+            # A forward branch on which threads diverge (the if / else of a Cond, emmyptx/kernel.py:825-840): the threads
+            # that take it wait at the label, the others go on; everybody between here and the label runs masked.
+            t = taken[self.active]
+            forward = self.labels.get(ops[0], -1) > self.pc
+            if forward and (self.parked or (t.any() and not t.all())):
+                go = taken & self.active
+                self.parked[ops[0]] = self.parked.get(ops[0], np.zeros(self.n, bool)) | go
+                self.active = self.active & ~go
+                return
             # Any other branch belongs to a run-time loop (emmyptx/loops.py:231-264): its trip count does not depend on
             # the thread, so either every active thread takes it or none does. Divergence is refused.
-            t = taken[self.active]
             if t.size and t.all():
                 self.jump = ops[0]
             elif t.any():
-                raise PtxError("a branch on which the active threads diverge is not supported")
+                raise PtxError("a backward branch on which the active threads diverge is not supported")
             return
         if name == "ld" and parts[1] == "param":
             self._set(ops[0], self.param_addr[ops[1].strip("[]")])

@@ -480,3 +480,22 @@ def test_let_and_select_become_assigns():
         handle((g, k, launch))
     assert handle(ir.index_gather_kernel(2**16))["variant"] == "index_gather_i32"                        # the integer Let of the gather is untouched
 
+
+def test_cond_becomes_guarded_loads_and_a_where():
+    """torch.cat as one kernel: a Cond on the column index with a Load and a Write in each arm (emmyptx/kernel.py:825-840).
+    Both Loads run in every cell with their indices clamped into the buffers; the Write stores where(pred, a, b)."""
+    h = handle(ir.layout_kernel("s_cat_cond"))
+    assert h["variant"] == "pointwise_indexed" and h["inputs"] == ["A", "B"]
+    srcs = h["params"]["index_map"]["inputs"]
+    assert srcs[0] == {"buffer": "A", "offset": 0, "coef": [64, 1], "clamp": 2048}
+    assert srcs[1] == {"buffer": "B", "offset": -64, "coef": [48, 1], "clamp": 1536}
+    assert [st[0] for st in h["params"]["program"]["steps"]] == ["less", "where"]
+    g, k, launch = ir.layout_kernel("s_cat_cond")               # one arm that writes nothing: some cells would stay unwritten
+    k.body[0].body[0].else_body = []
+    with pytest.raises(CompileError):
+        handle((g, k, launch))
+    g, k, launch = ir.layout_kernel("s_cat_cond")               # arms writing different elements
+    k.body[0].body[0].else_body[1].index = [ir.Var("r0"), ir.Literal(0, "int")]
+    with pytest.raises(CompileError):
+        handle((g, k, launch))
+

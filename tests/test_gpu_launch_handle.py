@@ -165,3 +165,13 @@ def test_contraction_handle(cuda, lib):
     ref = torch.nn.functional.conv2d(x.double()[None], w.double())[0]
     assert torch.allclose(out.double(), ref, rtol=1e-5, atol=1e-4)
 
+
+def test_guarded_read_handle(cuda, lib):
+    """torch.cat as one kernel (a Cond on the column index): the handle's index map carries the clamp of each guarded read."""
+    import torch
+    from emmyptx import ir
+    a, b = torch.randn(32, 64, device=cuda), torch.randn(32, 48, device=cuda)
+    out = torch.zeros(32, 112, device=cuda)
+    assert launch(lib, handle_text(ir.layout_kernel("s_cat_cond")), [a, b, out]) == 0
+    assert torch.equal(out, torch.cat([a, b], -1))
+

@@ -97,3 +97,12 @@ def test_bool_outputs_compile_in_every_group(lib):
         assert "#define PW_OUT_DT 5" in rt.program_source(prog, group)
     assert rt.program_compile(prog) > 1000
 
+
+def test_guarded_reads_compile(lib):
+    """Inputs whose index is clamped into the buffer (Loads hoisted out of a Cond): the one-cell form with spelled-out loads."""
+    S = rt.PW_MAX_SLOTS
+    prog = {"in_dtypes": ["f32", "f32", "f32"], "out_dtype": "f32", "out_slot": 3, "consts": [64.0], "steps": [["less", 3, 2, S, 0], ["where", 3, 3, 0, 1]]}
+    imap = {"extents": [32, 112], "inputs": [{"offset": 0, "coef": [64, 1], "clamp": 2048}, {"offset": -64, "coef": [48, 1], "clamp": 1536}, {"axis": 1}],
+            "out": {"offset": 0, "coef": [112, 1]}}
+    assert rt.indexed_compile(prog, imap) > 1000
+
