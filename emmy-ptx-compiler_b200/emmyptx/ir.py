@@ -455,14 +455,16 @@ def colwise_kernel(op: str, rows: int, cols: int, eps: float = 1e-12, name: str 
     return g, kern, launch
 
 
-def rowwise_kernel(op: str, rows: int, cols: int, eps: float = 1e-5, name: str = "k_rowwise"):
+def rowwise_kernel(op: str, rows: int, cols: int, eps: float = 1e-5, name: str = "k_rowwise", lanes: bool = False):
     """A reduction over the last axis of X[rows, cols] (or a normalisation built on one) in the statement shapes the
-    reference lowers (emmyptx/kernel.py:786-797 `Accum` inside a `Loop`, :856-866 `WarpShuffle` to merge lanes): one tile
-    cell per row, a loop per pass over the row."""
+    reference lowers (emmyptx/kernel.py:786-797 `Accum` inside a `Loop`): one tile cell -- one thread of the reference's
+    kernel -- per row, a loop per pass over the row. `lanes=True` appends a `WarpShuffle` after every loop (:856-866): the
+    form a schedule with one warp per row ends its loops with; with one thread per row the reference's butterfly would
+    add up 32 different rows, so that form is only for exercising the matcher, never compiled for its result."""
     r0, c0 = Axis("r0", Dim(rows)), Axis("c0", Dim(cols))
     ld = lambda: Load(["x"], "X", [Var("r0"), Var("c0")])
-    shuffle = lambda st, o: WarpShuffle([st], [st + "_b"], [Assign(st, Op(o), [st, st + "_b"])], 32)
-    fold = lambda st, o, pre=(): [Loop(c0, [ld(), *pre, Accum(st, None, pre[-1].name if pre else "x", Op(o))]), shuffle(st, o)]
+    shuffle = lambda st, o: [WarpShuffle([st], [st + "_b"], [Assign(st, Op(o), [st, st + "_b"])], 32)] if lanes else []
+    fold = lambda st, o, pre=(): [Loop(c0, [ld(), *pre, Accum(st, None, pre[-1].name if pre else "x", Op(o))]), *shuffle(st, o)]
     inputs, body, out, is_map = [tensor("X", [rows, cols], "f32")], [], None, False
     if op in ("sum", "mean", "amax", "amin", "prod"):
         body = fold("acc", {"sum": "add", "mean": "add", "amax": "maximum", "amin": "minimum", "prod": "multiply"}[op])
@@ -476,7 +478,7 @@ def rowwise_kernel(op: str, rows: int, cols: int, eps: float = 1e-5, name: str =
     elif op == "dot":                                   # a matrix-vector product: the vector is the second input
         inputs.append(tensor("W", [cols], "f32"))
         body = [Loop(c0, [ld(), Load(["w"], "W", [Var("c0")]), Assign("p", Op("multiply"), ["x", "w"]), Accum("acc", None, "p", Op("add"))]),
-                shuffle("acc", "add")]
+                *shuffle("acc", "add")]
         out = "acc"
     elif op in ("var", "std", "layer_norm"):
         body = fold("acc", "add") + [Assign("mean", Op("multiply"), ["acc", 1.0 / cols])]
@@ -524,7 +526,7 @@ def rowwise_kernel(op: str, rows: int, cols: int, eps: float = 1e-5, name: str =
         body.append(Write("Y", [Var("r0")], [out]))
     kern = KernelOp(name, [Tile([r0], body)])
     g = _graph(kern, inputs, [tensor("Y", [rows, cols] if is_map else [rows], "f32")])
-    return g, kern, _launch(kern, [t.name for t in inputs] + ["Y"], rows * 32)
+    return g, kern, _launch(kern, [t.name for t in inputs] + ["Y"], rows * 32 if lanes else rows)
 
 
 def gemm_kernel(m: int, n: int, k: int, dtype: str = "f16", epilogue: str | None = None, b_trans: bool = False,

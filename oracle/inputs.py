@@ -75,6 +75,16 @@ def layout_buffers(tensors: dict, arg_order: list) -> dict:
     return bufs
 
 
+def seeded_buffers(tensors: dict, arg_order: list) -> dict:
+    """Buffers for a kernel whose last argument is its output: argument i ~ N(0, 1) seeded with i (tools/run_local.py:86-87),
+    the output zeroed (:92-93)."""
+    bufs = {}
+    for i, name in enumerate(arg_order):
+        shape = tensors[name]["shape"]
+        bufs[name] = np.zeros(shape, np.float32) if i == len(arg_order) - 1 else np.random.default_rng(i).standard_normal(shape).astype(np.float32)
+    return bufs
+
+
 LAYOUT_EXPECTED = {     # what each data-movement case computes, on the buffers of layout_buffers (numpy, exact)
     "s_transpose": lambda b: b["X"].T, "s_permute": lambda b: b["X"].transpose(2, 0, 1) * np.float32(2), "s_slice": lambda b: b["X"][:, 10:50] * np.float32(2),
     "s_strided_slice": lambda b: b["X"][::2] + np.float32(1), "s_flip": lambda b: b["X"][:, ::-1], "s_stack": lambda b: np.stack([b["A"], b["B"]]),
@@ -99,4 +109,35 @@ def conv_expected(case: str, b: dict) -> np.ndarray:
     if case == "c_conv1d":
         return np.einsum("oct,cit->oi", w, win)
     return np.einsum("ocuv,cijuv->oij", w, win)
+
+
+def reduce_expected(name: str, b: dict) -> np.ndarray:
+    """What the seeded row / column / fp32-product kernels compute (tools/torch_cases/reductions.py, fused.py, matmul.py),
+    in float64 on the buffers of seeded_buffers. `row_<op>` reduces the last axis of X, `col_<op>` the first."""
+    f = lambda k: b[k].astype(np.float64)
+    if name == "m_mm":
+        return f("A") @ f("B")
+    if name == "m_bmm":
+        return np.einsum("bmk,bkn->bmn", f("A"), f("B"))
+    if name == "m_linear_bias_relu":
+        return np.maximum(f("A") @ f("B").T + f("bias"), 0.0)
+    if name == "m_transpose_lhs":
+        return f("A").T @ f("B")
+    kind, op = name.split("_", 1)
+    x = f("X") if kind == "row" else f("X").T                 # reduce the last axis either way
+    mx = x.max(-1, keepdims=True)
+    lse = np.log(np.exp(x - mx).sum(-1, keepdims=True)) + mx
+    n = x.shape[-1]
+    mean = x.mean(-1, keepdims=True)
+    var_b = ((x - mean) ** 2).mean(-1, keepdims=True)
+    out = {
+        "sum": lambda: x.sum(-1), "mean": lambda: x.mean(-1), "amax": lambda: x.max(-1), "amin": lambda: x.min(-1), "prod": lambda: x.prod(-1),
+        "norm2": lambda: np.sqrt((x * x).sum(-1)), "var": lambda: x.var(-1, ddof=1), "std": lambda: x.std(-1, ddof=1), "logsumexp": lambda: lse[..., 0],
+        "softmax": lambda: np.exp(x - lse), "log_softmax": lambda: x - lse,
+        "layer_norm": lambda: (x - mean) / np.sqrt(var_b + 1e-5) * f("W") + f("B"),
+        "rms_norm": lambda: x / np.sqrt((x * x).mean(-1, keepdims=True) + 1e-5) * f("W"),
+        "normalize": lambda: x / np.maximum(np.sqrt((x * x).sum(-1, keepdims=True)), 1e-12),
+        "dot": lambda: x @ f("W"),
+    }[op]()
+    return out if kind == "row" or out.ndim == 1 else out.T
 

@@ -191,6 +191,23 @@ class Interpreter:
             elif t.any():
                 raise PtxError("a backward branch on which the active threads diverge is not supported")
             return
+        if name == "activemask":                                  # whole warps run (the launch is a whole number of warps)
+            self._set(ops[0], np.full(self.n, -1, np.int32), mask)
+            return
+        if name == "shfl":
+            # shfl.sync.bfly.b32 d, a, delta, clamp, membermask: lane l reads lane l ^ delta of its warp. Threads are laid
+            # out block after block and blocks are whole warps, so warp-mates are 32 consecutive positions.
+            if parts[2] != "bfly":
+                raise PtxError(f"shfl mode {parts[2]!r} is not supported")
+            if self.n % 32:
+                raise PtxError("shuffles need a whole number of warps")
+            delta = int(ops[2], 0)
+            src = self.reg[ops[1]]
+            partner = np.arange(self.n) ^ delta
+            got = src[partner]
+            got = np.where(self.active[partner], got, src)           # an inactive source lane returns the caller's own value
+            self._set(ops[0], got, mask)
+            return
         if name == "ld" and parts[1] == "param":
             self._set(ops[0], self.param_addr[ops[1].strip("[]")])
         elif name == "cvta":

@@ -52,6 +52,13 @@ for name, info in manifest.items():
         out[f"{name}.o"] = bufs["O"]
         print(name, bufs["O"][0, 0, :4])
         continue
+    if info.get("seeded"):
+        bufs = inputs.seeded_buffers(info["tensors"], info["launch"]["arg_order"])
+        ptx_interp.run_entry((HERE / f"{name}.ref.ptx").read_text(), bufs, info["launch"]["grid"][0], info["launch"]["block"][0])
+        result = info["launch"]["arg_order"][-1]
+        out[f"{name}.out"] = bufs[result]
+        print(name, bufs[result].reshape(-1)[:4])
+        continue
     if info.get("layout"):
         bufs = inputs.layout_buffers(info["tensors"], info["launch"]["arg_order"])
         ptx_interp.run_entry((HERE / f"{name}.ref.ptx").read_text(), bufs, info["launch"]["grid"][0], info["launch"]["block"][0])

@@ -175,6 +175,23 @@ CONV = ["c_conv1d", "c_conv2d"]                                                 
 for name in CONV:
     CASES[name] = ir.conv_kernel(name, name=name)
 
+# Row and column reductions / normalisations (tools/torch_cases/reductions.py, fused.py) in the one-thread-per-row form, and
+# the float32 products written as scalar loops (matmul.py:9-14): compiled by the reference as they are, executed on the CPU
+# into golden vectors and on the GPU next to this library's kernels.
+ROWS = ["sum", "mean", "amax", "amin", "prod", "norm2", "var", "std", "logsumexp", "softmax", "log_softmax", "layer_norm", "rms_norm",
+        "normalize", "dot"]
+COLS = ["sum", "amax", "softmax"]
+REDUCE = {}
+for op in ROWS:
+    REDUCE[f"row_{op}"] = ir.rowwise_kernel(op, 64, 256, name=f"row_{op}")
+for op in COLS:
+    REDUCE[f"col_{op}"] = ir.colwise_kernel(op, 256, 64, name=f"col_{op}")
+REDUCE["m_mm"] = ir.matmul_f32_kernel(128, 80, 96, name="m_mm")
+REDUCE["m_bmm"] = ir.matmul_f32_kernel(64, 48, 32, batch=4, name="m_bmm")
+REDUCE["m_linear_bias_relu"] = ir.matmul_f32_kernel(64, 96, 128, b_trans=True, bias=True, relu=True, name="m_linear_bias_relu")
+REDUCE["m_transpose_lhs"] = ir.matmul_f32_kernel(128, 80, 96, a_trans=True, name="m_transpose_lhs")
+CASES.update(REDUCE)
+
 for name, (graph, kernel, launch) in CASES.items():
     ptx = compile_kernel(graph, kernel, launch, target="sm_89")
     (HERE / f"{name}.ref.ptx").write_text(ptx)
@@ -182,6 +199,7 @@ for name, (graph, kernel, launch) in CASES.items():
                                        split_k=GEMM_OUT.get(name, (None, 1))[1])} if name in GEMMS else {}),
                       **({"attention": dict(zip(("units", "seq_q", "seq_k", "d", "causal", "scale"), ATTENTION[name]))} if name in ATTENTION else {}),
                       **({"layout": True} if name in LAYOUT or name in CONV else {}),
+                      **({"seeded": True} if name in REDUCE else {}),
                       "tensors": {t.name: {"shape": [d.as_static() for d in t.shape], "dtype": t.dtype.name}
                                   for n in graph.nodes.values() for t in n.outputs}}
     print(f"{name}: {len(ptx.splitlines())} lines of PTX")

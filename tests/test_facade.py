@@ -499,3 +499,13 @@ def test_cond_becomes_guarded_loads_and_a_where():
     with pytest.raises(CompileError):
         handle((g, k, launch))
 
+
+def test_row_ops_match_with_and_without_a_warp_shuffle():
+    """The row kernels are recognised from one thread per row (a loop per pass: the form whose reference PTX the fixtures
+    hold) and from the same loops followed by a WarpShuffle (emmyptx/kernel.py:856-866: how a warp-per-row schedule ends them)."""
+    for op in ("sum", "softmax", "layer_norm", "dot"):
+        plain, laned = handle(ir.rowwise_kernel(op, 48, 256)), handle(ir.rowwise_kernel(op, 48, 256, lanes=True))
+        assert plain["variant"] == laned["variant"] == "rowwise_f32" and plain["params"] == laned["params"]
+    kinds = {type(s).__name__ for s in ir.rowwise_kernel("sum", 8, 64)[1].body[0].body}
+    assert "WarpShuffle" not in kinds and "WarpShuffle" in {type(s).__name__ for s in ir.rowwise_kernel("sum", 8, 64, lanes=True)[1].body[0].body}
+

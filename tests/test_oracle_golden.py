@@ -190,3 +190,22 @@ def test_convolution_fixture_is_the_float64_convolution(golden, case):
     assert golden[f"{case}.out"].shape == ref.shape
     assert np.abs(golden[f"{case}.out"].astype(np.float64) - ref).max() < 2e-5
 
+
+SEEDED = [f"row_{op}" for op in ("sum", "mean", "amax", "amin", "prod", "norm2", "var", "std", "logsumexp", "softmax", "log_softmax", "layer_norm",
+                                 "rms_norm", "normalize", "dot")] + ["col_sum", "col_amax", "col_softmax", "m_mm", "m_bmm", "m_linear_bias_relu", "m_transpose_lhs"]
+
+
+@pytest.mark.parametrize("case", SEEDED)
+def test_reduction_and_f32_product_fixtures(golden, case):
+    """The reference's PTX for the row / column reductions and normalisations (one thread per row: a loop per pass) and for
+    the float32 products written as scalar loops, executed on the CPU: the float64 value of the same expression, to within
+    fp32 accumulation (1e-5 of the result's scale, the reference's own class for these cases; 1e-4 for the 96- to 128-term
+    dot products)."""
+    info = json.loads((GOLDEN / "reference_ptx_manifest.json").read_text())[case]
+    bufs = inputs.seeded_buffers(info["tensors"], info["launch"]["arg_order"])
+    ref = inputs.reduce_expected(case, bufs)
+    got = golden[f"{case}.out"].astype(np.float64)
+    assert got.shape == ref.shape
+    tol = 1e-4 if case.startswith("m_") or case == "row_dot" else 1e-5
+    assert np.all(np.abs(got - ref) <= tol * np.maximum(1.0, np.abs(ref).max())), (case, np.abs(got - ref).max())
+
