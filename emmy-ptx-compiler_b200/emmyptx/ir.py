@@ -395,6 +395,18 @@ def elementwise_kernel(n: int, inputs: dict, steps: list, out_dtype: str = "f32"
     return g, k, launch
 
 
+def int_elementwise_kernel(n: int, steps: list, in_dtype: str = "i32", out_dtype: str = "i32", inputs=("a",), name: str = "k_int"):
+    """An integer cell program: integer-typed Assigns over the s32 op table (emmyptx/ops.py:294-309) on i32 / i64 buffers of
+    n elements each; `steps` as in elementwise_kernel."""
+    a0 = Axis("a0", Dim(n))
+    body = [Load([b], b, [Var("a0")]) for b in inputs]
+    body += [Assign(v, Op(op), list(args), DType("int")) for v, op, args in steps]
+    body.append(Write("out", [Var("a0")], [steps[-1][0]]))
+    k = KernelOp(name, [Tile([a0], body)])
+    g = _graph(k, [tensor(b, [n], in_dtype) for b in inputs], [tensor("out", [n], out_dtype)])
+    return g, k, _launch(k, [*inputs, "out"], n)
+
+
 def index_gather_kernel(n: int, mul: int = 7919, add: int = 13, div: int = 3, shift: int = 2, name: str = "k_gather"):
     """y[i] = (x[(i*mul + add) % n] // div) ^ (i >> shift), int32."""
     a0 = Axis("a0", Dim(n))

@@ -52,6 +52,8 @@ for name, info in manifest.items():
         out[f"{name}.o"] = bufs["O"]
         print(name, bufs["O"][0, 0, :4])
         continue
+    if info.get("elementwise"):
+        continue                          # run on the GPU only, next to the library's kernels
     if info.get("seeded"):
         bufs = inputs.seeded_buffers(info["tensors"], info["launch"]["arg_order"])
         ptx_interp.run_entry((HERE / f"{name}.ref.ptx").read_text(), bufs, info["launch"]["grid"][0], info["launch"]["block"][0])

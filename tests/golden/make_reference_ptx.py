@@ -192,6 +192,19 @@ REDUCE["m_linear_bias_relu"] = ir.matmul_f32_kernel(64, 96, 128, b_trans=True, b
 REDUCE["m_transpose_lhs"] = ir.matmul_f32_kernel(128, 80, 96, a_trans=True, name="m_transpose_lhs")
 CASES.update(REDUCE)
 
+# The pointwise and dtype cases as elementwise kernels (tests/elementwise_cases.py): only ever run on the GPU next to this
+# library's kernels (no CPU golden vectors: the interpreter does not model every approximation these use).
+sys.path.insert(0, str(HERE.parent))
+import elementwise_cases  # noqa: E402
+
+ELEMENTWISE = {}
+for case, (ins, steps, _expr, _tol) in elementwise_cases.CASES.items():
+    ELEMENTWISE[f"ew_{case}"] = ir.elementwise_kernel(4096, ins, steps, elementwise_cases.OUT_DTYPE.get(case, "f32"), name=f"ew_{case}")
+for case, (steps, in_dt, out_dt, ins) in elementwise_cases.INT_CASES.items():
+    ELEMENTWISE[f"ew_{case}"] = ir.int_elementwise_kernel(4096, steps, in_dt, out_dt, ins, name=f"ew_{case}")
+ELEMENTWISE["ew_d_bool_in"] = ir.elementwise_kernel(4096, *elementwise_cases.BOOL_IN, name="ew_d_bool_in")
+CASES.update(ELEMENTWISE)
+
 for name, (graph, kernel, launch) in CASES.items():
     ptx = compile_kernel(graph, kernel, launch, target="sm_89")
     (HERE / f"{name}.ref.ptx").write_text(ptx)
@@ -200,6 +213,7 @@ for name, (graph, kernel, launch) in CASES.items():
                       **({"attention": dict(zip(("units", "seq_q", "seq_k", "d", "causal", "scale"), ATTENTION[name]))} if name in ATTENTION else {}),
                       **({"layout": True} if name in LAYOUT or name in CONV else {}),
                       **({"seeded": True} if name in REDUCE else {}),
+                      **({"elementwise": True} if name in ELEMENTWISE else {}),
                       "tensors": {t.name: {"shape": [d.as_static() for d in t.shape], "dtype": t.dtype.name}
                                   for n in graph.nodes.values() for t in n.outputs}}
     print(f"{name}: {len(ptx.splitlines())} lines of PTX")

@@ -26,102 +26,7 @@ def program_form(request):
     yield request.param
     runtime.set_pointwise_jit(before)
 
-# id -> (inputs, steps, torch expression over float64 tensors named like the inputs, tolerance)
-CASES = {
-    "p_abs": ({"x": "f32"}, [("a", "abs", ["x"])], "torch.abs(x)", ROUND),
-    "p_neg_sub": ({"x": "f32", "y": "f32"}, [("a", "negative", ["x"]), ("b", "subtract", ["a", "y"])], "-x - y", ROUND),
-    "p_div": ({"x": "f32", "y": "f32"}, [("a", "abs", ["y"]), ("b", "add", ["a", 0.5]), ("c", "divide", ["x", "b"])], "x / (y.abs() + 0.5)", ROUND),
-    "p_max_min": ({"x": "f32", "y": "f32"}, [("a", "maximum", ["x", "y"]), ("b", "minimum", ["x", "y"]), ("c", "add", ["a", "b"])],
-                  "torch.maximum(x, y) + torch.minimum(x, y)", ROUND),
-    "p_log": ({"x": "f32"}, [("a", "abs", ["x"]), ("b", "add", ["a", 0.5]), ("c", "log", ["b"])], "torch.log(x.abs() + 0.5)", TRANS),
-    "p_sqrt_rsqrt": ({"x": "f32"}, [("a", "abs", ["x"]), ("b", "sqrt", ["a"]), ("c", "add", ["a", 0.1]), ("d", "rsqrt", ["c"]), ("e", "add", ["b", "d"])],
-                     "torch.sqrt(x.abs()) + torch.rsqrt(x.abs() + 0.1)", TRANS),
-    "p_reciprocal": ({"x": "f32"}, [("a", "abs", ["x"]), ("b", "add", ["a", 0.5]), ("c", "reciprocal", ["b"])], "torch.reciprocal(x.abs() + 0.5)", ROUND),
-    "p_sigmoid": ({"x": "f32"}, [("a", "sigmoid", ["x"])], "torch.sigmoid(x)", TRANS),
-    "p_relu": ({"x": "f32"}, [("a", "relu", ["x"])], "torch.relu(x)", ROUND),
-    "p_gelu_erf": ({"x": "f32"}, [("a", "multiply", ["x", 0.7071067811865476]), ("b", "erf", ["a"]), ("c", "add", ["b", 1.0]),
-                                  ("d", "multiply", ["x", 0.5]), ("e", "multiply", ["d", "c"])], "F.gelu(x)", TRANS),
-    "p_silu": ({"x": "f32"}, [("a", "sigmoid", ["x"]), ("b", "multiply", ["x", "a"])], "F.silu(x)", TRANS),
-    "p_erf": ({"x": "f32"}, [("a", "erf", ["x"])], "torch.erf(x)", TRANS),
-    "p_sin_cos": ({"x": "f32"}, [("a", "multiply", ["x", 3.0]), ("b", "sin", ["a"]), ("c", "cos", ["a"]), ("d", "add", ["b", "c"])],
-                  "torch.sin(x * 3) + torch.cos(x * 3)", TRANS),
-    "p_square_cube": ({"x": "f32"}, [("a", "square", ["x"]), ("b", "multiply", ["a", "x"]), ("c", "add", ["a", "b"])], "x ** 2 + x ** 3", ROUND),
-    "p_pow_frac": ({"x": "f32"}, [("a", "abs", ["x"]), ("b", "add", ["a", 0.1]), ("c", "pow", ["b", 0.7])], "torch.pow(x.abs() + 0.1, 0.7)", TRANS),
-    "p_clamp": ({"x": "f32"}, [("a", "maximum", ["x", -0.5]), ("b", "minimum", ["a", 0.5])], "torch.clamp(x, -0.5, 0.5)", ROUND),
-    "p_where": ({"x": "f32"}, [("m", "greater", ["x", 0.0]), ("a", "multiply", ["x", 0.1]), ("b", "where", ["m", "x", "a"])],
-                "torch.where(x > 0, x, x * 0.1)", ROUND),
-    "p_cmp_to_float": ({"x": "f32", "y": "f32"}, [("m", "greater", ["x", "y"])], "(x > y).double()", ROUND),
-    "p_lerp": ({"x": "f32", "y": "f32"}, [("a", "subtract", ["y", "x"]), ("b", "multiply", ["a", 0.3]), ("c", "add", ["x", "b"])],
-               "torch.lerp(x, y, 0.3)", ROUND),
-    "p_addcmul": ({"x": "f32", "y": "f32", "z": "f32"}, [("a", "multiply", ["y", "z"]), ("b", "multiply", ["a", 0.5]), ("c", "add", ["x", "b"])],
-                  "torch.addcmul(x, y, z, value=0.5)", ROUND),
-    "p_remainder": ({"x": "f32"}, [("a", "multiply", ["x", 5.0]), ("b", "remainder", ["a", 1.5])], "torch.remainder(x * 5, 1.5)", TRANS),
-    "p_floor_divide": ({"x": "f32"}, [("a", "multiply", ["x", 5.0]), ("b", "floor_divide", ["a", 1.5])], "torch.floor_divide(x * 5, 1.5)", ROUND),
-    "d_f16_add": ({"x": "f16", "y": "f16"}, [("a", "add", ["x", "y"])], "x + y", HALF),
-    "d_bf16_add": ({"x": "bf16", "y": "bf16"}, [("a", "add", ["x", "y"])], "x + y", HALF),
-    "d_bf16_gelu": ({"x": "bf16"}, [("a", "multiply", ["x", 0.7071067811865476]), ("b", "erf", ["a"]), ("c", "add", ["b", 1.0]),
-                                    ("d", "multiply", ["x", 0.5]), ("e", "multiply", ["d", "c"])], "F.gelu(x)", HALF),
-    "d_f32_to_f16": ({"x": "f32"}, [("a", "copy", ["x"])], "x", HALF),
-    "d_f16_gelu": ({"x": "f16"}, [("a", "multiply", ["x", 0.7071067811865476]), ("b", "erf", ["a"]), ("c", "add", ["b", 1.0]),
-                                  ("d", "multiply", ["x", 0.5]), ("e", "multiply", ["d", "c"])], "F.gelu(x)", HALF),
-    # cases the reference's front end decomposes before its compiler sees them; here they are written over the op table directly
-    "p_gelu_tanh": ({"x": "f32"}, [("a", "square", ["x"]), ("b", "multiply", ["a", "x"]), ("c", "multiply", ["b", 0.044715]), ("d", "add", ["x", "c"]),
-                                   ("e", "multiply", ["d", 0.7978845608028654]), ("f", "tanh", ["e"]), ("g", "add", ["f", 1.0]),
-                                   ("h", "multiply", ["x", 0.5]), ("i", "multiply", ["h", "g"])], "F.gelu(x, approximate='tanh')", TRANS),
-    "p_softplus": ({"x": "f32"}, [("a", "exp", ["x"]), ("b", "add", ["a", 1.0]), ("c", "log", ["b"])], "F.softplus(x)", TRANS),
-    "p_mish": ({"x": "f32"}, [("a", "exp", ["x"]), ("b", "add", ["a", 1.0]), ("c", "log", ["b"]), ("d", "tanh", ["c"]), ("e", "multiply", ["x", "d"])],
-               "F.mish(x)", TRANS),
-    "p_elu": ({"x": "f32"}, [("m", "greater", ["x", 0.0]), ("a", "exp", ["x"]), ("b", "subtract", ["a", 1.0]), ("c", "where", ["m", "x", "b"])], "F.elu(x)", TRANS),
-    "p_leaky_relu": ({"x": "f32"}, [("m", "greater", ["x", 0.0]), ("a", "multiply", ["x", 0.1]), ("b", "where", ["m", "x", "a"])], "F.leaky_relu(x, 0.1)", ROUND),
-    "p_hardtanh": ({"x": "f32"}, [("a", "maximum", ["x", -1.0]), ("b", "minimum", ["a", 1.0])], "F.hardtanh(x)", ROUND),
-    "p_hardswish": ({"x": "f32"}, [("a", "add", ["x", 3.0]), ("b", "maximum", ["a", 0.0]), ("c", "minimum", ["b", 6.0]), ("d", "multiply", ["x", "c"]),
-                                   ("e", "divide", ["d", 6.0])], "F.hardswish(x)", ROUND),
-    "p_relu6": ({"x": "f32"}, [("a", "multiply", ["x", 4.0]), ("b", "maximum", ["a", 0.0]), ("c", "minimum", ["b", 6.0])], "F.relu6(x * 4)", ROUND),
-    "p_log1p": ({"x": "f32"}, [("a", "abs", ["x"]), ("b", "add", ["a", 1.0]), ("c", "log", ["b"])], "torch.log1p(x.abs())", TRANS),
-    "p_expm1": ({"x": "f32"}, [("a", "exp", ["x"]), ("b", "subtract", ["a", 1.0])], "torch.expm1(x)", TRANS),
-    "p_floor": ({"x": "f32"}, [("a", "multiply", ["x", 3.0]), ("b", "floor_divide", ["a", 1.0])], "torch.floor(x * 3)", ROUND),
-    "p_floor_ceil": ({"x": "f32"}, [("a", "multiply", ["x", 3.0]), ("b", "floor_divide", ["a", 1.0]), ("c", "multiply", ["x", -5.0]),
-                                    ("d", "floor_divide", ["c", 1.0]), ("e", "subtract", ["b", "d"])], "torch.floor(x * 3) + torch.ceil(x * 5)", ROUND),
-    # round half to even: floor, then one up when the fraction is above a half, or exactly a half with an odd floor
-    "p_round": ({"x": "f32"}, [("a", "multiply", ["x", 3.0]), ("r", "floor_divide", ["a", 1.0]), ("d", "subtract", ["a", "r"]), ("g", "greater", ["d", 0.5]),
-                               ("t", "equal", ["d", 0.5]), ("o", "remainder", ["r", 2.0]), ("u", "multiply", ["t", "o"]), ("v", "maximum", ["g", "u"]),
-                               ("w", "add", ["r", "v"])], "torch.round(x * 3)", ROUND),
-    "p_trunc": ({"x": "f32"}, [("a", "multiply", ["x", 3.0]), ("f", "floor_divide", ["a", 1.0]), ("n", "negative", ["a"]), ("g", "floor_divide", ["n", 1.0]),
-                               ("c", "negative", ["g"]), ("m", "greater_equal", ["a", 0.0]), ("t", "where", ["m", "f", "c"])], "torch.trunc(x * 3)", ROUND),
-    "p_sign": ({"x": "f32"}, [("p", "greater", ["x", 0.0]), ("n", "less", ["x", 0.0]), ("s", "subtract", ["p", "n"])], "torch.sign(x)", ROUND),
-    "p_exp2_log2": ({"x": "f32"}, [("a", "multiply", ["x", 0.6931471805599453]), ("b", "exp", ["a"]), ("c", "abs", ["x"]), ("d", "add", ["c", 0.5]),
-                                   ("e", "log", ["d"]), ("f", "multiply", ["e", 1.4426950408889634]), ("g", "add", ["b", "f"])],
-                    "torch.exp2(x) + torch.log2(x.abs() + 0.5)", TRANS),
-    # atan: |x| or its reciprocal in [0, 1], halved once more by atan(t) = 2 atan(t / (1 + sqrt(1 + t^2))), then the odd series to u^11
-    "p_atan": ({"x": "f32"}, [("ax", "abs", ["x"]), ("rc", "reciprocal", ["ax"]), ("t", "minimum", ["ax", "rc"]), ("t2", "square", ["t"]), ("q", "add", ["t2", 1.0]),
-                              ("sq", "sqrt", ["q"]), ("dn", "add", ["sq", 1.0]), ("u", "divide", ["t", "dn"]), ("u2", "square", ["u"]),
-                              ("p5", "multiply", ["u2", -0.09090909090909091]), ("p4", "add", ["p5", 0.1111111111111111]), ("p4m", "multiply", ["p4", "u2"]),
-                              ("p3", "add", ["p4m", -0.14285714285714285]), ("p3m", "multiply", ["p3", "u2"]), ("p2", "add", ["p3m", 0.2]),
-                              ("p2m", "multiply", ["p2", "u2"]), ("p1", "add", ["p2m", -0.3333333333333333]), ("p1m", "multiply", ["p1", "u2"]),
-                              ("p0", "add", ["p1m", 1.0]), ("at", "multiply", ["p0", "u"]), ("a2", "multiply", ["at", 2.0]),
-                              ("big", "greater", ["ax", 1.0]), ("co", "subtract", [1.5707963267948966, "a2"]), ("r", "where", ["big", "co", "a2"]),
-                              ("neg", "less", ["x", 0.0]), ("nr", "negative", ["r"]), ("out", "where", ["neg", "nr", "r"])], "torch.atan(x)", TRANS),
-    # atan2(x, y): the angle of (y, x) -- atan of min / max of the magnitudes as in p_atan (one halving, series to u^11),
-    # then pi/2 - a where |x| > |y|, pi - a where y < 0, and the sign of x
-    "p_atan2": ({"x": "f32", "y": "f32"}, [("ax", "abs", ["x"]), ("ay", "abs", ["y"]), ("lo", "minimum", ["ax", "ay"]), ("hi", "maximum", ["ax", "ay"]),
-                                           ("t", "divide", ["lo", "hi"]), ("t2", "square", ["t"]), ("q", "add", ["t2", 1.0]), ("sq", "sqrt", ["q"]),
-                                           ("dn", "add", ["sq", 1.0]), ("u", "divide", ["t", "dn"]), ("u2", "square", ["u"]),
-                                           ("p5", "multiply", ["u2", -0.09090909090909091]), ("p4", "add", ["p5", 0.1111111111111111]), ("p4m", "multiply", ["p4", "u2"]),
-                                           ("p3", "add", ["p4m", -0.14285714285714285]), ("p3m", "multiply", ["p3", "u2"]), ("p2", "add", ["p3m", 0.2]),
-                                           ("p2m", "multiply", ["p2", "u2"]), ("p1", "add", ["p2m", -0.3333333333333333]), ("p1m", "multiply", ["p1", "u2"]),
-                                           ("p0", "add", ["p1m", 1.0]), ("at", "multiply", ["p0", "u"]), ("a2", "multiply", ["at", 2.0]),
-                                           ("steep", "greater", ["ax", "ay"]), ("co", "subtract", [1.5707963267948966, "a2"]), ("r1", "where", ["steep", "co", "a2"]),
-                                           ("left", "less", ["y", 0.0]), ("su", "subtract", [3.141592653589793, "r1"]), ("r2", "where", ["left", "su", "r1"]),
-                                           ("neg", "less", ["x", 0.0]), ("nr", "negative", ["r2"]), ("out", "where", ["neg", "nr", "r2"])], "torch.atan2(x, y)", TRANS),
-    "p_cmp_bool_out": ({"x": "f32", "y": "f32"}, [("m", "greater", ["x", "y"])], "x > y", ROUND),
-    "p_pow_tensor": ({"x": "f32", "y": "f32"}, [("a", "abs", ["x"]), ("b", "add", ["a", 0.1]), ("c", "pow", ["b", "y"])], "torch.pow(x.abs() + 0.1, y)", (1e-4, 1e-5)),
-    "p_masked_fill": ({"x": "f32"}, [("m", "less", ["x", 0.0]), ("a", "where", ["m", 0.0, "x"])], "x.masked_fill(x < 0, 0.0)", ROUND),
-    # fmod keeps the dividend's sign: a - b * trunc(a / b)
-    "p_fmod": ({"x": "f32"}, [("a", "multiply", ["x", 5.0]), ("q", "divide", ["a", 1.5]), ("f", "floor_divide", ["q", 1.0]), ("n", "negative", ["q"]),
-                              ("g", "floor_divide", ["n", 1.0]), ("c", "negative", ["g"]), ("m", "greater_equal", ["q", 0.0]), ("t", "where", ["m", "f", "c"]),
-                              ("p", "multiply", ["t", 1.5]), ("r", "subtract", ["a", "p"])], "torch.fmod(x * 5, 1.5)", TRANS),
-}
-OUT_DTYPE = {"p_cmp_bool_out": "bool", "d_f16_gelu": "f16", "d_f16_add": "f16", "d_bf16_add": "bf16", "d_bf16_gelu": "bf16", "d_f32_to_f16": "f16"}
+from elementwise_cases import BOOL_IN, CASES, INT_CASES, OUT_DTYPE  # noqa: E402  (the cases as data, shared with the fixture generator)
 
 
 def _expected(expr, arrays):
@@ -154,6 +59,52 @@ def test_reference_pointwise_cases(case, n, cuda):
     assert res["ok"], (case, res)
 
 
+@pytest.mark.parametrize("case", sorted(CASES))
+def test_reference_kernel_for_the_same_ir(case, cuda, program_form):
+    """Kernel against kernel: the reference compiler's PTX for the same elementwise IR (tests/golden/ew_<case>.ref.ptx,
+    one thread per element) JIT-loaded on this GPU and run on the same device buffers. Both results sit inside the
+    reference's class of the float64 expression, and they agree with each other inside it."""
+    import torch
+    from pathlib import Path
+    from emmyptx.ptx_driver import PtxModule
+    from oracle import reference
+    if program_form != "compiled":
+        pytest.skip("one comparison per case is enough")
+    golden = Path(__file__).resolve().parent / "golden"
+    manifest = json.loads((golden / "reference_ptx_manifest.json").read_text())[f"ew_{case}"]
+    inputs, steps, expr, tol = CASES[case]
+    out_dtype = OUT_DTYPE.get(case, "f32")
+    n = 4096
+    built = ir.elementwise_kernel(n, inputs, steps, out_dtype, name=f"ew_{case}")
+    assert built[2] == manifest["launch"]                                # the fixture was made from this IR
+    handle = json.loads(compile_kernel(*built))
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16, "bool": torch.bool}
+    dev, arrays = {}, {}
+    for i, (b, dt) in enumerate(inputs.items()):
+        host = run_local.to_device(np.random.default_rng(i).standard_normal([n]), dt)
+        arrays[b] = run_local.from_device(host, dt).astype(np.float64)
+        t = torch.from_numpy(np.ascontiguousarray(host))
+        dev[b] = (t.view(torch.bfloat16) if dt == "bf16" else t).to(cuda)
+    ours = torch.zeros(n, dtype=tdt[out_dtype], device=cuda)
+    theirs = torch.zeros(n, dtype=tdt[out_dtype], device=cuda)
+    run_local.init()
+    run_local.launch(handle, dict(dev, out=ours))
+    launch = built[2]
+    with PtxModule((golden / f"ew_{case}.ref.ptx").read_text()) as m:
+        m.launch(m.function(f"ew_{case}"), [dev[nm].data_ptr() if nm != "out" else theirs.data_ptr() for nm in launch["arg_order"]],
+                 launch["grid"][0], launch["block"][0])
+        m.synchronize()
+    torch.cuda.synchronize()
+    ref = _expected(expr, arrays)
+    rtol, atol = tol if isinstance(tol, tuple) else (tol, tol)
+    o, t = ours.double().cpu().numpy(), theirs.double().cpu().numpy()
+    assert reference.compare(o, ref, rtol, atol)["ok"]
+    res = reference.compare(t, ref, rtol, atol)
+    assert res["ok"], ("the reference's kernel against float64", case, res)
+    res = reference.compare(o, t, 2 * rtol, 2 * atol)
+    assert res["ok"], ("kernel against kernel", case, res)
+
+
 def test_program_limits_are_compile_errors():
     from emmyptx.kernel import CompileError
     steps = [(f"v{i}", "add", ["x" if i == 0 else f"v{i-1}", float(i)]) for i in range(20)]            # 20 distinct constants
@@ -169,15 +120,7 @@ def test_program_limits_are_compile_errors():
 
 # ---- integer programs and bool inputs (tools/torch_cases/dtypes.py:11-16) -----------------------------------------
 def _int_kernel(n, steps, in_dt="i32", out_dt="i32", ins=("a",)):
-    """Kernel IR of an integer cell program: integer-typed Assigns over the s32 op table (emmyptx/ops.py:294-309)."""
-    from emmyptx.ir import Assign, Axis, DType, Dim, KernelOp, Load, Op, Tile, Var, Write, _graph, _launch, tensor
-    a0 = Axis("a0", Dim(n))
-    body = [Load([b], b, [Var("a0")]) for b in ins]
-    body += [Assign(v, Op(op), list(args), DType("int")) for v, op, args in steps]
-    body.append(Write("out", [Var("a0")], [steps[-1][0]]))
-    k = KernelOp("k_int", [Tile([a0], body)])
-    g = _graph(k, [tensor(b, [n], in_dt) for b in ins], [tensor("out", [n], out_dt)])
-    return g, k, _launch(k, [*ins, "out"], n)
+    return ir.int_elementwise_kernel(n, steps, in_dt, out_dt, ins)
 
 
 def _run_built(built, arrays, out_dtype, n, **kw):
@@ -242,6 +185,46 @@ def test_bool_mask_input(n, cuda):
     built = ir.elementwise_kernel(n, {"x": "f32", "m": "bool"}, [("nx", "negative", ["x"]), ("y", "where", ["m", "x", "nx"])])
     got = _run_built(built, {"x": x, "m": m}, torch.float32, n)
     assert np.array_equal(got, np.where(m, x, -x))
+
+
+@pytest.mark.parametrize("case", sorted(INT_CASES) + ["d_bool_in"])
+def test_integer_and_bool_input_kernels_against_the_reference_kernel(case, cuda, program_form):
+    """The reference's PTX for the same integer IR (div.s32 / rem.s32: truncating `//` and `%`, which `int_div="trunc"`
+    reproduces) and for the bool-input program, on the same device buffers: bit for bit."""
+    import torch
+    from pathlib import Path
+    from emmyptx.kernel import KernelCompiler
+    from emmyptx.ptx_driver import PtxModule
+    if program_form != "compiled":
+        pytest.skip("one comparison per case is enough")
+    golden = Path(__file__).resolve().parent / "golden"
+    n = 4096
+    rng = np.random.default_rng(5)
+    if case == "d_bool_in":
+        built = ir.elementwise_kernel(n, *BOOL_IN, name="ew_d_bool_in")
+        host = {"x": rng.standard_normal(n).astype(np.float32), "m": rng.standard_normal(n) > 0}
+        out_dt = torch.float32
+    else:
+        steps, in_dt, out_dt_name, ins = INT_CASES[case]
+        built = ir.int_elementwise_kernel(n, steps, in_dt, out_dt_name, ins, name=f"ew_{case}")
+        npdt = np.int64 if in_dt == "i64" else np.int32
+        lo, hi = (-2**31, 2**31) if case == "int_wrap_shift" else (-8, 8)
+        host = {b: rng.integers(lo, hi, n).astype(npdt) for b in ins}
+        out_dt = torch.int64 if out_dt_name == "i64" else torch.int32
+    manifest = json.loads((golden / "reference_ptx_manifest.json").read_text())[f"ew_{case}"]
+    assert built[2] == manifest["launch"]
+    handle = json.loads(KernelCompiler(*built, int_div="trunc").compile())
+    dev = {b: torch.from_numpy(a).to(cuda) for b, a in host.items()}
+    ours, theirs = torch.zeros(n, dtype=out_dt, device=cuda), torch.zeros(n, dtype=out_dt, device=cuda)
+    run_local.init()
+    run_local.launch(handle, dict(dev, out=ours))
+    launch = built[2]
+    with PtxModule((golden / f"ew_{case}.ref.ptx").read_text()) as m:
+        m.launch(m.function(f"ew_{case}"), [dev[nm].data_ptr() if nm != "out" else theirs.data_ptr() for nm in launch["arg_order"]],
+                 launch["grid"][0], launch["block"][0])
+        m.synchronize()
+    torch.cuda.synchronize()
+    assert torch.equal(ours, theirs)
 
 
 # ---- broadcast inputs (f_batch_norm_eval, m_outer, s_expand: tools/torch_cases/fused.py:18-20, matmul.py:23, shapes.py) ----
