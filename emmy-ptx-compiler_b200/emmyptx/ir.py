@@ -395,6 +395,21 @@ def elementwise_kernel(n: int, inputs: dict, steps: list, out_dtype: str = "f32"
     return g, k, launch
 
 
+def broadcast_kernel(rows: int, cols: int, loads: list, steps: list, inputs: dict, name: str = "k_bcast"):
+    """An elementwise kernel over a [rows, cols] tile whose inputs may be smaller than the tile: `loads` is a list of
+    (value, buffer, axis names) -- a buffer indexed by ("r0", "c0") is the matrix, by ("c0",) a row vector, by ("r0",) a
+    column vector -- `inputs` maps buffer -> shape (fp32), `steps` as in elementwise_kernel. The reference's broadcast cases:
+    f_batch_norm_eval, m_outer, s_expand, p_bcast_rowcol (tools/torch_cases/fused.py:18-20, matmul.py:23, shapes.py:19,
+    pointwise.py:56)."""
+    r0, c0 = Axis("r0", Dim(rows)), Axis("c0", Dim(cols))
+    body = [Load([v], buf, [Var(a) for a in axes]) for v, buf, axes in loads]
+    body += [Assign(v, Op(op), list(args)) for v, op, args in steps]
+    body.append(Write("out", [Var("r0"), Var("c0")], [steps[-1][0]]))
+    k = KernelOp(name, [Tile([r0, c0], body)])
+    g = _graph(k, [tensor(nm, shp, "f32") for nm, shp in inputs.items()], [tensor("out", [rows, cols], "f32")])
+    return g, k, _launch(k, [*inputs, "out"], rows * cols)
+
+
 def int_elementwise_kernel(n: int, steps: list, in_dtype: str = "i32", out_dtype: str = "i32", inputs=("a",), name: str = "k_int"):
     """An integer cell program: integer-typed Assigns over the s32 op table (emmyptx/ops.py:294-309) on i32 / i64 buffers of
     n elements each; `steps` as in elementwise_kernel."""

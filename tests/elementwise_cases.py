@@ -116,3 +116,15 @@ INT_CASES = {
 # d_bool_in (dtypes.py:16): a bool buffer as a graph input of a float program
 BOOL_IN = ({"x": "f32", "m": "bool"}, [("nx", "negative", ["x"]), ("y", "where", ["m", "x", "nx"])])
 
+# Broadcast inputs at [33, 61] (ragged against every access width): id -> (loads, steps, inputs {buffer: shape}, numpy expression)
+BCAST_SHAPE = (33, 61)
+BCAST_CASES = {
+    "f_batch_norm_eval": ([("x", "X", ("r0", "c0")), ("m", "M", ("c0",)), ("w", "W", ("c0",)), ("b", "B", ("c0",))],
+                          [("d", "subtract", ["x", "m"]), ("s", "multiply", ["d", "w"]), ("o", "add", ["s", "b"])],
+                          {"X": [33, 61], "M": [61], "W": [61], "B": [61]}, "(X - M) * W + B"),
+    "m_outer": ([("a", "A", ("r0",)), ("v", "V", ("c0",))], [("o", "multiply", ["a", "v"])], {"A": [33], "V": [61]}, "A[:, None] * V[None, :]"),
+    "p_bcast_rowcol": ([("x", "X", ("r0", "c0")), ("r", "R", ("c0",)), ("c", "C", ("r0",))], [("p", "multiply", ["x", "r"]), ("o", "add", ["p", "c"])],
+                       {"X": [33, 61], "R": [61], "C": [33]}, "X * R + C[:, None]"),
+    "s_expand": ([("v", "V", ("c0",))], [("o", "add", ["v", 0.0])], {"V": [61]}, "np.broadcast_to(V, (33, 61)) + np.float32(0)"),
+}
+

@@ -26,7 +26,7 @@ def program_form(request):
     yield request.param
     runtime.set_pointwise_jit(before)
 
-from elementwise_cases import BOOL_IN, CASES, INT_CASES, OUT_DTYPE  # noqa: E402  (the cases as data, shared with the fixture generator)
+from elementwise_cases import BCAST_CASES, BCAST_SHAPE, BOOL_IN, CASES, INT_CASES, OUT_DTYPE  # noqa: E402  (the cases as data, shared with the fixture generator)
 
 
 def _expected(expr, arrays):
@@ -229,14 +229,45 @@ def test_integer_and_bool_input_kernels_against_the_reference_kernel(case, cuda,
 
 # ---- broadcast inputs (f_batch_norm_eval, m_outer, s_expand: tools/torch_cases/fused.py:18-20, matmul.py:23, shapes.py) ----
 def _tile2(rows, cols, loads, steps, ins, out_shape):
-    from emmyptx.ir import Assign, Axis, Dim, KernelOp, Load, Op, Tile, Var, Write, _graph, _launch, tensor
-    r0, c0 = Axis("r0", Dim(rows)), Axis("c0", Dim(cols))
-    body = [Load([v], buf, [Var(a) for a in axes]) for v, buf, axes in loads]
-    body += [Assign(v, Op(op), list(args)) for v, op, args in steps]
-    body.append(Write("out", [Var("r0"), Var("c0")], [steps[-1][0]]))
-    k = KernelOp("k_bcast", [Tile([r0, c0], body)])
-    g = _graph(k, [tensor(nm, shp, "f32") for nm, shp in ins.items()], [tensor("out", out_shape, "f32")])
-    return g, k, _launch(k, [*ins, "out"], rows * cols)
+    assert list(out_shape) == [rows, cols]
+    return ir.broadcast_kernel(rows, cols, loads, steps, ins)
+
+
+@pytest.mark.parametrize("case", sorted(BCAST_CASES))
+def test_broadcast_kernels_against_the_reference_kernel(case, cuda, program_form):
+    """The reference's PTX for the same broadcast IR on the same device buffers. Ours equals numpy bit for bit (every
+    operation rounded on its own, as torch evaluates the expression); the reference's kernel agrees bit for bit where there
+    is one operation per element, and to one rounding (1e-6) where a multiply feeds an add: the driver's JIT contracts
+    those two of its PTX into a fused multiply-add."""
+    import torch
+    from pathlib import Path
+    from emmyptx.ptx_driver import PtxModule
+    if program_form != "compiled":
+        pytest.skip("one comparison per case is enough")
+    golden = Path(__file__).resolve().parent / "golden"
+    loads, steps, ins, expr = BCAST_CASES[case]
+    rows, cols = BCAST_SHAPE
+    built = ir.broadcast_kernel(rows, cols, loads, steps, ins, name=f"bc_{case}")
+    manifest = json.loads((golden / "reference_ptx_manifest.json").read_text())[f"bc_{case}"]
+    assert built[2] == manifest["launch"]
+    handle = json.loads(compile_kernel(*built))
+    assert handle["variant"] == "pointwise_program"
+    host = {nm: np.random.default_rng(i).standard_normal(shp).astype(np.float32) for i, (nm, shp) in enumerate(ins.items())}
+    dev = {nm: torch.from_numpy(a).to(cuda) for nm, a in host.items()}
+    ours, theirs = torch.zeros(rows, cols, device=cuda), torch.zeros(rows, cols, device=cuda)
+    run_local.init()
+    run_local.launch(handle, dict(dev, out=ours))
+    launch = built[2]
+    with PtxModule((golden / f"bc_{case}.ref.ptx").read_text()) as m:
+        m.launch(m.function(f"bc_{case}"), [dev[nm].data_ptr() if nm != "out" else theirs.data_ptr() for nm in launch["arg_order"]],
+                 launch["grid"][0], launch["block"][0])
+        m.synchronize()
+    torch.cuda.synchronize()
+    if [st[1] for st in steps][-2:] == ["multiply", "add"]:
+        assert torch.allclose(ours, theirs, rtol=1e-6, atol=1e-6)
+    else:
+        assert torch.equal(ours, theirs)
+    assert np.array_equal(ours.cpu().numpy(), eval(expr, {"np": np, **host}).astype(np.float32))
 
 
 @pytest.mark.parametrize("rows,cols", [(32, 64), (33, 61), (67, 1032)])
