@@ -383,6 +383,11 @@ class Interpreter:
         mods = parts[1:]
         dst_ty, src_ty = mods[-2], mods[-1]
         rnd = mods[0] if len(mods) == 3 else None
+        if dst_ty == "f32" and src_ty in ("f16", "bf16"):       # widening a 16-bit element (exact)
+            h = np.asarray(self.reg[ops[1]]).astype(np.uint16)
+            wide = h.view(np.float16).astype(np.float32) if src_ty == "f16" else (h.astype(np.uint32) << np.uint32(16)).view(np.float32)
+            self._set(ops[0], wide, mask)
+            return
         a = V(ops[1], src_ty)
         if dst_ty == "f32" and src_ty == "f32":
             f = {"rni": np.rint, "rzi": np.trunc, "rmi": np.floor, "rpi": np.ceil}[rnd]

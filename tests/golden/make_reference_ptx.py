@@ -65,7 +65,8 @@ GEMMS = {       # name: (m, n, k, dtype, b_trans, batch, device)
     "m_bf16_mm": (512, 512, 512, "bf16", False, (), True),                   # matmul.py:30
     "m_f16_linear": (64, 512, 256, "f16", True, (), True),                   # matmul.py:32, B stored N x K
     "m_f16_bmm": (128, 96, 64, "f16", False, (4,), True),                    # matmul.py:31
-    "c3_f16_mm_4096": (4096, 4096, 4096, "f16", False, (), True),            # configuration 3: timed on the device only
+    "c3_f16_mm_4096": (4096, 4096, 4096, "f16", False, (), True),            # configuration 3: run on the device only
+    "c4_bf16_mm_16384": (16384, 16384, 16384, "bf16", False, (), True),      # configuration 4's product (its GELU is refused as a fused store)
     "m_f16_mm_f32out": (128, 128, 256, "f16", False, (), True),              # the accumulator stored to an f32 buffer (mma.py:205-207)
     "m_bf16_mm_splitk4": (128, 128, 256, "bf16", False, (), True),           # four cells per output cell, red.add.f32 (mma.py:239-240)
 }
@@ -76,6 +77,19 @@ ATTENTION = {   # name: (units shape, seq_q, seq_k, d, causal, scale)
     "f_sdpa": ([1, 2], 64, 64, 32, False, None),                              # fused.py:21-22
     "t_causal_sdpa": ([1, 4], 128, 128, 64, True, None),                      # models.py:17-19
     "f_masked_attn_manual": ([1], 64, 64, 32, True, 0.17677669),              # fused.py:31-36: scores above the diagonal filled
+}
+
+
+# The same scalar loops on 16-bit buffers (loads widened to fp32, the result rounded once at the store): what pins the
+# tensor-core attention kernels, which take f16 / bf16 at head sizes 64 and 128, to a kernel the reference compiles.
+ATTENTION16 = {   # name: (units shape, seq_q, seq_k, d, causal, scale, dtype)
+    "att16_bf16_causal_d64": ([1, 2], 128, 128, 64, True, None, "bf16"),
+    "att16_f16_d128": ([2], 128, 128, 128, False, None, "f16"),
+    # long enough for the two-tile kernel (eight key tiles): run on the GPU only, next to both kernel forms
+    "att16_bf16_s1024_d128": ([2], 1024, 1024, 128, False, None, "bf16"),
+    "att16_bf16_causal_s1024_d128": ([2], 1024, 1024, 128, True, None, "bf16"),
+    # one unit of configuration 5 (4096 x 4096 x 128, bf16)
+    "att16_bf16_s4096_d128": ([1], 4096, 4096, 128, False, None, "bf16"),
 }
 
 
@@ -163,6 +177,11 @@ for name, (units, sq, sk, d, causal, scale) in ATTENTION.items():
     assert_indices_are_axes(graph, kernel)
     CASES[name] = (graph, kernel, launch)
 
+for name, (units, sq, sk, d, causal, scale, dtype) in ATTENTION16.items():
+    graph, kernel, launch = ir.attention_scalar_kernel(units, sq, sk, d, dtype, scale, causal, name=name)
+    assert_indices_are_axes(graph, kernel)
+    CASES[name] = (graph, kernel, launch)
+
 LAYOUT = ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_stack", "s_tril", "s_cat_a", "s_cat_b",      # shapes.py:6-19
           "s_roll", "s_embedding", "s_gather", "s_tril_select", "s_window_let", "s_cat_cond",
           "c_avg_pool1d", "c_max_pool2d"]                                                                              # conv.py:8-9
@@ -213,6 +232,7 @@ for name, (graph, kernel, launch) in CASES.items():
     manifest[name] = {"entry": kernel.name, "launch": launch, **({"gemm": dict(zip(("m", "n", "k", "dtype", "b_trans", "batch", "device"), GEMMS[name]), out_f32=name in GEMM_OUT,
                                        split_k=GEMM_OUT.get(name, (None, 1))[1])} if name in GEMMS else {}),
                       **({"attention": dict(zip(("units", "seq_q", "seq_k", "d", "causal", "scale"), ATTENTION[name]))} if name in ATTENTION else {}),
+                      **({"attention": dict(zip(("units", "seq_q", "seq_k", "d", "causal", "scale", "dtype"), ATTENTION16[name]))} if name in ATTENTION16 else {}),
                       **({"layout": True} if name in LAYOUT or name in CONV else {}),
                       **({"seeded": True} if name in REDUCE else {}),
                       **({"elementwise": True} if name in ELEMENTWISE else {}),

@@ -146,6 +146,109 @@ def test_attention_against_the_reference_kernel(manifest, cuda, case):
     assert np.allclose(cpu, theirs_np, rtol=1e-5, atol=4e-6)          # ex2.approx and the division differ in the last bits
 
 
+@pytest.mark.parametrize("case", ["c3_f16_mm_4096", "c4_bf16_mm_16384"])
+def test_benchmark_size_products_against_the_reference_kernel(manifest, cuda, case):
+    """Configurations 3 and 4 at their own sizes (4096^3 fp16; 16384^3 bf16): the reference's tensor-core lowering of the same
+    IR (one warp per m16n8k16 cell, fragments read from global memory, emmyptx/mma.py:128-180) and `gemm_tcgen05_kernel` on
+    the same device buffers. Both accumulate in fp32 and round once, so the outputs agree to one unit of the output type
+    (the k order differs), and most elements are identical. Configuration 4's tanh-GELU cannot be part of the reference's
+    store, so the fused epilogue is checked against the same GELU applied to this library's own unfused product."""
+    import torch
+    from emmyptx import runtime
+    info = manifest[case]
+    g = info["gemm"]
+    td = torch.float16 if g["dtype"] == "f16" else torch.bfloat16
+    gen = torch.Generator(device=cuda)
+    gen.manual_seed(5)
+    a = (torch.randn(g["m"], g["k"], device=cuda, generator=gen) / g["k"] ** 0.5).to(td)
+    b = (torch.randn(g["k"], g["n"], device=cuda, generator=gen) / g["k"] ** 0.5).to(td)
+    theirs = torch.zeros(g["m"], g["n"], device=cuda, dtype=td)
+    torch.cuda.synchronize()
+    run_ptx((GOLDEN / f"{case}.ref.ptx").read_text(), info["entry"], [a.data_ptr(), b.data_ptr(), theirs.data_ptr()],
+            info["launch"]["grid"][0], info["launch"]["block"][0])
+    ours = runtime.gemm(a, b)
+    torch.cuda.synchronize()
+    unit = 2.0 ** (-8 if g["dtype"] == "bf16" else -11)
+    rows = torch.randperm(g["m"], device=cuda, generator=gen)[:1024]                 # a sample of whole rows keeps the fp32 copies small
+    o, t = ours[rows].float(), theirs[rows].float()
+    assert bool(((o - t).abs() <= unit * t.abs() + 1e-3 * unit).all())
+    assert float((ours[rows] == theirs[rows]).float().mean()) > 0.9
+    ref = (a[rows[:64]].double() @ b.double())
+    assert bool(((ours[rows[:64]].double() - ref).abs() <= unit * ref.abs() + 1e-3).all())
+    if case.startswith("c4"):
+        del theirs
+        fused = runtime.gemm(a, b, epilogue="gelu_tanh")
+        torch.cuda.synchronize()
+        want = torch.nn.functional.gelu(ours[rows].float(), approximate="tanh")
+        # the fused epilogue sees the fp32 accumulator, the comparison its bf16 rounding: two roundings apart at most
+        assert bool(((fused[rows].float() - want).abs() <= 2 * unit * want.abs() + 2 * unit * 0.05).all())
+    assert runtime.device_status() == 0
+
+
+@pytest.mark.parametrize("case", ["att16_bf16_s1024_d128", "att16_bf16_causal_s1024_d128", "att16_bf16_s4096_d128"])
+def test_both_attention_forms_against_the_reference_kernel(manifest, cuda, case):
+    """Eight key tiles per unit and more (the last case is one unit of configuration 5: 4096 x 4096 x 128): long enough for
+    `attention_fwd_pair_kernel` (two query tiles per CTA), which the library would pick here only with more units, so both
+    forms are forced in turn and compared with the reference's scalar-loop
+    kernel for the same IR on the same device buffers (a few seconds of CUDA-core work). Both forms inside the reference's
+    bf16 class of the float64 attention and within two units of bf16 of the reference's kernel."""
+    import torch
+    from emmyptx import runtime
+    info = manifest[case]
+    a = info["attention"]
+    units = int(np.prod(a["units"]))
+    q, k, v = (t.to(cuda) for t in inputs.attention_inputs(units, a["seq_q"], a["seq_k"], a["d"], a["dtype"]))
+    theirs = torch.zeros_like(q)
+    torch.cuda.synchronize()
+    run_ptx((GOLDEN / f"{case}.ref.ptx").read_text(), info["entry"], [q.data_ptr(), k.data_ptr(), v.data_ptr(), theirs.data_ptr()],
+            info["launch"]["grid"][0], info["launch"]["block"][0])
+    torch.cuda.synchronize()
+    ref = reference.attention_reference(q.cpu(), k.cpu(), v.cpu(), scale=None, double=True, causal=a["causal"]).numpy()
+    theirs_np = theirs.cpu().double().numpy()
+    assert reference.compare(theirs_np, ref, rtol=5e-2, atol=5e-1)["ok"]
+    unit = 2.0 ** -8 * max(1.0, float(np.abs(ref).max()))
+    for form in ("one_tile", "two_tiles"):
+        ours = runtime.attention(q, k, v, causal=a["causal"], form=form)
+        torch.cuda.synchronize()
+        ours_np = ours.cpu().double().numpy()
+        assert reference.compare(ours_np, ref, rtol=5e-2, atol=5e-1)["ok"], form
+        assert np.abs(ours_np - theirs_np).max() <= 2 * unit, (form, float(np.abs(ours_np - theirs_np).max()))
+    assert runtime.device_status() == 0
+
+
+@pytest.mark.parametrize("case", ["att16_bf16_causal_d64", "att16_f16_d128"])
+def test_tensor_core_attention_against_the_reference_kernel(manifest, cuda, case):
+    """16-bit q, k, v at the head sizes the tensor-core kernels take: the reference's PTX for the scalar-loop kernel on
+    16-bit buffers (every product and sum in fp32, one rounding at the store) and `attention_fwd_kernel` (tcgen05; P rounded
+    to 16 bits before the second product) on the same device buffers. Both inside the reference's 16-bit matmul class of the
+    float64 attention (HALF_MM / BF16_MM, tools/torch_cases/matmul.py:7), kernel against kernel within two units of the
+    output type at the result's scale, and the CPU execution of the PTX agreeing with the GPU's to one unit."""
+    import torch
+    from emmyptx import ir, runtime
+    from emmyptx.kernel import compile_kernel
+    info = manifest[case]
+    a = info["attention"]
+    units = int(np.prod(a["units"]))
+    handle = json.loads(compile_kernel(*ir.attention_scalar_kernel(a["units"], a["seq_q"], a["seq_k"], a["d"], a["dtype"], a["scale"], a["causal"], name=case)))
+    assert handle["variant"] == "attention_fwd" and handle["params"]["dtype"] == a["dtype"] and handle["params"]["causal"] == a["causal"]
+    q, k, v = (t.to(cuda) for t in inputs.attention_inputs(units, a["seq_q"], a["seq_k"], a["d"], a["dtype"]))
+    theirs = torch.zeros_like(q)
+    torch.cuda.synchronize()
+    run_ptx((GOLDEN / f"{case}.ref.ptx").read_text(), info["entry"], [q.data_ptr(), k.data_ptr(), v.data_ptr(), theirs.data_ptr()],
+            info["launch"]["grid"][0], info["launch"]["block"][0])
+    ours = runtime.attention(q, k, v, scale=handle["params"]["scale"], causal=a["causal"])
+    torch.cuda.synchronize()
+    ref = reference.attention_reference(q.cpu(), k.cpu(), v.cpu(), scale=handle["params"]["scale"], double=True, causal=a["causal"]).numpy()
+    tol = dict(rtol=5e-2, atol=5e-1) if a["dtype"] == "bf16" else dict(rtol=2e-2, atol=1e-1)
+    theirs_np, ours_np = theirs.cpu().double().numpy(), ours.cpu().double().numpy()
+    assert reference.compare(theirs_np, ref, **tol)["ok"]
+    assert reference.compare(ours_np, ref, **tol)["ok"]
+    unit = (2.0 ** -8 if a["dtype"] == "bf16" else 2.0 ** -11) * max(1.0, float(np.abs(ref).max()))
+    assert np.abs(ours_np - theirs_np).max() <= 2 * unit, float(np.abs(ours_np - theirs_np).max())
+    cpu = np.load(GOLDEN / "golden.npz")[f"{case}.o"].astype(np.float64)
+    assert np.abs(cpu - theirs_np).max() <= unit
+
+
 @pytest.mark.parametrize("case", ["m_f16_mm_f32out", "m_bf16_mm_splitk4"])
 def test_f32_output_gemm_against_the_reference_kernel(manifest, cuda, case):
     """The reference's store of an accumulator fragment to an f32 buffer, plain and as the split-K form (four cells per

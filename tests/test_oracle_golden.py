@@ -209,3 +209,16 @@ def test_reduction_and_f32_product_fixtures(golden, case):
     tol = 1e-4 if case.startswith("m_") or case == "row_dot" else 1e-5
     assert np.all(np.abs(got - ref) <= tol * np.maximum(1.0, np.abs(ref).max())), (case, np.abs(got - ref).max())
 
+
+@pytest.mark.parametrize("case", ["att16_bf16_causal_d64", "att16_f16_d128"])
+def test_16_bit_attention_fixture(golden, case):
+    """The reference's PTX for the scalar-loop attention on 16-bit buffers, executed on the CPU: the float64 attention of the
+    same rounded operands to within one rounding to the output type."""
+    import torch
+    a = json.loads((GOLDEN / "reference_ptx_manifest.json").read_text())[case]["attention"]
+    units = int(np.prod(a["units"]))
+    q, k, v = inputs.attention_inputs(units, a["seq_q"], a["seq_k"], a["d"], a["dtype"])
+    ref = reference.attention_reference(q, k, v, scale=a["scale"], double=True, causal=a["causal"]).numpy()
+    unit = (2.0 ** -8 if a["dtype"] == "bf16" else 2.0 ** -11) * max(1.0, float(np.abs(ref).max()))
+    assert np.abs(golden[f"{case}.o"].astype(np.float64) - ref).max() <= unit
+
