@@ -33,7 +33,8 @@ class PtxModule:
     def launch(self, fn, pointers: list[int], grid: int, block: int, smem_bytes: int = 0, stream: int = 0) -> None:
         """Enqueue on `stream` (a CUstream handle; 0 = the NULL stream, which is what the reference's runner uses
         and what torch calls its default stream); does not synchronise."""
-        holders = [ctypes.c_uint64(p) for p in pointers]
+        # device pointers as integers; by-value scalar parameters as ctypes values (c_float, c_int32: emmyptx/kernel.py:171-178)
+        holders = [p if isinstance(p, ctypes._SimpleCData) else ctypes.c_uint64(p) for p in pointers]
         params = (ctypes.c_void_p * len(holders))(*[ctypes.cast(ctypes.byref(h), ctypes.c_void_p) for h in holders])
         self._check(self.cu.cuLaunchKernel(fn, grid, 1, 1, block, 1, 1, smem_bytes, ctypes.c_void_p(stream or None), params, None), "cuLaunchKernel")
 

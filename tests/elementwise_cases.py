@@ -128,3 +128,21 @@ BCAST_CASES = {
     "s_expand": ([("v", "V", ("c0",))], [("o", "add", ["v", 0.0])], {"V": [61]}, "np.broadcast_to(V, (33, 61)) + np.float32(0)"),
 }
 
+# By-value scalar parameters of a launch (emmyptx/kernel.py:166-183): id -> (inputs, steps, output dtype, scalars, integer program?)
+SCALAR_CASES = {
+    "sc_axpy2": ({"x": "f32", "y": "f32"}, [("ax", "multiply", ["x", "alpha"]), ("s", "add", ["ax", "y"]), ("o", "multiply", ["s", 2.0])], "f32",
+                 {"alpha": "f32"}, False),
+    "sc_imul": ({"a": "i32"}, [("t", "multiply", ["a", "k"]), ("o", "add", ["t", 7])], "i32", {"k": "s32"}, True),
+}
+
+
+def scalar_kernel(ir, case: str, n: int = 5000):
+    """(graph, kernel, launch) of a SCALAR_CASES entry, built with the given ir module."""
+    ins, steps, out_dt, scalars, integer = SCALAR_CASES[case]
+    built = ir.elementwise_kernel(n, ins, steps, out_dtype=out_dt, scalars=scalars, name=case)
+    if integer:
+        for st in built[1].body[0].body:
+            if type(st).__name__ == "Assign":
+                st.dtype = "i32"
+    return built
+

@@ -223,6 +223,8 @@ for case, (steps, in_dt, out_dt, ins) in elementwise_cases.INT_CASES.items():
     ELEMENTWISE[f"ew_{case}"] = ir.int_elementwise_kernel(4096, steps, in_dt, out_dt, ins, name=f"ew_{case}")
 for case, (loads, steps, ins, _expr) in elementwise_cases.BCAST_CASES.items():
     ELEMENTWISE[f"bc_{case}"] = ir.broadcast_kernel(*elementwise_cases.BCAST_SHAPE, loads, steps, ins, name=f"bc_{case}")
+for case in elementwise_cases.SCALAR_CASES:
+    ELEMENTWISE[case] = elementwise_cases.scalar_kernel(ir, case)
 ELEMENTWISE["ew_d_bool_in"] = ir.elementwise_kernel(4096, *elementwise_cases.BOOL_IN, name="ew_d_bool_in")
 CASES.update(ELEMENTWISE)
 

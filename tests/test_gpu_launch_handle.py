@@ -175,3 +175,37 @@ def test_guarded_read_handle(cuda, lib):
     assert launch(lib, handle_text(ir.layout_kernel("s_cat_cond")), [a, b, out]) == 0
     assert torch.equal(out, torch.cat([a, b], -1))
 
+
+@pytest.mark.parametrize("case,value", [("sc_axpy2", 0.5), ("sc_axpy2", -3.25), ("sc_imul", -11)])
+def test_scalar_parameters_against_the_reference_kernel(case, value, cuda, lib):
+    """The reference's PTX for the same IR takes the scalar as a `.param .f32` / `.param .s32` in the same position of the
+    argument list; this library's handle takes it through `emmyb200_launch`. Same buffers, same value: the integer
+    program bit for bit, the float one to one rounding (the driver's JIT contracts the reference's multiply and add)."""
+    import ctypes as ct
+    from pathlib import Path
+    import torch
+    from emmyptx import ir
+    from emmyptx.ptx_driver import PtxModule
+    from elementwise_cases import SCALAR_CASES, scalar_kernel
+    golden = Path(__file__).resolve().parent / "golden"
+    built = scalar_kernel(ir, case)
+    manifest = json.loads((golden / "reference_ptx_manifest.json").read_text())[case]
+    assert built[2]["arg_order"] == manifest["launch"]["arg_order"]
+    ins, _steps, out_dt, scalars, integer = SCALAR_CASES[case]
+    n = 5000
+    g = torch.Generator().manual_seed(0)
+    bufs = [(torch.randint(-1000, 1000, (n,), dtype=torch.int32, generator=g) if integer else torch.randn(n, generator=g)).to(cuda) for _ in ins]
+    tdt = torch.int32 if integer else torch.float32
+    ours, theirs = torch.zeros(n, dtype=tdt, device=cuda), torch.zeros(n, dtype=tdt, device=cuda)
+    scalar = ct.c_int32(value) if integer else ct.c_float(value)
+    assert launch(lib, handle_text(built), [*bufs, ours, scalar]) == 0
+    launch_d = built[2]
+    with PtxModule((golden / f"{case}.ref.ptx").read_text()) as m:
+        m.launch(m.function(case), [*[b.data_ptr() for b in bufs], theirs.data_ptr(), scalar], launch_d["grid"][0], launch_d["block"][0])
+        m.synchronize()
+    torch.cuda.synchronize()
+    if integer:
+        assert torch.equal(ours, theirs) and torch.equal(ours.cpu(), bufs[0].cpu() * value + 7)
+    else:
+        assert torch.allclose(ours, theirs, rtol=1e-6, atol=1e-6)
+
