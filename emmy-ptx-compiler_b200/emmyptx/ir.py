@@ -747,6 +747,12 @@ def layout_kernel(case: str, name: str | None = None):
                              [Load(["a"], "A", [Var("r0"), Var("c0")]), Write("out", [Var("r0"), Var("c0")], ["a"])],
                              [Load(["b"], "B", [Var("r0"), sub(Var("c0"), lit(64))]), Write("out", [Var("r0"), Var("c0")], ["b"])])],
                        [32, 112], None, None),
+        # F.pad(x, (3, 3)) as a Cond: inside the window the shifted element, zero in the border
+        "s_pad_cond": ([A("r0", 8), A("c0", 70)], {"X": [8, 64]}, [],
+                       [Cond(BinaryExpr("&&", BinaryExpr(">=", Var("c0"), lit(3)), BinaryExpr("<", Var("c0"), lit(67))),
+                             [Load(["x"], "X", [Var("r0"), sub(Var("c0"), lit(3))]), Write("out", [Var("r0"), Var("c0")], ["x"])],
+                             [Write("out", [Var("r0"), Var("c0")], [0.0])])],
+                       [8, 70], None, None),
         # a rotation: the index wraps around along one axis
         "s_roll": ([A("r0", 64), A("c0", 128)], {"X": [64, 128]}, [("x", "X", [Var("r0"), BinaryExpr("%", add(Var("c0"), lit(125)), lit(128))])], [],
                    [64, 128], [Var("r0"), Var("c0")], "x"),

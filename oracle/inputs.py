@@ -88,7 +88,7 @@ def seeded_buffers(tensors: dict, arg_order: list) -> dict:
 LAYOUT_EXPECTED = {     # what each data-movement case computes, on the buffers of layout_buffers (numpy, exact)
     "s_transpose": lambda b: b["X"].T, "s_permute": lambda b: b["X"].transpose(2, 0, 1) * np.float32(2), "s_slice": lambda b: b["X"][:, 10:50] * np.float32(2),
     "s_strided_slice": lambda b: b["X"][::2] + np.float32(1), "s_flip": lambda b: b["X"][:, ::-1], "s_stack": lambda b: np.stack([b["A"], b["B"]]),
-    "s_cat_cond": lambda b: np.concatenate([b["A"], b["B"]], -1),
+    "s_cat_cond": lambda b: np.concatenate([b["A"], b["B"]], -1), "s_pad_cond": lambda b: np.pad(b["X"], ((0, 0), (3, 3))),
     "s_tril": lambda b: np.tril(b["X"]), "s_tril_select": lambda b: np.tril(b["X"]),
     "s_window_let": lambda b: np.where((np.arange(128) >= 3) & (np.arange(128) < 120), b["X"], np.float32(0)) * np.float32(2), "s_repeat": lambda b: np.tile(b["X"], (2, 1)),
     "s_roll": lambda b: np.roll(b["X"], 3, -1), "s_embedding": lambda b: b["SRC"][np.abs(b["IDX"]) % 100],

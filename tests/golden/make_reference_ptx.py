@@ -183,7 +183,7 @@ for name, (units, sq, sk, d, causal, scale, dtype) in ATTENTION16.items():
     CASES[name] = (graph, kernel, launch)
 
 LAYOUT = ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_stack", "s_tril", "s_cat_a", "s_cat_b",      # shapes.py:6-19
-          "s_roll", "s_embedding", "s_gather", "s_tril_select", "s_window_let", "s_cat_cond",
+          "s_roll", "s_embedding", "s_gather", "s_tril_select", "s_window_let", "s_cat_cond", "s_pad_cond",
           "c_avg_pool1d", "c_max_pool2d"]                                                                              # conv.py:8-9
 for name in LAYOUT:
     graph, kernel, launch = ir.layout_kernel(name, name=name)

@@ -170,7 +170,7 @@ def test_f32_output_gemm_fixture(golden, case):
 
 
 @pytest.mark.parametrize("case", ["s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_stack", "s_tril", "s_cat_a", "s_cat_b",
-                                  "s_roll", "s_embedding", "s_gather", "c_avg_pool1d", "c_max_pool2d", "s_tril_select", "s_window_let", "s_cat_cond"])
+                                  "s_roll", "s_embedding", "s_gather", "c_avg_pool1d", "c_max_pool2d", "s_tril_select", "s_window_let", "s_cat_cond", "s_pad_cond"])
 def test_layout_fixture_is_what_numpy_computes(golden, case):
     """The reference's PTX for the data-movement kernels, executed on the CPU, moves exactly the elements the torch
     expression of the case moves (tools/torch_cases/shapes.py:6-19)."""

@@ -74,7 +74,7 @@ def accepted_cases(ir):
     yield "t_causal_sdpa", ir.attention_scalar_kernel([1, 4], 128, 128, 64, causal=True)
     yield "f_masked_attn_manual", ir.attention_scalar_kernel([1], 64, 64, 32, scale=0.17677669, causal=True)
     for case in ("s_transpose", "s_permute", "s_slice", "s_strided_slice", "s_flip", "s_repeat", "s_stack", "s_tril", "s_cat_a", "s_cat_b", "s_roll",
-                 "s_embedding", "s_gather", "c_avg_pool1d", "c_max_pool2d", "s_tril_select", "s_window_let", "s_cat_cond"):
+                 "s_embedding", "s_gather", "c_avg_pool1d", "c_max_pool2d", "s_tril_select", "s_window_let", "s_cat_cond", "s_pad_cond"):
         yield case, ir.layout_kernel(case)
     for case in ("c_conv1d", "c_conv2d"):
         yield case, ir.conv_kernel(case)
