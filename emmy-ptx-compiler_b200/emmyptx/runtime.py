@@ -465,11 +465,15 @@ class HostGemm:
     in and being multiplied, so that a call costs about as long as the larger of its host-to-device copies and its
     arithmetic instead of their sum. Device buffers are allocated once, in the constructor."""
 
-    def __init__(self, m: int, n: int, k: int, dtype, device, epilogue: str | None = None, chunks: int = 16):
+    def __init__(self, m: int, n: int, k: int, dtype, device, epilogue: str | None = None, chunks: int = 8, overlap_calls: bool = True):
+        """`overlap_calls`: the copy-in of a call starts as soon as the previous call's last product has been computed,
+        while that call's last rows are still on their way back to the host (the host link carries both directions at
+        once); the host inputs must then be ready when the call is made, not merely ordered after earlier work on `stream`."""
         import torch
         while chunks > 1 and (m % chunks or (m // chunks) % 128):
             chunks -= 1                                                        # whole row blocks per chunk
         self.m, self.n, self.k, self.epilogue, self.chunks, self.rows = m, n, k, epilogue, chunks, m // chunks
+        self.overlap_calls, self.called = overlap_calls, False
         self.a = torch.empty(m, k, dtype=dtype, device=device)
         self.b = torch.empty(k, n, dtype=dtype, device=device)
         self.c = torch.empty(m, n, dtype=dtype, device=device)
@@ -481,8 +485,12 @@ class HostGemm:
         """Enqueue the whole call; `c_host` is complete when `stream` (default: the current one) has caught up."""
         import torch
         main = torch.cuda.current_stream() if stream is None else stream
-        self.copy_in.wait_stream(main)                                         # the buffers may still be in use by earlier work
+        if self.overlap_calls and self.called:
+            self.copy_in.wait_event(self.ev_done[-1])                          # the previous call's products have read A and B
+        else:
+            self.copy_in.wait_stream(main)                                     # the buffers may still be in use by earlier work
         self.copy_out.wait_stream(main)
+        self.called = True
         with torch.cuda.stream(self.copy_in):
             self.b.copy_(b_host, non_blocking=True)
             self.ev_in[0].record()

@@ -209,6 +209,18 @@ def test_host_buffer_call_overlaps_copies_and_matches_the_device_call(cuda):
     torch.cuda.synchronize()
     expect = runtime.gemm(a.to(cuda), b.to(cuda), epilogue="gelu_tanh").cpu()
     assert torch.equal(c_h, expect)
+    # back-to-back calls on different host buffers: the second call's copy-in overlaps the first one's copy-back
+    a2, b2 = (x.flip(0).contiguous().pin_memory() for x in (a, b))
+    c2 = torch.zeros(m, n, dtype=torch.bfloat16).pin_memory()
+    for overlap in (True, False):
+        call = runtime.HostGemm(m, n, k, torch.bfloat16, cuda, epilogue="gelu_tanh", chunks=4, overlap_calls=overlap)
+        c_h.zero_(), c2.zero_()
+        call(a_h, b_h, c_h)
+        call(a2, b2, c2)
+        call(a_h, b_h, c_h)
+        torch.cuda.synchronize()
+        assert torch.equal(c_h, expect)
+        assert torch.equal(c2, runtime.gemm(a2.to(cuda), b2.to(cuda), epilogue="gelu_tanh").cpu())
     assert runtime.HostGemm(300, 64, 64, torch.bfloat16, cuda, chunks=8).chunks == 1     # no whole-block split: one chunk
 
 
