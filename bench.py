@@ -1032,6 +1032,31 @@ def measure(torch, dist, world, local_rank, wl, steps: int, warmup: int, pk, pk_
             "parity": parity, "device_status": status}
 
 
+def bind_to_gpu_cpus(torch, local_rank: int):
+    """Run this rank on the CPUs next to its GPU (NVML's CPU affinity of the device, found by PCI address), so that the
+    pinned host buffers it allocates and fills afterwards are first touched on that GPU's NUMA node: with several ranks
+    copying at once, host memory on the wrong node is what the host link waits for. Only this process's affinity is set.
+    Returns the CPU list, or None when NVML is not there, the mask is empty or EMMYB200_BENCH_AFFINITY=0."""
+    if os.environ.get("EMMYB200_BENCH_AFFINITY", "1") == "0" or not hasattr(os, "sched_setaffinity"):
+        return None
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        p = torch.cuda.get_device_properties(local_rank)
+        handle = pynvml.nvmlDeviceGetHandleByPciBusId(f"{p.pci_domain_id:08x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0".encode())
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = [64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1]
+        allowed = set(os.sched_getaffinity(0))
+        cpus = [c for c in cpus if c in allowed]
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return cpus
+    except Exception:  # noqa: BLE001 - a missing NVML binding or an odd topology must not stop the bench
+        return None
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1057,6 +1082,7 @@ def main() -> int:
         raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    cpus = bind_to_gpu_cpus(torch, local_rank) if world > 1 else None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -1083,6 +1109,7 @@ def main() -> int:
         "collective": "none" if world == 1 else getattr(wl, "collective", "nccl all_gather of the output shards"),
         "roofline": m["roofline"], "e2e": m["e2e"], "parity": m["parity"], "gpu_launches": m["launches"], "clocks": m["clocks"],
         "device_status": m["device_status"],
+        "cpu_affinity": None if cpus is None else f"{len(cpus)} CPUs next to the GPU (rank 0: {cpus[0]}..{cpus[-1]})",
         "step_definition": f"one pass of the workload; the timed region is steps x inner_repeats = {args.steps * m['inner_repeats']} passes, "
                            "ms_per_step and value are per pass",
     }
