@@ -616,11 +616,13 @@ template <typename I> __device__ __forceinline__ void pw_ix_tiles(const void* p0
         if (a != PW_RAXIS && a != PW_WAXIS) batch *= (I)m.extent[a];
     const i64 work = (i64)batch * tiles_r * tiles_w;
     const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
-    for (i64 w = blockIdx.x; w < work; w += gridDim.x) {
+    I d[PW_NAXES > 0 ? PW_NAXES : 1];
+    I at = 0, to = 0, r0 = 0, w0 = 0;
+    // where tile w starts: the digits of the other axes, the bases of both maps, the tile's corner
+    auto origin = [&](i64 w) {
         I rem = (I)w;
         const I tw = rem % tiles_w; rem /= tiles_w;
         const I tr = rem % tiles_r; rem /= tiles_r;
-        I d[PW_NAXES > 0 ? PW_NAXES : 1];
 #pragma unroll
         for (int a = PW_NAXES - 1; a >= 0; --a) {
             if (a == PW_RAXIS || a == PW_WAXIS) { d[a] = 0; continue; }
@@ -629,15 +631,18 @@ template <typename I> __device__ __forceinline__ void pw_ix_tiles(const void* p0
             d[a] = rem - q * e;
             rem = q;
         }
-        I at = (I)m.in_offset[PW_TIN], to = (I)m.out_offset;
+        at = (I)m.in_offset[PW_TIN];
+        to = (I)m.out_offset;
 #pragma unroll
         for (int a = 0; a < PW_NAXES; ++a) {
             at += (I)m.in_coef[PW_TIN][a] * d[a];
             to += (I)m.out_coef[a] * d[a];
         }
-        const I r0 = tr * PW_TT, w0 = tw * PW_TT;
-        __syncthreads();                                        // the previous tile has been read out
-        PW_T got[PW_TT / 8][PW_TT / 32];                        // every load of the tile is issued before the first shared store
+        r0 = tr * PW_TT;
+        w0 = tw * PW_TT;
+    };
+    PW_T got[PW_TT / 8][PW_TT / 32];
+    auto fetch = [&]() {                                        // every load of a tile is issued before anything uses one
 #pragma unroll
         for (int k = 0; k < PW_TT / 8; ++k)
 #pragma unroll
@@ -645,24 +650,35 @@ template <typename I> __device__ __forceinline__ void pw_ix_tiles(const void* p0
                 const I r = r0 + x + 32 * q, v = w0 + y + 8 * k;
                 got[k][q] = (r < er && v < ew) ? pw_ld1<PW_TDT>(src, (i64)(at + r + (I)m.in_coef[PW_TIN][PW_WAXIS] * v)) : (PW_T)0;
             }
+    };
+    i64 w = blockIdx.x;
+    if (w < work) { origin(w); fetch(); }
+    for (; w < work; w += gridDim.x) {
+        __syncthreads();                                        // the previous tile has been read out
 #pragma unroll
         for (int k = 0; k < PW_TT / 8; ++k)
 #pragma unroll
             for (int q = 0; q < PW_TT / 32; ++q) tile[y + 8 * k][x + 32 * q] = got[k][q];
         __syncthreads();
+        // this tile's corner and bases for the store phase; then the next tile's loads go out and fly during the stores
+        const I s_to = to, s_r0 = r0, s_w0 = w0;
+        I sd[PW_NAXES > 0 ? PW_NAXES : 1];
+#pragma unroll
+        for (int a = 0; a < PW_NAXES; ++a) sd[a] = d[a];
+        if (w + gridDim.x < work) { origin(w + gridDim.x); fetch(); }
 #pragma unroll
         for (int kq = 0; kq < (PW_TT / 8) * (PW_TT / 32); ++kq) {
             const int k = kq / (PW_TT / 32), q = kq % (PW_TT / 32);
-            const I v = w0 + x + 32 * q, r = r0 + y + 8 * k;
+            const I v = s_w0 + x + 32 * q, r = s_r0 + y + 8 * k;
             if (r < er && v < ew) {
-                d[PW_RAXIS] = r;
-                d[PW_WAXIS] = v;
+                sd[PW_RAXIS] = r;
+                sd[PW_WAXIS] = v;
                 const PW_T val = tile[x + 32 * q][y + 8 * k];
-                const PW_T v0 = PW_KIND0 ? (PW_T)d[m.in_axis[0]] : val;
-                const PW_T v1 = PW_N_IN > 1 ? (PW_KIND1 ? (PW_T)d[m.in_axis[1]] : val) : (PW_T)0;
-                const PW_T v2 = PW_N_IN > 2 ? (PW_KIND2 ? (PW_T)d[m.in_axis[2]] : val) : (PW_T)0;
-                const PW_T v3 = PW_N_IN > 3 ? (PW_KIND3 ? (PW_T)d[m.in_axis[3]] : val) : (PW_T)0;
-                pw_st1(out, (i64)(to + (I)m.out_coef[PW_RAXIS] * r + v), pw_cell(v0, v1, v2, v3, c));
+                const PW_T v0 = PW_KIND0 ? (PW_T)sd[m.in_axis[0]] : val;
+                const PW_T v1 = PW_N_IN > 1 ? (PW_KIND1 ? (PW_T)sd[m.in_axis[1]] : val) : (PW_T)0;
+                const PW_T v2 = PW_N_IN > 2 ? (PW_KIND2 ? (PW_T)sd[m.in_axis[2]] : val) : (PW_T)0;
+                const PW_T v3 = PW_N_IN > 3 ? (PW_KIND3 ? (PW_T)sd[m.in_axis[3]] : val) : (PW_T)0;
+                pw_st1(out, (i64)(s_to + (I)m.out_coef[PW_RAXIS] * r + v), pw_cell(v0, v1, v2, v3, c));
             }
         }
     }
