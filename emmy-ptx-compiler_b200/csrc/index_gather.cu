@@ -101,16 +101,25 @@ __global__ void __launch_bounds__(NT) gather_tiled_kernel(GatherParams p) {
         // Full block away from the matrix's short last row: every load is issued before the first
         // shared-memory store, so a warp keeps TU/8 * TV/32 independent loads in flight.
         int32_t vals[TU / kWarps][TV / 32];
+        if constexpr (POW2) {
+            // n divides 2^32: the running index may wrap a uint32 freely and is reduced by one mask per load
+            const uint32_t j0 = j_base + lane;
 #pragma unroll
-        for (int k = 0; k < TU / kWarps; ++k) {
+            for (int k = 0; k < TU / kWarps; ++k)
 #pragma unroll
-            for (int c = 0; c < TV / 32; ++c) {
-                uint32_t j = j_base + lane + 32 * c;
-                if (j >= n) j -= n;
-                vals[k][c] = __ldg(p.x + j);
+                for (int c = 0; c < TV / 32; ++c) vals[k][c] = __ldg(p.x + ((j0 + (uint32_t)k * step + 32u * c) & (n - 1)));
+        } else {
+#pragma unroll
+            for (int k = 0; k < TU / kWarps; ++k) {
+#pragma unroll
+                for (int c = 0; c < TV / 32; ++c) {
+                    uint32_t j = j_base + lane + 32 * c;
+                    if (j >= n) j -= n;
+                    vals[k][c] = __ldg(p.x + j);
+                }
+                j_base += step;
+                if (j_base >= n) j_base -= n;
             }
-            j_base += step;
-            if (j_base >= n) j_base -= n;
         }
 #pragma unroll
         for (int k = 0; k < TU / kWarps; ++k)
@@ -142,7 +151,8 @@ __global__ void __launch_bounds__(NT) gather_tiled_kernel(GatherParams p) {
 #pragma unroll
             for (int r = 0; r < TU / 32; ++r) {
                 uint32_t i = i_base + 32 * r;
-                if (i >= n) i -= n;
+                if constexpr (POW2) i &= n - 1;
+                else if (i >= n) i -= n;
                 p.y[i] = div_const<TRUNC, DIV1>(tile[lane + 32 * r][c], p.dc) ^ (int32_t)(i >> p.shift);
             }
         }
