@@ -437,8 +437,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 //   warps 12-15  output: normalise O_i by the row sums, stage it in shared memory and store it (TMA, or multimem.st
 //              for a multicast destination) while the MMA warp is already working on the next pair of tiles.
 // Work items (unit, pair of query tiles) are dealt round-robin. With the causal flag a pair's cost grows with its
-// position, so a CTA takes pairs two at a time, the k-th longest together with the k-th shortest of the same unit:
-// every such couple costs the same, and the static deal stays balanced. Every wait is bounded; the groups meet only
+// position, so the pairs of all units are dealt longest first in rounds that alternate direction (pair_item): the
+// static deal stays balanced to within a few key tiles per CTA. Every wait is bounded; the groups meet only
 // through mbarriers (no bar.sync inside the role loops), so a wait that gives up cannot strand another warp.
 constexpr int kPairThreads = 512;
 constexpr int kKvStages = 4;
@@ -479,13 +479,15 @@ __device__ __forceinline__ bool pair_item(const AttParams& p, int it, PairItem& 
         unit = (int)(t / q_pairs);
         pr = (int)(t % q_pairs);
     } else {
-        const int couples = (q_pairs + 1) >> 1;                         // per unit
-        const long long s = (long long)blockIdx.x + (long long)(it >> 1) * gridDim.x;
-        if (s >= (long long)p.units * couples) return false;
-        unit = (int)(s / couples);
-        const int k = (int)(s % couples);
-        pr = (it & 1) ? k : q_pairs - 1 - k;                            // the long one first
-        if ((it & 1) && k == q_pairs - 1 - k) { w.unit = unit; w.row0 = 0; w.n[0] = w.n[1] = 0; return true; }   // odd count: the middle pair stands alone
+        // Pairs of every unit sorted by length, longest first (pair pr walks 2 pr + 2 key tiles), dealt in rounds of
+        // gridDim.x that alternate direction: after every two rounds the CTAs' sums differ by at most one step of the
+        // length, and the last, partial round holds the shortest pairs.
+        const long long total = (long long)p.units * q_pairs;
+        const long long pos = (it & 1) ? (long long)gridDim.x - 1 - blockIdx.x : (long long)blockIdx.x;
+        const long long t = (long long)it * gridDim.x + pos;
+        if (t >= total) return false;
+        unit = (int)(t % p.units);
+        pr = q_pairs - 1 - (int)(t / p.units);
     }
     const int kv_all = (p.seq_k + kTileK - 1) / kTileK;
     w.unit = unit;
@@ -961,7 +963,7 @@ static int launch_attention(const void* Q, const void* K, const void* V, void* c
     // Which form. Measured over units x sequence length x head size, with and without the causal flag (bf16, both forms
     // forced in the same run): the two-tile form is 2-34 % faster once a unit has eight or more key tiles and there is
     // at least one pair of query tiles per SM (its persistent CTAs walk the keys once for two tiles, and with the causal
-    // flag its couples of long and short pairs keep every SM busy to the end); for short sequences or few work items the
+    // flag its sorted, alternating deal of the pairs keeps every SM busy to the end); for short sequences or few work items the
     // one-tile form, with twice as many and smaller work items, is 1-67 % faster. A flag overrides the choice.
     const int64_t pair_items = units * ((p.q_tiles + 1) / 2);
     const bool two_tiles = (form_flags & EMMYB200_ATT_FORM_TWO_TILES) ? true
@@ -971,7 +973,7 @@ static int launch_attention(const void* Q, const void* K, const void* V, void* c
         auto pair_kernel = attention_fwd_pair_kernel<D, BF16>;
         EMMY_CUDA(cudaFuncSetAttribute(pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kTotal));
         const int64_t q_pairs = (p.q_tiles + 1) / 2;
-        const int64_t deals = causal ? units * ((q_pairs + 1) / 2) : units * q_pairs;
+        const int64_t deals = units * q_pairs;
         const int grid = (int)(deals < sm_count() ? deals : sm_count());
         pair_kernel<<<grid, kPairThreads, P::kTotal, stream>>>(mq, mk, mv, out, p);
         return launch_status("attention_fwd_pair_kernel");
