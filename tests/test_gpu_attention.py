@@ -102,7 +102,9 @@ def test_rows_sum_property(cuda):
     assert (a.float() - b.float()).abs().max() <= 1e-2 * a.float().std() + 1e-2 * a.float().abs().max()
 
 
-@pytest.mark.parametrize("units,s,d", [(2, 256, 128), (3, 300, 128), (2, 64, 32 * 2), (1, 1000, 128), (2, 129, 64)])
+@pytest.mark.parametrize("units,s,d", [(2, 256, 128), (3, 300, 128), (2, 64, 32 * 2), (1, 1000, 128), (2, 129, 64),
+                                       (80, 512, 64),      # more pairs of tiles than SMs: a second, partial round of the deal
+                                       (60, 768, 128)])    # 180 pairs of three lengths
 @pytest.mark.parametrize("dtype", ["bf16", "f16"])
 @pytest.mark.parametrize("form", FORMS)
 def test_causal(units, s, d, dtype, form, cuda):
