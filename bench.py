@@ -728,7 +728,8 @@ class AttentionWorkload(Workload):
         t = self.torch
         self.host = {n: getattr(self, n).cpu().pin_memory() for n in "qkv"}
         self.host["o"] = t.empty_like(self.o, device="cpu").pin_memory()
-        return 3 * self.q.numel() * 2, self.o.numel() * 2
+        # bytes of the whole job, like `value`: every rank copies its own units
+        return 3 * self.q.numel() * 2 * self.world, self.o.numel() * 2 * self.world
 
     def e2e_step(self):
         for n in "qkv":
