@@ -967,6 +967,26 @@ def inner_repeats(torch, dist, world, fn, steps: int) -> int:
     return max(1, int(-(-MIN_REGION_S // max(probe * steps, 1e-9))))
 
 
+NVLINK_GBS = 770.0     # measured peer-copy rate of this pool's B200s, per direction per GPU (900 nominal)
+
+
+def fused_roofline(wl, world: int, ms_per_step: float, pk: dict):
+    """The bound of a sharded step whose kernel also gathers its output: the slower of the rank's flops at the measured
+    sustained tensor peak and the bytes every GPU must take in from its peers ((N-1)/N of the whole output) at the
+    measured peer-copy rate. `frac` is that target over the measured step (kernel, gather and group barrier)."""
+    if world <= 1 or not getattr(wl, "gather", False) or wl.bound != "tensor":
+        return None
+    out_bytes = (wl.m * wl.n if hasattr(wl, "m") else wl.units * wl.seq * wl.d) * 2
+    cross = out_bytes * (world - 1) / world
+    flops_ms = wl.kernel_work_per_launch() / (pk["bf16_tflops_sustained"] * 1e12) * 1e3
+    link_ms = cross / (NVLINK_GBS * 1e9) * 1e3
+    target = max(flops_ms, link_ms)
+    return {"bound": "tensor" if flops_ms >= link_ms else "nvlink", "flops_ms": flops_ms, "link_ms": link_ms,
+            "bytes_in_per_gpu": cross, "link_GBps": NVLINK_GBS, "target_ms": target, "frac": target / ms_per_step,
+            "note": "a multicast store also comes back to its sender, so through the multicast mapping every GPU takes in the whole "
+                    "output: a bare multicast copy of the shards on 8 GPUs takes in 715 GB/s per GPU"}
+
+
 def roofline_block(wl, k_ms: float, pk: dict, pk_kind: str, traffic, clocks: dict) -> dict:
     if wl.bound == "tensor":
         achieved = wl.kernel_work_per_launch() / (k_ms * 1e-3) / 1e12
@@ -1029,7 +1049,10 @@ def measure(torch, dist, world, local_rank, wl, steps: int, warmup: int, pk, pk_
             "clocks": clocks.summary(),
             "e2e": {"value": wl.work_per_step() / (e2e_ms * 1e-3) / scale, "unit": wl.unit, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps, "warmup": 3,
-                    "h2d_GBps_per_rank": h2d / max(world, 1) / (e2e_ms * 1e-3) / 1e9},
+                    "h2d_GBps_per_rank": h2d / max(world, 1) / (e2e_ms * 1e-3) / 1e9,
+                    "limiter": (f"host link: {(h2d + d2h) / (e2e_ms * 1e-3) / 1e9:.0f} GB/s over all ranks, both directions, next to "
+                                f"{ms_per_step:.3f} ms of device work per step") if e2e_ms > 1.3 * ms_per_step else "device work"},
+            "fused_roofline": fused_roofline(wl, world, ms_per_step, pk),
             "parity": parity, "device_status": status}
 
 
@@ -1109,7 +1132,7 @@ def main() -> int:
         "config": config_for(args.workload, world, args.size),
         "collective": "none" if world == 1 else getattr(wl, "collective", "nccl all_gather of the output shards"),
         "roofline": m["roofline"], "e2e": m["e2e"], "parity": m["parity"], "gpu_launches": m["launches"], "clocks": m["clocks"],
-        "device_status": m["device_status"],
+        "device_status": m["device_status"], "fused_roofline": m["fused_roofline"],
         "cpu_affinity": None if cpus is None else f"{len(cpus)} CPUs next to the GPU (rank 0: {cpus[0]}..{cpus[-1]})",
         "step_definition": f"one pass of the workload; the timed region is steps x inner_repeats = {args.steps * m['inner_repeats']} passes, "
                            "ms_per_step and value are per pass",
@@ -1124,7 +1147,7 @@ def main() -> int:
             line["other_workloads"] = {"c5": {"workload": WORKLOADS["c5"], "value": m5["value"], "unit": wl5.unit,
                                               "ms_per_step": m5["ms_per_step"], "kernel_ms": m5["roofline"]["kernel_ms"],
                                               "inner_repeats": m5["inner_repeats"], "collective": wl5.collective,
-                                              "roofline": m5["roofline"], "e2e": m5["e2e"], "parity": m5["parity"], "clocks": m5["clocks"],
+                                              "roofline": m5["roofline"], "fused_roofline": m5["fused_roofline"], "e2e": m5["e2e"], "parity": m5["parity"], "clocks": m5["clocks"],
                                               "config": config_for("c5", world)}}
             del wl5
         except Exception as e:  # noqa: BLE001 - must not hide the main line
